@@ -1,0 +1,266 @@
+"""Pins the CPU oracle: the reference's own known-answer tests, float64 finite
+differences (the reference's gradient-truth method, lib/LuxTestUtils/src/autodiff.jl:147-294)
+and an independent torch-CPU cross-check."""
+import math
+
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+from oracle import luxlib_oracle as O
+
+ACTS = ["identity", "relu", "gelu", "tanh", "sigmoid", "swish"]
+
+
+# ----------------------------------------------------------------------------
+# Known-answer tests held by the reference for this path
+# ----------------------------------------------------------------------------
+def test_kat_batchnorm_values_and_running_stats():
+    # test/core_layers/normalize_tests.jl:10-49
+    x = np.array([[1, 3, 5], [2, 4, 6]], dtype=np.float32)
+    g, b = np.ones(2, np.float32), np.zeros(2, np.float32)
+    rm, rv = np.zeros(2, np.float32), np.ones(2, np.float32)
+    y, (nrm, nrv) = O.batchnorm(x, g, b, rm, rv, True, "identity", 0.1, 1e-5)
+    np.testing.assert_allclose(y, [[-1.22474, 0, 1.22474], [-1.22474, 0, 1.22474]], atol=1e-5)
+    np.testing.assert_allclose(nrm, [0.3, 0.4], rtol=1e-6)
+    expect = 0.1 * x.var(axis=1) * (3 / 2) + 0.9
+    np.testing.assert_allclose(nrv, expect, rtol=1e-6)
+    np.testing.assert_allclose(nrv, [1.3, 1.3], rtol=1e-6)
+    yt, (rm2, rv2) = O.batchnorm(x, g, b, nrm, nrv, False, "identity", 0.1, 1e-5)
+    assert abs(yt[0, 0] - (1 - 0.3) / math.sqrt(1.3)) < 1e-5
+    assert rm2 is nrm and rv2 is nrv  # inference leaves the statistics untouched
+
+
+def test_kat_dense_ones():
+    # test/core_layers/basic_tests.jl:151-193
+    W1, W2 = np.ones((1, 10), np.float32), np.ones((2, 10), np.float32)
+    z1, z2 = np.zeros(1, np.float32), np.zeros(2, np.float32)
+    assert (O.fused_dense_bias_activation("identity", W1, np.ones((10, 1), np.float32), z1) == 10).all()
+    assert (O.fused_dense_bias_activation("identity", W1, np.ones((10, 2), np.float32), z1) == 10 * np.ones((1, 2))).all()
+    x = np.concatenate([np.ones((10, 1)), 2 * np.ones((10, 1))], axis=1).astype(np.float32)
+    assert (O.fused_dense_bias_activation("identity", W2, x, z2) == np.array([[10, 20], [10, 20]])).all()
+    assert (O.fused_dense_bias_activation("identity", W2, x, None) == np.array([[10, 20], [10, 20]])).all()
+
+
+def test_kat_conv_asymmetric_padding():
+    # test/core_layers/conv_tests.jl:53-69
+    x = np.ones((28, 28, 1, 1), np.float32)
+    w = np.ones((3, 3, 1, 1), np.float32)
+    cd = O.ConvDims.make(2, pad=(0, 1, 1, 2))
+    y = O.fused_conv_bias_activation("relu", w, x, np.zeros(1, np.float32), cd)[:, :, 0, 0]
+    assert y.shape == (27, 29)
+    assert y[0, 0] == 6 and y[1, 1] == 9 and y[-1, 0] == 4
+    assert y[0, -1] == 3 and y[0, -2] == 6 and y[-1, -1] == 2
+
+
+@pytest.mark.parametrize("k", [(3, 3), (3, 1), (1, 3)])
+def test_kat_conv_delta_image_reproduces_weight(k):
+    # test/core_layers/conv_tests.jl:145-190 — the default is a true convolution
+    rng = np.random.default_rng(0)
+    x = np.zeros((7, 7, 1, 1), np.float32)
+    x[3, 3, 0, 0] = 1
+    w = rng.standard_normal(k + (1, 1)).astype(np.float32)
+    y = O.conv(x, w, O.ConvDims.make(2))
+    expect = np.zeros((7 - k[0] + 1, 7 - k[1] + 1, 1, 1), np.float32)
+    r0 = slice(1, -1) if k[0] == 3 else slice(3, 4)
+    r1 = slice(1, -1) if k[1] == 3 else slice(3, 4)
+    expect[r0, r1, 0, 0] = w[:, :, 0, 0]
+    np.testing.assert_allclose(y, expect, atol=1e-6)
+
+
+def test_kat_layernorm_property():
+    # lib/LuxLib/test/normalization/layernorm_tests.jl:54-57: mean≈0, std≈1 without affine
+    rng = np.random.default_rng(1)
+    x = rng.standard_normal((4, 4, 6, 3)).astype(np.float32)
+    y = O.layernorm(x, None, None, "identity", dims=(0, 1, 2), eps=1e-5)
+    assert np.allclose(y.mean(axis=(0, 1, 2)), 0, atol=1e-3)
+    assert np.allclose(y.std(axis=(0, 1, 2)), 1, atol=1e-3)
+    with pytest.raises(ValueError):
+        O.layernorm(x, None, None, "identity", dims=None)
+    with pytest.raises(AssertionError):
+        O.layernorm(x[..., 0, 0], np.ones((4, 4), np.float32), np.ones((4, 4), np.float32), dims=None)
+
+
+def test_fixed_array_generator():
+    a = O.generate_fixed_array((2, 3))
+    np.testing.assert_allclose(a, np.array([[1, 3, 5], [2, 4, 6]]) / 6, rtol=1e-7)
+
+
+def test_default_epsilon():
+    assert abs(O.default_epsilon(np.float32) - 1.1337e-5) < 1e-8
+    assert abs(O.default_epsilon("bf16") - 0.03125) < 1e-9
+
+
+def test_round_bf16_matches_torch():
+    rng = np.random.default_rng(2)
+    a = (rng.standard_normal(10000) * 10 ** rng.uniform(-6, 6, 10000)).astype(np.float32)
+    ref = torch.from_numpy(a).to(torch.bfloat16).to(torch.float32).numpy()
+    assert (O.round_bf16(a) == ref).all()
+
+
+# ----------------------------------------------------------------------------
+# finite differences in float64
+# ----------------------------------------------------------------------------
+def _fd(f, x, h=1e-6):
+    g = np.zeros_like(x)
+    it = np.nditer(x, flags=["multi_index"])
+    for _ in it:
+        i = it.multi_index
+        old = x[i]
+        x[i] = old + h
+        fp = f()
+        x[i] = old - h
+        fm = f()
+        x[i] = old
+        g[i] = (fp - fm) / (2 * h)
+    return g
+
+
+@pytest.mark.parametrize("act", ACTS)
+@pytest.mark.parametrize("gelu", ["tanh", "erf"])
+def test_activation_derivative_fd(act, gelu):
+    if act != "gelu" and gelu == "erf":
+        pytest.skip("variant only matters for gelu")
+    x = np.linspace(-4, 4, 41) + 0.013
+    y = O.act_fn(act, x, gelu)
+    d = O.act_grad(act, y, x, gelu)
+    fd = (O.act_fn(act, x + 1e-6, gelu) - O.act_fn(act, x - 1e-6, gelu)) / 2e-6
+    np.testing.assert_allclose(d, fd, atol=1e-7, rtol=1e-6)
+
+
+@pytest.mark.parametrize("act", ACTS)
+def test_dense_rrule_fd(act):
+    rng = np.random.default_rng(3)
+    W, x, b = rng.standard_normal((4, 5)), rng.standard_normal((5, 3)), rng.standard_normal(4)
+    c = rng.standard_normal((4, 3))
+    y, pb = O.fused_dense_rrule(act, W, x, b)
+    dW, dx, db = pb(c)
+    loss = lambda: float((O.fused_dense_bias_activation(act, W, x, b) * c).sum())
+    np.testing.assert_allclose(dW, _fd(loss, W), atol=1e-6, rtol=1e-5)
+    np.testing.assert_allclose(dx, _fd(loss, x), atol=1e-6, rtol=1e-5)
+    np.testing.assert_allclose(db, _fd(loss, b), atol=1e-6, rtol=1e-5)
+
+
+CONV_CASES = [
+    # (spatial, k, cin, cout, stride, pad, dilation, groups, flip)  — shapes of lib/LuxLib/test/common_ops/conv_tests.jl:87-92
+    ((4, 4), (3, 3), 4, 8, 1, 0, 1, 1, False),
+    ((4, 4), (3, 3), 4, 8, 1, 0, 1, 2, False),
+    ((5, 4), (3, 3), 4, 8, 2, (1, 1), 1, 1, False),
+    ((6, 5), (3, 2), 2, 4, (2, 1), (0, 1, 1, 2), 1, 1, True),
+    ((7,), (3,), 2, 4, 1, 1, 2, 1, False),
+    ((4, 4, 3), (2, 2, 2), 2, 2, 1, 0, 1, 1, False),
+]
+
+
+@pytest.mark.parametrize("case", CONV_CASES)
+def test_conv_rrule_fd(case):
+    sp, k, cin, cout, stride, pad, dil, groups, flip = case
+    rng = np.random.default_rng(4)
+    nd = len(sp)
+    cd = O.ConvDims.make(nd, stride, pad, dil, groups, flip)
+    x = rng.standard_normal(sp + (cin, 2))
+    w = rng.standard_normal(k + (cin // groups, cout))
+    b = rng.standard_normal(cout)
+    y, pb = O.fused_conv_rrule("gelu", w, x, b, cd)
+    c = rng.standard_normal(y.shape)
+    dw, dx, db = pb(c)
+    loss = lambda: float((O.fused_conv_bias_activation("gelu", w, x, b, cd) * c).sum())
+    np.testing.assert_allclose(dw, _fd(loss, w), atol=1e-6, rtol=1e-5)
+    np.testing.assert_allclose(dx, _fd(loss, x), atol=1e-6, rtol=1e-5)
+    np.testing.assert_allclose(db, _fd(loss, b), atol=1e-6, rtol=1e-5)
+
+
+@pytest.mark.parametrize("act", ["identity", "relu", "swish"])
+@pytest.mark.parametrize("affine", [True, False])
+def test_batchnorm_rrule_fd(act, affine):
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((3, 2, 4, 3)) + 0.3
+    g = rng.uniform(0.5, 1.5, 4) if affine else None
+    b = rng.standard_normal(4) if affine else None
+    rm, rv = np.zeros(4), np.ones(4)
+    z, stats, pb = O.batchnorm_rrule(x, g, b, rm, rv, True, act, 0.1, 1e-5)
+    c = rng.standard_normal(z.shape)
+    dx, dg, db = pb(c)
+    loss = lambda: float((O.batchnorm(x, g, b, rm, rv, True, act, 0.1, 1e-5)[0] * c).sum())
+    np.testing.assert_allclose(dx, _fd(loss, x), atol=1e-6, rtol=1e-4)
+    if affine:
+        np.testing.assert_allclose(dg, _fd(loss, g), atol=1e-6, rtol=1e-5)
+        np.testing.assert_allclose(db, _fd(loss, b), atol=1e-6, rtol=1e-5)
+
+
+@pytest.mark.parametrize("shape,groups", [((6, 2), 2), ((4, 4, 6, 2), 3), ((2, 2, 6, 2), 2)])
+@pytest.mark.parametrize("act", ["identity", "gelu"])
+def test_groupnorm_rrule_fd(shape, groups, act):
+    # shapes of lib/LuxLib/test/normalization/groupnorm_tests.jl:100
+    rng = np.random.default_rng(6)
+    x = rng.standard_normal(shape)
+    g, b = rng.uniform(0.5, 1.5, shape[-2]), rng.standard_normal(shape[-2])
+    z, pb = O.groupnorm_rrule(x, g, b, groups, act, 1e-5)
+    c = rng.standard_normal(z.shape)
+    dx, dg, db = pb(c)
+    loss = lambda: float((O.groupnorm(x, g, b, groups, act, 1e-5) * c).sum())
+    np.testing.assert_allclose(dx, _fd(loss, x), atol=1e-6, rtol=1e-4)
+    np.testing.assert_allclose(dg, _fd(loss, g), atol=1e-6, rtol=1e-5)
+    np.testing.assert_allclose(db, _fd(loss, b), atol=1e-6, rtol=1e-5)
+
+
+@pytest.mark.parametrize("act", ["identity", "tanh"])
+def test_layernorm_rrule_fd(act):
+    rng = np.random.default_rng(7)
+    x = rng.standard_normal((5, 3, 4))
+    g, b = rng.uniform(0.5, 1.5, (5, 3)), rng.standard_normal((5, 3))
+    z, pb = O.layernorm_rrule(x, g, b, act, None, 1e-5)
+    c = rng.standard_normal(z.shape)
+    dx, dg, db = pb(c)
+    loss = lambda: float((O.layernorm(x, g, b, act, None, 1e-5) * c).sum())
+    np.testing.assert_allclose(dx, _fd(loss, x), atol=1e-6, rtol=1e-4)
+    np.testing.assert_allclose(dg, _fd(loss, g), atol=1e-6, rtol=1e-5)
+    np.testing.assert_allclose(db, _fd(loss, b), atol=1e-6, rtol=1e-5)
+
+
+# ----------------------------------------------------------------------------
+# independent cross-check against torch CPU (stand-in for the vendor libraries
+# the reference's GPU path would call)
+# ----------------------------------------------------------------------------
+def _to_torch_nchw(a):  # Julia (W,H,C,N) -> torch (N,C,H,W)
+    return torch.from_numpy(np.ascontiguousarray(a.transpose(tuple(reversed(range(a.ndim))))))
+
+
+def test_conv_matches_torch_cross_correlation_and_flip():
+    rng = np.random.default_rng(8)
+    x = rng.standard_normal((9, 8, 4, 2))
+    w = rng.standard_normal((3, 3, 2, 6))
+    xt, wt = _to_torch_nchw(x), _to_torch_nchw(w)  # weight -> (Cout, Cin/g, kH, kW)
+    ref = F.conv2d(xt, wt, stride=(1, 2), padding=(1, 0), groups=2)  # torch order: (H, W)
+    cd = O.ConvDims.make(2, stride=(2, 1), pad=(0, 0, 1, 1), groups=2, flipkernel=True)
+    np.testing.assert_allclose(_to_torch_nchw(O.conv(x, w, cd)).numpy(), ref.numpy(), atol=1e-10)
+    cd2 = O.ConvDims.make(2, stride=(2, 1), pad=(0, 0, 1, 1), groups=2, flipkernel=False)
+    ref2 = F.conv2d(xt, torch.flip(wt, dims=(2, 3)), stride=(1, 2), padding=(1, 0), groups=2)
+    np.testing.assert_allclose(_to_torch_nchw(O.conv(x, w, cd2)).numpy(), ref2.numpy(), atol=1e-10)
+
+
+def test_norms_match_torch():
+    rng = np.random.default_rng(9)
+    x = rng.standard_normal((5, 4, 6, 3))
+    g, b = rng.uniform(0.5, 1.5, 6), rng.standard_normal(6)
+    xt = _to_torch_nchw(x)
+    ref = F.group_norm(xt, 3, torch.from_numpy(g), torch.from_numpy(b), eps=1e-5)
+    np.testing.assert_allclose(_to_torch_nchw(O.groupnorm(x, g, b, 3, "identity", 1e-5)).numpy(), ref.numpy(), atol=1e-10)
+    rm, rv = torch.zeros(6, dtype=torch.float64), torch.ones(6, dtype=torch.float64)
+    ref = F.batch_norm(xt, rm, rv, torch.from_numpy(g), torch.from_numpy(b), training=True, momentum=0.1, eps=1e-5)
+    y, (nrm, nrv) = O.batchnorm(x, g, b, np.zeros(6), np.ones(6), True, "identity", 0.1, 1e-5)
+    np.testing.assert_allclose(_to_torch_nchw(y).numpy(), ref.numpy(), atol=1e-10)
+    np.testing.assert_allclose(nrm, rm.numpy(), atol=1e-12)
+    np.testing.assert_allclose(nrv, rv.numpy(), atol=1e-12)
+    x2 = rng.standard_normal((16, 7))
+    g2, b2 = rng.uniform(0.5, 1.5, 16), rng.standard_normal(16)
+    ref = F.layer_norm(torch.from_numpy(x2.T.copy()), (16,), torch.from_numpy(g2), torch.from_numpy(b2), 1e-5)
+    np.testing.assert_allclose(O.layernorm(x2, g2, b2, "identity", None, 1e-5).T, ref.numpy(), atol=1e-10)
+
+
+def test_gelu_variants_match_torch():
+    x = np.linspace(-5, 5, 101)
+    np.testing.assert_allclose(O.act_fn("gelu", x, "tanh"), F.gelu(torch.from_numpy(x), approximate="tanh").numpy(), atol=1e-12)
+    np.testing.assert_allclose(O.act_fn("gelu", x, "erf"), F.gelu(torch.from_numpy(x)).numpy(), atol=1e-12)
+    np.testing.assert_allclose(O.act_fn("swish", x), F.silu(torch.from_numpy(x)).numpy(), atol=1e-12)
