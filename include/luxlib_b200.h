@@ -1,0 +1,220 @@
+/*
+ * luxlib_b200.h — C ABI of libluxlib_b200.so: hand-written sm_100a kernels for LuxLib's
+ * fused layer hot path (dense / conv / batch-, group-, layer-norm, bias+activation) and
+ * their reverse-mode rules.
+ *
+ * Conventions (all entry points):
+ *   - Every array is a raw DEVICE pointer to Julia column-major storage. "ld*" arguments are
+ *     leading dimensions in elements.
+ *   - `dtype` selects the storage type of every tensor argument of the call (LB2_F32 or
+ *     LB2_BF16); accumulation is always fp32. Per-channel statistics (save_mean, save_invstd)
+ *     and workspaces are always fp32.
+ *   - Work is enqueued asynchronously on `stream` (a cudaStream_t passed as void*); the library
+ *     never synchronises the device, never allocates device memory, never falls back to a
+ *     vendor library or to the CPU. Scratch memory is supplied by the caller (`workspace`,
+ *     `workspace_bytes`; sizes from the lb2_*_workspace_bytes queries, which are upper bounds
+ *     that depend only on the listed extents). A workspace must be 256-byte aligned.
+ *   - Return value: 0 (LB2_OK) or a negative lb2_status. Nothing is launched when an error is
+ *     returned. Zero-sized problems return LB2_OK without launching
+ *     (lib/LuxLib/test/common_ops/bias_act_tests.jl:119-131).
+ *   - Re-entrant; the current CUDA device of the calling thread is used.
+ *
+ * Each declaration cites the reference interface (path inside LuxDL/Lux.jl) it replaces.
+ */
+#ifndef LUXLIB_B200_H
+#define LUXLIB_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define LB2_API __attribute__((visibility("default")))
+#else
+#define LB2_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  LB2_OK = 0,
+  LB2_BAD_ARG = -1,           /* null pointer, unknown enum, inconsistent optional arguments */
+  LB2_BAD_SHAPE = -2,         /* DimensionMismatch in the reference */
+  LB2_BAD_ALIGN = -3,         /* pointer not aligned to the element size / vector width */
+  LB2_UNSUPPORTED_DTYPE = -4, /* e.g. Float64: caller keeps those on its old path */
+  LB2_LAUNCH_FAIL = -5,       /* CUDA reported an error at launch */
+  LB2_TIMEOUT = -6,           /* a bounded device-side wait expired (reported by lb2_poll_device_status) */
+  LB2_WORKSPACE_TOO_SMALL = -7
+} lb2_status;
+
+typedef enum { LB2_F32 = 0, LB2_BF16 = 1 } lb2_dtype;
+
+/* Activations named by the north-star path (NNlib scalar functions). tanh_fast / sigmoid_fast,
+ * which NNlib.fast_act substitutes at src/layers/basic.jl:368, map to TANH / SIGMOID. */
+typedef enum {
+  LB2_ACT_IDENTITY = 0,
+  LB2_ACT_RELU = 1,
+  LB2_ACT_GELU_TANH = 2, /* 0.5x(1+tanh(sqrt(2/pi)(x+0.044715x^3))) */
+  LB2_ACT_GELU_ERF = 3,  /* 0.5x(1+erf(x/sqrt2)) */
+  LB2_ACT_TANH = 4,
+  LB2_ACT_SIGMOID = 5,
+  LB2_ACT_SWISH = 6
+} lb2_act;
+
+/* flags */
+#define LB2_FLAG_TF32_1X 1u /* fp32 GEMM/conv: single-pass TF32 (rel err ~1e-3) instead of the
+                               default error-compensated 3xTF32 split (rel err ~1e-6) */
+#define LB2_FLAG_FORCE_SIMT 2u /* route a contraction through the CUDA-core kernel (debug / odd shapes) */
+
+/* ---- library ------------------------------------------------------------------------- */
+LB2_API int32_t lb2_version(void);
+LB2_API const char* lb2_status_string(int32_t status);
+/* Thread-local description of the last non-OK status returned on this thread. Mirrors the
+ * 0 / -1 + warning convention of cublaslt_matmul_fused!
+ * (lib/LuxLib/ext/CUDAExt/cublaslt.jl:184-185,292), without its fallback (:386-402). */
+LB2_API const char* lb2_last_error_string(void);
+/* Reads (and clears) the device-side status word that kernels with bounded waits write when a
+ * wait expires. Synchronises `stream`. Returns LB2_OK or LB2_TIMEOUT. */
+LB2_API int32_t lb2_poll_device_status(void* stream);
+
+/* ---- activation / bias-activation ------------------------------------------------------ */
+/* y = act.(x) over n elements.  Replaces activation!  (lib/LuxLib/src/impl/activation.jl:103-133). */
+LB2_API int32_t lb2_act_fwd(void* y, const void* x, int64_t n, int32_t dtype, int32_t act, void* stream);
+/* dx = dy .* act'(out, pre).  `pre` may be NULL for identity/relu/tanh/sigmoid (derivative from the
+ * output only, lib/LuxLib/src/traits.jl:59-65); `out` may be NULL when `pre` is given.
+ * Replaces ∇activation (lib/LuxLib/src/impl/activation.jl:135-154). */
+LB2_API int32_t lb2_act_bwd(void* dx, const void* dy, const void* out, const void* pre, int64_t n,
+                    int32_t dtype, int32_t act, void* stream);
+/* y[s,c,b] = act(x[s,c,b] + bias[c]) on the (S, C, B) view of x
+ * (lib/LuxLib/src/impl/bias_activation.jl:222-270; view at :229-235). bias may be NULL. */
+LB2_API int32_t lb2_bias_act_fwd(void* y, const void* x, const void* bias, int64_t S, int64_t C, int64_t B,
+                         int32_t dtype, int32_t act, void* stream);
+/* dx = dy .* act'; dbias[c] = sum_{s,b} dx   (rrule lib/LuxLib/src/impl/bias_activation.jl:55-141,
+ * ∇bias_add lib/LuxLib/src/impl/common_ops.jl:25-38). dbias may be NULL. dx may alias dy. */
+LB2_API size_t lb2_bias_act_bwd_workspace_bytes(int64_t S, int64_t C, int64_t B);
+LB2_API int32_t lb2_bias_act_bwd(void* dx, void* dbias, const void* dy, const void* out, const void* pre,
+                         int64_t S, int64_t C, int64_t B, int32_t dtype, int32_t act,
+                         void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- dense ----------------------------------------------------------------------------- */
+/* y (M x N) = act.(W (M x K) * x (K x N) .+ b (M)); optionally also stores the pre-activation
+ * (needed by the gelu / swish pullback). Replaces fused_dense! / cublasLt_fused_dense!
+ * (lib/LuxLib/src/impl/dense.jl:46-69, lib/LuxLib/ext/CUDAExt/cublaslt.jl:351-403) and
+ * matmuladd! (lib/LuxLib/src/impl/matmul.jl:73-94) when act = identity. b, preact may be NULL. */
+LB2_API size_t lb2_dense_fwd_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t dtype, uint32_t flags);
+LB2_API int32_t lb2_dense_fwd(void* y, void* preact, const void* W, const void* x, const void* b,
+                      int64_t M, int64_t N, int64_t K, int64_t ldw, int64_t ldx, int64_t ldy,
+                      int32_t dtype, int32_t act, uint32_t flags, void* workspace,
+                      size_t workspace_bytes, void* stream);
+/* Pullback of the above (lib/LuxLib/src/impl/dense.jl:71-113,290-291):
+ *   g  = dy .* act'(out, preact)          (out and/or preact as for lb2_act_bwd; ld = ldy)
+ *   dW = g * x'   dx = W' * g   db = sum over columns of g
+ * Any of dW, dx, db may be NULL (not computed). accumulate != 0 adds into dW, dx, db instead of
+ * overwriting them — the Enzyme shadow contract (lib/LuxLib/src/impl/dense.jl:253-283). */
+LB2_API size_t lb2_dense_bwd_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t dtype, int32_t act,
+                                     uint32_t flags);
+LB2_API int32_t lb2_dense_bwd(void* dW, void* dx, void* db, const void* dy, const void* out,
+                      const void* preact, const void* W, const void* x, int64_t M, int64_t N,
+                      int64_t K, int64_t ldw, int64_t ldx, int64_t ldy, int32_t dtype, int32_t act,
+                      int32_t accumulate, uint32_t flags, void* workspace, size_t workspace_bytes,
+                      void* stream);
+/* C (M x N) = op(A) * op(B) (+ C when accumulate), op = transpose when trans* != 0; A is stored
+ * (M x K) or (K x M), B (K x N) or (N x K). Replaces matmul! on CuArrays
+ * (lib/LuxLib/src/impl/matmul.jl:96-125) and the two GEMMs of its rrule (:228-249). */
+LB2_API size_t lb2_matmul_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t dtype, uint32_t flags);
+LB2_API int32_t lb2_matmul(void* C, const void* A, const void* B, int64_t M, int64_t N, int64_t K,
+                   int64_t lda, int64_t ldb, int64_t ldc, int32_t transA, int32_t transB,
+                   int32_t dtype, int32_t accumulate, uint32_t flags, void* workspace,
+                   size_t workspace_bytes, void* stream);
+
+/* ---- convolution ------------------------------------------------------------------------ */
+/* The fields NNlib.DenseConvDims is built from at src/layers/conv.jl:253-256. Arrays are
+ * x (in[0..nd) , Cin, N), w (k[0..nd), Cin/groups, Cout), y (out[0..nd), Cout, N), column-major. */
+typedef struct {
+  int32_t ndim;      /* spatial rank 1..3 */
+  int32_t in[3];     /* input spatial extents */
+  int32_t k[3];      /* kernel extents */
+  int32_t stride[3];
+  int32_t pad_lo[3];
+  int32_t pad_hi[3];
+  int32_t dilation[3];
+  int32_t groups;
+  int32_t flipkernel; /* 0 = true convolution (kernel flipped, the Lux default); 1 = cross-correlation */
+  int32_t cin, cout, batch;
+} lb2_conv_desc;
+/* Fills out[0..ndim) with (in + pad_lo + pad_hi - dil*(k-1) - 1) / stride + 1 (src/layers/conv.jl:175-177). */
+LB2_API int32_t lb2_conv_output_size(const lb2_conv_desc* d, int32_t* out);
+/* y = act.(conv(x, w) .+ b); optional pre-activation store. Replaces conv_bias_act / conv!
+ * for CUDADevice (lib/LuxLib/src/impl/conv.jl:42-60,157-166). */
+LB2_API size_t lb2_conv_fwd_workspace_bytes(const lb2_conv_desc* d, int32_t dtype);
+LB2_API int32_t lb2_conv_fwd(void* y, void* preact, const void* x, const void* w, const void* b,
+                     const lb2_conv_desc* d, int32_t dtype, int32_t act, uint32_t flags,
+                     void* workspace, size_t workspace_bytes, void* stream);
+/* Pullback ∇fused_conv (lib/LuxLib/src/impl/conv.jl:261-275): g = dy .* act'(out, preact);
+ * dw = ∇conv_filter(x, g); dx = ∇conv_data(g, w); db = sum_{spatial,N} g. Outputs may be NULL. */
+LB2_API size_t lb2_conv_bwd_workspace_bytes(const lb2_conv_desc* d, int32_t dtype, int32_t act);
+LB2_API int32_t lb2_conv_bwd(void* dw, void* dx, void* db, const void* dy, const void* out,
+                     const void* preact, const void* x, const void* w, const lb2_conv_desc* d,
+                     int32_t dtype, int32_t act, uint32_t flags, void* workspace,
+                     size_t workspace_bytes, void* stream);
+
+/* ---- batchnorm --------------------------------------------------------------------------- */
+/* x viewed as (S = prod(spatial), C, B) exactly as lib/LuxLib/src/impl/batchnorm.jl:90.
+ * Training forward: batch statistics (biased variance), y = act(x*g' + b'), g' = gamma/sqrt(var+eps),
+ * b' = beta - mean*g' (impl/batchnorm.jl:149-176); save_mean / save_invstd (fp32, C) are kept for
+ * the backward; when rmean/rvar are given the updated running statistics
+ * new = (1-m)*old + m*{mean, var*n/(n-1)} (lib/LuxLib/src/impl/normalization.jl:95-110) are written
+ * to new_rmean/new_rvar (dtype `dtype`; may alias rmean/rvar). gamma/beta both NULL or both given.
+ * Replaces Impl.batchnorm for CuArrays (lib/LuxLib/ext/cuDNNExt/cuDNNExt.jl:26-40) and
+ * batchnorm_affine_normalize_internal! (lib/LuxLib/src/impl/batchnorm.jl:302-331). */
+LB2_API size_t lb2_batchnorm_workspace_bytes(int64_t S, int64_t C, int64_t B);
+LB2_API int32_t lb2_batchnorm_fwd_train(void* y, float* save_mean, float* save_invstd, void* new_rmean,
+                                void* new_rvar, const void* x, const void* gamma, const void* beta,
+                                const void* rmean, const void* rvar, int64_t S, int64_t C, int64_t B,
+                                double momentum, double eps, int32_t dtype, int32_t act,
+                                void* workspace, size_t workspace_bytes, void* stream);
+/* Inference forward with given statistics (lib/LuxLib/src/impl/normalization.jl:136-143). */
+LB2_API int32_t lb2_batchnorm_fwd_infer(void* y, const void* x, const void* gamma, const void* beta,
+                                const void* rmean, const void* rvar, int64_t S, int64_t C, int64_t B,
+                                double eps, int32_t dtype, int32_t act, void* stream);
+/* Backward of the training forward: ∇batchnorm_affine_normalize (impl/batchnorm.jl:517-663)
+ * chained through the mean_var rrule (lib/LuxLib/src/impl/common_ops.jl:45-61); the activation
+ * derivative is applied inside from the recomputed pre-activation. dgamma/dbeta NULL when
+ * gamma is NULL. */
+LB2_API int32_t lb2_batchnorm_bwd(void* dx, void* dgamma, void* dbeta, const void* dy, const void* x,
+                          const void* gamma, const void* beta, const float* save_mean,
+                          const float* save_invstd, int64_t S, int64_t C, int64_t B, int32_t dtype,
+                          int32_t act, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- groupnorm ----------------------------------------------------------------------------- */
+/* x viewed as (S, C/G, G, B) (lib/LuxLib/src/impl/groupnorm.jl:5-22,76-78); statistics per
+ * (group, sample); save_mean / save_invstd are fp32 of length G*B. Replaces
+ * groupnorm_affine_normalize_internal! (impl/groupnorm.jl:286-313). */
+LB2_API int32_t lb2_groupnorm_fwd(void* y, float* save_mean, float* save_invstd, const void* x,
+                          const void* gamma, const void* beta, int64_t S, int64_t C, int64_t G,
+                          int64_t B, double eps, int32_t dtype, int32_t act, void* stream);
+/* ∇groupnorm_affine_normalize! (impl/groupnorm.jl:477-564) chained through mean_var. */
+LB2_API size_t lb2_groupnorm_bwd_workspace_bytes(int64_t S, int64_t C, int64_t G, int64_t B);
+LB2_API int32_t lb2_groupnorm_bwd(void* dx, void* dgamma, void* dbeta, const void* dy, const void* x,
+                          const void* gamma, const void* beta, const float* save_mean,
+                          const float* save_invstd, int64_t S, int64_t C, int64_t G, int64_t B,
+                          int32_t dtype, int32_t act, void* workspace, size_t workspace_bytes,
+                          void* stream);
+
+/* ---- layernorm ------------------------------------------------------------------------------ */
+/* Row case of Impl.layernorm (lib/LuxLib/src/impl/layernorm.jl:3-14): x viewed as (D, R) with the
+ * normalised dims leading; gamma/beta of length D or both NULL. */
+LB2_API int32_t lb2_layernorm_fwd(void* y, float* save_mean, float* save_invstd, const void* x,
+                          const void* gamma, const void* beta, int64_t D, int64_t R, double eps,
+                          int32_t dtype, int32_t act, void* stream);
+LB2_API size_t lb2_layernorm_bwd_workspace_bytes(int64_t D, int64_t R);
+LB2_API int32_t lb2_layernorm_bwd(void* dx, void* dgamma, void* dbeta, const void* dy, const void* x,
+                          const void* gamma, const void* beta, const float* save_mean,
+                          const float* save_invstd, int64_t D, int64_t R, int32_t dtype, int32_t act,
+                          void* workspace, size_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LUXLIB_B200_H */

@@ -1,0 +1,93 @@
+// Library-level entry points: version, status strings, thread-local error text and the
+// per-device status word that kernels with bounded waits report through.
+#include <stdarg.h>
+#include <string.h>
+
+#include <mutex>
+
+#include "common.cuh"
+
+namespace lb2 {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+
+int32_t fail(int32_t status, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return status;
+}
+
+// Per-device caches, created lazily under a mutex — the analogue of the cuBLASLt handle cache
+// at lib/LuxLib/ext/CUDAExt/cublaslt.jl:66-82.
+static std::mutex g_mu;
+static int g_sm_count[64] = {0};
+
+int sm_count() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (g_sm_count[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    g_sm_count[dev] = n;
+  }
+  return g_sm_count[dev];
+}
+
+// One status word per device, living in the module's own global memory (no allocation).
+__device__ unsigned int g_device_status = 0;
+
+unsigned int* device_status_word() {
+  unsigned int* p = nullptr;
+  if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_device_status) != cudaSuccess) return nullptr;
+  return p;
+}
+
+}  // namespace lb2
+
+extern "C" {
+
+int32_t lb2_version(void) { return 100; }
+
+const char* lb2_status_string(int32_t s) {
+  switch (s) {
+    case LB2_OK: return "ok";
+    case LB2_BAD_ARG: return "bad argument";
+    case LB2_BAD_SHAPE: return "dimension mismatch";
+    case LB2_BAD_ALIGN: return "misaligned pointer or leading dimension";
+    case LB2_UNSUPPORTED_DTYPE: return "unsupported dtype";
+    case LB2_LAUNCH_FAIL: return "kernel launch failed";
+    case LB2_TIMEOUT: return "device-side wait timed out";
+    case LB2_WORKSPACE_TOO_SMALL: return "workspace too small";
+    default: return "unknown status";
+  }
+}
+
+const char* lb2_last_error_string(void) { return lb2::g_err; }
+
+int32_t lb2_poll_device_status(void* stream) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  unsigned int* p = lb2::device_status_word();
+  if (!p) return lb2::fail(LB2_LAUNCH_FAIL, "status word unavailable");
+  unsigned int h = 0;
+  if (cudaMemcpyAsync(&h, p, sizeof(h), cudaMemcpyDeviceToHost, st) != cudaSuccess ||
+      cudaStreamSynchronize(st) != cudaSuccess)
+    return lb2::fail(LB2_LAUNCH_FAIL, "status read failed: %s", cudaGetErrorString(cudaGetLastError()));
+  if (h != 0) {
+    cudaMemsetAsync(p, 0, sizeof(h), st);
+    cudaStreamSynchronize(st);
+    return lb2::fail(LB2_TIMEOUT, "a bounded device-side wait expired (code 0x%x)", h);
+  }
+  return LB2_OK;
+}
+
+}  // extern "C"

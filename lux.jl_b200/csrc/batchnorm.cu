@@ -1,0 +1,442 @@
+// BatchNorm forward (training / inference) and backward on the (S, C, B) column-major view
+// (lib/LuxLib/src/impl/batchnorm.jl:90): per-channel statistics over (S, B).
+//
+// A channel's data is B strided runs of S contiguous elements, so every pass is a grid of
+// (channel, batch-chunk) CTAs moving 128-bit vectors. Training forward = statistics pass
+// (shifted sums, fp32 per thread, fp64 when the chunk partials are combined) + a tiny
+// per-channel finalise (mean, 1/sqrt(var+eps), fused scale/shift, running-statistics update)
+// + apply pass. Backward = one reduction pass producing BOTH sums (sum d, sum d*(x-mean)) +
+// finalise (dgamma, dbeta, dx coefficients) + apply pass. The apply passes walk memory in the
+// opposite direction to the reduction passes so the tail of the tensor is still in the 126 MB L2.
+// Cross-CTA reductions go through caller-provided fp32 partials in a fixed order: deterministic.
+//
+// Algorithmic bytes per element: forward 2*sizeof(T) (read x, write y), backward 3*sizeof(T);
+// the implementation reads x twice forward and x, dy twice backward (tensor larger than on-chip
+// memory), so its HBM traffic is 3 and 5 element-sizes.
+#include "common.cuh"
+
+namespace lb2 {
+
+struct BnPlan {
+  int chunks;
+  int64_t rows_per_chunk;
+};
+
+static BnPlan bn_plan(int64_t S, int64_t C, int64_t B) {
+  const int64_t target = (int64_t)sm_count() * 4;
+  int64_t per_chunk_ctas = (S == 1) ? (C + 31) / 32 : C;
+  if (per_chunk_ctas < 1) per_chunk_ctas = 1;
+  int64_t chunks = (target + per_chunk_ctas - 1) / per_chunk_ctas;
+  const int64_t max_chunks = (S == 1) ? (B + 31) / 32 : B;
+  if (chunks > max_chunks) chunks = max_chunks;
+  if (chunks < 1) chunks = 1;
+  if (chunks > 512) chunks = 512;
+  BnPlan p;
+  p.rows_per_chunk = (B + chunks - 1) / chunks;
+  p.chunks = (int)((B + p.rows_per_chunk - 1) / p.rows_per_chunk);
+  return p;
+}
+
+// workspace (fp32): partial[chunks][C][2] | coef[C][4]
+static size_t bn_ws_bytes(int64_t S, int64_t C, int64_t B) {
+  // upper bound on chunks over both regimes
+  return align_up(((size_t)bn_plan(S, C, B).chunks * (size_t)C * 2 + (size_t)C * 4) * sizeof(float), 256);
+}
+
+// ---------------------------------------------------------------------------------------------
+// reduction passes.  MODE 0: forward statistics  (a = sum (x-K), b = sum (x-K)^2, K = x[0,c,0])
+//                    MODE 1: backward            (a = sum d,     b = sum d*(x-mean), d = dy*act')
+// ---------------------------------------------------------------------------------------------
+template <typename T, int MODE, int ACT, bool AFFINE, bool VEC>
+__global__ void __launch_bounds__(256) bn_reduce_kernel(float* __restrict__ partial, const T* __restrict__ x,
+                                                        const T* __restrict__ dy, const T* __restrict__ gamma,
+                                                        const T* __restrict__ beta, const float* __restrict__ mean_in,
+                                                        const float* __restrict__ inv_in, int64_t S, int64_t C,
+                                                        int64_t B, int64_t rows_per_chunk, int act_rt) {
+  constexpr bool FAST = sizeof(T) == 2;
+  constexpr int V = VEC ? Vec16<T>::N : 1;
+  __shared__ float red[32];
+  const int64_t c = blockIdx.x;
+  const int64_t b_begin = (int64_t)blockIdx.y * rows_per_chunk;
+  const int64_t b_end = min(B, b_begin + rows_per_chunk);
+  const int64_t sv = S / V;
+  float K = 0.f, mean = 0.f, gp = 1.f, bp = 0.f;
+  if constexpr (MODE == 0) {
+    K = to_f32(x[c * S]);
+  } else {
+    mean = mean_in[c];
+    if constexpr (ACT != LB2_ACT_IDENTITY) {
+      const float inv = inv_in[c];
+      gp = inv; bp = -mean * inv;
+      if constexpr (AFFINE) { gp = to_f32(gamma[c]) * inv; bp = to_f32(beta[c]) - mean * gp; }
+    }
+  }
+  float a = 0.f, q = 0.f;
+  const int64_t items = (b_end - b_begin) * sv;
+  for (int64_t it = threadIdx.x; it < items; it += blockDim.x) {
+    const int64_t b = b_begin + it / sv;
+    const int64_t e = (b * C + c) * S + (it % sv) * V;
+    if constexpr (VEC) {
+      Vec16<T> xv = load16(x + e);
+      if constexpr (MODE == 0) {
+#pragma unroll
+        for (int j = 0; j < V; ++j) { float d = xv.get(j) - K; a += d; q += d * d; }
+      } else {
+        Vec16<T> gv = load16(dy + e);
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          float d = gv.get(j);
+          if constexpr (ACT != LB2_ACT_IDENTITY) d *= act_grad_pre_any<ACT, FAST>(act_rt, fmaf(xv.get(j), gp, bp));
+          a += d;
+          q += d * (xv.get(j) - mean);
+        }
+      }
+    } else {
+      const float xv = to_f32(x[e]);
+      if constexpr (MODE == 0) {
+        float d = xv - K; a += d; q += d * d;
+      } else {
+        float d = to_f32(dy[e]);
+        if constexpr (ACT != LB2_ACT_IDENTITY) d *= act_grad_pre_any<ACT, FAST>(act_rt, fmaf(xv, gp, bp));
+        a += d;
+        q += d * (xv - mean);
+      }
+    }
+  }
+  a = block_sum(a, red);
+  q = block_sum(q, red);
+  if (threadIdx.x == 0) {
+    float* p = partial + ((int64_t)blockIdx.y * C + c) * 2;
+    p[0] = a;
+    p[1] = q;
+  }
+}
+
+// S == 1: x is a C x B matrix, channels contiguous. block (32, 8); grid (ceil(C/32), chunks).
+template <typename T, int MODE, int ACT, bool AFFINE>
+__global__ void __launch_bounds__(256) bn_reduce_s1_kernel(float* __restrict__ partial, const T* __restrict__ x,
+                                                           const T* __restrict__ dy, const T* __restrict__ gamma,
+                                                           const T* __restrict__ beta, const float* __restrict__ mean_in,
+                                                           const float* __restrict__ inv_in, int64_t C, int64_t B,
+                                                           int64_t rows_per_chunk, int act_rt) {
+  constexpr bool FAST = sizeof(T) == 2;
+  __shared__ float ra[8][33], rq[8][33];
+  const int64_t c = (int64_t)blockIdx.x * 32 + threadIdx.x;
+  const int64_t b_begin = (int64_t)blockIdx.y * rows_per_chunk;
+  const int64_t b_end = min(B, b_begin + rows_per_chunk);
+  float a = 0.f, q = 0.f;
+  if (c < C) {
+    float K = 0.f, mean = 0.f, gp = 1.f, bp = 0.f;
+    if constexpr (MODE == 0) {
+      K = to_f32(x[c]);
+    } else {
+      mean = mean_in[c];
+      if constexpr (ACT != LB2_ACT_IDENTITY) {
+        const float inv = inv_in[c];
+        gp = inv; bp = -mean * inv;
+        if constexpr (AFFINE) { gp = to_f32(gamma[c]) * inv; bp = to_f32(beta[c]) - mean * gp; }
+      }
+    }
+    for (int64_t b = b_begin + threadIdx.y; b < b_end; b += 8) {
+      const float xv = to_f32(x[b * C + c]);
+      if constexpr (MODE == 0) {
+        float d = xv - K; a += d; q += d * d;
+      } else {
+        float d = to_f32(dy[b * C + c]);
+        if constexpr (ACT != LB2_ACT_IDENTITY) d *= act_grad_pre_any<ACT, FAST>(act_rt, fmaf(xv, gp, bp));
+        a += d;
+        q += d * (xv - mean);
+      }
+    }
+  }
+  ra[threadIdx.y][threadIdx.x] = a;
+  rq[threadIdx.y][threadIdx.x] = q;
+  __syncthreads();
+  if (threadIdx.y == 0 && c < C) {
+    float sa = 0.f, sq = 0.f;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) { sa += ra[r][threadIdx.x]; sq += rq[r][threadIdx.x]; }
+    float* p = partial + ((int64_t)blockIdx.y * C + c) * 2;
+    p[0] = sa;
+    p[1] = sq;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// finalise kernels (one thread per channel; fp64 combination of the chunk partials)
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void bn_finalize_fwd_kernel(float* __restrict__ save_mean, float* __restrict__ save_inv,
+                                       float* __restrict__ coef, T* __restrict__ new_rmean, T* __restrict__ new_rvar,
+                                       const T* __restrict__ rmean, const T* __restrict__ rvar,
+                                       const T* __restrict__ gamma, const T* __restrict__ beta,
+                                       const T* __restrict__ x, const float* __restrict__ partial, int64_t S, int64_t C,
+                                       int64_t B, int chunks, float momentum, float eps) {
+  const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  double a = 0.0, q = 0.0;
+  for (int k = 0; k < chunks; ++k) {
+    a += (double)partial[((int64_t)k * C + c) * 2];
+    q += (double)partial[((int64_t)k * C + c) * 2 + 1];
+  }
+  const double n = (double)S * (double)B;
+  const double K = (double)to_f32(x[c * S]);
+  const double mean_d = K + a / n;
+  double var_d = (q - a * a / n) / n;
+  if (var_d < 0.0) var_d = 0.0;
+  const float mean = (float)mean_d, var = (float)var_d;
+  const float inv = 1.f / sqrtf(var + eps);
+  save_mean[c] = mean;
+  save_inv[c] = inv;
+  float gp = inv, bp = -mean * inv;
+  if (gamma) { gp = to_f32(gamma[c]) * inv; bp = to_f32(beta[c]) - mean * gp; }
+  coef[c * 4 + 0] = gp;
+  coef[c * 4 + 1] = bp;
+  if (rmean) {
+    // lib/LuxLib/src/impl/normalization.jl:95-110: m1 = momentum, m2 = momentum * n/(n-1), m3 = 1 - m1
+    const float nf = (float)n;
+    const float m1 = momentum, m2 = momentum * nf / (nf - 1.f), m3 = 1.f - m1;
+    new_rmean[c] = from_f32<T>(m3 * to_f32(rmean[c]) + m1 * mean);
+    new_rvar[c] = from_f32<T>(m3 * to_f32(rvar[c]) + m2 * var);
+  }
+}
+
+template <typename T>
+__global__ void bn_finalize_bwd_kernel(T* __restrict__ dgamma, T* __restrict__ dbeta, float* __restrict__ coef,
+                                       const T* __restrict__ gamma, const float* __restrict__ save_mean,
+                                       const float* __restrict__ save_inv, const float* __restrict__ partial,
+                                       int64_t S, int64_t C, int64_t B, int chunks) {
+  const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  double a = 0.0, q = 0.0;
+  for (int k = 0; k < chunks; ++k) {
+    a += (double)partial[((int64_t)k * C + c) * 2];
+    q += (double)partial[((int64_t)k * C + c) * 2 + 1];
+  }
+  const float n = (float)((double)S * (double)B);
+  const float inv = save_inv[c], mean = save_mean[c];
+  const float sd = (float)a, sdx = (float)q;
+  if (dgamma) {
+    dgamma[c] = from_f32<T>(sdx * inv);
+    dbeta[c] = from_f32<T>(sd);
+  }
+  const float gp = gamma ? to_f32(gamma[c]) * inv : inv;
+  // dx = gp * (d - sd/n - (x-mean) * inv^2 * sdx/n) = gp*d + cx*x + c0
+  const float k2 = inv * inv * sdx / n;
+  coef[c * 4 + 0] = gp;
+  coef[c * 4 + 1] = -gp * k2;                      // multiplies x
+  coef[c * 4 + 2] = gp * (k2 * mean - sd / n);     // constant
+}
+
+// ---------------------------------------------------------------------------------------------
+// apply passes (vector index reversed: the end of the tensor was read last by the reduction)
+// ---------------------------------------------------------------------------------------------
+// MODE 0: y = act(x*gp + bp) from coef (training)      MODE 1: same from running statistics
+// MODE 2: dx = c0*d + c1*x + c2, d = dy*act'(x*gp_fwd + bp_fwd)
+template <typename T, int MODE, int ACT, bool AFFINE, bool VEC>
+__global__ void __launch_bounds__(256) bn_apply_kernel(T* __restrict__ out, const T* __restrict__ x,
+                                                       const T* __restrict__ dy, const float* __restrict__ coef,
+                                                       const T* __restrict__ gamma, const T* __restrict__ beta,
+                                                       const T* __restrict__ rmean, const T* __restrict__ rvar,
+                                                       const float* __restrict__ mean_in,
+                                                       const float* __restrict__ inv_in, int64_t S, int64_t C,
+                                                       int64_t n, float eps, int act_rt) {
+  constexpr bool FAST = sizeof(T) == 2;
+  constexpr int V = VEC ? Vec16<T>::N : 1;
+  const int64_t nvec = n / V;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i0 < nvec; i0 += stride) {
+    const int64_t i = nvec - 1 - i0;
+    const int64_t e = i * V;
+    const int64_t c = (e / S) % C;
+    float gp, bp;
+    if constexpr (MODE == 0) {
+      gp = coef[c * 4];
+      bp = coef[c * 4 + 1];
+    } else if constexpr (MODE == 1) {
+      const float inv = 1.f / sqrtf(to_f32(rvar[c]) + eps);
+      const float mean = to_f32(rmean[c]);
+      gp = inv; bp = -mean * inv;
+      if constexpr (AFFINE) { gp = to_f32(gamma[c]) * inv; bp = to_f32(beta[c]) - mean * gp; }
+    } else {
+      gp = 1.f; bp = 0.f;
+      if constexpr (ACT != LB2_ACT_IDENTITY) {
+        const float inv = inv_in[c], mean = mean_in[c];
+        gp = inv; bp = -mean * inv;
+        if constexpr (AFFINE) { gp = to_f32(gamma[c]) * inv; bp = to_f32(beta[c]) - mean * gp; }
+      }
+    }
+    if constexpr (MODE == 2) {
+      const float c0 = coef[c * 4], c1 = coef[c * 4 + 1], c2 = coef[c * 4 + 2];
+      if constexpr (VEC) {
+        Vec16<T> xv = load16_stream(x + e), gv = load16_stream(dy + e), o;
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          float d = gv.get(j);
+          if constexpr (ACT != LB2_ACT_IDENTITY) d *= act_grad_pre_any<ACT, FAST>(act_rt, fmaf(xv.get(j), gp, bp));
+          o.set(j, fmaf(c0, d, fmaf(c1, xv.get(j), c2)));
+        }
+        store16_stream(out + e, o);
+      } else {
+        const float xv = to_f32(x[e]);
+        float d = to_f32(dy[e]);
+        if constexpr (ACT != LB2_ACT_IDENTITY) d *= act_grad_pre_any<ACT, FAST>(act_rt, fmaf(xv, gp, bp));
+        out[e] = from_f32<T>(fmaf(c0, d, fmaf(c1, xv, c2)));
+      }
+    } else {
+      if constexpr (VEC) {
+        Vec16<T> xv = load16_stream(x + e), o;
+#pragma unroll
+        for (int j = 0; j < V; ++j) o.set(j, act_apply_any<ACT, FAST>(act_rt, fmaf(xv.get(j), gp, bp)));
+        store16_stream(out + e, o);
+      } else {
+        out[e] = from_f32<T>(act_apply_any<ACT, FAST>(act_rt, fmaf(to_f32(x[e]), gp, bp)));
+      }
+    }
+  }
+}
+
+static unsigned apply_grid(int64_t items) {
+  int64_t g = (items + 255) / 256, cap = (int64_t)sm_count() * 16;
+  return (unsigned)(g < 1 ? 1 : (g > cap ? cap : g));
+}
+
+template <typename T, int MODE, int ACT, bool AFFINE>
+static void bn_reduce_launch(float* partial, const T* x, const T* dy, const T* g, const T* b, const float* sm,
+                             const float* si, int64_t S, int64_t C, int64_t B, const BnPlan& p, int act, cudaStream_t st) {
+  constexpr int V = Vec16<T>::N;
+  if (S == 1) {
+    dim3 grid((unsigned)((C + 31) / 32), p.chunks), block(32, 8);
+    bn_reduce_s1_kernel<T, MODE, ACT, AFFINE><<<grid, block, 0, st>>>(partial, x, dy, g, b, sm, si, C, B, p.rows_per_chunk, act);
+  } else {
+    dim3 grid((unsigned)C, p.chunks);
+    const bool vec = aligned_to(x, 16) && (!dy || aligned_to(dy, 16)) && S % V == 0;
+    if (vec) bn_reduce_kernel<T, MODE, ACT, AFFINE, true><<<grid, 256, 0, st>>>(partial, x, dy, g, b, sm, si, S, C, B, p.rows_per_chunk, act);
+    else bn_reduce_kernel<T, MODE, ACT, AFFINE, false><<<grid, 256, 0, st>>>(partial, x, dy, g, b, sm, si, S, C, B, p.rows_per_chunk, act);
+  }
+}
+
+template <typename T, int MODE, int ACT, bool AFFINE>
+static void bn_apply_launch(T* out, const T* x, const T* dy, const float* coef, const T* g, const T* b, const T* rm,
+                            const T* rv, const float* sm, const float* si, int64_t S, int64_t C, int64_t B, float eps,
+                            int act, cudaStream_t st) {
+  constexpr int V = Vec16<T>::N;
+  const int64_t n = S * C * B;
+  const bool vec = aligned_to(out, 16) && aligned_to(x, 16) && (!dy || aligned_to(dy, 16)) && S % V == 0;
+  if (vec) bn_apply_kernel<T, MODE, ACT, AFFINE, true><<<apply_grid(n / V), 256, 0, st>>>(out, x, dy, coef, g, b, rm, rv, sm, si, S, C, n, eps, act);
+  else bn_apply_kernel<T, MODE, ACT, AFFINE, false><<<apply_grid(n), 256, 0, st>>>(out, x, dy, coef, g, b, rm, rv, sm, si, S, C, n, eps, act);
+}
+
+static int32_t check_bn(const void* out, const void* x, const void* gamma, const void* beta, int64_t S, int64_t C,
+                        int64_t B, int32_t dtype, int32_t act) {
+  LB2_REQUIRE(S >= 0 && C >= 0 && B >= 0, LB2_BAD_SHAPE, "negative extent");
+  LB2_REQUIRE(valid_dtype(dtype), LB2_UNSUPPORTED_DTYPE, "dtype %d not supported", (int)dtype);
+  LB2_REQUIRE(valid_act(act), LB2_BAD_ARG, "unknown activation %d", (int)act);
+  if (S == 0 || C == 0 || B == 0) return LB2_OK;
+  LB2_REQUIRE(out && x, LB2_BAD_ARG, "null tensor pointer");
+  LB2_REQUIRE((gamma == nullptr) == (beta == nullptr), LB2_BAD_ARG, "scale and bias must both be given or both be null");
+  const size_t es = dtype_size(dtype);
+  LB2_REQUIRE(aligned_to(out, es) && aligned_to(x, es) && aligned_to(gamma, es) && aligned_to(beta, es), LB2_BAD_ALIGN,
+              "pointer not aligned to the element size");
+  return LB2_OK;
+}
+
+}  // namespace lb2
+
+using namespace lb2;
+
+extern "C" {
+
+size_t lb2_batchnorm_workspace_bytes(int64_t S, int64_t C, int64_t B) {
+  if (S <= 0 || C <= 0 || B <= 0) return 0;
+  return bn_ws_bytes(S, C, B);
+}
+
+int32_t lb2_batchnorm_fwd_train(void* y, float* save_mean, float* save_invstd, void* new_rmean, void* new_rvar,
+                                const void* x, const void* gamma, const void* beta, const void* rmean,
+                                const void* rvar, int64_t S, int64_t C, int64_t B, double momentum, double eps,
+                                int32_t dtype, int32_t act, void* workspace, size_t workspace_bytes, void* stream) {
+  int32_t rc = check_bn(y, x, gamma, beta, S, C, B, dtype, act);
+  if (rc != LB2_OK) return rc;
+  if (S == 0 || C == 0 || B == 0) return LB2_OK;
+  LB2_REQUIRE(save_mean && save_invstd, LB2_BAD_ARG, "save_mean / save_invstd are null");
+  LB2_REQUIRE((rmean == nullptr) == (rvar == nullptr), LB2_BAD_ARG, "running mean and variance must both be given or both be null");
+  LB2_REQUIRE(!rmean || (new_rmean && new_rvar), LB2_BAD_ARG, "outputs for the updated running statistics are null");
+  LB2_REQUIRE(workspace && workspace_bytes >= bn_ws_bytes(S, C, B), LB2_WORKSPACE_TOO_SMALL, "workspace of %zu bytes needed", bn_ws_bytes(S, C, B));
+  LB2_REQUIRE(aligned_to(workspace, 16), LB2_BAD_ALIGN, "workspace must be 16-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const BnPlan p = bn_plan(S, C, B);
+  float* partial = (float*)workspace;
+  float* coef = partial + (size_t)p.chunks * C * 2;
+  LB2_DISPATCH_DTYPE(dtype, {
+    bn_reduce_launch<T, 0, LB2_ACT_IDENTITY, false>(partial, (const T*)x, nullptr, nullptr, nullptr, nullptr, nullptr, S, C, B, p, act, st);
+    LB2_CHECK_LAUNCH("batchnorm statistics");
+    bn_finalize_fwd_kernel<T><<<(unsigned)((C + 127) / 128), 128, 0, st>>>(
+        save_mean, save_invstd, coef, (T*)new_rmean, (T*)new_rvar, (const T*)rmean, (const T*)rvar, (const T*)gamma,
+        (const T*)beta, (const T*)x, partial, S, C, B, p.chunks, (float)momentum, (float)eps);
+    LB2_CHECK_LAUNCH("batchnorm finalise");
+    LB2_DISPATCH_ACT3(act, {
+      bn_apply_launch<T, 0, ACT, false>((T*)y, (const T*)x, nullptr, coef, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, S, C, B, (float)eps, act, st);
+    });
+    LB2_CHECK_LAUNCH("batchnorm apply");
+  });
+  return LB2_OK;
+}
+
+int32_t lb2_batchnorm_fwd_infer(void* y, const void* x, const void* gamma, const void* beta, const void* rmean,
+                                const void* rvar, int64_t S, int64_t C, int64_t B, double eps, int32_t dtype,
+                                int32_t act, void* stream) {
+  int32_t rc = check_bn(y, x, gamma, beta, S, C, B, dtype, act);
+  if (rc != LB2_OK) return rc;
+  if (S == 0 || C == 0 || B == 0) return LB2_OK;
+  LB2_REQUIRE(rmean && rvar, LB2_BAD_ARG, "running statistics are required for inference");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  LB2_DISPATCH_DTYPE(dtype, {
+    LB2_DISPATCH_ACT3(act, {
+      if (gamma) bn_apply_launch<T, 1, ACT, true>((T*)y, (const T*)x, nullptr, nullptr, (const T*)gamma, (const T*)beta, (const T*)rmean, (const T*)rvar, nullptr, nullptr, S, C, B, (float)eps, act, st);
+      else bn_apply_launch<T, 1, ACT, false>((T*)y, (const T*)x, nullptr, nullptr, nullptr, nullptr, (const T*)rmean, (const T*)rvar, nullptr, nullptr, S, C, B, (float)eps, act, st);
+    });
+    LB2_CHECK_LAUNCH("batchnorm inference");
+  });
+  return LB2_OK;
+}
+
+int32_t lb2_batchnorm_bwd(void* dx, void* dgamma, void* dbeta, const void* dy, const void* x, const void* gamma,
+                          const void* beta, const float* save_mean, const float* save_invstd, int64_t S, int64_t C,
+                          int64_t B, int32_t dtype, int32_t act, void* workspace, size_t workspace_bytes,
+                          void* stream) {
+  int32_t rc = check_bn(dx, x, gamma, beta, S, C, B, dtype, act);
+  if (rc != LB2_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (S == 0 || C == 0 || B == 0) {
+    if (C > 0 && dgamma) {
+      cudaMemsetAsync(dgamma, 0, (size_t)C * dtype_size(dtype), st);
+      cudaMemsetAsync(dbeta, 0, (size_t)C * dtype_size(dtype), st);
+    }
+    return LB2_OK;
+  }
+  LB2_REQUIRE(dy && save_mean && save_invstd, LB2_BAD_ARG, "null tensor pointer");
+  LB2_REQUIRE(!gamma || (dgamma && dbeta), LB2_BAD_ARG, "dgamma/dbeta required when scale is given");
+  LB2_REQUIRE(workspace && workspace_bytes >= bn_ws_bytes(S, C, B), LB2_WORKSPACE_TOO_SMALL, "workspace of %zu bytes needed", bn_ws_bytes(S, C, B));
+  LB2_REQUIRE(aligned_to(workspace, 16), LB2_BAD_ALIGN, "workspace must be 16-byte aligned");
+  const BnPlan p = bn_plan(S, C, B);
+  float* partial = (float*)workspace;
+  float* coef = partial + (size_t)p.chunks * C * 2;
+  LB2_DISPATCH_DTYPE(dtype, {
+    LB2_DISPATCH_ACT3(act, {
+      if (gamma) bn_reduce_launch<T, 1, ACT, true>(partial, (const T*)x, (const T*)dy, (const T*)gamma, (const T*)beta, save_mean, save_invstd, S, C, B, p, act, st);
+      else bn_reduce_launch<T, 1, ACT, false>(partial, (const T*)x, (const T*)dy, nullptr, nullptr, save_mean, save_invstd, S, C, B, p, act, st);
+    });
+    LB2_CHECK_LAUNCH("batchnorm backward reduction");
+    bn_finalize_bwd_kernel<T><<<(unsigned)((C + 127) / 128), 128, 0, st>>>((T*)dgamma, (T*)dbeta, coef, (const T*)gamma, save_mean, save_invstd, partial, S, C, B, p.chunks);
+    LB2_CHECK_LAUNCH("batchnorm backward finalise");
+    LB2_DISPATCH_ACT3(act, {
+      if (gamma) bn_apply_launch<T, 2, ACT, true>((T*)dx, (const T*)x, (const T*)dy, coef, (const T*)gamma, (const T*)beta, nullptr, nullptr, save_mean, save_invstd, S, C, B, 0.f, act, st);
+      else bn_apply_launch<T, 2, ACT, false>((T*)dx, (const T*)x, (const T*)dy, coef, nullptr, nullptr, nullptr, nullptr, save_mean, save_invstd, S, C, B, 0.f, act, st);
+    });
+    LB2_CHECK_LAUNCH("batchnorm backward apply");
+  });
+  return LB2_OK;
+}
+
+}  // extern "C"

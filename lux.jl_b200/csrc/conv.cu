@@ -1,0 +1,147 @@
+// Convolution entry points: y = act(conv(x, w) + b) and the pullback ∇fused_conv
+// (lib/LuxLib/src/impl/conv.jl:261-275): g = dy .* act', dw = ∇conv_filter(x, g),
+// dx = ∇conv_data(g, w), db = sum over (spatial, batch) of g.
+#include "conv.cuh"
+#include "eltwise.cuh"
+
+using namespace lb2;
+
+namespace {
+
+int32_t make_geom(const lb2_conv_desc* d, ConvGeom* g) {
+  LB2_REQUIRE(d != nullptr, LB2_BAD_ARG, "conv descriptor is null");
+  LB2_REQUIRE(d->ndim >= 1 && d->ndim <= 3, LB2_BAD_SHAPE, "spatial rank %d not in 1..3", (int)d->ndim);
+  LB2_REQUIRE(d->groups >= 1 && d->cin >= 0 && d->cout >= 0 && d->batch >= 0, LB2_BAD_SHAPE, "bad channel / batch extents");
+  LB2_REQUIRE(d->cin % d->groups == 0 && d->cout % d->groups == 0, LB2_BAD_SHAPE,
+              "channels (%d -> %d) must be divisible by groups (%d)", (int)d->cin, (int)d->cout, (int)d->groups);
+  for (int i = 0; i < 3; ++i) {
+    const bool live = i < d->ndim;
+    g->in[i] = live ? d->in[i] : 1;
+    g->k[i] = live ? d->k[i] : 1;
+    g->stride[i] = live ? d->stride[i] : 1;
+    g->pad_lo[i] = live ? d->pad_lo[i] : 0;
+    g->pad_hi[i] = live ? d->pad_hi[i] : 0;
+    g->dil[i] = live ? d->dilation[i] : 1;
+    LB2_REQUIRE(g->in[i] >= 0 && g->k[i] >= 1 && g->stride[i] >= 1 && g->dil[i] >= 1 && g->pad_lo[i] >= 0 && g->pad_hi[i] >= 0,
+                LB2_BAD_SHAPE, "bad extent / stride / dilation / padding in dim %d", i);
+    const int span = g->in[i] + g->pad_lo[i] + g->pad_hi[i] - g->dil[i] * (g->k[i] - 1) - 1;
+    g->out[i] = span < 0 ? 0 : span / g->stride[i] + 1;
+  }
+  g->groups = d->groups;
+  g->flip = d->flipkernel ? 1 : 0;
+  g->cin = d->cin;
+  g->cout = d->cout;
+  g->batch = d->batch;
+  g->ndim = d->ndim;
+  return LB2_OK;
+}
+
+int64_t y_numel(const ConvGeom& g) { return (int64_t)g.out[0] * g.out[1] * g.out[2] * g.cout * g.batch; }
+int64_t y_spatial(const ConvGeom& g) { return (int64_t)g.out[0] * g.out[1] * g.out[2]; }
+
+struct ConvBwdLayout {
+  size_t g_bytes, red_bytes;
+  size_t total() const { return g_bytes + red_bytes; }
+};
+ConvBwdLayout conv_bwd_layout(const ConvGeom& g, int32_t dtype, int32_t act) {
+  ConvBwdLayout l{};
+  const int64_t n = y_numel(g);
+  if (n <= 0) return l;
+  l.g_bytes = act == LB2_ACT_IDENTITY ? 0 : align_up((size_t)n * dtype_size(dtype), 256);
+  l.red_bytes = act_bwd_workspace_bytes(y_spatial(g), g.cout, g.batch);
+  return l;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t lb2_conv_output_size(const lb2_conv_desc* d, int32_t* out) {
+  ConvGeom g;
+  int32_t rc = make_geom(d, &g);
+  if (rc != LB2_OK) return rc;
+  LB2_REQUIRE(out != nullptr, LB2_BAD_ARG, "out is null");
+  for (int i = 0; i < d->ndim; ++i) out[i] = g.out[i];
+  return LB2_OK;
+}
+
+size_t lb2_conv_fwd_workspace_bytes(const lb2_conv_desc* d, int32_t dtype) {
+  (void)d; (void)dtype;
+  return 0;
+}
+
+int32_t lb2_conv_fwd(void* y, void* preact, const void* x, const void* w, const void* b, const lb2_conv_desc* d,
+                     int32_t dtype, int32_t act, uint32_t flags, void* workspace, size_t workspace_bytes,
+                     void* stream) {
+  (void)flags; (void)workspace; (void)workspace_bytes;
+  LB2_REQUIRE(valid_dtype(dtype), LB2_UNSUPPORTED_DTYPE, "dtype %d not supported", (int)dtype);
+  LB2_REQUIRE(valid_act(act), LB2_BAD_ARG, "unknown activation %d", (int)act);
+  ConvGeom g;
+  int32_t rc = make_geom(d, &g);
+  if (rc != LB2_OK) return rc;
+  if (y_numel(g) == 0) return LB2_OK;
+  LB2_REQUIRE(y && x && w, LB2_BAD_ARG, "null tensor pointer");
+  const size_t es = dtype_size(dtype);
+  LB2_REQUIRE(aligned_to(y, es) && aligned_to(preact, es) && aligned_to(x, es) && aligned_to(w, es) && aligned_to(b, es),
+              LB2_BAD_ALIGN, "pointer not aligned to the element size");
+  return conv_fwd_direct(y, preact, x, w, b, g, dtype, act, static_cast<cudaStream_t>(stream));
+}
+
+size_t lb2_conv_bwd_workspace_bytes(const lb2_conv_desc* d, int32_t dtype, int32_t act) {
+  ConvGeom g;
+  if (!valid_dtype(dtype) || make_geom(d, &g) != LB2_OK) return 0;
+  return conv_bwd_layout(g, dtype, act).total();
+}
+
+int32_t lb2_conv_bwd(void* dw, void* dx, void* db, const void* dy, const void* out, const void* preact,
+                     const void* x, const void* w, const lb2_conv_desc* d, int32_t dtype, int32_t act, uint32_t flags,
+                     void* workspace, size_t workspace_bytes, void* stream) {
+  (void)flags;
+  LB2_REQUIRE(valid_dtype(dtype), LB2_UNSUPPORTED_DTYPE, "dtype %d not supported", (int)dtype);
+  LB2_REQUIRE(valid_act(act), LB2_BAD_ARG, "unknown activation %d", (int)act);
+  ConvGeom g;
+  int32_t rc = make_geom(d, &g);
+  if (rc != LB2_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t es = dtype_size(dtype);
+  const int64_t nw = (int64_t)g.k[0] * g.k[1] * g.k[2] * (g.cin / g.groups) * g.cout;
+  const int64_t nx = (int64_t)g.in[0] * g.in[1] * g.in[2] * g.cin * g.batch;
+  if (y_numel(g) == 0) {  // nothing flows back: zero gradients
+    if (dw && nw > 0) cudaMemsetAsync(dw, 0, (size_t)nw * es, st);
+    if (dx && nx > 0) cudaMemsetAsync(dx, 0, (size_t)nx * es, st);
+    if (db && g.cout > 0) cudaMemsetAsync(db, 0, (size_t)g.cout * es, st);
+    return LB2_OK;
+  }
+  rc = check_act_bwd_args(dy, out, preact, dtype, act);
+  if (rc != LB2_OK) return rc;
+  LB2_REQUIRE((!dw || x) && (!dx || w), LB2_BAD_ARG, "x / w needed for the requested gradients are null");
+  LB2_REQUIRE(aligned_to(dw, es) && aligned_to(dx, es) && aligned_to(db, es) && aligned_to(dy, es) && aligned_to(out, es) &&
+                  aligned_to(preact, es) && aligned_to(x, es) && aligned_to(w, es),
+              LB2_BAD_ALIGN, "pointer not aligned to the element size");
+  const ConvBwdLayout lay = conv_bwd_layout(g, dtype, act);
+  LB2_REQUIRE(workspace != nullptr && workspace_bytes >= lay.total(), LB2_WORKSPACE_TOO_SMALL, "workspace of %zu bytes needed", lay.total());
+  LB2_REQUIRE(aligned_to(workspace, 256), LB2_BAD_ALIGN, "workspace must be 256-byte aligned");
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  float* red = reinterpret_cast<float*>(ws + lay.g_bytes);
+  const int64_t S = y_spatial(g);
+  const void* gptr = dy;
+  if (act != LB2_ACT_IDENTITY) {
+    rc = launch_act_bwd(ws, db, dy, out, preact, S, g.cout, g.batch, g.cout, g.cout, g.cout, dtype, act, 0, red, st);
+    if (rc != LB2_OK) return rc;
+    gptr = ws;
+  } else if (db) {
+    rc = launch_act_bwd(nullptr, db, dy, nullptr, nullptr, S, g.cout, g.batch, g.cout, g.cout, g.cout, dtype, act, 0, red, st);
+    if (rc != LB2_OK) return rc;
+  }
+  if (dw) {
+    rc = conv_wgrad_direct(dw, x, gptr, g, dtype, st);
+    if (rc != LB2_OK) return rc;
+  }
+  if (dx && nx > 0) {
+    rc = conv_dgrad_direct(dx, gptr, w, g, dtype, st);
+    if (rc != LB2_OK) return rc;
+  }
+  return LB2_OK;
+}
+
+}  // extern "C"

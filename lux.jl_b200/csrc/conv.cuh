@@ -1,0 +1,18 @@
+// Internal convolution interface.
+#pragma once
+#include "common.cuh"
+
+namespace lb2 {
+
+// lb2_conv_desc normalised to three spatial dims (missing dims have extent 1).
+struct ConvGeom {
+  int in[3], k[3], stride[3], pad_lo[3], pad_hi[3], dil[3], out[3];
+  int groups, flip, cin, cout, batch, ndim;
+};
+
+int32_t conv_fwd_direct(void* y, void* preact, const void* x, const void* w, const void* bias, const ConvGeom& g,
+                        int32_t dtype, int32_t act, cudaStream_t st);
+int32_t conv_dgrad_direct(void* dx, const void* dy, const void* w, const ConvGeom& g, int32_t dtype, cudaStream_t st);
+int32_t conv_wgrad_direct(void* dw, const void* x, const void* dy, const ConvGeom& g, int32_t dtype, cudaStream_t st);
+
+}  // namespace lb2

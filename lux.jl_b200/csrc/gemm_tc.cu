@@ -1,0 +1,553 @@
+// Tensor-core GEMM for sm_100a: TMA -> 128B-swizzled shared-memory ring -> tcgen05.mma with the
+// accumulator in TMEM -> tcgen05.ld epilogue with bias + activation fused.
+//
+//   D[Mm x Nn] = A[Mm x Kc] * B[Nn x Kc]^T      (D column-major, Mm contiguous)
+//
+// One persistent CTA per SM, 256 threads, warp-specialised:
+//   warp 0      TMA producer (one elected lane): fills a ring of STAGES {A,B} k-blocks
+//   warp 1      MMA issuer  (one elected lane): 4 tcgen05.mma (K=16 bf16 / K=8 tf32) per k-block,
+//               tcgen05.commit releases the smem stage / publishes the accumulator
+//   warp 2      TMEM allocator (512 columns = two 128 x BN fp32 accumulators, so the epilogue of
+//               tile i overlaps the main loop of tile i+1)
+//   warps 4-7   epilogue: tcgen05.ld 32 lanes x 32 columns -> +bias -> activation -> global
+//               (lane = output row = contiguous index of D, so every warp store is a 64/128-byte run)
+// Operands may be K-major or MN-major in global memory; both are fetched with tiled TMA boxes
+// of 128-byte rows (SWIZZLE_128B) and described to the MMA through the matching shared-memory
+// matrix descriptor, so no transposition pass ever runs. fp32 storage uses kind::tf32, by default
+// as an error-compensated 3-product split (hi*hi + lo*hi + hi*lo) that restores ~fp32 accuracy.
+// No TMA multicast is used anywhere. Every mbarrier wait is bounded; on expiry the kernel sets
+// a status word, drains and returns, and the host reports LB2_TIMEOUT from lb2_poll_device_status.
+//
+// Roofline: tensor-pipe bound; algorithmic FLOPs = 2*Mm*Nn*Kc per launch.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "gemm.cuh"
+
+namespace lb2 {
+
+// ----------------------------------------------------------------------------------------------
+// PTX wrappers
+// ----------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait: gives up after kWaitLimitNs of wall time (checked every 256 polls), records `code`
+// in the status word and returns false.
+constexpr uint64_t kWaitLimitNs = 2000000000ull;
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned int* status, unsigned int code) {
+  uint32_t spins = 0;
+  uint64_t t0 = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 0xFFu) == 0) {
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > kWaitLimitNs) {
+        atomicOr(status, code);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int32_t c0, int32_t c1, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+template <bool TF32>
+__device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  if constexpr (TF32) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// ----------------------------------------------------------------------------------------------
+// kernel
+// ----------------------------------------------------------------------------------------------
+// How one operand tile is fetched and described (filled in on the host).
+struct OperandPlan {
+  int32_t boxes;        // TMA boxes per k-block
+  int32_t box_bytes;    // bytes each box lands in shared memory
+  int32_t mn_step;      // MN-major: elements of the MN extent covered by one box; K-major: unused
+  int32_t mn_major;     // 1: coordinates are {mn, k}; 0: {k, mn}
+  uint32_t desc_hi;     // upper 32 bits of the UMMA smem descriptor (SBO, version, swizzle)
+  uint32_t desc_lbo;    // LBO field already shifted into bits [16,30) of the lower word
+  uint32_t k_advance;   // descriptor start-address increment (bytes >> 4) per MMA k-step
+};
+
+struct TcParams {
+  OperandPlan a, b;
+  int64_t Mm, Nn, Kc;
+  int32_t bk;           // elements of K per k-block (64 bf16 / 32 tf32)
+  int32_t tiles_m, tiles_n, num_kb;
+  uint32_t idesc;
+  void* D;
+  int64_t ldd;
+  const void* bias;
+  void* preact;
+  int32_t act, accumulate;
+  unsigned int* status;
+};
+
+constexpr int kBM = 128;
+constexpr int kThreads = 256;
+constexpr int kKSteps = 4;  // MMA k-steps per k-block (128 bytes of K per row / 32 bytes per step)
+
+template <int BN, bool TF32, bool SPLIT3> struct TcCfg {
+  static constexpr int A_BYTES = kBM * 128;
+  static constexpr int B_BYTES = BN * 128;
+  static constexpr int STAGE_BYTES = (A_BYTES + B_BYTES) * (SPLIT3 ? 2 : 1);
+  static constexpr int STAGES = (200 * 1024) / STAGE_BYTES < 8 ? (200 * 1024) / STAGE_BYTES : 8;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+template <int BN, bool TF32, bool SPLIT3, int ACT, typename OutT>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const __grid_constant__ CUtensorMap tmA_lo, const __grid_constant__ CUtensorMap tmB_lo,
+               const __grid_constant__ TcParams p) {
+  using Cfg = TcCfg<BN, TF32, SPLIT3>;
+  constexpr int STAGES = Cfg::STAGES;
+  constexpr bool FAST = sizeof(OutT) == 2;
+  extern __shared__ uint8_t smem_raw[];
+  // SWIZZLE_128B tiles must start on 1024-byte boundaries
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + STAGES * Cfg::STAGE_BYTES);
+  uint64_t* full = bars;                    // [STAGES]  TMA -> MMA
+  uint64_t* empty = bars + STAGES;          // [STAGES]  MMA -> TMA
+  uint64_t* acc_full = bars + 2 * STAGES;   // [2]       MMA -> epilogue
+  uint64_t* acc_empty = acc_full + 2;       // [2]       epilogue -> MMA
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 4); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 2) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      if constexpr (SPLIT3) { tma_prefetch_desc(&tmA_lo); tma_prefetch_desc(&tmB_lo); }
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % p.tiles_m) * kBM, n0 = (tile / p.tiles_m) * BN;
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1u, p.status, 0x1u)) { ok = false; break; }
+          mbar_expect_tx(&full[stage], Cfg::STAGE_BYTES);
+          const uint32_t sA = smem_base + stage * Cfg::STAGE_BYTES;
+          const uint32_t sB = sA + Cfg::A_BYTES;
+          const int k0 = kb * p.bk;
+          for (int bx = 0; bx < p.a.boxes; ++bx) {
+            const int32_t c0 = p.a.mn_major ? m0 + bx * p.a.mn_step : k0;
+            const int32_t c1 = p.a.mn_major ? k0 : m0;
+            tma_load_2d(sA + bx * p.a.box_bytes, &tmA, c0, c1, &full[stage]);
+            if constexpr (SPLIT3) tma_load_2d(sA + Cfg::A_BYTES + Cfg::B_BYTES + bx * p.a.box_bytes, &tmA_lo, c0, c1, &full[stage]);
+          }
+          for (int bx = 0; bx < p.b.boxes; ++bx) {
+            const int32_t c0 = p.b.mn_major ? n0 + bx * p.b.mn_step : k0;
+            const int32_t c1 = p.b.mn_major ? k0 : n0;
+            tma_load_2d(sB + bx * p.b.box_bytes, &tmB, c0, c1, &full[stage]);
+            if constexpr (SPLIT3) tma_load_2d(sB + Cfg::A_BYTES + Cfg::B_BYTES + bx * p.b.box_bytes, &tmB_lo, c0, c1, &full[stage]);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1u, p.status, 0x2u)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!mbar_wait(&full[stage], phase, p.status, 0x4u)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sA = smem_base + stage * Cfg::STAGE_BYTES;
+          const uint32_t sB = sA + Cfg::A_BYTES;
+          const uint32_t a_lo32 = ((sA >> 4) & 0x3FFFu) | p.a.desc_lbo;
+          const uint32_t b_lo32 = ((sB >> 4) & 0x3FFFu) | p.b.desc_lbo;
+          constexpr uint32_t LO_OFF = (Cfg::A_BYTES + Cfg::B_BYTES) >> 4;
+#pragma unroll
+          for (int ks = 0; ks < kKSteps; ++ks) {
+            const uint64_t ad = ((uint64_t)p.a.desc_hi << 32) | (uint64_t)(a_lo32 + ks * p.a.k_advance);
+            const uint64_t bd = ((uint64_t)p.b.desc_hi << 32) | (uint64_t)(b_lo32 + ks * p.b.k_advance);
+            umma<TF32>(d_tmem, ad, bd, p.idesc, (kb | ks) != 0 ? 1u : 0u);
+            if constexpr (SPLIT3) {
+              umma<TF32>(d_tmem, ad + LO_OFF, bd, p.idesc, 1u);  // lo(A) * hi(B)
+              umma<TF32>(d_tmem, ad, bd + LO_OFF, p.idesc, 1u);  // hi(A) * lo(B)
+            }
+          }
+          umma_commit(&empty[stage]);  // frees the smem stage once these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) umma_commit(&acc_full[acc]);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  } else if (warp >= 4) {
+    // ---------------- epilogue ----------------
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    uint32_t acc = 0, acc_phase = 0;
+    OutT* D = reinterpret_cast<OutT*>(p.D);
+    OutT* P = reinterpret_cast<OutT*>(p.preact);
+    const OutT* bias = reinterpret_cast<const OutT*>(p.bias);
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      const int m0 = (tile % p.tiles_m) * kBM, n0 = (tile / p.tiles_m) * BN;
+      if (!mbar_wait(&acc_full[acc], acc_phase, p.status, 0x8u)) { ok = false; break; }
+      tc_fence_after();
+      const int64_t m = (int64_t)m0 + q * 32 + lane;
+      const bool m_ok = m < p.Mm;
+      float bv = 0.f;
+      if (bias != nullptr && m_ok) bv = to_f32(bias[m]);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c * 32, r);
+        tmem_ld_wait();
+        if (m_ok) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int64_t n = (int64_t)n0 + c * 32 + j;
+            if (n < p.Nn) {
+              float v = __uint_as_float(r[j]) + bv;
+              const int64_t off = n * p.ldd + m;
+              if (P != nullptr) P[off] = from_f32<OutT>(v);
+              v = act_apply_any<ACT, FAST>(p.act, v);
+              if (p.accumulate) v += to_f32(D[off]);
+              D[off] = from_f32<OutT>(v);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    // After an expired wait, copies may still be landing: give them a bounded moment first.
+    if (*reinterpret_cast<volatile unsigned int*>(p.status) != 0) {
+      for (int i = 0; i < 64; ++i) __nanosleep(2000);
+    }
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ----------------------------------------------------------------------------------------------
+// host side
+// ----------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  });
+  return fn;
+}
+
+// 2-D map over an operand. K-major: dims {K, MN}; MN-major: dims {MN, K}. Box = 128-byte rows.
+static bool make_operand_map(CUtensorMap* map, const GemmOperand& op, int64_t mn, int64_t kc, int elem_bytes,
+                             int tile_mn, int bk, OperandPlan* plan, bool tf32) {
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) return false;
+  const int row_elems = 128 / elem_bytes;  // elements in a 128-byte row
+  cuuint64_t dims[2];
+  cuuint32_t box[2];
+  if (op.mn_major) {
+    dims[0] = (cuuint64_t)mn; dims[1] = (cuuint64_t)kc;
+    box[0] = (cuuint32_t)row_elems; box[1] = (cuuint32_t)bk;
+    plan->boxes = tile_mn / row_elems;
+    plan->box_bytes = bk * 128;
+    plan->mn_step = row_elems;
+    plan->mn_major = 1;
+    // canonical MN-major SW128 layout: 8 k-rows of 128 bytes form an atom (SBO = 1024 between
+    // atoms along K); the next 128 bytes of MN live in the next box (LBO = box_bytes).
+    plan->desc_lbo = ((uint32_t)(plan->box_bytes >> 4) & 0x3FFFu) << 16;
+    plan->k_advance = (uint32_t)(((tf32 ? 8 : 16) * 128) >> 4);
+  } else {
+    dims[0] = (cuuint64_t)kc; dims[1] = (cuuint64_t)mn;
+    box[0] = (cuuint32_t)row_elems; box[1] = (cuuint32_t)tile_mn;
+    plan->boxes = 1;
+    plan->box_bytes = tile_mn * 128;
+    plan->mn_step = 0;
+    plan->mn_major = 0;
+    plan->desc_lbo = (1u & 0x3FFFu) << 16;  // ignored for swizzled K-major layouts
+    plan->k_advance = 32 >> 4;              // 32 bytes of K per MMA step inside the 128-byte row
+  }
+  // SBO = 1024 bytes (8 rows x 128 bytes), descriptor version 1 (bits 46-47), SWIZZLE_128B (bits 61-63 = 2)
+  plan->desc_hi = (uint32_t)((1024u >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
+  cuuint64_t strides[1] = {(cuuint64_t)op.ld * (cuuint64_t)elem_bytes};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
+                   const_cast<void*>(op.ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+bool gemm_tc_supported(const void* D, int64_t ldd, GemmOperand A, GemmOperand B, int64_t Mm, int64_t Nn, int64_t Kc,
+                       int32_t dtype, int split3) {
+  (void)ldd;
+  if (Mm <= 0 || Nn <= 0 || Kc <= 0) return false;
+  if (Mm > 0x7FFFFFFF || Nn > 0x7FFFFFFF || Kc > 0x7FFFFFFF) return false;
+  const size_t es = dtype_size(dtype);
+  if (!aligned_to(D, es)) return false;
+  if (!(dtype == LB2_F32 && split3)) {  // the 3xTF32 route reads packed, aligned copies of its operands instead
+    if (!aligned_to(A.ptr, 16) || !aligned_to(B.ptr, 16)) return false;
+    if ((A.ld * (int64_t)es) % 16 != 0 || (B.ld * (int64_t)es) % 16 != 0) return false;
+  }
+  if (!encode_fn()) return false;
+  return true;
+}
+
+// hi = round-to-nearest tf32 of x, lo = x - hi (exact in fp32). The copies are packed: leading
+// dimension = rows rounded up to 4 elements (the 16-byte TMA stride rule).
+__global__ void __launch_bounds__(256) split_tf32_kernel(float* __restrict__ hi, float* __restrict__ lo,
+                                                         const float* __restrict__ x, int64_t rows, int64_t cols,
+                                                         int64_t ld_in, int64_t ld_out) {
+  const int64_t n = rows * cols;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t c = i / rows, r = i % rows;
+    const float v = x[c * ld_in + r];
+    uint32_t h;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(v));
+    const float hf = __uint_as_float(h);
+    hi[c * ld_out + r] = hf;
+    lo[c * ld_out + r] = v - hf;
+  }
+}
+
+static int64_t packed_ld(int64_t rows) { return (rows + 3) / 4 * 4; }
+static int64_t operand_rows(const GemmOperand& op, int64_t mn, int64_t kc) { return op.mn_major ? mn : kc; }
+static int64_t operand_cols(const GemmOperand& op, int64_t mn, int64_t kc) { return op.mn_major ? kc : mn; }
+static size_t operand_bytes(const GemmOperand& op, int64_t mn, int64_t kc) {
+  return align_up((size_t)packed_ld(operand_rows(op, mn, kc)) * (size_t)operand_cols(op, mn, kc) * sizeof(float), 256);
+}
+
+size_t gemm_tc_split_workspace_bytes(GemmOperand A, GemmOperand B, int64_t Mm, int64_t Nn, int64_t Kc) {
+  return 2 * operand_bytes(A, Mm, Kc) + 2 * operand_bytes(B, Nn, Kc);
+}
+
+template <int BN, bool TF32, bool SPLIT3, typename OutT>
+static int32_t tc_launch_cfg(const CUtensorMap& mA, const CUtensorMap& mB, const CUtensorMap& mAl, const CUtensorMap& mBl,
+                             const TcParams& p, cudaStream_t st) {
+  using Cfg = TcCfg<BN, TF32, SPLIT3>;
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  auto launch = [&](auto kernel) -> int32_t {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return fail(LB2_LAUNCH_FAIL, "gemm_tc: cannot reserve %d bytes of shared memory: %s", Cfg::SMEM_BYTES, cudaGetErrorString(e));
+    kernel<<<grid, kThreads, Cfg::SMEM_BYTES, st>>>(mA, mB, mAl, mBl, p);
+    LB2_CHECK_LAUNCH("gemm_tc");
+    return LB2_OK;
+  };
+  switch (p.act) {
+    case LB2_ACT_IDENTITY: return launch(gemm_tc_kernel<BN, TF32, SPLIT3, LB2_ACT_IDENTITY, OutT>);
+    case LB2_ACT_RELU: return launch(gemm_tc_kernel<BN, TF32, SPLIT3, LB2_ACT_RELU, OutT>);
+    case LB2_ACT_GELU_TANH: return launch(gemm_tc_kernel<BN, TF32, SPLIT3, LB2_ACT_GELU_TANH, OutT>);
+    default: return launch(gemm_tc_kernel<BN, TF32, SPLIT3, -1, OutT>);
+  }
+}
+
+int32_t gemm_tc_launch(void* D, int64_t ldd, GemmOperand A, GemmOperand B, int64_t Mm, int64_t Nn, int64_t Kc,
+                       int32_t dtype, int split3, const GemmEpilogue& epi, void* split_ws, cudaStream_t st) {
+  const bool tf32 = dtype == LB2_F32;
+  const int es = tf32 ? 4 : 2;
+  const int bk = 128 / es;
+  // BN = 256 halves the A-operand traffic per FLOP; BN = 128 keeps more tiles for small problems and
+  // leaves room for the doubled 3xTF32 stages.
+  const bool split = tf32 && split3;
+  int bn = 256;
+  if (split) bn = 128;
+  else if (((Mm + kBM - 1) / kBM) * ((Nn + 255) / 256) < sm_count()) bn = 128;
+
+  TcParams p{};
+  CUtensorMap mA, mB, mAl, mBl;
+  if (!split) {
+    if (!make_operand_map(&mA, A, Mm, Kc, es, kBM, bk, &p.a, tf32) || !make_operand_map(&mB, B, Nn, Kc, es, bn, bk, &p.b, tf32))
+      return fail(LB2_LAUNCH_FAIL, "gemm_tc: cuTensorMapEncodeTiled failed");
+    mAl = mA; mBl = mB;
+  } else {
+    LB2_REQUIRE(split_ws != nullptr && aligned_to(split_ws, 256), LB2_WORKSPACE_TOO_SMALL, "3xTF32 GEMM needs its split workspace");
+    uint8_t* w = static_cast<uint8_t*>(split_ws);
+    float* a_hi = reinterpret_cast<float*>(w); w += operand_bytes(A, Mm, Kc);
+    float* a_lo = reinterpret_cast<float*>(w); w += operand_bytes(A, Mm, Kc);
+    float* b_hi = reinterpret_cast<float*>(w); w += operand_bytes(B, Nn, Kc);
+    float* b_lo = reinterpret_cast<float*>(w);
+    const int64_t a_rows = operand_rows(A, Mm, Kc), a_cols = operand_cols(A, Mm, Kc);
+    const int64_t b_rows = operand_rows(B, Nn, Kc), b_cols = operand_cols(B, Nn, Kc);
+    const int g = sm_count() * 8;
+    split_tf32_kernel<<<g, 256, 0, st>>>(a_hi, a_lo, (const float*)A.ptr, a_rows, a_cols, A.ld, packed_ld(a_rows));
+    split_tf32_kernel<<<g, 256, 0, st>>>(b_hi, b_lo, (const float*)B.ptr, b_rows, b_cols, B.ld, packed_ld(b_rows));
+    LB2_CHECK_LAUNCH("split_tf32");
+    GemmOperand Ah = A, Al = A, Bh = B, Bl = B;
+    Ah.ptr = a_hi; Al.ptr = a_lo; Bh.ptr = b_hi; Bl.ptr = b_lo;
+    Ah.ld = Al.ld = packed_ld(a_rows);
+    Bh.ld = Bl.ld = packed_ld(b_rows);
+    OperandPlan dummy;
+    if (!make_operand_map(&mA, Ah, Mm, Kc, es, kBM, bk, &p.a, tf32) || !make_operand_map(&mAl, Al, Mm, Kc, es, kBM, bk, &dummy, tf32) ||
+        !make_operand_map(&mB, Bh, Nn, Kc, es, bn, bk, &p.b, tf32) || !make_operand_map(&mBl, Bl, Nn, Kc, es, bn, bk, &dummy, tf32))
+      return fail(LB2_LAUNCH_FAIL, "gemm_tc: cuTensorMapEncodeTiled failed (split operands)");
+  }
+  p.Mm = Mm; p.Nn = Nn; p.Kc = Kc;
+  p.bk = bk;
+  p.tiles_m = (int)((Mm + kBM - 1) / kBM);
+  p.tiles_n = (int)((Nn + bn - 1) / bn);
+  p.num_kb = (int)((Kc + bk - 1) / bk);
+  // instruction descriptor: D = f32 (bit 4), A/B format (bits 7-9 / 10-12: 1 = bf16, 2 = tf32),
+  // A/B major (bits 15 / 16: 1 = MN-major), N >> 3 (bits 17-22), M >> 4 (bits 24-28)
+  const uint32_t fmt = tf32 ? 2u : 1u;
+  p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((A.mn_major ? 1u : 0u) << 15) | ((B.mn_major ? 1u : 0u) << 16) |
+            ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+  p.D = D; p.ldd = ldd;
+  p.bias = epi.bias; p.preact = epi.preact; p.act = epi.act; p.accumulate = epi.accumulate;
+  p.status = device_status_word();
+  LB2_REQUIRE(p.status != nullptr, LB2_LAUNCH_FAIL, "gemm_tc: device status word unavailable");
+  if (tf32) {
+    if (split) return tc_launch_cfg<128, true, true, float>(mA, mB, mAl, mBl, p, st);
+    if (bn == 256) return tc_launch_cfg<256, true, false, float>(mA, mB, mAl, mBl, p, st);
+    return tc_launch_cfg<128, true, false, float>(mA, mB, mAl, mBl, p, st);
+  }
+  if (bn == 256) return tc_launch_cfg<256, false, false, __nv_bfloat16>(mA, mB, mAl, mBl, p, st);
+  return tc_launch_cfg<128, false, false, __nv_bfloat16>(mA, mB, mAl, mBl, p, st);
+}
+
+// ----------------------------------------------------------------------------------------------
+// dispatch between the tensor-core and CUDA-core kernels
+// ----------------------------------------------------------------------------------------------
+static bool use_tc(const void* D, int64_t ldd, GemmOperand A, GemmOperand B, int64_t Mm, int64_t Nn, int64_t Kc,
+                   int32_t dtype, uint32_t flags) {
+  if (flags & LB2_FLAG_FORCE_SIMT) return false;
+  if (Mm * Nn * Kc < (int64_t)64 * 64 * 64) return false;  // latency-bound either way; skip descriptor encoding
+  return gemm_tc_supported(D, ldd, A, B, Mm, Nn, Kc, dtype, (flags & LB2_FLAG_TF32_1X) ? 0 : 1);
+}
+
+size_t gemm_workspace_bytes(GemmOperand A, GemmOperand B, int64_t Mm, int64_t Nn, int64_t Kc, int32_t dtype,
+                            uint32_t flags) {
+  if (dtype != LB2_F32 || (flags & (LB2_FLAG_TF32_1X | LB2_FLAG_FORCE_SIMT))) return 0;
+  if (Mm <= 0 || Nn <= 0 || Kc <= 0) return 0;
+  return gemm_tc_split_workspace_bytes(A, B, Mm, Nn, Kc);
+}
+
+int32_t gemm_dispatch(void* D, int64_t ldd, GemmOperand A, GemmOperand B, int64_t Mm, int64_t Nn, int64_t Kc,
+                      int32_t dtype, uint32_t flags, const GemmEpilogue& epi, void* ws, size_t ws_bytes,
+                      cudaStream_t st) {
+  if (Mm == 0 || Nn == 0) return LB2_OK;
+  if (Kc > 0 && use_tc(D, ldd, A, B, Mm, Nn, Kc, dtype, flags)) {
+    const int split3 = (dtype == LB2_F32 && !(flags & LB2_FLAG_TF32_1X)) ? 1 : 0;
+    if (split3) {
+      const size_t need = gemm_tc_split_workspace_bytes(A, B, Mm, Nn, Kc);
+      LB2_REQUIRE(ws != nullptr && ws_bytes >= need, LB2_WORKSPACE_TOO_SMALL, "fp32 GEMM needs %zu bytes of workspace", need);
+    }
+    return gemm_tc_launch(D, ldd, A, B, Mm, Nn, Kc, dtype, split3, epi, ws, st);
+  }
+  return gemm_simt_launch(D, ldd, A, B, Mm, Nn, Kc, dtype, epi, st);
+}
+
+}  // namespace lb2

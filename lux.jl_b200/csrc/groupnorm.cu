@@ -1,0 +1,427 @@
+// LayerNorm and GroupNorm, forward and backward: bandwidth-bound kernels that normalise
+// contiguous "rows" (a LayerNorm row of D features; a GroupNorm group of S*C/G elements).
+//
+// HBM layout: Julia column-major, so the normalised extent is contiguous. Fast path: the whole
+// row is read ONCE with 128-bit loads into registers (NV vectors per thread), statistics are
+// taken with a two-pass (mean, then centred sum of squares) reduction over registers through
+// warp shuffles / shared memory, and the result is written with 128-bit stores — algorithmic
+// traffic only (read x, write y; backward: read x, dy, write dx). The backward fuses both of its
+// reductions (sum g, sum g*xhat) in one pass and accumulates the affine gradients on the side.
+// A generic multi-pass path (second and third reads served by L2) covers shapes the fast path
+// cannot take. All cross-CTA reductions are two-stage in a fixed order: deterministic.
+//
+// Algorithmic bytes per element: forward 2*sizeof(T), backward 3*sizeof(T).
+#include "norm_common.cuh"
+
+namespace lb2 {
+
+// =============================================================================================
+// GroupNorm: row = one (group, sample) block of L = S * Cg contiguous elements; channel of
+// element i is g*Cg + i / S.
+// =============================================================================================
+template <typename T, int ACT, bool AFFINE, int NV, int BT>
+__global__ void __launch_bounds__(BT) gn_fwd_cached_kernel(T* __restrict__ y, float* __restrict__ mean_out,
+                                                           float* __restrict__ inv_out, const T* __restrict__ x,
+                                                           const T* __restrict__ gamma, const T* __restrict__ beta,
+                                                           int64_t S, int64_t Cg, int64_t G, int64_t rows, float eps, int act_rt) {
+  constexpr bool FAST = sizeof(T) == 2;
+  constexpr int V = Vec16<T>::N;
+  __shared__ float red[32];
+  const int64_t L = S * Cg;
+  const float invL = 1.f / (float)L;
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const int64_t g = row % G;
+    const T* xr = x + row * L;
+    Vec16<T> xv[NV];
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int64_t i = ((int64_t)k * BT + threadIdx.x) * V;
+      if (i < L) {
+        xv[k] = load16_stream(xr + i);
+#pragma unroll
+        for (int j = 0; j < V; ++j) s += xv[k].get(j);
+      }
+    }
+    const float mean = block_sum(s, red) * invL;
+    float q = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int64_t i = ((int64_t)k * BT + threadIdx.x) * V;
+      if (i < L) {
+#pragma unroll
+        for (int j = 0; j < V; ++j) { float d = xv[k].get(j) - mean; q += d * d; }
+      }
+    }
+    const float var = block_sum(q, red) * invL;
+    const float inv = 1.f / sqrtf(var + eps);
+    if (threadIdx.x == 0) { mean_out[row] = mean; inv_out[row] = inv; }
+    T* yr = y + row * L;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int64_t i = ((int64_t)k * BT + threadIdx.x) * V;
+      if (i < L) {
+        float gp = inv, bp = -mean * inv;
+        if constexpr (AFFINE) {  // S % V == 0: one channel per vector
+          const int64_t c = g * Cg + i / S;
+          gp = to_f32(gamma[c]) * inv;
+          bp = to_f32(beta[c]) - mean * gp;
+        }
+        Vec16<T> o;
+#pragma unroll
+        for (int j = 0; j < V; ++j) o.set(j, act_apply_any<ACT, FAST>(act_rt, fmaf(xv[k].get(j), gp, bp)));
+        store16_stream(yr + i, o);
+      }
+    }
+  }
+}
+
+template <typename T, int ACT, bool AFFINE>
+__global__ void __launch_bounds__(512) gn_fwd_generic_kernel(T* __restrict__ y, float* __restrict__ mean_out,
+                                                             float* __restrict__ inv_out, const T* __restrict__ x,
+                                                             const T* __restrict__ gamma, const T* __restrict__ beta,
+                                                             int64_t S, int64_t Cg, int64_t G, int64_t rows, float eps, int act_rt) {
+  constexpr bool FAST = sizeof(T) == 2;
+  __shared__ float red[32];
+  const int64_t L = S * Cg;
+  const float invL = 1.f / (float)L;
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const int64_t g = row % G;
+    const T* xr = x + row * L;
+    float s = 0.f;
+    for (int64_t i = threadIdx.x; i < L; i += blockDim.x) s += to_f32(xr[i]);
+    const float mean = block_sum(s, red) * invL;
+    float q = 0.f;
+    for (int64_t i = threadIdx.x; i < L; i += blockDim.x) { float d = to_f32(xr[i]) - mean; q += d * d; }
+    const float var = block_sum(q, red) * invL;
+    const float inv = 1.f / sqrtf(var + eps);
+    if (threadIdx.x == 0) { mean_out[row] = mean; inv_out[row] = inv; }
+    T* yr = y + row * L;
+    for (int64_t i = threadIdx.x; i < L; i += blockDim.x) {
+      float gp = inv, bp = -mean * inv;
+      if constexpr (AFFINE) {
+        const int64_t c = g * Cg + i / S;
+        gp = to_f32(gamma[c]) * inv;
+        bp = to_f32(beta[c]) - mean * gp;
+      }
+      yr[i] = from_f32<T>(act_apply_any<ACT, FAST>(act_rt, fmaf(to_f32(xr[i]), gp, bp)));
+    }
+  }
+}
+
+// Backward. Per-channel sums ds[j] = sum_s d*xhat, db[j] = sum_s d (d = dy*act') are formed first
+// (they are also the affine-gradient contributions of this sample), the two group reductions
+// follow from them: sum g = sum_j gamma_j db[j], sum g*xhat = sum_j gamma_j ds[j].
+// chan_out: [B][C][2] fp32 per-sample channel sums for the finishing kernel.
+// Fast path needs S % (32*V) == 0 so that every warp-wide vector row lies in one channel.
+template <typename T, int ACT, bool AFFINE, int NV, int BT>
+__global__ void __launch_bounds__(BT) gn_bwd_cached_kernel(T* __restrict__ dx, float* __restrict__ chan_out,
+                                                           const T* __restrict__ dy, const T* __restrict__ x,
+                                                           const T* __restrict__ gamma, const T* __restrict__ beta,
+                                                           const float* __restrict__ mean_in,
+                                                           const float* __restrict__ inv_in, int64_t S, int64_t Cg,
+                                                           int64_t G, int64_t rows, int act_rt) {
+  constexpr bool FAST = sizeof(T) == 2;
+  constexpr int V = Vec16<T>::N;
+  constexpr int NW = BT / 32;
+  extern __shared__ float dyn[];            // ds[Cg], db[Cg]
+  __shared__ float slots[2][NV][NW];
+  __shared__ float red[32];
+  float* ds = dyn;
+  float* dbs = dyn + Cg;
+  const int64_t L = S * Cg;
+  const float invL = 1.f / (float)L;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t slots_per_chan = S / (32 * V);
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const int64_t g = row % G, n = row / G;
+    const T* xr = x + row * L;
+    const T* dyr = dy + row * L;
+    const float mean = mean_in[row], inv = inv_in[row];
+    Vec16<T> xv[NV];
+    float dv[NV][V];
+    __syncthreads();  // previous row's readers of ds/dbs/slots are done
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int64_t i = ((int64_t)k * BT + threadIdx.x) * V;
+      float a = 0.f, b = 0.f;
+      if (i < L) {
+        xv[k] = load16_stream(xr + i);
+        Vec16<T> gy = load16_stream(dyr + i);
+        float gp = inv, bp = -mean * inv;
+        if constexpr (AFFINE && ACT != LB2_ACT_IDENTITY) {
+          const int64_t c = g * Cg + i / S;
+          gp = to_f32(gamma[c]) * inv;
+          bp = to_f32(beta[c]) - mean * gp;
+        }
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          float d = gy.get(j);
+          if constexpr (ACT != LB2_ACT_IDENTITY) d *= act_grad_pre_any<ACT, FAST>(act_rt, fmaf(xv[k].get(j), gp, bp));
+          dv[k][j] = d;
+          a += d * ((xv[k].get(j) - mean) * inv);
+          b += d;
+        }
+      }
+      a = warp_sum(a);
+      b = warp_sum(b);
+      if (lane == 0) { slots[0][k][warp] = a; slots[1][k][warp] = b; }
+    }
+    __syncthreads();
+    // channel j owns slots_per_chan consecutive (k, warp) slots in element order
+    for (int64_t j = threadIdx.x; j < Cg; j += BT) {
+      float a = 0.f, b = 0.f;
+      const int64_t first = j * slots_per_chan;
+      for (int64_t q = 0; q < slots_per_chan; ++q) {
+        const int64_t sl = first + q;  // global warp-row index = k*NW + warp
+        a += slots[0][sl / NW][sl % NW];
+        b += slots[1][sl / NW][sl % NW];
+      }
+      ds[j] = a;
+      dbs[j] = b;
+      if constexpr (AFFINE) {
+        float* co = chan_out + ((n * (G * Cg)) + g * Cg + j) * 2;
+        co[0] = a;
+        co[1] = b;
+      }
+    }
+    __syncthreads();
+    float s1 = 0.f, s2 = 0.f;
+    for (int64_t j = threadIdx.x; j < Cg; j += BT) {
+      float gm = 1.f;
+      if constexpr (AFFINE) gm = to_f32(gamma[g * Cg + j]);
+      s1 += gm * dbs[j];
+      s2 += gm * ds[j];
+    }
+    const float m1 = block_sum(s1, red) * invL;
+    const float m2 = block_sum(s2, red) * invL;
+    T* dxr = dx + row * L;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int64_t i = ((int64_t)k * BT + threadIdx.x) * V;
+      if (i < L) {
+        float gm = 1.f;
+        if constexpr (AFFINE) gm = to_f32(gamma[g * Cg + i / S]);
+        Vec16<T> o;
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          const float xh = (xv[k].get(j) - mean) * inv;
+          o.set(j, inv * (dv[k][j] * gm - m1 - xh * m2));
+        }
+        store16_stream(dxr + i, o);
+      }
+    }
+  }
+}
+
+// Generic backward: one warp per channel for the per-channel sums, scalar accesses.
+template <typename T, int ACT, bool AFFINE>
+__global__ void __launch_bounds__(512) gn_bwd_generic_kernel(T* __restrict__ dx, float* __restrict__ chan_out,
+                                                             const T* __restrict__ dy, const T* __restrict__ x,
+                                                             const T* __restrict__ gamma, const T* __restrict__ beta,
+                                                             const float* __restrict__ mean_in,
+                                                             const float* __restrict__ inv_in, int64_t S, int64_t Cg,
+                                                             int64_t G, int64_t rows, int act_rt) {
+  constexpr bool FAST = sizeof(T) == 2;
+  extern __shared__ float dyn[];
+  __shared__ float red[32];
+  float* ds = dyn;
+  float* dbs = dyn + Cg;
+  const int64_t L = S * Cg;
+  const float invL = 1.f / (float)L;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const int64_t g = row % G, n = row / G;
+    const T* xr = x + row * L;
+    const T* dyr = dy + row * L;
+    const float mean = mean_in[row], inv = inv_in[row];
+    auto d_of = [&](int64_t i, int64_t c, float& xh) {
+      const float xv = to_f32(xr[i]);
+      xh = (xv - mean) * inv;
+      float d = to_f32(dyr[i]);
+      if constexpr (ACT != LB2_ACT_IDENTITY) {
+        float gp = inv, bp = -mean * inv;
+        if constexpr (AFFINE) { gp = to_f32(gamma[c]) * inv; bp = to_f32(beta[c]) - mean * gp; }
+        d *= act_grad_pre_any<ACT, FAST>(act_rt, fmaf(xv, gp, bp));
+      }
+      return d;
+    };
+    __syncthreads();
+    for (int64_t j = warp; j < Cg; j += nw) {
+      float a = 0.f, b = 0.f;
+      for (int64_t s = lane; s < S; s += 32) {
+        float xh;
+        const float d = d_of(j * S + s, g * Cg + j, xh);
+        a += d * xh;
+        b += d;
+      }
+      a = warp_sum(a);
+      b = warp_sum(b);
+      if (lane == 0) {
+        ds[j] = a;
+        dbs[j] = b;
+        if constexpr (AFFINE) {
+          float* co = chan_out + ((n * (G * Cg)) + g * Cg + j) * 2;
+          co[0] = a;
+          co[1] = b;
+        }
+      }
+    }
+    __syncthreads();
+    float s1 = 0.f, s2 = 0.f;
+    for (int64_t j = threadIdx.x; j < Cg; j += blockDim.x) {
+      float gm = 1.f;
+      if constexpr (AFFINE) gm = to_f32(gamma[g * Cg + j]);
+      s1 += gm * dbs[j];
+      s2 += gm * ds[j];
+    }
+    const float m1 = block_sum(s1, red) * invL;
+    const float m2 = block_sum(s2, red) * invL;
+    T* dxr = dx + row * L;
+    for (int64_t i = threadIdx.x; i < L; i += blockDim.x) {
+      const int64_t c = g * Cg + i / S;
+      float xh;
+      const float d = d_of(i, c, xh);
+      float gm = 1.f;
+      if constexpr (AFFINE) gm = to_f32(gamma[c]);
+      dxr[i] = from_f32<T>(inv * (d * gm - m1 - xh * m2));
+    }
+  }
+}
+
+// dgamma[c] = sum_n chan[n][c][0], dbeta[c] = sum_n chan[n][c][1]   (n ascending)
+template <typename T>
+__global__ void gn_finish_kernel(T* __restrict__ dgamma, T* __restrict__ dbeta, const float* __restrict__ chan,
+                                 int64_t C, int64_t B) {
+  const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  float sg = 0.f, sb = 0.f;
+  for (int64_t n = 0; n < B; ++n) {
+    sg += chan[(n * C + c) * 2];
+    sb += chan[(n * C + c) * 2 + 1];
+  }
+  dgamma[c] = from_f32<T>(sg);
+  dbeta[c] = from_f32<T>(sb);
+}
+
+template <typename T, int ACT, bool AFFINE>
+static int32_t gn_fwd_launch(T* y, float* sm, float* si, const T* x, const T* g, const T* b, int64_t S, int64_t C,
+                             int64_t G, int64_t B, float eps, int32_t act, cudaStream_t st) {
+  constexpr int V = Vec16<T>::N;
+  const int64_t Cg = C / G, L = S * Cg, rows = G * B;
+  const bool al = aligned_to(y, 16) && aligned_to(x, 16) && (S % V == 0);
+  const int sms = sm_count();
+  const int64_t vecs = L / V;
+  int grid = (int)(rows < (int64_t)sms * 4 ? rows : (int64_t)sms * 4);
+  if (al && vecs <= 256 * 8) {
+    const int nv = vecs <= 256 ? 1 : (vecs <= 512 ? 2 : (vecs <= 1024 ? 4 : 8));
+    if (nv == 1) gn_fwd_cached_kernel<T, ACT, AFFINE, 1, 256><<<grid, 256, 0, st>>>(y, sm, si, x, g, b, S, Cg, G, rows, eps, act);
+    else if (nv == 2) gn_fwd_cached_kernel<T, ACT, AFFINE, 2, 256><<<grid, 256, 0, st>>>(y, sm, si, x, g, b, S, Cg, G, rows, eps, act);
+    else if (nv == 4) gn_fwd_cached_kernel<T, ACT, AFFINE, 4, 256><<<grid, 256, 0, st>>>(y, sm, si, x, g, b, S, Cg, G, rows, eps, act);
+    else gn_fwd_cached_kernel<T, ACT, AFFINE, 8, 256><<<grid, 256, 0, st>>>(y, sm, si, x, g, b, S, Cg, G, rows, eps, act);
+  } else if (al && vecs <= 512 * 8) {
+    grid = (int)(rows < (int64_t)sms * 2 ? rows : (int64_t)sms * 2);
+    gn_fwd_cached_kernel<T, ACT, AFFINE, 8, 512><<<grid, 512, 0, st>>>(y, sm, si, x, g, b, S, Cg, G, rows, eps, act);
+  } else if (al && vecs <= 1024 * 8) {
+    grid = (int)(rows < (int64_t)sms ? rows : (int64_t)sms);
+    gn_fwd_cached_kernel<T, ACT, AFFINE, 8, 1024><<<grid, 1024, 0, st>>>(y, sm, si, x, g, b, S, Cg, G, rows, eps, act);
+  } else {
+    gn_fwd_generic_kernel<T, ACT, AFFINE><<<grid, 512, 0, st>>>(y, sm, si, x, g, b, S, Cg, G, rows, eps, act);
+  }
+  LB2_CHECK_LAUNCH("groupnorm_fwd");
+  return LB2_OK;
+}
+
+template <typename T, int ACT, bool AFFINE>
+static int32_t gn_bwd_launch(T* dx, T* dg, T* db, const T* dy, const T* x, const T* g, const T* b, const float* sm,
+                             const float* si, int64_t S, int64_t C, int64_t G, int64_t B, float* ws, int32_t act, cudaStream_t st) {
+  constexpr int V = Vec16<T>::N;
+  const int64_t Cg = C / G, L = S * Cg, rows = G * B;
+  const size_t dyn = (size_t)Cg * 2 * sizeof(float);
+  LB2_REQUIRE(dyn <= 40 * 1024, LB2_BAD_SHAPE, "groupnorm backward supports at most 5120 channels per group");
+  const bool al = aligned_to(dx, 16) && aligned_to(dy, 16) && aligned_to(x, 16) && (S % (32 * V) == 0);
+  const int sms = sm_count();
+  const int64_t vecs = L / V;
+  int grid = (int)(rows < (int64_t)sms * 2 ? rows : (int64_t)sms * 2);
+  if (al && vecs <= 512 * 4) {
+    const int nv = vecs <= 512 ? 1 : (vecs <= 1024 ? 2 : 4);
+    if (nv == 1) gn_bwd_cached_kernel<T, ACT, AFFINE, 1, 512><<<grid, 512, dyn, st>>>(dx, ws, dy, x, g, b, sm, si, S, Cg, G, rows, act);
+    else if (nv == 2) gn_bwd_cached_kernel<T, ACT, AFFINE, 2, 512><<<grid, 512, dyn, st>>>(dx, ws, dy, x, g, b, sm, si, S, Cg, G, rows, act);
+    else gn_bwd_cached_kernel<T, ACT, AFFINE, 4, 512><<<grid, 512, dyn, st>>>(dx, ws, dy, x, g, b, sm, si, S, Cg, G, rows, act);
+  } else if (al && vecs <= 1024 * 4) {
+    grid = (int)(rows < (int64_t)sms ? rows : (int64_t)sms);
+    gn_bwd_cached_kernel<T, ACT, AFFINE, 4, 1024><<<grid, 1024, dyn, st>>>(dx, ws, dy, x, g, b, sm, si, S, Cg, G, rows, act);
+  } else {
+    gn_bwd_generic_kernel<T, ACT, AFFINE><<<grid, 512, dyn, st>>>(dx, ws, dy, x, g, b, sm, si, S, Cg, G, rows, act);
+  }
+  LB2_CHECK_LAUNCH("groupnorm_bwd");
+  if constexpr (AFFINE) {
+    gn_finish_kernel<T><<<(unsigned)((C + 127) / 128), 128, 0, st>>>(dg, db, ws, C, B);
+    LB2_CHECK_LAUNCH("groupnorm_bwd_finish");
+  }
+  return LB2_OK;
+}
+
+}  // namespace lb2
+
+using namespace lb2;
+
+extern "C" {
+
+int32_t lb2_groupnorm_fwd(void* y, float* save_mean, float* save_invstd, const void* x, const void* gamma,
+                          const void* beta, int64_t S, int64_t C, int64_t G, int64_t B, double eps, int32_t dtype,
+                          int32_t act, void* stream) {
+  LB2_REQUIRE(S >= 0 && C >= 0 && B >= 0 && G >= 1, LB2_BAD_SHAPE, "bad extent");
+  LB2_REQUIRE(C % G == 0, LB2_BAD_SHAPE, "number of channels (%lld) must be divisible by groups (%lld)", (long long)C, (long long)G);
+  if (S == 0 || C == 0 || B == 0) return LB2_OK;
+  int32_t rc = check_norm_common(y, x, gamma, beta, save_mean, save_invstd, dtype, act);
+  if (rc != LB2_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  LB2_DISPATCH_DTYPE(dtype, {
+    LB2_DISPATCH_ACT3(act, {
+      if (gamma) return gn_fwd_launch<T, ACT, true>((T*)y, save_mean, save_invstd, (const T*)x, (const T*)gamma, (const T*)beta, S, C, G, B, (float)eps, act, st);
+      else return gn_fwd_launch<T, ACT, false>((T*)y, save_mean, save_invstd, (const T*)x, nullptr, nullptr, S, C, G, B, (float)eps, act, st);
+    });
+  });
+  return LB2_OK;
+}
+
+size_t lb2_groupnorm_bwd_workspace_bytes(int64_t S, int64_t C, int64_t G, int64_t B) {
+  (void)S; (void)G;
+  if (C <= 0 || B <= 0) return 0;
+  return align_up((size_t)C * (size_t)B * 2 * sizeof(float), 256);
+}
+
+int32_t lb2_groupnorm_bwd(void* dx, void* dgamma, void* dbeta, const void* dy, const void* x, const void* gamma,
+                          const void* beta, const float* save_mean, const float* save_invstd, int64_t S, int64_t C,
+                          int64_t G, int64_t B, int32_t dtype, int32_t act, void* workspace, size_t workspace_bytes,
+                          void* stream) {
+  LB2_REQUIRE(S >= 0 && C >= 0 && B >= 0 && G >= 1, LB2_BAD_SHAPE, "bad extent");
+  LB2_REQUIRE(C % G == 0, LB2_BAD_SHAPE, "number of channels (%lld) must be divisible by groups (%lld)", (long long)C, (long long)G);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (S == 0 || C == 0 || B == 0) {
+    if (C > 0 && dgamma && valid_dtype(dtype)) {
+      cudaMemsetAsync(dgamma, 0, (size_t)C * dtype_size(dtype), st);
+      cudaMemsetAsync(dbeta, 0, (size_t)C * dtype_size(dtype), st);
+    }
+    return LB2_OK;
+  }
+  int32_t rc = check_norm_common(dx, x, gamma, beta, save_mean, save_invstd, dtype, act);
+  if (rc != LB2_OK) return rc;
+  LB2_REQUIRE(dy != nullptr, LB2_BAD_ARG, "dy is null");
+  LB2_REQUIRE(!gamma || (dgamma && dbeta), LB2_BAD_ARG, "dgamma/dbeta required when scale is given");
+  if (gamma) {
+    LB2_REQUIRE(workspace && workspace_bytes >= lb2_groupnorm_bwd_workspace_bytes(S, C, G, B), LB2_WORKSPACE_TOO_SMALL,
+                "workspace of %zu bytes needed", lb2_groupnorm_bwd_workspace_bytes(S, C, G, B));
+    LB2_REQUIRE(aligned_to(workspace, 16), LB2_BAD_ALIGN, "workspace must be 16-byte aligned");
+  }
+  LB2_DISPATCH_DTYPE(dtype, {
+    LB2_DISPATCH_ACT3(act, {
+      if (gamma) return gn_bwd_launch<T, ACT, true>((T*)dx, (T*)dgamma, (T*)dbeta, (const T*)dy, (const T*)x, (const T*)gamma, (const T*)beta, save_mean, save_invstd, S, C, G, B, (float*)workspace, act, st);
+      else return gn_bwd_launch<T, ACT, false>((T*)dx, nullptr, nullptr, (const T*)dy, (const T*)x, nullptr, nullptr, save_mean, save_invstd, S, C, G, B, (float*)workspace, act, st);
+    });
+  });
+  return LB2_OK;
+}
+
+}  // extern "C"

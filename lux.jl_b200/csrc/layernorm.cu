@@ -1,0 +1,456 @@
+// LayerNorm and GroupNorm, forward and backward: bandwidth-bound kernels that normalise
+// contiguous "rows" (a LayerNorm row of D features; a GroupNorm group of S*C/G elements).
+//
+// HBM layout: Julia column-major, so the normalised extent is contiguous. Fast path: the whole
+// row is read ONCE with 128-bit loads into registers (NV vectors per thread), statistics are
+// taken with a two-pass (mean, then centred sum of squares) reduction over registers through
+// warp shuffles / shared memory, and the result is written with 128-bit stores — algorithmic
+// traffic only (read x, write y; backward: read x, dy, write dx). The backward fuses both of its
+// reductions (sum g, sum g*xhat) in one pass and accumulates the affine gradients on the side.
+// A generic multi-pass path (second and third reads served by L2) covers shapes the fast path
+// cannot take. All cross-CTA reductions are two-stage in a fixed order: deterministic.
+//
+// Algorithmic bytes per element: forward 2*sizeof(T), backward 3*sizeof(T).
+#include "norm_common.cuh"
+
+namespace lb2 {
+
+// =============================================================================================
+// LayerNorm
+// =============================================================================================
+// RT = threads per row (32: one warp per row, 8 rows per CTA; 256/512: one CTA per row).
+template <typename T, int ACT, bool AFFINE, int RT, int NV, int BT>
+__global__ void __launch_bounds__(BT) ln_fwd_cached_kernel(T* __restrict__ y, float* __restrict__ mean_out,
+                                                           float* __restrict__ inv_out, const T* __restrict__ x,
+                                                           const T* __restrict__ gamma, const T* __restrict__ beta,
+                                                           int64_t D, int64_t R, float eps, int act_rt) {
+  constexpr bool FAST = sizeof(T) == 2;
+  constexpr int V = Vec16<T>::N;
+  constexpr int ROWS = BT / RT;
+  __shared__ float red[32];
+  const int t = threadIdx.x % RT, slot = threadIdx.x / RT;
+  Vec16<T> gv[NV], bv[NV];
+  if constexpr (AFFINE) {
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int64_t i = ((int64_t)k * RT + t) * V;
+      if (i < D) { gv[k] = load16(gamma + i); bv[k] = load16(beta + i); }
+    }
+  }
+  const float invD = 1.f / (float)D;
+  for (int64_t row = (int64_t)blockIdx.x * ROWS + slot; row < R; row += (int64_t)gridDim.x * ROWS) {
+    const T* xr = x + row * D;
+    Vec16<T> xv[NV];
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int64_t i = ((int64_t)k * RT + t) * V;
+      if (i < D) {
+        xv[k] = load16_stream(xr + i);
+#pragma unroll
+        for (int j = 0; j < V; ++j) s += xv[k].get(j);
+      }
+    }
+    const float mean = row_sum<RT>(s, red) * invD;
+    float q = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int64_t i = ((int64_t)k * RT + t) * V;
+      if (i < D) {
+#pragma unroll
+        for (int j = 0; j < V; ++j) { float d = xv[k].get(j) - mean; q += d * d; }
+      }
+    }
+    const float var = row_sum<RT>(q, red) * invD;
+    const float inv = 1.f / sqrtf(var + eps);
+    if (t == 0) { mean_out[row] = mean; inv_out[row] = inv; }
+    T* yr = y + row * D;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int64_t i = ((int64_t)k * RT + t) * V;
+      if (i < D) {
+        Vec16<T> o;
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          float gp = inv, bp = -mean * inv;
+          if constexpr (AFFINE) { gp = gv[k].get(j) * inv; bp = bv[k].get(j) - mean * gp; }
+          o.set(j, act_apply_any<ACT, FAST>(act_rt, fmaf(xv[k].get(j), gp, bp)));
+        }
+        store16_stream(yr + i, o);
+      }
+    }
+  }
+}
+
+// Generic: one CTA per row, scalar accesses, three passes (passes 2 and 3 hit L1/L2).
+template <typename T, int ACT, bool AFFINE>
+__global__ void __launch_bounds__(256) ln_fwd_generic_kernel(T* __restrict__ y, float* __restrict__ mean_out,
+                                                             float* __restrict__ inv_out, const T* __restrict__ x,
+                                                             const T* __restrict__ gamma, const T* __restrict__ beta,
+                                                             int64_t D, int64_t R, float eps, int act_rt) {
+  constexpr bool FAST = sizeof(T) == 2;
+  __shared__ float red[32];
+  const float invD = 1.f / (float)D;
+  for (int64_t row = blockIdx.x; row < R; row += gridDim.x) {
+    const T* xr = x + row * D;
+    float s = 0.f;
+    for (int64_t i = threadIdx.x; i < D; i += blockDim.x) s += to_f32(xr[i]);
+    const float mean = block_sum(s, red) * invD;
+    float q = 0.f;
+    for (int64_t i = threadIdx.x; i < D; i += blockDim.x) { float d = to_f32(xr[i]) - mean; q += d * d; }
+    const float var = block_sum(q, red) * invD;
+    const float inv = 1.f / sqrtf(var + eps);
+    if (threadIdx.x == 0) { mean_out[row] = mean; inv_out[row] = inv; }
+    T* yr = y + row * D;
+    for (int64_t i = threadIdx.x; i < D; i += blockDim.x) {
+      float gp = inv, bp = -mean * inv;
+      if constexpr (AFFINE) { gp = to_f32(gamma[i]) * inv; bp = to_f32(beta[i]) - mean * gp; }
+      yr[i] = from_f32<T>(act_apply_any<ACT, FAST>(act_rt, fmaf(to_f32(xr[i]), gp, bp)));
+    }
+  }
+}
+
+// Backward, cached. partial: [gridDim.x][2][D] fp32 (dgamma then dbeta) when AFFINE.
+template <typename T, int ACT, bool AFFINE, int RT, int NV, int BT>
+__global__ void __launch_bounds__(BT) ln_bwd_cached_kernel(T* __restrict__ dx, float* __restrict__ partial,
+                                                           const T* __restrict__ dy, const T* __restrict__ x,
+                                                           const T* __restrict__ gamma, const T* __restrict__ beta,
+                                                           const float* __restrict__ mean_in,
+                                                           const float* __restrict__ inv_in, int64_t D, int64_t R, int act_rt) {
+  constexpr bool FAST = sizeof(T) == 2;
+  constexpr int V = Vec16<T>::N;
+  constexpr int ROWS = BT / RT;
+  __shared__ float red[32];
+  const int t = threadIdx.x % RT, slot = threadIdx.x / RT;
+  Vec16<T> gv[NV], bv[NV];
+  float adg[NV][V], adb[NV][V];
+  if constexpr (AFFINE) {
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int64_t i = ((int64_t)k * RT + t) * V;
+      if (i < D) { gv[k] = load16(gamma + i); bv[k] = load16(beta + i); }
+#pragma unroll
+      for (int j = 0; j < V; ++j) { adg[k][j] = 0.f; adb[k][j] = 0.f; }
+    }
+  }
+  const float invD = 1.f / (float)D;
+  for (int64_t row = (int64_t)blockIdx.x * ROWS + slot; row < R; row += (int64_t)gridDim.x * ROWS) {
+    const T* xr = x + row * D;
+    const T* dyr = dy + row * D;
+    const float mean = mean_in[row], inv = inv_in[row];
+    Vec16<T> xv[NV], gy[NV];  // gy is overwritten in place with g = dy*act'*gamma (kept in fp32 bits for f32)
+    float gf[NV][V];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int64_t i = ((int64_t)k * RT + t) * V;
+      if (i < D) {
+        xv[k] = load16_stream(xr + i);
+        gy[k] = load16_stream(dyr + i);
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          const float xh = (xv[k].get(j) - mean) * inv;
+          float d = gy[k].get(j);
+          if constexpr (ACT != LB2_ACT_IDENTITY) {
+            float gp = inv, bp = -mean * inv;
+            if constexpr (AFFINE) { gp = gv[k].get(j) * inv; bp = bv[k].get(j) - mean * gp; }
+            d *= act_grad_pre_any<ACT, FAST>(act_rt, fmaf(xv[k].get(j), gp, bp));
+          }
+          float g = d;
+          if constexpr (AFFINE) {
+            adg[k][j] += d * xh;
+            adb[k][j] += d;
+            g = d * gv[k].get(j);
+          }
+          gf[k][j] = g;
+          s1 += g;
+          s2 += g * xh;
+        }
+      }
+    }
+    // both reductions of the backward in one pass over registers
+    const float m1 = row_sum<RT>(s1, red) * invD;
+    const float m2 = row_sum<RT>(s2, red) * invD;
+    T* dxr = dx + row * D;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int64_t i = ((int64_t)k * RT + t) * V;
+      if (i < D) {
+        Vec16<T> o;
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          const float xh = (xv[k].get(j) - mean) * inv;
+          o.set(j, inv * (gf[k][j] - m1 - xh * m2));
+        }
+        store16_stream(dxr + i, o);
+      }
+    }
+  }
+  if constexpr (AFFINE) {
+    float* pg = partial + (int64_t)blockIdx.x * 2 * D;
+    float* pb = pg + D;
+    if constexpr (ROWS == 1) {
+#pragma unroll
+      for (int k = 0; k < NV; ++k) {
+        const int64_t i = ((int64_t)k * RT + t) * V;
+        if (i < D) {
+#pragma unroll
+          for (int j = 0; j < V; ++j) { pg[i + j] = adg[k][j]; pb[i + j] = adb[k][j]; }
+        }
+      }
+    } else {
+      // warp-per-row: fold the CTA's row slots through shared memory in slot order
+      __shared__ float fold[ROWS][32 * V + 1];
+      for (int pass = 0; pass < 2; ++pass) {
+#pragma unroll
+        for (int k = 0; k < NV; ++k) {
+          __syncthreads();
+#pragma unroll
+          for (int j = 0; j < V; ++j) fold[slot][t * V + j] = pass == 0 ? adg[k][j] : adb[k][j];
+          __syncthreads();
+          for (int col = threadIdx.x; col < 32 * V; col += BT) {
+            float s = 0.f;
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r) s += fold[r][col];
+            const int64_t i = (int64_t)k * RT * V + col;
+            if (i < D) (pass == 0 ? pg : pb)[i] = s;
+          }
+        }
+      }
+    }
+  }
+}
+
+// Backward, generic: one CTA per row; affine-gradient partials accumulate in the workspace rows
+// owned by this CTA (each feature is always touched by the same thread: no race).
+template <typename T, int ACT, bool AFFINE>
+__global__ void __launch_bounds__(256) ln_bwd_generic_kernel(T* __restrict__ dx, float* __restrict__ partial,
+                                                             const T* __restrict__ dy, const T* __restrict__ x,
+                                                             const T* __restrict__ gamma, const T* __restrict__ beta,
+                                                             const float* __restrict__ mean_in,
+                                                             const float* __restrict__ inv_in, int64_t D, int64_t R, int act_rt) {
+  constexpr bool FAST = sizeof(T) == 2;
+  __shared__ float red[32];
+  float* pg = partial + (int64_t)blockIdx.x * 2 * D;
+  float* pb = pg + D;
+  if constexpr (AFFINE) {
+    for (int64_t i = threadIdx.x; i < D; i += blockDim.x) { pg[i] = 0.f; pb[i] = 0.f; }
+  }
+  const float invD = 1.f / (float)D;
+  for (int64_t row = blockIdx.x; row < R; row += gridDim.x) {
+    const T* xr = x + row * D;
+    const T* dyr = dy + row * D;
+    const float mean = mean_in[row], inv = inv_in[row];
+    auto g_of = [&](int64_t i, float& xh, float& d) {
+      const float xv = to_f32(xr[i]);
+      xh = (xv - mean) * inv;
+      d = to_f32(dyr[i]);
+      if constexpr (ACT != LB2_ACT_IDENTITY) {
+        float gp = inv, bp = -mean * inv;
+        if constexpr (AFFINE) { gp = to_f32(gamma[i]) * inv; bp = to_f32(beta[i]) - mean * gp; }
+        d *= act_grad_pre_any<ACT, FAST>(act_rt, fmaf(xv, gp, bp));
+      }
+      float g = d;
+      if constexpr (AFFINE) g = d * to_f32(gamma[i]);
+      return g;
+    };
+    float s1 = 0.f, s2 = 0.f;
+    for (int64_t i = threadIdx.x; i < D; i += blockDim.x) {
+      float xh, d;
+      const float g = g_of(i, xh, d);
+      s1 += g;
+      s2 += g * xh;
+      if constexpr (AFFINE) { pg[i] += d * xh; pb[i] += d; }
+    }
+    const float m1 = block_sum(s1, red) * invD;
+    const float m2 = block_sum(s2, red) * invD;
+    T* dxr = dx + row * D;
+    for (int64_t i = threadIdx.x; i < D; i += blockDim.x) {
+      float xh, d;
+      const float g = g_of(i, xh, d);
+      dxr[i] = from_f32<T>(inv * (g - m1 - xh * m2));
+    }
+  }
+}
+
+// out[i] = sum_k partial[k][which][i]   (k in launch order)
+template <typename T>
+__global__ void ln_finish_kernel(T* __restrict__ dgamma, T* __restrict__ dbeta, const float* __restrict__ partial,
+                                 int64_t D, int parts) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= D) return;
+  float sg = 0.f, sb = 0.f;
+  for (int k = 0; k < parts; ++k) {
+    sg += partial[((int64_t)k * 2) * D + i];
+    sb += partial[((int64_t)k * 2 + 1) * D + i];
+  }
+  dgamma[i] = from_f32<T>(sg);
+  dbeta[i] = from_f32<T>(sb);
+}
+
+struct LnPlan {
+  bool cached;
+  int rt, nv, bt, grid;
+};
+
+template <typename T> static LnPlan ln_plan(int64_t D, int64_t R, bool aligned, bool bwd) {
+  constexpr int V = Vec16<T>::N;
+  LnPlan p{};
+  const int sms = sm_count();
+  p.cached = aligned && (D % V == 0);
+  const int64_t vecs = D / V;
+  const int max_nv = bwd ? 4 : 8;
+  if (p.cached && vecs <= 32 * 4) {  // small rows: one warp per row
+    p.rt = 32; p.bt = 256;
+    p.nv = vecs <= 32 ? 1 : (vecs <= 64 ? 2 : 4);
+    int64_t ctas = (R + 7) / 8;
+    p.grid = (int)(ctas < (int64_t)sms * 8 ? ctas : (int64_t)sms * 8);
+  } else if (p.cached && vecs <= 256 * max_nv) {
+    p.rt = 256; p.bt = 256;
+    p.nv = vecs <= 256 ? 1 : (vecs <= 512 ? 2 : (vecs <= 1024 ? 4 : 8));
+    p.grid = (int)(R < (int64_t)sms * 4 ? R : (int64_t)sms * 4);
+  } else if (p.cached && vecs <= 512 * max_nv) {
+    p.rt = 512; p.bt = 512;
+    p.nv = vecs <= 512 * 4 ? 4 : 8;
+    p.grid = (int)(R < (int64_t)sms * 2 ? R : (int64_t)sms * 2);
+  } else {
+    p.cached = false;
+    p.rt = 256; p.bt = 256; p.nv = 0;
+    p.grid = (int)(R < (int64_t)sms * 4 ? R : (int64_t)sms * 4);
+  }
+  if (p.grid < 1) p.grid = 1;
+  return p;
+}
+
+#define LN_LAUNCH_CACHED(KERNEL, RT_, NV_, BT_, ...)                                   \
+  KERNEL<T, ACT, AFFINE, RT_, NV_, BT_><<<p.grid, BT_, 0, st>>>(__VA_ARGS__, act)
+
+#define LN_SWITCH(KERNEL, ...)                                                          \
+  if (p.rt == 32) {                                                                     \
+    if (p.nv == 1) LN_LAUNCH_CACHED(KERNEL, 32, 1, 256, __VA_ARGS__);                   \
+    else if (p.nv == 2) LN_LAUNCH_CACHED(KERNEL, 32, 2, 256, __VA_ARGS__);              \
+    else LN_LAUNCH_CACHED(KERNEL, 32, 4, 256, __VA_ARGS__);                             \
+  } else if (p.rt == 256) {                                                             \
+    if (p.nv == 1) LN_LAUNCH_CACHED(KERNEL, 256, 1, 256, __VA_ARGS__);                  \
+    else if (p.nv == 2) LN_LAUNCH_CACHED(KERNEL, 256, 2, 256, __VA_ARGS__);             \
+    else if (p.nv == 4) LN_LAUNCH_CACHED(KERNEL, 256, 4, 256, __VA_ARGS__);             \
+    else LN_LAUNCH_CACHED(KERNEL, 256, 8, 256, __VA_ARGS__);                            \
+  } else {                                                                              \
+    if (p.nv == 4) LN_LAUNCH_CACHED(KERNEL, 512, 4, 512, __VA_ARGS__);                  \
+    else LN_LAUNCH_CACHED(KERNEL, 512, 8, 512, __VA_ARGS__);                            \
+  }
+
+// the backward never caches more than 4 vectors per thread (see ln_plan)
+#define LN_SWITCH_BWD(KERNEL, ...)                                                      \
+  if (p.rt == 32) {                                                                     \
+    if (p.nv == 1) LN_LAUNCH_CACHED(KERNEL, 32, 1, 256, __VA_ARGS__);                   \
+    else if (p.nv == 2) LN_LAUNCH_CACHED(KERNEL, 32, 2, 256, __VA_ARGS__);              \
+    else LN_LAUNCH_CACHED(KERNEL, 32, 4, 256, __VA_ARGS__);                             \
+  } else if (p.rt == 256) {                                                             \
+    if (p.nv == 1) LN_LAUNCH_CACHED(KERNEL, 256, 1, 256, __VA_ARGS__);                  \
+    else if (p.nv == 2) LN_LAUNCH_CACHED(KERNEL, 256, 2, 256, __VA_ARGS__);             \
+    else LN_LAUNCH_CACHED(KERNEL, 256, 4, 256, __VA_ARGS__);                            \
+  } else {                                                                              \
+    LN_LAUNCH_CACHED(KERNEL, 512, 4, 512, __VA_ARGS__);                                 \
+  }
+
+template <typename T, int ACT, bool AFFINE>
+static int32_t ln_fwd_launch(T* y, float* sm, float* si, const T* x, const T* g, const T* b, int64_t D, int64_t R,
+                             float eps, int32_t act, cudaStream_t st) {
+  const bool al = aligned_to(y, 16) && aligned_to(x, 16) && (!g || (aligned_to(g, 16) && aligned_to(b, 16)));
+  const LnPlan p = ln_plan<T>(D, R, al, false);
+  if (p.cached) {
+    LN_SWITCH(ln_fwd_cached_kernel, y, sm, si, x, g, b, D, R, eps);
+  } else {
+    ln_fwd_generic_kernel<T, ACT, AFFINE><<<p.grid, 256, 0, st>>>(y, sm, si, x, g, b, D, R, eps, act);
+  }
+  LB2_CHECK_LAUNCH("layernorm_fwd");
+  return LB2_OK;
+}
+
+template <typename T, int ACT, bool AFFINE>
+static int32_t ln_bwd_launch(T* dx, T* dg, T* db, const T* dy, const T* x, const T* g, const T* b, const float* sm,
+                             const float* si, int64_t D, int64_t R, float* ws, int32_t act, cudaStream_t st) {
+  const bool al = aligned_to(dx, 16) && aligned_to(dy, 16) && aligned_to(x, 16) &&
+                  (!g || (aligned_to(g, 16) && aligned_to(b, 16)));
+  const LnPlan p = ln_plan<T>(D, R, al, true);
+  if (p.cached) {
+    LN_SWITCH_BWD(ln_bwd_cached_kernel, dx, ws, dy, x, g, b, sm, si, D, R);
+  } else {
+    ln_bwd_generic_kernel<T, ACT, AFFINE><<<p.grid, 256, 0, st>>>(dx, ws, dy, x, g, b, sm, si, D, R, act);
+  }
+  LB2_CHECK_LAUNCH("layernorm_bwd");
+  if constexpr (AFFINE) {
+    ln_finish_kernel<T><<<(unsigned)((D + 255) / 256), 256, 0, st>>>(dg, db, ws, D, p.grid);
+    LB2_CHECK_LAUNCH("layernorm_bwd_finish");
+  }
+  return LB2_OK;
+}
+
+static size_t ln_bwd_ws_bytes(int64_t D, int64_t R) {
+  // upper bound over both dtypes / alignments: grid <= 8 * SMs
+  int64_t g = (int64_t)sm_count() * 8;
+  if (R < g) g = R;
+  if (g < 1) g = 1;
+  return align_up((size_t)g * 2 * (size_t)D * sizeof(float), 256);
+}
+
+}  // namespace lb2
+
+using namespace lb2;
+
+extern "C" {
+
+int32_t lb2_layernorm_fwd(void* y, float* save_mean, float* save_invstd, const void* x, const void* gamma,
+                          const void* beta, int64_t D, int64_t R, double eps, int32_t dtype, int32_t act,
+                          void* stream) {
+  LB2_REQUIRE(D >= 0 && R >= 0, LB2_BAD_SHAPE, "negative extent");
+  if (D == 0 || R == 0) return LB2_OK;
+  int32_t rc = check_norm_common(y, x, gamma, beta, save_mean, save_invstd, dtype, act);
+  if (rc != LB2_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  LB2_DISPATCH_DTYPE(dtype, {
+    LB2_DISPATCH_ACT3(act, {
+      if (gamma) return ln_fwd_launch<T, ACT, true>((T*)y, save_mean, save_invstd, (const T*)x, (const T*)gamma, (const T*)beta, D, R, (float)eps, act, st);
+      else return ln_fwd_launch<T, ACT, false>((T*)y, save_mean, save_invstd, (const T*)x, nullptr, nullptr, D, R, (float)eps, act, st);
+    });
+  });
+  return LB2_OK;
+}
+
+size_t lb2_layernorm_bwd_workspace_bytes(int64_t D, int64_t R) {
+  if (D <= 0 || R <= 0) return 0;
+  return ln_bwd_ws_bytes(D, R);
+}
+
+int32_t lb2_layernorm_bwd(void* dx, void* dgamma, void* dbeta, const void* dy, const void* x, const void* gamma,
+                          const void* beta, const float* save_mean, const float* save_invstd, int64_t D, int64_t R,
+                          int32_t dtype, int32_t act, void* workspace, size_t workspace_bytes, void* stream) {
+  LB2_REQUIRE(D >= 0 && R >= 0, LB2_BAD_SHAPE, "negative extent");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (D == 0 || R == 0) {
+    if (D > 0 && dgamma && valid_dtype(dtype)) {
+      cudaMemsetAsync(dgamma, 0, (size_t)D * dtype_size(dtype), st);
+      cudaMemsetAsync(dbeta, 0, (size_t)D * dtype_size(dtype), st);
+    }
+    return LB2_OK;
+  }
+  int32_t rc = check_norm_common(dx, x, gamma, beta, save_mean, save_invstd, dtype, act);
+  if (rc != LB2_OK) return rc;
+  LB2_REQUIRE(dy != nullptr, LB2_BAD_ARG, "dy is null");
+  LB2_REQUIRE(!gamma || (dgamma && dbeta), LB2_BAD_ARG, "dgamma/dbeta required when scale is given");
+  if (gamma) {
+    LB2_REQUIRE(workspace && workspace_bytes >= ln_bwd_ws_bytes(D, R), LB2_WORKSPACE_TOO_SMALL,
+                "workspace of %zu bytes needed", ln_bwd_ws_bytes(D, R));
+    LB2_REQUIRE(aligned_to(workspace, 16), LB2_BAD_ALIGN, "workspace must be 16-byte aligned");
+  }
+  LB2_DISPATCH_DTYPE(dtype, {
+    LB2_DISPATCH_ACT3(act, {
+      if (gamma) return ln_bwd_launch<T, ACT, true>((T*)dx, (T*)dgamma, (T*)dbeta, (const T*)dy, (const T*)x, (const T*)gamma, (const T*)beta, save_mean, save_invstd, D, R, (float*)workspace, act, st);
+      else return ln_bwd_launch<T, ACT, false>((T*)dx, nullptr, nullptr, (const T*)dy, (const T*)x, nullptr, nullptr, save_mean, save_invstd, D, R, (float*)workspace, act, st);
+    });
+  });
+  return LB2_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,19 @@
+"""luxlib_b200 — host-side mirror of LuxLib's fused-layer operator API over libluxlib_b200.so
+(hand-written sm_100a kernels). Importing this package never touches a GPU; the first op call
+loads the shared library and fails loudly if it has not been built."""
+from . import _cabi
+from ._cabi import ArgumentError, DimensionMismatch, LuxLibB200Error
+from .arrays import as_colmajor, from_numpy, is_colmajor, jl_empty, jl_zeros, to_numpy
+from .ops import (ConvDims, batchnorm, bias_activation, default_epsilon, fast_activation,
+                  fused_conv_bias_activation, fused_dense_bias_activation, groupnorm, layernorm, matmul,
+                  needs_preactivation, rrule_batchnorm, rrule_bias_activation, rrule_fused_conv,
+                  rrule_fused_dense, rrule_groupnorm, rrule_layernorm)
+
+__all__ = [
+    "ArgumentError", "DimensionMismatch", "LuxLibB200Error", "ConvDims",
+    "as_colmajor", "from_numpy", "is_colmajor", "jl_empty", "jl_zeros", "to_numpy",
+    "fused_dense_bias_activation", "fused_conv_bias_activation", "batchnorm", "groupnorm", "layernorm",
+    "bias_activation", "fast_activation", "matmul", "default_epsilon", "needs_preactivation",
+    "rrule_fused_dense", "rrule_fused_conv", "rrule_batchnorm", "rrule_groupnorm", "rrule_layernorm",
+    "rrule_bias_activation",
+]

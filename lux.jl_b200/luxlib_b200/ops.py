@@ -1,0 +1,525 @@
+"""Host-side mirror of the LuxLib operator API for the B200 path.
+
+Same names, argument order and error behaviour as LuxLib's public ops
+(lib/LuxLib/src/api/{dense,conv,batchnorm,groupnorm,layernorm,bias_activation,activation}.jl);
+every op is one or two calls into libluxlib_b200.so through the C ABI. `rrule_*` functions mirror
+the ChainRulesCore rules Zygote calls: they return the primal and a pullback closure.
+
+Arrays are column-major device arrays (see arrays.py); activations are named by string
+("identity", "relu", "gelu", "tanh", "sigmoid", "swish" and NNlib's *_fast aliases).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import warnings
+from dataclasses import dataclass
+from typing import Optional, Sequence, Tuple
+
+import torch
+
+from . import _cabi
+from ._cabi import ArgumentError, DimensionMismatch
+from .arrays import as_colmajor, current_stream, dtype_code, jl_empty, ptr, workspace
+
+# --------------------------------------------------------------------------------------------
+# activations
+# --------------------------------------------------------------------------------------------
+GELU_VARIANT = "tanh"  # which formula the name "gelu" denotes: "tanh" or "erf"
+
+_ACT_CODES = {
+    "identity": _cabi.ACT_IDENTITY, "relu": _cabi.ACT_RELU, "tanh": _cabi.ACT_TANH, "tanh_fast": _cabi.ACT_TANH,
+    "sigmoid": _cabi.ACT_SIGMOID, "sigmoid_fast": _cabi.ACT_SIGMOID, "swish": _cabi.ACT_SWISH, "silu": _cabi.ACT_SWISH,
+    "gelu_tanh": _cabi.ACT_GELU_TANH, "gelu_erf": _cabi.ACT_GELU_ERF,
+}
+
+
+def act_code(act: str) -> int:
+    if act == "gelu":
+        return _cabi.ACT_GELU_TANH if GELU_VARIANT == "tanh" else _cabi.ACT_GELU_ERF
+    try:
+        return _ACT_CODES[act]
+    except KeyError:
+        raise ArgumentError(f"activation {act!r} is not fused by the B200 path") from None
+
+
+def needs_preactivation(act: str) -> bool:
+    """activation_has_rrule but not activation_intermediate_not_needed
+    (lib/LuxLib/src/traits.jl:59-69): gelu and swish need the pre-activation for their derivative."""
+    return act_code(act) in (_cabi.ACT_GELU_TANH, _cabi.ACT_GELU_ERF, _cabi.ACT_SWISH)
+
+
+# --------------------------------------------------------------------------------------------
+# helpers
+# --------------------------------------------------------------------------------------------
+_warned_mixed = False
+
+
+def _promote(*ts):
+    """Mixed element types are promoted with a one-time warning (lib/LuxLib/ext/CUDAExt/cublaslt.jl:46-64)."""
+    global _warned_mixed
+    present = [t for t in ts if t is not None]
+    dt = present[0].dtype
+    for t in present[1:]:
+        dt = torch.promote_types(dt, t.dtype)
+    if any(t.dtype != dt for t in present):
+        if not _warned_mixed:
+            warnings.warn("Mixed-precision inputs: promoting to " + str(dt), stacklevel=3)
+            _warned_mixed = True
+        ts = tuple(None if t is None else t.to(dt) for t in ts)
+    return ts
+
+
+def _matrix_ld(t: torch.Tensor) -> Tuple[torch.Tensor, int]:
+    """A column-major matrix and its leading dimension; copies when the first index is not contiguous."""
+    if t.dim() != 2:
+        raise DimensionMismatch(f"expected a matrix, got {t.dim()} dims")
+    m, n = t.shape
+    if t.numel() == 0:
+        return t, max(m, 1)
+    if t.stride(0) == 1 and (n == 1 or t.stride(1) >= max(m, 1)):
+        return t, (t.stride(1) if n > 1 else max(m, 1))
+    if m == 1 and n >= 1 and t.stride(1) >= 1:
+        return t, t.stride(1)
+    t = as_colmajor(t.contiguous() if not t.is_contiguous() else t)
+    return t, max(m, 1)
+
+
+def _ws(nbytes: int, device):
+    w = workspace(nbytes, device)
+    return w, ptr(w), int(nbytes) if w is not None else 0
+
+
+# --------------------------------------------------------------------------------------------
+# dense
+# --------------------------------------------------------------------------------------------
+def _dense_fwd(act: str, weight, x, b, want_preact: bool, flags: int = 0):
+    lib = _cabi.load()
+    weight, x, b = _promote(weight, x, b)
+    if weight.dim() != 2:
+        raise DimensionMismatch("weight must be a matrix")
+    vec_in = x.dim() == 1
+    if vec_in:  # a vector is one column (lib/LuxLib/src/impl/matmul.jl:3-5)
+        x = x.reshape(-1, 1)
+    M, K = weight.shape
+    if x.shape[0] != K:
+        raise DimensionMismatch(f"size(weight, 2) = {K} does not match size(x, 1) = {x.shape[0]}")
+    if b is not None and b.shape[0] != M:
+        raise DimensionMismatch(f"length(b) = {b.shape[0]} does not match size(weight, 1) = {M}")
+    N = x.shape[1]
+    W, ldw = _matrix_ld(weight)
+    X, ldx = _matrix_ld(x)
+    dt = dtype_code(W.dtype)
+    y = jl_empty((M, N), W.dtype, W.device)
+    pre = jl_empty((M, N), W.dtype, W.device) if want_preact else None
+    _, wsp, wsn = _ws(lib.lb2_dense_fwd_workspace_bytes(M, N, K, dt, flags), W.device)
+    _cabi.check(lib.lb2_dense_fwd(ptr(y), ptr(pre), ptr(W), ptr(X), ptr(b), M, N, K, ldw, ldx, max(M, 1), dt,
+                                  act_code(act), flags, wsp, wsn, current_stream(W.device)))
+    if vec_in:
+        y = y.reshape(-1)
+        pre = None if pre is None else pre.reshape(-1)
+    return y, pre, (W, ldw, X, ldx, b, M, N, K, dt)
+
+
+def fused_dense_bias_activation(act: str, weight, x, b=None, *, flags: int = 0):
+    """y = act.(weight * x .+ b) — lib/LuxLib/src/api/dense.jl:33-37."""
+    return _dense_fwd(act, weight, x, b, False, flags)[0]
+
+
+def rrule_fused_dense(act: str, weight, x, b=None, *, flags: int = 0):
+    """rrule(fused_dense) — lib/LuxLib/src/impl/dense.jl:71-113. Returns y and a pullback
+    Δ -> (∂weight, ∂x, ∂b); the pre-activation is cached only for gelu / swish (case B)."""
+    lib = _cabi.load()
+    keep_pre = needs_preactivation(act)
+    y, pre, (W, ldw, X, ldx, bb, M, N, K, dt) = _dense_fwd(act, weight, x, b, keep_pre, flags)
+    code = act_code(act)
+
+    def pullback(delta):
+        d = as_colmajor(delta.reshape(M, N).to(W.dtype))
+        dW = jl_empty((M, K), W.dtype, W.device)
+        dx = jl_empty((K, N), W.dtype, W.device)
+        db = jl_empty((M,), W.dtype, W.device) if bb is not None else None
+        y2, pre2 = y.reshape(M, N), (None if pre is None else pre.reshape(M, N))
+        _, wsp, wsn = _ws(lib.lb2_dense_bwd_workspace_bytes(M, N, K, dt, code, flags), W.device)
+        _cabi.check(lib.lb2_dense_bwd(ptr(dW), ptr(dx), ptr(db), ptr(d), None if keep_pre else ptr(y2), ptr(pre2),
+                                      ptr(W), ptr(X), M, N, K, ldw, ldx, max(M, 1), dt, code, 0, flags, wsp, wsn,
+                                      current_stream(W.device)))
+        return dW, (dx.reshape(x.shape) if x.dim() == 1 else dx), db
+
+    return y, pullback
+
+
+def matmul(A, B, *, transA=False, transB=False, flags: int = 0):
+    """op(A) * op(B) on column-major matrices — matmul! (lib/LuxLib/src/impl/matmul.jl:96-125)."""
+    lib = _cabi.load()
+    A, B = _promote(A, B)
+    A2, lda = _matrix_ld(A)
+    B2, ldb = _matrix_ld(B)
+    M, K = (A2.shape[1], A2.shape[0]) if transA else A2.shape
+    Kb, N = (B2.shape[1], B2.shape[0]) if transB else B2.shape
+    if K != Kb:
+        raise DimensionMismatch(f"inner dimensions differ: {K} vs {Kb}")
+    dt = dtype_code(A2.dtype)
+    Cm = jl_empty((M, N), A2.dtype, A2.device)
+    _, wsp, wsn = _ws(lib.lb2_matmul_workspace_bytes(M, N, K, dt, flags), A2.device)
+    _cabi.check(lib.lb2_matmul(ptr(Cm), ptr(A2), ptr(B2), M, N, K, lda, ldb, max(M, 1), int(transA), int(transB), dt, 0,
+                               flags, wsp, wsn, current_stream(A2.device)))
+    return Cm
+
+
+# --------------------------------------------------------------------------------------------
+# bias + activation
+# --------------------------------------------------------------------------------------------
+def _scb(x: torch.Tensor):
+    """(S, C, B) view sizes of lib/LuxLib/src/impl/bias_activation.jl:229-235."""
+    if x.dim() == 1:
+        return 1, x.shape[0], 1
+    s = 1
+    for d in x.shape[:-2]:
+        s *= d
+    return s, x.shape[-2], x.shape[-1]
+
+
+def bias_activation(act: str, x, bias=None):
+    """act.(x .+ bias) with bias along dim N-1 — lib/LuxLib/src/api/bias_activation.jl:15-45."""
+    lib = _cabi.load()
+    x, bias = _promote(x, bias)
+    S, Cc, B = _scb(x)
+    if bias is not None and bias.shape[0] != Cc:
+        raise DimensionMismatch("length(bias) must equal size(x, N-1)")
+    X = as_colmajor(x)
+    y = jl_empty(X.shape, X.dtype, X.device)
+    _cabi.check(lib.lb2_bias_act_fwd(ptr(y), ptr(X), ptr(bias), S, Cc, B, dtype_code(X.dtype), act_code(act),
+                                     current_stream(X.device)))
+    return y
+
+
+def fast_activation(act: str, x):
+    """act.(x) — lib/LuxLib/src/api/activation.jl (fast_activation)."""
+    return bias_activation(act, x, None)
+
+
+def rrule_bias_activation(act: str, x, bias=None):
+    """rrule(bias_activation) — lib/LuxLib/src/impl/bias_activation.jl:55-141."""
+    lib = _cabi.load()
+    x, bias = _promote(x, bias)
+    S, Cc, B = _scb(x)
+    X = as_colmajor(x)
+    code = act_code(act)
+    keep_pre = needs_preactivation(act)
+    pre = bias_activation("identity", X, bias) if keep_pre else None
+    y = bias_activation(act, X, bias)
+
+    def pullback(delta):
+        d = as_colmajor(delta.to(X.dtype))
+        dx = jl_empty(X.shape, X.dtype, X.device)
+        db = jl_empty((Cc,), X.dtype, X.device) if bias is not None else None
+        _, wsp, wsn = _ws(lib.lb2_bias_act_bwd_workspace_bytes(S, Cc, B), X.device)
+        _cabi.check(lib.lb2_bias_act_bwd(ptr(dx), ptr(db), ptr(d), None if keep_pre else ptr(y), ptr(pre), S, Cc, B,
+                                         dtype_code(X.dtype), code, wsp, wsn, current_stream(X.device)))
+        return dx, db
+
+    return y, pullback
+
+
+# --------------------------------------------------------------------------------------------
+# convolution
+# --------------------------------------------------------------------------------------------
+@dataclass
+class ConvDims:
+    """The fields of NNlib.DenseConvDims built at src/layers/conv.jl:253-256."""
+    stride: Tuple[int, ...]
+    padding: Tuple[int, ...]   # (lo_1, hi_1, lo_2, hi_2, ...)
+    dilation: Tuple[int, ...]
+    groups: int = 1
+    flipkernel: bool = False   # False: true convolution (Lux default); True: cross-correlation
+
+    @staticmethod
+    def make(nd: int, stride=1, padding=0, dilation=1, groups=1, flipkernel=False) -> "ConvDims":
+        def tup(v, n):
+            return tuple(int(q) for q in v) if isinstance(v, (tuple, list)) else (int(v),) * n
+        s, d, p = tup(stride, nd), tup(dilation, nd), tup(padding, 2 * nd)
+        if len(p) == nd:
+            p = tuple(q for v in p for q in (v, v))
+        if not (len(s) == nd and len(d) == nd and len(p) == 2 * nd):
+            raise DimensionMismatch("stride / dilation / padding rank does not match the spatial rank")
+        return ConvDims(s, p, d, int(groups), bool(flipkernel))
+
+
+def _conv_desc(weight, x, cd: ConvDims) -> _cabi.ConvDesc:
+    nd = x.dim() - 2
+    if weight.dim() != x.dim() or nd < 1 or nd > 3:
+        raise DimensionMismatch("weight and x must have the same rank (3 to 5)")
+    if len(cd.stride) != nd:
+        raise DimensionMismatch("ConvDims rank does not match the arrays")
+    cin, n = x.shape[-2], x.shape[-1]
+    cin_g, cout = weight.shape[-2], weight.shape[-1]
+    if cin_g * cd.groups != cin or cout % cd.groups != 0:
+        raise DimensionMismatch(f"channels: x has {cin}, weight expects {cin_g} x {cd.groups} groups -> {cout}")
+    d = _cabi.ConvDesc()
+    d.ndim = nd
+    for i in range(3):
+        live = i < nd
+        d.in_[i] = x.shape[i] if live else 1
+        d.k[i] = weight.shape[i] if live else 1
+        d.stride[i] = cd.stride[i] if live else 1
+        d.pad_lo[i] = cd.padding[2 * i] if live else 0
+        d.pad_hi[i] = cd.padding[2 * i + 1] if live else 0
+        d.dilation[i] = cd.dilation[i] if live else 1
+    d.groups, d.flipkernel, d.cin, d.cout, d.batch = cd.groups, int(cd.flipkernel), cin, cout, n
+    return d
+
+
+def _conv_fwd(act, weight, x, b, cd, want_preact, flags=0):
+    lib = _cabi.load()
+    weight, x, b = _promote(weight, x, b)
+    d = _conv_desc(weight, x, cd)
+    if b is not None and b.shape[0] != d.cout:
+        raise DimensionMismatch("length(bias) must equal the number of output channels")
+    Wt, X = as_colmajor(weight), as_colmajor(x)
+    osz = (C.c_int32 * 3)()
+    _cabi.check(lib.lb2_conv_output_size(C.byref(d), osz))
+    yshape = tuple(osz[i] for i in range(d.ndim)) + (d.cout, d.batch)
+    y = jl_empty(yshape, X.dtype, X.device)
+    pre = jl_empty(yshape, X.dtype, X.device) if want_preact else None
+    dt = dtype_code(X.dtype)
+    _, wsp, wsn = _ws(lib.lb2_conv_fwd_workspace_bytes(C.byref(d), dt), X.device)
+    _cabi.check(lib.lb2_conv_fwd(ptr(y), ptr(pre), ptr(X), ptr(Wt), ptr(b), C.byref(d), dt, act_code(act), flags, wsp, wsn,
+                                 current_stream(X.device)))
+    return y, pre, (Wt, X, b, d, dt)
+
+
+def fused_conv_bias_activation(act: str, weight, x, b, cdims: ConvDims, *, flags: int = 0):
+    """act.(conv(x, weight, cdims) .+ b) — lib/LuxLib/src/api/conv.jl:30-38."""
+    return _conv_fwd(act, weight, x, b, cdims, False, flags)[0]
+
+
+def rrule_fused_conv(act: str, weight, x, b, cdims: ConvDims, *, flags: int = 0):
+    """rrule(fused_conv) + ∇fused_conv — lib/LuxLib/src/impl/conv.jl:204-275.
+    Pullback Δ -> (∂weight, ∂x, ∂b)."""
+    lib = _cabi.load()
+    keep_pre = needs_preactivation(act)
+    y, pre, (Wt, X, bb, d, dt) = _conv_fwd(act, weight, x, b, cdims, keep_pre, flags)
+    code = act_code(act)
+
+    def pullback(delta):
+        dl = as_colmajor(delta.to(X.dtype))  # NNlib.colmajor(Δ): impl/conv.jl:263
+        dw = jl_empty(Wt.shape, X.dtype, X.device)
+        dx = jl_empty(X.shape, X.dtype, X.device)
+        db = jl_empty((d.cout,), X.dtype, X.device) if bb is not None else None
+        _, wsp, wsn = _ws(lib.lb2_conv_bwd_workspace_bytes(C.byref(d), dt, code), X.device)
+        _cabi.check(lib.lb2_conv_bwd(ptr(dw), ptr(dx), ptr(db), ptr(dl), None if keep_pre else ptr(y), ptr(pre), ptr(X),
+                                     ptr(Wt), C.byref(d), dt, code, flags, wsp, wsn, current_stream(X.device)))
+        return dw, dx, db
+
+    return y, pullback
+
+
+# --------------------------------------------------------------------------------------------
+# normalisation
+# --------------------------------------------------------------------------------------------
+def default_epsilon(dtype: torch.dtype) -> float:
+    """eps(T)^(5/7) — lib/LuxLib/src/utils.jl:130."""
+    return float(torch.finfo(dtype).eps) ** (5.0 / 7.0)
+
+
+def _check_affine(scale, bias):
+    if (scale is None) != (bias is None):
+        raise ArgumentError("scale and bias must both be given or both be nothing")
+
+
+def batchnorm(x, scale, bias, running_mean, running_var, training: bool, act: str = "identity",
+              momentum: float = 0.1, epsilon: Optional[float] = None):
+    """LuxLib.batchnorm — lib/LuxLib/src/api/batchnorm.jl:31-55.
+
+    Returns (y, (running_mean′, running_var′)). The four statistics cases of
+    lib/LuxLib/src/impl/normalization.jl:116-143 apply: training with running statistics updates
+    them (new arrays); training without returns (None, None); inference with running statistics
+    uses them unchanged; inference without falls back to batch statistics."""
+    y, stats, _ = _batchnorm_fwd(x, scale, bias, running_mean, running_var, training, act, momentum, epsilon)
+    return y, stats
+
+
+def _batchnorm_fwd(x, scale, bias, rmean, rvar, training, act, momentum, epsilon):
+    lib = _cabi.load()
+    _check_affine(scale, bias)
+    if (rmean is None) != (rvar is None):
+        raise ArgumentError("running_mean and running_var must both be given or both be nothing")
+    if x.dim() < 2:
+        raise DimensionMismatch("batchnorm needs at least 2 dims (channels, batch)")
+    X = as_colmajor(x)
+    S, Cc, B = _scb(X)
+    for v, name in ((scale, "scale"), (bias, "bias"), (rmean, "running_mean"), (rvar, "running_var")):
+        if v is not None and v.shape[0] != Cc:
+            raise DimensionMismatch(f"length({name}) must equal the number of channels {Cc}")
+    eps = default_epsilon(X.dtype) if epsilon is None else float(epsilon)
+    dt = dtype_code(X.dtype)
+    dev = X.device
+    y = jl_empty(X.shape, X.dtype, dev)
+    code = act_code(act)
+    cast = lambda v: None if v is None else v.to(X.dtype)
+    scale_c, bias_c, rmean_c, rvar_c = cast(scale), cast(bias), cast(rmean), cast(rvar)
+    if training or rmean is None:
+        save_mean = torch.empty(Cc, dtype=torch.float32, device=dev)
+        save_inv = torch.empty(Cc, dtype=torch.float32, device=dev)
+        update = training and rmean is not None
+        new_rm = torch.empty_like(rmean_c) if update else None
+        new_rv = torch.empty_like(rvar_c) if update else None
+        _, wsp, wsn = _ws(lib.lb2_batchnorm_workspace_bytes(S, Cc, B), dev)
+        _cabi.check(lib.lb2_batchnorm_fwd_train(ptr(y), ptr(save_mean), ptr(save_inv), ptr(new_rm), ptr(new_rv), ptr(X),
+                                                ptr(scale_c), ptr(bias_c), ptr(rmean_c) if update else None,
+                                                ptr(rvar_c) if update else None, S, Cc, B, float(momentum), eps, dt,
+                                                code, wsp, wsn, current_stream(dev)))
+        stats = (new_rm, new_rv) if update else (rmean, rvar)
+        return y, stats, (X, scale_c, bias_c, save_mean, save_inv, S, Cc, B, dt, code, True)
+    _cabi.check(lib.lb2_batchnorm_fwd_infer(ptr(y), ptr(X), ptr(scale_c), ptr(bias_c), ptr(rmean_c), ptr(rvar_c), S, Cc, B,
+                                            eps, dt, code, current_stream(dev)))
+    return y, (rmean, rvar), (X, scale_c, bias_c, None, None, S, Cc, B, dt, code, False)
+
+
+def rrule_batchnorm(x, scale, bias, running_mean, running_var, training: bool, act: str = "identity",
+                    momentum: float = 0.1, epsilon: Optional[float] = None):
+    """Forward + pullback Δ -> (∂x, ∂scale, ∂bias) of batchnorm with batch statistics:
+    rrule(batchnorm_affine_normalize_internal) (lib/LuxLib/src/impl/batchnorm.jl:405-443) chained
+    through the mean_var rule (lib/LuxLib/src/impl/common_ops.jl:45-61)."""
+    lib = _cabi.load()
+    y, stats, (X, sc, bi, save_mean, save_inv, S, Cc, B, dt, code, batch_stats) = _batchnorm_fwd(
+        x, scale, bias, running_mean, running_var, training, act, momentum, epsilon)
+    if not batch_stats:
+        raise ArgumentError("the fused batchnorm pullback covers batch statistics (training mode)")
+
+    def pullback(delta):
+        d = as_colmajor(delta.to(X.dtype))
+        dx = jl_empty(X.shape, X.dtype, X.device)
+        dg = torch.empty(Cc, dtype=X.dtype, device=X.device) if sc is not None else None
+        db = torch.empty(Cc, dtype=X.dtype, device=X.device) if sc is not None else None
+        _, wsp, wsn = _ws(lib.lb2_batchnorm_workspace_bytes(S, Cc, B), X.device)
+        _cabi.check(lib.lb2_batchnorm_bwd(ptr(dx), ptr(dg), ptr(db), ptr(d), ptr(X), ptr(sc), ptr(bi), ptr(save_mean),
+                                          ptr(save_inv), S, Cc, B, dt, code, wsp, wsn, current_stream(X.device)))
+        return dx, dg, db
+
+    return y, stats, pullback
+
+
+def _gn_sizes(x, groups):
+    if x.dim() < 2:
+        raise DimensionMismatch("groupnorm needs at least 2 dims (channels, batch)")
+    S, Cc, B = _scb(x)
+    if Cc % groups != 0:
+        raise ArgumentError(f"Number of channels {Cc} must be divisible by the number of groups {groups}")
+    return S, Cc, B
+
+
+def _groupnorm_fwd(x, scale, bias, groups, act, epsilon):
+    lib = _cabi.load()
+    _check_affine(scale, bias)
+    X = as_colmajor(x)
+    S, Cc, B = _gn_sizes(X, groups)
+    if scale is not None and (scale.shape[0] != Cc or bias.shape[0] != Cc):
+        raise ArgumentError("length(scale) and length(bias) must equal the number of channels")
+    eps = default_epsilon(X.dtype) if epsilon is None else float(epsilon)
+    dt, code, dev = dtype_code(X.dtype), act_code(act), X.device
+    y = jl_empty(X.shape, X.dtype, dev)
+    sm = torch.empty(groups * B, dtype=torch.float32, device=dev)
+    si = torch.empty(groups * B, dtype=torch.float32, device=dev)
+    sc = None if scale is None else scale.to(X.dtype)
+    bi = None if bias is None else bias.to(X.dtype)
+    _cabi.check(lib.lb2_groupnorm_fwd(ptr(y), ptr(sm), ptr(si), ptr(X), ptr(sc), ptr(bi), S, Cc, groups, B, eps, dt, code,
+                                      current_stream(dev)))
+    return y, (X, sc, bi, sm, si, S, Cc, B, dt, code)
+
+
+def groupnorm(x, scale, bias, groups: int, act: str = "identity", epsilon: Optional[float] = None):
+    """LuxLib.groupnorm — lib/LuxLib/src/api/groupnorm.jl:26-69."""
+    return _groupnorm_fwd(x, scale, bias, groups, act, epsilon)[0]
+
+
+def rrule_groupnorm(x, scale, bias, groups: int, act: str = "identity", epsilon: Optional[float] = None):
+    """rrule(groupnorm_affine_normalize_internal) (lib/LuxLib/src/impl/groupnorm.jl:349-381) chained
+    through mean_var. Pullback Δ -> (∂x, ∂scale, ∂bias)."""
+    lib = _cabi.load()
+    y, (X, sc, bi, sm, si, S, Cc, B, dt, code) = _groupnorm_fwd(x, scale, bias, groups, act, epsilon)
+
+    def pullback(delta):
+        d = as_colmajor(delta.to(X.dtype))
+        dx = jl_empty(X.shape, X.dtype, X.device)
+        dg = torch.empty(Cc, dtype=X.dtype, device=X.device) if sc is not None else None
+        db = torch.empty(Cc, dtype=X.dtype, device=X.device) if sc is not None else None
+        _, wsp, wsn = _ws(lib.lb2_groupnorm_bwd_workspace_bytes(S, Cc, groups, B), X.device)
+        _cabi.check(lib.lb2_groupnorm_bwd(ptr(dx), ptr(dg), ptr(db), ptr(d), ptr(X), ptr(sc), ptr(bi), ptr(sm), ptr(si), S,
+                                          Cc, groups, B, dt, code, wsp, wsn, current_stream(X.device)))
+        return dx, dg, db
+
+    return y, pullback
+
+
+def _ln_rows(x, scale, bias, dims):
+    """Resolves `dims` (1-based, Julia style; None, "colon", int, or a tuple) to the (D, R) row view.
+    Only leading dims with scale/bias of the row shape take the fused path
+    (lib/LuxLib/src/impl/layernorm.jl:16-33)."""
+    _check_affine(scale, bias)
+    N = x.dim()
+    if dims is None:
+        if scale is None:
+            raise ArgumentError("`dims` must be passed explicitly if `scale` and `bias` are `nothing`")
+        M = scale.dim()
+        assert N > M, "`x` must have more dimensions than `scale` and `bias` when `dims` is `nothing`"
+        dims = tuple(range(1, N - M + 1))
+    elif dims == "colon":
+        dims = tuple(range(1, N + 1))
+    elif isinstance(dims, int):
+        dims = (dims,)
+    dims = tuple(sorted(int(d) for d in dims))
+    if dims != tuple(range(1, len(dims) + 1)):
+        raise ArgumentError("the fused layernorm covers leading dims only; other `dims` stay on the generic path")
+    D = 1
+    for d in x.shape[:len(dims)]:
+        D *= d
+    R = x.numel() // D if D > 0 else 0
+    if scale is not None:
+        lead = tuple(x.shape[:len(dims)])
+        for v in (scale, bias):
+            vs = tuple(v.shape)
+            if vs[:len(lead)] != lead or any(d != 1 for d in vs[len(lead):]):
+                raise ArgumentError("the fused layernorm needs scale / bias of the normalised shape")
+    return D, R
+
+
+def _layernorm_fwd(x, scale, bias, act, dims, epsilon):
+    lib = _cabi.load()
+    D, R = _ln_rows(x, scale, bias, dims)
+    X = as_colmajor(x)
+    eps = default_epsilon(X.dtype) if epsilon is None else float(epsilon)
+    dt, code, dev = dtype_code(X.dtype), act_code(act), X.device
+    y = jl_empty(X.shape, X.dtype, dev)
+    sm = torch.empty(max(R, 1), dtype=torch.float32, device=dev)
+    si = torch.empty(max(R, 1), dtype=torch.float32, device=dev)
+    sc = None if scale is None else as_colmajor(scale.to(X.dtype))
+    bi = None if bias is None else as_colmajor(bias.to(X.dtype))
+    _cabi.check(lib.lb2_layernorm_fwd(ptr(y), ptr(sm), ptr(si), ptr(X), ptr(sc), ptr(bi), D, R, eps, dt, code,
+                                      current_stream(dev)))
+    return y, (X, sc, bi, sm, si, D, R, dt, code)
+
+
+def layernorm(x, scale=None, bias=None, act: str = "identity", dims=None, epsilon: Optional[float] = None):
+    """LuxLib.layernorm — lib/LuxLib/src/api/layernorm.jl:32-43 (op default dims = 1:N-1 is the
+    caller's to pass; `dims=None` derives them from the affine rank)."""
+    return _layernorm_fwd(x, scale, bias, act, dims, epsilon)[0]
+
+
+def rrule_layernorm(x, scale=None, bias=None, act: str = "identity", dims=None, epsilon: Optional[float] = None):
+    """Pullback Δ -> (∂x, ∂scale, ∂bias) — what broadcast AD through affine_normalize and the mean_var
+    rule yields (lib/LuxLib/src/impl/normalization.jl:11-17, common_ops.jl:45-61), in one kernel."""
+    lib = _cabi.load()
+    y, (X, sc, bi, sm, si, D, R, dt, code) = _layernorm_fwd(x, scale, bias, act, dims, epsilon)
+
+    def pullback(delta):
+        d = as_colmajor(delta.to(X.dtype))
+        dx = jl_empty(X.shape, X.dtype, X.device)
+        dg = jl_empty(sc.shape, X.dtype, X.device) if sc is not None else None
+        db = jl_empty(sc.shape, X.dtype, X.device) if sc is not None else None
+        _, wsp, wsn = _ws(lib.lb2_layernorm_bwd_workspace_bytes(D, R), X.device)
+        _cabi.check(lib.lb2_layernorm_bwd(ptr(dx), ptr(dg), ptr(db), ptr(d), ptr(X), ptr(sc), ptr(bi), ptr(sm), ptr(si), D, R,
+                                          dt, code, wsp, wsn, current_stream(X.device)))
+        return dx, dg, db
+
+    return y, pullback

@@ -1,0 +1,335 @@
+"""GPU parity tests: every op of the hot path, called through the C ABI (via the host mirror),
+compared with the CPU oracle on identical seeded inputs.
+
+Tolerances (the ones the path's contract states): fp32 outputs and gradients rel-L2 <= 1e-5;
+bf16 storage with fp32 accumulation rel-L2 <= 1e-2; BatchNorm running statistics rel <= 1e-5.
+"""
+import numpy as np
+import pytest
+import torch
+
+import luxlib_b200 as L
+from oracle import luxlib_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+TOL = {"f32": 1e-5, "bf16": 1e-2}
+TDT = {"f32": torch.float32, "bf16": torch.bfloat16}
+ACTS = ["identity", "relu", "gelu", "tanh", "sigmoid", "swish"]
+
+
+def dev(a, dt):
+    return None if a is None else L.from_numpy(a, "cuda", TDT[dt])
+
+
+def prep(a, dt):
+    """Oracle-side view of an input: bf16 rows see the bf16-rounded values."""
+    if a is None:
+        return None
+    a = np.asarray(a, dtype=np.float32)
+    return O.round_bf16(a) if dt == "bf16" else a
+
+
+def check(got, want, dt, what, tol=None):
+    if want is None:
+        assert got is None
+        return
+    g = L.to_numpy(got).astype(np.float64)
+    w = np.asarray(want, dtype=np.float64)
+    assert g.shape == w.shape, f"{what}: shape {g.shape} vs {w.shape}"
+    assert np.isfinite(g).all(), f"{what}: non-finite values"
+    err = O.rel_l2(g, w)
+    assert err <= (tol or TOL[dt]), f"{what}: rel-L2 {err:.3e} > {(tol or TOL[dt]):.1e}"
+
+
+# ------------------------------------------------------------------------------------------
+# activation / bias-activation
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("act", ACTS)
+@pytest.mark.parametrize("shape", [(5,), (7, 3), (4, 4, 6, 2), (8, 16, 3), (33, 5, 2), (1024, 8, 4)])
+def test_bias_activation_fwd_bwd(dt, act, shape):
+    rng = np.random.default_rng(10)
+    x = prep(rng.standard_normal(shape), dt)
+    c = shape[-2] if len(shape) > 1 else shape[0]
+    b = prep(rng.uniform(-0.5, 0.5, c), dt)
+    y_ref, pb_ref = O.bias_activation_rrule(act, x, b)
+    y, pb = L.rrule_bias_activation(act, dev(x, dt), dev(b, dt))
+    check(y, y_ref, dt, "y")
+    delta = prep(rng.standard_normal(shape), dt)
+    dx_ref, db_ref = pb_ref(delta)
+    dx, db = pb(dev(delta, dt))
+    check(dx, dx_ref, dt, "dx")
+    check(db, db_ref, dt, "db")
+    # no-bias variant == fast_activation
+    check(L.fast_activation(act, dev(x, dt)), O.act_fn(act, x), dt, "fast_activation")
+
+
+def test_zero_sized_arrays():
+    # lib/LuxLib/test/common_ops/bias_act_tests.jl:119-131
+    x = L.jl_empty((4, 3, 2, 0), torch.float32, "cuda")
+    b = torch.zeros(2, device="cuda")
+    assert L.bias_activation("relu", x, b).shape == (4, 3, 2, 0)
+    assert L.fused_dense_bias_activation("relu", L.jl_empty((3, 0), torch.float32, "cuda"),
+                                         L.jl_empty((0, 2), torch.float32, "cuda"), None).shape == (3, 2)
+
+
+# ------------------------------------------------------------------------------------------
+# dense
+# ------------------------------------------------------------------------------------------
+DENSE_SHAPES = [
+    (4, 3, 4), (32, 3, 32), (10, 128, 256), (256, 128, 784),   # small / config-1 layers (CUDA cores or 3xTF32)
+    (128, 256, 64), (256, 512, 512), (384, 200, 136), (130, 300, 72),  # tensor-core path incl. ragged tiles
+]
+
+
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("act", ["identity", "relu", "gelu", "tanh", "swish"])
+@pytest.mark.parametrize("mnk", DENSE_SHAPES)
+def test_fused_dense_fwd_bwd(dt, act, mnk):
+    M, N, K = mnk
+    rng = np.random.default_rng(M * 7 + N * 3 + K)
+    W = prep(O.glorot_uniform(rng, (M, K)), dt)
+    x = prep(rng.standard_normal((K, N)), dt)
+    b = prep(rng.uniform(-0.1, 0.1, M), dt)
+    y_ref, pb_ref = O.fused_dense_rrule(act, W, x, b)
+    y, pb = L.rrule_fused_dense(act, dev(W, dt), dev(x, dt), dev(b, dt))
+    check(y, y_ref, dt, "y")
+    delta = prep(rng.standard_normal((M, N)), dt)
+    dW_ref, dx_ref, db_ref = pb_ref(delta)
+    dW, dx, db = pb(dev(delta, dt))
+    check(dW, dW_ref, dt, "dW")
+    check(dx, dx_ref, dt, "dx")
+    check(db, db_ref, dt, "db")
+    assert L._cabi.load().lb2_poll_device_status(None) == 0
+
+
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+def test_dense_no_bias_and_vector_input(dt):
+    rng = np.random.default_rng(11)
+    W = prep(rng.standard_normal((24, 40)), dt)
+    x = prep(rng.standard_normal(40), dt)
+    y = L.fused_dense_bias_activation("sigmoid", dev(W, dt), dev(x, dt), None)
+    check(y, O.act_fn("sigmoid", W @ x), dt, "y(vector)")
+    with pytest.raises(L.DimensionMismatch):
+        L.fused_dense_bias_activation("relu", dev(W, dt), dev(rng.standard_normal((39, 2)), dt), None)
+
+
+def test_dense_known_answers():
+    # test/core_layers/basic_tests.jl:151-193
+    W = torch.ones(2, 10, device="cuda").T.contiguous().T
+    x = L.from_numpy(np.concatenate([np.ones((10, 1)), 2 * np.ones((10, 1))], 1).astype(np.float32))
+    y = L.fused_dense_bias_activation("identity", L.as_colmajor(W), x, torch.zeros(2, device="cuda"))
+    assert (L.to_numpy(y) == np.array([[10, 20], [10, 20]])).all()
+
+
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("ta,tb", [(False, False), (True, False), (False, True), (True, True)])
+def test_matmul_all_layouts(dt, ta, tb):
+    rng = np.random.default_rng(12)
+    M, N, K = 192, 264, 160
+    A = prep(rng.standard_normal((K, M) if ta else (M, K)), dt)
+    B = prep(rng.standard_normal((N, K) if tb else (K, N)), dt)
+    ref = (A.T if ta else A) @ (B.T if tb else B)
+    check(L.matmul(dev(A, dt), dev(B, dt), transA=ta, transB=tb), ref, dt, "C")
+
+
+def test_dense_tf32_single_pass_flag_is_looser_but_close():
+    rng = np.random.default_rng(13)
+    W, x = rng.standard_normal((256, 512)).astype(np.float32), rng.standard_normal((512, 256)).astype(np.float32)
+    y = L.fused_dense_bias_activation("identity", dev(W, "f32"), dev(x, "f32"), None, flags=L._cabi.FLAG_TF32_1X)
+    assert O.rel_l2(L.to_numpy(y), W @ x) < 2e-3
+    y3 = L.fused_dense_bias_activation("identity", dev(W, "f32"), dev(x, "f32"), None)
+    assert O.rel_l2(L.to_numpy(y3), W.astype(np.float64) @ x.astype(np.float64)) < 2e-6
+
+
+# ------------------------------------------------------------------------------------------
+# convolution
+# ------------------------------------------------------------------------------------------
+CONV_CASES = [
+    # spatial, k, cin, cout, stride, pad, dilation, groups, flip
+    ((4, 4), (3, 3), 4, 8, 1, 0, 1, 1, False),
+    ((4, 4), (3, 3), 4, 8, 1, 0, 1, 2, False),
+    ((5, 4), (3, 3), 4, 8, 2, (1, 1), 1, 1, False),
+    ((6, 5), (3, 2), 2, 4, (2, 1), (0, 1, 1, 2), 1, 1, True),
+    ((9,), (3,), 2, 4, 1, 1, 2, 1, False),
+    ((4, 4, 3), (2, 2, 2), 2, 2, 1, 0, 1, 1, False),
+    ((16, 8), (3, 3), 16, 16, 1, 1, 1, 1, False),
+]
+
+
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("act", ["identity", "sigmoid", "gelu"])
+@pytest.mark.parametrize("case", CONV_CASES)
+def test_fused_conv_fwd_bwd(dt, act, case):
+    sp, k, cin, cout, stride, pad, dil, groups, flip = case
+    nd = len(sp)
+    rng = np.random.default_rng(14)
+    x = prep(rng.standard_normal(sp + (cin, 2)), dt)
+    w = prep(O.kaiming_normal(rng, k + (cin // groups, cout)), dt)
+    b = prep(rng.uniform(-0.1, 0.1, cout), dt)
+    ocd = O.ConvDims.make(nd, stride, pad, dil, groups, flip)
+    lcd = L.ConvDims.make(nd, stride, pad, dil, groups, flip)
+    y_ref, pb_ref = O.fused_conv_rrule(act, w, x, b, ocd)
+    y, pb = L.rrule_fused_conv(act, dev(w, dt), dev(x, dt), dev(b, dt), lcd)
+    check(y, y_ref, dt, "y")
+    delta = prep(rng.standard_normal(y_ref.shape), dt)
+    dw_ref, dx_ref, db_ref = pb_ref(delta)
+    dw, dx, db = pb(dev(delta, dt))
+    check(dw, dw_ref, dt, "dw")
+    check(dx, dx_ref, dt, "dx")
+    check(db, db_ref, dt, "db")
+
+
+def test_conv_known_answers():
+    # test/core_layers/conv_tests.jl:53-69 and :145-158
+    x = L.from_numpy(np.ones((28, 28, 1, 1), np.float32))
+    w = L.from_numpy(np.ones((3, 3, 1, 1), np.float32))
+    y = L.to_numpy(L.fused_conv_bias_activation("relu", w, x, torch.zeros(1, device="cuda"),
+                                                L.ConvDims.make(2, padding=(0, 1, 1, 2))))[:, :, 0, 0]
+    assert y.shape == (27, 29)
+    assert (y[0, 0], y[1, 1], y[-1, 0], y[0, -1], y[0, -2], y[-1, -1]) == (6, 9, 4, 3, 6, 2)
+    img = np.zeros((7, 7, 1, 1), np.float32)
+    img[3, 3] = 1
+    wt = np.random.default_rng(0).standard_normal((3, 3, 1, 1)).astype(np.float32)
+    y = L.to_numpy(L.fused_conv_bias_activation("identity", L.from_numpy(wt), L.from_numpy(img), None, L.ConvDims.make(2)))
+    np.testing.assert_allclose(y[1:-1, 1:-1, 0, 0], wt[:, :, 0, 0], atol=1e-6)
+
+
+# ------------------------------------------------------------------------------------------
+# batchnorm
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("act", ["identity", "relu", "sigmoid"])
+@pytest.mark.parametrize("shape", [(4, 4, 6, 2), (8, 2), (64, 48), (12, 12, 16, 8), (7, 5, 3, 4)])
+@pytest.mark.parametrize("affine", [True, False])
+def test_batchnorm_train_fwd_bwd(dt, act, shape, affine):
+    rng = np.random.default_rng(15)
+    c = shape[-2]
+    x = prep(rng.standard_normal(shape) * rng.uniform(0.5, 2, (c, 1)) + 0.3, dt)
+    g = prep(rng.uniform(0.5, 1.5, c), dt) if affine else None
+    b = prep(rng.standard_normal(c) * 0.1, dt) if affine else None
+    rm, rv = prep(rng.standard_normal(c) * 0.1, dt), prep(rng.uniform(0.5, 1.5, c), dt)
+    z_ref, (rm_ref, rv_ref), pb_ref = O.batchnorm_rrule(x, g, b, rm, rv, True, act, 0.1, 1e-5)
+    z, (nrm, nrv), pb = L.rrule_batchnorm(dev(x, dt), dev(g, dt), dev(b, dt), dev(rm, dt), dev(rv, dt), True, act, 0.1, 1e-5)
+    check(z, z_ref, dt, "y")
+    check(nrm, rm_ref, dt, "running_mean", tol=1e-5 if dt == "f32" else None)
+    check(nrv, rv_ref, dt, "running_var", tol=1e-5 if dt == "f32" else None)
+    delta = prep(rng.standard_normal(shape), dt)
+    dx_ref, dg_ref, db_ref = pb_ref(delta)
+    dx, dg, db = pb(dev(delta, dt))
+    # the gradient w.r.t. x cancels heavily; judge it on the scale of its inputs like the reference's atol
+    check(dx, dx_ref, dt, "dx", tol=(2e-5 if dt == "f32" else 2e-2))
+    check(dg, dg_ref, dt, "dgamma")
+    check(db, db_ref, dt, "dbeta")
+
+
+def test_batchnorm_known_answers_and_modes():
+    # test/core_layers/normalize_tests.jl:10-49
+    x = L.from_numpy(np.array([[1, 3, 5], [2, 4, 6]], np.float32))
+    one, zero = torch.ones(2, device="cuda"), torch.zeros(2, device="cuda")
+    y, (rm, rv) = L.batchnorm(x, one, zero, zero.clone(), one.clone(), True, "identity", 0.1, 1e-5)
+    np.testing.assert_allclose(L.to_numpy(y), [[-1.22474, 0, 1.22474]] * 2, atol=1e-5)
+    np.testing.assert_allclose(L.to_numpy(rm), [0.3, 0.4], rtol=1e-6)
+    np.testing.assert_allclose(L.to_numpy(rv), [1.3, 1.3], rtol=1e-6)
+    yt, (rm2, rv2) = L.batchnorm(x, one, zero, rm, rv, False, "identity", 0.1, 1e-5)
+    assert abs(L.to_numpy(yt)[0, 0] - (1 - 0.3) / np.sqrt(1.3)) < 1e-5
+    assert rm2 is rm and rv2 is rv
+    # training without running statistics: batch statistics, nothing returned
+    y3, (a, b) = L.batchnorm(x, one, zero, None, None, True, "identity", 0.1, 1e-5)
+    assert a is None and b is None
+    np.testing.assert_allclose(L.to_numpy(y3), L.to_numpy(y), atol=1e-6)
+
+
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+def test_batchnorm_inference(dt):
+    rng = np.random.default_rng(16)
+    x = prep(rng.standard_normal((6, 5, 8, 3)), dt)
+    g, b = prep(rng.uniform(0.5, 1.5, 8), dt), prep(rng.standard_normal(8), dt)
+    rm, rv = prep(rng.standard_normal(8) * 0.2, dt), prep(rng.uniform(0.5, 2, 8), dt)
+    y_ref, _ = O.batchnorm(x, g, b, rm, rv, False, "relu", 0.1, 1e-5)
+    y, _ = L.batchnorm(dev(x, dt), dev(g, dt), dev(b, dt), dev(rm, dt), dev(rv, dt), False, "relu", 0.1, 1e-5)
+    check(y, y_ref, dt, "y")
+
+
+# ------------------------------------------------------------------------------------------
+# groupnorm / layernorm
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("act", ["identity", "relu", "gelu"])
+@pytest.mark.parametrize("shape,groups", [((6, 2), 2), ((4, 4, 6, 2), 3), ((2, 2, 6, 2), 2), ((16, 16, 32, 4), 4),
+                                          ((32, 32, 16, 3), 2), ((8, 128, 64, 2), 4), ((7, 3, 10, 2), 5)])
+@pytest.mark.parametrize("affine", [True, False])
+def test_groupnorm_fwd_bwd(dt, act, shape, groups, affine):
+    rng = np.random.default_rng(17)
+    c = shape[-2]
+    x = prep(rng.standard_normal(shape) * rng.uniform(0.5, 2, (c, 1)), dt)
+    g = prep(rng.uniform(0.5, 1.5, c), dt) if affine else None
+    b = prep(rng.standard_normal(c) * 0.1, dt) if affine else None
+    z_ref, pb_ref = O.groupnorm_rrule(x, g, b, groups, act, 1e-5)
+    z, pb = L.rrule_groupnorm(dev(x, dt), dev(g, dt), dev(b, dt), groups, act, 1e-5)
+    check(z, z_ref, dt, "y")
+    delta = prep(rng.standard_normal(shape), dt)
+    dx_ref, dg_ref, db_ref = pb_ref(delta)
+    dx, dg, db = pb(dev(delta, dt))
+    check(dx, dx_ref, dt, "dx", tol=(2e-5 if dt == "f32" else 2e-2))
+    check(dg, dg_ref, dt, "dgamma")
+    check(db, db_ref, dt, "dbeta")
+
+
+def test_groupnorm_errors():
+    x = L.jl_zeros((4, 4, 6, 2), torch.float32, "cuda")
+    with pytest.raises(L.ArgumentError):
+        L.groupnorm(x, None, None, 4)
+    with pytest.raises(L.ArgumentError):
+        L.groupnorm(x, torch.ones(5, device="cuda"), torch.ones(5, device="cuda"), 3)
+
+
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("act", ["identity", "tanh"])
+@pytest.mark.parametrize("shape,nd", [((16, 7), 1), ((4096, 9), 1), ((4, 4, 6, 3), 3), ((100, 33), 1), ((6000, 4), 1),
+                                      ((24576, 3), 1), ((1030, 5), 1)])
+@pytest.mark.parametrize("affine", [True, False])
+def test_layernorm_fwd_bwd(dt, act, shape, nd, affine):
+    rng = np.random.default_rng(18)
+    x = prep(rng.standard_normal(shape) * 1.5 + 0.2, dt)
+    # explicit dims: scale / bias carry the layer's shape (shape..., 1) (src/layers/normalize.jl:581-587)
+    ashape = shape[:nd] + (1,) * (len(shape) - nd)
+    g = prep(rng.uniform(0.5, 1.5, ashape), dt) if affine else None
+    b = prep(rng.standard_normal(ashape) * 0.1, dt) if affine else None
+    dims0 = tuple(range(nd))
+    z_ref, pb_ref = O.layernorm_rrule(x, g, b, act, dims0, 1e-5)
+    z, pb = L.rrule_layernorm(dev(x, dt), dev(g, dt), dev(b, dt), act, tuple(d + 1 for d in dims0), 1e-5)
+    check(z, z_ref, dt, "y")
+    delta = prep(rng.standard_normal(shape), dt)
+    dx_ref, dg_ref, db_ref = pb_ref(delta)
+    dx, dg, db = pb(dev(delta, dt))
+    check(dx, dx_ref, dt, "dx", tol=(2e-5 if dt == "f32" else 2e-2))
+    check(dg, dg_ref, dt, "dgamma")
+    check(db, db_ref, dt, "dbeta")
+
+
+def test_layernorm_dims_nothing_derives_rows_from_the_affine_rank():
+    rng = np.random.default_rng(20)
+    x = rng.standard_normal((48, 5)).astype(np.float32)
+    g, b = rng.uniform(0.5, 1.5, 48).astype(np.float32), rng.standard_normal(48).astype(np.float32)
+    y = L.layernorm(dev(x, "f32"), dev(g, "f32"), dev(b, "f32"), "identity", None, 1e-5)
+    check(y, O.layernorm(x, g, b, "identity", None, 1e-5), "f32", "y")
+
+
+def test_layernorm_property_and_errors():
+    # lib/LuxLib/test/normalization/layernorm_tests.jl:54-57,100-113
+    x = L.from_numpy(np.random.default_rng(19).standard_normal((4, 4, 6, 3)).astype(np.float32))
+    y = L.to_numpy(L.layernorm(x, None, None, "identity", (1, 2, 3), 1e-5))
+    assert np.allclose(y.mean(axis=(0, 1, 2)), 0, atol=1e-3) and np.allclose(y.std(axis=(0, 1, 2)), 1, atol=1e-3)
+    with pytest.raises(L.ArgumentError):
+        L.layernorm(x, None, None, "identity", None)
+    with pytest.raises(AssertionError):
+        s = torch.ones(4, 4, device="cuda")
+        L.layernorm(x[:, :, 0, 0], s, s, "identity", None)
+
+
+def test_float64_is_left_to_the_caller():
+    x = torch.zeros(4, 4, dtype=torch.float64, device="cuda")
+    with pytest.raises(L.LuxLibB200Error):
+        L.fast_activation("relu", x)
