@@ -381,13 +381,20 @@ static bool make_operand_map(CUtensorMap* map, const GemmOperand& op, int64_t mn
     plan->desc_lbo = (1u & 0x3FFFu) << 16;  // ignored for swizzled K-major layouts
     plan->k_advance = 32 >> 4;              // 32 bytes of K per MMA step inside the 128-byte row
   }
-  // SBO = 1024 bytes (8 rows x 128 bytes), descriptor version 1 (bits 46-47), SWIZZLE_128B (bits 61-63 = 2)
-  plan->desc_hi = (uint32_t)((1024u >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
+  // Descriptor upper word: SBO (bits 32-45), version 1 (bits 46-47), layout type (bits 61-63).
+  // 16-bit and K-major operands: SWIZZLE_128B (type 2), atoms of 8 rows x 128 bytes -> SBO = 1024.
+  // MN-major tf32 operands: the tensor core transposes 32-bit elements only from the "128-byte
+  // swizzle with 32-byte atoms" layout (type 1): atoms of 4 k-rows x 128 bytes -> SBO = 512, and
+  // the TMA box is written with the matching CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B mode.
+  const bool base32 = tf32 && op.mn_major;
+  const uint32_t sbo = base32 ? 512u : 1024u;
+  plan->desc_hi = (uint32_t)((sbo >> 4) & 0x3FFFu) | (1u << 14) | ((base32 ? 1u : 2u) << 29);
   cuuint64_t strides[1] = {(cuuint64_t)op.ld * (cuuint64_t)elem_bytes};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
                    const_cast<void*>(op.ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                   base32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }
 
