@@ -174,6 +174,24 @@ LB2_API int32_t lb2_batchnorm_fwd_train(void* y, float* save_mean, float* save_i
                                 const void* rmean, const void* rvar, int64_t S, int64_t C, int64_t B,
                                 double momentum, double eps, int32_t dtype, int32_t act,
                                 void* workspace, size_t workspace_bytes, void* stream);
+/* Same operation as lb2_batchnorm_fwd_train for callers that cannot hand over a workspace because
+ * they have no way to allocate one: code that runs where the host's GPU allocator must not be
+ * entered (a Julia finalizer or another GC-time callback, where CUDA.jl's memory pool is off
+ * limits) or a host whose device memory was carved up front by its owner, which gives this library
+ * tensors but no allocator. It has no counterpart in the reference. The scratch is a fixed array
+ * inside the library (LB2_BATCHNORM_STATIC_SCRATCH_BYTES per GPU, held from library load until
+ * process exit); the call allocates nothing and calls no allocating routine. Problems whose scratch
+ * need (lb2_batchnorm_workspace_bytes) exceeds that size are rejected with
+ * LB2_WORKSPACE_TOO_SMALL. The first call on each device looks up the array's device address;
+ * make that first call before any stream capture. All calls on a device share the one array:
+ * two calls whose kernels may overlap on the GPU (different streams) race on it — serialise them. */
+#define LB2_BATCHNORM_STATIC_SCRATCH_BYTES (4u << 20)
+LB2_API int32_t lb2_batchnorm_fwd_train_static(void* y, float* save_mean, float* save_invstd,
+                                               void* new_rmean, void* new_rvar, const void* x,
+                                               const void* gamma, const void* beta, const void* rmean,
+                                               const void* rvar, int64_t S, int64_t C, int64_t B,
+                                               double momentum, double eps, int32_t dtype, int32_t act,
+                                               void* stream);
 /* Inference forward with given statistics (lib/LuxLib/src/impl/normalization.jl:136-143). */
 LB2_API int32_t lb2_batchnorm_fwd_infer(void* y, const void* x, const void* gamma, const void* beta,
                                 const void* rmean, const void* rvar, int64_t S, int64_t C, int64_t B,

@@ -13,6 +13,8 @@
 // Algorithmic bytes per element: forward 2*sizeof(T) (read x, write y), backward 3*sizeof(T);
 // the implementation reads x twice forward and x, dy twice backward (tensor larger than on-chip
 // memory), so its HBM traffic is 3 and 5 element-sizes.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace lb2 {
@@ -341,6 +343,36 @@ static int32_t check_bn(const void* out, const void* x, const void* gamma, const
   return LB2_OK;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Built-in scratch for lb2_batchnorm_fwd_train_static: lives in the library image, so every GPU
+// that loads the library holds these 4 MiB until the process exits. All calls share it and it
+// keeps whatever the previous call left there; the statistics pass overwrites every partial it
+// later reads, so nothing has to be cleared between calls.
+// ---------------------------------------------------------------------------------------------
+constexpr size_t kBnStaticFloats = (size_t)LB2_BATCHNORM_STATIC_SCRATCH_BYTES / sizeof(float);
+static __device__ __align__(256) float g_bn_static_scratch[kBnStaticFloats];
+
+// In host code `g_bn_static_scratch` only names the symbol; the address a kernel can use has to be
+// asked for, once per device and with that device current.
+static int32_t bn_static_scratch_ptr(float** out) {
+  static std::mutex mu;
+  static float* cached[64] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(LB2_LAUNCH_FAIL, "cudaGetDevice: %s", cudaGetErrorString(e));
+  LB2_REQUIRE(dev >= 0 && dev < 64, LB2_BAD_ARG, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lk(mu);
+  if (cached[dev] == nullptr) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_bn_static_scratch);
+    if (e != cudaSuccess || p == nullptr)
+      return fail(LB2_LAUNCH_FAIL, "cudaGetSymbolAddress(built-in batchnorm scratch): %s", cudaGetErrorString(e));
+    cached[dev] = p;
+  }
+  *out = cached[dev];
+  return LB2_OK;
+}
+
 }  // namespace lb2
 
 using namespace lb2;
@@ -437,6 +469,24 @@ int32_t lb2_batchnorm_bwd(void* dx, void* dgamma, void* dbeta, const void* dy, c
     LB2_CHECK_LAUNCH("batchnorm backward apply");
   });
   return LB2_OK;
+}
+
+int32_t lb2_batchnorm_fwd_train_static(void* y, float* save_mean, float* save_invstd, void* new_rmean,
+                                       void* new_rvar, const void* x, const void* gamma, const void* beta,
+                                       const void* rmean, const void* rvar, int64_t S, int64_t C, int64_t B,
+                                       double momentum, double eps, int32_t dtype, int32_t act, void* stream) {
+  if (S > 0 && C > 0 && B > 0) {
+    const size_t need = bn_ws_bytes(S, C, B);
+    LB2_REQUIRE(need <= (size_t)LB2_BATCHNORM_STATIC_SCRATCH_BYTES, LB2_WORKSPACE_TOO_SMALL,
+                "this problem needs %zu bytes of scratch; the built-in scratch holds %zu (use lb2_batchnorm_fwd_train "
+                "with a caller workspace instead)",
+                need, (size_t)LB2_BATCHNORM_STATIC_SCRATCH_BYTES);
+  }
+  float* scratch = nullptr;
+  int32_t rc = bn_static_scratch_ptr(&scratch);
+  if (rc != LB2_OK) return rc;
+  return lb2_batchnorm_fwd_train(y, save_mean, save_invstd, new_rmean, new_rvar, x, gamma, beta, rmean, rvar, S, C, B,
+                                 momentum, eps, dtype, act, scratch, (size_t)LB2_BATCHNORM_STATIC_SCRATCH_BYTES, stream);
 }
 
 }  // extern "C"

@@ -51,6 +51,7 @@ PROTOTYPES = {
     "lb2_conv_bwd": (_i32, [_p, _p, _p, _p, _p, _p, _p, _p, C.POINTER(ConvDesc), _i32, _i32, _u32, _p, _sz, _p]),
     "lb2_batchnorm_workspace_bytes": (_sz, [_i64, _i64, _i64]),
     "lb2_batchnorm_fwd_train": (_i32, [_p, _fp, _fp, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _dbl, _dbl, _i32, _i32, _p, _sz, _p]),
+    "lb2_batchnorm_fwd_train_static": (_i32, [_p, _fp, _fp, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _dbl, _dbl, _i32, _i32, _p]),
     "lb2_batchnorm_fwd_infer": (_i32, [_p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _dbl, _i32, _i32, _p]),
     "lb2_batchnorm_bwd": (_i32, [_p, _p, _p, _p, _p, _p, _p, _fp, _fp, _i64, _i64, _i64, _i32, _i32, _p, _sz, _p]),
     "lb2_groupnorm_fwd": (_i32, [_p, _fp, _fp, _p, _p, _p, _i64, _i64, _i64, _i64, _dbl, _i32, _i32, _p]),

@@ -65,6 +65,15 @@ def test_status_codes_for_bad_arguments():
     assert lib.lb2_status_string(_cabi.TIMEOUT) == b"device-side wait timed out"
 
 
+def test_static_scratch_entry_point_rejects_oversized_problems_before_touching_the_gpu():
+    lib = _cabi.load()
+    S, C, B = 1, 1 << 18, 2
+    assert lib.lb2_batchnorm_workspace_bytes(S, C, B) > (4 << 20)
+    rc = lib.lb2_batchnorm_fwd_train_static(16, 16, 16, None, None, 16, None, None, None, None, S, C, B, 0.1, 1e-5,
+                                            _cabi.F32, _cabi.ACT_IDENTITY, None)
+    assert rc == _cabi.WORKSPACE_TOO_SMALL and b"built-in scratch" in lib.lb2_last_error_string()
+
+
 def test_conv_descriptor_and_output_size():
     lib = _cabi.load()
     d = _cabi.ConvDesc()
