@@ -1,0 +1,201 @@
+"""Data-parallel plumbing: the mirror of Lux's `DistributedUtils` for the one exchange step the
+hot path has — all-reduce(avg) of parameter gradients (src/distributed/public_api.jl:270-278 →
+ext/MPINCCLExt.jl:71-77).
+
+One process per GPU, launched by torchrun; `torch.distributed` (NCCL over NVLink/NVSwitch on
+device tensors, gloo for host tensors) plays the role NCCL.jl + MPI.jl play in the reference.
+On top of the reference's per-leaf all-reduce there is a bucketed variant: gradients are packed
+into one flat buffer per dtype and reduced with a single collective (per-launch latency, not
+link bandwidth, dominates 62 small leaves on NVSwitch).
+"""
+from __future__ import annotations
+
+import math
+import os
+from dataclasses import dataclass
+from typing import Any, Callable, Sequence
+
+import torch
+import torch.distributed as dist
+
+
+class NCCLBackend:
+    """Device tensors over NCCL (ext/MPINCCLExt.jl); host tensors fall back to the wrapped
+    host backend exactly like `NCCLBackend` falls back to its `mpi_backend` (:40-54,79-84)."""
+    name = "nccl"
+
+
+class GlooBackend:
+    """Host-memory backend (stands where `MPIBackend`, ext/MPIExt.jl, stands in the reference)."""
+    name = "gloo"
+
+
+_state = {"initialized": False, "backend": None, "host_group": None}
+
+
+def initialized(backend=None) -> bool:
+    return _state["initialized"]
+
+
+def initialize(backend=NCCLBackend, *, timeout_s: float = 600.0, force: bool = False):
+    """DistributedUtils.initialize (src/distributed/public_api.jl:20-47): start the process group
+    from the launcher's environment (RANK, WORLD_SIZE, MASTER_ADDR, MASTER_PORT, LOCAL_RANK) and
+    bind this rank to GPU `local_rank % device_count` (lib/MLDataDevices/ext/CUDAExt.jl:48-51)."""
+    if _state["initialized"] and not force:
+        return
+    import datetime
+    name = backend.name if not isinstance(backend, str) else backend
+    if name == "nccl":
+        if not torch.cuda.is_available():
+            raise RuntimeError("NCCLBackend needs CUDA devices")
+        local = int(os.environ.get("LOCAL_RANK", os.environ.get("RANK", "0")))
+        torch.cuda.set_device(local % torch.cuda.device_count())
+    if not dist.is_initialized():
+        dist.init_process_group(name, timeout=datetime.timedelta(seconds=timeout_s))
+    _state.update(initialized=True, backend=name)
+    if name == "nccl":  # host arrays travel over a gloo group, as CPU arrays travel over MPI in the reference
+        _state["host_group"] = dist.new_group(backend="gloo")
+
+
+def get_distributed_backend(backend=NCCLBackend):
+    if not _state["initialized"]:
+        raise RuntimeError("call DistributedUtils.initialize first")
+    return backend() if isinstance(backend, type) else backend
+
+
+def local_rank(backend=None) -> int:
+    return dist.get_rank()
+
+
+def total_workers(backend=None) -> int:
+    return dist.get_world_size()
+
+
+def _group_for(t: torch.Tensor):
+    if _state["backend"] == "nccl" and not t.is_cuda:
+        return _state["host_group"]
+    return None
+
+
+avg = "avg"
+
+_OPS = {"+": dist.ReduceOp.SUM, "sum": dist.ReduceOp.SUM, "*": dist.ReduceOp.PRODUCT, "prod": dist.ReduceOp.PRODUCT,
+        "max": dist.ReduceOp.MAX, "min": dist.ReduceOp.MIN}
+
+
+def bcast_(backend, sendrecvbuf: torch.Tensor, *, root: int = 0) -> torch.Tensor:
+    """bcast! (public_api.jl:92-117)."""
+    dist.broadcast(sendrecvbuf, src=root, group=_group_for(sendrecvbuf))
+    return sendrecvbuf
+
+
+def allreduce_(backend, sendrecvbuf: torch.Tensor, op=avg) -> torch.Tensor:
+    """allreduce! (public_api.jl:119-152). `avg` maps to NCCL's native average on device tensors
+    (ext/MPINCCLExt.jl:74) and to sum followed by a division on host tensors (ext/MPIExt.jl:108-128)."""
+    g = _group_for(sendrecvbuf)
+    if op == avg:
+        if sendrecvbuf.is_cuda and _state["backend"] == "nccl":
+            dist.all_reduce(sendrecvbuf, op=dist.ReduceOp.AVG, group=g)
+        else:
+            dist.all_reduce(sendrecvbuf, op=dist.ReduceOp.SUM, group=g)
+            sendrecvbuf.div_(dist.get_world_size())
+        return sendrecvbuf
+    dist.all_reduce(sendrecvbuf, op=_OPS[op], group=g)
+    return sendrecvbuf
+
+
+def reduce_(backend, sendrecvbuf: torch.Tensor, op="+", *, root: int = 0) -> torch.Tensor:
+    """reduce! (public_api.jl:154-188): result valid on `root` only."""
+    g = _group_for(sendrecvbuf)
+    if op == avg:
+        dist.reduce(sendrecvbuf, dst=root, op=dist.ReduceOp.SUM, group=g)
+        if dist.get_rank() == root:
+            sendrecvbuf.div_(dist.get_world_size())
+        return sendrecvbuf
+    dist.reduce(sendrecvbuf, dst=root, op=_OPS[op], group=g)
+    return sendrecvbuf
+
+
+def synchronize(backend, ps: Any, *, root: int = 0) -> Any:
+    """synchronize!! (public_api.jl:197-226, 280-284): broadcast every array / number leaf of a nested
+    structure from `root`; anything else (strings, None, symbols) is returned unchanged."""
+    if isinstance(ps, torch.Tensor):
+        return bcast_(backend, ps, root=root)
+    if isinstance(ps, dict):
+        return {k: synchronize(backend, v, root=root) for k, v in ps.items()}
+    if isinstance(ps, tuple) and hasattr(ps, "_fields"):  # namedtuple
+        return type(ps)(*(synchronize(backend, v, root=root) for v in ps))
+    if isinstance(ps, (tuple, list)):
+        return type(ps)(synchronize(backend, v, root=root) for v in ps)
+    if isinstance(ps, bool):
+        t = torch.tensor([int(ps)])
+        return bool(bcast_(backend, t, root=root).item())
+    if isinstance(ps, (int, float)):
+        t = torch.tensor([ps], dtype=torch.float64 if isinstance(ps, float) else torch.int64)
+        return type(ps)(bcast_(backend, t, root=root).item())
+    return ps
+
+
+class DistributedDataContainer:
+    """Contiguous-block shard of a dataset (ext/MLUtilsExt.jl:9-20): ceil(n / workers) consecutive
+    indices per rank; the last rank may get fewer."""
+
+    def __init__(self, backend, data, *, rank: int | None = None, workers: int | None = None):
+        total = len(data)
+        workers = total_workers(backend) if workers is None else workers
+        rank = local_rank(backend) if rank is None else rank
+        per = int(math.ceil(total / workers)) if total else 0
+        lo = min(rank * per, total)
+        self.data, self.idxs = data, list(range(lo, min(lo + per, total)))
+
+    def __len__(self):
+        return len(self.idxs)
+
+    def __getitem__(self, i):
+        return self.data[self.idxs[i]]
+
+
+@dataclass
+class DistributedOptimizer:
+    """DistributedOptimizer (public_api.jl:270-278): averages each gradient leaf across the workers
+    before delegating to the wrapped rule. `rule(state, param, grad) -> (state, update)`.
+
+    `bucketed=True` reduces all leaves of one dtype in a single flat collective."""
+    backend: Any
+    rule: Callable
+    bucketed: bool = False
+
+    def apply(self, state, param: torch.Tensor, grad: torch.Tensor):
+        allreduce_(self.backend, grad, avg)
+        return self.rule(state, param, grad)
+
+    def apply_all(self, states: Sequence, params: Sequence[torch.Tensor], grads: Sequence[torch.Tensor]):
+        if self.bucketed:
+            allreduce_bucketed_(self.backend, list(grads))
+            return [self.rule(s, p, g) for s, p, g in zip(states, params, grads)]
+        return [self.apply(s, p, g) for s, p, g in zip(states, params, grads)]
+
+
+def allreduce_bucketed_(backend, grads: Sequence[torch.Tensor], op=avg, bucket_bytes: int = 64 << 20):
+    """All-reduce many gradient leaves with one collective per (dtype, device) bucket: pack → reduce →
+    unpack. Same result as the per-leaf loop of public_api.jl:275-278 (sums are element-wise)."""
+    groups: dict = {}
+    for g in grads:
+        groups.setdefault((g.dtype, g.device), []).append(g)
+    for leaves in groups.values():
+        start = 0
+        while start < len(leaves):
+            size, end = 0, start
+            while end < len(leaves) and (end == start or size + leaves[end].numel() * leaves[end].element_size() <= bucket_bytes):
+                size += leaves[end].numel() * leaves[end].element_size()
+                end += 1
+            chunk = leaves[start:end]
+            flat = torch.cat([t.reshape(-1) for t in chunk])
+            allreduce_(backend, flat, op)
+            off = 0
+            for t in chunk:
+                n = t.numel()
+                t.copy_(flat[off:off + n].view_as(t))
+                off += n
+            start = end
+    return grads

@@ -1,0 +1,77 @@
+"""Committed golden vectors (tests/golden/fixed_array_cases.npz, made by tests/golden/make_golden.py
+from the reference test-suite's deterministic inputs): the oracle must keep reproducing them (CPU)
+and the CUDA path must match them (GPU, fp32, rel-L2 <= 1e-5)."""
+import importlib.util
+import os
+
+import numpy as np
+import pytest
+
+from oracle import luxlib_oracle as O
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+GOLD = np.load(os.path.join(HERE, "golden", "fixed_array_cases.npz"))
+_spec = importlib.util.spec_from_file_location("make_golden", os.path.join(HERE, "golden", "make_golden.py"))
+make_golden = importlib.util.module_from_spec(_spec)
+_spec.loader.exec_module(make_golden)
+
+
+def test_oracle_reproduces_the_committed_vectors():
+    cases = make_golden.cases()
+    assert sorted({k.split("/")[0] for k in GOLD.files}) == sorted(cases)
+    for name, d in cases.items():
+        for k, v in d.items():
+            assert O.rel_l2(np.asarray(v, np.float32), GOLD[f"{name}/{k}"]) < 1e-6, f"{name}/{k}"
+
+
+@pytest.mark.gpu
+def test_cuda_path_matches_the_committed_vectors():
+    import torch
+    import luxlib_b200 as L
+    f = lambda shp: L.from_numpy(O.generate_fixed_array(shp, np.float32))
+    seed = lambda y: L.from_numpy(np.ones(y.shape, np.float32) * 0.5 + L.to_numpy(y) * 0.25)
+
+    def cmp(name, got: dict, denom_floor=None):
+        for k, v in got.items():
+            want = GOLD[f"{name}/{k}"].astype(np.float64)
+            g = L.to_numpy(v).astype(np.float64)
+            den = max(np.linalg.norm(want), denom_floor or 0.0)
+            err = np.linalg.norm(g - want) / den if den > 0 else np.linalg.norm(g)
+            assert err <= 1e-5, f"{name}/{k}: rel-L2 {err:.3e}"
+
+    for i, (k, pad, stride, groups) in enumerate(make_golden.CONV):
+        x, w, b = f((4, 4, 4, 2)), f(k + (4 // groups, 8)), f((8,))
+        cd = L.ConvDims.make(2, stride, pad, 1, groups, False)
+        for act in ("identity", "sigmoid", "gelu"):
+            y, pb = L.rrule_fused_conv(act, w, x, b, cd)
+            dw, dx, db = pb(seed(y))
+            cmp(f"conv{i}_{act}", dict(y=y, dw=dw, dx=dx, db=db))
+    for shp in ((4, 4, 6, 2), (8, 2)):
+        c = shp[-2]
+        x, g, b = f(shp), f((c,)), f((c,))
+        for act in ("identity", "sigmoid"):
+            z, (nrm, nrv), pb = L.rrule_batchnorm(x, g, b, torch.zeros(c, device="cuda"), torch.ones(c, device="cuda"), True, act, 0.9, 1e-5)
+            d = seed(z)
+            dx, dg, dbt = pb(d)
+            name = f"bn{'x'.join(map(str, shp))}_{act}"
+            cmp(name, dict(y=z, rmean=nrm, rvar=nrv, dgamma=dg, dbeta=dbt))
+            # dx cancels (tiny by construction on these ramps): judged against the size of its terms
+            xn = O.generate_fixed_array(shp, np.float64).reshape((-1,) + shp[-2:], order="F")
+            gp = (O.generate_fixed_array((c,), np.float64) / np.sqrt(xn.var(axis=(0, 2)) + 1e-5))
+            floor = np.linalg.norm(L.to_numpy(d).reshape((-1,) + shp[-2:], order="F") * gp[None, :, None])
+            cmp(name, dict(dx=dx), denom_floor=floor)
+    for shp, nd in (((4, 4, 6, 2), 3), ((6, 3), 1)):
+        ashape = shp[:nd] + (1,) * (len(shp) - nd)
+        z, pb = L.rrule_layernorm(f(shp), f(ashape), f(ashape), "identity", tuple(range(1, nd + 1)), 1e-5)
+        d = seed(z)
+        dx, dg, dbt = pb(d)
+        name = f"ln{'x'.join(map(str, shp))}"
+        cmp(name, dict(y=z, dgamma=dg, dbeta=dbt))
+        cmp(name, dict(dx=dx), denom_floor=np.linalg.norm(L.to_numpy(d)) * 10)
+    for shp, groups in (((4, 4, 6, 2), 3), ((6, 2), 2)):
+        z, pb = L.rrule_groupnorm(f(shp), f((6,)), f((6,)), groups, "identity", 1e-5)
+        d = seed(z)
+        dx, dg, dbt = pb(d)
+        name = f"gn{'x'.join(map(str, shp))}_g{groups}"
+        cmp(name, dict(y=z, dgamma=dg, dbeta=dbt))
+        cmp(name, dict(dx=dx), denom_floor=np.linalg.norm(L.to_numpy(d)) * 10)
