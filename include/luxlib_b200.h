@@ -66,6 +66,7 @@ typedef enum {
 #define LB2_FLAG_TF32_1X 1u /* fp32 GEMM/conv: single-pass TF32 (rel err ~1e-3) instead of the
                                default error-compensated 3xTF32 split (rel err ~1e-6) */
 #define LB2_FLAG_FORCE_SIMT 2u /* route a contraction through the CUDA-core kernel (debug / odd shapes) */
+#define LB2_FLAG_CTA_PAIR 4u /* tensor-core GEMM: use the CTA-pair (cta_group::2, 256x256 tile) kernel when the problem is large enough */
 
 /* ---- library ------------------------------------------------------------------------- */
 LB2_API int32_t lb2_version(void);

@@ -35,7 +35,8 @@ bool gemm_tc_supported(const void* D, int64_t ldd, GemmOperand A, GemmOperand B,
 // gemm_tc_split_workspace_bytes(...) bytes of scratch for the hi/lo operand copies.
 size_t gemm_tc_split_workspace_bytes(GemmOperand A, GemmOperand B, int64_t Mm, int64_t Nn, int64_t Kc);
 int32_t gemm_tc_launch(void* D, int64_t ldd, GemmOperand A, GemmOperand B, int64_t Mm, int64_t Nn, int64_t Kc,
-                       int32_t dtype, int split3, const GemmEpilogue& epi, void* split_ws, cudaStream_t st);
+                       int32_t dtype, int split3, uint32_t flags, const GemmEpilogue& epi, void* split_ws,
+                       cudaStream_t st);
 
 // Picks the tensor-core kernel when it applies, the CUDA-core kernel otherwise.
 size_t gemm_workspace_bytes(GemmOperand A, GemmOperand B, int64_t Mm, int64_t Nn, int64_t Kc, int32_t dtype,

@@ -20,6 +20,7 @@
 //
 // Roofline: tensor-pipe bound; algorithmic FLOPs = 2*Mm*Nn*Kc per launch.
 #include <cuda.h>
+#include <stdlib.h>
 
 #include <mutex>
 
@@ -134,6 +135,70 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// ---- CTA-pair (cta_group::2) variants -----------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of `local_addr` (a shared::cta address) in CTA `rank` of this cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t cluster_addr, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_addr), "r"(bytes) : "memory");
+}
+// TMA load issued by either CTA of a pair: data lands in the issuing CTA's shared memory, the
+// transaction bytes are counted on the barrier `bar_cluster_addr` (the pair leader's).
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int32_t c0, int32_t c1, uint32_t bar_cluster_addr) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(bar_cluster_addr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// one commit that arrives on the barrier at the same offset in both CTAs of the pair
+__device__ __forceinline__ void umma_commit_pair_both(uint32_t local_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(local_addr), "h"((uint16_t)3) : "memory");
+}
+template <bool TF32>
+__device__ __forceinline__ void umma_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  if constexpr (TF32) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+// completion of all MMAs issued so far by this thread -> one arrival on the barrier at `cluster_addr`
+// (which may live in either CTA of the pair)
+__device__ __forceinline__ void umma_commit_pair(uint32_t cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr) : "memory");
+}
+
 // ----------------------------------------------------------------------------------------------
 // kernel
 // ----------------------------------------------------------------------------------------------
@@ -160,6 +225,7 @@ struct TcParams {
   void* preact;
   int32_t act, accumulate;
   unsigned int* status;
+  uint32_t debug;  // experiment switches (LB2_GEMM_DEBUG): 1 skip epilogue work, 2 skip MMAs, 4 skip TMA loads
 };
 
 constexpr int kBM = 128;
@@ -222,6 +288,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int m0 = (tile % p.tiles_m) * kBM, n0 = (tile / p.tiles_m) * BN;
         for (int kb = 0; kb < p.num_kb; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, p.status, 0x1u)) { ok = false; break; }
+          if (p.debug & 4u) { mbar_arrive(&full[stage]); if (++stage == STAGES) { stage = 0; phase ^= 1u; } continue; }
           mbar_expect_tx(&full[stage], Cfg::STAGE_BYTES);
           const uint32_t sA = smem_base + stage * Cfg::STAGE_BYTES;
           const uint32_t sB = sA + Cfg::A_BYTES;
@@ -263,6 +330,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           for (int ks = 0; ks < kKSteps; ++ks) {
             const uint64_t ad = ((uint64_t)p.a.desc_hi << 32) | (uint64_t)(a_lo32 + ks * p.a.k_advance);
             const uint64_t bd = ((uint64_t)p.b.desc_hi << 32) | (uint64_t)(b_lo32 + ks * p.b.k_advance);
+            if (p.debug & 2u) continue;
             umma<TF32>(d_tmem, ad, bd, p.idesc, (kb | ks) != 0 ? 1u : 0u);
             if constexpr (SPLIT3) {
               umma<TF32>(d_tmem, ad + LO_OFF, bd, p.idesc, 1u);  // lo(A) * hi(B)
@@ -293,7 +361,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       float bv = 0.f;
       if (bias != nullptr && m_ok) bv = to_f32(bias[m]);
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = 0; c < ((p.debug & 1u) ? 0 : BN / 32); ++c) {
         uint32_t r[32];
         tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c * 32, r);
         tmem_ld_wait();
@@ -329,6 +397,386 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ----------------------------------------------------------------------------------------------
+// fp32-accurate kernel (3xTF32 with register accumulation).
+// The tensor core adds into its TMEM accumulator with truncation, and that error grows linearly
+// with the number of accumulating MMAs (measured: ~1e-7 relative per MMA, 1.9e-5 at K = 512 when a
+// whole K loop accumulates in TMEM). Here TMEM only ever holds ONE k-block's worth of products
+// (12 MMAs: hi*hi, lo*hi, hi*lo over 4 k-steps): after every k-block the eight epilogue warps pull
+// the 128 x 128 partial out of TMEM (two chunk buffers, so the next k-block's MMAs overlap) and add
+// it, round-to-nearest, into fp32 registers (64 per thread). Bias, activation and the store happen
+// once per tile from those registers. 128 x 128 tiles, 3 stages of {A_hi, B_hi, A_lo, B_lo}.
+// ----------------------------------------------------------------------------------------------
+constexpr int kAccThreads = 384;  // warps 0-2 as in the other kernels, warps 4-11 accumulate + epilogue
+constexpr int kAccBN = 128;
+
+template <int ACT>
+__global__ void __launch_bounds__(kAccThreads, 1)
+gemm_tc_f32acc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                      const __grid_constant__ CUtensorMap tmA_lo, const __grid_constant__ CUtensorMap tmB_lo,
+                      const __grid_constant__ TcParams p) {
+  using Cfg = TcCfg<kAccBN, true, true>;
+  constexpr int STAGES = Cfg::STAGES;
+  constexpr int BN = kAccBN;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + STAGES * Cfg::STAGE_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + STAGES;
+  uint64_t* chunk_full = bars + 2 * STAGES;   // [2] MMA -> accumulating warps (one k-block of products is in TMEM)
+  uint64_t* chunk_empty = chunk_full + 2;     // [2] accumulating warps -> MMA (chunk buffer may be overwritten)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(chunk_empty + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&chunk_full[a], 1); mbar_init(&chunk_empty[a], 8); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 2) {
+    tmem_alloc(tmem_slot, 256);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB); tma_prefetch_desc(&tmA_lo); tma_prefetch_desc(&tmB_lo);
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % p.tiles_m) * kBM, n0 = (tile / p.tiles_m) * BN;
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1u, p.status, 0x100u)) { ok = false; break; }
+          mbar_expect_tx(&full[stage], Cfg::STAGE_BYTES);
+          const uint32_t sA = smem_base + stage * Cfg::STAGE_BYTES;
+          const uint32_t sB = sA + Cfg::A_BYTES;
+          constexpr uint32_t LO = Cfg::A_BYTES + Cfg::B_BYTES;
+          const int k0 = kb * p.bk;
+          for (int bx = 0; bx < p.a.boxes; ++bx) {
+            const int32_t c0 = p.a.mn_major ? m0 + bx * p.a.mn_step : k0;
+            const int32_t c1 = p.a.mn_major ? k0 : m0;
+            tma_load_2d(sA + bx * p.a.box_bytes, &tmA, c0, c1, &full[stage]);
+            tma_load_2d(sA + LO + bx * p.a.box_bytes, &tmA_lo, c0, c1, &full[stage]);
+          }
+          for (int bx = 0; bx < p.b.boxes; ++bx) {
+            const int32_t c0 = p.b.mn_major ? n0 + bx * p.b.mn_step : k0;
+            const int32_t c1 = p.b.mn_major ? k0 : n0;
+            tma_load_2d(sB + bx * p.b.box_bytes, &tmB, c0, c1, &full[stage]);
+            tma_load_2d(sB + LO + bx * p.b.box_bytes, &tmB_lo, c0, c1, &full[stage]);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0, ch = 0, ch_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!mbar_wait(&chunk_empty[ch], ch_phase ^ 1u, p.status, 0x200u)) { ok = false; break; }
+          if (!mbar_wait(&full[stage], phase, p.status, 0x400u)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + ch * BN;
+          const uint32_t sA = smem_base + stage * Cfg::STAGE_BYTES;
+          const uint32_t sB = sA + Cfg::A_BYTES;
+          const uint32_t a_lo32 = ((sA >> 4) & 0x3FFFu) | p.a.desc_lbo;
+          const uint32_t b_lo32 = ((sB >> 4) & 0x3FFFu) | p.b.desc_lbo;
+          constexpr uint32_t LO_OFF = (Cfg::A_BYTES + Cfg::B_BYTES) >> 4;
+          // small terms first, so the large hi*hi products are added last
+#pragma unroll
+          for (int ks = 0; ks < kKSteps; ++ks) {
+            const uint64_t ad = ((uint64_t)p.a.desc_hi << 32) | (uint64_t)(a_lo32 + ks * p.a.k_advance);
+            const uint64_t bd = ((uint64_t)p.b.desc_hi << 32) | (uint64_t)(b_lo32 + ks * p.b.k_advance);
+            umma<true>(d_tmem, ad + LO_OFF, bd, p.idesc, ks != 0 ? 1u : 0u);
+            umma<true>(d_tmem, ad, bd + LO_OFF, p.idesc, 1u);
+          }
+#pragma unroll
+          for (int ks = 0; ks < kKSteps; ++ks) {
+            const uint64_t ad = ((uint64_t)p.a.desc_hi << 32) | (uint64_t)(a_lo32 + ks * p.a.k_advance);
+            const uint64_t bd = ((uint64_t)p.b.desc_hi << 32) | (uint64_t)(b_lo32 + ks * p.b.k_advance);
+            umma<true>(d_tmem, ad, bd, p.idesc, 1u);
+          }
+          umma_commit(&empty[stage]);
+          umma_commit(&chunk_full[ch]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          if (++ch == 2) { ch = 0; ch_phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp >= 4) {
+    const int q = warp & 3;             // TMEM lane quarter
+    const int half = (warp - 4) >> 2;   // which 64 of the tile's 128 columns
+    uint32_t ch = 0, ch_phase = 0;
+    float* D = reinterpret_cast<float*>(p.D);
+    float* P = reinterpret_cast<float*>(p.preact);
+    const float* bias = reinterpret_cast<const float*>(p.bias);
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      const int m0 = (tile % p.tiles_m) * kBM, n0 = (tile / p.tiles_m) * BN;
+      float sum[64];
+#pragma unroll
+      for (int j = 0; j < 64; ++j) sum[j] = 0.f;
+      for (int kb = 0; kb < p.num_kb; ++kb) {
+        if (!mbar_wait(&chunk_full[ch], ch_phase, p.status, 0x800u)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + ch * BN + half * 64;
+        uint32_t r0[32], r1[32];
+        tmem_ld32(t0, r0);
+        tmem_ld32(t0 + 32, r1);
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&chunk_empty[ch]);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) { sum[j] += __uint_as_float(r0[j]); sum[32 + j] += __uint_as_float(r1[j]); }
+        if (++ch == 2) { ch = 0; ch_phase ^= 1u; }
+      }
+      if (!ok) break;
+      const int64_t m = (int64_t)m0 + q * 32 + lane;
+      if (m < p.Mm) {
+        const float bv = bias != nullptr ? bias[m] : 0.f;
+#pragma unroll
+        for (int j = 0; j < 64; ++j) {
+          const int64_t n = (int64_t)n0 + half * 64 + j;
+          if (n < p.Nn) {
+            float v = sum[j] + bv;
+            const int64_t off = n * p.ldd + m;
+            if (P != nullptr) P[off] = v;
+            v = act_apply_any<ACT, false>(p.act, v);
+            if (p.accumulate) v += D[off];
+            D[off] = v;
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    if (*reinterpret_cast<volatile unsigned int*>(p.status) != 0) {
+      for (int i = 0; i < 64; ++i) __nanosleep(2000);
+    }
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 256);
+  }
+}
+
+// ----------------------------------------------------------------------------------------------
+// CTA-pair kernel: two CTAs on the two SMs of a TPC work on one 256 x 256 tile with
+// tcgen05.mma.cta_group::2. Each CTA loads its own 128 rows of A and its own 128 rows of B per
+// k-block (32 KB instead of the 48 KB a lone CTA needs for half the MMA work), so operand ingest
+// per tensor-pipe cycle drops from 96 to 64 bytes; each CTA keeps its 128 x 256 half of the
+// accumulator in its own TMEM (double-buffered) and runs its own epilogue. The leader CTA (cluster
+// rank 0) issues all MMAs. Synchronisation: the leader's `full` barriers count both CTAs' TMA
+// bytes (the partner's loads carry cta_group::2 and name the leader's barrier); stage release and
+// accumulator hand-over are tcgen05.commit arrivals sent to each CTA's own barrier (two commits,
+// one per CTA — no multicast anywhere); the partner's epilogue reports back with remote mbarrier
+// arrivals. All waits are time-bounded as in the single-CTA kernel.
+// ----------------------------------------------------------------------------------------------
+constexpr int kPairBN = 256;
+
+template <bool TF32, bool SPLIT3> struct PairCfg {
+  static constexpr int A_BYTES = kBM * 128;       // this CTA's 128 rows of A
+  static constexpr int B_BYTES = kBM * 128;       // this CTA's 128 of the tile's 256 B rows
+  static constexpr int STAGE_BYTES = (A_BYTES + B_BYTES) * (SPLIT3 ? 2 : 1);
+  static constexpr int STAGES = (192 * 1024) / STAGE_BYTES;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+};
+
+template <bool TF32, bool SPLIT3, int ACT, typename OutT>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const __grid_constant__ CUtensorMap tmA_lo, const __grid_constant__ CUtensorMap tmB_lo,
+                    const __grid_constant__ TcParams p) {
+  using Cfg = PairCfg<TF32, SPLIT3>;
+  constexpr int STAGES = Cfg::STAGES;
+  constexpr int BN = kPairBN;
+  constexpr bool FAST = sizeof(OutT) == 2;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + STAGES * Cfg::STAGE_BYTES);
+  uint64_t* full = bars;                    // [STAGES]  both CTAs' TMA -> leader's MMA (leader's copy is used)
+  uint64_t* empty = bars + STAGES;          // [STAGES]  MMA -> this CTA's TMA producer
+  uint64_t* acc_full = bars + 2 * STAGES;   // [2]       MMA -> this CTA's epilogue
+  uint64_t* acc_empty = acc_full + 2;       // [2]       both CTAs' epilogues -> leader's MMA
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_cta_rank();        // 0 = leader
+  const int num_tiles = p.tiles_m * p.tiles_n;     // 256 x 256 tiles
+  const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 2); mbar_init(&empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 8); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 2) {
+    tmem_alloc_pair(tmem_slot, 512);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  cluster_sync_all();   // barriers of both CTAs are initialised before anyone signals across
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer (one per CTA) ----------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      if constexpr (SPLIT3) { tma_prefetch_desc(&tmA_lo); tma_prefetch_desc(&tmB_lo); }
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+        const int m0 = (tile % p.tiles_m) * (2 * kBM) + (int)rank * kBM;
+        const int n0 = (tile / p.tiles_m) * BN + (int)rank * (BN / 2);
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1u, p.status, 0x10u)) { ok = false; break; }
+          const uint32_t leader_full = map_to_cta(smem_u32(&full[stage]), 0);
+          if (p.debug & 4u) {
+            if (rank == 0) mbar_arrive(&full[stage]); else mbar_arrive_cluster(leader_full);
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            continue;
+          }
+          if (rank == 0) mbar_expect_tx(&full[stage], Cfg::STAGE_BYTES);
+          else mbar_expect_tx_cluster(leader_full, Cfg::STAGE_BYTES);
+          const uint32_t sA = smem_base + stage * Cfg::STAGE_BYTES;
+          const uint32_t sB = sA + Cfg::A_BYTES;
+          const int k0 = kb * p.bk;
+          for (int bx = 0; bx < p.a.boxes; ++bx) {
+            const int32_t c0 = p.a.mn_major ? m0 + bx * p.a.mn_step : k0;
+            const int32_t c1 = p.a.mn_major ? k0 : m0;
+            tma_load_2d_pair(sA + bx * p.a.box_bytes, &tmA, c0, c1, leader_full);
+            if constexpr (SPLIT3) tma_load_2d_pair(sA + Cfg::A_BYTES + Cfg::B_BYTES + bx * p.a.box_bytes, &tmA_lo, c0, c1, leader_full);
+          }
+          for (int bx = 0; bx < p.b.boxes; ++bx) {
+            const int32_t c0 = p.b.mn_major ? n0 + bx * p.b.mn_step : k0;
+            const int32_t c1 = p.b.mn_major ? k0 : n0;
+            tma_load_2d_pair(sB + bx * p.b.box_bytes, &tmB, c0, c1, leader_full);
+            if constexpr (SPLIT3) tma_load_2d_pair(sB + Cfg::A_BYTES + Cfg::B_BYTES + bx * p.b.box_bytes, &tmB_lo, c0, c1, leader_full);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (leader CTA only) ----------------
+    if (lane == 0 && rank == 0) {
+      uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1u, p.status, 0x20u)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!mbar_wait(&full[stage], phase, p.status, 0x40u)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sA = smem_base + stage * Cfg::STAGE_BYTES;
+          const uint32_t sB = sA + Cfg::A_BYTES;
+          const uint32_t a_lo32 = ((sA >> 4) & 0x3FFFu) | p.a.desc_lbo;
+          const uint32_t b_lo32 = ((sB >> 4) & 0x3FFFu) | p.b.desc_lbo;
+          constexpr uint32_t LO_OFF = (Cfg::A_BYTES + Cfg::B_BYTES) >> 4;
+#pragma unroll
+          for (int ks = 0; ks < kKSteps; ++ks) {
+            const uint64_t ad = ((uint64_t)p.a.desc_hi << 32) | (uint64_t)(a_lo32 + ks * p.a.k_advance);
+            const uint64_t bd = ((uint64_t)p.b.desc_hi << 32) | (uint64_t)(b_lo32 + ks * p.b.k_advance);
+            if (p.debug & 2u) continue;
+            umma_pair<TF32>(d_tmem, ad, bd, p.idesc, (kb | ks) != 0 ? 1u : 0u);
+            if constexpr (SPLIT3) {
+              umma_pair<TF32>(d_tmem, ad + LO_OFF, bd, p.idesc, 1u);
+              umma_pair<TF32>(d_tmem, ad, bd + LO_OFF, p.idesc, 1u);
+            }
+          }
+          // release this stage in both CTAs once the MMAs above have read it
+          if (p.debug & 8u) {
+            umma_commit_pair_both(smem_u32(&empty[stage]));
+          } else {
+            umma_commit_pair(smem_u32(&empty[stage]));
+            umma_commit_pair(map_to_cta(smem_u32(&empty[stage]), 1));
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) {
+          if (p.debug & 8u) {
+            umma_commit_pair_both(smem_u32(&acc_full[acc]));
+          } else {
+            umma_commit_pair(smem_u32(&acc_full[acc]));
+            umma_commit_pair(map_to_cta(smem_u32(&acc_full[acc]), 1));
+          }
+        }
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  } else if (warp >= 4) {
+    // ---------------- epilogue (both CTAs, each on its own 128 rows) ----------------
+    const int q = warp & 3;
+    uint32_t acc = 0, acc_phase = 0;
+    OutT* D = reinterpret_cast<OutT*>(p.D);
+    OutT* P = reinterpret_cast<OutT*>(p.preact);
+    const OutT* bias = reinterpret_cast<const OutT*>(p.bias);
+    bool ok = true;
+    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+      const int m0 = (tile % p.tiles_m) * (2 * kBM) + (int)rank * kBM;
+      const int n0 = (tile / p.tiles_m) * BN;
+      if (!mbar_wait(&acc_full[acc], acc_phase, p.status, 0x80u)) { ok = false; break; }
+      tc_fence_after();
+      const int64_t m = (int64_t)m0 + q * 32 + lane;
+      const bool m_ok = m < p.Mm;
+      float bv = 0.f;
+      if (bias != nullptr && m_ok) bv = to_f32(bias[m]);
+#pragma unroll 1
+      for (int c = 0; c < ((p.debug & 1u) ? 0 : BN / 32); ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c * 32, r);
+        tmem_ld_wait();
+        if (m_ok) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int64_t n = (int64_t)n0 + c * 32 + j;
+            if (n < p.Nn) {
+              float v = __uint_as_float(r[j]) + bv;
+              const int64_t off = n * p.ldd + m;
+              if (P != nullptr) P[off] = from_f32<OutT>(v);
+              v = act_apply_any<ACT, FAST>(p.act, v);
+              if (p.accumulate) v += to_f32(D[off]);
+              D[off] = from_f32<OutT>(v);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if (rank == 0) mbar_arrive(&acc_empty[acc]);
+        else mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[acc]), 0));
+      }
+      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before();
+  cluster_sync_all();   // neither CTA leaves (or frees TMEM) while its partner may still touch it
+  if (warp == 2) {
+    if (*reinterpret_cast<volatile unsigned int*>(p.status) != 0) {
+      for (int i = 0; i < 64; ++i) __nanosleep(2000);
+    }
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, 512);
   }
 }
 
@@ -462,16 +910,98 @@ static int32_t tc_launch_cfg(const CUtensorMap& mA, const CUtensorMap& mB, const
   }
 }
 
+static int32_t tc_launch_f32acc(const CUtensorMap& mA, const CUtensorMap& mB, const CUtensorMap& mAl, const CUtensorMap& mBl,
+                                const TcParams& p, cudaStream_t st) {
+  using Cfg = TcCfg<kAccBN, true, true>;
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  auto launch = [&](auto kernel) -> int32_t {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return fail(LB2_LAUNCH_FAIL, "gemm_tc_f32acc: cannot reserve %d bytes of shared memory: %s", Cfg::SMEM_BYTES, cudaGetErrorString(e));
+    kernel<<<grid, kAccThreads, Cfg::SMEM_BYTES, st>>>(mA, mB, mAl, mBl, p);
+    LB2_CHECK_LAUNCH("gemm_tc_f32acc");
+    return LB2_OK;
+  };
+  switch (p.act) {
+    case LB2_ACT_IDENTITY: return launch(gemm_tc_f32acc_kernel<LB2_ACT_IDENTITY>);
+    case LB2_ACT_RELU: return launch(gemm_tc_f32acc_kernel<LB2_ACT_RELU>);
+    default: return launch(gemm_tc_f32acc_kernel<-1>);
+  }
+}
+
+template <bool TF32, bool SPLIT3, typename OutT>
+static int32_t tc_launch_pair(const CUtensorMap& mA, const CUtensorMap& mB, const CUtensorMap& mAl, const CUtensorMap& mBl,
+                              const TcParams& p, cudaStream_t st) {
+  using Cfg = PairCfg<TF32, SPLIT3>;
+  const int tiles = p.tiles_m * p.tiles_n;
+  auto launch = [&](auto kernel) -> int32_t {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return fail(LB2_LAUNCH_FAIL, "gemm_tc_pair: cannot reserve %d bytes of shared memory: %s", Cfg::SMEM_BYTES, cudaGetErrorString(e));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(sm_count() & ~1, 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    // Tiles are dealt round-robin to the clusters, so every cluster must be resident from the
+    // start: launch exactly as many CTA pairs as the device can hold at once (GPC boundaries can
+    // leave a few SMs unpaired). Cached per device.
+    static std::mutex mu;
+    static int resident[64] = {0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    int clusters = 0;
+    {
+      std::lock_guard<std::mutex> lk(mu);
+      if (dev >= 0 && dev < 64 && resident[dev] == 0) {
+        int n = 0;
+        e = cudaOccupancyMaxActiveClusters(&n, kernel, &cfg);
+        if (e != cudaSuccess || n <= 0) {
+          cudaGetLastError();
+          n = sm_count() / 2;
+        }
+        resident[dev] = n;
+        if (getenv("LB2_DEBUG")) fprintf(stderr, "[lb2] gemm_tc_pair: %d resident CTA pairs on device %d\n", n, dev);
+      }
+      clusters = (dev >= 0 && dev < 64) ? resident[dev] : sm_count() / 2;
+    }
+    if (tiles < clusters) clusters = tiles;
+    cfg.gridDim = dim3(2 * clusters, 1, 1);
+    e = cudaLaunchKernelEx(&cfg, kernel, mA, mB, mAl, mBl, p);
+    if (e != cudaSuccess) return fail(LB2_LAUNCH_FAIL, "gemm_tc_pair: %s", cudaGetErrorString(e));
+    return LB2_OK;
+  };
+  switch (p.act) {
+    case LB2_ACT_IDENTITY: return launch(gemm_tc_pair_kernel<TF32, SPLIT3, LB2_ACT_IDENTITY, OutT>);
+    case LB2_ACT_RELU: return launch(gemm_tc_pair_kernel<TF32, SPLIT3, LB2_ACT_RELU, OutT>);
+    case LB2_ACT_GELU_TANH: return launch(gemm_tc_pair_kernel<TF32, SPLIT3, LB2_ACT_GELU_TANH, OutT>);
+    default: return launch(gemm_tc_pair_kernel<TF32, SPLIT3, -1, OutT>);
+  }
+}
+
 int32_t gemm_tc_launch(void* D, int64_t ldd, GemmOperand A, GemmOperand B, int64_t Mm, int64_t Nn, int64_t Kc,
-                       int32_t dtype, int split3, const GemmEpilogue& epi, void* split_ws, cudaStream_t st) {
+                       int32_t dtype, int split3, uint32_t flags, const GemmEpilogue& epi, void* split_ws,
+                       cudaStream_t st) {
   const bool tf32 = dtype == LB2_F32;
   const int es = tf32 ? 4 : 2;
   const int bk = 128 / es;
   // BN = 256 halves the A-operand traffic per FLOP; BN = 128 keeps more tiles for small problems and
   // leaves room for the doubled 3xTF32 stages.
   const bool split = tf32 && split3;
+  // Default: the single-CTA kernel (BN = 128 when that is what it takes to fill the machine). The
+  // CTA-pair kernel is opt-in (LB2_FLAG_CTA_PAIR): it moves a third fewer operand bytes but its
+  // cta_group::2 MMA stream measured no faster on the dense benchmark shape.
+  const int64_t pair_tiles = ((Mm + 2 * kBM - 1) / (2 * kBM)) * ((Nn + kPairBN - 1) / kPairBN);
+  const bool pair = !split && (flags & LB2_FLAG_CTA_PAIR) && pair_tiles >= sm_count() / 4;
   int bn = 256;
-  if (split) bn = 128;
+  if (pair) bn = kPairBN / 2;  // rows of B each CTA of a pair loads
+  else if (split) bn = 128;
   else if (((Mm + kBM - 1) / kBM) * ((Nn + 255) / 256) < sm_count()) bn = 128;
 
   TcParams p{};
@@ -504,20 +1034,29 @@ int32_t gemm_tc_launch(void* D, int64_t ldd, GemmOperand A, GemmOperand B, int64
   }
   p.Mm = Mm; p.Nn = Nn; p.Kc = Kc;
   p.bk = bk;
-  p.tiles_m = (int)((Mm + kBM - 1) / kBM);
-  p.tiles_n = (int)((Nn + bn - 1) / bn);
+  const int tile_m = pair ? 2 * kBM : kBM, tile_n = pair ? kPairBN : bn;
+  p.tiles_m = (int)((Mm + tile_m - 1) / tile_m);
+  p.tiles_n = (int)((Nn + tile_n - 1) / tile_n);
   p.num_kb = (int)((Kc + bk - 1) / bk);
   // instruction descriptor: D = f32 (bit 4), A/B format (bits 7-9 / 10-12: 1 = bf16, 2 = tf32),
   // A/B major (bits 15 / 16: 1 = MN-major), N >> 3 (bits 17-22), M >> 4 (bits 24-28)
   const uint32_t fmt = tf32 ? 2u : 1u;
   p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((A.mn_major ? 1u : 0u) << 15) | ((B.mn_major ? 1u : 0u) << 16) |
-            ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+            ((uint32_t)(tile_n >> 3) << 17) | ((uint32_t)(tile_m >> 4) << 24);
   p.D = D; p.ldd = ldd;
   p.bias = epi.bias; p.preact = epi.preact; p.act = epi.act; p.accumulate = epi.accumulate;
   p.status = device_status_word();
   LB2_REQUIRE(p.status != nullptr, LB2_LAUNCH_FAIL, "gemm_tc: device status word unavailable");
+  {
+    static const uint32_t dbg = getenv("LB2_GEMM_DEBUG") ? (uint32_t)atoi(getenv("LB2_GEMM_DEBUG")) : 0u;
+    p.debug = dbg;
+  }
+  if (pair) {
+    if (tf32) return tc_launch_pair<true, false, float>(mA, mB, mAl, mBl, p, st);
+    return tc_launch_pair<false, false, __nv_bfloat16>(mA, mB, mAl, mBl, p, st);
+  }
   if (tf32) {
-    if (split) return tc_launch_cfg<128, true, true, float>(mA, mB, mAl, mBl, p, st);
+    if (split) return tc_launch_f32acc(mA, mB, mAl, mBl, p, st);
     if (bn == 256) return tc_launch_cfg<256, true, false, float>(mA, mB, mAl, mBl, p, st);
     return tc_launch_cfg<128, true, false, float>(mA, mB, mAl, mBl, p, st);
   }
@@ -552,7 +1091,7 @@ int32_t gemm_dispatch(void* D, int64_t ldd, GemmOperand A, GemmOperand B, int64_
       const size_t need = gemm_tc_split_workspace_bytes(A, B, Mm, Nn, Kc);
       LB2_REQUIRE(ws != nullptr && ws_bytes >= need, LB2_WORKSPACE_TOO_SMALL, "fp32 GEMM needs %zu bytes of workspace", need);
     }
-    return gemm_tc_launch(D, ldd, A, B, Mm, Nn, Kc, dtype, split3, epi, ws, st);
+    return gemm_tc_launch(D, ldd, A, B, Mm, Nn, Kc, dtype, split3, flags, epi, ws, st);
   }
   return gemm_simt_launch(D, ldd, A, B, Mm, Nn, Kc, dtype, epi, st);
 }

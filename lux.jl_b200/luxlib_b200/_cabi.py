@@ -12,7 +12,7 @@ LIB_PATH = os.path.join(os.path.dirname(_HERE), "lib", "libluxlib_b200.so")
 OK, BAD_ARG, BAD_SHAPE, BAD_ALIGN, UNSUPPORTED_DTYPE, LAUNCH_FAIL, TIMEOUT, WORKSPACE_TOO_SMALL = 0, -1, -2, -3, -4, -5, -6, -7
 F32, BF16 = 0, 1
 ACT_IDENTITY, ACT_RELU, ACT_GELU_TANH, ACT_GELU_ERF, ACT_TANH, ACT_SIGMOID, ACT_SWISH = range(7)
-FLAG_TF32_1X, FLAG_FORCE_SIMT = 1, 2
+FLAG_TF32_1X, FLAG_FORCE_SIMT, FLAG_CTA_PAIR = 1, 2, 4
 
 
 class ConvDesc(C.Structure):

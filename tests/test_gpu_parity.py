@@ -140,6 +140,39 @@ def test_matmul_all_layouts(dt, ta, tb):
     check(L.matmul(dev(A, dt), dev(B, dt), transA=ta, transB=tb), ref, dt, "C")
 
 
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("flags", [0, 4])  # single-CTA kernel (default) and CTA-pair kernel (LB2_FLAG_CTA_PAIR)
+@pytest.mark.parametrize("mnk", [(2048, 2560, 512), (2100, 2330, 200), (2560, 2304, 2560), (2500, 2190, 2328)])
+def test_fused_dense_large_tiles_both_tensor_core_kernels(dt, flags, mnk):
+    M, N, K = mnk
+    rng = np.random.default_rng(21)
+    W = prep(O.glorot_uniform(rng, (M, K)), dt)
+    x = prep(rng.standard_normal((K, N)), dt)
+    b = prep(rng.uniform(-0.1, 0.1, M), dt)
+    y_ref, pb_ref = O.fused_dense_rrule("gelu", W, x, b)
+    y, pb = L.rrule_fused_dense("gelu", dev(W, dt), dev(x, dt), dev(b, dt), flags=flags)
+    check(y, y_ref, dt, "y")
+    delta = prep(rng.standard_normal((M, N)), dt)
+    dW_ref, dx_ref, db_ref = pb_ref(delta)
+    dW, dx, db = pb(dev(delta, dt))
+    check(dW, dW_ref, dt, "dW")
+    check(dx, dx_ref, dt, "dx")
+    check(db, db_ref, dt, "db")
+    assert L._cabi.load().lb2_poll_device_status(None) == 0
+
+
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("ta,tb", [(False, False), (True, False), (False, True), (True, True)])
+def test_matmul_all_layouts_cta_pair_kernel(dt, ta, tb):
+    rng = np.random.default_rng(22)
+    M, N, K = 2304, 2250, 328
+    A = prep(rng.standard_normal((K, M) if ta else (M, K)), dt)
+    B = prep(rng.standard_normal((N, K) if tb else (K, N)), dt)
+    ref = (A.T if ta else A) @ (B.T if tb else B)
+    check(L.matmul(dev(A, dt), dev(B, dt), transA=ta, transB=tb, flags=L._cabi.FLAG_CTA_PAIR), ref, dt, "C")
+    assert L._cabi.load().lb2_poll_device_status(None) == 0
+
+
 def test_dense_tf32_single_pass_flag_is_looser_but_close():
     rng = np.random.default_rng(13)
     W, x = rng.standard_normal((256, 512)).astype(np.float32), rng.standard_normal((512, 256)).astype(np.float32)
