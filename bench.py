@@ -333,15 +333,118 @@ def run_gpu_arm(args):
     return 0
 
 
+# ---------------------------------------------------------------------------------------------
+# secondary workloads (the other configurations of the path): one JSON line each, single GPU
+# ---------------------------------------------------------------------------------------------
+def hbm_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f).get("hbm_gbs", 6552.0), "measured"
+    return 6650.0, "fallback"
+
+
+def run_secondary(args):
+    """--workload ln | gn | bn | conv  [--dtype f32|bf16]: norm rows report algorithmic GB/s
+    (5*numel*sizeof(T) per fwd+bwd step) against the measured HBM copy bandwidth; conv reports
+    TFLOP/s (3 x 2*Wo*Ho*N*Cout*Cin*kW*kH per step) against the measured bf16 tensor peak."""
+    import torch
+    import luxlib_b200 as L
+    from oracle import luxlib_oracle as O
+    torch.cuda.set_device(0)
+    tdt = torch.float32 if args.dtype == "f32" else torch.bfloat16
+    es = 4 if args.dtype == "f32" else 2
+    g = torch.Generator(device="cuda").manual_seed(3)
+    rn = lambda *shape: torch.randn(*shape, device="cuda", generator=g)
+    cm = lambda t: t.permute(*reversed(range(t.dim()))) if t.dim() > 1 else t  # row-major bytes -> Julia shape
+    wl = args.workload
+    if wl == "ln":
+        D, R = 4096, 16384
+        x = cm((rn(R, D) * 1.3).to(tdt)); dy = cm(rn(R, D).to(tdt))
+        gam = (torch.rand(D, device="cuda", generator=g) + 0.5).to(tdt); bet = (rn(D) * 0.1).to(tdt)
+        def step():
+            y, pb = L.rrule_layernorm(x, gam, bet, "identity", None, 1e-5)
+            return pb(dy)
+        numel, launches, name = D * R, 3, "LayerNorm 4096x16384 (rows of 4096), affine, fwd+bwd"
+    elif wl == "gn":
+        shape = (128, 512, 32, 32)  # N, C, H, W row-major == WHCN column-major
+        x = cm((rn(*shape) * (torch.rand(1, 512, 1, 1, device="cuda", generator=g) * 1.5 + 0.5)).to(tdt)); dy = cm(rn(*shape).to(tdt))
+        gam = (torch.rand(512, device="cuda", generator=g) + 0.5).to(tdt); bet = (rn(512) * 0.1).to(tdt)
+        def step():
+            y, pb = L.rrule_groupnorm(x, gam, bet, 32, "identity", 1e-5)
+            return pb(dy)
+        numel, launches, name = 128 * 512 * 32 * 32, 3, "GroupNorm(32 groups) 32x32x512x128, affine, fwd+bwd"
+    elif wl == "bn":
+        shape = (256, 64, 56, 56)
+        x = cm(rn(*shape).to(tdt)); dy = cm(rn(*shape).to(tdt))
+        gam = torch.ones(64, device="cuda", dtype=tdt); bet = torch.zeros(64, device="cuda", dtype=tdt)
+        rm = torch.zeros(64, device="cuda", dtype=tdt); rv = torch.ones(64, device="cuda", dtype=tdt)
+        def step():
+            y, st, pb = L.rrule_batchnorm(x, gam, bet, rm, rv, True, "relu", 0.1, 1e-5)
+            return pb(dy)
+        numel, launches, name = 256 * 64 * 56 * 56, 6, "BatchNorm(64)+relu 56x56x64x256 training, running stats, fwd+bwd"
+    elif wl == "conv":
+        x = cm(rn(256, 64, 56, 56).to(tdt)); dy = cm(rn(256, 64, 56, 56).to(tdt))
+        w = cm((rn(64, 64, 3, 3) * (2.0 / 576) ** 0.5).to(tdt)); b = torch.zeros(64, device="cuda", dtype=tdt)
+        cd = L.ConvDims.make(2, 1, 1, 1, 1, False)
+        def step():
+            y, pb = L.rrule_fused_conv("identity", w, x, b, cd)
+            return pb(dy)
+        numel, launches, name = 256 * 64 * 56 * 56, 0, "Conv 3x3 64->64 s1 p1 on 56x56x64x256, fwd + dx + dw + db"
+    else:
+        raise SystemExit(f"unknown workload {wl}")
+    warm = max(args.warmup, 3)
+    for _ in range(warm):
+        step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(0)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler.start()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1) / args.steps
+    rc = L._cabi.load().lb2_poll_device_status(None)
+    if rc != 0:
+        raise SystemExit(f"device status {rc}")
+    if wl == "conv":
+        flop = 3 * 2.0 * 56 * 56 * 256 * 64 * 64 * 9
+        sustained, burst, which = measured_peaks()
+        val = flop / (ms * 1e-3) / 1e12
+        line = {"metric": "fused conv+bias+act fwd+bwd TFLOP/s", "value": val, "unit": "TFLOP/s",
+                "roofline": {"bound": "tensor", "achieved": val, "peak": sustained, "unit": "TFLOP/s", "frac": val / sustained,
+                             "traffic": None, "peak_source": f"{which}: bf16_tflops_sustained; whole step (layout passes, 3 GEMM-like kernels, reductions)"}}
+    else:
+        byts = 5.0 * numel * es
+        peak, which = hbm_peak()
+        val = byts / (ms * 1e-3) / 1e9
+        line = {"metric": "norm fwd+bwd HBM GB/s", "value": val, "unit": "GB/s",
+                "roofline": {"bound": "hbm", "achieved": val, "peak": peak, "unit": "GB/s", "frac": val / peak, "traffic": None,
+                             "peak_source": f"{which}: hbm_gbs; algorithmic bytes 5*numel*sizeof(T) over the whole fwd+bwd step"}}
+    line.update({"n_gpus": 1, "steps": args.steps, "warmup": warm, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+                 "vs_baseline": None, "dtype": args.dtype, "data": "synthetic", "config": {"workload": name}, "clocks": clocks,
+                 "gpu_launches": launches * args.steps if launches else None})
+    print(json.dumps(line), flush=True)
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="dense", choices=["dense", "ln", "gn", "bn", "conv"],
+                    help="dense = the headline configuration (default); the others are single-GPU secondary rows")
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "f32"], help="storage type of the secondary workloads")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)
+    if args.workload != "dense":
+        return run_secondary(args)
     return run_gpu_arm(args)
 
 

@@ -1,0 +1,707 @@
+// Tensor-core convolution for sm_100a (bf16 storage, fp32 accumulation in TMEM): implicit GEMM on
+// the WHCN (column-major) layout without an im2col buffer.
+//
+// Shapes taken: 2-D, stride 1, dilation 1, groups 1, output width == input width ("same" along W),
+// W*sizeof(T) a multiple of 16 bytes. Everything else stays on the direct kernels.
+//
+// Formulation. With s = w + W*h the flattened spatial index of one image, a kernel tap (tw, th) reads
+// x at s + (tw - pad_w) + (th - pad_h)*W. The H part of that shift is a multiple of 16 bytes and is
+// applied as a TMA start coordinate on a 4-D tensor map (s, channel, image, copy) whose out-of-range
+// rows are zero-filled — that is the top/bottom padding. The W part is a single-element shift, which
+// TMA cannot start on, so a bandwidth pass first writes kW copies of the input, copy t shifted by
+// t - pad_w along W with zeros at the row ends (the left/right padding). The GEMM then is
+//   y[s, co] (+)= sum over k-blocks (tap, 64 input channels) of  A_kb[s, ci] * Wp[co, kb*64 + ci]
+// with A MN-major (s contiguous) straight from the shifted copies, the packed filter Wp K-major and
+// RESIDENT in shared memory for the whole persistent CTA (it is the same for every tile), M = 128
+// spatial positions, N = 64 or 128 output channels, fp32 accumulators double-buffered in TMEM.
+// The data gradient is the same kernel on dy with the filter packed flipped and transposed.
+// The filter gradient contracts over (s, image): per CTA a K-range of 64-position blocks, A = two
+// taps' shifted input rows stacked to M = 128 (K-major), B = dy rows (K-major), fp32 partials per
+// K-split in the workspace and a fixed-order reduction — deterministic.
+//
+// Roofline: tensor pipe; algorithmic FLOPs = 2*Wo*Ho*N*Cout*Cin*kW*kH per pass.
+#include "conv.cuh"
+#include "tc_ptx.cuh"
+
+namespace lb2 {
+
+constexpr int kConvThreads = 256;
+constexpr int kConvBM = 128;
+constexpr int kMaxKb = 96;
+
+// ----------------------------------------------------------------------------------------------
+// layout passes
+// ----------------------------------------------------------------------------------------------
+// out[t][n][c][h][w] = in[n][c][h][w + t - pad_w]  (0 outside the row), t = 0..kW-1
+template <typename T>
+__global__ void __launch_bounds__(256) conv_shift_copies_kernel(T* __restrict__ out, const T* __restrict__ in,
+                                                                int W, int64_t rows, int kW, int pad_w) {
+  // one thread per 8-element group of a row; rows = H*C*N
+  const int groups = (W + 7) / 8;
+  const int64_t total = rows * groups;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = i / groups;
+    const int w0 = (int)(i % groups) * 8;
+    const T* src = in + row * W;
+    // the 8 outputs of every copy need inputs w0 - pad_w + t .. +7: fetch the covering window once
+    T win[8 + 8];
+    const int lo = w0 - pad_w;  // window start (copy 0)
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const int w = lo + j;
+      win[j] = (j < 8 + kW - 1 && w >= 0 && w < W) ? src[w] : from_f32<T>(0.f);
+    }
+    for (int t = 0; t < kW; ++t) {
+      T* dst = out + ((int64_t)t * rows + row) * W + w0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (w0 + j < W) dst[j] = win[j + t];
+    }
+  }
+}
+
+// Packed filter for the forward / data-gradient GEMM: Wp[nrow][kb*64 + j], nrow = GEMM output channel,
+// k-block kb = (tap, 64-channel chunk). `transpose` selects the data-gradient packing (output channel
+// of the GEMM = conv input channel, taps reversed).
+struct PackGeom {
+  int kW, kH, cin, cout;   // of the convolution's filter w (kW, kH, cin, cout)
+  int flip;                // ConvDims flipkernel
+  int transpose;           // 0: forward, 1: data gradient
+  int chunks;              // 64-channel chunks of the contracted channel count
+  int n_rows, k_total;     // rows (padded to the N tile) and columns of Wp
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) conv_pack_filter_kernel(T* __restrict__ wp, const T* __restrict__ w,
+                                                               const PackGeom g) {
+  const int64_t total = (int64_t)g.n_rows * g.k_total;
+  const int kc = g.transpose ? g.cout : g.cin;   // contracted channels
+  const int nc = g.transpose ? g.cin : g.cout;   // GEMM output channels
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int row = (int)(i / g.k_total);
+    const int col = (int)(i % g.k_total);
+    const int kb = col / 64, j = col % 64;
+    const int tap = kb / g.chunks, c = (kb % g.chunks) * 64 + j;
+    const int tw = tap % g.kW, th = tap / g.kW;   // tap position: x offset (tw - pad_w, th - pad_h)
+    float v = 0.f;
+    if (row < nc && c < kc) {
+      // forward: tap position t corresponds to filter index k with t = flip ? k : K-1-k
+      // data gradient: position t' = K-1-t of the forward tap
+      int tw_f = g.transpose ? g.kW - 1 - tw : tw, th_f = g.transpose ? g.kH - 1 - th : th;
+      const int kw = g.flip ? tw_f : g.kW - 1 - tw_f, kh = g.flip ? th_f : g.kH - 1 - th_f;
+      const int ci = g.transpose ? row : c, co = g.transpose ? c : row;
+      v = to_f32(w[((int64_t)(co * g.cin + ci) * g.kH + kh) * g.kW + kw]);
+    }
+    wp[i] = from_f32<T>(v);
+  }
+}
+
+// ----------------------------------------------------------------------------------------------
+// forward / data-gradient kernel
+// ----------------------------------------------------------------------------------------------
+struct ConvTcParams {
+  int32_t S_out;          // flattened output positions per image (W * Ho)
+  int32_t n_img, n_out;   // images, GEMM output channels
+  int32_t tiles_m, tiles_n, num_kb;
+  int32_t stages;         // A-operand ring depth
+  uint32_t idesc;
+  uint32_t a_desc_hi, a_desc_lbo, a_k_advance;
+  uint32_t b_desc_hi, b_desc_lbo, b_k_advance;
+  void* y;
+  void* preact;
+  const void* bias;       // per GEMM output channel, or null
+  int32_t act;
+  unsigned int* status;
+  int16_t a_shift[kMaxKb];   // start-coordinate offset along s (multiple of 8 elements)
+  int16_t a_chan[kMaxKb];    // first contracted channel of the k-block
+  int8_t a_copy[kMaxKb];     // which W-shifted copy
+};
+
+template <int BN, int ACT>
+__global__ void __launch_bounds__(kConvThreads, 1)
+conv_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
+                   const __grid_constant__ ConvTcParams p) {
+  constexpr int A_BYTES = kConvBM * 128;   // 128 positions x 64 channels bf16
+  constexpr int B_BYTES = BN * 128;        // BN output channels x 64 contracted channels
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t sB0 = smem_base;                                // resident filter: num_kb tiles
+  const uint32_t sA0 = smem_base + p.num_kb * B_BYTES;           // A ring
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + p.num_kb * B_BYTES + p.stages * A_BYTES);
+  uint64_t* full = bars;                       // [stages]
+  uint64_t* empty = bars + p.stages;           // [stages]
+  uint64_t* acc_full = bars + 2 * p.stages;    // [2]
+  uint64_t* acc_empty = acc_full + 2;          // [2]
+  uint64_t* b_full = acc_empty + 2;            // [1] resident filter landed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(b_full + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_per_n = p.tiles_m * p.n_img;
+  const int num_tiles = tiles_per_n * p.tiles_n;
+  const int stages = p.stages;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 4); }
+    mbar_init(b_full, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 2) {
+    tmem_alloc(tmem_slot, 2 * BN);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // This CTA's tiles all use the same n-tile when tiles_n == 1 (the common case); with several
+  // n-tiles the resident filter would differ per tile, so the grid is partitioned by n-tile instead:
+  // CTA b works on n-tile (b % tiles_n) and strides over the (m, image) tiles of that n-tile.
+  const int nt = blockIdx.x % p.tiles_n;
+  const int first = blockIdx.x / p.tiles_n, step = gridDim.x / p.tiles_n;
+  const int n0 = nt * BN;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tmX);
+      tma_prefetch_desc(&tmW);
+      mbar_expect_tx(b_full, (uint32_t)(p.num_kb * B_BYTES));
+      for (int kb = 0; kb < p.num_kb; ++kb) tma_load_2d(sB0 + kb * B_BYTES, &tmW, kb * 64, n0, b_full);
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int t = first; t < tiles_per_n && ok; t += step) {
+        const int m0 = (t % p.tiles_m) * kConvBM, img = t / p.tiles_m;
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1u, p.status, 0x1000u)) { ok = false; break; }
+          mbar_expect_tx(&full[stage], A_BYTES);
+          const uint32_t sA = sA0 + stage * A_BYTES;
+          const int c0 = m0 + p.a_shift[kb];
+          tma_load_4d(sA, &tmX, c0, p.a_chan[kb], img, p.a_copy[kb], &full[stage]);
+          tma_load_4d(sA + A_BYTES / 2, &tmX, c0 + 64, p.a_chan[kb], img, p.a_copy[kb], &full[stage]);
+          if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+      bool ok = mbar_wait(b_full, 0, p.status, 0x2000u);
+      for (int t = first; t < tiles_per_n && ok; t += step) {
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1u, p.status, 0x4000u)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!mbar_wait(&full[stage], phase, p.status, 0x8000u)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sA = sA0 + stage * A_BYTES;
+          const uint32_t sB = sB0 + kb * B_BYTES;
+          const uint32_t a_lo32 = ((sA >> 4) & 0x3FFFu) | p.a_desc_lbo;
+          const uint32_t b_lo32 = ((sB >> 4) & 0x3FFFu) | p.b_desc_lbo;
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) {
+            const uint64_t ad = ((uint64_t)p.a_desc_hi << 32) | (uint64_t)(a_lo32 + ks * p.a_k_advance);
+            const uint64_t bd = ((uint64_t)p.b_desc_hi << 32) | (uint64_t)(b_lo32 + ks * p.b_k_advance);
+            umma<false>(d_tmem, ad, bd, p.idesc, (kb | ks) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty[stage]);
+          if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) umma_commit(&acc_full[acc]);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  } else if (warp >= 4) {
+    const int q = warp & 3;
+    uint32_t acc = 0, acc_phase = 0;
+    __nv_bfloat16* Y = reinterpret_cast<__nv_bfloat16*>(p.y);
+    __nv_bfloat16* P = reinterpret_cast<__nv_bfloat16*>(p.preact);
+    const __nv_bfloat16* bias = reinterpret_cast<const __nv_bfloat16*>(p.bias);
+    bool ok = true;
+    for (int t = first; t < tiles_per_n && ok; t += step) {
+      const int m0 = (t % p.tiles_m) * kConvBM, img = t / p.tiles_m;
+      if (!mbar_wait(&acc_full[acc], acc_phase, p.status, 0x10000u)) { ok = false; break; }
+      tc_fence_after();
+      const int s = m0 + q * 32 + lane;
+      const bool s_ok = s < p.S_out;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c * 32, r);
+        tmem_ld_wait();
+        if (s_ok) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int co = n0 + c * 32 + j;
+            if (co < p.n_out) {
+              float v = __uint_as_float(r[j]);
+              if (bias != nullptr) v += __bfloat162float(bias[co]);
+              const int64_t off = (int64_t)s + (int64_t)p.S_out * (co + (int64_t)p.n_out * img);
+              if (P != nullptr) P[off] = __float2bfloat16_rn(v);
+              Y[off] = __float2bfloat16_rn(act_apply_any<ACT, true>(p.act, v));
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    if (*reinterpret_cast<volatile unsigned int*>(p.status) != 0) {
+      for (int i = 0; i < 64; ++i) __nanosleep(2000);
+    }
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 2 * BN);
+  }
+}
+
+
+// ----------------------------------------------------------------------------------------------
+// filter-gradient kernel
+// ----------------------------------------------------------------------------------------------
+// Row groups of 64 rows each: rg = tap * chunks + chunk. An M tile stacks row groups 2j and 2j+1.
+struct ConvWgParams {
+  int32_t S_out, n_img, n_out;       // contraction extent per image, images, dy channels (GEMM N)
+  int32_t s_blocks;                  // 64-position blocks per image
+  int32_t m_tiles, tiles_n, splits;  // work item = (m tile, n tile, K split)
+  int32_t kb_total, kb_per_split;
+  int32_t n_rg;                      // number of row groups
+  int32_t stages;
+  uint32_t idesc;
+  uint32_t desc_hi, desc_lbo, k_advance;   // both operands K-major SW128
+  float* partial;                    // [splits][m_tiles*128][n_pad]
+  int32_t n_pad;
+  unsigned int* status;
+  int16_t rg_shift[2 * kMaxKb];      // per row group: start offset along s, first channel, copy
+  int16_t rg_chan[2 * kMaxKb];
+  int8_t rg_copy[2 * kMaxKb];
+};
+
+template <int BN>
+__global__ void __launch_bounds__(kConvThreads, 1)
+conv_tc_wgrad_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmG,
+                     const __grid_constant__ ConvWgParams p) {
+  constexpr int A_BYTES = kConvBM * 128;
+  constexpr int B_BYTES = BN * 128;
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + p.stages * STAGE_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + p.stages;
+  uint64_t* acc_full = bars + 2 * p.stages;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int stages = p.stages;
+  const int num_items = p.m_tiles * p.tiles_n * p.splits;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 4); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 2) {
+    tmem_alloc(tmem_slot, 2 * BN);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // item -> (m tile fastest, n tile, split)
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tmX);
+      tma_prefetch_desc(&tmG);
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+        const int mt = item % p.m_tiles, nt = (item / p.m_tiles) % p.tiles_n, z = item / (p.m_tiles * p.tiles_n);
+        const int kb_lo = z * p.kb_per_split, kb_hi = min(p.kb_total, kb_lo + p.kb_per_split);
+        const int rg0 = 2 * mt, rg1 = 2 * mt + 1;
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1u, p.status, 0x20000u)) { ok = false; break; }
+          const int img = kb / p.s_blocks, s0 = (kb % p.s_blocks) * 64;
+          const uint32_t sA = smem_base + stage * STAGE_BYTES, sB = sA + A_BYTES;
+          const bool two = rg1 < p.n_rg;
+          mbar_expect_tx(&full[stage], (uint32_t)(B_BYTES + (two ? A_BYTES : A_BYTES / 2)));
+          tma_load_4d(sA, &tmX, s0 + p.rg_shift[rg0], p.rg_chan[rg0], img, p.rg_copy[rg0], &full[stage]);
+          if (two) tma_load_4d(sA + A_BYTES / 2, &tmX, s0 + p.rg_shift[rg1], p.rg_chan[rg1], img, p.rg_copy[rg1], &full[stage]);
+          tma_load_4d(sB, &tmG, s0, nt * BN, img, 0, &full[stage]);
+          if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+        const int z = item / (p.m_tiles * p.tiles_n);
+        const int kb_lo = z * p.kb_per_split, kb_hi = min(p.kb_total, kb_lo + p.kb_per_split);
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1u, p.status, 0x40000u)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {
+          if (!mbar_wait(&full[stage], phase, p.status, 0x80000u)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sA = smem_base + stage * STAGE_BYTES, sB = sA + A_BYTES;
+          const uint32_t a_lo32 = ((sA >> 4) & 0x3FFFu) | p.desc_lbo;
+          const uint32_t b_lo32 = ((sB >> 4) & 0x3FFFu) | p.desc_lbo;
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) {
+            const uint64_t ad = ((uint64_t)p.desc_hi << 32) | (uint64_t)(a_lo32 + ks * p.k_advance);
+            const uint64_t bd = ((uint64_t)p.desc_hi << 32) | (uint64_t)(b_lo32 + ks * p.k_advance);
+            umma<false>(d_tmem, ad, bd, p.idesc, (kb > kb_lo || ks != 0) ? 1u : 0u);
+          }
+          umma_commit(&empty[stage]);
+          if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) umma_commit(&acc_full[acc]);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  } else if (warp >= 4) {
+    const int q = warp & 3;
+    uint32_t acc = 0, acc_phase = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+      const int mt = item % p.m_tiles, nt = (item / p.m_tiles) % p.tiles_n, z = item / (p.m_tiles * p.tiles_n);
+      const int kb_lo = z * p.kb_per_split;
+      const bool empty_range = kb_lo >= p.kb_total;   // a split with no k-blocks contributes zeros
+      if (!empty_range) {
+        if (!mbar_wait(&acc_full[acc], acc_phase, p.status, 0x100000u)) { ok = false; break; }
+        tc_fence_after();
+      }
+      const int row = mt * 128 + q * 32 + lane;
+      float* dst = p.partial + ((int64_t)z * p.m_tiles * 128 + row) * p.n_pad + nt * BN;
+      // A row group that was not loaded (odd tail) leaves stale shared memory under the MMA: its rows
+      // are never read by the reduction, but they are written as zeros to keep the buffer defined.
+      const bool live = (row / 64) < p.n_rg;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        if (!empty_range) {
+          tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c * 32, r);
+          tmem_ld_wait();
+        }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) dst[c * 32 + j] = (live && !empty_range) ? __uint_as_float(r[j]) : 0.f;
+      }
+      if (!empty_range) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[acc]);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    if (*reinterpret_cast<volatile unsigned int*>(p.status) != 0) {
+      for (int i = 0; i < 64; ++i) __nanosleep(2000);
+    }
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 2 * BN);
+  }
+}
+
+// dw[kw,kh,ci,co] = sum over splits (ascending) of partial[z][(tap, chunk, ci % 64)][co]
+template <typename T>
+__global__ void __launch_bounds__(256) conv_wgrad_reduce_kernel(T* __restrict__ dw, const float* __restrict__ partial,
+                                                                int kW, int kH, int cin, int cout, int flip, int chunks,
+                                                                int rows_pad, int n_pad, int splits) {
+  const int64_t total = (int64_t)kW * kH * cin * cout;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t r = i;
+    const int kw = (int)(r % kW); r /= kW;
+    const int kh = (int)(r % kH); r /= kH;
+    const int ci = (int)(r % cin);
+    const int co = (int)(r / cin);
+    const int tw = flip ? kw : kW - 1 - kw, th = flip ? kh : kH - 1 - kh;
+    const int rg = (th * kW + tw) * chunks + ci / 64;
+    const int64_t row = (int64_t)rg * 64 + ci % 64;
+    float s = 0.f;
+    for (int z = 0; z < splits; ++z) s += partial[((int64_t)z * rows_pad + row) * n_pad + co];
+    dw[i] = from_f32<T>(s);
+  }
+}
+
+
+// ----------------------------------------------------------------------------------------------
+// host side
+// ----------------------------------------------------------------------------------------------
+// One implicit-GEMM problem: out (W, Ho, Cn, N) = taps over in (W, Hi, Ck, N)
+struct ConvGemm {
+  int W, Hi, Ho, Ck, Cn, N, kW, kH, pad_w, pad_h;
+};
+
+static bool bf16_map_4d(CUtensorMap* map, const void* ptr, int64_t d0, int64_t d1, int64_t d2, int64_t d3,
+                        int box0, int box1) {
+  TensorMapEncodeFn enc = tensor_map_encoder();
+  if (!enc) return false;
+  cuuint64_t dims[4] = {(cuuint64_t)d0, (cuuint64_t)d1, (cuuint64_t)d2, (cuuint64_t)d3};
+  cuuint64_t strides[3] = {(cuuint64_t)d0 * 2, (cuuint64_t)d0 * d1 * 2, (cuuint64_t)d0 * d1 * d2 * 2};
+  cuuint32_t box[4] = {(cuuint32_t)box0, (cuuint32_t)box1, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+static bool bf16_map_2d(CUtensorMap* map, const void* ptr, int64_t d0, int64_t d1, int box0, int box1) {
+  TensorMapEncodeFn enc = tensor_map_encoder();
+  if (!enc) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)d0, (cuuint64_t)d1};
+  cuuint64_t strides[1] = {(cuuint64_t)d0 * 2};
+  cuuint32_t box[2] = {(cuuint32_t)box0, (cuuint32_t)box1};
+  cuuint32_t estr[2] = {1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+static int conv_bn(int cn) { return cn <= 64 ? 64 : 128; }
+static int conv_chunks(int ck) { return (ck + 63) / 64; }
+static int conv_fwd_stages(const ConvGemm& c) {
+  const int num_kb = c.kW * c.kH * conv_chunks(c.Ck);
+  const int resident = num_kb * conv_bn(c.Cn) * 128;
+  int st = (200 * 1024 - resident) / (kConvBM * 128);
+  return st > 8 ? 8 : st;
+}
+
+static bool conv_gemm_ok(const ConvGemm& c) {
+  if (c.W % 8 != 0 || c.kW > 8 || c.kW < 1 || c.kH < 1) return false;
+  const int num_kb = c.kW * c.kH * conv_chunks(c.Ck);
+  if (num_kb > kMaxKb) return false;
+  if ((int64_t)(c.kH + c.pad_h) * c.W > 32000) return false;
+  if (conv_fwd_stages(c) < 3) return false;
+  if ((int64_t)c.W * c.Hi >= (1 << 30) || (int64_t)c.W * c.Ho >= (1 << 30)) return false;
+  return tensor_map_encoder() != nullptr;
+}
+
+bool conv_tc_supported(const ConvGeom& g, int32_t dtype) {
+  if (dtype != LB2_BF16 || g.ndim != 2 || g.groups != 1) return false;
+  if (g.stride[0] != 1 || g.stride[1] != 1 || g.dil[0] != 1 || g.dil[1] != 1) return false;
+  if (g.out[0] != g.in[0] || g.out[0] <= 0 || g.out[1] <= 0 || g.batch <= 0 || g.cin <= 0 || g.cout <= 0) return false;
+  if (g.pad_lo[0] > g.k[0] - 1 || g.pad_lo[1] > g.k[1] - 1) return false;  // data gradient needs K-1-pad >= 0
+  const ConvGemm f{g.in[0], g.in[1], g.out[1], g.cin, g.cout, g.batch, g.k[0], g.k[1], g.pad_lo[0], g.pad_lo[1]};
+  const ConvGemm d{g.in[0], g.out[1], g.in[1], g.cout, g.cin, g.batch, g.k[0], g.k[1], g.k[0] - 1 - g.pad_lo[0], g.k[1] - 1 - g.pad_lo[1]};
+  if (!conv_gemm_ok(f) || !conv_gemm_ok(d)) return false;
+  if (g.k[0] * g.k[1] * conv_chunks(g.cin) > 2 * kMaxKb) return false;
+  return true;
+}
+
+static size_t copies_bytes(const ConvGemm& c) { return align_up((size_t)c.kW * c.W * c.Hi * c.Ck * c.N * 2, 1024); }
+static size_t packed_bytes(const ConvGemm& c) {
+  const int bn = conv_bn(c.Cn);
+  const size_t rows = (size_t)((c.Cn + bn - 1) / bn) * bn;
+  return align_up(rows * (size_t)(c.kW * c.kH * conv_chunks(c.Ck) * 64) * 2, 1024);
+}
+
+static unsigned flat_grid_tc(int64_t total) {
+  int64_t gsz = (total + 255) / 256, cap = (int64_t)sm_count() * 16;
+  return (unsigned)(gsz < 1 ? 1 : (gsz > cap ? cap : gsz));
+}
+
+// out = act(implicit GEMM + bias); workspace = shifted copies | packed filter
+static int32_t run_conv_gemm(void* out, void* preact, const void* bias, int32_t act, const void* in, const void* w,
+                             const ConvGemm& c, const PackGeom& pg, uint8_t* ws, cudaStream_t st) {
+  using T = __nv_bfloat16;
+  T* copies = reinterpret_cast<T*>(ws);
+  T* wp = reinterpret_cast<T*>(ws + copies_bytes(c));
+  const int64_t rows = (int64_t)c.Hi * c.Ck * c.N;
+  conv_shift_copies_kernel<T><<<flat_grid_tc(rows * ((c.W + 7) / 8)), 256, 0, st>>>(copies, (const T*)in, c.W, rows, c.kW, c.pad_w);
+  conv_pack_filter_kernel<T><<<flat_grid_tc((int64_t)pg.n_rows * pg.k_total), 256, 0, st>>>(wp, (const T*)w, pg);
+  LB2_CHECK_LAUNCH("conv_tc layout passes");
+
+  const int bn = conv_bn(c.Cn);
+  ConvTcParams p{};
+  p.S_out = c.W * c.Ho;
+  p.n_img = c.N;
+  p.n_out = c.Cn;
+  p.tiles_m = (p.S_out + kConvBM - 1) / kConvBM;
+  p.tiles_n = (c.Cn + bn - 1) / bn;
+  const int chunks = conv_chunks(c.Ck);
+  p.num_kb = c.kW * c.kH * chunks;
+  p.stages = conv_fwd_stages(c);
+  for (int kb = 0; kb < p.num_kb; ++kb) {
+    const int tap = kb / chunks, tw = tap % c.kW, th = tap / c.kW;
+    p.a_shift[kb] = (int16_t)((th - c.pad_h) * c.W);
+    p.a_chan[kb] = (int16_t)((kb % chunks) * 64);
+    p.a_copy[kb] = (int8_t)tw;
+  }
+  // A: bf16, MN-major, two boxes of (64 positions x 64 channels): LBO = 8192, SBO = 1024, 16 channels (2048 B) per MMA
+  p.a_desc_hi = (uint32_t)((1024u >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
+  p.a_desc_lbo = ((8192u >> 4) & 0x3FFFu) << 16;
+  p.a_k_advance = 2048u >> 4;
+  // B: bf16, K-major rows of 128 bytes: SBO = 1024, 32 bytes per MMA
+  p.b_desc_hi = p.a_desc_hi;
+  p.b_desc_lbo = 1u << 16;
+  p.b_k_advance = 32u >> 4;
+  p.idesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | (0u << 16) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(kConvBM >> 4) << 24);
+  p.y = out; p.preact = preact; p.bias = bias; p.act = act;
+  p.status = device_status_word();
+  LB2_REQUIRE(p.status != nullptr, LB2_LAUNCH_FAIL, "conv_tc: device status word unavailable");
+  CUtensorMap mX, mW;
+  if (!bf16_map_4d(&mX, copies, (int64_t)c.W * c.Hi, c.Ck, c.N, c.kW, 64, 64) ||
+      !bf16_map_2d(&mW, wp, pg.k_total, pg.n_rows, 64, bn))
+    return fail(LB2_LAUNCH_FAIL, "conv_tc: cuTensorMapEncodeTiled failed");
+  const int smem = p.num_kb * bn * 128 + p.stages * kConvBM * 128 + 1024 + 256 + 64 * 8;
+  const int tiles_per_n = p.tiles_m * p.n_img;
+  int per_n = sm_count() / p.tiles_n;
+  if (per_n > tiles_per_n) per_n = tiles_per_n;
+  if (per_n < 1) per_n = 1;
+  const int grid = per_n * p.tiles_n;
+  auto launch = [&](auto kernel) -> int32_t {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return fail(LB2_LAUNCH_FAIL, "conv_tc: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    kernel<<<grid, kConvThreads, smem, st>>>(mX, mW, p);
+    LB2_CHECK_LAUNCH("conv_tc_fwd");
+    return LB2_OK;
+  };
+  if (bn == 64) {
+    switch (act) {
+      case LB2_ACT_IDENTITY: return launch(conv_tc_fwd_kernel<64, LB2_ACT_IDENTITY>);
+      case LB2_ACT_RELU: return launch(conv_tc_fwd_kernel<64, LB2_ACT_RELU>);
+      default: return launch(conv_tc_fwd_kernel<64, -1>);
+    }
+  }
+  switch (act) {
+    case LB2_ACT_IDENTITY: return launch(conv_tc_fwd_kernel<128, LB2_ACT_IDENTITY>);
+    case LB2_ACT_RELU: return launch(conv_tc_fwd_kernel<128, LB2_ACT_RELU>);
+    default: return launch(conv_tc_fwd_kernel<128, -1>);
+  }
+}
+
+static ConvGemm fwd_gemm(const ConvGeom& g) {
+  return ConvGemm{g.in[0], g.in[1], g.out[1], g.cin, g.cout, g.batch, g.k[0], g.k[1], g.pad_lo[0], g.pad_lo[1]};
+}
+static ConvGemm dgrad_gemm(const ConvGeom& g) {
+  return ConvGemm{g.in[0], g.out[1], g.in[1], g.cout, g.cin, g.batch, g.k[0], g.k[1], g.k[0] - 1 - g.pad_lo[0], g.k[1] - 1 - g.pad_lo[1]};
+}
+static PackGeom pack_geom(const ConvGeom& g, const ConvGemm& c, int transpose) {
+  PackGeom pg{};
+  pg.kW = g.k[0]; pg.kH = g.k[1]; pg.cin = g.cin; pg.cout = g.cout; pg.flip = g.flip; pg.transpose = transpose;
+  pg.chunks = conv_chunks(c.Ck);
+  const int bn = conv_bn(c.Cn);
+  pg.n_rows = ((c.Cn + bn - 1) / bn) * bn;
+  pg.k_total = c.kW * c.kH * pg.chunks * 64;
+  return pg;
+}
+
+size_t conv_tc_fwd_workspace_bytes(const ConvGeom& g) {
+  const ConvGemm c = fwd_gemm(g);
+  return copies_bytes(c) + packed_bytes(c);
+}
+
+int32_t conv_tc_fwd(void* y, void* preact, const void* x, const void* w, const void* bias, const ConvGeom& g,
+                    int32_t act, void* ws, cudaStream_t st) {
+  const ConvGemm c = fwd_gemm(g);
+  return run_conv_gemm(y, preact, bias, act, x, w, c, pack_geom(g, c, 0), static_cast<uint8_t*>(ws), st);
+}
+
+// ---- filter gradient plan
+struct WgPlan {
+  int bn, chunks, n_rg, m_tiles, tiles_n, s_blocks, kb_total, splits, kb_per_split, stages, n_pad;
+};
+static WgPlan wg_plan(const ConvGeom& g) {
+  WgPlan w{};
+  w.bn = conv_bn(g.cout);
+  w.chunks = conv_chunks(g.cin);
+  w.n_rg = g.k[0] * g.k[1] * w.chunks;
+  w.m_tiles = (w.n_rg + 1) / 2;
+  w.tiles_n = (g.cout + w.bn - 1) / w.bn;
+  w.n_pad = w.tiles_n * w.bn;
+  const int S_out = g.out[0] * g.out[1];
+  w.s_blocks = (S_out + 63) / 64;
+  w.kb_total = g.batch * w.s_blocks;
+  int splits = sm_count() / (w.m_tiles * w.tiles_n);
+  if (splits < 1) splits = 1;
+  if (splits > w.kb_total) splits = w.kb_total;
+  w.kb_per_split = (w.kb_total + splits - 1) / splits;
+  w.splits = (w.kb_total + w.kb_per_split - 1) / w.kb_per_split;
+  w.stages = (200 * 1024) / (kConvBM * 128 + w.bn * 128);
+  if (w.stages > 8) w.stages = 8;
+  return w;
+}
+static size_t wg_partial_bytes(const WgPlan& w) {
+  return align_up((size_t)w.splits * w.m_tiles * 128 * w.n_pad * sizeof(float), 1024);
+}
+
+size_t conv_tc_bwd_workspace_bytes(const ConvGeom& g) {
+  const ConvGemm d = dgrad_gemm(g), f = fwd_gemm(g);
+  const size_t dgrad = copies_bytes(d) + packed_bytes(d);
+  const size_t wgrad = copies_bytes(f) + wg_partial_bytes(wg_plan(g));
+  return dgrad > wgrad ? dgrad : wgrad;   // the two gradients run one after the other in the same region
+}
+
+int32_t conv_tc_dgrad(void* dx, const void* gy, const void* w, const ConvGeom& g, void* ws, cudaStream_t st) {
+  const ConvGemm c = dgrad_gemm(g);
+  return run_conv_gemm(dx, nullptr, nullptr, LB2_ACT_IDENTITY, gy, w, c, pack_geom(g, c, 1), static_cast<uint8_t*>(ws), st);
+}
+
+int32_t conv_tc_wgrad(void* dw, const void* x, const void* gy, const ConvGeom& g, void* ws_, cudaStream_t st) {
+  using T = __nv_bfloat16;
+  uint8_t* ws = static_cast<uint8_t*>(ws_);
+  const ConvGemm f = fwd_gemm(g);
+  const WgPlan w = wg_plan(g);
+  T* copies = reinterpret_cast<T*>(ws);
+  float* partial = reinterpret_cast<float*>(ws + copies_bytes(f));
+  const int64_t rows = (int64_t)f.Hi * f.Ck * f.N;
+  conv_shift_copies_kernel<T><<<flat_grid_tc(rows * ((f.W + 7) / 8)), 256, 0, st>>>(copies, (const T*)x, f.W, rows, f.kW, f.pad_w);
+  LB2_CHECK_LAUNCH("conv_tc shifted copies");
+  ConvWgParams p{};
+  p.S_out = g.out[0] * g.out[1];
+  p.n_img = g.batch; p.n_out = g.cout;
+  p.s_blocks = w.s_blocks; p.m_tiles = w.m_tiles; p.tiles_n = w.tiles_n; p.splits = w.splits;
+  p.kb_total = w.kb_total; p.kb_per_split = w.kb_per_split; p.n_rg = w.n_rg; p.stages = w.stages;
+  p.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(w.bn >> 3) << 17) | ((uint32_t)(kConvBM >> 4) << 24);
+  p.desc_hi = (uint32_t)((1024u >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
+  p.desc_lbo = 1u << 16;
+  p.k_advance = 32u >> 4;
+  p.partial = partial; p.n_pad = w.n_pad;
+  p.status = device_status_word();
+  LB2_REQUIRE(p.status != nullptr, LB2_LAUNCH_FAIL, "conv_tc: device status word unavailable");
+  for (int rg = 0; rg < w.n_rg; ++rg) {
+    const int tap = rg / w.chunks, tw = tap % f.kW, th = tap / f.kW;
+    p.rg_shift[rg] = (int16_t)((th - f.pad_h) * f.W);
+    p.rg_chan[rg] = (int16_t)((rg % w.chunks) * 64);
+    p.rg_copy[rg] = (int8_t)tw;
+  }
+  CUtensorMap mX, mG;
+  if (!bf16_map_4d(&mX, copies, (int64_t)f.W * f.Hi, f.Ck, f.N, f.kW, 64, 64) ||
+      !bf16_map_4d(&mG, gy, (int64_t)p.S_out, g.cout, g.batch, 1, 64, w.bn))
+    return fail(LB2_LAUNCH_FAIL, "conv_tc: cuTensorMapEncodeTiled failed");
+  const int smem = w.stages * (kConvBM * 128 + w.bn * 128) + 1024 + 256 + 64 * 8;
+  const int items = w.m_tiles * w.tiles_n * w.splits;
+  const int grid = items < sm_count() ? items : sm_count();
+  auto launch = [&](auto kernel) -> int32_t {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return fail(LB2_LAUNCH_FAIL, "conv_tc: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    kernel<<<grid, kConvThreads, smem, st>>>(mX, mG, p);
+    LB2_CHECK_LAUNCH("conv_tc_wgrad");
+    return LB2_OK;
+  };
+  int32_t rc = w.bn == 64 ? launch(conv_tc_wgrad_kernel<64>) : launch(conv_tc_wgrad_kernel<128>);
+  if (rc != LB2_OK) return rc;
+  const int64_t nw = (int64_t)g.k[0] * g.k[1] * g.cin * g.cout;
+  conv_wgrad_reduce_kernel<T><<<flat_grid_tc(nw), 256, 0, st>>>((T*)dw, partial, g.k[0], g.k[1], g.cin, g.cout, g.flip, w.chunks,
+                                                              w.m_tiles * 128, w.n_pad, w.splits);
+  LB2_CHECK_LAUNCH("conv_wgrad_reduce");
+  return LB2_OK;
+}
+
+}  // namespace lb2

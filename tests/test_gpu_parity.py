@@ -220,6 +220,43 @@ def test_fused_conv_fwd_bwd(dt, act, case):
     check(db, db_ref, dt, "db")
 
 
+TC_CONV_CASES = [
+    # spatial, k, cin, cout, pad, flip  — shapes the tensor-core implicit-GEMM path takes (bf16, stride 1, W % 8 == 0)
+    ((16, 8), (3, 3), 16, 16, 1, False),
+    ((56, 12), (3, 3), 64, 64, 1, False),
+    ((24, 9), (3, 3), 80, 72, (1, 1, 0, 2), True),
+    ((32, 10), (1, 1), 64, 128, 0, False),
+    ((40, 7), (5, 3), 32, 40, (2, 2, 1, 1), False),
+    ((16, 6), (3, 3), 64, 96, 1, False),
+    ((8, 40), (3, 5), 130, 48, (1, 1, 2, 2), False),
+]
+
+
+@pytest.mark.parametrize("force_simt", [False, True])
+@pytest.mark.parametrize("act", ["identity", "relu", "gelu"])
+@pytest.mark.parametrize("case", TC_CONV_CASES)
+def test_fused_conv_tensor_core_path_bf16(case, act, force_simt):
+    sp, k, cin, cout, pad, flip = case
+    dt = "bf16"
+    rng = np.random.default_rng(23)
+    x = prep(rng.standard_normal(sp + (cin, 3)), dt)
+    w = prep(O.kaiming_normal(rng, k + (cin, cout)), dt)
+    b = prep(rng.uniform(-0.1, 0.1, cout), dt)
+    ocd = O.ConvDims.make(2, 1, pad, 1, 1, flip)
+    lcd = L.ConvDims.make(2, 1, pad, 1, 1, flip)
+    flags = L._cabi.FLAG_FORCE_SIMT if force_simt else 0
+    y_ref, pb_ref = O.fused_conv_rrule(act, w, x, b, ocd)
+    y, pb = L.rrule_fused_conv(act, dev(w, dt), dev(x, dt), dev(b, dt), lcd, flags=flags)
+    check(y, y_ref, dt, "y")
+    delta = prep(rng.standard_normal(y_ref.shape), dt)
+    dw_ref, dx_ref, db_ref = pb_ref(delta)
+    dw, dx, db = pb(dev(delta, dt))
+    check(dw, dw_ref, dt, "dw")
+    check(dx, dx_ref, dt, "dx")
+    check(db, db_ref, dt, "db")
+    assert L._cabi.load().lb2_poll_device_status(None) == 0
+
+
 def test_conv_known_answers():
     # test/core_layers/conv_tests.jl:53-69 and :145-158
     x = L.from_numpy(np.ones((28, 28, 1, 1), np.float32))
