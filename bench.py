@@ -204,7 +204,7 @@ def run_gpu_arm(args):
         y, pullback = L.rrule_fused_dense(ACT, W, x, b)
         dW, dx, db = pullback(dy)
         if dist is not None:  # DistributedOptimizer: allreduce(avg) of every parameter-gradient leaf
-            dist.all_reduce(dW, op=dist.ReduceOp.AVG)
+            dist.all_reduce(dW.T, op=dist.ReduceOp.AVG)  # dW is column-major: .T is the contiguous view of the same memory
             dist.all_reduce(db, op=dist.ReduceOp.AVG)
         return y, dW, dx, db
 
@@ -235,7 +235,7 @@ def run_gpu_arm(args):
         fwd_ev[i][1].record()
         dW, dx, db = pullback(dy)
         if dist is not None:
-            dist.all_reduce(dW, op=dist.ReduceOp.AVG)
+            dist.all_reduce(dW.T, op=dist.ReduceOp.AVG)  # dW is column-major: .T is the contiguous view of the same memory
             dist.all_reduce(db, op=dist.ReduceOp.AVG)
     e1.record()
     barrier()
@@ -269,7 +269,7 @@ def run_gpu_arm(args):
         y, pullback = L.rrule_fused_dense(ACT, W, dxbuf.T, b)
         dW, dx, db = pullback(dybuf.T)
         if dist is not None:
-            dist.all_reduce(dW, op=dist.ReduceOp.AVG)
+            dist.all_reduce(dW.T, op=dist.ReduceOp.AVG)  # dW is column-major: .T is the contiguous view of the same memory
             dist.all_reduce(db, op=dist.ReduceOp.AVG)
         hy.copy_(y.T, non_blocking=True)
         hdW.copy_(dW.T, non_blocking=True)

@@ -25,7 +25,7 @@
 
 namespace lb2 {
 
-constexpr int kConvThreads = 256;
+constexpr int kConvThreads = 384;   // warps 0-2: TMA / MMA / TMEM, warps 4-11: epilogue (two per TMEM lane quarter)
 constexpr int kConvBM = 128;
 constexpr int kMaxKb = 96;
 
@@ -58,6 +58,58 @@ __global__ void __launch_bounds__(256) conv_shift_copies_kernel(T* __restrict__ 
         if (w0 + j < W) dst[j] = win[j + t];
     }
   }
+}
+
+// 2-byte elements, compile-time kernel width and padding: every thread moves 16-byte vectors. The 8
+// outputs of copy t start D = t - PAD elements away from the thread's aligned group, so they are
+// cut out of the three aligned vectors around it with static funnel shifts.
+template <int KW, int PAD>
+__global__ void __launch_bounds__(256) conv_shift_copies_vec_kernel(uint16_t* __restrict__ out, const uint16_t* __restrict__ in,
+                                                                    int W, int64_t rows) {
+  const int groups = W / 8;
+  const int64_t total = rows * groups;
+  const int64_t copy_stride = rows * W;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = i / groups;
+    const int gq = (int)(i % groups);
+    const uint4* src = reinterpret_cast<const uint4*>(in + row * W);
+    const uint4 z = make_uint4(0, 0, 0, 0);
+    const uint4 vm = gq > 0 ? __ldg(src + gq - 1) : z;
+    const uint4 v0 = __ldg(src + gq);
+    const uint4 vp = gq + 1 < groups ? __ldg(src + gq + 1) : z;
+    const uint32_t win[12] = {vm.x, vm.y, vm.z, vm.w, v0.x, v0.y, v0.z, v0.w, vp.x, vp.y, vp.z, vp.w};  // 24 elements, ours at 8..15
+#pragma unroll
+    for (int t = 0; t < KW; ++t) {
+      constexpr int BASE = 8 - PAD;         // element index of output 0 of copy 0 inside the window
+      const int e = BASE + t;               // compile-time after unrolling
+      uint32_t o[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int q = (e >> 1) + k;
+        o[k] = (e & 1) ? __funnelshift_r(win[q], win[q + 1], 16) : win[q];
+      }
+      __stcs(reinterpret_cast<uint4*>(out + (int64_t)t * copy_stride + row * W) + gq, make_uint4(o[0], o[1], o[2], o[3]));
+    }
+  }
+}
+
+static bool launch_shift_copies_vec(void* out, const void* in, int W, int64_t rows, int kW, int pad_w, unsigned grid,
+                                    cudaStream_t st) {
+  uint16_t* o = static_cast<uint16_t*>(out);
+  const uint16_t* i = static_cast<const uint16_t*>(in);
+#define LB2_SHIFT_CASE(KW_, PAD_)                                                         \
+  if (kW == KW_ && pad_w == PAD_) {                                                       \
+    conv_shift_copies_vec_kernel<KW_, PAD_><<<grid, 256, 0, st>>>(o, i, W, rows);         \
+    return true;                                                                          \
+  }
+  LB2_SHIFT_CASE(1, 0)
+  LB2_SHIFT_CASE(3, 1)
+  LB2_SHIFT_CASE(3, 0)
+  LB2_SHIFT_CASE(3, 2)
+  LB2_SHIFT_CASE(5, 2)
+  LB2_SHIFT_CASE(7, 3)
+#undef LB2_SHIFT_CASE
+  return false;
 }
 
 // Packed filter for the forward / data-gradient GEMM: Wp[nrow][kb*64 + j], nrow = GEMM output channel,
@@ -143,9 +195,18 @@ conv_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 4); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 8); }
     mbar_init(b_full, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __shared__ float sbias[BN];
+  {
+    const int nt_ = blockIdx.x % p.tiles_n;
+    const __nv_bfloat16* bias = reinterpret_cast<const __nv_bfloat16*>(p.bias);
+    for (int c = threadIdx.x; c < BN; c += blockDim.x) {
+      const int co = nt_ * BN + c;
+      sbias[c] = (bias != nullptr && co < p.n_out) ? __bfloat162float(bias[co]) : 0.f;
+    }
   }
   if (warp == 2) {
     tmem_alloc(tmem_slot, 2 * BN);
@@ -213,11 +274,16 @@ conv_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
       }
     }
   } else if (warp >= 4) {
-    const int q = warp & 3;
+    // Two warps share each TMEM lane quarter and split the tile's columns. A thread owns one output
+    // position s and walks its channels with a pointer stride of S_out (channel planes of y).
+    const int q = warp & 3, half = (warp - 4) >> 2;
+    constexpr int COLS = BN / 2;
     uint32_t acc = 0, acc_phase = 0;
     __nv_bfloat16* Y = reinterpret_cast<__nv_bfloat16*>(p.y);
     __nv_bfloat16* P = reinterpret_cast<__nv_bfloat16*>(p.preact);
-    const __nv_bfloat16* bias = reinterpret_cast<const __nv_bfloat16*>(p.bias);
+    const int64_t cs = p.S_out;
+    const int col0 = n0 + half * COLS;
+    const int lim = min(COLS, p.n_out - col0);   // live columns of this warp (may be <= 0)
     bool ok = true;
     for (int t = first; t < tiles_per_n && ok; t += step) {
       const int m0 = (t % p.tiles_m) * kConvBM, img = t / p.tiles_m;
@@ -225,24 +291,27 @@ conv_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
       tc_fence_after();
       const int s = m0 + q * 32 + lane;
       const bool s_ok = s < p.S_out;
+      const int64_t base = (int64_t)s + cs * ((int64_t)p.n_out * img + col0);
+      __nv_bfloat16* yp = Y + base;
+      __nv_bfloat16* pp = P != nullptr ? P + base : nullptr;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = 0; c < COLS / 32; ++c) {
         uint32_t r[32];
-        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c * 32, r);
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + half * COLS + c * 32, r);
         tmem_ld_wait();
         if (s_ok) {
+          const float* sb = sbias + half * COLS + c * 32;
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
-            const int co = n0 + c * 32 + j;
-            if (co < p.n_out) {
-              float v = __uint_as_float(r[j]);
-              if (bias != nullptr) v += __bfloat162float(bias[co]);
-              const int64_t off = (int64_t)s + (int64_t)p.S_out * (co + (int64_t)p.n_out * img);
-              if (P != nullptr) P[off] = __float2bfloat16_rn(v);
-              Y[off] = __float2bfloat16_rn(act_apply_any<ACT, true>(p.act, v));
+            if (c * 32 + j < lim) {
+              const float v = __uint_as_float(r[j]) + sb[j];
+              if (pp != nullptr) pp[j * cs] = __float2bfloat16_rn(v);
+              yp[j * cs] = __float2bfloat16_rn(act_apply_any<ACT, true>(p.act, v));
             }
           }
         }
+        yp += 32 * cs;
+        if (pp != nullptr) pp += 32 * cs;
       }
       tc_fence_before();
       __syncwarp();
@@ -307,7 +376,7 @@ conv_tc_wgrad_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 4); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 8); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 2) {
@@ -389,8 +458,9 @@ conv_tc_wgrad_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
       // A row group that was not loaded (odd tail) leaves stale shared memory under the MMA: its rows
       // are never read by the reduction, but they are written as zeros to keep the buffer defined.
       const bool live = (row / 64) < p.n_rg;
+      const int half = (warp - 4) >> 2;   // two warps per lane quarter split the columns
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
         uint32_t r[32];
         if (!empty_range) {
           tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c * 32, r);
@@ -523,7 +593,8 @@ static int32_t run_conv_gemm(void* out, void* preact, const void* bias, int32_t 
   T* copies = reinterpret_cast<T*>(ws);
   T* wp = reinterpret_cast<T*>(ws + copies_bytes(c));
   const int64_t rows = (int64_t)c.Hi * c.Ck * c.N;
-  conv_shift_copies_kernel<T><<<flat_grid_tc(rows * ((c.W + 7) / 8)), 256, 0, st>>>(copies, (const T*)in, c.W, rows, c.kW, c.pad_w);
+  if (!launch_shift_copies_vec(copies, in, c.W, rows, c.kW, c.pad_w, flat_grid_tc(rows * (c.W / 8)), st))
+    conv_shift_copies_kernel<T><<<flat_grid_tc(rows * ((c.W + 7) / 8)), 256, 0, st>>>(copies, (const T*)in, c.W, rows, c.kW, c.pad_w);
   conv_pack_filter_kernel<T><<<flat_grid_tc((int64_t)pg.n_rows * pg.k_total), 256, 0, st>>>(wp, (const T*)w, pg);
   LB2_CHECK_LAUNCH("conv_tc layout passes");
 
@@ -661,7 +732,8 @@ int32_t conv_tc_wgrad(void* dw, const void* x, const void* gy, const ConvGeom& g
   T* copies = reinterpret_cast<T*>(ws);
   float* partial = reinterpret_cast<float*>(ws + copies_bytes(f));
   const int64_t rows = (int64_t)f.Hi * f.Ck * f.N;
-  conv_shift_copies_kernel<T><<<flat_grid_tc(rows * ((f.W + 7) / 8)), 256, 0, st>>>(copies, (const T*)x, f.W, rows, f.kW, f.pad_w);
+  if (!launch_shift_copies_vec(copies, x, f.W, rows, f.kW, f.pad_w, flat_grid_tc(rows * (f.W / 8)), st))
+    conv_shift_copies_kernel<T><<<flat_grid_tc(rows * ((f.W + 7) / 8)), 256, 0, st>>>(copies, (const T*)x, f.W, rows, f.kW, f.pad_w);
   LB2_CHECK_LAUNCH("conv_tc shifted copies");
   ConvWgParams p{};
   p.S_out = g.out[0] * g.out[1];

@@ -70,8 +70,10 @@ template <int BN, bool TF32, bool SPLIT3> struct TcCfg {
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
+constexpr int kThreadsSingle = 384;  // warps 0-2: TMA / MMA / TMEM, warps 4-11: epilogue (two per TMEM lane quarter)
+
 template <int BN, bool TF32, bool SPLIT3, int ACT, typename OutT>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreadsSingle, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmA_lo, const __grid_constant__ CUtensorMap tmB_lo,
                const __grid_constant__ TcParams p) {
@@ -94,7 +96,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 4); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 8); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 2) {
@@ -176,39 +178,48 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
   } else if (warp >= 4) {
     // ---------------- epilogue ----------------
-    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    // Two warps share each TMEM lane quarter and split the tile's columns. A thread owns output row m
+    // (the contiguous index of D) and walks its columns with a pointer stride of ldd.
+    const int q = warp & 3, half = (warp - 4) >> 2;
+    constexpr int COLS = BN / 2;
     uint32_t acc = 0, acc_phase = 0;
     OutT* D = reinterpret_cast<OutT*>(p.D);
     OutT* P = reinterpret_cast<OutT*>(p.preact);
     const OutT* bias = reinterpret_cast<const OutT*>(p.bias);
+    const int64_t ldd = p.ldd;
+    const bool accumulate = p.accumulate != 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-      const int m0 = (tile % p.tiles_m) * kBM, n0 = (tile / p.tiles_m) * BN;
+      const int m0 = (tile % p.tiles_m) * kBM, n0 = (tile / p.tiles_m) * BN + half * COLS;
       if (!mbar_wait(&acc_full[acc], acc_phase, p.status, 0x8u)) { ok = false; break; }
       tc_fence_after();
       const int64_t m = (int64_t)m0 + q * 32 + lane;
       const bool m_ok = m < p.Mm;
       float bv = 0.f;
       if (bias != nullptr && m_ok) bv = to_f32(bias[m]);
+      const int64_t rem = p.Nn - n0;
+      const int lim = rem < COLS ? (int)rem : COLS;   // live columns (may be <= 0)
+      OutT* dp = D + (int64_t)n0 * ldd + m;
+      OutT* pp = P != nullptr ? P + (int64_t)n0 * ldd + m : nullptr;
 #pragma unroll 1
-      for (int c = 0; c < ((p.debug & 1u) ? 0 : BN / 32); ++c) {
+      for (int c = 0; c < ((p.debug & 1u) ? 0 : COLS / 32); ++c) {
         uint32_t r[32];
-        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c * 32, r);
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + half * COLS + c * 32, r);
         tmem_ld_wait();
         if (m_ok) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
-            const int64_t n = (int64_t)n0 + c * 32 + j;
-            if (n < p.Nn) {
+            if (c * 32 + j < lim) {
               float v = __uint_as_float(r[j]) + bv;
-              const int64_t off = n * p.ldd + m;
-              if (P != nullptr) P[off] = from_f32<OutT>(v);
+              if (pp != nullptr) pp[j * ldd] = from_f32<OutT>(v);
               v = act_apply_any<ACT, FAST>(p.act, v);
-              if (p.accumulate) v += to_f32(D[off]);
-              D[off] = from_f32<OutT>(v);
+              if (accumulate) v += to_f32(dp[j * ldd]);
+              dp[j * ldd] = from_f32<OutT>(v);
             }
           }
         }
+        dp += 32 * ldd;
+        if (pp != nullptr) pp += 32 * ldd;
       }
       tc_fence_before();
       __syncwarp();
@@ -728,7 +739,7 @@ static int32_t tc_launch_cfg(const CUtensorMap& mA, const CUtensorMap& mB, const
   auto launch = [&](auto kernel) -> int32_t {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return fail(LB2_LAUNCH_FAIL, "gemm_tc: cannot reserve %d bytes of shared memory: %s", Cfg::SMEM_BYTES, cudaGetErrorString(e));
-    kernel<<<grid, kThreads, Cfg::SMEM_BYTES, st>>>(mA, mB, mAl, mBl, p);
+    kernel<<<grid, kThreadsSingle, Cfg::SMEM_BYTES, st>>>(mA, mB, mAl, mBl, p);
     LB2_CHECK_LAUNCH("gemm_tc");
     return LB2_OK;
   };

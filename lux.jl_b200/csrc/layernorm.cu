@@ -12,6 +12,7 @@
 //
 // Algorithmic bytes per element: forward 2*sizeof(T), backward 3*sizeof(T).
 #include "norm_common.cuh"
+#include "tc_ptx.cuh"
 
 namespace lb2 {
 
@@ -77,6 +78,237 @@ __global__ void __launch_bounds__(BT) ln_fwd_cached_kernel(T* __restrict__ y, fl
           o.set(j, act_apply_any<ACT, FAST>(act_rt, fmaf(xv[k].get(j), gp, bp)));
         }
         store16_stream(yr + i, o);
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Ring-buffered variants (one CTA per row, 256 compute threads + one copy-producer warp).
+// The phases of a row (load, two reductions, store) leave the memory system idle while a CTA
+// reduces, and with rows held in registers only a couple of CTAs fit per SM. Here a producer
+// warp streams whole rows into a shared-memory ring with 1-D bulk copies (cp.async.bulk +
+// mbarrier transaction counts), several rows ahead of the compute warps, so loads stay in
+// flight through every phase. Compute warps copy their vectors from the ring into registers and
+// release the stage at once. Waits are time-bounded; an expired wait raises an abort flag that
+// all compute threads observe at the same point (after a barrier), so nobody is left behind.
+// ---------------------------------------------------------------------------------------------
+constexpr int kRingCompute = 256;
+constexpr int kRingThreads = kRingCompute + 32;
+
+template <typename T, int ACT, bool AFFINE, int NV>
+__global__ void __launch_bounds__(kRingThreads)
+ln_fwd_ring_kernel(T* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ inv_out, const T* __restrict__ x,
+                   const T* __restrict__ gamma, const T* __restrict__ beta, int64_t D, int64_t R, float eps, int act_rt,
+                   int stages, unsigned int* status) {
+  constexpr bool FAST = sizeof(T) == 2;
+  constexpr int V = Vec16<T>::N;
+  extern __shared__ __align__(1024) uint8_t ring_smem[];
+  uint64_t* full = reinterpret_cast<uint64_t*>(ring_smem);
+  uint64_t* empty = full + stages;
+  float* red = reinterpret_cast<float*>(ring_smem + 256);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(ring_smem + 768);
+  uint8_t* data = ring_smem + 1024;
+  const uint32_t row_bytes = (uint32_t)(D * sizeof(T));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, t = threadIdx.x;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], kRingCompute / 32); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  const int64_t nrows = blockIdx.x < R ? (R - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  if (warp == kRingCompute / 32) {
+    if (lane == 0) {
+      for (int64_t i = 0; i < nrows; ++i) {
+        const int st = (int)(i % stages);
+        const uint32_t ph = (uint32_t)((i / stages) & 1);
+        if (!mbar_wait(&empty[st], ph ^ 1u, status, 0x200000u)) break;
+        const int64_t row = blockIdx.x + i * gridDim.x;
+        mbar_expect_tx(&full[st], row_bytes);
+        bulk_load_1d(smem_u32(data + (size_t)st * row_bytes), x + row * D, row_bytes, &full[st]);
+      }
+    }
+    return;
+  }
+  Vec16<T> gv[NV], bv[NV];
+  if constexpr (AFFINE) {
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int64_t i = ((int64_t)k * kRingCompute + t) * V;
+      if (i < D) { gv[k] = load16(gamma + i); bv[k] = load16(beta + i); }
+    }
+  }
+  const float invD = 1.f / (float)D;
+  for (int64_t it = 0; it < nrows; ++it) {
+    const int st = (int)(it % stages);
+    const uint32_t ph = (uint32_t)((it / stages) & 1);
+    const int64_t row = blockIdx.x + it * gridDim.x;
+    if (!mbar_wait(&full[st], ph, status, 0x400000u)) *abort_flag = 1;
+    const T* sx = reinterpret_cast<const T*>(data + (size_t)st * row_bytes);
+    Vec16<T> xv[NV];
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int64_t i = ((int64_t)k * kRingCompute + t) * V;
+      if (i < D) {
+        xv[k] = load16(sx + i);
+#pragma unroll
+        for (int j = 0; j < V; ++j) s += xv[k].get(j);
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty[st]);
+    const float mean = group_sum(s, red, kRingCompute) * invD;
+    if (*abort_flag) break;
+    float q = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int64_t i = ((int64_t)k * kRingCompute + t) * V;
+      if (i < D) {
+#pragma unroll
+        for (int j = 0; j < V; ++j) { float d = xv[k].get(j) - mean; q += d * d; }
+      }
+    }
+    const float var = group_sum(q, red, kRingCompute) * invD;
+    const float inv = 1.f / sqrtf(var + eps);
+    if (t == 0) { mean_out[row] = mean; inv_out[row] = inv; }
+    T* yr = y + row * D;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int64_t i = ((int64_t)k * kRingCompute + t) * V;
+      if (i < D) {
+        Vec16<T> o;
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          float gp = inv, bp = -mean * inv;
+          if constexpr (AFFINE) { gp = gv[k].get(j) * inv; bp = bv[k].get(j) - mean * gp; }
+          o.set(j, act_apply_any<ACT, FAST>(act_rt, fmaf(xv[k].get(j), gp, bp)));
+        }
+        store16_stream(yr + i, o);
+      }
+    }
+  }
+}
+
+template <typename T, int ACT, bool AFFINE, int NV>
+__global__ void __launch_bounds__(kRingThreads)
+ln_bwd_ring_kernel(T* __restrict__ dx, float* __restrict__ partial, const T* __restrict__ dy, const T* __restrict__ x,
+                   const T* __restrict__ gamma, const T* __restrict__ beta, const float* __restrict__ mean_in,
+                   const float* __restrict__ inv_in, int64_t D, int64_t R, int act_rt, int stages, unsigned int* status) {
+  constexpr bool FAST = sizeof(T) == 2;
+  constexpr int V = Vec16<T>::N;
+  extern __shared__ __align__(1024) uint8_t ring_smem[];
+  uint64_t* full = reinterpret_cast<uint64_t*>(ring_smem);
+  uint64_t* empty = full + stages;
+  float* red = reinterpret_cast<float*>(ring_smem + 256);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(ring_smem + 768);
+  uint8_t* data = ring_smem + 1024;
+  const uint32_t row_bytes = (uint32_t)(D * sizeof(T));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, t = threadIdx.x;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], kRingCompute / 32); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  const int64_t nrows = blockIdx.x < R ? (R - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  if (warp == kRingCompute / 32) {
+    if (lane == 0) {
+      for (int64_t i = 0; i < nrows; ++i) {
+        const int st = (int)(i % stages);
+        const uint32_t ph = (uint32_t)((i / stages) & 1);
+        if (!mbar_wait(&empty[st], ph ^ 1u, status, 0x800000u)) break;
+        const int64_t row = blockIdx.x + i * gridDim.x;
+        mbar_expect_tx(&full[st], 2 * row_bytes);
+        bulk_load_1d(smem_u32(data + (size_t)st * 2 * row_bytes), x + row * D, row_bytes, &full[st]);
+        bulk_load_1d(smem_u32(data + (size_t)st * 2 * row_bytes + row_bytes), dy + row * D, row_bytes, &full[st]);
+      }
+    }
+    return;
+  }
+  Vec16<T> gv[NV], bv[NV];
+  float adg[NV][V], adb[NV][V];
+  if constexpr (AFFINE) {
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int64_t i = ((int64_t)k * kRingCompute + t) * V;
+      if (i < D) { gv[k] = load16(gamma + i); bv[k] = load16(beta + i); }
+#pragma unroll
+      for (int j = 0; j < V; ++j) { adg[k][j] = 0.f; adb[k][j] = 0.f; }
+    }
+  }
+  const float invD = 1.f / (float)D;
+  for (int64_t it = 0; it < nrows; ++it) {
+    const int st = (int)(it % stages);
+    const uint32_t ph = (uint32_t)((it / stages) & 1);
+    const int64_t row = blockIdx.x + it * gridDim.x;
+    const float mean = mean_in[row], inv = inv_in[row];
+    if (!mbar_wait(&full[st], ph, status, 0x1000000u)) *abort_flag = 1;
+    const T* sx = reinterpret_cast<const T*>(data + (size_t)st * 2 * row_bytes);
+    const T* sdy = reinterpret_cast<const T*>(data + (size_t)st * 2 * row_bytes + row_bytes);
+    Vec16<T> xv[NV], gy[NV];
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int64_t i = ((int64_t)k * kRingCompute + t) * V;
+      if (i < D) { xv[k] = load16(sx + i); gy[k] = load16(sdy + i); }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty[st]);
+    float gf[NV][V];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int64_t i = ((int64_t)k * kRingCompute + t) * V;
+      if (i < D) {
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          const float xh = (xv[k].get(j) - mean) * inv;
+          float d = gy[k].get(j);
+          if constexpr (ACT != LB2_ACT_IDENTITY) {
+            float gp = inv, bp = -mean * inv;
+            if constexpr (AFFINE) { gp = gv[k].get(j) * inv; bp = bv[k].get(j) - mean * gp; }
+            d *= act_grad_pre_any<ACT, FAST>(act_rt, fmaf(xv[k].get(j), gp, bp));
+          }
+          float g = d;
+          if constexpr (AFFINE) {
+            adg[k][j] += d * xh;
+            adb[k][j] += d;
+            g = d * gv[k].get(j);
+          }
+          gf[k][j] = g;
+          s1 += g;
+          s2 += g * xh;
+        }
+      }
+    }
+    const float2 m12 = group_sum2(s1, s2, red, kRingCompute);
+    if (*abort_flag) break;
+    const float m1 = m12.x * invD, m2 = m12.y * invD;
+    T* dxr = dx + row * D;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int64_t i = ((int64_t)k * kRingCompute + t) * V;
+      if (i < D) {
+        Vec16<T> o;
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          const float xh = (xv[k].get(j) - mean) * inv;
+          o.set(j, inv * (gf[k][j] - m1 - xh * m2));
+        }
+        store16_stream(dxr + i, o);
+      }
+    }
+  }
+  if constexpr (AFFINE) {
+    float* pg = partial + (int64_t)blockIdx.x * 2 * D;
+    float* pb = pg + D;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int64_t i = ((int64_t)k * kRingCompute + t) * V;
+      if (i < D) {
+#pragma unroll
+        for (int j = 0; j < V; ++j) { pg[i + j] = adg[k][j]; pb[i + j] = adb[k][j]; }
       }
     }
   }
@@ -273,24 +505,37 @@ __global__ void __launch_bounds__(256) ln_bwd_generic_kernel(T* __restrict__ dx,
   }
 }
 
-// out[i] = sum_k partial[k][which][i]   (k in launch order)
+// out[i] = sum_k partial[k][which][i]. block (32 features, 8 slices): slice y adds parts y, y+8, ... in
+// ascending order, then the eight slice sums are added in slice order: a fixed order, deterministic.
 template <typename T>
-__global__ void ln_finish_kernel(T* __restrict__ dgamma, T* __restrict__ dbeta, const float* __restrict__ partial,
-                                 int64_t D, int parts) {
-  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= D) return;
-  float sg = 0.f, sb = 0.f;
-  for (int k = 0; k < parts; ++k) {
-    sg += partial[((int64_t)k * 2) * D + i];
-    sb += partial[((int64_t)k * 2 + 1) * D + i];
+__global__ void __launch_bounds__(256) ln_finish_kernel(T* __restrict__ dgamma, T* __restrict__ dbeta,
+                                                        const float* __restrict__ partial, int64_t D, int parts) {
+  __shared__ float sg[8][33], sb[8][33];
+  const int64_t i = (int64_t)blockIdx.x * 32 + threadIdx.x;
+  float ag = 0.f, ab = 0.f;
+  if (i < D) {
+    for (int k = threadIdx.y; k < parts; k += 8) {
+      ag += partial[((int64_t)k * 2) * D + i];
+      ab += partial[((int64_t)k * 2 + 1) * D + i];
+    }
   }
-  dgamma[i] = from_f32<T>(sg);
-  dbeta[i] = from_f32<T>(sb);
+  sg[threadIdx.y][threadIdx.x] = ag;
+  sb[threadIdx.y][threadIdx.x] = ab;
+  __syncthreads();
+  if (threadIdx.y == 0 && i < D) {
+    float tg = 0.f, tb = 0.f;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) { tg += sg[r][threadIdx.x]; tb += sb[r][threadIdx.x]; }
+    dgamma[i] = from_f32<T>(tg);
+    dbeta[i] = from_f32<T>(tb);
+  }
 }
 
 struct LnPlan {
   bool cached;
   int rt, nv, bt, grid;
+  bool ring;        // rows streamed through a shared-memory ring by a producer warp
+  int stages, smem;
 };
 
 template <typename T> static LnPlan ln_plan(int64_t D, int64_t R, bool aligned, bool bwd) {
@@ -318,9 +563,48 @@ template <typename T> static LnPlan ln_plan(int64_t D, int64_t R, bool aligned, 
     p.rt = 256; p.bt = 256; p.nv = 0;
     p.grid = (int)(R < (int64_t)sms * 4 ? R : (int64_t)sms * 4);
   }
+  if (p.cached && p.rt == 256) {
+    // ring variant: stage = one row of x (forward) or of x and dy (backward)
+    const int64_t stage_bytes = D * (int64_t)sizeof(T) * (bwd ? 2 : 1);
+    int stages = (int)((96 * 1024) / stage_bytes);
+    if (stages > 6) stages = 6;
+    if (stages < 2 && 2 * stage_bytes <= 200 * 1024) stages = 2;
+    if (stages >= 2) {
+      p.ring = true;
+      p.stages = stages;
+      p.smem = 1024 + (int)(stages * stage_bytes);
+      int per_sm = (220 * 1024) / p.smem;
+      if (per_sm > 4) per_sm = 4;
+      if (per_sm < 1) per_sm = 1;
+      p.grid = (int)(R < (int64_t)sms * per_sm ? R : (int64_t)sms * per_sm);
+    }
+  }
   if (p.grid < 1) p.grid = 1;
   return p;
 }
+
+template <typename K>
+static int32_t ring_smem_attr(K kernel, int smem) {
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return fail(LB2_LAUNCH_FAIL, "layernorm: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+  return LB2_OK;
+}
+
+#define LN_RING_CASE(KERNEL, NV_, ...)                                                        \
+  {                                                                                           \
+    int32_t rc__ = ring_smem_attr(KERNEL<T, ACT, AFFINE, NV_>, p.smem);                       \
+    if (rc__ != LB2_OK) return rc__;                                                          \
+    KERNEL<T, ACT, AFFINE, NV_><<<p.grid, kRingThreads, p.smem, st>>>(__VA_ARGS__);           \
+  }
+#define LN_RING_SWITCH(KERNEL, ...)                                  \
+  if (p.nv == 1) LN_RING_CASE(KERNEL, 1, __VA_ARGS__)                \
+  else if (p.nv == 2) LN_RING_CASE(KERNEL, 2, __VA_ARGS__)           \
+  else if (p.nv == 4) LN_RING_CASE(KERNEL, 4, __VA_ARGS__)           \
+  else LN_RING_CASE(KERNEL, 8, __VA_ARGS__)
+#define LN_RING_SWITCH_BWD(KERNEL, ...)                              \
+  if (p.nv == 1) LN_RING_CASE(KERNEL, 1, __VA_ARGS__)                \
+  else if (p.nv == 2) LN_RING_CASE(KERNEL, 2, __VA_ARGS__)           \
+  else LN_RING_CASE(KERNEL, 4, __VA_ARGS__)
 
 #define LN_LAUNCH_CACHED(KERNEL, RT_, NV_, BT_, ...)                                   \
   KERNEL<T, ACT, AFFINE, RT_, NV_, BT_><<<p.grid, BT_, 0, st>>>(__VA_ARGS__, act)
@@ -359,7 +643,11 @@ static int32_t ln_fwd_launch(T* y, float* sm, float* si, const T* x, const T* g,
                              float eps, int32_t act, cudaStream_t st) {
   const bool al = aligned_to(y, 16) && aligned_to(x, 16) && (!g || (aligned_to(g, 16) && aligned_to(b, 16)));
   const LnPlan p = ln_plan<T>(D, R, al, false);
-  if (p.cached) {
+  if (p.ring) {
+    unsigned int* status = device_status_word();
+    LB2_REQUIRE(status != nullptr, LB2_LAUNCH_FAIL, "layernorm: device status word unavailable");
+    LN_RING_SWITCH(ln_fwd_ring_kernel, y, sm, si, x, g, b, D, R, eps, act, p.stages, status)
+  } else if (p.cached) {
     LN_SWITCH(ln_fwd_cached_kernel, y, sm, si, x, g, b, D, R, eps);
   } else {
     ln_fwd_generic_kernel<T, ACT, AFFINE><<<p.grid, 256, 0, st>>>(y, sm, si, x, g, b, D, R, eps, act);
@@ -374,14 +662,18 @@ static int32_t ln_bwd_launch(T* dx, T* dg, T* db, const T* dy, const T* x, const
   const bool al = aligned_to(dx, 16) && aligned_to(dy, 16) && aligned_to(x, 16) &&
                   (!g || (aligned_to(g, 16) && aligned_to(b, 16)));
   const LnPlan p = ln_plan<T>(D, R, al, true);
-  if (p.cached) {
+  if (p.ring) {
+    unsigned int* status = device_status_word();
+    LB2_REQUIRE(status != nullptr, LB2_LAUNCH_FAIL, "layernorm: device status word unavailable");
+    LN_RING_SWITCH_BWD(ln_bwd_ring_kernel, dx, ws, dy, x, g, b, sm, si, D, R, act, p.stages, status)
+  } else if (p.cached) {
     LN_SWITCH_BWD(ln_bwd_cached_kernel, dx, ws, dy, x, g, b, sm, si, D, R);
   } else {
     ln_bwd_generic_kernel<T, ACT, AFFINE><<<p.grid, 256, 0, st>>>(dx, ws, dy, x, g, b, sm, si, D, R, act);
   }
   LB2_CHECK_LAUNCH("layernorm_bwd");
   if constexpr (AFFINE) {
-    ln_finish_kernel<T><<<(unsigned)((D + 255) / 256), 256, 0, st>>>(dg, db, ws, D, p.grid);
+    ln_finish_kernel<T><<<(unsigned)((D + 31) / 32), dim3(32, 8), 0, st>>>(dg, db, ws, D, p.grid);
     LB2_CHECK_LAUNCH("layernorm_bwd_finish");
   }
   return LB2_OK;

@@ -187,6 +187,36 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map
       : "memory");
 }
 
+// 1-D bulk copy global -> shared (16-byte aligned addresses, size a multiple of 16 bytes)
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
+               "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
+// Sum over the first `nthreads` threads of the CTA (a multiple of 32, they must all call) through named
+// barrier 1, so that other warps of the CTA (a copy-producer warp) need not take part.
+__device__ __forceinline__ float group_sum(float v, float* smem, int nthreads) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = nthreads >> 5;
+  v = warp_sum(v);
+  asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+  if (lane == 0) smem[w] = v;
+  asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+  float t = (lane < nw) ? smem[lane] : 0.f;
+  return warp_sum(t);
+}
+// two sums at once (one barrier pair)
+__device__ __forceinline__ float2 group_sum2(float a, float b, float* smem, int nthreads) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = nthreads >> 5;
+  a = warp_sum(a);
+  b = warp_sum(b);
+  asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+  if (lane == 0) { smem[w] = a; smem[32 + w] = b; }
+  asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+  float ta = (lane < nw) ? smem[lane] : 0.f, tb = (lane < nw) ? smem[32 + lane] : 0.f;
+  return make_float2(warp_sum(ta), warp_sum(tb));
+}
+
 // cuTensorMapEncodeTiled through the runtime's driver entry point (no link-time libcuda dependency).
 typedef CUresult (*TensorMapEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                       const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,

@@ -79,13 +79,24 @@ def _group_for(t: torch.Tensor):
 
 avg = "avg"
 
+
+def _wire(t: torch.Tensor) -> torch.Tensor:
+    """A contiguous view of the same memory for the collective: column-major (Julia-layout) arrays are
+    handed over as their reversed-axes view, everything else must already be contiguous."""
+    if t.is_contiguous():
+        return t
+    r = t.permute(*reversed(range(t.dim())))
+    if r.is_contiguous():
+        return r
+    raise ValueError("collectives need a dense array (column-major or row-major)")
+
 _OPS = {"+": dist.ReduceOp.SUM, "sum": dist.ReduceOp.SUM, "*": dist.ReduceOp.PRODUCT, "prod": dist.ReduceOp.PRODUCT,
         "max": dist.ReduceOp.MAX, "min": dist.ReduceOp.MIN}
 
 
 def bcast_(backend, sendrecvbuf: torch.Tensor, *, root: int = 0) -> torch.Tensor:
     """bcast! (public_api.jl:92-117)."""
-    dist.broadcast(sendrecvbuf, src=root, group=_group_for(sendrecvbuf))
+    dist.broadcast(_wire(sendrecvbuf), src=root, group=_group_for(sendrecvbuf))
     return sendrecvbuf
 
 
@@ -95,12 +106,12 @@ def allreduce_(backend, sendrecvbuf: torch.Tensor, op=avg) -> torch.Tensor:
     g = _group_for(sendrecvbuf)
     if op == avg:
         if sendrecvbuf.is_cuda and _state["backend"] == "nccl":
-            dist.all_reduce(sendrecvbuf, op=dist.ReduceOp.AVG, group=g)
+            dist.all_reduce(_wire(sendrecvbuf), op=dist.ReduceOp.AVG, group=g)
         else:
-            dist.all_reduce(sendrecvbuf, op=dist.ReduceOp.SUM, group=g)
+            dist.all_reduce(_wire(sendrecvbuf), op=dist.ReduceOp.SUM, group=g)
             sendrecvbuf.div_(dist.get_world_size())
         return sendrecvbuf
-    dist.all_reduce(sendrecvbuf, op=_OPS[op], group=g)
+    dist.all_reduce(_wire(sendrecvbuf), op=_OPS[op], group=g)
     return sendrecvbuf
 
 
@@ -108,11 +119,11 @@ def reduce_(backend, sendrecvbuf: torch.Tensor, op="+", *, root: int = 0) -> tor
     """reduce! (public_api.jl:154-188): result valid on `root` only."""
     g = _group_for(sendrecvbuf)
     if op == avg:
-        dist.reduce(sendrecvbuf, dst=root, op=dist.ReduceOp.SUM, group=g)
+        dist.reduce(_wire(sendrecvbuf), dst=root, op=dist.ReduceOp.SUM, group=g)
         if dist.get_rank() == root:
             sendrecvbuf.div_(dist.get_world_size())
         return sendrecvbuf
-    dist.reduce(sendrecvbuf, dst=root, op=_OPS[op], group=g)
+    dist.reduce(_wire(sendrecvbuf), dst=root, op=_OPS[op], group=g)
     return sendrecvbuf
 
 

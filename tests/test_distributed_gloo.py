@@ -61,6 +61,9 @@ def _primitives(D, be, rank, world):
     buf = torch.full((512,), float(rank + 1))
     D.allreduce_(be, buf, D.avg)
     assert torch.allclose(buf, torch.full((512,), sum(range(1, world + 1)) / world))
+    col = torch.full((4, 6), float(rank + 1)).T   # column-major (non-contiguous) array
+    D.allreduce_(be, col, D.avg)
+    assert torch.allclose(col, torch.full((6, 4), sum(range(1, world + 1)) / world))
     buf = torch.full((512,), float(rank + 1))
     D.reduce_(be, buf, "+", root=0)
     if rank == 0:
