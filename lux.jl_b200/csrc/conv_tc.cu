@@ -20,6 +20,8 @@
 // K-split in the workspace and a fixed-order reduction — deterministic.
 //
 // Roofline: tensor pipe; algorithmic FLOPs = 2*Wo*Ho*N*Cout*Cin*kW*kH per pass.
+#include <stdlib.h>
+
 #include "conv.cuh"
 #include "tc_ptx.cuh"
 
@@ -167,6 +169,7 @@ struct ConvTcParams {
   int16_t a_shift[kMaxKb];   // start-coordinate offset along s (multiple of 8 elements)
   int16_t a_chan[kMaxKb];    // first contracted channel of the k-block
   int8_t a_copy[kMaxKb];     // which W-shifted copy
+  uint32_t debug;            // experiment switches (LB2_GEMM_DEBUG): 1 skip epilogue work, 2 skip MMAs, 4 skip A loads
 };
 
 template <int BN, int ACT>
@@ -236,6 +239,7 @@ conv_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
         const int m0 = (t % p.tiles_m) * kConvBM, img = t / p.tiles_m;
         for (int kb = 0; kb < p.num_kb; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, p.status, 0x1000u)) { ok = false; break; }
+          if (p.debug & 4u) { mbar_arrive(&full[stage]); if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; } continue; }
           mbar_expect_tx(&full[stage], A_BYTES);
           const uint32_t sA = sA0 + stage * A_BYTES;
           const int c0 = m0 + p.a_shift[kb];
@@ -255,7 +259,7 @@ conv_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < p.num_kb; ++kb) {
           if (!mbar_wait(&full[stage], phase, p.status, 0x8000u)) { ok = false; break; }
-          tc_fence_after();
+          if (!(p.debug & 8u)) tc_fence_after();
           const uint32_t sA = sA0 + stage * A_BYTES;
           const uint32_t sB = sB0 + kb * B_BYTES;
           const uint32_t a_lo32 = ((sA >> 4) & 0x3FFFu) | p.a_desc_lbo;
@@ -264,9 +268,10 @@ conv_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
           for (int ks = 0; ks < 4; ++ks) {
             const uint64_t ad = ((uint64_t)p.a_desc_hi << 32) | (uint64_t)(a_lo32 + ks * p.a_k_advance);
             const uint64_t bd = ((uint64_t)p.b_desc_hi << 32) | (uint64_t)(b_lo32 + ks * p.b_k_advance);
+            if (p.debug & 2u) continue;
             umma<false>(d_tmem, ad, bd, p.idesc, (kb | ks) != 0 ? 1u : 0u);
           }
-          umma_commit(&empty[stage]);
+          if (p.debug & 16u) mbar_arrive(&empty[stage]); else umma_commit(&empty[stage]);
           if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
         }
         if (ok) umma_commit(&acc_full[acc]);
@@ -287,7 +292,7 @@ conv_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
     bool ok = true;
     for (int t = first; t < tiles_per_n && ok; t += step) {
       const int m0 = (t % p.tiles_m) * kConvBM, img = t / p.tiles_m;
-      if (!mbar_wait(&acc_full[acc], acc_phase, p.status, 0x10000u)) { ok = false; break; }
+      if (!mbar_wait_warp(&acc_full[acc], acc_phase, p.status, 0x10000u)) { ok = false; break; }
       tc_fence_after();
       const int s = m0 + q * 32 + lane;
       const bool s_ok = s < p.S_out;
@@ -295,7 +300,7 @@ conv_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
       __nv_bfloat16* yp = Y + base;
       __nv_bfloat16* pp = P != nullptr ? P + base : nullptr;
 #pragma unroll 1
-      for (int c = 0; c < COLS / 32; ++c) {
+      for (int c = 0; c < ((p.debug & 1u) ? 0 : COLS / 32); ++c) {
         uint32_t r[32];
         tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + half * COLS + c * 32, r);
         tmem_ld_wait();
@@ -331,6 +336,275 @@ conv_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
   }
 }
 
+
+// ----------------------------------------------------------------------------------------------
+// forward / data-gradient kernel, shift-in-epilogue variant (kernel width <= 4, 64-channel N tiles)
+// ----------------------------------------------------------------------------------------------
+// Reads x directly (no shifted copies). For every kernel row th the A tile (128 positions x 64
+// channels) is loaded ONCE and multiplied with the kW filter taps of that row into kW separate TMEM
+// accumulators D_tw. The taps' single-element shifts along W are applied when the accumulators
+// are combined: y[s] = sum_tw D_tw[s + tw - pad_w] (masked where w + tw - pad_w leaves the image
+// row). Accumulator rows are TMEM lanes, so the shift is a warp shuffle, with the few rows that
+// cross a warp boundary exchanged through shared memory. A tile covers MMA rows s0-8 .. s0+119 and
+// produces the 112 outputs s0 .. s0+111 (the 8-row halo keeps the TMA start coordinate 16-byte
+// aligned). Besides a third of the operand traffic this gives the tensor core kW independent
+// accumulation chains to interleave (back-to-back MMAs into ONE accumulator are latency-bound at
+// this N) and 4*kW MMAs per pipeline hand-over instead of 4.
+struct ConvTc2Params {
+  int32_t W, S_out, n_img, n_out;
+  int32_t tiles_m, tiles_n, kW, kH, chunks, pad_w;
+  int32_t stages;
+  uint32_t idesc;
+  uint32_t a_desc_hi, a_desc_lbo, a_k_advance;
+  uint32_t b_desc_hi, b_desc_lbo, b_k_advance;
+  void* y;
+  void* preact;
+  const void* bias;
+  int32_t act;
+  unsigned int* status;
+  int16_t row_shift[16];   // per kernel row th: (th - pad_h) * W
+  uint32_t debug;          // experiment switches (LB2_GEMM_DEBUG)
+};
+
+constexpr int kHalo = 8;
+constexpr int kTileOut = kConvBM - 2 * kHalo;   // 112 outputs per tile
+
+template <int KW, int ACT>
+__global__ void __launch_bounds__(kConvThreads, 1)
+conv_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
+                    const __grid_constant__ CUtensorMap tmY, const __grid_constant__ CUtensorMap tmP,
+                    const __grid_constant__ ConvTc2Params p) {
+  constexpr int BN = 64;
+  constexpr int A_BYTES = kConvBM * 128;
+  constexpr int B_BYTES = BN * 128;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const int num_b = KW * p.kH * p.chunks;       // resident filter tiles, index (th*kW + tw)*chunks + chunk
+  const int num_kb = p.kH * p.chunks;             // A stages per tile
+  const uint32_t sB0 = smem_base;
+  const uint32_t sA0 = smem_base + num_b * B_BYTES;
+  uint8_t* after = smem_gen + num_b * B_BYTES + p.stages * A_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(after);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + p.stages;
+  uint64_t* acc_full = bars + 2 * p.stages;
+  uint64_t* acc_empty = acc_full + 2;
+  uint64_t* b_full = acc_empty + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(b_full + 1);
+  // accumulator rows that cross a warp boundary: edge[parity][half][quarter][tw][3 rows][32 cols]
+  float* edge = reinterpret_cast<float*>(after + 512);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(after + 448);
+  constexpr int EDGE_Q = KW * 3 * 32;   // floats per (parity, half, quarter)
+  // output staging for the TMA store: [64 channels][112 positions] bf16, one tile for y and one for the
+  // pre-activation. Rows of a tile start 16 bytes off a 32-byte sector in global memory, so direct
+  // 2-byte stores from registers would leave half-written sectors; the tiled store writes whole runs.
+  constexpr int STAGE_OUT = BN * kTileOut * 2;
+  uint8_t* out_stage = after + 512 + 2 * 2 * 4 * EDGE_Q * 4;
+  __shared__ float sbias[BN];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int stages = p.stages;
+  const int tiles_per_n = p.tiles_m * p.n_img;
+  const int nt = blockIdx.x % p.tiles_n;
+  const int first = blockIdx.x / p.tiles_n, step = gridDim.x / p.tiles_n;
+  const int n0 = nt * BN;
+  constexpr uint32_t tmem_cols = (2 * KW * BN) > 256 ? 512u : 256u;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 8); }
+    mbar_init(b_full, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  {
+    const __nv_bfloat16* bias = reinterpret_cast<const __nv_bfloat16*>(p.bias);
+    for (int c = threadIdx.x; c < BN; c += blockDim.x)
+      sbias[c] = (bias != nullptr && n0 + c < p.n_out) ? __bfloat162float(bias[n0 + c]) : 0.f;
+  }
+  if (warp == 2) {
+    tmem_alloc(tmem_slot, tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tmX);
+      tma_prefetch_desc(&tmW);
+      mbar_expect_tx(b_full, (uint32_t)(num_b * B_BYTES));
+      // packed filter column block (th*KW + tw)*chunks + chunk  ->  resident slot (th*chunks + chunk)*KW + tw,
+      // so that the KW taps of one (kernel row, channel chunk) form ONE K-major operand of KW*64 rows
+      for (int th = 0; th < p.kH; ++th)
+        for (int tw = 0; tw < KW; ++tw)
+          for (int ch = 0; ch < p.chunks; ++ch)
+            tma_load_2d(sB0 + ((th * p.chunks + ch) * KW + tw) * B_BYTES, &tmW, ((th * KW + tw) * p.chunks + ch) * 64, n0, b_full);
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int t = first; t < tiles_per_n && ok; t += step) {
+        const int s0 = (t % p.tiles_m) * kTileOut - kHalo, img = t / p.tiles_m;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1u, p.status, 0x1000u)) { ok = false; break; }
+          if (p.debug & 4u) { mbar_arrive(&full[stage]); if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; } continue; }
+          mbar_expect_tx(&full[stage], A_BYTES);
+          const uint32_t sA = sA0 + stage * A_BYTES;
+          const int th = kb / p.chunks, chunk = kb % p.chunks;
+          const int c0 = s0 + p.row_shift[th];
+          tma_load_4d(sA, &tmX, c0, chunk * 64, img, 0, &full[stage]);
+          tma_load_4d(sA + A_BYTES / 2, &tmX, c0 + 64, chunk * 64, img, 0, &full[stage]);
+          if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+      bool ok = mbar_wait(b_full, 0, p.status, 0x2000u);
+      for (int t = first; t < tiles_per_n && ok; t += step) {
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1u, p.status, 0x4000u)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d0 = tmem_base + acc * (KW * BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full[stage], phase, p.status, 0x8000u)) { ok = false; break; }
+          tc_fence_after();
+          const int th = kb / p.chunks, chunk = kb % p.chunks;
+          const uint32_t sA = sA0 + stage * A_BYTES;
+          const uint32_t a_lo32 = ((sA >> 4) & 0x3FFFu) | p.a_desc_lbo;
+          // one MMA of N = KW*64 per k-step: its column blocks are the per-tap accumulators D_tw
+          const uint32_t sB = sB0 + (uint32_t)((th * p.chunks + chunk) * KW * B_BYTES);
+          const uint32_t b_lo32 = ((sB >> 4) & 0x3FFFu) | p.b_desc_lbo;
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) {
+            const uint64_t ad = ((uint64_t)p.a_desc_hi << 32) | (uint64_t)(a_lo32 + ks * p.a_k_advance);
+            const uint64_t bd = ((uint64_t)p.b_desc_hi << 32) | (uint64_t)(b_lo32 + ks * p.b_k_advance);
+            if (p.debug & 2u) continue;
+            umma<false>(d0, ad, bd, p.idesc, (kb | ks) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty[stage]);
+          if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) umma_commit(&acc_full[acc]);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  } else if (warp >= 4) {
+    const int q = warp & 3, half = (warp - 4) >> 2;   // lane quarter; which 32 of the 64 channels
+    const int r = q * 32 + lane;                      // MMA row of this thread
+    uint32_t acc = 0, acc_phase = 0;
+    const __nv_bfloat16* P = reinterpret_cast<const __nv_bfloat16*>(p.preact);   // only tested for null here
+    const float* sb = sbias + half * 32;
+    uint32_t parity = 0;
+    for (int t = first; t < tiles_per_n; t += step, parity ^= 1u) {
+      const int s0 = (t % p.tiles_m) * kTileOut - kHalo, img = t / p.tiles_m;
+      if (!mbar_wait_warp(&acc_full[acc], acc_phase, p.status, 0x10000u)) *abort_flag = 1;
+      tc_fence_after();
+      if (p.debug & 1u) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[acc]);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+        continue;
+      }
+      const int s = s0 + r;
+      const int w = ((s % p.W) + p.W) % p.W;   // column inside the image row (s is negative in the first halo)
+      const uint32_t t_acc = tmem_base + ((uint32_t)(q * 32) << 16) + acc * (KW * BN) + half * 32;
+      float* eb = edge + (size_t)((parity * 2 + half) * 4 + q) * EDGE_Q;
+      // pass 1: publish the rows a neighbouring quarter needs (last -d rows for d < 0, first d rows for d > 0)
+#pragma unroll
+      for (int tw = 0; tw < KW; ++tw) {
+        const int d = tw - p.pad_w;
+        if (d != 0 && !(p.debug & 32u)) {
+          uint32_t rt[32];
+          tmem_ld32(t_acc + tw * BN, rt);
+          tmem_ld_wait();
+          int idx = -1;
+          if (d < 0 && lane >= 32 + d) idx = lane - (32 + d);
+          if (d > 0 && lane < d) idx = lane;
+          if (idx >= 0) {
+            float* e = eb + (tw * 3 + idx) * 32;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) e[j] = __uint_as_float(rt[j]);
+          }
+        }
+      }
+      // one barrier over all eight epilogue warps: edge rows are published, the previous tile's store has
+      // finished reading the staging buffers, and an expired wait is seen by everyone at the same point
+      if (warp == 4 && lane == 0) tma_store_wait_read<0>();
+      asm volatile("bar.sync 4, 256;" ::: "memory");
+      if (*abort_flag) break;
+      // pass 2: combine the taps
+      float out[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) out[j] = sb[j];
+#pragma unroll
+      for (int tw = 0; tw < KW; ++tw) {
+        const int d = tw - p.pad_w;
+        if ((p.debug & 16u) && d != 0) continue;
+        uint32_t rt[32];
+        tmem_ld32(t_acc + tw * BN, rt);
+        tmem_ld_wait();
+        if (d == 0) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) out[j] += __uint_as_float(rt[j]);
+        } else {
+          const bool in_row = (w + d >= 0) && (w + d < p.W);
+          const int src = lane + d;
+          const bool local = src >= 0 && src < 32;
+          const int qn = src < 0 ? q - 1 : q + 1;
+          const float* en = nullptr;
+          if (!local && qn >= 0 && qn < 4) {
+            const float* nb = edge + (size_t)((parity * 2 + half) * 4 + qn) * EDGE_Q;
+            en = nb + (tw * 3 + (src < 0 ? lane : src - 32)) * 32;
+          }
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float v = __shfl_sync(0xffffffffu, __uint_as_float(rt[j]), src & 31);
+            if (!local) v = en != nullptr ? en[j] : 0.f;
+            if (in_row) out[j] += v;
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+      // stage the tile in shared memory ([channel][position]) and let one thread issue the tiled store
+      const bool valid = r >= kHalo && r < kConvBM - kHalo;
+      if (valid && !(p.debug & 8u)) {
+        __nv_bfloat16* so = reinterpret_cast<__nv_bfloat16*>(out_stage) + (half * 32) * kTileOut + (r - kHalo);
+        __nv_bfloat16* sp = so + BN * kTileOut;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          if (P != nullptr) sp[j * kTileOut] = __float2bfloat16_rn(out[j]);
+          so[j * kTileOut] = __float2bfloat16_rn(act_apply_any<ACT, true>(p.act, out[j]));
+        }
+      }
+      fence_proxy_async_smem();
+      asm volatile("bar.sync 4, 256;" ::: "memory");
+      if (warp == 4 && lane == 0 && !(p.debug & 8u)) {
+        const int so0 = (t % p.tiles_m) * kTileOut;
+        tma_store_3d(&tmY, smem_u32(out_stage), so0, n0, img);
+        if (P != nullptr) tma_store_3d(&tmP, smem_u32(out_stage + STAGE_OUT), so0, n0, img);
+        tma_store_commit();
+      }
+      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+    }
+    if (warp == 4 && lane == 0) tma_store_wait_all<0>();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    if (*reinterpret_cast<volatile unsigned int*>(p.status) != 0) {
+      for (int i = 0; i < 64; ++i) __nanosleep(2000);
+    }
+    tc_fence_after();
+    tmem_dealloc(tmem_base, tmem_cols);
+  }
+}
 
 // ----------------------------------------------------------------------------------------------
 // filter-gradient kernel
@@ -450,7 +724,7 @@ conv_tc_wgrad_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
       const int kb_lo = z * p.kb_per_split;
       const bool empty_range = kb_lo >= p.kb_total;   // a split with no k-blocks contributes zeros
       if (!empty_range) {
-        if (!mbar_wait(&acc_full[acc], acc_phase, p.status, 0x100000u)) { ok = false; break; }
+        if (!mbar_wait_warp(&acc_full[acc], acc_phase, p.status, 0x100000u)) { ok = false; break; }
         tc_fence_after();
       }
       const int row = mt * 128 + q * 32 + lane;
@@ -543,6 +817,19 @@ static bool bf16_map_2d(CUtensorMap* map, const void* ptr, int64_t d0, int64_t d
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// output tensor (S_out, channels, images) for the tiled store: box = 112 positions x 64 channels, no swizzle
+static bool bf16_map_out(CUtensorMap* map, const void* ptr, int64_t s_out, int64_t ch, int64_t n) {
+  TensorMapEncodeFn enc = tensor_map_encoder();
+  if (!enc) return false;
+  cuuint64_t dims[3] = {(cuuint64_t)s_out, (cuuint64_t)ch, (cuuint64_t)n};
+  cuuint64_t strides[2] = {(cuuint64_t)s_out * 2, (cuuint64_t)s_out * ch * 2};
+  cuuint32_t box[3] = {(cuuint32_t)(kConvBM - 16), 64, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 static int conv_bn(int cn) { return cn <= 64 ? 64 : 128; }
 static int conv_chunks(int ck) { return (ck + 63) / 64; }
 static int conv_fwd_stages(const ConvGemm& c) {
@@ -552,7 +839,20 @@ static int conv_fwd_stages(const ConvGemm& c) {
   return st > 8 ? 8 : st;
 }
 
+// shift-in-epilogue kernel: kernel width <= 4, filter resident next to at least 3 A stages and the edge buffers
+static int conv_fwd2_stages(const ConvGemm& c) {
+  if (c.kW > 4 || c.kH > 16) return 0;
+  const int resident = c.kW * c.kH * conv_chunks(c.Ck) * 64 * 128;
+  const int edges = 2 * 2 * 4 * c.kW * 3 * 32 * 4 + 2 * 64 * (kConvBM - 16) * 2;   // edge rows + output staging
+  int st = (198 * 1024 - resident - edges) / (kConvBM * 128);
+  return st > 8 ? 8 : st;
+}
+static bool conv_use_fwd2(const ConvGemm& c) { return conv_fwd2_stages(c) >= 3; }
+
 static bool conv_gemm_ok(const ConvGemm& c) {
+  if (c.W % 8 == 0 && c.kW >= 1 && c.kH >= 1 && conv_use_fwd2(c) && (int64_t)(c.kH + c.pad_h) * c.W <= 32000 &&
+      (int64_t)c.W * c.Hi < (1 << 30) && (int64_t)c.W * c.Ho < (1 << 30))
+    return tensor_map_encoder() != nullptr;
   if (c.W % 8 != 0 || c.kW > 8 || c.kW < 1 || c.kH < 1) return false;
   const int num_kb = c.kW * c.kH * conv_chunks(c.Ck);
   if (num_kb > kMaxKb) return false;
@@ -575,8 +875,9 @@ bool conv_tc_supported(const ConvGeom& g, int32_t dtype) {
 }
 
 static size_t copies_bytes(const ConvGemm& c) { return align_up((size_t)c.kW * c.W * c.Hi * c.Ck * c.N * 2, 1024); }
+static size_t gemm_copies_bytes(const ConvGemm& c) { return conv_use_fwd2(c) ? 0 : copies_bytes(c); }
 static size_t packed_bytes(const ConvGemm& c) {
-  const int bn = conv_bn(c.Cn);
+  const int bn = conv_use_fwd2(c) ? 64 : conv_bn(c.Cn);
   const size_t rows = (size_t)((c.Cn + bn - 1) / bn) * bn;
   return align_up(rows * (size_t)(c.kW * c.kH * conv_chunks(c.Ck) * 64) * 2, 1024);
 }
@@ -590,6 +891,63 @@ static unsigned flat_grid_tc(int64_t total) {
 static int32_t run_conv_gemm(void* out, void* preact, const void* bias, int32_t act, const void* in, const void* w,
                              const ConvGemm& c, const PackGeom& pg, uint8_t* ws, cudaStream_t st) {
   using T = __nv_bfloat16;
+  if (conv_use_fwd2(c)) {
+    T* wp2 = reinterpret_cast<T*>(ws);
+    conv_pack_filter_kernel<T><<<flat_grid_tc((int64_t)pg.n_rows * pg.k_total), 256, 0, st>>>(wp2, (const T*)w, pg);
+    LB2_CHECK_LAUNCH("conv_tc filter packing");
+    ConvTc2Params q{};
+    q.W = c.W; q.S_out = c.W * c.Ho; q.n_img = c.N; q.n_out = c.Cn;
+    q.tiles_m = (q.S_out + kTileOut - 1) / kTileOut;
+    q.tiles_n = (c.Cn + 63) / 64;
+    q.kW = c.kW; q.kH = c.kH; q.chunks = conv_chunks(c.Ck); q.pad_w = c.pad_w;
+    q.stages = conv_fwd2_stages(c);
+    for (int th = 0; th < c.kH; ++th) q.row_shift[th] = (int16_t)((th - c.pad_h) * c.W);
+    q.a_desc_hi = (uint32_t)((1024u >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
+    q.a_desc_lbo = ((8192u >> 4) & 0x3FFFu) << 16;
+    q.a_k_advance = 2048u >> 4;
+    q.b_desc_hi = q.a_desc_hi;
+    q.b_desc_lbo = 1u << 16;
+    q.b_k_advance = 32u >> 4;
+    q.idesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | ((uint32_t)((c.kW * 64) >> 3) << 17) | ((uint32_t)(kConvBM >> 4) << 24);
+    q.y = out; q.preact = preact; q.bias = bias; q.act = act;
+    {
+      static const uint32_t dbg2 = getenv("LB2_GEMM_DEBUG") ? (uint32_t)atoi(getenv("LB2_GEMM_DEBUG")) : 0u;
+      q.debug = dbg2;
+    }
+    q.status = device_status_word();
+    LB2_REQUIRE(q.status != nullptr, LB2_LAUNCH_FAIL, "conv_tc: device status word unavailable");
+    CUtensorMap mX2, mW2, mY2, mP2;
+    if (!bf16_map_4d(&mX2, in, (int64_t)c.W * c.Hi, c.Ck, c.N, 1, 64, 64) || !bf16_map_2d(&mW2, wp2, pg.k_total, pg.n_rows, 64, 64) ||
+        !bf16_map_out(&mY2, out, q.S_out, c.Cn, c.N) || !bf16_map_out(&mP2, preact != nullptr ? preact : out, q.S_out, c.Cn, c.N))
+      return fail(LB2_LAUNCH_FAIL, "conv_tc: cuTensorMapEncodeTiled failed");
+    const int num_b = c.kW * c.kH * q.chunks;
+    const int smem2 = num_b * 64 * 128 + q.stages * kConvBM * 128 + 512 + 2 * 2 * 4 * c.kW * 3 * 32 * 4 + 2 * 64 * kTileOut * 2 + 1024 + 256;
+    const int tiles_per_n2 = q.tiles_m * q.n_img;
+    int per_n2 = sm_count() / q.tiles_n;
+    if (per_n2 > tiles_per_n2) per_n2 = tiles_per_n2;
+    if (per_n2 < 1) per_n2 = 1;
+    const int grid2 = per_n2 * q.tiles_n;
+    auto launch2 = [&](auto kernel) -> int32_t {
+      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2);
+      if (e != cudaSuccess) return fail(LB2_LAUNCH_FAIL, "conv_tc: cannot reserve %d bytes of shared memory: %s", smem2, cudaGetErrorString(e));
+      kernel<<<grid2, kConvThreads, smem2, st>>>(mX2, mW2, mY2, mP2, q);
+      LB2_CHECK_LAUNCH("conv_tc_fwd2");
+      return LB2_OK;
+    };
+#define LB2_FWD2_ACT(KW_)                                                                    \
+    switch (act) {                                                                           \
+      case LB2_ACT_IDENTITY: return launch2(conv_tc_fwd2_kernel<KW_, LB2_ACT_IDENTITY>);     \
+      case LB2_ACT_RELU: return launch2(conv_tc_fwd2_kernel<KW_, LB2_ACT_RELU>);             \
+      default: return launch2(conv_tc_fwd2_kernel<KW_, -1>);                                 \
+    }
+    switch (c.kW) {
+      case 1: LB2_FWD2_ACT(1)
+      case 2: LB2_FWD2_ACT(2)
+      case 3: LB2_FWD2_ACT(3)
+      default: LB2_FWD2_ACT(4)
+    }
+#undef LB2_FWD2_ACT
+  }
   T* copies = reinterpret_cast<T*>(ws);
   T* wp = reinterpret_cast<T*>(ws + copies_bytes(c));
   const int64_t rows = (int64_t)c.Hi * c.Ck * c.N;
@@ -624,6 +982,10 @@ static int32_t run_conv_gemm(void* out, void* preact, const void* bias, int32_t 
   p.b_k_advance = 32u >> 4;
   p.idesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | (0u << 16) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(kConvBM >> 4) << 24);
   p.y = out; p.preact = preact; p.bias = bias; p.act = act;
+  {
+    static const uint32_t dbg = getenv("LB2_GEMM_DEBUG") ? (uint32_t)atoi(getenv("LB2_GEMM_DEBUG")) : 0u;
+    p.debug = dbg;
+  }
   p.status = device_status_word();
   LB2_REQUIRE(p.status != nullptr, LB2_LAUNCH_FAIL, "conv_tc: device status word unavailable");
   CUtensorMap mX, mW;
@@ -667,7 +1029,7 @@ static PackGeom pack_geom(const ConvGeom& g, const ConvGemm& c, int transpose) {
   PackGeom pg{};
   pg.kW = g.k[0]; pg.kH = g.k[1]; pg.cin = g.cin; pg.cout = g.cout; pg.flip = g.flip; pg.transpose = transpose;
   pg.chunks = conv_chunks(c.Ck);
-  const int bn = conv_bn(c.Cn);
+  const int bn = conv_use_fwd2(c) ? 64 : conv_bn(c.Cn);
   pg.n_rows = ((c.Cn + bn - 1) / bn) * bn;
   pg.k_total = c.kW * c.kH * pg.chunks * 64;
   return pg;
@@ -675,7 +1037,7 @@ static PackGeom pack_geom(const ConvGeom& g, const ConvGemm& c, int transpose) {
 
 size_t conv_tc_fwd_workspace_bytes(const ConvGeom& g) {
   const ConvGemm c = fwd_gemm(g);
-  return copies_bytes(c) + packed_bytes(c);
+  return gemm_copies_bytes(c) + packed_bytes(c);
 }
 
 int32_t conv_tc_fwd(void* y, void* preact, const void* x, const void* w, const void* bias, const ConvGeom& g,
@@ -714,7 +1076,7 @@ static size_t wg_partial_bytes(const WgPlan& w) {
 
 size_t conv_tc_bwd_workspace_bytes(const ConvGeom& g) {
   const ConvGemm d = dgrad_gemm(g), f = fwd_gemm(g);
-  const size_t dgrad = copies_bytes(d) + packed_bytes(d);
+  const size_t dgrad = gemm_copies_bytes(d) + packed_bytes(d);
   const size_t wgrad = copies_bytes(f) + wg_partial_bytes(wg_plan(g));
   return dgrad > wgrad ? dgrad : wgrad;   // the two gradients run one after the other in the same region
 }

@@ -191,7 +191,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       const int m0 = (tile % p.tiles_m) * kBM, n0 = (tile / p.tiles_m) * BN + half * COLS;
-      if (!mbar_wait(&acc_full[acc], acc_phase, p.status, 0x8u)) { ok = false; break; }
+      if (!mbar_wait_warp(&acc_full[acc], acc_phase, p.status, 0x8u)) { ok = false; break; }
       tc_fence_after();
       const int64_t m = (int64_t)m0 + q * 32 + lane;
       const bool m_ok = m < p.Mm;
@@ -369,7 +369,7 @@ gemm_tc_f32acc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 #pragma unroll
       for (int j = 0; j < 64; ++j) sum[j] = 0.f;
       for (int kb = 0; kb < p.num_kb; ++kb) {
-        if (!mbar_wait(&chunk_full[ch], ch_phase, p.status, 0x800u)) { ok = false; break; }
+        if (!mbar_wait_warp(&chunk_full[ch], ch_phase, p.status, 0x800u)) { ok = false; break; }
         tc_fence_after();
         const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + ch * BN + half * 64;
         uint32_t r0[32], r1[32];
@@ -573,7 +573,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
       const int m0 = (tile % p.tiles_m) * (2 * kBM) + (int)rank * kBM;
       const int n0 = (tile / p.tiles_m) * BN;
-      if (!mbar_wait(&acc_full[acc], acc_phase, p.status, 0x80u)) { ok = false; break; }
+      if (!mbar_wait_warp(&acc_full[acc], acc_phase, p.status, 0x80u)) { ok = false; break; }
       tc_fence_after();
       const int64_t m = (int64_t)m0 + q * 32 + lane;
       const bool m_ok = m < p.Mm;

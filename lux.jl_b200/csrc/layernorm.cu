@@ -144,7 +144,7 @@ ln_fwd_ring_kernel(T* __restrict__ y, float* __restrict__ mean_out, float* __res
     const int st = (int)(it % stages);
     const uint32_t ph = (uint32_t)((it / stages) & 1);
     const int64_t row = blockIdx.x + it * gridDim.x;
-    if (!mbar_wait(&full[st], ph, status, 0x400000u)) *abort_flag = 1;
+    if (!mbar_wait_warp(&full[st], ph, status, 0x400000u)) *abort_flag = 1;
     const T* sx = reinterpret_cast<const T*>(data + (size_t)st * row_bytes);
     Vec16<T> xv[NV];
     float s = 0.f;
@@ -244,7 +244,7 @@ ln_bwd_ring_kernel(T* __restrict__ dx, float* __restrict__ partial, const T* __r
     const uint32_t ph = (uint32_t)((it / stages) & 1);
     const int64_t row = blockIdx.x + it * gridDim.x;
     const float mean = mean_in[row], inv = inv_in[row];
-    if (!mbar_wait(&full[st], ph, status, 0x1000000u)) *abort_flag = 1;
+    if (!mbar_wait_warp(&full[st], ph, status, 0x1000000u)) *abort_flag = 1;
     const T* sx = reinterpret_cast<const T*>(data + (size_t)st * 2 * row_bytes);
     const T* sdy = reinterpret_cast<const T*>(data + (size_t)st * 2 * row_bytes + row_bytes);
     Vec16<T> xv[NV], gy[NV];
