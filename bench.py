@@ -186,6 +186,8 @@ def run_gpu_arm(args):
         dist = dist_mod
         dist.init_process_group("nccl", device_id=device)
     lib = _cabi.load()
+    if world > 1:   # leave a few SMs to the NCCL all-reduce that runs under the dX GEMM
+        lib.lb2_set_reserved_sms(int(os.environ.get("LB2_BENCH_RESERVED_SMS", "0")))
 
     # every rank holds the same parameters and its own batch shard
     Wn, xn, bn, dyn = make_inputs(1, N)
@@ -200,12 +202,24 @@ def run_gpu_arm(args):
     dy = L.from_numpy(dyn, device, bf)
     del Wn, bn
 
+    pending = []
+
+    def start_allreduce(dW, db):
+        # DistributedOptimizer's all-reduce(avg) of every parameter-gradient leaf, started as soon as the
+        # leaves exist so that it runs underneath the dX GEMM. dW is column-major: .T is the contiguous
+        # view of the same memory.
+        pending.append(dist.all_reduce(dW.T, op=dist.ReduceOp.AVG, async_op=True))
+        pending.append(dist.all_reduce(db, op=dist.ReduceOp.AVG, async_op=True))
+
     def step():
         y, pullback = L.rrule_fused_dense(ACT, W, x, b)
-        dW, dx, db = pullback(dy)
-        if dist is not None:  # DistributedOptimizer: allreduce(avg) of every parameter-gradient leaf
-            dist.all_reduce(dW.T, op=dist.ReduceOp.AVG)  # dW is column-major: .T is the contiguous view of the same memory
-            dist.all_reduce(db, op=dist.ReduceOp.AVG)
+        if dist is None:
+            dW, dx, db = pullback(dy)
+        else:
+            dW, dx, db = pullback(dy, on_param_grads=start_allreduce)
+            for h in pending:
+                h.wait()          # stream-level wait: the next step's work is ordered after the reduced gradients
+            pending.clear()
         return y, dW, dx, db
 
     def barrier():
@@ -233,10 +247,13 @@ def run_gpu_arm(args):
         fwd_ev[i][0].record()
         y, pullback = L.rrule_fused_dense(ACT, W, x, b)
         fwd_ev[i][1].record()
-        dW, dx, db = pullback(dy)
-        if dist is not None:
-            dist.all_reduce(dW.T, op=dist.ReduceOp.AVG)  # dW is column-major: .T is the contiguous view of the same memory
-            dist.all_reduce(db, op=dist.ReduceOp.AVG)
+        if dist is None:
+            dW, dx, db = pullback(dy)
+        else:
+            dW, dx, db = pullback(dy, on_param_grads=start_allreduce)
+            for h in pending:
+                h.wait()
+            pending.clear()
     e1.record()
     barrier()
     clocks = sampler.stop()
@@ -267,10 +284,13 @@ def run_gpu_arm(args):
         dxbuf.copy_(hx, non_blocking=True)
         dybuf.copy_(hdy, non_blocking=True)
         y, pullback = L.rrule_fused_dense(ACT, W, dxbuf.T, b)
-        dW, dx, db = pullback(dybuf.T)
-        if dist is not None:
-            dist.all_reduce(dW.T, op=dist.ReduceOp.AVG)  # dW is column-major: .T is the contiguous view of the same memory
-            dist.all_reduce(db, op=dist.ReduceOp.AVG)
+        if dist is None:
+            dW, dx, db = pullback(dybuf.T)
+        else:
+            dW, dx, db = pullback(dybuf.T, on_param_grads=start_allreduce)
+            for h in pending:
+                h.wait()
+            pending.clear()
         hy.copy_(y.T, non_blocking=True)
         hdW.copy_(dW.T, non_blocking=True)
         hdx.copy_(dx.T, non_blocking=True)
@@ -321,7 +341,7 @@ def run_gpu_arm(args):
             "clocks": clocks,
             "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_s * 1e3, "steps": e2e_steps},
-            "gpu_launches": 5 * args.steps,
+            "gpu_launches": 5 * args.steps,   # fwd GEMM, g = dy*act' (+db partials), db finish, dW GEMM, dX GEMM
             "roofline": roofline,
             "cpu_baseline": cpu,
             "pct_of_measured_peak": {"sustained": value / world / sustained, "burst": value / world / burst},

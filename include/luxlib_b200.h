@@ -71,6 +71,11 @@ typedef enum {
 /* ---- library ------------------------------------------------------------------------- */
 LB2_API int32_t lb2_version(void);
 LB2_API const char* lb2_status_string(int32_t status);
+/* Process-wide: the persistent tensor-core GEMM launches at most (SM count - n) CTAs, leaving n SMs
+ * free for a kernel that runs beside it — the NCCL all-reduce of parameter gradients that Lux's
+ * DistributedOptimizer issues (src/distributed/public_api.jl:275-278) can then overlap with the
+ * remaining backward GEMM. n = 0 (default) uses every SM. */
+LB2_API int32_t lb2_set_reserved_sms(int32_t n);
 /* Thread-local description of the last non-OK status returned on this thread. Mirrors the
  * 0 / -1 + warning convention of cublaslt_matmul_fused!
  * (lib/LuxLib/ext/CUDAExt/cublaslt.jl:184-185,292), without its fallback (:386-402). */

@@ -163,6 +163,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const uint64_t ad = ((uint64_t)p.a.desc_hi << 32) | (uint64_t)(a_lo32 + ks * p.a.k_advance);
             const uint64_t bd = ((uint64_t)p.b.desc_hi << 32) | (uint64_t)(b_lo32 + ks * p.b.k_advance);
             if (p.debug & 2u) continue;
+            if (p.debug & 32u) {  // experiment: alternate between the two accumulators (two independent chains)
+              umma<TF32>(tmem_base + ((ks & 1) ? BN : 0), ad, bd, p.idesc, 1u);
+              continue;
+            }
             umma<TF32>(d_tmem, ad, bd, p.idesc, (kb | ks) != 0 ? 1u : 0u);
             if constexpr (SPLIT3) {
               umma<TF32>(d_tmem, ad + LO_OFF, bd, p.idesc, 1u);  // lo(A) * hi(B)
@@ -536,6 +540,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             const uint64_t ad = ((uint64_t)p.a.desc_hi << 32) | (uint64_t)(a_lo32 + ks * p.a.k_advance);
             const uint64_t bd = ((uint64_t)p.b.desc_hi << 32) | (uint64_t)(b_lo32 + ks * p.b.k_advance);
             if (p.debug & 2u) continue;
+            if (p.debug & 32u) {
+              umma_pair<TF32>(tmem_base + ((ks & 1) ? BN : 0), ad, bd, p.idesc, 1u);
+              continue;
+            }
             umma_pair<TF32>(d_tmem, ad, bd, p.idesc, (kb | ks) != 0 ? 1u : 0u);
             if constexpr (SPLIT3) {
               umma_pair<TF32>(d_tmem, ad + LO_OFF, bd, p.idesc, 1u);
@@ -735,7 +743,7 @@ static int32_t tc_launch_cfg(const CUtensorMap& mA, const CUtensorMap& mB, const
                              const TcParams& p, cudaStream_t st) {
   using Cfg = TcCfg<BN, TF32, SPLIT3>;
   const int tiles = p.tiles_m * p.tiles_n;
-  const int grid = tiles < sm_count() ? tiles : sm_count();
+  const int grid = tiles < persistent_sm_budget() ? tiles : persistent_sm_budget();
   auto launch = [&](auto kernel) -> int32_t {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return fail(LB2_LAUNCH_FAIL, "gemm_tc: cannot reserve %d bytes of shared memory: %s", Cfg::SMEM_BYTES, cudaGetErrorString(e));

@@ -31,6 +31,7 @@ _fp = C.c_void_p  # float* passed as raw device pointers
 PROTOTYPES = {
     "lb2_version": (_i32, []),
     "lb2_status_string": (C.c_char_p, [_i32]),
+    "lb2_set_reserved_sms": (_i32, [_i32]),
     "lb2_last_error_string": (C.c_char_p, []),
     "lb2_poll_device_status": (_i32, [_p]),
     "lb2_act_fwd": (_i32, [_p, _p, _i64, _i32, _i32, _p]),

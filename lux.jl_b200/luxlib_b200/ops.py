@@ -133,7 +133,22 @@ def rrule_fused_dense(act: str, weight, x, b=None, *, flags: int = 0):
     y, pre, (W, ldw, X, ldx, bb, M, N, K, dt) = _dense_fwd(act, weight, x, b, keep_pre, flags)
     code = act_code(act)
 
-    def pullback(delta):
+    def pullback(delta, on_param_grads=None):
+        """Δ -> (∂weight, ∂x, ∂b). `on_param_grads(dW, db)`, when given, is called as soon as the
+        parameter gradients are enqueued and before ∂x is computed, so a data-parallel caller can
+        start their all-reduce underneath the remaining GEMM (same kernels, three C calls instead of one)."""
+        if on_param_grads is not None:
+            d = as_colmajor(delta.reshape(M, N).to(W.dtype))
+            g = jl_empty((M, N), W.dtype, W.device)
+            db = jl_empty((M,), W.dtype, W.device) if bb is not None else None
+            y2, pre2 = y.reshape(M, N), (None if pre is None else pre.reshape(M, N))
+            _, wsp, wsn = _ws(lib.lb2_bias_act_bwd_workspace_bytes(1, M, N), W.device)
+            _cabi.check(lib.lb2_bias_act_bwd(ptr(g), ptr(db), ptr(d), None if keep_pre else ptr(y2), ptr(pre2), 1, M, N, dt,
+                                             code, wsp, wsn, current_stream(W.device)))
+            dW = matmul(g, X, transB=True, flags=flags)      # g * x'
+            on_param_grads(dW, db)
+            dx = matmul(W, g, transA=True, flags=flags)      # W' * g
+            return dW, (dx.reshape(x.shape) if x.dim() == 1 else dx), db
         d = as_colmajor(delta.reshape(M, N).to(W.dtype))
         dW = jl_empty((M, K), W.dtype, W.device)
         dx = jl_empty((K, N), W.dtype, W.device)
