@@ -271,14 +271,12 @@ __global__ void __launch_bounds__(256) bn_apply_kernel(T* __restrict__ out, cons
     if constexpr (MODE == 2) {
       const float c0 = coef[c * 4], c1 = coef[c * 4 + 1], c2 = coef[c * 4 + 2];
       if constexpr (VEC) {
-        Vec16<T> xv = load16_stream(x + e), gv = load16_stream(dy + e), o;
-#pragma unroll
-        for (int j = 0; j < V; ++j) {
+        const Vec16<T> xv = load16_stream(x + e), gv = load16_stream(dy + e);
+        store16_stream(out + e, vec_from<T>([&](int j) {
           float d = gv.get(j);
           if constexpr (ACT != LB2_ACT_IDENTITY) d *= act_grad_pre_any<ACT, FAST>(act_rt, fmaf(xv.get(j), gp, bp));
-          o.set(j, fmaf(c0, d, fmaf(c1, xv.get(j), c2)));
-        }
-        store16_stream(out + e, o);
+          return fmaf(c0, d, fmaf(c1, xv.get(j), c2));
+        }));
       } else {
         const float xv = to_f32(x[e]);
         float d = to_f32(dy[e]);
@@ -287,10 +285,8 @@ __global__ void __launch_bounds__(256) bn_apply_kernel(T* __restrict__ out, cons
       }
     } else {
       if constexpr (VEC) {
-        Vec16<T> xv = load16_stream(x + e), o;
-#pragma unroll
-        for (int j = 0; j < V; ++j) o.set(j, act_apply_any<ACT, FAST>(act_rt, fmaf(xv.get(j), gp, bp)));
-        store16_stream(out + e, o);
+        const Vec16<T> xv = load16_stream(x + e);
+        store16_stream(out + e, vec_from<T>([&](int j) { return act_apply_any<ACT, FAST>(act_rt, fmaf(xv.get(j), gp, bp)); }));
       } else {
         out[e] = from_f32<T>(act_apply_any<ACT, FAST>(act_rt, fmaf(to_f32(x[e]), gp, bp)));
       }

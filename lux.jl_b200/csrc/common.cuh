@@ -50,25 +50,47 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(flo
 // 16-byte vector of T: 4 floats or 8 bf16.
 template <typename T> struct Vec16 {
   static constexpr int N = 16 / sizeof(T);
-  uint4 raw;
+  union {
+    uint4 raw;
+    uint32_t w[4];
+  };
+  __device__ __forceinline__ Vec16() {}
   __device__ __forceinline__ float get(int i) const {
     if constexpr (sizeof(T) == 4) {
-      return __uint_as_float((&raw.x)[i]);
+      return __uint_as_float(w[i]);
     } else {
-      uint32_t w = (&raw.x)[i >> 1];
-      return __uint_as_float((i & 1) ? (w & 0xFFFF0000u) : (w << 16));
+      const uint32_t u = w[i >> 1];
+      return __uint_as_float((i & 1) ? (u & 0xFFFF0000u) : (u << 16));
     }
   }
   __device__ __forceinline__ void set(int i, float v) {
     if constexpr (sizeof(T) == 4) {
-      (&raw.x)[i] = __float_as_uint(v);
+      w[i] = __float_as_uint(v);
     } else {
-      uint32_t h = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(v));
-      uint32_t& w = (&raw.x)[i >> 1];
-      w = (i & 1) ? ((w & 0x0000FFFFu) | (h << 16)) : ((w & 0xFFFF0000u) | h);
+      const uint32_t h = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(v));
+      uint32_t& u = w[i >> 1];
+      u = (i & 1) ? ((u & 0x0000FFFFu) | (h << 16)) : ((u & 0xFFFF0000u) | h);
+    }
+  }
+  // elements i (even) and i+1 at once: one packed conversion for bf16
+  __device__ __forceinline__ void set2(int i, float a, float b) {
+    if constexpr (sizeof(T) == 4) {
+      w[i] = __float_as_uint(a);
+      w[i + 1] = __float_as_uint(b);
+    } else {
+      uint32_t u;
+      asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(u) : "f"(b), "f"(a));
+      w[i >> 1] = u;
     }
   }
 };
+// builds a vector from f(j), j = 0..N-1, converting two elements per instruction for bf16
+template <typename T, typename F> __device__ __forceinline__ Vec16<T> vec_from(F&& f) {
+  Vec16<T> o;
+#pragma unroll
+  for (int j = 0; j < Vec16<T>::N; j += 2) o.set2(j, f(j), f(j + 1));
+  return o;
+}
 template <typename T> __device__ __forceinline__ Vec16<T> load16(const T* p) {
   Vec16<T> v;
   v.raw = *reinterpret_cast<const uint4*>(p);

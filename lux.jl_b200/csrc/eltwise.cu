@@ -27,10 +27,8 @@ __global__ void __launch_bounds__(256) bias_act_fwd_kernel(T* __restrict__ y, co
       // VEC is only selected when S % V == 0 (one channel per vector) or there is no bias
       float b = 0.f;
       if constexpr (HAS_BIAS) b = to_f32(bias[(e / S) % C]);
-      Vec16<T> v = load16_stream(x + e);
-#pragma unroll
-      for (int j = 0; j < V; ++j) v.set(j, act_apply<ACT, FAST>(v.get(j) + b));
-      store16_stream(y + e, v);
+      const Vec16<T> v = load16_stream(x + e);
+      store16_stream(y + e, vec_from<T>([&](int j) { return act_apply<ACT, FAST>(v.get(j) + b); }));
     } else {
       float b = 0.f;
       if constexpr (HAS_BIAS) b = to_f32(bias[(e / S) % C]);
@@ -55,11 +53,9 @@ __global__ void __launch_bounds__(256) bias_act_fwd_s1_kernel(T* __restrict__ y,
     const int64_t e = i * V;
     const int64_t c = e % C;  // C % V == 0 on the vector path
     if constexpr (VEC) {
-      Vec16<T> v = load16_stream(x + e);
-      Vec16<T> bv = load16(bias + c);
-#pragma unroll
-      for (int j = 0; j < V; ++j) v.set(j, act_apply<ACT, FAST>(v.get(j) + bv.get(j)));
-      store16_stream(y + e, v);
+      const Vec16<T> v = load16_stream(x + e);
+      const Vec16<T> bv = load16(bias + c);
+      store16_stream(y + e, vec_from<T>([&](int j) { return act_apply<ACT, FAST>(v.get(j) + bv.get(j)); }));
     } else {
       y[e] = from_f32<T>(act_apply<ACT, FAST>(to_f32(x[e]) + to_f32(bias[c])));
     }
@@ -125,8 +121,8 @@ __global__ void __launch_bounds__(256) act_bwd_s1_kernel(T* __restrict__ dx, flo
         Vec16<T> g = load16_stream(dy + b * ld_dy + c0);
         if constexpr (ACT != LB2_ACT_IDENTITY) {
           Vec16<T> r = load16_stream(ref + b * ld_ref + c0);
-#pragma unroll
-          for (int j = 0; j < V; ++j) g.set(j, g.get(j) * dact_sel<ACT, FAST, FROM_PRE>(r.get(j)));
+          const Vec16<T> g0 = g;
+          g = vec_from<T>([&](int j) { return g0.get(j) * dact_sel<ACT, FAST, FROM_PRE>(r.get(j)); });
         }
         if (dx) store16(dx + b * ld_dx + c0, g);
         if constexpr (WANT_SUM) {
@@ -178,8 +174,8 @@ __global__ void __launch_bounds__(256) act_bwd_kernel(T* __restrict__ dx, float*
       Vec16<T> g = load16_stream(dy + e);
       if constexpr (ACT != LB2_ACT_IDENTITY) {
         Vec16<T> r = load16_stream(ref + e);
-#pragma unroll
-        for (int j = 0; j < V; ++j) g.set(j, g.get(j) * dact_sel<ACT, FAST, FROM_PRE>(r.get(j)));
+        const Vec16<T> g0 = g;
+        g = vec_from<T>([&](int j) { return g0.get(j) * dact_sel<ACT, FAST, FROM_PRE>(r.get(j)); });
       }
       if (dx) store16(dx + e, g);
       if constexpr (WANT_SUM) {
@@ -213,9 +209,7 @@ __global__ void __launch_bounds__(256) act_bwd_flat_kernel(T* __restrict__ dx, c
     if constexpr (VEC) {
       Vec16<T> g = load16_stream(dy + e);
       Vec16<T> r = load16_stream(ref + e);
-#pragma unroll
-      for (int j = 0; j < V; ++j) g.set(j, g.get(j) * dact_sel<ACT, FAST, FROM_PRE>(r.get(j)));
-      store16_stream(dx + e, g);
+      store16_stream(dx + e, vec_from<T>([&](int j) { return g.get(j) * dact_sel<ACT, FAST, FROM_PRE>(r.get(j)); }));
     } else {
       dx[e] = from_f32<T>(to_f32(dy[e]) * dact_sel<ACT, FAST, FROM_PRE>(to_f32(ref[e])));
     }

@@ -11,7 +11,10 @@
 // cannot take. All cross-CTA reductions are two-stage in a fixed order: deterministic.
 //
 // Algorithmic bytes per element: forward 2*sizeof(T), backward 3*sizeof(T).
+#include <stdlib.h>
+
 #include "norm_common.cuh"
+#include "tc_ptx.cuh"
 
 namespace lb2 {
 
@@ -67,10 +70,7 @@ __global__ void __launch_bounds__(BT) gn_fwd_cached_kernel(T* __restrict__ y, fl
           gp = to_f32(gamma[c]) * inv;
           bp = to_f32(beta[c]) - mean * gp;
         }
-        Vec16<T> o;
-#pragma unroll
-        for (int j = 0; j < V; ++j) o.set(j, act_apply_any<ACT, FAST>(act_rt, fmaf(xv[k].get(j), gp, bp)));
-        store16_stream(yr + i, o);
+        store16_stream(yr + i, vec_from<T>([&](int j) { return act_apply_any<ACT, FAST>(act_rt, fmaf(xv[k].get(j), gp, bp)); }));
       }
     }
   }
@@ -202,13 +202,10 @@ __global__ void __launch_bounds__(BT) gn_bwd_cached_kernel(T* __restrict__ dx, f
       if (i < L) {
         float gm = 1.f;
         if constexpr (AFFINE) gm = to_f32(gamma[g * Cg + i / S]);
-        Vec16<T> o;
-#pragma unroll
-        for (int j = 0; j < V; ++j) {
+        store16_stream(dxr + i, vec_from<T>([&](int j) {
           const float xh = (xv[k].get(j) - mean) * inv;
-          o.set(j, inv * (dv[k][j] * gm - m1 - xh * m2));
-        }
-        store16_stream(dxr + i, o);
+          return inv * (dv[k][j] * gm - m1 - xh * m2);
+        }));
       }
     }
   }
@@ -289,6 +286,289 @@ __global__ void __launch_bounds__(512) gn_bwd_generic_kernel(T* __restrict__ dx,
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Streaming variants for rows of any length. A producer warp feeds fixed-size chunks of the row
+// through a shared-memory ring with 1-D bulk copies, several chunks (and rows) ahead of the 256
+// compute threads, once per pass over the row: the first pass comes from HBM, the repeats hit L2
+// (a CTA's row is at most a few hundred KB old). The copies never stop while the compute threads
+// sit in a reduction, and nothing is cached in registers, so two CTAs share an SM.
+// Forward: three passes (sum, centred squares, apply) - the same two-pass variance as the cached
+// kernel. Backward: two passes (per-channel sums, dx). Waits are time-bounded; a thread whose wait
+// expired stops touching the ring and all threads leave together after the next reduction.
+// ---------------------------------------------------------------------------------------------
+constexpr int kGnCompute = 256;
+constexpr int kGnThreads = kGnCompute + 32;
+constexpr int kGnVecsPerChunk = 2;                              // 16-byte vectors per thread per chunk
+constexpr uint32_t kGnChunkBytes = kGnCompute * 16 * kGnVecsPerChunk;  // 8 KB per tensor
+constexpr int kGnHeaderBytes = 1024;
+
+template <typename T, int ACT, bool AFFINE>
+__global__ void __launch_bounds__(kGnThreads, 2)
+gn_fwd_stream_kernel(T* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ inv_out,
+                     const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta, uint32_t S,
+                     uint32_t Cg, uint32_t G, int64_t rows, float eps, int act_rt, int stages, unsigned int* status) {
+  constexpr bool FAST = sizeof(T) == 2;
+  constexpr int V = Vec16<T>::N;
+  constexpr uint32_t CE = kGnChunkBytes / sizeof(T);  // elements per chunk
+  extern __shared__ __align__(1024) uint8_t gn_smem[];
+  uint64_t* full = reinterpret_cast<uint64_t*>(gn_smem);
+  uint64_t* empty = full + stages;
+  float* red = reinterpret_cast<float*>(gn_smem + 256);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gn_smem + 768);
+  uint8_t* data = gn_smem + kGnHeaderBytes;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, t = threadIdx.x;
+  const uint32_t L = S * Cg;
+  const uint32_t nchunks = (L + CE - 1) / CE;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], kGnCompute / 32); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  const int64_t nrows = blockIdx.x < rows ? (rows - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  if (warp == kGnCompute / 32) {
+    if (lane == 0) {
+      uint32_t st = 0, ph = 0;
+      for (int64_t r = 0; r < nrows; ++r) {
+        const T* xr = x + (blockIdx.x + r * gridDim.x) * (int64_t)L;
+        for (int pass = 0; pass < 3; ++pass) {
+          for (uint32_t c = 0; c < nchunks; ++c) {
+            if (!mbar_wait(&empty[st], ph ^ 1u, status, 0x2000000u)) return;
+            const uint32_t left = (L - c * CE) * (uint32_t)sizeof(T);
+            const uint32_t bytes = left < kGnChunkBytes ? left : kGnChunkBytes;
+            mbar_expect_tx(&full[st], bytes);
+            bulk_load_1d(smem_u32(data + (size_t)st * kGnChunkBytes), xr + (size_t)c * CE, bytes, &full[st]);
+            if (++st == (uint32_t)stages) { st = 0; ph ^= 1u; }
+          }
+        }
+      }
+    }
+    return;
+  }
+  const float invL = 1.f / (float)L;
+  uint32_t st = 0, ph = 0;
+  bool dead = false;
+  // one pass over the row's chunks; body(vector, element offset in row)
+  auto sweep = [&](auto&& body) {
+    for (uint32_t c = 0; c < nchunks; ++c) {
+      if (!dead && !mbar_wait_warp(&full[st], ph, status, 0x4000000u)) { dead = true; *abort_flag = 1; }
+      if (!dead) {
+        const T* sx = reinterpret_cast<const T*>(data + (size_t)st * kGnChunkBytes);
+#pragma unroll
+        for (int k = 0; k < kGnVecsPerChunk; ++k) {
+          const uint32_t off = (uint32_t)(k * kGnCompute + t) * V;
+          const uint32_t i = c * CE + off;
+          if (i < L) body(load16(sx + off), i);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[st]);
+      }
+      if (++st == (uint32_t)stages) { st = 0; ph ^= 1u; }
+    }
+  };
+  for (int64_t r = 0; r < nrows; ++r) {
+    const int64_t row = blockIdx.x + r * gridDim.x;
+    const uint32_t g = (uint32_t)(row % G);
+    float s = 0.f;
+    sweep([&](const Vec16<T>& v, uint32_t) {
+#pragma unroll
+      for (int j = 0; j < V; ++j) s += v.get(j);
+    });
+    const float mean = group_sum(s, red, kGnCompute) * invL;
+    if (*abort_flag) break;
+    float q = 0.f;
+    sweep([&](const Vec16<T>& v, uint32_t) {
+#pragma unroll
+      for (int j = 0; j < V; ++j) { const float d = v.get(j) - mean; q = fmaf(d, d, q); }
+    });
+    const float var = group_sum(q, red, kGnCompute) * invL;
+    if (*abort_flag) break;
+    const float inv = 1.f / sqrtf(var + eps);
+    if (t == 0) { mean_out[row] = mean; inv_out[row] = inv; }
+    T* yr = y + row * (int64_t)L;
+    sweep([&](const Vec16<T>& v, uint32_t i) {
+      float gp = inv, bp = -mean * inv;
+      if constexpr (AFFINE) {  // S % V == 0: one channel per vector
+        const uint32_t c = g * Cg + i / S;
+        gp = to_f32(gamma[c]) * inv;
+        bp = to_f32(beta[c]) - mean * gp;
+      }
+      store16_stream(yr + i, vec_from<T>([&](int j) { return act_apply_any<ACT, FAST>(act_rt, fmaf(v.get(j), gp, bp)); }));
+    });
+  }
+}
+
+// Backward; shared memory after the header: ds[Cg], db[Cg], slots[2][nslots] (one slot per
+// warp-wide vector row of the group, in element order), then the ring (x chunk + dy chunk per stage).
+template <typename T, int ACT, bool AFFINE>
+__global__ void __launch_bounds__(kGnThreads, 2)
+gn_bwd_stream_kernel(T* __restrict__ dx, float* __restrict__ chan_out, const T* __restrict__ dy,
+                     const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
+                     const float* __restrict__ mean_in, const float* __restrict__ inv_in, uint32_t S, uint32_t Cg,
+                     uint32_t G, int64_t rows, int act_rt, int stages, uint32_t aux_bytes, unsigned int* status) {
+  constexpr bool FAST = sizeof(T) == 2;
+  constexpr int V = Vec16<T>::N;
+  constexpr uint32_t CE = kGnChunkBytes / sizeof(T);
+  constexpr uint32_t kSlotsPerChunk = kGnVecsPerChunk * (kGnCompute / 32);
+  extern __shared__ __align__(1024) uint8_t gn_smem[];
+  uint64_t* full = reinterpret_cast<uint64_t*>(gn_smem);
+  uint64_t* empty = full + stages;
+  float* red = reinterpret_cast<float*>(gn_smem + 256);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gn_smem + 768);
+  const uint32_t L = S * Cg;
+  const uint32_t nslots = L / (32 * V);
+  float* ds = reinterpret_cast<float*>(gn_smem + kGnHeaderBytes);
+  float* dbs = ds + Cg;
+  float* slot_a = dbs + Cg;
+  float* slot_b = slot_a + nslots;
+  uint8_t* data = gn_smem + kGnHeaderBytes + aux_bytes;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, t = threadIdx.x;
+  const uint32_t nchunks = (L + CE - 1) / CE;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], kGnCompute / 32); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  const int64_t nrows = blockIdx.x < rows ? (rows - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  if (warp == kGnCompute / 32) {
+    if (lane == 0) {
+      uint32_t st = 0, ph = 0;
+      for (int64_t r = 0; r < nrows; ++r) {
+        const int64_t base = (blockIdx.x + r * gridDim.x) * (int64_t)L;
+        for (int pass = 0; pass < 2; ++pass) {
+          for (uint32_t c = 0; c < nchunks; ++c) {
+            if (!mbar_wait(&empty[st], ph ^ 1u, status, 0x8000000u)) return;
+            const uint32_t left = (L - c * CE) * (uint32_t)sizeof(T);
+            const uint32_t bytes = left < kGnChunkBytes ? left : kGnChunkBytes;
+            uint8_t* dst = data + (size_t)st * 2 * kGnChunkBytes;
+            mbar_expect_tx(&full[st], 2 * bytes);
+            bulk_load_1d(smem_u32(dst), x + base + (size_t)c * CE, bytes, &full[st]);
+            bulk_load_1d(smem_u32(dst + kGnChunkBytes), dy + base + (size_t)c * CE, bytes, &full[st]);
+            if (++st == (uint32_t)stages) { st = 0; ph ^= 1u; }
+          }
+        }
+      }
+    }
+    return;
+  }
+  const float invL = 1.f / (float)L;
+  const uint32_t slots_per_chan = S / (32 * V);
+  uint32_t st = 0, ph = 0;
+  bool dead = false;
+  for (int64_t r = 0; r < nrows; ++r) {
+    const int64_t row = blockIdx.x + r * gridDim.x;
+    const uint32_t g = (uint32_t)(row % G);
+    const int64_t n = row / G;
+    const float mean = mean_in[row], inv = inv_in[row];
+    // d = dy * act'(pre) for one vector; xh = normalised input
+    auto d_of = [&](const Vec16<T>& xv, const Vec16<T>& gy, uint32_t i, int j) {
+      float d = gy.get(j);
+      if constexpr (ACT != LB2_ACT_IDENTITY) {
+        float gp = inv, bp = -mean * inv;
+        if constexpr (AFFINE) {
+          const uint32_t c = g * Cg + i / S;
+          gp = to_f32(gamma[c]) * inv;
+          bp = to_f32(beta[c]) - mean * gp;
+        }
+        d *= act_grad_pre_any<ACT, FAST>(act_rt, fmaf(xv.get(j), gp, bp));
+      }
+      return d;
+    };
+    // pass 1: one (sum d*xh, sum d) pair per warp-wide vector row
+    for (uint32_t c = 0; c < nchunks; ++c) {
+      if (!dead && !mbar_wait_warp(&full[st], ph, status, 0x10000000u)) { dead = true; *abort_flag = 1; }
+      const T* sx = reinterpret_cast<const T*>(data + (size_t)st * 2 * kGnChunkBytes);
+      const T* sdy = reinterpret_cast<const T*>(data + (size_t)st * 2 * kGnChunkBytes + kGnChunkBytes);
+#pragma unroll
+      for (int k = 0; k < kGnVecsPerChunk; ++k) {
+        const uint32_t off = (uint32_t)(k * kGnCompute + t) * V;
+        const uint32_t i = c * CE + off;
+        float a = 0.f, b = 0.f;
+        if (!dead && i < L) {
+          const Vec16<T> xv = load16(sx + off), gy = load16(sdy + off);
+#pragma unroll
+          for (int j = 0; j < V; ++j) {
+            const float d = d_of(xv, gy, i, j);
+            a = fmaf(d, (xv.get(j) - mean) * inv, a);
+            b += d;
+          }
+        }
+        a = warp_sum(a);
+        b = warp_sum(b);
+        const uint32_t sl = c * kSlotsPerChunk + (uint32_t)(k * (kGnCompute / 32) + warp);
+        if (lane == 0 && sl < nslots) { slot_a[sl] = a; slot_b[sl] = b; }
+      }
+      if (!dead) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[st]);
+      }
+      if (++st == (uint32_t)stages) { st = 0; ph ^= 1u; }
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(kGnCompute) : "memory");
+    // channel j owns slots_per_chan consecutive slots
+    for (uint32_t j = t; j < Cg; j += kGnCompute) {
+      float a = 0.f, b = 0.f;
+      const uint32_t first = j * slots_per_chan;
+      for (uint32_t q = 0; q < slots_per_chan; ++q) { a += slot_a[first + q]; b += slot_b[first + q]; }
+      ds[j] = a;
+      dbs[j] = b;
+      if constexpr (AFFINE) {
+        float* co = chan_out + ((n * ((int64_t)G * Cg)) + (int64_t)g * Cg + j) * 2;
+        co[0] = a;
+        co[1] = b;
+      }
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(kGnCompute) : "memory");
+    float s1 = 0.f, s2 = 0.f;
+    for (uint32_t j = t; j < Cg; j += kGnCompute) {
+      float gm = 1.f;
+      if constexpr (AFFINE) gm = to_f32(gamma[g * Cg + j]);
+      s1 = fmaf(gm, dbs[j], s1);
+      s2 = fmaf(gm, ds[j], s2);
+    }
+    const float2 m12 = group_sum2(s1, s2, red, kGnCompute);
+    if (*abort_flag) break;
+    const float m1 = m12.x * invL, m2 = m12.y * invL;
+    T* dxr = dx + row * (int64_t)L;
+    // pass 2: dx = inv * (d*gamma - m1 - xh*m2)
+    for (uint32_t c = 0; c < nchunks; ++c) {
+      if (!dead && !mbar_wait_warp(&full[st], ph, status, 0x20000000u)) { dead = true; *abort_flag = 1; }
+      if (!dead) {
+        const T* sx = reinterpret_cast<const T*>(data + (size_t)st * 2 * kGnChunkBytes);
+        const T* sdy = reinterpret_cast<const T*>(data + (size_t)st * 2 * kGnChunkBytes + kGnChunkBytes);
+#pragma unroll
+        for (int k = 0; k < kGnVecsPerChunk; ++k) {
+          const uint32_t off = (uint32_t)(k * kGnCompute + t) * V;
+          const uint32_t i = c * CE + off;
+          if (i < L) {
+            const Vec16<T> xv = load16(sx + off), gy = load16(sdy + off);
+            float gm = 1.f;
+            if constexpr (AFFINE) gm = to_f32(gamma[g * Cg + i / S]);
+            store16_stream(dxr + i, vec_from<T>([&](int j) {
+              const float xh = (xv.get(j) - mean) * inv;
+              return inv * (d_of(xv, gy, i, j) * gm - m1 - xh * m2);
+            }));
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[st]);
+      }
+      if (++st == (uint32_t)stages) { st = 0; ph ^= 1u; }
+    }
+  }
+}
+
+// Experiment switch: environment variable LB2_GN_STREAM, bit 0 = forward, bit 1 = backward
+// streaming kernels allowed (default: backward only; the cached forward is faster wherever it applies).
+static int gn_stream_mask() {
+  static const int m = [] {
+    const char* e = getenv("LB2_GN_STREAM");
+    return e ? atoi(e) : 2;
+  }();
+  return m;
+}
+
 // dgamma[c] = sum_n chan[n][c][0], dbeta[c] = sum_n chan[n][c][1]   (n ascending)
 template <typename T>
 __global__ void gn_finish_kernel(T* __restrict__ dgamma, T* __restrict__ dbeta, const float* __restrict__ chan,
@@ -313,7 +593,17 @@ static int32_t gn_fwd_launch(T* y, float* sm, float* si, const T* x, const T* g,
   const int sms = sm_count();
   const int64_t vecs = L / V;
   int grid = (int)(rows < (int64_t)sms * 4 ? rows : (int64_t)sms * 4);
-  if (al && vecs <= 256 * 8) {
+  const bool fits32 = L < (int64_t)1 << 31 && G < (int64_t)1 << 31;
+  if ((gn_stream_mask() & 1) && al && fits32 && L * (int64_t)sizeof(T) >= 2 * (int64_t)kGnChunkBytes) {
+    unsigned int* status = device_status_word();
+    LB2_REQUIRE(status != nullptr, LB2_LAUNCH_FAIL, "groupnorm: device status word unavailable");
+    const int stages = 12;
+    const int smem = kGnHeaderBytes + stages * (int)kGnChunkBytes;
+    cudaError_t e = cudaFuncSetAttribute(gn_fwd_stream_kernel<T, ACT, AFFINE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    LB2_REQUIRE(e == cudaSuccess, LB2_LAUNCH_FAIL, "groupnorm: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    grid = (int)(rows < (int64_t)sms * 2 ? rows : (int64_t)sms * 2);
+    gn_fwd_stream_kernel<T, ACT, AFFINE><<<grid, kGnThreads, smem, st>>>(y, sm, si, x, g, b, (uint32_t)S, (uint32_t)Cg, (uint32_t)G, rows, eps, act, stages, status);
+  } else if (al && vecs <= 256 * 8) {
     const int nv = vecs <= 256 ? 1 : (vecs <= 512 ? 2 : (vecs <= 1024 ? 4 : 8));
     if (nv == 1) gn_fwd_cached_kernel<T, ACT, AFFINE, 1, 256><<<grid, 256, 0, st>>>(y, sm, si, x, g, b, S, Cg, G, rows, eps, act);
     else if (nv == 2) gn_fwd_cached_kernel<T, ACT, AFFINE, 2, 256><<<grid, 256, 0, st>>>(y, sm, si, x, g, b, S, Cg, G, rows, eps, act);
@@ -343,7 +633,19 @@ static int32_t gn_bwd_launch(T* dx, T* dg, T* db, const T* dy, const T* x, const
   const int sms = sm_count();
   const int64_t vecs = L / V;
   int grid = (int)(rows < (int64_t)sms * 2 ? rows : (int64_t)sms * 2);
-  if (al && vecs <= 512 * 4) {
+  const bool fits32 = L < (int64_t)1 << 31 && G < (int64_t)1 << 31;
+  const size_t aux = align_up((size_t)(2 * Cg + 2 * (L / (32 * V))) * sizeof(float), 128);
+  if ((gn_stream_mask() & 2) && al && fits32 && aux <= 64 * 1024 && L * (int64_t)sizeof(T) >= 2 * (int64_t)kGnChunkBytes) {
+    unsigned int* status = device_status_word();
+    LB2_REQUIRE(status != nullptr, LB2_LAUNCH_FAIL, "groupnorm: device status word unavailable");
+    const int stages = 6;
+    const int smem = kGnHeaderBytes + (int)aux + stages * 2 * (int)kGnChunkBytes;
+    cudaError_t e = cudaFuncSetAttribute(gn_bwd_stream_kernel<T, ACT, AFFINE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    LB2_REQUIRE(e == cudaSuccess, LB2_LAUNCH_FAIL, "groupnorm: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    const int per_sm = smem <= 112 * 1024 ? 2 : 1;
+    grid = (int)(rows < (int64_t)sms * per_sm ? rows : (int64_t)sms * per_sm);
+    gn_bwd_stream_kernel<T, ACT, AFFINE><<<grid, kGnThreads, smem, st>>>(dx, ws, dy, x, g, b, sm, si, (uint32_t)S, (uint32_t)Cg, (uint32_t)G, rows, act, stages, (uint32_t)aux, status);
+  } else if (al && vecs <= 512 * 4) {
     const int nv = vecs <= 512 ? 1 : (vecs <= 1024 ? 2 : 4);
     if (nv == 1) gn_bwd_cached_kernel<T, ACT, AFFINE, 1, 512><<<grid, 512, dyn, st>>>(dx, ws, dy, x, g, b, sm, si, S, Cg, G, rows, act);
     else if (nv == 2) gn_bwd_cached_kernel<T, ACT, AFFINE, 2, 512><<<grid, 512, dyn, st>>>(dx, ws, dy, x, g, b, sm, si, S, Cg, G, rows, act);

@@ -70,14 +70,11 @@ __global__ void __launch_bounds__(BT) ln_fwd_cached_kernel(T* __restrict__ y, fl
     for (int k = 0; k < NV; ++k) {
       const int64_t i = ((int64_t)k * RT + t) * V;
       if (i < D) {
-        Vec16<T> o;
-#pragma unroll
-        for (int j = 0; j < V; ++j) {
+        store16_stream(yr + i, vec_from<T>([&](int j) {
           float gp = inv, bp = -mean * inv;
           if constexpr (AFFINE) { gp = gv[k].get(j) * inv; bp = bv[k].get(j) - mean * gp; }
-          o.set(j, act_apply_any<ACT, FAST>(act_rt, fmaf(xv[k].get(j), gp, bp)));
-        }
-        store16_stream(yr + i, o);
+          return act_apply_any<ACT, FAST>(act_rt, fmaf(xv[k].get(j), gp, bp));
+        }));
       }
     }
   }
@@ -178,21 +175,18 @@ ln_fwd_ring_kernel(T* __restrict__ y, float* __restrict__ mean_out, float* __res
     for (int k = 0; k < NV; ++k) {
       const int64_t i = ((int64_t)k * kRingCompute + t) * V;
       if (i < D) {
-        Vec16<T> o;
-#pragma unroll
-        for (int j = 0; j < V; ++j) {
+        store16_stream(yr + i, vec_from<T>([&](int j) {
           float gp = inv, bp = -mean * inv;
           if constexpr (AFFINE) { gp = gv[k].get(j) * inv; bp = bv[k].get(j) - mean * gp; }
-          o.set(j, act_apply_any<ACT, FAST>(act_rt, fmaf(xv[k].get(j), gp, bp)));
-        }
-        store16_stream(yr + i, o);
+          return act_apply_any<ACT, FAST>(act_rt, fmaf(xv[k].get(j), gp, bp));
+        }));
       }
     }
   }
 }
 
 template <typename T, int ACT, bool AFFINE, int NV>
-__global__ void __launch_bounds__(kRingThreads)
+__global__ void __launch_bounds__(kRingThreads, (NV * Vec16<T>::N <= 16) ? 2 : 1)
 ln_bwd_ring_kernel(T* __restrict__ dx, float* __restrict__ partial, const T* __restrict__ dy, const T* __restrict__ x,
                    const T* __restrict__ gamma, const T* __restrict__ beta, const float* __restrict__ mean_in,
                    const float* __restrict__ inv_in, int64_t D, int64_t R, int act_rt, int stages, unsigned int* status) {
@@ -247,58 +241,62 @@ ln_bwd_ring_kernel(T* __restrict__ dx, float* __restrict__ partial, const T* __r
     if (!mbar_wait_warp(&full[st], ph, status, 0x1000000u)) *abort_flag = 1;
     const T* sx = reinterpret_cast<const T*>(data + (size_t)st * 2 * row_bytes);
     const T* sdy = reinterpret_cast<const T*>(data + (size_t)st * 2 * row_bytes + row_bytes);
-    Vec16<T> xv[NV], gy[NV];
-#pragma unroll
-    for (int k = 0; k < NV; ++k) {
-      const int64_t i = ((int64_t)k * kRingCompute + t) * V;
-      if (i < D) { xv[k] = load16(sx + i); gy[k] = load16(sdy + i); }
-    }
-    __syncwarp();
-    if (lane == 0) mbar_arrive(&empty[st]);
-    float gf[NV][V];
+    // The row stays in its ring stage through both passes (registers hold only the dgamma/dbeta
+    // accumulators), so two CTAs fit on an SM and one reduces while the other streams.
+    const float nmi = -mean * inv;
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
       const int64_t i = ((int64_t)k * kRingCompute + t) * V;
       if (i < D) {
+        const Vec16<T> xv = load16(sx + i), gy = load16(sdy + i);
 #pragma unroll
         for (int j = 0; j < V; ++j) {
-          const float xh = (xv[k].get(j) - mean) * inv;
-          float d = gy[k].get(j);
+          const float xh = (xv.get(j) - mean) * inv;
+          float d = gy.get(j);
           if constexpr (ACT != LB2_ACT_IDENTITY) {
-            float gp = inv, bp = -mean * inv;
+            float gp = inv, bp = nmi;
             if constexpr (AFFINE) { gp = gv[k].get(j) * inv; bp = bv[k].get(j) - mean * gp; }
-            d *= act_grad_pre_any<ACT, FAST>(act_rt, fmaf(xv[k].get(j), gp, bp));
+            d *= act_grad_pre_any<ACT, FAST>(act_rt, fmaf(xv.get(j), gp, bp));
           }
           float g = d;
           if constexpr (AFFINE) {
-            adg[k][j] += d * xh;
+            adg[k][j] = fmaf(d, xh, adg[k][j]);
             adb[k][j] += d;
             g = d * gv[k].get(j);
           }
-          gf[k][j] = g;
           s1 += g;
-          s2 += g * xh;
+          s2 = fmaf(g, xh, s2);
         }
       }
     }
     const float2 m12 = group_sum2(s1, s2, red, kRingCompute);
     if (*abort_flag) break;
     const float m1 = m12.x * invD, m2 = m12.y * invD;
+    // dx = inv * (g - m1 - xh * m2)
+    const float c0 = -inv * m1, c1 = -inv * m2;
     T* dxr = dx + row * D;
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
       const int64_t i = ((int64_t)k * kRingCompute + t) * V;
       if (i < D) {
-        Vec16<T> o;
-#pragma unroll
-        for (int j = 0; j < V; ++j) {
-          const float xh = (xv[k].get(j) - mean) * inv;
-          o.set(j, inv * (gf[k][j] - m1 - xh * m2));
-        }
-        store16_stream(dxr + i, o);
+        const Vec16<T> xv = load16(sx + i), gy = load16(sdy + i);
+        store16_stream(dxr + i, vec_from<T>([&](int j) {
+          const float xh = (xv.get(j) - mean) * inv;
+          float d = gy.get(j);
+          if constexpr (ACT != LB2_ACT_IDENTITY) {
+            float gp = inv, bp = nmi;
+            if constexpr (AFFINE) { gp = gv[k].get(j) * inv; bp = bv[k].get(j) - mean * gp; }
+            d *= act_grad_pre_any<ACT, FAST>(act_rt, fmaf(xv.get(j), gp, bp));
+          }
+          float gi = d * inv;
+          if constexpr (AFFINE) gi *= gv[k].get(j);
+          return fmaf(xh, c1, gi + c0);
+        }));
       }
     }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty[st]);
   }
   if constexpr (AFFINE) {
     float* pg = partial + (int64_t)blockIdx.x * 2 * D;
@@ -408,13 +406,10 @@ __global__ void __launch_bounds__(BT) ln_bwd_cached_kernel(T* __restrict__ dx, f
     for (int k = 0; k < NV; ++k) {
       const int64_t i = ((int64_t)k * RT + t) * V;
       if (i < D) {
-        Vec16<T> o;
-#pragma unroll
-        for (int j = 0; j < V; ++j) {
+        store16_stream(dxr + i, vec_from<T>([&](int j) {
           const float xh = (xv[k].get(j) - mean) * inv;
-          o.set(j, inv * (gf[k][j] - m1 - xh * m2));
-        }
-        store16_stream(dxr + i, o);
+          return inv * (gf[k][j] - m1 - xh * m2);
+        }));
       }
     }
   }

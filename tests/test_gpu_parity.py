@@ -337,7 +337,10 @@ def test_batchnorm_inference(dt):
 @pytest.mark.parametrize("dt", ["f32", "bf16"])
 @pytest.mark.parametrize("act", ["identity", "relu", "gelu"])
 @pytest.mark.parametrize("shape,groups", [((6, 2), 2), ((4, 4, 6, 2), 3), ((2, 2, 6, 2), 2), ((16, 16, 32, 4), 4),
-                                          ((32, 32, 16, 3), 2), ((8, 128, 64, 2), 4), ((7, 3, 10, 2), 5)])
+                                          ((32, 32, 16, 3), 2), ((8, 128, 64, 2), 4), ((7, 3, 10, 2), 5),
+                                          # rows streamed in chunks: ragged last chunk, forward-only eligibility,
+                                          # more rows than resident CTAs
+                                          ((16, 16, 80, 2), 2), ((6, 6, 256, 2), 2), ((32, 32, 32, 40), 8)])
 @pytest.mark.parametrize("affine", [True, False])
 def test_groupnorm_fwd_bwd(dt, act, shape, groups, affine):
     rng = np.random.default_rng(17)
