@@ -43,9 +43,9 @@ def flops_per_step() -> float:
 
 def make_inputs(seed: int, n_cols: int):
     """Seeded synthetic inputs with the reference initialisers' distributions."""
-    from oracle import luxlib_oracle as O
     rng = np.random.default_rng(seed)
-    W = O.glorot_uniform(rng, (M, K))
+    # glorot_uniform (lib/WeightInitializers/src/initializers.jl:28-36): (rand - 0.5) * sqrt(24 / (fan_in + fan_out))
+    W = ((rng.random((M, K), dtype=np.float64) - 0.5) * np.sqrt(24.0 / (M + K))).astype(np.float32)
     x = rng.standard_normal((K, n_cols), dtype=np.float32)
     b = rng.uniform(-0.1, 0.1, M).astype(np.float32)
     dy = rng.standard_normal((M, n_cols), dtype=np.float32)
@@ -370,7 +370,6 @@ def run_secondary(args):
     TFLOP/s (3 x 2*Wo*Ho*N*Cout*Cin*kW*kH per step) against the measured bf16 tensor peak."""
     import torch
     import luxlib_b200 as L
-    from oracle import luxlib_oracle as O
     torch.cuda.set_device(0)
     tdt = torch.float32 if args.dtype == "f32" else torch.bfloat16
     es = 4 if args.dtype == "f32" else 2

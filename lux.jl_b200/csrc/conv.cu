@@ -49,7 +49,7 @@ ConvBwdLayout conv_bwd_layout(const ConvGeom& g, int32_t dtype, int32_t act) {
   if (n <= 0) return l;
   l.g_bytes = act == LB2_ACT_IDENTITY ? 0 : align_up((size_t)n * dtype_size(dtype), 1024);
   l.red_bytes = align_up(act_bwd_workspace_bytes(y_spatial(g), g.cout, g.batch), 1024);
-  l.tc_bytes = conv_tc_supported(g, dtype) ? conv_tc_bwd_workspace_bytes(g) : 0;
+  l.tc_bytes = conv_tc_supported(g, dtype) ? conv_tc_bwd_workspace_bytes(g, dtype) : 0;
   return l;
 }
 
@@ -69,7 +69,7 @@ int32_t lb2_conv_output_size(const lb2_conv_desc* d, int32_t* out) {
 size_t lb2_conv_fwd_workspace_bytes(const lb2_conv_desc* d, int32_t dtype) {
   ConvGeom g;
   if (!valid_dtype(dtype) || make_geom(d, &g) != LB2_OK || y_numel(g) == 0) return 0;
-  return conv_tc_supported(g, dtype) ? conv_tc_fwd_workspace_bytes(g) : 0;
+  return conv_tc_supported(g, dtype) ? conv_tc_fwd_workspace_bytes(g, dtype) : 0;
 }
 
 int32_t lb2_conv_fwd(void* y, void* preact, const void* x, const void* w, const void* b, const lb2_conv_desc* d,
@@ -86,10 +86,10 @@ int32_t lb2_conv_fwd(void* y, void* preact, const void* x, const void* w, const 
   LB2_REQUIRE(aligned_to(y, es) && aligned_to(preact, es) && aligned_to(x, es) && aligned_to(w, es) && aligned_to(b, es),
               LB2_BAD_ALIGN, "pointer not aligned to the element size");
   if (!(flags & LB2_FLAG_FORCE_SIMT) && conv_tc_supported(g, dtype)) {
-    const size_t need = conv_tc_fwd_workspace_bytes(g);
+    const size_t need = conv_tc_fwd_workspace_bytes(g, dtype);
     LB2_REQUIRE(workspace != nullptr && workspace_bytes >= need, LB2_WORKSPACE_TOO_SMALL, "workspace of %zu bytes needed", need);
     LB2_REQUIRE(aligned_to(workspace, 256) && aligned_to(x, 16) && aligned_to(y, 2), LB2_BAD_ALIGN, "workspace must be 256-byte aligned");
-    return conv_tc_fwd(y, preact, x, w, b, g, act, workspace, static_cast<cudaStream_t>(stream));
+    return conv_tc_fwd(y, preact, x, w, b, g, dtype, act, workspace, static_cast<cudaStream_t>(stream));
   }
   return conv_fwd_direct(y, preact, x, w, b, g, dtype, act, static_cast<cudaStream_t>(stream));
 }
@@ -142,11 +142,11 @@ int32_t lb2_conv_bwd(void* dw, void* dx, void* db, const void* dy, const void* o
   const bool tc = !(flags & LB2_FLAG_FORCE_SIMT) && lay.tc_bytes > 0 && aligned_to(gptr, 16) && aligned_to(x, 16);
   void* tc_ws = ws + lay.g_bytes + lay.red_bytes;
   if (dw) {
-    rc = tc ? conv_tc_wgrad(dw, x, gptr, g, tc_ws, st) : conv_wgrad_direct(dw, x, gptr, g, dtype, st);
+    rc = tc ? conv_tc_wgrad(dw, x, gptr, g, dtype, tc_ws, st) : conv_wgrad_direct(dw, x, gptr, g, dtype, st);
     if (rc != LB2_OK) return rc;
   }
   if (dx && nx > 0) {
-    rc = tc ? conv_tc_dgrad(dx, gptr, w, g, tc_ws, st) : conv_dgrad_direct(dx, gptr, w, g, dtype, st);
+    rc = tc ? conv_tc_dgrad(dx, gptr, w, g, dtype, tc_ws, st) : conv_dgrad_direct(dx, gptr, w, g, dtype, st);
     if (rc != LB2_OK) return rc;
   }
   return LB2_OK;

@@ -15,13 +15,22 @@ int32_t conv_fwd_direct(void* y, void* preact, const void* x, const void* w, con
 int32_t conv_dgrad_direct(void* dx, const void* dy, const void* w, const ConvGeom& g, int32_t dtype, cudaStream_t st);
 int32_t conv_wgrad_direct(void* dw, const void* x, const void* dy, const ConvGeom& g, int32_t dtype, cudaStream_t st);
 
-// Tensor-core implicit-GEMM path (bf16; 2-D, stride 1, dilation 1, groups 1, output width == input width).
+// Tensor-core implicit-GEMM path (2-D, stride 1, dilation 1, groups 1, output width == input width);
+// bf16 in conv_tc.cu, Float32 (split tf32 with register accumulation) in conv_tc_f32.cu.
 bool conv_tc_supported(const ConvGeom& g, int32_t dtype);
-size_t conv_tc_fwd_workspace_bytes(const ConvGeom& g);
-size_t conv_tc_bwd_workspace_bytes(const ConvGeom& g);
+size_t conv_tc_fwd_workspace_bytes(const ConvGeom& g, int32_t dtype);
+size_t conv_tc_bwd_workspace_bytes(const ConvGeom& g, int32_t dtype);
 int32_t conv_tc_fwd(void* y, void* preact, const void* x, const void* w, const void* bias, const ConvGeom& g,
-                    int32_t act, void* ws, cudaStream_t st);
-int32_t conv_tc_dgrad(void* dx, const void* gy, const void* w, const ConvGeom& g, void* ws, cudaStream_t st);
-int32_t conv_tc_wgrad(void* dw, const void* x, const void* gy, const ConvGeom& g, void* ws, cudaStream_t st);
+                    int32_t dtype, int32_t act, void* ws, cudaStream_t st);
+int32_t conv_tc_dgrad(void* dx, const void* gy, const void* w, const ConvGeom& g, int32_t dtype, void* ws, cudaStream_t st);
+int32_t conv_tc_wgrad(void* dw, const void* x, const void* gy, const ConvGeom& g, int32_t dtype, void* ws, cudaStream_t st);
+
+bool conv_tc_f32_supported(const ConvGeom& g);
+size_t conv_tc_f32_fwd_workspace_bytes(const ConvGeom& g);
+size_t conv_tc_f32_bwd_workspace_bytes(const ConvGeom& g);
+int32_t conv_tc_f32_fwd(void* y, void* preact, const void* x, const void* w, const void* bias, const ConvGeom& g,
+                        int32_t act, void* ws, cudaStream_t st);
+int32_t conv_tc_f32_dgrad(void* dx, const void* gy, const void* w, const ConvGeom& g, void* ws, cudaStream_t st);
+int32_t conv_tc_f32_wgrad(void* dw, const void* x, const void* gy, const ConvGeom& g, void* ws, cudaStream_t st);
 
 }  // namespace lb2

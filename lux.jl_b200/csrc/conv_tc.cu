@@ -863,6 +863,7 @@ static bool conv_gemm_ok(const ConvGemm& c) {
 }
 
 bool conv_tc_supported(const ConvGeom& g, int32_t dtype) {
+  if (dtype == LB2_F32) return conv_tc_f32_supported(g);
   if (dtype != LB2_BF16 || g.ndim != 2 || g.groups != 1) return false;
   if (g.stride[0] != 1 || g.stride[1] != 1 || g.dil[0] != 1 || g.dil[1] != 1) return false;
   if (g.out[0] != g.in[0] || g.out[0] <= 0 || g.out[1] <= 0 || g.batch <= 0 || g.cin <= 0 || g.cout <= 0) return false;
@@ -1035,13 +1036,15 @@ static PackGeom pack_geom(const ConvGeom& g, const ConvGemm& c, int transpose) {
   return pg;
 }
 
-size_t conv_tc_fwd_workspace_bytes(const ConvGeom& g) {
+size_t conv_tc_fwd_workspace_bytes(const ConvGeom& g, int32_t dtype) {
+  if (dtype == LB2_F32) return conv_tc_f32_fwd_workspace_bytes(g);
   const ConvGemm c = fwd_gemm(g);
   return gemm_copies_bytes(c) + packed_bytes(c);
 }
 
 int32_t conv_tc_fwd(void* y, void* preact, const void* x, const void* w, const void* bias, const ConvGeom& g,
-                    int32_t act, void* ws, cudaStream_t st) {
+                    int32_t dtype, int32_t act, void* ws, cudaStream_t st) {
+  if (dtype == LB2_F32) return conv_tc_f32_fwd(y, preact, x, w, bias, g, act, ws, st);
   const ConvGemm c = fwd_gemm(g);
   return run_conv_gemm(y, preact, bias, act, x, w, c, pack_geom(g, c, 0), static_cast<uint8_t*>(ws), st);
 }
@@ -1074,19 +1077,22 @@ static size_t wg_partial_bytes(const WgPlan& w) {
   return align_up((size_t)w.splits * w.m_tiles * 128 * w.n_pad * sizeof(float), 1024);
 }
 
-size_t conv_tc_bwd_workspace_bytes(const ConvGeom& g) {
+size_t conv_tc_bwd_workspace_bytes(const ConvGeom& g, int32_t dtype) {
+  if (dtype == LB2_F32) return conv_tc_f32_bwd_workspace_bytes(g);
   const ConvGemm d = dgrad_gemm(g), f = fwd_gemm(g);
   const size_t dgrad = gemm_copies_bytes(d) + packed_bytes(d);
   const size_t wgrad = copies_bytes(f) + wg_partial_bytes(wg_plan(g));
   return dgrad > wgrad ? dgrad : wgrad;   // the two gradients run one after the other in the same region
 }
 
-int32_t conv_tc_dgrad(void* dx, const void* gy, const void* w, const ConvGeom& g, void* ws, cudaStream_t st) {
+int32_t conv_tc_dgrad(void* dx, const void* gy, const void* w, const ConvGeom& g, int32_t dtype, void* ws, cudaStream_t st) {
+  if (dtype == LB2_F32) return conv_tc_f32_dgrad(dx, gy, w, g, ws, st);
   const ConvGemm c = dgrad_gemm(g);
   return run_conv_gemm(dx, nullptr, nullptr, LB2_ACT_IDENTITY, gy, w, c, pack_geom(g, c, 1), static_cast<uint8_t*>(ws), st);
 }
 
-int32_t conv_tc_wgrad(void* dw, const void* x, const void* gy, const ConvGeom& g, void* ws_, cudaStream_t st) {
+int32_t conv_tc_wgrad(void* dw, const void* x, const void* gy, const ConvGeom& g, int32_t dtype, void* ws_, cudaStream_t st) {
+  if (dtype == LB2_F32) return conv_tc_f32_wgrad(dw, x, gy, g, ws_, st);
   using T = __nv_bfloat16;
   uint8_t* ws = static_cast<uint8_t*>(ws_);
   const ConvGemm f = fwd_gemm(g);

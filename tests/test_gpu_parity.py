@@ -229,15 +229,16 @@ TC_CONV_CASES = [
     ((40, 7), (5, 3), 32, 40, (2, 2, 1, 1), False),
     ((16, 6), (3, 3), 64, 96, 1, False),
     ((8, 40), (3, 5), 130, 48, (1, 1, 2, 2), False),
+    ((12, 9), (3, 3), 24, 20, 1, False),     # W % 4 == 0 only: Float32 tensor-core path, bf16 direct path
 ]
 
 
 @pytest.mark.parametrize("force_simt", [False, True])
 @pytest.mark.parametrize("act", ["identity", "relu", "gelu"])
+@pytest.mark.parametrize("dt", ["bf16", "f32"])
 @pytest.mark.parametrize("case", TC_CONV_CASES)
-def test_fused_conv_tensor_core_path_bf16(case, act, force_simt):
+def test_fused_conv_tensor_core_path(case, dt, act, force_simt):
     sp, k, cin, cout, pad, flip = case
-    dt = "bf16"
     rng = np.random.default_rng(23)
     x = prep(rng.standard_normal(sp + (cin, 3)), dt)
     w = prep(O.kaiming_normal(rng, k + (cin, cout)), dt)
