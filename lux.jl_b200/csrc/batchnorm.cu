@@ -74,26 +74,48 @@ __global__ void __launch_bounds__(256) bn_reduce_kernel(float* __restrict__ part
     }
   }
   float a = 0.f, q = 0.f;
-  const int64_t items = (b_end - b_begin) * sv;
-  for (int64_t it = threadIdx.x; it < items; it += blockDim.x) {
-    const int64_t b = b_begin + it / sv;
-    const int64_t e = (b * C + c) * S + (it % sv) * V;
-    if constexpr (VEC) {
-      Vec16<T> xv = load16(x + e);
-      if constexpr (MODE == 0) {
+  if constexpr (VEC) {
+    // A warp takes units of 128 vectors (4 per lane, all loads issued before any is used) of one
+    // sample's channel plane; the unit -> (sample, segment) division happens once per unit.
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t upr = (uint32_t)((sv + 127) / 128);   // units per channel plane
+    const int64_t units = (b_end - b_begin) * (int64_t)upr;
+    for (int64_t u = warp; u < units; u += 8) {
+      const int64_t b = b_begin + u / upr;
+      const int64_t v0 = (int64_t)(u % upr) * 128 + lane;
+      const T* xr = x + (b * C + c) * S;
+      Vec16<T> xv[4], gv[4];
 #pragma unroll
-        for (int j = 0; j < V; ++j) { float d = xv.get(j) - K; a += d; q += d * d; }
-      } else {
-        Vec16<T> gv = load16(dy + e);
-#pragma unroll
-        for (int j = 0; j < V; ++j) {
-          float d = gv.get(j);
-          if constexpr (ACT != LB2_ACT_IDENTITY) d *= act_grad_pre_any<ACT, FAST>(act_rt, fmaf(xv.get(j), gp, bp));
-          a += d;
-          q += d * (xv.get(j) - mean);
+      for (int k = 0; k < 4; ++k) {
+        const int64_t v = v0 + k * 32;
+        if (v < sv) {
+          xv[k] = load16(xr + v * V);
+          if constexpr (MODE == 1) gv[k] = load16(dy + (b * C + c) * S + v * V);
         }
       }
-    } else {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        if (v0 + k * 32 < sv) {
+          if constexpr (MODE == 0) {
+#pragma unroll
+            for (int j = 0; j < V; ++j) { const float d = xv[k].get(j) - K; a += d; q = fmaf(d, d, q); }
+          } else {
+#pragma unroll
+            for (int j = 0; j < V; ++j) {
+              float d = gv[k].get(j);
+              if constexpr (ACT != LB2_ACT_IDENTITY) d *= act_grad_pre_any<ACT, FAST>(act_rt, fmaf(xv[k].get(j), gp, bp));
+              a += d;
+              q = fmaf(d, xv[k].get(j) - mean, q);
+            }
+          }
+        }
+      }
+    }
+  } else {
+    const int64_t items = (b_end - b_begin) * sv;
+    for (int64_t it = threadIdx.x; it < items; it += blockDim.x) {
+      const int64_t b = b_begin + it / sv;
+      const int64_t e = (b * C + c) * S + (it % sv) * V;
       const float xv = to_f32(x[e]);
       if constexpr (MODE == 0) {
         float d = xv - K; a += d; q += d * d;
@@ -235,6 +257,31 @@ __global__ void bn_finalize_bwd_kernel(T* __restrict__ dgamma, T* __restrict__ d
 // ---------------------------------------------------------------------------------------------
 // MODE 0: y = act(x*gp + bp) from coef (training)      MODE 1: same from running statistics
 // MODE 2: dx = c0*d + c1*x + c2, d = dy*act'(x*gp_fwd + bp_fwd)
+template <typename T, int MODE, int ACT, bool AFFINE>
+__device__ __forceinline__ void bn_channel_coefs(int64_t c, const float* __restrict__ coef, const T* __restrict__ gamma,
+                                                 const T* __restrict__ beta, const T* __restrict__ rmean,
+                                                 const T* __restrict__ rvar, const float* __restrict__ mean_in,
+                                                 const float* __restrict__ inv_in, float eps, float& gp, float& bp) {
+  if constexpr (MODE == 0) {
+    gp = coef[c * 4];
+    bp = coef[c * 4 + 1];
+  } else if constexpr (MODE == 1) {
+    const float inv = 1.f / sqrtf(to_f32(rvar[c]) + eps);
+    const float mean = to_f32(rmean[c]);
+    gp = inv; bp = -mean * inv;
+    if constexpr (AFFINE) { gp = to_f32(gamma[c]) * inv; bp = to_f32(beta[c]) - mean * gp; }
+  } else {
+    gp = 1.f; bp = 0.f;
+    if constexpr (ACT != LB2_ACT_IDENTITY) {
+      const float inv = inv_in[c], mean = mean_in[c];
+      gp = inv; bp = -mean * inv;
+      if constexpr (AFFINE) { gp = to_f32(gamma[c]) * inv; bp = to_f32(beta[c]) - mean * gp; }
+    }
+  }
+}
+
+// VEC: a warp takes units of 128 vectors (4 per lane) of one (sample, channel) plane, so the channel
+// and its coefficients are worked out once per unit and four loads per tensor are in flight per lane.
 template <typename T, int MODE, int ACT, bool AFFINE, bool VEC>
 __global__ void __launch_bounds__(256) bn_apply_kernel(T* __restrict__ out, const T* __restrict__ x,
                                                        const T* __restrict__ dy, const float* __restrict__ coef,
@@ -244,49 +291,67 @@ __global__ void __launch_bounds__(256) bn_apply_kernel(T* __restrict__ out, cons
                                                        const float* __restrict__ inv_in, int64_t S, int64_t C,
                                                        int64_t n, float eps, int act_rt) {
   constexpr bool FAST = sizeof(T) == 2;
-  constexpr int V = VEC ? Vec16<T>::N : 1;
-  const int64_t nvec = n / V;
-  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  for (int64_t i0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i0 < nvec; i0 += stride) {
-    const int64_t i = nvec - 1 - i0;
-    const int64_t e = i * V;
-    const int64_t c = (e / S) % C;
-    float gp, bp;
-    if constexpr (MODE == 0) {
-      gp = coef[c * 4];
-      bp = coef[c * 4 + 1];
-    } else if constexpr (MODE == 1) {
-      const float inv = 1.f / sqrtf(to_f32(rvar[c]) + eps);
-      const float mean = to_f32(rmean[c]);
-      gp = inv; bp = -mean * inv;
-      if constexpr (AFFINE) { gp = to_f32(gamma[c]) * inv; bp = to_f32(beta[c]) - mean * gp; }
-    } else {
-      gp = 1.f; bp = 0.f;
-      if constexpr (ACT != LB2_ACT_IDENTITY) {
-        const float inv = inv_in[c], mean = mean_in[c];
-        gp = inv; bp = -mean * inv;
-        if constexpr (AFFINE) { gp = to_f32(gamma[c]) * inv; bp = to_f32(beta[c]) - mean * gp; }
+  if constexpr (VEC) {
+    constexpr int V = Vec16<T>::N;
+    const int lane = threadIdx.x & 31;
+    const int64_t sv = S / V;
+    const uint32_t upr = (uint32_t)((sv + 127) / 128);
+    const int64_t planes = n / S;
+    const int64_t units = planes * (int64_t)upr;
+    const int64_t wstride = (int64_t)gridDim.x * (blockDim.x >> 5);
+    for (int64_t u0 = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); u0 < units; u0 += wstride) {
+      const int64_t u = units - 1 - u0;
+      const int64_t plane = u / upr;
+      const int64_t v0 = (int64_t)(u % upr) * 128 + lane;
+      const int64_t c = plane % C;
+      float gp, bp;
+      bn_channel_coefs<T, MODE, ACT, AFFINE>(c, coef, gamma, beta, rmean, rvar, mean_in, inv_in, eps, gp, bp);
+      const T* xr = x + plane * S;
+      T* outr = out + plane * S;
+      Vec16<T> xv[4], gv[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int64_t v = v0 + k * 32;
+        if (v < sv) {
+          xv[k] = load16_stream(xr + v * V);
+          if constexpr (MODE == 2) gv[k] = load16_stream(dy + plane * S + v * V);
+        }
+      }
+      if constexpr (MODE == 2) {
+        const float c0 = coef[c * 4], c1 = coef[c * 4 + 1], c2 = coef[c * 4 + 2];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int64_t v = v0 + k * 32;
+          if (v < sv) {
+            store16_stream(outr + v * V, vec_from<T>([&](int j) {
+              float d = gv[k].get(j);
+              if constexpr (ACT != LB2_ACT_IDENTITY) d *= act_grad_pre_any<ACT, FAST>(act_rt, fmaf(xv[k].get(j), gp, bp));
+              return fmaf(c0, d, fmaf(c1, xv[k].get(j), c2));
+            }));
+          }
+        }
+      } else {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int64_t v = v0 + k * 32;
+          if (v < sv)
+            store16_stream(outr + v * V, vec_from<T>([&](int j) { return act_apply_any<ACT, FAST>(act_rt, fmaf(xv[k].get(j), gp, bp)); }));
+        }
       }
     }
-    if constexpr (MODE == 2) {
-      const float c0 = coef[c * 4], c1 = coef[c * 4 + 1], c2 = coef[c * 4 + 2];
-      if constexpr (VEC) {
-        const Vec16<T> xv = load16_stream(x + e), gv = load16_stream(dy + e);
-        store16_stream(out + e, vec_from<T>([&](int j) {
-          float d = gv.get(j);
-          if constexpr (ACT != LB2_ACT_IDENTITY) d *= act_grad_pre_any<ACT, FAST>(act_rt, fmaf(xv.get(j), gp, bp));
-          return fmaf(c0, d, fmaf(c1, xv.get(j), c2));
-        }));
-      } else {
+  } else {
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i0 < n; i0 += stride) {
+      const int64_t e = n - 1 - i0;
+      const int64_t c = (e / S) % C;
+      float gp, bp;
+      bn_channel_coefs<T, MODE, ACT, AFFINE>(c, coef, gamma, beta, rmean, rvar, mean_in, inv_in, eps, gp, bp);
+      if constexpr (MODE == 2) {
+        const float c0 = coef[c * 4], c1 = coef[c * 4 + 1], c2 = coef[c * 4 + 2];
         const float xv = to_f32(x[e]);
         float d = to_f32(dy[e]);
         if constexpr (ACT != LB2_ACT_IDENTITY) d *= act_grad_pre_any<ACT, FAST>(act_rt, fmaf(xv, gp, bp));
         out[e] = from_f32<T>(fmaf(c0, d, fmaf(c1, xv, c2)));
-      }
-    } else {
-      if constexpr (VEC) {
-        const Vec16<T> xv = load16_stream(x + e);
-        store16_stream(out + e, vec_from<T>([&](int j) { return act_apply_any<ACT, FAST>(act_rt, fmaf(xv.get(j), gp, bp)); }));
       } else {
         out[e] = from_f32<T>(act_apply_any<ACT, FAST>(act_rt, fmaf(to_f32(x[e]), gp, bp)));
       }
@@ -321,7 +386,8 @@ static void bn_apply_launch(T* out, const T* x, const T* dy, const float* coef, 
   constexpr int V = Vec16<T>::N;
   const int64_t n = S * C * B;
   const bool vec = aligned_to(out, 16) && aligned_to(x, 16) && (!dy || aligned_to(dy, 16)) && S % V == 0;
-  if (vec) bn_apply_kernel<T, MODE, ACT, AFFINE, true><<<apply_grid(n / V), 256, 0, st>>>(out, x, dy, coef, g, b, rm, rv, sm, si, S, C, n, eps, act);
+  const int64_t units = (n / S) * ((S / V + 127) / 128);   // one warp per unit, 8 warps per CTA
+  if (vec) bn_apply_kernel<T, MODE, ACT, AFFINE, true><<<apply_grid(units * 32), 256, 0, st>>>(out, x, dy, coef, g, b, rm, rv, sm, si, S, C, n, eps, act);
   else bn_apply_kernel<T, MODE, ACT, AFFINE, false><<<apply_grid(n), 256, 0, st>>>(out, x, dy, coef, g, b, rm, rv, sm, si, S, C, n, eps, act);
 }
 

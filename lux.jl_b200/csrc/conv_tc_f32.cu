@@ -2,11 +2,11 @@
 // kind::tf32 MMAs made fp32-accurate.
 //
 // Accuracy. A tf32 product keeps 11 bits of each factor, so every operand is split on the way in,
-// hi = tf32(x), lo = x - hi, and each k-block issues three products (lo*hi, hi*lo, then hi*hi). The
+// hi = tf32(x), lo = x - hi, and each k-block forms three products (hi*hi, hi*lo, lo*hi). The
 // tensor core also TRUNCATES when it adds into its TMEM accumulator, an error that grows with the
 // number of accumulating MMAs (about 1e-7 relative each), so TMEM only ever holds one k-block's
-// 12 MMAs: the eight accumulating warps pull that partial out of TMEM (two chunk buffers, the next
-// k-block's MMAs overlap) and add it round-to-nearest into fp32 registers. The filter gradient,
+// MMAs (hi*hi in one accumulator, the two small products in another): the eight accumulating warps
+// pull those partials out of TMEM (a ring of chunk buffers, so the following k-blocks' MMAs overlap) and add it round-to-nearest into fp32 registers. The filter gradient,
 // whose contraction runs over every output position of every image, stays within 1e-5 this way.
 //
 // Shapes taken: as the bf16 path (2-D, stride 1, dilation 1, groups 1, output width == input
@@ -126,7 +126,7 @@ __global__ void __launch_bounds__(256) conv_pack_split_filter_kernel(float* __re
 struct ConvF32Params {
   int32_t S_out, n_img, n_out;
   int32_t tiles_m, tiles_n, num_kb;
-  uint32_t idesc;
+  uint32_t idesc, idesc_wide;   // MMA width BN (A_lo * B_hi) and 2*BN (A_hi * [B_hi ; B_lo])
   uint32_t a_desc_hi, a_desc_lbo, a_k_advance;
   uint32_t b_desc_hi, b_desc_lbo, b_k_advance;
   float* y;
@@ -142,30 +142,30 @@ struct ConvF32Params {
 template <int BN> struct ConvF32Cfg {
   static constexpr int A_BYTES = kF32BM * 128;            // 128 positions x 32 channels (fp32), one of hi / lo
   static constexpr int B_BYTES = BN * 128;                // BN rows x 32 contracted elements
-  static constexpr int LO_OFF = A_BYTES + B_BYTES;        // stage = [A_hi | B_hi | A_lo | B_lo]
-  static constexpr int STAGE_BYTES = 2 * LO_OFF;
+  static constexpr int STAGE_BYTES = 2 * (A_BYTES + B_BYTES);   // stage = [A_hi | A_lo | B_hi | B_lo]
+  static constexpr int CHUNK_COLS = 2 * BN;               // TMEM columns per k-block: [hi*hi | hi*lo + lo*hi]
+  static constexpr int CHUNKS = 512 / CHUNK_COLS < 4 ? 512 / CHUNK_COLS : 4;
   static constexpr int STAGES = (200 * 1024) / STAGE_BYTES;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
 };
 
-// one k-block's 12 MMAs: small products first so that the large hi*hi terms are added last
-__device__ __forceinline__ void issue_split_kblock(uint32_t d_tmem, uint32_t sA, uint32_t sB, uint32_t lo_off16,
+// One k-block = 8 MMAs. B_hi and B_lo sit back to back in the stage, so per k-step ONE MMA of width 2*BN
+// forms A_hi * [B_hi ; B_lo] (columns [0, BN) = hi*hi, [BN, 2*BN) = hi*lo) and a second of width BN adds
+// A_lo * B_hi onto the small-term columns. The large and the small products thus have accumulators
+// of their own and meet in fp32 registers.
+__device__ __forceinline__ void issue_split_kblock(uint32_t d_tmem, uint32_t bn, uint32_t sA_hi, uint32_t sA_lo, uint32_t sB,
                                                    uint32_t a_hi, uint32_t a_lbo, uint32_t a_adv, uint32_t b_hi,
-                                                   uint32_t b_lbo, uint32_t b_adv, uint32_t idesc) {
-  const uint32_t a_lo32 = ((sA >> 4) & 0x3FFFu) | a_lbo;
-  const uint32_t b_lo32 = ((sB >> 4) & 0x3FFFu) | b_lbo;
+                                                   uint32_t b_lbo, uint32_t b_adv, uint32_t idesc_wide, uint32_t idesc) {
+  const uint32_t ah32 = ((sA_hi >> 4) & 0x3FFFu) | a_lbo;
+  const uint32_t al32 = ((sA_lo >> 4) & 0x3FFFu) | a_lbo;
+  const uint32_t b32 = ((sB >> 4) & 0x3FFFu) | b_lbo;
 #pragma unroll
   for (int ks = 0; ks < 4; ++ks) {
-    const uint64_t ad = ((uint64_t)a_hi << 32) | (uint64_t)(a_lo32 + ks * a_adv);
-    const uint64_t bd = ((uint64_t)b_hi << 32) | (uint64_t)(b_lo32 + ks * b_adv);
-    umma<true>(d_tmem, ad + lo_off16, bd, idesc, ks != 0 ? 1u : 0u);
-    umma<true>(d_tmem, ad, bd + lo_off16, idesc, 1u);
-  }
-#pragma unroll
-  for (int ks = 0; ks < 4; ++ks) {
-    const uint64_t ad = ((uint64_t)a_hi << 32) | (uint64_t)(a_lo32 + ks * a_adv);
-    const uint64_t bd = ((uint64_t)b_hi << 32) | (uint64_t)(b_lo32 + ks * b_adv);
-    umma<true>(d_tmem, ad, bd, idesc, 1u);
+    const uint64_t adh = ((uint64_t)a_hi << 32) | (uint64_t)(ah32 + ks * a_adv);
+    const uint64_t adl = ((uint64_t)a_hi << 32) | (uint64_t)(al32 + ks * a_adv);
+    const uint64_t bd = ((uint64_t)b_hi << 32) | (uint64_t)(b32 + ks * b_adv);
+    umma<true>(d_tmem, adh, bd, idesc_wide, ks != 0 ? 1u : 0u);
+    umma<true>(d_tmem + bn, adl, bd, idesc, 1u);
   }
 }
 
@@ -182,9 +182,9 @@ conv_tc_f32_fwd_kernel(const __grid_constant__ CUtensorMap tmXh, const __grid_co
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + STAGES * Cfg::STAGE_BYTES);
   uint64_t* full = bars;
   uint64_t* empty = bars + STAGES;
-  uint64_t* chunk_full = bars + 2 * STAGES;   // [2] MMA -> accumulating warps
-  uint64_t* chunk_empty = chunk_full + 2;     // [2] accumulating warps -> MMA
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(chunk_empty + 2);
+  uint64_t* chunk_full = bars + 2 * STAGES;   // [CHUNKS] MMA -> accumulating warps
+  uint64_t* chunk_empty = chunk_full + Cfg::CHUNKS;     // [CHUNKS] accumulating warps -> MMA
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(chunk_empty + Cfg::CHUNKS);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_per_n = p.tiles_m * p.n_img;
@@ -192,11 +192,11 @@ conv_tc_f32_fwd_kernel(const __grid_constant__ CUtensorMap tmXh, const __grid_co
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(&chunk_full[a], 1); mbar_init(&chunk_empty[a], 8); }
+    for (int a = 0; a < Cfg::CHUNKS; ++a) { mbar_init(&chunk_full[a], 1); mbar_init(&chunk_empty[a], 8); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 2) {
-    tmem_alloc(tmem_slot, 2 * BN);
+    tmem_alloc(tmem_slot, Cfg::CHUNKS * Cfg::CHUNK_COLS);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -216,15 +216,15 @@ conv_tc_f32_fwd_kernel(const __grid_constant__ CUtensorMap tmXh, const __grid_co
         for (int kb = 0; kb < p.num_kb; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, p.status, 0x1000u)) { ok = false; break; }
           mbar_expect_tx(&full[stage], Cfg::STAGE_BYTES);
-          const uint32_t sA = smem_base + stage * Cfg::STAGE_BYTES, sB = sA + Cfg::A_BYTES;
+          const uint32_t sA = smem_base + stage * Cfg::STAGE_BYTES, sB = sA + 2 * Cfg::A_BYTES;
           const int c0 = m0 + p.a_shift[kb];
 #pragma unroll
           for (int bx = 0; bx < 4; ++bx) {   // four boxes of 32 positions x 32 channels
             tma_load_4d(sA + bx * 4096, &tmXh, c0 + bx * 32, p.a_chan[kb], img, p.a_copy[kb], &full[stage]);
-            tma_load_4d(sA + Cfg::LO_OFF + bx * 4096, &tmXl, c0 + bx * 32, p.a_chan[kb], img, p.a_copy[kb], &full[stage]);
+            tma_load_4d(sA + Cfg::A_BYTES + bx * 4096, &tmXl, c0 + bx * 32, p.a_chan[kb], img, p.a_copy[kb], &full[stage]);
           }
           tma_load_2d(sB, &tmWh, kb * 32, n0, &full[stage]);
-          tma_load_2d(sB + Cfg::LO_OFF, &tmWl, kb * 32, n0, &full[stage]);
+          tma_load_2d(sB + Cfg::B_BYTES, &tmWl, kb * 32, n0, &full[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
@@ -238,13 +238,13 @@ conv_tc_f32_fwd_kernel(const __grid_constant__ CUtensorMap tmXh, const __grid_co
           if (!mbar_wait(&chunk_empty[ch], ch_phase ^ 1u, p.status, 0x2000u)) { ok = false; break; }
           if (!mbar_wait(&full[stage], phase, p.status, 0x4000u)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t sA = smem_base + stage * Cfg::STAGE_BYTES, sB = sA + Cfg::A_BYTES;
-          issue_split_kblock(tmem_base + ch * BN, sA, sB, (uint32_t)(Cfg::LO_OFF >> 4), p.a_desc_hi, p.a_desc_lbo,
-                             p.a_k_advance, p.b_desc_hi, p.b_desc_lbo, p.b_k_advance, p.idesc);
+          const uint32_t sA = smem_base + stage * Cfg::STAGE_BYTES, sB = sA + 2 * Cfg::A_BYTES;
+          issue_split_kblock(tmem_base + ch * Cfg::CHUNK_COLS, BN, sA, sA + Cfg::A_BYTES, sB, p.a_desc_hi, p.a_desc_lbo,
+                             p.a_k_advance, p.b_desc_hi, p.b_desc_lbo, p.b_k_advance, p.idesc_wide, p.idesc);
           umma_commit(&empty[stage]);
           umma_commit(&chunk_full[ch]);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
-          if (++ch == 2) { ch = 0; ch_phase ^= 1u; }
+          if (++ch == Cfg::CHUNKS) { ch = 0; ch_phase ^= 1u; }
         }
       }
     }
@@ -264,17 +264,20 @@ conv_tc_f32_fwd_kernel(const __grid_constant__ CUtensorMap tmXh, const __grid_co
       for (int kb = 0; kb < p.num_kb; ++kb) {
         if (!mbar_wait_warp(&chunk_full[ch], ch_phase, p.status, 0x8000u)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + ch * BN + half * COLS;
-        uint32_t r[COLS];
+        const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + ch * Cfg::CHUNK_COLS + half * COLS;
+        uint32_t r[COLS], rs[COLS];   // hi*hi and the two small products
 #pragma unroll
-        for (int c = 0; c < COLS / 32; ++c) tmem_ld32(t0 + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
+        for (int c = 0; c < COLS / 32; ++c) {
+          tmem_ld32(t0 + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
+          tmem_ld32(t0 + BN + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&rs[c * 32]));
+        }
         tmem_ld_wait();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&chunk_empty[ch]);
 #pragma unroll
-        for (int j = 0; j < COLS; ++j) sum[j] += __uint_as_float(r[j]);
-        if (++ch == 2) { ch = 0; ch_phase ^= 1u; }
+        for (int j = 0; j < COLS; ++j) sum[j] += __uint_as_float(rs[j]) + __uint_as_float(r[j]);
+        if (++ch == Cfg::CHUNKS) { ch = 0; ch_phase ^= 1u; }
       }
       if (!ok) break;
       const int s = m0 + q * 32 + lane;
@@ -303,7 +306,7 @@ conv_tc_f32_fwd_kernel(const __grid_constant__ CUtensorMap tmXh, const __grid_co
       for (int i = 0; i < 64; ++i) __nanosleep(2000);
     }
     tc_fence_after();
-    tmem_dealloc(tmem_base, 2 * BN);
+    tmem_dealloc(tmem_base, Cfg::CHUNKS * Cfg::CHUNK_COLS);
   }
 }
 
@@ -318,7 +321,7 @@ struct ConvF32WgParams {
   int32_t m_tiles, tiles_n, splits;
   int32_t kb_total, kb_per_split;
   int32_t n_rg;
-  uint32_t idesc;
+  uint32_t idesc, idesc_wide;
   uint32_t desc_hi, desc_lbo, k_advance;   // both operands K-major SW128
   float* partial;                    // [splits][m_tiles*128][n_pad]
   int32_t n_pad;
@@ -342,19 +345,19 @@ conv_tc_f32_wgrad_kernel(const __grid_constant__ CUtensorMap tmXh, const __grid_
   uint64_t* full = bars;
   uint64_t* empty = bars + STAGES;
   uint64_t* chunk_full = bars + 2 * STAGES;
-  uint64_t* chunk_empty = chunk_full + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(chunk_empty + 2);
+  uint64_t* chunk_empty = chunk_full + Cfg::CHUNKS;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(chunk_empty + Cfg::CHUNKS);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_items = p.m_tiles * p.tiles_n * p.splits;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(&chunk_full[a], 1); mbar_init(&chunk_empty[a], 8); }
+    for (int a = 0; a < Cfg::CHUNKS; ++a) { mbar_init(&chunk_full[a], 1); mbar_init(&chunk_empty[a], 8); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 2) {
-    tmem_alloc(tmem_slot, 2 * BN);
+    tmem_alloc(tmem_slot, Cfg::CHUNKS * Cfg::CHUNK_COLS);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -376,16 +379,16 @@ conv_tc_f32_wgrad_kernel(const __grid_constant__ CUtensorMap tmXh, const __grid_
         for (int kb = kb_lo; kb < kb_hi; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, p.status, 0x20000u)) { ok = false; break; }
           const int img = kb / p.s_blocks, s0 = (kb % p.s_blocks) * 32;
-          const uint32_t sA = smem_base + stage * Cfg::STAGE_BYTES, sB = sA + Cfg::A_BYTES;
+          const uint32_t sA = smem_base + stage * Cfg::STAGE_BYTES, sB = sA + 2 * Cfg::A_BYTES;
           mbar_expect_tx(&full[stage], (uint32_t)(2 * (Cfg::B_BYTES + (two ? Cfg::A_BYTES : Cfg::A_BYTES / 2))));
           tma_load_4d(sA, &tmXh, s0 + p.rg_shift[rg0], p.rg_chan[rg0], img, p.rg_copy[rg0], &full[stage]);
-          tma_load_4d(sA + Cfg::LO_OFF, &tmXl, s0 + p.rg_shift[rg0], p.rg_chan[rg0], img, p.rg_copy[rg0], &full[stage]);
+          tma_load_4d(sA + Cfg::A_BYTES, &tmXl, s0 + p.rg_shift[rg0], p.rg_chan[rg0], img, p.rg_copy[rg0], &full[stage]);
           if (two) {
             tma_load_4d(sA + Cfg::A_BYTES / 2, &tmXh, s0 + p.rg_shift[rg1], p.rg_chan[rg1], img, p.rg_copy[rg1], &full[stage]);
-            tma_load_4d(sA + Cfg::LO_OFF + Cfg::A_BYTES / 2, &tmXl, s0 + p.rg_shift[rg1], p.rg_chan[rg1], img, p.rg_copy[rg1], &full[stage]);
+            tma_load_4d(sA + Cfg::A_BYTES + Cfg::A_BYTES / 2, &tmXl, s0 + p.rg_shift[rg1], p.rg_chan[rg1], img, p.rg_copy[rg1], &full[stage]);
           }
           tma_load_4d(sB, &tmGh, s0, nt * BN, img, 0, &full[stage]);
-          tma_load_4d(sB + Cfg::LO_OFF, &tmGl, s0, nt * BN, img, 0, &full[stage]);
+          tma_load_4d(sB + Cfg::B_BYTES, &tmGl, s0, nt * BN, img, 0, &full[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
@@ -401,13 +404,13 @@ conv_tc_f32_wgrad_kernel(const __grid_constant__ CUtensorMap tmXh, const __grid_
           if (!mbar_wait(&chunk_empty[ch], ch_phase ^ 1u, p.status, 0x40000u)) { ok = false; break; }
           if (!mbar_wait(&full[stage], phase, p.status, 0x80000u)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t sA = smem_base + stage * Cfg::STAGE_BYTES, sB = sA + Cfg::A_BYTES;
-          issue_split_kblock(tmem_base + ch * BN, sA, sB, (uint32_t)(Cfg::LO_OFF >> 4), p.desc_hi, p.desc_lbo, p.k_advance,
-                             p.desc_hi, p.desc_lbo, p.k_advance, p.idesc);
+          const uint32_t sA = smem_base + stage * Cfg::STAGE_BYTES, sB = sA + 2 * Cfg::A_BYTES;
+          issue_split_kblock(tmem_base + ch * Cfg::CHUNK_COLS, BN, sA, sA + Cfg::A_BYTES, sB, p.desc_hi, p.desc_lbo, p.k_advance,
+                             p.desc_hi, p.desc_lbo, p.k_advance, p.idesc_wide, p.idesc);
           umma_commit(&empty[stage]);
           umma_commit(&chunk_full[ch]);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
-          if (++ch == 2) { ch = 0; ch_phase ^= 1u; }
+          if (++ch == Cfg::CHUNKS) { ch = 0; ch_phase ^= 1u; }
         }
       }
     }
@@ -425,17 +428,20 @@ conv_tc_f32_wgrad_kernel(const __grid_constant__ CUtensorMap tmXh, const __grid_
       for (int kb = kb_lo; kb < kb_hi; ++kb) {
         if (!mbar_wait_warp(&chunk_full[ch], ch_phase, p.status, 0x100000u)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + ch * BN + half * COLS;
-        uint32_t r[COLS];
+        const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + ch * Cfg::CHUNK_COLS + half * COLS;
+        uint32_t r[COLS], rs[COLS];   // hi*hi and the two small products
 #pragma unroll
-        for (int c = 0; c < COLS / 32; ++c) tmem_ld32(t0 + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
+        for (int c = 0; c < COLS / 32; ++c) {
+          tmem_ld32(t0 + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
+          tmem_ld32(t0 + BN + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&rs[c * 32]));
+        }
         tmem_ld_wait();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&chunk_empty[ch]);
 #pragma unroll
-        for (int j = 0; j < COLS; ++j) sum[j] += __uint_as_float(r[j]);
-        if (++ch == 2) { ch = 0; ch_phase ^= 1u; }
+        for (int j = 0; j < COLS; ++j) sum[j] += __uint_as_float(rs[j]) + __uint_as_float(r[j]);
+        if (++ch == Cfg::CHUNKS) { ch = 0; ch_phase ^= 1u; }
       }
       if (!ok) break;
       const int row = mt * 128 + q * 32 + lane;
@@ -455,7 +461,7 @@ conv_tc_f32_wgrad_kernel(const __grid_constant__ CUtensorMap tmXh, const __grid_
       for (int i = 0; i < 64; ++i) __nanosleep(2000);
     }
     tc_fence_after();
-    tmem_dealloc(tmem_base, 2 * BN);
+    tmem_dealloc(tmem_base, Cfg::CHUNKS * Cfg::CHUNK_COLS);
   }
 }
 
@@ -591,6 +597,7 @@ int32_t run_f32_gemm(float* out, float* preact, const float* bias, int32_t act, 
   p.b_desc_lbo = 1u << 16;
   p.b_k_advance = 32u >> 4;
   p.idesc = (1u << 4) | (2u << 7) | (2u << 10) | (1u << 15) | (0u << 16) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(kF32BM >> 4) << 24);
+  p.idesc_wide = (p.idesc & ~(0x3Fu << 17)) | ((uint32_t)((2 * bn) >> 3) << 17);
   p.y = out; p.preact = preact; p.bias = bias; p.act = act;
   p.status = device_status_word();
   LB2_REQUIRE(p.status != nullptr, LB2_LAUNCH_FAIL, "conv_tc_f32: device status word unavailable");
@@ -701,6 +708,7 @@ int32_t conv_tc_f32_wgrad(void* dw, const void* x, const void* gy, const ConvGeo
   p.s_blocks = w.s_blocks; p.m_tiles = w.m_tiles; p.tiles_n = w.tiles_n; p.splits = w.splits;
   p.kb_total = w.kb_total; p.kb_per_split = w.kb_per_split; p.n_rg = w.n_rg;
   p.idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(w.bn >> 3) << 17) | ((uint32_t)(kF32BM >> 4) << 24);
+  p.idesc_wide = (p.idesc & ~(0x3Fu << 17)) | ((uint32_t)((2 * w.bn) >> 3) << 17);
   p.desc_hi = (uint32_t)((1024u >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
   p.desc_lbo = 1u << 16;
   p.k_advance = 32u >> 4;
