@@ -318,7 +318,10 @@ def run_gpu_arm(args):
         achieved = 2.0 * M * N * K / (fwd_ms * 1e-3) / 1e12
         roofline = {
             "bound": "tensor", "kernel": "gemm_tc_kernel (forward GEMM, bias+gelu epilogue)", "achieved": achieved,
-            "peak": sustained, "unit": "TFLOP/s", "frac": achieved / sustained, "traffic": None,
+            "peak": sustained, "unit": "TFLOP/s", "frac": achieved / sustained,
+            # dram__bytes_read.sum + dram__bytes_write.sum of one forward launch, from the ncu launch-list pass
+            # summarised in profiles/gemm_tc_kernel_dense_c2_bf16.md (132.1 MB + 103.3 MB)
+            "traffic": 235.4e6, "traffic_unit": "bytes per launch",
             "peak_source": f"{which}: bf16_tflops_sustained (kernel timed inside a long step); burst figure {burst}",
             "launch_ms": fwd_ms,
         }
