@@ -13,6 +13,8 @@
 // Algorithmic bytes per element: forward 2*sizeof(T) (read x, write y), backward 3*sizeof(T);
 // the implementation reads x twice forward and x, dy twice backward (tensor larger than on-chip
 // memory), so its HBM traffic is 3 and 5 element-sizes.
+#include <stdlib.h>
+
 #include <mutex>
 
 #include "common.cuh"
@@ -39,10 +41,29 @@ static BnPlan bn_plan(int64_t S, int64_t C, int64_t B) {
   return p;
 }
 
-// workspace (fp32): partial[chunks][C][2] | coef[C][4]
-static size_t bn_ws_bytes(int64_t S, int64_t C, int64_t B) {
+// Plan of the fused (single cooperative launch) path; see bn_fused_kernel.
+struct BnFusedPlan {
+  bool ok;
+  int grid;        // CTAs, all co-resident
+  int nsub;        // CTA subsets working on different channel groups at the same time
+  int gc_fwd;      // channels per group, forward (x only) / backward (x and dy); nsub groups together fit the L2 budget
+  int gc_bwd;
+};
+constexpr int kBnFusedMaxGc = 64;
+static BnFusedPlan bn_fused_plan(int64_t S, int64_t C, int64_t B, size_t es);
+
+// workspace (fp32): partial[chunks][C][2] | coef[C][4] | fused path: 32 barrier counters 128 B apart (4 KB) | cta_partial[2][grid][kBnFusedMaxGc][2]
+static size_t bn_classic_ws_bytes(int64_t S, int64_t C, int64_t B) {
   // upper bound on chunks over both regimes
   return align_up(((size_t)bn_plan(S, C, B).chunks * (size_t)C * 2 + (size_t)C * 4) * sizeof(float), 256);
+}
+static size_t bn_fused_ws_bytes(const BnFusedPlan& f) {
+  return f.ok ? 4096 + align_up((size_t)2 * f.grid * kBnFusedMaxGc * 2 * sizeof(float), 256) : 0;   // 32 counters, 128 B apart
+}
+static size_t bn_ws_bytes(int64_t S, int64_t C, int64_t B) {
+  // the fused plan depends on the element size only through the group size; size for the larger (2-byte) grid
+  const size_t f4 = bn_fused_ws_bytes(bn_fused_plan(S, C, B, 4)), f2 = bn_fused_ws_bytes(bn_fused_plan(S, C, B, 2));
+  return bn_classic_ws_bytes(S, C, B) + (f4 > f2 ? f4 : f2);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -391,6 +412,330 @@ static void bn_apply_launch(T* out, const T* x, const T* dy, const float* coef, 
   else bn_apply_kernel<T, MODE, ACT, AFFINE, false><<<apply_grid(n), 256, 0, st>>>(out, x, dy, coef, g, b, rm, rv, sm, si, S, C, n, eps, act);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Fused path: statistics and normalisation in ONE cooperative launch, one L2-sized group of channels
+// at a time. All CTAs reduce the group (per-CTA, per-channel partials in a fixed order), meet at a
+// grid barrier, every CTA finishes the group's coefficients for itself (fp64 combine of the same
+// partials in the same order, so all CTAs agree bit for bit), then the same warps re-read the same
+// units - now from L2 - and write the result. HBM traffic drops from 3 + 5 to the algorithmic 2 + 3
+// element-sizes. The barrier is a global counter with a time-bounded spin (cooperative launch
+// guarantees co-residency); on expiry the kernel records a status code and every CTA returns.
+// A unit = 128 vectors (4 per lane) of one (sample, channel) plane, as in bn_apply_kernel.
+// ---------------------------------------------------------------------------------------------
+struct BnFusedArgs {
+  void* out;             // y or dx
+  const void* x;
+  const void* dy;        // backward only
+  const void* gamma;
+  const void* beta;
+  const void* rmean;     // forward: running statistics in (may be null)
+  const void* rvar;
+  void* new_rmean;
+  void* new_rvar;
+  float* save_mean;      // forward: written; backward: read
+  float* save_inv;
+  void* dgamma;          // backward
+  void* dbeta;
+  float* cta_partial;    // [2][grid][kBnFusedMaxGc][2]
+  unsigned int* counter;
+  unsigned int* status;
+  int64_t S, C, B;
+  int gc;
+  int nsub;              // independent subsets of CTAs, each with its own barrier and its own channel groups
+  float momentum, eps;
+  int act_rt;
+};
+
+__device__ __forceinline__ bool bn_grid_barrier(unsigned int* counter, unsigned int target, unsigned int* status) {
+  __shared__ int ok_flag;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int ok = 1;
+    __threadfence();
+    atomicAdd(counter, 1u);
+    unsigned int spins = 0;
+    unsigned long long t0 = 0;
+    while (true) {
+      unsigned int v;
+      asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
+      if (v >= target) break;
+      if ((++spins & 0x3FFu) == 0) {
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+        if (t0 == 0) {
+          t0 = now;
+        } else if (now - t0 > 2000000000ull) {
+          atomicOr(status, 0x40000000u);
+          ok = 0;
+          break;
+        }
+      }
+    }
+    ok_flag = ok;
+  }
+  __syncthreads();
+  return ok_flag != 0;
+}
+
+template <typename T, bool BWD, int ACT, bool AFFINE>
+__global__ void __launch_bounds__(256) bn_fused_kernel(const BnFusedArgs a) {
+  constexpr bool FAST = sizeof(T) == 2;
+  constexpr int V = Vec16<T>::N;
+  __shared__ float2 warp_acc[8][kBnFusedMaxGc];
+  __shared__ float4 coef_s[kBnFusedMaxGc];   // fwd: (gp, bp, K, -); bwd: (c0, c1, c2, -)
+  __shared__ float2 fwd_s[kBnFusedMaxGc];    // bwd: forward (gp, bp) for act'
+  const T* x = static_cast<const T*>(a.x);
+  const T* dy = static_cast<const T*>(a.dy);
+  const T* gamma = static_cast<const T*>(a.gamma);
+  const T* beta = static_cast<const T*>(a.beta);
+  T* out = static_cast<T*>(a.out);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t S = a.S, C = a.C, B = a.B;
+  const int64_t sv = S / V;
+  const uint32_t upr = (uint32_t)((sv + 127) / 128);
+  // CTA b belongs to subset b % nsub (so every subset spans all SMs) and is CTA number b / nsub in it.
+  // Subsets run out of phase with each other, which keeps HBM busy while one of them sits in its barrier.
+  const int sub = (int)(blockIdx.x % a.nsub), rank = (int)(blockIdx.x / a.nsub);
+  const int sub_ctas = ((int)gridDim.x - sub + a.nsub - 1) / a.nsub;
+  const int64_t wtot = (int64_t)sub_ctas * 8, w0 = (int64_t)rank * 8 + warp;
+  const double n = (double)S * (double)B;
+  unsigned int barrier_no = 0;
+  unsigned int* counter = a.counter + sub * 32;
+  const int64_t ngroups = (C + a.gc - 1) / a.gc;
+  for (int64_t gi = sub, grp = 0; gi < ngroups; gi += a.nsub, ++grp) {
+    const int64_t c0 = gi * a.gc;
+    const int gc = (int)min((int64_t)a.gc, C - c0);
+    const int64_t units = (int64_t)gc * B * upr;
+    // per-channel constants of the reduction
+    if (threadIdx.x < gc) {
+      const int64_t c = c0 + threadIdx.x;
+      if constexpr (!BWD) {
+        coef_s[threadIdx.x] = make_float4(0.f, 0.f, to_f32(x[c * S]), 0.f);   // K = first element of the channel
+      } else {
+        const float mean = a.save_mean[c], inv = a.save_inv[c];
+        float gp = inv, bp = -mean * inv;
+        if constexpr (AFFINE) { gp = to_f32(gamma[c]) * inv; bp = to_f32(beta[c]) - mean * gp; }
+        fwd_s[threadIdx.x] = make_float2(gp, bp);
+        coef_s[threadIdx.x] = make_float4(0.f, 0.f, mean, 0.f);
+      }
+    }
+    for (int i = threadIdx.x; i < 8 * kBnFusedMaxGc; i += 256) (&warp_acc[0][0])[i] = make_float2(0.f, 0.f);
+    __syncthreads();
+    // ---- phase 1: sums. A lane keeps its running pair while consecutive units stay in one channel (always, when
+    // a group is a single channel) and the warp reduces it only when the channel changes: no shuffles between
+    // the loads of successive units.
+    float s1 = 0.f, s2 = 0.f;
+    uint32_t cl_run = 0xFFFFFFFFu;
+    auto flush = [&]() {
+      if (cl_run != 0xFFFFFFFFu) {
+        const float t1 = warp_sum(s1), t2 = warp_sum(s2);
+        if (lane == 0) { warp_acc[warp][cl_run].x += t1; warp_acc[warp][cl_run].y += t2; }
+      }
+      s1 = 0.f; s2 = 0.f;
+    };
+#pragma unroll 2
+    for (int64_t u = w0; u < units; u += wtot) {
+      const uint32_t plane = (uint32_t)(u / upr), seg = (uint32_t)(u % upr);
+      const uint32_t b = plane / (uint32_t)gc, cl = plane % (uint32_t)gc;
+      if (cl != cl_run) { flush(); cl_run = cl; }
+      const int64_t v0 = (int64_t)seg * 128 + lane;
+      const int64_t base = ((int64_t)b * C + c0 + cl) * S;
+      Vec16<T> xv[4], gv[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int64_t v = v0 + k * 32;
+        if (v < sv) {
+          xv[k] = load16(x + base + v * V);
+          if constexpr (BWD) gv[k] = load16(dy + base + v * V);
+        }
+      }
+      const float shift = coef_s[cl].z;   // K (forward) or mean (backward)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        if (v0 + k * 32 < sv) {
+#pragma unroll
+          for (int j = 0; j < V; ++j) {
+            if constexpr (!BWD) {
+              const float d = xv[k].get(j) - shift;
+              s1 += d;
+              s2 = fmaf(d, d, s2);
+            } else {
+              float d = gv[k].get(j);
+              if constexpr (ACT != LB2_ACT_IDENTITY) d *= act_grad_pre_any<ACT, FAST>(a.act_rt, fmaf(xv[k].get(j), fwd_s[cl].x, fwd_s[cl].y));
+              s1 += d;
+              s2 = fmaf(d, xv[k].get(j) - shift, s2);
+            }
+          }
+        }
+      }
+    }
+    flush();
+    __syncthreads();
+    float* part = a.cta_partial + ((size_t)(grp & 1) * gridDim.x) * kBnFusedMaxGc * 2;
+    if (threadIdx.x < gc) {
+      float sa = 0.f, sq = 0.f;
+#pragma unroll
+      for (int r = 0; r < 8; ++r) { sa += warp_acc[r][threadIdx.x].x; sq += warp_acc[r][threadIdx.x].y; }
+      part[((size_t)blockIdx.x * kBnFusedMaxGc + threadIdx.x) * 2] = sa;
+      part[((size_t)blockIdx.x * kBnFusedMaxGc + threadIdx.x) * 2 + 1] = sq;
+    }
+    ++barrier_no;
+    if (!bn_grid_barrier(counter, barrier_no * (unsigned int)sub_ctas, a.status)) return;
+    // ---- every CTA finishes the group's coefficients: warp per channel, fp64, fixed order
+    for (int cl = warp; cl < gc; cl += 8) {
+      double da = 0.0, dq = 0.0;
+      for (int r = lane; r < sub_ctas; r += 32) {
+        const size_t k = (size_t)sub + (size_t)r * a.nsub;   // CTA r of this subset
+        da += (double)__ldcg(part + (k * kBnFusedMaxGc + cl) * 2);
+        dq += (double)__ldcg(part + (k * kBnFusedMaxGc + cl) * 2 + 1);
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        da += __shfl_xor_sync(0xffffffffu, da, o);
+        dq += __shfl_xor_sync(0xffffffffu, dq, o);
+      }
+      if (lane == 0) {
+        const int64_t c = c0 + cl;
+        if constexpr (!BWD) {
+          const double K = (double)coef_s[cl].z;
+          const double mean_d = K + da / n;
+          double var_d = (dq - da * da / n) / n;
+          if (var_d < 0.0) var_d = 0.0;
+          const float mean = (float)mean_d, var = (float)var_d;
+          const float inv = 1.f / sqrtf(var + a.eps);
+          float gp = inv, bp = -mean * inv;
+          if (gamma) { gp = to_f32(gamma[c]) * inv; bp = to_f32(beta[c]) - mean * gp; }
+          coef_s[cl] = make_float4(gp, bp, 0.f, 0.f);
+          if (rank == 0) {
+            a.save_mean[c] = mean;
+            a.save_inv[c] = inv;
+            if (a.rmean) {
+              const float nf = (float)n;
+              const float m1 = a.momentum, m2 = a.momentum * nf / (nf - 1.f), m3 = 1.f - m1;
+              static_cast<T*>(a.new_rmean)[c] = from_f32<T>(m3 * to_f32(static_cast<const T*>(a.rmean)[c]) + m1 * mean);
+              static_cast<T*>(a.new_rvar)[c] = from_f32<T>(m3 * to_f32(static_cast<const T*>(a.rvar)[c]) + m2 * var);
+            }
+          }
+        } else {
+          const float nf = (float)n;
+          const float inv = a.save_inv[c], mean = a.save_mean[c];
+          const float sd = (float)da, sdx = (float)dq;
+          if (rank == 0 && a.dgamma) {
+            static_cast<T*>(a.dgamma)[c] = from_f32<T>(sdx * inv);
+            static_cast<T*>(a.dbeta)[c] = from_f32<T>(sd);
+          }
+          const float gp = gamma ? to_f32(gamma[c]) * inv : inv;
+          const float k2 = inv * inv * sdx / nf;
+          coef_s[cl] = make_float4(gp, -gp * k2, gp * (k2 * mean - sd / nf), 0.f);
+        }
+      }
+    }
+    __syncthreads();
+    // ---- phase 2: the same warps revisit the same units (L2 hits) and write the result
+#pragma unroll 2
+    for (int64_t u = w0; u < units; u += wtot) {
+      const uint32_t plane = (uint32_t)(u / upr), seg = (uint32_t)(u % upr);
+      const uint32_t b = plane / (uint32_t)gc, cl = plane % (uint32_t)gc;
+      const int64_t v0 = (int64_t)seg * 128 + lane;
+      const int64_t base = ((int64_t)b * C + c0 + cl) * S;
+      Vec16<T> xv[4], gv[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int64_t v = v0 + k * 32;
+        if (v < sv) {
+          xv[k] = load16_stream(x + base + v * V);
+          if constexpr (BWD) gv[k] = load16_stream(dy + base + v * V);
+        }
+      }
+      const float4 cf = coef_s[cl];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int64_t v = v0 + k * 32;
+        if (v < sv) {
+          if constexpr (!BWD) {
+            store16_stream(out + base + v * V, vec_from<T>([&](int j) { return act_apply_any<ACT, FAST>(a.act_rt, fmaf(xv[k].get(j), cf.x, cf.y)); }));
+          } else {
+            const float2 fw = fwd_s[cl];
+            store16_stream(out + base + v * V, vec_from<T>([&](int j) {
+              float d = gv[k].get(j);
+              if constexpr (ACT != LB2_ACT_IDENTITY) d *= act_grad_pre_any<ACT, FAST>(a.act_rt, fmaf(xv[k].get(j), fw.x, fw.y));
+              return fmaf(cf.x, d, fmaf(cf.y, xv[k].get(j), cf.z));
+            }));
+          }
+        }
+      }
+    }
+    __syncthreads();   // coef_s / warp_acc are rewritten by the next group
+  }
+}
+
+// Experiment switches (environment): LB2_BN_FUSED is a bit mask (1 = forward, 2 = backward may take the fused
+// path; 0 keeps the three-kernel path everywhere; unset = see bn_fused_mask); LB2_BN_L2_MB sets the bytes all subsets' channel groups may
+// occupy together (default 40); LB2_BN_NSUB the number of CTA subsets.
+static int bn_env_int(const char* name, int dflt) {
+  const char* e = getenv(name);
+  return e ? atoi(e) : dflt;
+}
+
+// Default: the fused path for 4-byte elements only. Measured on the 56x56x64x256 tensor: Float32 3844 GB/s fused
+// against 3577 GB/s with three kernels; bf16 (a 103 MB tensor, most of which the three-kernel path already finds
+// in L2 by walking backwards) 2865 against 3250.
+static int bn_fused_mask(size_t es) {
+  static const int m = bn_env_int("LB2_BN_FUSED", -1);
+  return m >= 0 ? m : (es == 4 ? 3 : 0);
+}
+
+static BnFusedPlan bn_fused_plan(int64_t S, int64_t C, int64_t B, size_t es) {
+  static const int l2_mb = bn_env_int("LB2_BN_L2_MB", 40);
+  BnFusedPlan f{};
+  const int64_t V = (int64_t)(16 / es);
+  if (S <= 1 || S % V != 0) return f;
+  const double plane_set = (double)S * (double)B * (double)es;           // one channel, all samples
+  if ((double)C * plane_set < 16.0 * 1024 * 1024) return f;              // small tensors live in L2 anyway
+  static const int nsub_env = bn_env_int("LB2_BN_NSUB", 16);
+  int nsub = nsub_env < 1 ? 1 : (nsub_env > 32 ? 32 : nsub_env);
+  if (nsub > C) nsub = (int)C;
+  const double budget = (double)l2_mb * 1024 * 1024 / nsub;
+  int64_t gf = (int64_t)(budget / plane_set), gb = (int64_t)(budget / (2.0 * plane_set));
+  if (gf < 1) gf = 1;
+  if (gb < 1) gb = 1;
+  if (2.0 * plane_set * nsub > 100.0 * 1024 * 1024) return f;   // even one channel per subset would overflow L2
+  if (gf > kBnFusedMaxGc) gf = kBnFusedMaxGc;
+  if (gb > kBnFusedMaxGc) gb = kBnFusedMaxGc;
+  if (gf > C) gf = C;
+  if (gb > C) gb = C;
+  int dev = 0, coop = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return f;
+  static int coop_cache[64] = {0};   // 0 unknown, 1 yes, -1 no
+  if (dev >= 0 && dev < 64 && coop_cache[dev] == 0) {
+    cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev);
+    coop_cache[dev] = coop ? 1 : -1;
+  }
+  if (dev < 0 || dev >= 64 || coop_cache[dev] != 1) return f;
+  f.ok = true;
+  f.grid = sm_count() * 3;
+  f.nsub = nsub;
+  f.gc_fwd = (int)gf;
+  f.gc_bwd = (int)gb;
+  return f;
+}
+
+template <typename T, bool BWD, int ACT, bool AFFINE>
+static int32_t bn_fused_launch(BnFusedArgs& a, int grid, cudaStream_t st) {
+  auto kernel = bn_fused_kernel<T, BWD, ACT, AFFINE>;
+  int per_sm = 0;
+  cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, 256, 0);
+  if (e != cudaSuccess || per_sm < 1) return fail(LB2_LAUNCH_FAIL, "batchnorm: occupancy query failed: %s", cudaGetErrorString(e));
+  const int max_grid = per_sm * sm_count();
+  if (grid > max_grid) grid = max_grid;   // the workspace was sized for the planned (larger or equal) grid
+  e = cudaMemsetAsync(a.counter, 0, 4096, st);
+  if (e != cudaSuccess) return fail(LB2_LAUNCH_FAIL, "batchnorm: counter reset failed: %s", cudaGetErrorString(e));
+  void* params[] = {&a};
+  e = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(kernel), dim3((unsigned)grid), dim3(256), params, 0, st);
+  if (e != cudaSuccess) return fail(LB2_LAUNCH_FAIL, "batchnorm: cooperative launch failed: %s", cudaGetErrorString(e));
+  return LB2_OK;
+}
+
 static int32_t check_bn(const void* out, const void* x, const void* gamma, const void* beta, int64_t S, int64_t C,
                         int64_t B, int32_t dtype, int32_t act) {
   LB2_REQUIRE(S >= 0 && C >= 0 && B >= 0, LB2_BAD_SHAPE, "negative extent");
@@ -462,6 +807,21 @@ int32_t lb2_batchnorm_fwd_train(void* y, float* save_mean, float* save_invstd, v
   const BnPlan p = bn_plan(S, C, B);
   float* partial = (float*)workspace;
   float* coef = partial + (size_t)p.chunks * C * 2;
+  const BnFusedPlan fp = bn_fused_plan(S, C, B, dtype_size(dtype));
+  if (fp.ok && (bn_fused_mask(dtype_size(dtype)) & 1) && aligned_to(y, 16) && aligned_to(x, 16)) {
+    uint8_t* fw = static_cast<uint8_t*>(workspace) + bn_classic_ws_bytes(S, C, B);
+    BnFusedArgs a{};
+    a.out = y; a.x = x; a.gamma = gamma; a.beta = beta; a.rmean = rmean; a.rvar = rvar;
+    a.new_rmean = new_rmean; a.new_rvar = new_rvar; a.save_mean = save_mean; a.save_inv = save_invstd;
+    a.counter = reinterpret_cast<unsigned int*>(fw);
+    a.cta_partial = reinterpret_cast<float*>(fw + 4096);
+    a.status = device_status_word();
+    LB2_REQUIRE(a.status != nullptr, LB2_LAUNCH_FAIL, "batchnorm: device status word unavailable");
+    a.S = S; a.C = C; a.B = B; a.gc = fp.gc_fwd; a.nsub = fp.nsub; a.momentum = (float)momentum; a.eps = (float)eps; a.act_rt = act;
+    LB2_DISPATCH_DTYPE(dtype, {
+      LB2_DISPATCH_ACT3(act, { return bn_fused_launch<T, false, ACT, false>(a, fp.grid, st); });
+    });
+  }
   LB2_DISPATCH_DTYPE(dtype, {
     bn_reduce_launch<T, 0, LB2_ACT_IDENTITY, false>(partial, (const T*)x, nullptr, nullptr, nullptr, nullptr, nullptr, S, C, B, p, act, st);
     LB2_CHECK_LAUNCH("batchnorm statistics");
@@ -516,6 +876,25 @@ int32_t lb2_batchnorm_bwd(void* dx, void* dgamma, void* dbeta, const void* dy, c
   const BnPlan p = bn_plan(S, C, B);
   float* partial = (float*)workspace;
   float* coef = partial + (size_t)p.chunks * C * 2;
+  const BnFusedPlan fp = bn_fused_plan(S, C, B, dtype_size(dtype));
+  if (fp.ok && (bn_fused_mask(dtype_size(dtype)) & 2) && aligned_to(dx, 16) && aligned_to(x, 16) && aligned_to(dy, 16)) {
+    uint8_t* fw = static_cast<uint8_t*>(workspace) + bn_classic_ws_bytes(S, C, B);
+    BnFusedArgs a{};
+    a.out = dx; a.x = x; a.dy = dy; a.gamma = gamma; a.beta = beta;
+    a.save_mean = const_cast<float*>(save_mean); a.save_inv = const_cast<float*>(save_invstd);
+    a.dgamma = dgamma; a.dbeta = dbeta;
+    a.counter = reinterpret_cast<unsigned int*>(fw);
+    a.cta_partial = reinterpret_cast<float*>(fw + 4096);
+    a.status = device_status_word();
+    LB2_REQUIRE(a.status != nullptr, LB2_LAUNCH_FAIL, "batchnorm: device status word unavailable");
+    a.S = S; a.C = C; a.B = B; a.gc = fp.gc_bwd; a.nsub = fp.nsub; a.act_rt = act;
+    LB2_DISPATCH_DTYPE(dtype, {
+      LB2_DISPATCH_ACT3(act, {
+        if (gamma) return bn_fused_launch<T, true, ACT, true>(a, fp.grid, st);
+        else return bn_fused_launch<T, true, ACT, false>(a, fp.grid, st);
+      });
+    });
+  }
   LB2_DISPATCH_DTYPE(dtype, {
     LB2_DISPATCH_ACT3(act, {
       if (gamma) bn_reduce_launch<T, 1, ACT, true>(partial, (const T*)x, (const T*)dy, (const T*)gamma, (const T*)beta, save_mean, save_invstd, S, C, B, p, act, st);

@@ -281,6 +281,20 @@ def test_conv_known_answers():
 @pytest.mark.parametrize("shape", [(4, 4, 6, 2), (8, 2), (64, 48), (12, 12, 16, 8), (7, 5, 3, 4)])
 @pytest.mark.parametrize("affine", [True, False])
 def test_batchnorm_train_fwd_bwd(dt, act, shape, affine):
+    _batchnorm_case(dt, act, shape, affine)
+
+
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("act", ["identity", "relu"])
+@pytest.mark.parametrize("shape", [(96, 96, 40, 24), (256, 256, 4, 64)])
+def test_batchnorm_large_tensors_take_the_single_launch_path(dt, act, shape):
+    # above 16 MB the statistics and the normalisation run in one cooperative launch, one L2-sized group of
+    # channels at a time; these shapes give one and several groups in either direction
+    _batchnorm_case(dt, act, shape, True)
+    assert L._cabi.load().lb2_poll_device_status(None) == 0
+
+
+def _batchnorm_case(dt, act, shape, affine):
     rng = np.random.default_rng(15)
     c = shape[-2]
     x = prep(rng.standard_normal(shape) * rng.uniform(0.5, 2, (c, 1)) + 0.3, dt)
@@ -416,3 +430,76 @@ def test_float64_is_left_to_the_caller():
     x = torch.zeros(4, 4, dtype=torch.float64, device="cuda")
     with pytest.raises(L.LuxLibB200Error):
         L.fast_activation("relu", x)
+
+
+# ------------------------------------------------------------------------------------------
+# whole configurations, chained through the rrules (small versions of the benchmark configs)
+# ------------------------------------------------------------------------------------------
+def test_config_mlp_forward_backward_of_mse():
+    """Dense(784 -> 256, relu) -> Dense(256 -> 10), Float32, batch 128, mean-squared error against one-hot targets:
+    loss, and the gradients of both layers' parameters and of the input, against the CPU restatement."""
+    rng = np.random.default_rng(0)
+    W1, W2 = O.glorot_uniform(rng, (256, 784)), O.glorot_uniform(rng, (10, 256))
+    b1, b2 = np.zeros(256, np.float32), np.zeros(10, np.float32)
+    x = rng.standard_normal((784, 128)).astype(np.float32)
+    t = np.zeros((10, 128), np.float32)
+    t[rng.integers(0, 10, 128), np.arange(128)] = 1.0
+
+    h_ref, pb1_ref = O.fused_dense_rrule("relu", W1, x, b1)
+    y_ref, pb2_ref = O.fused_dense_rrule("identity", W2, h_ref, b2)
+    loss_ref = np.mean((y_ref.astype(np.float64) - t) ** 2)
+    dy_ref = (2.0 * (y_ref - t) / y_ref.size).astype(np.float32)
+    dW2_ref, dh_ref, db2_ref = pb2_ref(dy_ref)
+    dW1_ref, dx_ref, db1_ref = pb1_ref(dh_ref)
+
+    h, pb1 = L.rrule_fused_dense("relu", dev(W1, "f32"), dev(x, "f32"), dev(b1, "f32"))
+    y, pb2 = L.rrule_fused_dense("identity", dev(W2, "f32"), h, dev(b2, "f32"))
+    check(y, y_ref, "f32", "y")
+    tt = dev(t, "f32")
+    loss = float(((y - tt).double() ** 2).mean())
+    assert abs(loss - loss_ref) <= 1e-5 * abs(loss_ref)
+    dy = 2.0 * (y - tt) / y.numel()
+    dW2, dh, db2 = pb2(dy)
+    dW1, dx, db1 = pb1(dh)
+    for got, ref, name in ((dW2, dW2_ref, "dW2"), (db2, db2_ref, "db2"), (dW1, dW1_ref, "dW1"), (db1, db1_ref, "db1"),
+                           (dx, dx_ref, "dx")):
+        check(got, ref, "f32", name)
+
+
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+def test_config_conv_batchnorm_relu_block(dt):
+    """Conv 3x3 64 -> 64 (stride 1, pad 1) -> BatchNorm(64) in training mode -> relu on a small WHCN input:
+    output, running statistics and the gradients of x, filter, bias, gamma and beta."""
+    rng = np.random.default_rng(2)
+    x = prep(rng.standard_normal((16, 12, 64, 4)), dt)
+    w = prep(O.kaiming_normal(rng, (3, 3, 64, 64)), dt)
+    b = prep(np.zeros(64), dt)
+    gam, bet = prep(np.ones(64), dt), prep(np.zeros(64), dt)
+    rm, rv = prep(np.zeros(64), dt), prep(np.ones(64), dt)
+    ocd, lcd = O.ConvDims.make(2, 1, 1, 1, 1, False), L.ConvDims.make(2, 1, 1, 1, 1, False)
+
+    c_ref, pbc_ref = O.fused_conv_rrule("identity", w, x, b, ocd)
+    c_in = prep(c_ref, dt)   # the conv output as the next op sees it in this storage type
+    z_ref, (rm_ref, rv_ref), pbn_ref = O.batchnorm_rrule(c_in, gam, bet, rm, rv, True, "relu", 0.1, 1e-5)
+    delta = prep(rng.standard_normal(z_ref.shape), dt)
+    dc_ref, dg_ref, dbt_ref = pbn_ref(delta)
+    dw_ref, dx_ref, db_ref = pbc_ref(prep(dc_ref, dt))
+
+    c, pbc = L.rrule_fused_conv("identity", dev(w, dt), dev(x, dt), dev(b, dt), lcd)
+    check(c, c_ref, dt, "conv")
+    # the block's tail is judged on the reference's conv output so that storage rounding of c does not stack up
+    z, (nrm, nrv), pbn = L.rrule_batchnorm(dev(c_in, dt), dev(gam, dt), dev(bet, dt), dev(rm, dt), dev(rv, dt), True,
+                                           "relu", 0.1, 1e-5)
+    check(z, z_ref, dt, "y")
+    check(nrm, rm_ref, dt, "running_mean", tol=1e-5 if dt == "f32" else None)
+    check(nrv, rv_ref, dt, "running_var", tol=1e-5 if dt == "f32" else None)
+    dc, dg, dbt = pbn(dev(delta, dt))
+    check(dg, dg_ref, dt, "dgamma")
+    check(dbt, dbt_ref, dt, "dbeta")
+    dw, dx, db = pbc(dev(prep(dc_ref, dt), dt))
+    check(dw, dw_ref, dt, "dw")
+    check(dx, dx_ref, dt, "dx")
+    # BatchNorm's input gradient sums to zero over each channel, so the conv bias gradient is pure cancellation:
+    # judge it on the size of the terms that cancel
+    check(db, db_ref, dt, "db", scale=np.abs(dc_ref).sum(axis=(0, 1, 3)))
+    assert L._cabi.load().lb2_poll_device_status(None) == 0
