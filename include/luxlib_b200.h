@@ -211,6 +211,63 @@ LB2_API int32_t lb2_batchnorm_bwd(void* dx, void* dgamma, void* dbeta, const voi
                           const float* save_invstd, int64_t S, int64_t C, int64_t B, int32_t dtype,
                           int32_t act, void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---- pooling ------------------------------------------------------------------------------- */
+/* Max / mean pooling on WHCN arrays: x (in..., channels, batch) -> y (out..., channels, batch). Backs the
+ * pooling layers of src/layers/pooling.jl:42-57 (NNlib.maxpool / NNlib.meanpool with a PoolDims; the global
+ * pools are the window == input case). NNlib CPU semantics: windows are clipped to the input, the mean divides
+ * by the full window size, the max-pool gradient goes to the first window element equal to the maximum
+ * (kw fastest). lb2_pool_bwd: dx from dy (and y, x for max pooling; both may be NULL for mean pooling). */
+enum { LB2_POOL_MAX = 0, LB2_POOL_MEAN = 1 };
+typedef struct lb2_pool_desc {
+  int32_t ndim;          /* spatial dims, 1..3 */
+  int32_t in[3];
+  int32_t k[3];
+  int32_t stride[3];
+  int32_t pad_lo[3];
+  int32_t pad_hi[3];
+  int32_t dilation[3];
+  int32_t channels;
+  int32_t batch;
+} lb2_pool_desc;
+LB2_API int32_t lb2_pool_output_size(const lb2_pool_desc* desc, int32_t* out);
+LB2_API int32_t lb2_pool_fwd(void* y, const void* x, const lb2_pool_desc* desc, int32_t kind, int32_t dtype, void* stream);
+LB2_API int32_t lb2_pool_bwd(void* dx, const void* dy, const void* y, const void* x, const lb2_pool_desc* desc,
+                          int32_t kind, int32_t dtype, void* stream);
+
+/* ---- optimiser step for a bucket of leaves ------------------------------------------------ */
+/* The leaf loop that Optimisers.update! runs under DistributedOptimizer
+ * (src/distributed/public_api.jl:270-278: allreduce!(backend, grad, avg) then apply! of the wrapped rule;
+ * src/helpers/training.jl:241-245) as ONE launch per bucket of leaves, issued right after the bucket's
+ * all-reduce. grad_scale multiplies every gradient first (1/world turns a sum all-reduce into the average).
+ * Rules as in Optimisers.jl 0.4.6 (Descent, Momentum, Adam); state arrays have the parameter's dtype;
+ * `master` (optional, fp32, same length) is updated in full precision and the parameter re-rounded from it.
+ * `step` counts from 1 (Adam bias correction 1 - beta^step). `leaves` is a HOST array of device pointers. */
+enum { LB2_OPT_DESCENT = 0, LB2_OPT_MOMENTUM = 1, LB2_OPT_ADAM = 2 };
+typedef struct lb2_opt_leaf {
+  void* param;
+  const void* grad;
+  void* state1;   /* Momentum: velocity; Adam: first moment; Descent: NULL */
+  void* state2;   /* Adam: second moment; otherwise NULL */
+  float* master;  /* optional fp32 master copy, or NULL */
+  int64_t n;
+} lb2_opt_leaf;
+LB2_API int32_t lb2_optimizer_step(const lb2_opt_leaf* leaves, int32_t n_leaves, int32_t rule, double eta,
+                          double rho_or_beta1, double beta2, double eps, int64_t step, double grad_scale,
+                          int32_t dtype, void* stream);
+
+/* ---- instancenorm --------------------------------------------------------------------------- */
+/* LuxLib.instancenorm (lib/LuxLib/src/api/instancenorm.jl:32-77; generic normalization path,
+ * lib/LuxLib/src/impl/normalization.jl:148-208 with reduce_dims = 1..N-2) is served by the existing
+ * kernels: per-instance statistics = lb2_groupnorm_fwd / lb2_groupnorm_bwd with G = C, running
+ * statistics in test mode = lb2_batchnorm_fwd_infer. This entry point is the one missing piece, the
+ * running-statistics update of training mode (update_normalization_statistics,
+ * impl/normalization.jl:95-110): the per-(channel, sample) statistics saved by lb2_groupnorm_fwd
+ * (row b*C + c; variance recovered as 1/invstd^2 - eps) are averaged over the batch, then
+ *   new_rmean = (1-m) rmean + m mean_b(mu),  new_rvar = (1-m) rvar + m S/(S-1) mean_b(var). */
+LB2_API int32_t lb2_instancenorm_update_stats(void* new_rmean, void* new_rvar, const void* rmean, const void* rvar,
+                          const float* save_mean, const float* save_invstd, int64_t S, int64_t C,
+                          int64_t B, double momentum, double eps, int32_t dtype, void* stream);
+
 /* ---- groupnorm ----------------------------------------------------------------------------- */
 /* x viewed as (S, C/G, G, B) (lib/LuxLib/src/impl/groupnorm.jl:5-22,76-78); statistics per
  * (group, sample); save_mean / save_invstd are fp32 of length G*B. Replaces

@@ -664,6 +664,27 @@ static int32_t gn_bwd_launch(T* dx, T* dg, T* db, const T* dy, const T* x, const
   return LB2_OK;
 }
 
+// InstanceNorm running statistics: one thread per channel walks the batch in order (deterministic).
+template <typename T>
+__global__ void in_update_stats_kernel(T* __restrict__ new_rmean, T* __restrict__ new_rvar, const T* __restrict__ rmean,
+                                       const T* __restrict__ rvar, const float* __restrict__ save_mean,
+                                       const float* __restrict__ save_inv, int64_t S, int64_t C, int64_t B,
+                                       float momentum, float eps) {
+  const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  float sm = 0.f, sv = 0.f;
+  for (int64_t b = 0; b < B; ++b) {
+    const float inv = save_inv[b * C + c];
+    sm += save_mean[b * C + c];
+    sv += 1.f / (inv * inv) - eps;
+  }
+  const float mu = sm / (float)B, var = sv / (float)B;
+  const float m = (float)S;
+  const float m1 = momentum, m2 = momentum * m / (m - 1.f), m3 = 1.f - m1;
+  new_rmean[c] = from_f32<T>(m3 * to_f32(rmean[c]) + m1 * mu);
+  new_rvar[c] = from_f32<T>(m3 * to_f32(rvar[c]) + m2 * var);
+}
+
 }  // namespace lb2
 
 using namespace lb2;
@@ -685,6 +706,25 @@ int32_t lb2_groupnorm_fwd(void* y, float* save_mean, float* save_invstd, const v
       else return gn_fwd_launch<T, ACT, false>((T*)y, save_mean, save_invstd, (const T*)x, nullptr, nullptr, S, C, G, B, (float)eps, act, st);
     });
   });
+  return LB2_OK;
+}
+
+int32_t lb2_instancenorm_update_stats(void* new_rmean, void* new_rvar, const void* rmean, const void* rvar,
+                                      const float* save_mean, const float* save_invstd, int64_t S, int64_t C, int64_t B,
+                                      double momentum, double eps, int32_t dtype, void* stream) {
+  LB2_REQUIRE(S >= 0 && C >= 0 && B >= 0, LB2_BAD_SHAPE, "bad extent");
+  LB2_REQUIRE(valid_dtype(dtype), LB2_UNSUPPORTED_DTYPE, "dtype %d not supported", (int)dtype);
+  if (C == 0) return LB2_OK;
+  LB2_REQUIRE(new_rmean && new_rvar && rmean && rvar, LB2_BAD_ARG, "null running-statistics pointer");
+  LB2_REQUIRE(B > 0 && S > 0, LB2_BAD_SHAPE, "running statistics need a non-empty batch");
+  LB2_REQUIRE(save_mean && save_invstd, LB2_BAD_ARG, "saved statistics are null");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  LB2_DISPATCH_DTYPE(dtype, {
+    in_update_stats_kernel<T><<<(unsigned)((C + 127) / 128), 128, 0, st>>>((T*)new_rmean, (T*)new_rvar, (const T*)rmean,
+                                                                          (const T*)rvar, save_mean, save_invstd, S, C, B,
+                                                                          (float)momentum, (float)eps);
+  });
+  LB2_CHECK_LAUNCH("instancenorm_update_stats");
   return LB2_OK;
 }
 

@@ -1,0 +1,208 @@
+// Max / mean pooling, forward and backward, on the WHCN (column-major) layout — the glue between the
+// conv blocks of a conv net (src/layers/pooling.jl:42-54 -> NNlib.maxpool / NNlib.meanpool, and the
+// global pools of :47-48,56-57 as the window == input case).
+//
+// Semantics follow NNlib's direct CPU kernels (NNlib 0.9, a dependency of the reference, not
+// vendored): windows are clipped to the input (padding never wins a max), the mean always divides
+// by the full window size, and the max-pool gradient goes to the FIRST element of the window that
+// equals the maximum, scanning kw fastest, then kh, then kd.
+// Bandwidth-bound: one thread per output (forward) / per input (backward, a gather over the windows
+// that cover it, so the sums are formed in a fixed order: deterministic, no atomics).
+#include "common.cuh"
+
+namespace lb2 {
+
+struct PoolGeom {
+  int in[3], k[3], stride[3], pad[3], dil[3], out[3];
+  int64_t planes;   // channels * batch
+};
+
+template <typename T, bool MAX>
+__global__ void __launch_bounds__(256) pool_fwd_kernel(T* __restrict__ y, const T* __restrict__ x, const PoolGeom g) {
+  const int64_t out_sp = (int64_t)g.out[0] * g.out[1] * g.out[2];
+  const int64_t in_sp = (int64_t)g.in[0] * g.in[1] * g.in[2];
+  const int64_t total = out_sp * g.planes;
+  const float inv_win = 1.f / (float)(g.k[0] * g.k[1] * g.k[2]);
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t r = i;
+    const int ow = (int)(r % g.out[0]); r /= g.out[0];
+    const int oh = (int)(r % g.out[1]); r /= g.out[1];
+    const int od = (int)(r % g.out[2]);
+    const int64_t plane = r / g.out[2];
+    const T* xp = x + plane * in_sp;
+    float acc = MAX ? -INFINITY : 0.f;
+    for (int kd = 0; kd < g.k[2]; ++kd) {
+      const int d = od * g.stride[2] - g.pad[2] + kd * g.dil[2];
+      if (d < 0 || d >= g.in[2]) continue;
+      for (int kh = 0; kh < g.k[1]; ++kh) {
+        const int h = oh * g.stride[1] - g.pad[1] + kh * g.dil[1];
+        if (h < 0 || h >= g.in[1]) continue;
+        for (int kw = 0; kw < g.k[0]; ++kw) {
+          const int w = ow * g.stride[0] - g.pad[0] + kw * g.dil[0];
+          if (w < 0 || w >= g.in[0]) continue;
+          const float v = to_f32(xp[((int64_t)d * g.in[1] + h) * g.in[0] + w]);
+          if (MAX) acc = fmaxf(acc, v); else acc += v;
+        }
+      }
+    }
+    y[i] = from_f32<T>(MAX ? acc : acc * inv_win);
+  }
+}
+
+// Does the window of output (ow, oh, od) give its max-pool gradient to input (w, h, d)? True when that
+// input is the first element, in (kw fastest, kh, kd) order, equal to the window maximum ymax.
+template <typename T>
+__device__ __forceinline__ bool first_max_is(const T* xp, const PoolGeom& g, int ow, int oh, int od, float ymax, int w, int h,
+                                             int d) {
+  for (int kd = 0; kd < g.k[2]; ++kd) {
+    const int dd = od * g.stride[2] - g.pad[2] + kd * g.dil[2];
+    if (dd < 0 || dd >= g.in[2]) continue;
+    for (int kh = 0; kh < g.k[1]; ++kh) {
+      const int hh = oh * g.stride[1] - g.pad[1] + kh * g.dil[1];
+      if (hh < 0 || hh >= g.in[1]) continue;
+      for (int kw = 0; kw < g.k[0]; ++kw) {
+        const int ww = ow * g.stride[0] - g.pad[0] + kw * g.dil[0];
+        if (ww < 0 || ww >= g.in[0]) continue;
+        if (to_f32(xp[((int64_t)dd * g.in[1] + hh) * g.in[0] + ww]) == ymax) return ww == w && hh == h && dd == d;
+      }
+    }
+  }
+  return false;
+}
+
+template <typename T, bool MAX>
+__global__ void __launch_bounds__(256) pool_bwd_kernel(T* __restrict__ dx, const T* __restrict__ dy, const T* __restrict__ y,
+                                                       const T* __restrict__ x, const PoolGeom g) {
+  const int64_t out_sp = (int64_t)g.out[0] * g.out[1] * g.out[2];
+  const int64_t in_sp = (int64_t)g.in[0] * g.in[1] * g.in[2];
+  const int64_t total = in_sp * g.planes;
+  const float inv_win = 1.f / (float)(g.k[0] * g.k[1] * g.k[2]);
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t r = i;
+    const int w = (int)(r % g.in[0]); r /= g.in[0];
+    const int h = (int)(r % g.in[1]); r /= g.in[1];
+    const int d = (int)(r % g.in[2]);
+    const int64_t plane = r / g.in[2];
+    const T* xp = x + plane * in_sp;
+    const T* yp = y + plane * out_sp;
+    const T* dyp = dy + plane * out_sp;
+    float acc = 0.f;
+    // outputs whose window holds this input: o*stride - pad + kk*dil == coordinate, kk in [0, k)
+    for (int kd = 0; kd < g.k[2]; ++kd) {
+      const int nd = d + g.pad[2] - kd * g.dil[2];
+      if (nd < 0 || nd % g.stride[2] != 0) continue;
+      const int od = nd / g.stride[2];
+      if (od >= g.out[2]) continue;
+      for (int kh = 0; kh < g.k[1]; ++kh) {
+        const int nh = h + g.pad[1] - kh * g.dil[1];
+        if (nh < 0 || nh % g.stride[1] != 0) continue;
+        const int oh = nh / g.stride[1];
+        if (oh >= g.out[1]) continue;
+        for (int kw = 0; kw < g.k[0]; ++kw) {
+          const int nw = w + g.pad[0] - kw * g.dil[0];
+          if (nw < 0 || nw % g.stride[0] != 0) continue;
+          const int ow = nw / g.stride[0];
+          if (ow >= g.out[0]) continue;
+          const int64_t o = ((int64_t)od * g.out[1] + oh) * g.out[0] + ow;
+          if (MAX) {
+            if (first_max_is(xp, g, ow, oh, od, to_f32(yp[o]), w, h, d)) acc += to_f32(dyp[o]);
+          } else {
+            acc += to_f32(dyp[o]) * inv_win;
+          }
+        }
+      }
+    }
+    dx[i] = from_f32<T>(acc);
+  }
+}
+
+static int32_t make_pool_geom(const lb2_pool_desc* d, PoolGeom* g) {
+  LB2_REQUIRE(d != nullptr, LB2_BAD_ARG, "pool descriptor is null");
+  LB2_REQUIRE(d->ndim >= 1 && d->ndim <= 3, LB2_BAD_SHAPE, "spatial rank %d not in 1..3", (int)d->ndim);
+  LB2_REQUIRE(d->channels >= 0 && d->batch >= 0, LB2_BAD_SHAPE, "bad channel / batch extents");
+  for (int i = 0; i < 3; ++i) {
+    const bool live = i < d->ndim;
+    g->in[i] = live ? d->in[i] : 1;
+    g->k[i] = live ? d->k[i] : 1;
+    g->stride[i] = live ? d->stride[i] : 1;
+    g->pad[i] = live ? d->pad_lo[i] : 0;
+    g->dil[i] = live ? d->dilation[i] : 1;
+    const int pad_hi = live ? d->pad_hi[i] : 0;
+    LB2_REQUIRE(g->in[i] >= 0 && g->k[i] >= 1 && g->stride[i] >= 1 && g->dil[i] >= 1 && g->pad[i] >= 0 && pad_hi >= 0, LB2_BAD_SHAPE,
+                "bad extent / window / stride / dilation / padding in dim %d", i);
+    const int span = g->in[i] + g->pad[i] + pad_hi - g->dil[i] * (g->k[i] - 1) - 1;
+    g->out[i] = span < 0 ? 0 : span / g->stride[i] + 1;
+  }
+  g->planes = (int64_t)d->channels * d->batch;
+  return LB2_OK;
+}
+
+static unsigned pool_grid(int64_t total) {
+  int64_t gsz = (total + 255) / 256, cap = (int64_t)sm_count() * 16;
+  return (unsigned)(gsz < 1 ? 1 : (gsz > cap ? cap : gsz));
+}
+
+}  // namespace lb2
+
+using namespace lb2;
+
+extern "C" {
+
+int32_t lb2_pool_output_size(const lb2_pool_desc* d, int32_t* out) {
+  PoolGeom g;
+  int32_t rc = make_pool_geom(d, &g);
+  if (rc != LB2_OK) return rc;
+  LB2_REQUIRE(out != nullptr, LB2_BAD_ARG, "out is null");
+  for (int i = 0; i < d->ndim; ++i) out[i] = g.out[i];
+  return LB2_OK;
+}
+
+int32_t lb2_pool_fwd(void* y, const void* x, const lb2_pool_desc* d, int32_t kind, int32_t dtype, void* stream) {
+  LB2_REQUIRE(valid_dtype(dtype), LB2_UNSUPPORTED_DTYPE, "dtype %d not supported", (int)dtype);
+  LB2_REQUIRE(kind == LB2_POOL_MAX || kind == LB2_POOL_MEAN, LB2_BAD_ARG, "unknown pooling kind %d", (int)kind);
+  PoolGeom g;
+  int32_t rc = make_pool_geom(d, &g);
+  if (rc != LB2_OK) return rc;
+  const int64_t total = (int64_t)g.out[0] * g.out[1] * g.out[2] * g.planes;
+  if (total == 0) return LB2_OK;
+  LB2_REQUIRE(y && x, LB2_BAD_ARG, "null tensor pointer");
+  LB2_REQUIRE(aligned_to(y, dtype_size(dtype)) && aligned_to(x, dtype_size(dtype)), LB2_BAD_ALIGN, "pointer not aligned to the element size");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  LB2_DISPATCH_DTYPE(dtype, {
+    if (kind == LB2_POOL_MAX) pool_fwd_kernel<T, true><<<pool_grid(total), 256, 0, st>>>((T*)y, (const T*)x, g);
+    else pool_fwd_kernel<T, false><<<pool_grid(total), 256, 0, st>>>((T*)y, (const T*)x, g);
+  });
+  LB2_CHECK_LAUNCH("pool_fwd");
+  return LB2_OK;
+}
+
+int32_t lb2_pool_bwd(void* dx, const void* dy, const void* y, const void* x, const lb2_pool_desc* d, int32_t kind,
+                     int32_t dtype, void* stream) {
+  LB2_REQUIRE(valid_dtype(dtype), LB2_UNSUPPORTED_DTYPE, "dtype %d not supported", (int)dtype);
+  LB2_REQUIRE(kind == LB2_POOL_MAX || kind == LB2_POOL_MEAN, LB2_BAD_ARG, "unknown pooling kind %d", (int)kind);
+  PoolGeom g;
+  int32_t rc = make_pool_geom(d, &g);
+  if (rc != LB2_OK) return rc;
+  const int64_t total = (int64_t)g.in[0] * g.in[1] * g.in[2] * g.planes;
+  if (total == 0) return LB2_OK;
+  LB2_REQUIRE(dx != nullptr, LB2_BAD_ARG, "dx is null");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t out_total = (int64_t)g.out[0] * g.out[1] * g.out[2] * g.planes;
+  if (out_total == 0) {
+    cudaMemsetAsync(dx, 0, (size_t)total * dtype_size(dtype), st);
+    return LB2_OK;
+  }
+  LB2_REQUIRE(dy != nullptr, LB2_BAD_ARG, "dy is null");
+  LB2_REQUIRE(kind == LB2_POOL_MEAN || (y && x), LB2_BAD_ARG, "max pooling needs y and x for its gradient");
+  const size_t es = dtype_size(dtype);
+  LB2_REQUIRE(aligned_to(dx, es) && aligned_to(dy, es) && aligned_to(y, es) && aligned_to(x, es), LB2_BAD_ALIGN,
+              "pointer not aligned to the element size");
+  LB2_DISPATCH_DTYPE(dtype, {
+    if (kind == LB2_POOL_MAX) pool_bwd_kernel<T, true><<<pool_grid(total), 256, 0, st>>>((T*)dx, (const T*)dy, (const T*)y, (const T*)x, g);
+    else pool_bwd_kernel<T, false><<<pool_grid(total), 256, 0, st>>>((T*)dx, (const T*)dy, nullptr, nullptr, g);
+  });
+  LB2_CHECK_LAUNCH("pool_bwd");
+  return LB2_OK;
+}
+
+}  // extern "C"

@@ -24,6 +24,26 @@ class ConvDesc(C.Structure):
     ]
 
 
+class PoolDesc(C.Structure):
+    """lb2_pool_desc"""
+    _fields_ = [
+        ("ndim", C.c_int32), ("in_", C.c_int32 * 3), ("k", C.c_int32 * 3), ("stride", C.c_int32 * 3),
+        ("pad_lo", C.c_int32 * 3), ("pad_hi", C.c_int32 * 3), ("dilation", C.c_int32 * 3),
+        ("channels", C.c_int32), ("batch", C.c_int32),
+    ]
+
+
+POOL_MAX, POOL_MEAN = 0, 1
+
+
+class OptLeaf(C.Structure):
+    """lb2_opt_leaf"""
+    _fields_ = [("param", C.c_void_p), ("grad", C.c_void_p), ("state1", C.c_void_p), ("state2", C.c_void_p),
+                ("master", C.c_void_p), ("n", C.c_int64)]
+
+
+OPT_DESCENT, OPT_MOMENTUM, OPT_ADAM = 0, 1, 2
+
 _p, _i64, _i32, _u32, _sz, _dbl = C.c_void_p, C.c_int64, C.c_int32, C.c_uint32, C.c_size_t, C.c_double
 _fp = C.c_void_p  # float* passed as raw device pointers
 
@@ -58,6 +78,11 @@ PROTOTYPES = {
     "lb2_groupnorm_fwd": (_i32, [_p, _fp, _fp, _p, _p, _p, _i64, _i64, _i64, _i64, _dbl, _i32, _i32, _p]),
     "lb2_groupnorm_bwd_workspace_bytes": (_sz, [_i64, _i64, _i64, _i64]),
     "lb2_groupnorm_bwd": (_i32, [_p, _p, _p, _p, _p, _p, _p, _fp, _fp, _i64, _i64, _i64, _i64, _i32, _i32, _p, _sz, _p]),
+    "lb2_pool_output_size": (_i32, [C.POINTER(PoolDesc), C.POINTER(C.c_int32)]),
+    "lb2_pool_fwd": (_i32, [_p, _p, C.POINTER(PoolDesc), _i32, _i32, _p]),
+    "lb2_pool_bwd": (_i32, [_p, _p, _p, _p, C.POINTER(PoolDesc), _i32, _i32, _p]),
+    "lb2_optimizer_step": (_i32, [C.POINTER(OptLeaf), _i32, _i32, _dbl, _dbl, _dbl, _dbl, _i64, _dbl, _i32, _p]),
+    "lb2_instancenorm_update_stats": (_i32, [_p, _p, _p, _p, _fp, _fp, _i64, _i64, _i64, _dbl, _dbl, _i32, _p]),
     "lb2_layernorm_fwd": (_i32, [_p, _fp, _fp, _p, _p, _p, _i64, _i64, _dbl, _i32, _i32, _p]),
     "lb2_layernorm_bwd_workspace_bytes": (_sz, [_i64, _i64]),
     "lb2_layernorm_bwd": (_i32, [_p, _p, _p, _p, _p, _p, _p, _fp, _fp, _i64, _i64, _i32, _i32, _p, _sz, _p]),

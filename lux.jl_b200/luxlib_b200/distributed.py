@@ -210,3 +210,92 @@ def allreduce_bucketed_(backend, grads: Sequence[torch.Tensor], op=avg, bucket_b
                 off += n
             start = end
     return grads
+
+
+class FusedOptimizer:
+    """The leaf loop of `Optimisers.update!` under `DistributedOptimizer`
+    (src/distributed/public_api.jl:270-278, src/helpers/training.jl:241-245) with one collective and one
+    optimiser launch per bucket: gradients of a bucket are summed across the workers in one flat
+    all-reduce, then `lb2_optimizer_step` updates every leaf of the bucket with the 1/world averaging
+    folded into the step. Rules: "descent", "momentum", "adam" (Optimisers.jl 0.4.6 definitions); state
+    arrays have the parameter's dtype; `master=True` keeps an fp32 master copy of bf16 parameters."""
+
+    RULES = {"descent": 0, "momentum": 1, "adam": 2}
+
+    def __init__(self, backend, rule: str = "adam", eta: float = 1e-3, rho: float = 0.9, beta=(0.9, 0.999),
+                 eps: float = 1e-8, master: bool = False, bucket_bytes: int = 64 << 20):
+        if rule not in self.RULES:
+            raise ValueError(f"unknown rule {rule!r}")
+        self.backend, self.rule, self.eta, self.rho, self.beta, self.eps = backend, rule, eta, rho, beta, eps
+        self.master, self.bucket_bytes = master, bucket_bytes
+        self.step_count = 0
+
+    def init(self, params: Sequence[torch.Tensor]):
+        """Optimisers.init per leaf."""
+        states = []
+        for p in params:
+            s1 = torch.zeros_like(p) if self.rule in ("momentum", "adam") else None
+            s2 = torch.zeros_like(p) if self.rule == "adam" else None
+            m = p.detach().to(torch.float32).clone() if (self.master and p.dtype != torch.float32) else None
+            states.append((s1, s2, m))
+        return states
+
+    def buckets(self, params: Sequence[torch.Tensor]):
+        """Leaf indices grouped by (dtype, device), split at bucket_bytes (order preserved)."""
+        groups: dict = {}
+        for i, p in enumerate(params):
+            groups.setdefault((p.dtype, p.device), []).append(i)
+        out = []
+        for idxs in groups.values():
+            cur, size = [], 0
+            for i in idxs:
+                nbytes = params[i].numel() * params[i].element_size()
+                if cur and size + nbytes > self.bucket_bytes:
+                    out.append(cur)
+                    cur, size = [], 0
+                cur.append(i)
+                size += nbytes
+            if cur:
+                out.append(cur)
+        return out
+
+    def update(self, states, params: Sequence[torch.Tensor], grads: Sequence[torch.Tensor]):
+        """In-place update of params and states from local gradients; returns states."""
+        from . import _cabi
+        from .arrays import current_stream, dtype_code
+        lib = _cabi.load()
+        world = total_workers(self.backend) if initialized() else 1
+        self.step_count += 1
+        for idxs in self.buckets(params):
+            chunk = [grads[i] for i in idxs]
+            if world > 1:
+                flat = torch.cat([_wire(t).reshape(-1) for t in chunk])
+                allreduce_(self.backend, flat, "sum")
+                views, off = [], 0
+                for t in chunk:
+                    views.append(flat[off:off + t.numel()])
+                    off += t.numel()
+            else:
+                views = [_wire(t).reshape(-1) for t in chunk]
+            leaves = (_cabi.OptLeaf * len(idxs))()
+            keep = []
+            for k, i in enumerate(idxs):
+                p = params[i]
+                pw = _wire(p)
+                if pw.data_ptr() != p.data_ptr() or not pw.is_contiguous():
+                    raise ValueError("parameters must be dense (column- or row-major contiguous)")
+                s1, s2, m = states[i]
+                gv = views[k] if views[k].is_contiguous() else views[k].contiguous()
+                keep.append(gv)
+                leaves[k].param = p.data_ptr()
+                leaves[k].grad = gv.data_ptr()
+                leaves[k].state1 = s1.data_ptr() if s1 is not None else None
+                leaves[k].state2 = s2.data_ptr() if s2 is not None else None
+                leaves[k].master = m.data_ptr() if m is not None else None
+                leaves[k].n = p.numel()
+            p0 = params[idxs[0]]
+            first = self.rho if self.rule == "momentum" else self.beta[0]
+            _cabi.check(lib.lb2_optimizer_step(leaves, len(idxs), self.RULES[self.rule], float(self.eta), float(first),
+                                               float(self.beta[1]), float(self.eps), self.step_count, 1.0 / world,
+                                               dtype_code(p0.dtype), current_stream(p0.device)))
+        return states

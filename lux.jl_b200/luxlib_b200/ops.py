@@ -236,6 +236,48 @@ def rrule_bias_activation(act: str, x, bias=None):
     return y, pullback
 
 
+def _add_act(code: int, X, Y):
+    lib = _cabi.load()
+    z = jl_empty(X.shape, X.dtype, X.device)
+    n = X.numel()
+    # the bias-activation kernel with one "channel" per element: z[e] = act(x[e] + y[e])
+    _cabi.check(lib.lb2_bias_act_fwd(ptr(z), ptr(X), ptr(Y), 1, n, 1, dtype_code(X.dtype), code, current_stream(X.device)))
+    return z
+
+
+def add_activation(act: str, x, y):
+    """act.(x .+ y) for two arrays of one shape: the residual join of a ResNet block
+    (perf/resnet/resnet.jl:6-7), on the bias-activation kernel."""
+    if tuple(x.shape) != tuple(y.shape):
+        raise DimensionMismatch("x and y must have the same shape")
+    x, y = _promote(x, y)
+    return _add_act(act_code(act), as_colmajor(x), as_colmajor(y))
+
+
+def rrule_add_activation(act: str, x, y):
+    """Forward + pullback Δ -> (∂x, ∂y) of act.(x .+ y); both inputs receive Δ .* act'."""
+    if tuple(x.shape) != tuple(y.shape):
+        raise DimensionMismatch("x and y must have the same shape")
+    lib = _cabi.load()
+    x, y = _promote(x, y)
+    X, Y = as_colmajor(x), as_colmajor(y)
+    code = act_code(act)
+    keep_pre = needs_preactivation(act)
+    pre = _add_act(_cabi.ACT_IDENTITY, X, Y) if keep_pre else None
+    z = _add_act(code, X, Y)
+
+    def pullback(delta):
+        d = as_colmajor(delta.to(X.dtype))
+        if code == _cabi.ACT_IDENTITY:
+            return d, d
+        g = jl_empty(X.shape, X.dtype, X.device)
+        _cabi.check(lib.lb2_act_bwd(ptr(g), ptr(d), None if keep_pre else ptr(z), ptr(pre), X.numel(), dtype_code(X.dtype), code,
+                                    current_stream(X.device)))
+        return g, g
+
+    return z, pullback
+
+
 # --------------------------------------------------------------------------------------------
 # convolution
 # --------------------------------------------------------------------------------------------
@@ -413,6 +455,138 @@ def rrule_batchnorm(x, scale, bias, running_mean, running_var, training: bool, a
         return dx, dg, db
 
     return y, stats, pullback
+
+
+@dataclass(frozen=True)
+class PoolDims:
+    """The fields of NNlib.PoolDims built by calculate_pool_dims (src/layers/pooling.jl:17-34)."""
+    kernel: Tuple[int, ...]
+    stride: Tuple[int, ...]
+    padding: Tuple[int, ...]   # (lo_1, hi_1, lo_2, hi_2, ...)
+    dilation: Tuple[int, ...]
+
+    @staticmethod
+    def make(kernel, stride=None, padding=0, dilation=1) -> "PoolDims":
+        k = tuple(int(q) for q in kernel) if isinstance(kernel, (tuple, list)) else (int(kernel),)
+        nd = len(k)
+
+        def tup(v, n):
+            return tuple(int(q) for q in v) if isinstance(v, (tuple, list)) else (int(v),) * n
+        s = k if stride is None else tup(stride, nd)   # NNlib: stride defaults to the window
+        d, p = tup(dilation, nd), tup(padding, 2 * nd)
+        if len(p) == nd:
+            p = tuple(q for v in p for q in (v, v))
+        if not (len(s) == nd and len(d) == nd and len(p) == 2 * nd):
+            raise DimensionMismatch("stride / dilation / padding rank does not match the window rank")
+        return PoolDims(k, s, p, d)
+
+    @staticmethod
+    def global_(x) -> "PoolDims":
+        """GlobalPoolMode (src/layers/pooling.jl:21-23): the window is the whole spatial extent."""
+        return PoolDims.make(tuple(x.shape[:-2]))
+
+    @staticmethod
+    def adaptive(x, out_size) -> "PoolDims":
+        """AdaptivePoolMode (src/layers/pooling.jl:29-34)."""
+        in_size = tuple(x.shape[:-2])
+        stride = tuple(i // o for i, o in zip(in_size, out_size))
+        kernel = tuple(i - (o - 1) * s for i, o, s in zip(in_size, out_size, stride))
+        return PoolDims.make(kernel, stride, 0, 1)
+
+
+def _pool_desc(x, pd: PoolDims) -> _cabi.PoolDesc:
+    nd = x.dim() - 2
+    if nd < 1 or nd > 3 or len(pd.kernel) != nd:
+        raise DimensionMismatch("PoolDims rank does not match the array (3 to 5 dims: spatial..., channels, batch)")
+    d = _cabi.PoolDesc()
+    d.ndim = nd
+    for i in range(3):
+        live = i < nd
+        d.in_[i] = x.shape[i] if live else 1
+        d.k[i] = pd.kernel[i] if live else 1
+        d.stride[i] = pd.stride[i] if live else 1
+        d.pad_lo[i] = pd.padding[2 * i] if live else 0
+        d.pad_hi[i] = pd.padding[2 * i + 1] if live else 0
+        d.dilation[i] = pd.dilation[i] if live else 1
+    d.channels, d.batch = x.shape[-2], x.shape[-1]
+    return d
+
+
+def _pool(kind: int, x, pd: PoolDims):
+    lib = _cabi.load()
+    X = as_colmajor(x)
+    d = _pool_desc(X, pd)
+    osz = (C.c_int32 * 3)()
+    _cabi.check(lib.lb2_pool_output_size(C.byref(d), osz))
+    y = jl_empty(tuple(osz[i] for i in range(d.ndim)) + (d.channels, d.batch), X.dtype, X.device)
+    dt = dtype_code(X.dtype)
+    _cabi.check(lib.lb2_pool_fwd(ptr(y), ptr(X), C.byref(d), kind, dt, current_stream(X.device)))
+
+    def pullback(delta):
+        dy = as_colmajor(delta.to(X.dtype))
+        if tuple(dy.shape) != tuple(y.shape):
+            raise DimensionMismatch("the cotangent must have the shape of the pooled output")
+        dx = jl_empty(X.shape, X.dtype, X.device)
+        _cabi.check(lib.lb2_pool_bwd(ptr(dx), ptr(dy), ptr(y), ptr(X), C.byref(d), kind, dt, current_stream(X.device)))
+        return dx
+
+    return y, pullback
+
+
+def maxpool(x, pd: PoolDims):
+    """NNlib.maxpool(x, pdims) as called by MaxPoolOp (src/layers/pooling.jl:44-46)."""
+    return _pool(_cabi.POOL_MAX, x, pd)[0]
+
+
+def meanpool(x, pd: PoolDims):
+    """NNlib.meanpool(x, pdims) as called by MeanPoolOp (src/layers/pooling.jl:53-55)."""
+    return _pool(_cabi.POOL_MEAN, x, pd)[0]
+
+
+def rrule_maxpool(x, pd: PoolDims):
+    """Forward + pullback Δ -> ∂x (NNlib.∇maxpool: the first maximal element of each window takes the gradient)."""
+    return _pool(_cabi.POOL_MAX, x, pd)
+
+
+def rrule_meanpool(x, pd: PoolDims):
+    """Forward + pullback Δ -> ∂x (NNlib.∇meanpool)."""
+    return _pool(_cabi.POOL_MEAN, x, pd)
+
+
+def instancenorm(x, scale, bias, running_mean=None, running_var=None, training: bool = True, act: str = "identity",
+                 momentum: float = 0.1, epsilon: Optional[float] = None):
+    """LuxLib.instancenorm — lib/LuxLib/src/api/instancenorm.jl:32-77. Returns y, (running_mean', running_var').
+    Per-instance statistics run on the groupnorm kernels with one channel per group; test mode with running
+    statistics is the batchnorm inference kernel; the running-statistics update of training mode
+    (lib/LuxLib/src/impl/normalization.jl:95-110) is lb2_instancenorm_update_stats."""
+    if x.dim() <= 2:
+        raise AssertionError(f"`ndims(x) = {x.dim()}` must be at least > 2.")
+    if (running_mean is None) != (running_var is None):
+        raise ArgumentError("running_mean and running_var must both be given or both be nothing")
+    if running_mean is not None and not training:
+        y, _ = batchnorm(x, scale, bias, running_mean, running_var, False, act, momentum, epsilon)
+        return y, (running_mean, running_var)
+    lib = _cabi.load()
+    Cc = x.shape[-2]
+    y, (X, sc, bi, sm, si, S, Cc, B, dt, code) = _groupnorm_fwd(x, scale, bias, Cc, act, epsilon)
+    if running_mean is None:
+        return y, (None, None)
+    if running_mean.shape[0] != Cc or running_var.shape[0] != Cc:
+        raise DimensionMismatch(f"length(running_mean) must equal the number of channels {Cc}")
+    eps = default_epsilon(X.dtype) if epsilon is None else float(epsilon)
+    rm, rv = running_mean.to(X.dtype), running_var.to(X.dtype)
+    nrm, nrv = torch.empty_like(rm), torch.empty_like(rv)
+    _cabi.check(lib.lb2_instancenorm_update_stats(ptr(nrm), ptr(nrv), ptr(rm), ptr(rv), ptr(sm), ptr(si), S, Cc, B,
+                                                  float(momentum), eps, dt, current_stream(X.device)))
+    return y, (nrm, nrv)
+
+
+def rrule_instancenorm(x, scale, bias, act: str = "identity", epsilon: Optional[float] = None):
+    """Forward + pullback Δ -> (∂x, ∂scale, ∂bias) of instancenorm with per-instance statistics (running
+    statistics are not differentiated, lib/LuxLib/src/impl/normalization.jl:108)."""
+    if x.dim() <= 2:
+        raise AssertionError(f"`ndims(x) = {x.dim()}` must be at least > 2.")
+    return rrule_groupnorm(x, scale, bias, x.shape[-2], act, epsilon)
 
 
 def _gn_sizes(x, groups):

@@ -563,6 +563,60 @@ def groupnorm_rrule(x, gamma, beta, groups: int, act="identity", eps=1e-5, gelu=
 
 
 # --------------------------------------------------------------------------- #
+# instancenorm
+# --------------------------------------------------------------------------- #
+def instancenorm(x, gamma, beta, rmean, rvar, training: bool, act="identity", momentum=0.1, eps=1e-5, gelu="tanh"):
+    """LuxLib.instancenorm — lib/LuxLib/src/api/instancenorm.jl:32-77 through the generic
+    `normalization` path (impl/normalization.jl:148-208) with reduce_dims = 1..N-2.
+
+    Statistics per (channel, sample) unless running statistics are given and training is false
+    (compute_batch_statistics, normalization.jl:116-143). In training mode with running statistics the
+    per-sample statistics are averaged over the batch before the update, and the variance correction
+    uses m = prod(size(x)[1:N-2]) (update_normalization_statistics, normalization.jl:95-110).
+    Returns y, (running_mean', running_var')."""
+    if x.ndim <= 2:
+        raise AssertionError(f"`ndims(x) = {x.ndim}` must be at least > 2.")   # api/instancenorm.jl:72-75
+    T = x.dtype.type
+    c, b = x.shape[-2], x.shape[-1]
+    if (gamma is None) != (beta is None):
+        raise ValueError("scale and bias must both be present or both be nothing")
+    x3 = x.reshape((-1, c, b), order="F")
+    S = x3.shape[0]
+    new_rmean, new_rvar = rmean, rvar
+    if rmean is not None and not training:
+        mu = rmean.astype(x.dtype)[None, :, None]
+        var = rvar.astype(x.dtype)[None, :, None]
+    else:
+        mu = x3.mean(axis=0, keepdims=True, dtype=x.dtype)
+        var = ((x3 - mu) ** 2).mean(axis=0, keepdims=True, dtype=x.dtype)
+        if rmean is not None:
+            mu_b = mu.mean(axis=2, dtype=x.dtype).reshape(-1)
+            var_b = var.mean(axis=2, dtype=x.dtype).reshape(-1)
+            m = T(S)
+            m1 = T(momentum)
+            m2 = T(momentum) * m / (m - T(1))
+            m3 = T(1) - m1
+            new_rmean = m3 * rmean + m1 * mu_b
+            new_rvar = m3 * rvar + m2 * var_b
+    # affine_normalize: normalization.jl:3-17
+    if gamma is None:
+        gp = T(1) / np.sqrt(var + T(eps))
+        bp = -mu * gp
+    else:
+        gp = gamma[None, :, None] / np.sqrt(var + T(eps))
+        bp = beta[None, :, None] - mu * gp
+    y = act_fn(act, x3 * gp + bp, gelu).reshape(x.shape, order="F")
+    return y, (new_rmean, new_rvar)
+
+
+def instancenorm_rrule(x, gamma, beta, act="identity", eps=1e-5, gelu="tanh"):
+    """Forward + pullback Δ -> (∂x, ∂scale, ∂bias) with per-instance statistics: the same arithmetic as
+    groupnorm with one channel per group (the statistics of impl/normalization.jl:116-121 chained through
+    the mean_var rule, impl/common_ops.jl:45-61)."""
+    return groupnorm_rrule(x, gamma, beta, x.shape[-2], act, eps, gelu)
+
+
+# --------------------------------------------------------------------------- #
 # layernorm (row case: dims = leading dims, γ/β of the row shape or None)
 # --------------------------------------------------------------------------- #
 def layernorm(x, gamma, beta, act="identity", dims=None, eps=1e-5, gelu="tanh"):
@@ -647,6 +701,115 @@ def glorot_uniform(rng: np.random.Generator, shape, gain=1.0, dtype=np.float32):
 def kaiming_normal(rng: np.random.Generator, shape, gain=math.sqrt(2.0), dtype=np.float32):
     fi, _ = nfan(shape)
     return (rng.standard_normal(shape) * (gain / math.sqrt(fi))).astype(dtype)
+
+
+# --------------------------------------------------------------------------- #
+# pooling (NNlib 0.9 direct CPU kernels, a dependency of the reference and not vendored; restated from
+# its published behaviour: windows clipped to the input, mean over the full window size, the max-pool
+# gradient to the first maximal element in (kw fastest, kh, kd) order). Call sites:
+# src/layers/pooling.jl:42-57.
+# --------------------------------------------------------------------------- #
+def _pool_setup(x, kernel, stride, padding, dilation):
+    nd = x.ndim - 2
+    k = tuple(kernel)
+    s = k if stride is None else ((stride,) * nd if np.isscalar(stride) else tuple(stride))
+    d = (dilation,) * nd if np.isscalar(dilation) else tuple(dilation)
+    p = (padding,) * (2 * nd) if np.isscalar(padding) else tuple(padding)
+    if len(p) == nd:
+        p = tuple(q for v in p for q in (v, v))
+    out = tuple((x.shape[i] + p[2 * i] + p[2 * i + 1] - d[i] * (k[i] - 1) - 1) // s[i] + 1 for i in range(nd))
+    return nd, k, s, d, p, out
+
+
+def _pool_windows(x, kernel, stride, padding, dilation):
+    """Yields (output index, list of input indices of the clipped window in kw-fastest order)."""
+    import itertools
+    nd, k, s, d, p, out = _pool_setup(x, kernel, stride, padding, dilation)
+    for o in itertools.product(*[range(n) for n in reversed(out)]):
+        o = tuple(reversed(o))
+        win = []
+        for kk in itertools.product(*[range(n) for n in reversed(k)]):
+            kk = tuple(reversed(kk))   # last spatial dim slowest, first (w) fastest
+            idx = tuple(o[i] * s[i] - p[2 * i] + kk[i] * d[i] for i in range(nd))
+            if all(0 <= idx[i] < x.shape[i] for i in range(nd)):
+                win.append(idx)
+        yield o, win
+
+
+def pool(kind: str, x, kernel, stride=None, padding=0, dilation=1):
+    """maxpool / meanpool forward."""
+    nd, k, s, d, p, out = _pool_setup(x, kernel, stride, padding, dilation)
+    y = np.zeros(out + x.shape[-2:], dtype=x.dtype)
+    T = x.dtype.type
+    for o, win in _pool_windows(x, kernel, stride, padding, dilation):
+        if kind == "max":
+            vals = np.stack([x[i] for i in win]) if win else np.full((1,) + x.shape[-2:], -np.inf, x.dtype)
+            y[o] = vals.max(axis=0)
+        else:
+            acc = np.zeros(x.shape[-2:], dtype=x.dtype)
+            for i in win:
+                acc = acc + x[i]
+            y[o] = acc * T(1.0 / float(np.prod(k)))
+    return y
+
+
+def pool_rrule(kind: str, x, kernel, stride=None, padding=0, dilation=1):
+    y = pool(kind, x, kernel, stride, padding, dilation)
+    nd, k, s, d, p, out = _pool_setup(x, kernel, stride, padding, dilation)
+
+    def pullback(dy):
+        dx = np.zeros_like(x)
+        T = x.dtype.type
+        for o, win in _pool_windows(x, kernel, stride, padding, dilation):
+            if kind == "max":
+                taken = np.zeros(x.shape[-2:], dtype=bool)
+                for i in win:
+                    hit = (x[i] == y[o]) & ~taken
+                    dx[i] += np.where(hit, dy[o], T(0))
+                    taken |= hit
+            else:
+                for i in win:
+                    dx[i] += dy[o] * T(1.0 / float(np.prod(k)))
+        return dx
+
+    return y, pullback
+
+
+# --------------------------------------------------------------------------- #
+# optimiser rules (Optimisers.jl 0.4.6 — a dependency of the reference, not vendored; restated from its
+# published rule definitions: Descent, Momentum, Adam). State lives in the parameter's dtype.
+# Call site: Optimisers.apply!(::DistributedOptimizer, ...) — src/distributed/public_api.jl:270-278.
+# --------------------------------------------------------------------------- #
+def optimiser_init(rule: str, x):
+    if rule == "descent":
+        return None
+    if rule == "momentum":
+        return np.zeros_like(x)
+    if rule == "adam":
+        return [np.zeros_like(x), np.zeros_like(x), 0]   # mt, vt, steps taken (beta^t carried implicitly)
+    raise ValueError(rule)
+
+
+def optimiser_apply(rule: str, state, x, dx, eta=1e-3, rho=0.9, beta=(0.9, 0.999), eps=1e-8):
+    """One `apply!` + subtraction: returns (state', x'). Arithmetic in the array's dtype."""
+    T = x.dtype.type
+    if rule == "descent":
+        return None, x - T(eta) * dx
+    if rule == "momentum":
+        v = T(rho) * state + T(eta) * dx
+        return v, x - v
+    if rule == "adam":
+        mt, vt, t = state
+        b1, b2 = T(beta[0]), T(beta[1])
+        mt = b1 * mt + (T(1) - b1) * dx
+        vt = b2 * vt + (T(1) - b2) * dx * dx
+        t += 1
+        b1t, b2t = T(1), T(1)
+        for _ in range(t):
+            b1t, b2t = b1t * b1, b2t * b2
+        step = mt / (T(1) - b1t) / (np.sqrt(vt / (T(1) - b2t)) + T(eps)) * T(eta)
+        return [mt, vt, t], x - step
+    raise ValueError(rule)
 
 
 def generate_fixed_array(shape, dtype=np.float32):

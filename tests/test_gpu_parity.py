@@ -374,6 +374,48 @@ def test_groupnorm_fwd_bwd(dt, act, shape, groups, affine):
     check(db, db_ref, dt, "dbeta")
 
 
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("act", ["identity", "relu"])
+@pytest.mark.parametrize("shape", [(4, 4, 6, 2), (16, 16, 8, 3), (7, 5, 3), (64, 64, 4, 2)])
+@pytest.mark.parametrize("affine", [True, False])
+def test_instancenorm_all_modes(dt, act, shape, affine):
+    # lib/LuxLib/test/normalization/instancenorm_tests.jl:18-80: without running statistics, with them in
+    # training mode (updated statistics returned) and in test mode (statistics used as they are)
+    rng = np.random.default_rng(21)
+    c = shape[-2]
+    x = prep(rng.standard_normal(shape) * 1.5 + 0.3, dt)
+    g = prep(rng.uniform(0.5, 1.5, c), dt) if affine else None
+    b = prep(rng.standard_normal(c) * 0.1, dt) if affine else None
+    rm, rv = prep(rng.uniform(0, 1, c), dt), prep(rng.standard_normal(c) ** 2 + 0.1, dt)
+    y_ref, _ = O.instancenorm(x, g, b, None, None, True, act, 0.1, 1e-5)
+    y, stats = L.instancenorm(dev(x, dt), dev(g, dt), dev(b, dt), None, None, True, act, 0.1, 1e-5)
+    check(y, y_ref, dt, "y")
+    assert stats == (None, None)
+    y_ref, (rm_ref, rv_ref) = O.instancenorm(x, g, b, rm, rv, True, act, 0.1, 1e-5)
+    y, (nrm, nrv) = L.instancenorm(dev(x, dt), dev(g, dt), dev(b, dt), dev(rm, dt), dev(rv, dt), True, act, 0.1, 1e-5)
+    check(y, y_ref, dt, "y (training, running statistics)")
+    check(nrm, rm_ref, dt, "running_mean", tol=1e-5 if dt == "f32" else None)
+    check(nrv, rv_ref, dt, "running_var", tol=1e-5 if dt == "f32" else None)
+    y_ref, _ = O.instancenorm(x, g, b, rm, rv, False, act, 0.1, 1e-5)
+    y, (srm, srv) = L.instancenorm(dev(x, dt), dev(g, dt), dev(b, dt), dev(rm, dt), dev(rv, dt), False, act, 0.1, 1e-5)
+    check(y, y_ref, dt, "y (test mode)")
+    check(srm, rm, dt, "running_mean unchanged")
+    z_ref, pb_ref = O.instancenorm_rrule(x, g, b, act, 1e-5)
+    z, pb = L.rrule_instancenorm(dev(x, dt), dev(g, dt), dev(b, dt), act, 1e-5)
+    check(z, z_ref, dt, "z")
+    delta = prep(rng.standard_normal(shape), dt)
+    dx_ref, dg_ref, db_ref = pb_ref(delta)
+    dx, dg, db = pb(dev(delta, dt))
+    check(dx, dx_ref, dt, "dx", scale=delta)
+    check(dg, dg_ref, dt, "dgamma")
+    check(db, db_ref, dt, "dbeta")
+
+
+def test_instancenorm_needs_three_dims():
+    with pytest.raises(AssertionError):
+        L.instancenorm(L.jl_zeros((4, 3), torch.float32, "cuda"), None, None)
+
+
 def test_groupnorm_errors():
     x = L.jl_zeros((4, 4, 6, 2), torch.float32, "cuda")
     with pytest.raises(L.ArgumentError):
@@ -503,3 +545,89 @@ def test_config_conv_batchnorm_relu_block(dt):
     # judge it on the size of the terms that cancel
     check(db, db_ref, dt, "db", scale=np.abs(dc_ref).sum(axis=(0, 1, 3)))
     assert L._cabi.load().lb2_poll_device_status(None) == 0
+
+
+# ------------------------------------------------------------------------------------------
+# optimiser step for a bucket of leaves (the update that follows the gradient all-reduce)
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("rule", ["descent", "momentum", "adam"])
+def test_fused_optimizer_matches_the_rule_definitions(dt, rule):
+    from luxlib_b200 import distributed as D
+    rng = np.random.default_rng(31)
+    shapes = [(33,), (64, 48), (3, 3, 8, 16), (5000,), (1,)] + [(17, 3)] * 60   # more leaves than one launch holds
+    params = [prep(rng.standard_normal(s), dt) for s in shapes]
+    opt = D.FusedOptimizer(D.NCCLBackend, rule, eta=0.05, rho=0.9, beta=(0.9, 0.999), eps=1e-8)
+    dparams = [dev(p, dt) for p in params]
+    states = opt.init(dparams)
+    ostates = [O.optimiser_init(rule, p.astype(np.float64)) for p in params]
+    oparams = [p.astype(np.float64) for p in params]
+    for _ in range(3):
+        grads = [prep(rng.standard_normal(s), dt) for s in shapes]
+        opt.update(states, dparams, [dev(g, dt) for g in grads])
+        for i, g in enumerate(grads):
+            ostates[i], oparams[i] = O.optimiser_apply(rule, ostates[i], oparams[i], g.astype(np.float64), 0.05, 0.9,
+                                                       (0.9, 0.999), 1e-8)
+    for i in (0, 1, 2, 3, 4, 30, 64):
+        check(dparams[i], oparams[i], dt, f"param {i}", tol=2e-6 if dt == "f32" else 2e-2)
+
+
+def test_fused_optimizer_master_copy_keeps_small_updates():
+    # bf16 parameter 1.0 with updates of 1e-4: without an fp32 master copy every step rounds away
+    from luxlib_b200 import distributed as D
+    p = torch.ones(1024, device="cuda", dtype=torch.bfloat16)
+    g = torch.ones(1024, device="cuda", dtype=torch.bfloat16)
+    opt = D.FusedOptimizer(D.NCCLBackend, "descent", eta=1e-4, master=True)
+    st = opt.init([p])
+    for _ in range(100):
+        opt.update(st, [p], [g])
+    assert abs(float(st[0][2][0]) - 0.99) < 1e-5          # the master copy took all 100 steps
+    assert abs(float(p[0]) - 0.99) < 4e-3                 # the parameter is its rounding
+
+
+# ------------------------------------------------------------------------------------------
+# pooling
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("kind", ["max", "mean"])
+@pytest.mark.parametrize("shape,k,stride,pad", [((8, 8, 3, 2), (2, 2), None, 0), ((9, 7, 4, 3), (3, 3), (2, 2), 1),
+                                                ((12, 10, 2, 2), (3, 2), (1, 2), (1, 2, 0, 1)), ((14, 5, 2), (3,), (2,), 1),
+                                                ((6, 5, 4, 3, 2), (2, 2, 2), None, 0), ((7, 7, 8, 2), (7, 7), None, 0)])
+def test_pooling_fwd_bwd(dt, kind, shape, k, stride, pad):
+    rng = np.random.default_rng(33)
+    x = prep(rng.standard_normal(shape), dt)
+    y_ref, pb_ref = O.pool_rrule(kind, x, k, stride, pad)
+    pd = L.PoolDims.make(k, stride, pad)
+    y, pb = (L.rrule_maxpool if kind == "max" else L.rrule_meanpool)(dev(x, dt), pd)
+    check(y, y_ref, dt, "y")
+    dy = prep(rng.standard_normal(y_ref.shape), dt)
+    check(pb(dev(dy, dt)), pb_ref(dy), dt, "dx")
+
+
+def test_maxpool_ties_and_global_pools():
+    x = L.jl_zeros((4, 4, 1, 1), torch.float32, "cuda")
+    y, pb = L.rrule_maxpool(x, L.PoolDims.make((2, 2)))
+    dx = L.to_numpy(pb(torch.ones_like(y)))
+    assert dx[0, 0, 0, 0] == 1 and dx[1, 0, 0, 0] == 0 and dx[0, 1, 0, 0] == 0 and dx.sum() == 4
+    xn = np.random.default_rng(34).standard_normal((5, 6, 3, 2)).astype(np.float32)
+    xg = L.from_numpy(xn)
+    np.testing.assert_allclose(L.to_numpy(L.meanpool(xg, L.PoolDims.global_(xg)))[0, 0], xn.mean(axis=(0, 1)), rtol=1e-6, atol=1e-7)
+    np.testing.assert_allclose(L.to_numpy(L.maxpool(xg, L.PoolDims.global_(xg)))[0, 0], xn.max(axis=(0, 1)))
+    assert L.PoolDims.adaptive(xg, (2, 3)).kernel == (3, 2)
+
+
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("act", ["identity", "relu", "gelu"])
+def test_residual_add_activation(dt, act):
+    # act.(x .+ y), the join of a residual block (perf/resnet/resnet.jl:6-7)
+    rng = np.random.default_rng(35)
+    x, y = prep(rng.standard_normal((9, 7, 5, 3)), dt), prep(rng.standard_normal((9, 7, 5, 3)), dt)
+    s = prep(x + y, dt) if dt == "f32" else (x + y)   # the kernel adds in fp32
+    z_ref = O.act_fn(act, s.astype(np.float32))
+    z, pb = L.rrule_add_activation(act, dev(x, dt), dev(y, dt))
+    check(z, z_ref, dt, "z")
+    delta = prep(rng.standard_normal(x.shape), dt)
+    dx, dy = pb(dev(delta, dt))
+    ref = O.grad_activation(delta, prep(z_ref, dt), act, s.astype(np.float32))
+    check(dx, ref, dt, "dx")
+    check(dy, ref, dt, "dy")

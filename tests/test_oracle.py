@@ -259,6 +259,74 @@ def test_norms_match_torch():
     np.testing.assert_allclose(O.layernorm(x2, g2, b2, "identity", None, 1e-5).T, ref.numpy(), atol=1e-10)
 
 
+def test_instancenorm_matches_torch_and_the_running_statistics_rule():
+    # independent cross-check of the restated generic normalization path (impl/normalization.jl:95-143)
+    rng = np.random.default_rng(11)
+    x = rng.standard_normal((5, 4, 6, 3))
+    g, b = rng.uniform(0.5, 1.5, 6), rng.standard_normal(6)
+    xt = _to_torch_nchw(x)
+    rm0, rv0 = rng.uniform(0, 1, 6), rng.uniform(0.5, 2, 6)
+    rm, rv = torch.from_numpy(rm0.copy()), torch.from_numpy(rv0.copy())
+    ref = F.instance_norm(xt, rm, rv, torch.from_numpy(g), torch.from_numpy(b), use_input_stats=True, momentum=0.1, eps=1e-5)
+    y, (nrm, nrv) = O.instancenorm(x, g, b, rm0, rv0, True, "identity", 0.1, 1e-5)
+    np.testing.assert_allclose(_to_torch_nchw(y).numpy(), ref.numpy(), atol=1e-10)
+    np.testing.assert_allclose(nrm, rm.numpy(), atol=1e-12)   # batch mean of per-sample means, S/(S-1) on the variance
+    np.testing.assert_allclose(nrv, rv.numpy(), atol=1e-12)
+    ref = F.instance_norm(xt, torch.from_numpy(rm0), torch.from_numpy(rv0), torch.from_numpy(g), torch.from_numpy(b),
+                          use_input_stats=False, eps=1e-5)
+    y, (srm, srv) = O.instancenorm(x, g, b, rm0, rv0, False, "identity", 0.1, 1e-5)
+    np.testing.assert_allclose(_to_torch_nchw(y).numpy(), ref.numpy(), atol=1e-10)
+    assert srm is rm0 and srv is rv0
+    with pytest.raises(AssertionError):
+        O.instancenorm(np.zeros((4, 3)), None, None, None, None, True)
+
+
+@pytest.mark.parametrize("kind", ["max", "mean"])
+@pytest.mark.parametrize("k,stride,pad", [((2, 2), None, 0), ((3, 3), (2, 2), 1), ((3, 2), (1, 2), (1, 0))])
+def test_pooling_matches_torch(kind, k, stride, pad):
+    # independent cross-check of the restated NNlib pooling (windows clipped, mean over the full window)
+    rng = np.random.default_rng(12)
+    x = rng.standard_normal((9, 8, 3, 2))
+    y, pb = O.pool_rrule(kind, x, k, stride, pad)
+    xt = _to_torch_nchw(x).requires_grad_(True)
+    st = k if stride is None else stride
+    pd = (pad, pad) if np.isscalar(pad) else pad
+    # torch's kernel / stride / padding are (H, W); ours are (W, H)
+    if kind == "max":
+        ref = F.max_pool2d(xt, (k[1], k[0]), (st[1], st[0]), (pd[1], pd[0]))
+    else:
+        ref = F.avg_pool2d(xt, (k[1], k[0]), (st[1], st[0]), (pd[1], pd[0]), count_include_pad=True)
+    np.testing.assert_allclose(_to_torch_nchw(y).numpy(), ref.detach().numpy(), atol=1e-12)
+    dy = rng.standard_normal(y.shape)
+    ref.backward(_to_torch_nchw(dy))
+    np.testing.assert_allclose(_to_torch_nchw(pb(dy)).numpy(), xt.grad.numpy(), atol=1e-12)
+
+
+def test_maxpool_gradient_goes_to_the_first_maximal_element():
+    x = np.zeros((4, 4, 1, 1))
+    y, pb = O.pool_rrule("max", x, (2, 2))
+    dx = pb(np.ones_like(y))
+    assert dx[0, 0, 0, 0] == 1 and dx[1, 0, 0, 0] == 0 and dx[0, 1, 0, 0] == 0 and dx.sum() == 4
+
+
+def test_optimiser_rules_match_torch_optim():
+    # Descent / Momentum / Adam as published for Optimisers.jl, against torch.optim on the same trajectory
+    rng = np.random.default_rng(13)
+    x0 = rng.standard_normal(50)
+    grads = [rng.standard_normal(50) for _ in range(5)]
+    for rule, make in (("descent", lambda p: torch.optim.SGD([p], lr=0.05)),
+                       ("momentum", lambda p: torch.optim.SGD([p], lr=0.05, momentum=0.9)),
+                       ("adam", lambda p: torch.optim.Adam([p], lr=0.05, betas=(0.9, 0.999), eps=1e-8))):
+        p = torch.tensor(x0.copy(), requires_grad=True)
+        opt = make(p)
+        x, st = x0.copy(), O.optimiser_init(rule, x0)
+        for g in grads:
+            p.grad = torch.from_numpy(g.copy())
+            opt.step()
+            st, x = O.optimiser_apply(rule, st, x, g, 0.05, 0.9, (0.9, 0.999), 1e-8)
+        np.testing.assert_allclose(x, p.detach().numpy(), rtol=1e-10, atol=1e-12)
+
+
 def test_gelu_variants_match_torch():
     x = np.linspace(-5, 5, 101)
     np.testing.assert_allclose(O.act_fn("gelu", x, "tanh"), F.gelu(torch.from_numpy(x), approximate="tanh").numpy(), atol=1e-12)
