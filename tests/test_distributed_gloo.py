@@ -128,3 +128,19 @@ def test_data_container_partition_sizes_without_processes():
     assert sizes == [4, 4, 2]   # ceil(10/3) = 4 per worker, the last one takes the rest
     assert [len(D.DistributedDataContainer(None, data, rank=r, workers=4)) for r in range(4)] == [3, 3, 3, 1]
     assert len(D.DistributedDataContainer(None, [], rank=0, workers=2)) == 0
+
+
+def test_fused_optimizer_buckets_follow_dtype_and_size_without_reordering():
+    # host logic only: which leaves share one collective + one optimiser launch
+    import torch
+    from luxlib_b200 import distributed as D
+    opt = D.FusedOptimizer(D.GlooBackend, "adam", bucket_bytes=1000)
+    params = [torch.zeros(100), torch.zeros(100), torch.zeros(10, dtype=torch.bfloat16), torch.zeros(200), torch.zeros(5)]
+    # fp32 leaves: 400 B + 400 B fit, the 800 B leaf starts a new bucket, the 20 B leaf joins it; bf16 apart
+    assert opt.buckets(params) == [[0, 1], [3, 4], [2]]
+    st = opt.init(params)
+    assert st[0][0].shape == params[0].shape and st[0][1] is not None and st[0][2] is None
+    assert D.FusedOptimizer(D.GlooBackend, "descent").init(params)[0] == (None, None, None)
+    assert D.FusedOptimizer(D.GlooBackend, "momentum", master=True).init(params)[2][2].dtype == torch.float32
+    with pytest.raises(ValueError):
+        D.FusedOptimizer(D.GlooBackend, "rmsprop")
