@@ -166,23 +166,46 @@ __global__ void __launch_bounds__(256) act_bwd_kernel(T* __restrict__ dx, float*
   const int64_t b_end = min(B, b_begin + rows_per_chunk);
   const int64_t sv = S / V;  // VEC only when S % V == 0
   float acc = 0.f;
-  const int64_t items = (b_end - b_begin) * sv;
-  for (int64_t it = threadIdx.x; it < items; it += blockDim.x) {
-    const int64_t b = b_begin + it / sv;
-    const int64_t e = (b * C + c) * S + (it % sv) * V;
-    if constexpr (VEC) {
-      Vec16<T> g = load16_stream(dy + e);
-      if constexpr (ACT != LB2_ACT_IDENTITY) {
-        Vec16<T> r = load16_stream(ref + e);
-        const Vec16<T> g0 = g;
-        g = vec_from<T>([&](int j) { return g0.get(j) * dact_sel<ACT, FAST, FROM_PRE>(r.get(j)); });
-      }
-      if (dx) store16(dx + e, g);
-      if constexpr (WANT_SUM) {
+  if constexpr (VEC) {
+    // A warp takes units of 128 vectors (4 per lane, all loads issued before any is used) of one (channel,
+    // sample) row; the unit -> (sample, segment) division happens once per unit.
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t upr = (uint32_t)((sv + 127) / 128);
+    const int64_t units = (b_end - b_begin) * (int64_t)upr;
+    for (int64_t u = warp; u < units; u += 8) {
+      const int64_t b = b_begin + u / upr;
+      const int64_t v0 = (int64_t)(u % upr) * 128 + lane;
+      const int64_t base = (b * C + c) * S;
+      Vec16<T> g[4], r[4];
 #pragma unroll
-        for (int j = 0; j < V; ++j) acc += g.get(j);
+      for (int k = 0; k < 4; ++k) {
+        const int64_t v = v0 + k * 32;
+        if (v < sv) {
+          g[k] = load16_stream(dy + base + v * V);
+          if constexpr (ACT != LB2_ACT_IDENTITY) r[k] = load16_stream(ref + base + v * V);
+        }
       }
-    } else {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int64_t v = v0 + k * 32;
+        if (v < sv) {
+          if constexpr (ACT != LB2_ACT_IDENTITY) {
+            const Vec16<T> g0 = g[k];
+            g[k] = vec_from<T>([&](int j) { return g0.get(j) * dact_sel<ACT, FAST, FROM_PRE>(r[k].get(j)); });
+          }
+          if (dx) store16(dx + base + v * V, g[k]);
+          if constexpr (WANT_SUM) {
+#pragma unroll
+            for (int j = 0; j < V; ++j) acc += g[k].get(j);
+          }
+        }
+      }
+    }
+  } else {
+    const int64_t items = (b_end - b_begin) * sv;
+    for (int64_t it = threadIdx.x; it < items; it += blockDim.x) {
+      const int64_t b = b_begin + it / sv;
+      const int64_t e = (b * C + c) * S + (it % sv) * V;
       float g = to_f32(dy[e]);
       if constexpr (ACT != LB2_ACT_IDENTITY) g *= dact_sel<ACT, FAST, FROM_PRE>(to_f32(ref[e]));
       T gs = from_f32<T>(g);

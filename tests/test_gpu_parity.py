@@ -569,7 +569,7 @@ def test_fused_optimizer_matches_the_rule_definitions(dt, rule):
             ostates[i], oparams[i] = O.optimiser_apply(rule, ostates[i], oparams[i], g.astype(np.float64), 0.05, 0.9,
                                                        (0.9, 0.999), 1e-8)
     for i in (0, 1, 2, 3, 4, 30, 64):
-        check(dparams[i], oparams[i], dt, f"param {i}", tol=2e-6 if dt == "f32" else 2e-2)
+        check(dparams[i], oparams[i], dt, f"param {i}", tol=None if dt == "f32" else 2e-2)
 
 
 def test_fused_optimizer_master_copy_keeps_small_updates():
