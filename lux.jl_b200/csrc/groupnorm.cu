@@ -398,8 +398,9 @@ gn_fwd_stream_kernel(T* __restrict__ y, float* __restrict__ mean_out, float* __r
   }
 }
 
-// Backward; shared memory after the header: ds[Cg], db[Cg], slots[2][nslots] (one slot per
-// warp-wide vector row of the group, in element order), then the ring (x chunk + dy chunk per stage).
+// Backward; shared memory after the header: ds[Cg], db[Cg], slots[nslots][8] pairs (every warp-wide
+// vector row of the group, in element order, leaves eight quarter-warp partial sums: two shuffle steps
+// per row instead of ten), then the ring (x chunk + dy chunk per stage).
 template <typename T, int ACT, bool AFFINE>
 __global__ void __launch_bounds__(kGnThreads, 2)
 gn_bwd_stream_kernel(T* __restrict__ dx, float* __restrict__ chan_out, const T* __restrict__ dy,
@@ -419,8 +420,7 @@ gn_bwd_stream_kernel(T* __restrict__ dx, float* __restrict__ chan_out, const T* 
   const uint32_t nslots = L / (32 * V);
   float* ds = reinterpret_cast<float*>(gn_smem + kGnHeaderBytes);
   float* dbs = ds + Cg;
-  float* slot_a = dbs + Cg;
-  float* slot_b = slot_a + nslots;
+  float2* slots = reinterpret_cast<float2*>(dbs + Cg);   // ds + 2*Cg floats: 8-byte aligned
   uint8_t* data = gn_smem + kGnHeaderBytes + aux_bytes;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, t = threadIdx.x;
   const uint32_t nchunks = (L + CE - 1) / CE;
@@ -494,10 +494,12 @@ gn_bwd_stream_kernel(T* __restrict__ dx, float* __restrict__ chan_out, const T* 
             b += d;
           }
         }
-        a = warp_sum(a);
-        b = warp_sum(b);
+        a += __shfl_xor_sync(0xffffffffu, a, 16);
+        b += __shfl_xor_sync(0xffffffffu, b, 16);
+        a += __shfl_xor_sync(0xffffffffu, a, 8);
+        b += __shfl_xor_sync(0xffffffffu, b, 8);
         const uint32_t sl = c * kSlotsPerChunk + (uint32_t)(k * (kGnCompute / 32) + warp);
-        if (lane == 0 && sl < nslots) { slot_a[sl] = a; slot_b[sl] = b; }
+        if (lane < 8 && sl < nslots) slots[sl * 8 + lane] = make_float2(a, b);
       }
       if (!dead) {
         __syncwarp();
@@ -506,17 +508,22 @@ gn_bwd_stream_kernel(T* __restrict__ dx, float* __restrict__ chan_out, const T* 
       if (++st == (uint32_t)stages) { st = 0; ph ^= 1u; }
     }
     asm volatile("bar.sync 1, %0;" ::"n"(kGnCompute) : "memory");
-    // channel j owns slots_per_chan consecutive slots
-    for (uint32_t j = t; j < Cg; j += kGnCompute) {
+    // channel j owns slots_per_chan consecutive rows = a contiguous run of 8 * slots_per_chan pairs;
+    // one warp per channel, lanes stride through the run, then a butterfly (fixed order: deterministic)
+    for (uint32_t j = warp; j < Cg; j += kGnCompute / 32) {
       float a = 0.f, b = 0.f;
-      const uint32_t first = j * slots_per_chan;
-      for (uint32_t q = 0; q < slots_per_chan; ++q) { a += slot_a[first + q]; b += slot_b[first + q]; }
-      ds[j] = a;
-      dbs[j] = b;
-      if constexpr (AFFINE) {
-        float* co = chan_out + ((n * ((int64_t)G * Cg)) + (int64_t)g * Cg + j) * 2;
-        co[0] = a;
-        co[1] = b;
+      const float2* run = slots + (size_t)j * slots_per_chan * 8;
+      for (uint32_t q = lane; q < slots_per_chan * 8; q += 32) { a += run[q].x; b += run[q].y; }
+      a = warp_sum(a);
+      b = warp_sum(b);
+      if (lane == 0) {
+        ds[j] = a;
+        dbs[j] = b;
+        if constexpr (AFFINE) {
+          float* co = chan_out + ((n * ((int64_t)G * Cg)) + (int64_t)g * Cg + j) * 2;
+          co[0] = a;
+          co[1] = b;
+        }
       }
     }
     asm volatile("bar.sync 1, %0;" ::"n"(kGnCompute) : "memory");
@@ -634,7 +641,7 @@ static int32_t gn_bwd_launch(T* dx, T* dg, T* db, const T* dy, const T* x, const
   const int64_t vecs = L / V;
   int grid = (int)(rows < (int64_t)sms * 2 ? rows : (int64_t)sms * 2);
   const bool fits32 = L < (int64_t)1 << 31 && G < (int64_t)1 << 31;
-  const size_t aux = align_up((size_t)(2 * Cg + 2 * (L / (32 * V))) * sizeof(float), 128);
+  const size_t aux = align_up((size_t)(2 * Cg + 2 + 16 * (L / (32 * V))) * sizeof(float), 128);
   if ((gn_stream_mask() & 2) && al && fits32 && aux <= 64 * 1024 && L * (int64_t)sizeof(T) >= 2 * (int64_t)kGnChunkBytes) {
     unsigned int* status = device_status_word();
     LB2_REQUIRE(status != nullptr, LB2_LAUNCH_FAIL, "groupnorm: device status word unavailable");
