@@ -141,6 +141,9 @@ int32_t lb2_conv_bwd(void* dw, void* dx, void* db, const void* dy, const void* o
   }
   const bool tc = !(flags & LB2_FLAG_FORCE_SIMT) && lay.tc_bytes > 0 && aligned_to(gptr, 16) && aligned_to(x, 16);
   void* tc_ws = ws + lay.g_bytes + lay.red_bytes;
+  if (tc && dtype == LB2_F32) {   // both gradients share one set of shifted copies of g
+    return conv_tc_f32_bwd(dw, (dx && nx > 0) ? dx : nullptr, x, gptr, w, g, tc_ws, st);
+  }
   if (dw) {
     rc = tc ? conv_tc_wgrad(dw, x, gptr, g, dtype, tc_ws, st) : conv_wgrad_direct(dw, x, gptr, g, dtype, st);
     if (rc != LB2_OK) return rc;

@@ -30,7 +30,8 @@ size_t conv_tc_f32_fwd_workspace_bytes(const ConvGeom& g);
 size_t conv_tc_f32_bwd_workspace_bytes(const ConvGeom& g);
 int32_t conv_tc_f32_fwd(void* y, void* preact, const void* x, const void* w, const void* bias, const ConvGeom& g,
                         int32_t act, void* ws, cudaStream_t st);
-int32_t conv_tc_f32_dgrad(void* dx, const void* gy, const void* w, const ConvGeom& g, void* ws, cudaStream_t st);
-int32_t conv_tc_f32_wgrad(void* dw, const void* x, const void* gy, const ConvGeom& g, void* ws, cudaStream_t st);
+// both gradients (either of dw, dx may be null) from one set of shifted copies of gy
+int32_t conv_tc_f32_bwd(void* dw, void* dx, const void* x, const void* gy, const void* w, const ConvGeom& g, void* ws,
+                        cudaStream_t st);
 
 }  // namespace lb2

@@ -1086,13 +1086,13 @@ size_t conv_tc_bwd_workspace_bytes(const ConvGeom& g, int32_t dtype) {
 }
 
 int32_t conv_tc_dgrad(void* dx, const void* gy, const void* w, const ConvGeom& g, int32_t dtype, void* ws, cudaStream_t st) {
-  if (dtype == LB2_F32) return conv_tc_f32_dgrad(dx, gy, w, g, ws, st);
+  if (dtype == LB2_F32) return fail(LB2_BAD_ARG, "Float32 gradients are computed by conv_tc_f32_bwd");
   const ConvGemm c = dgrad_gemm(g);
   return run_conv_gemm(dx, nullptr, nullptr, LB2_ACT_IDENTITY, gy, w, c, pack_geom(g, c, 1), static_cast<uint8_t*>(ws), st);
 }
 
 int32_t conv_tc_wgrad(void* dw, const void* x, const void* gy, const ConvGeom& g, int32_t dtype, void* ws_, cudaStream_t st) {
-  if (dtype == LB2_F32) return conv_tc_f32_wgrad(dw, x, gy, g, ws_, st);
+  if (dtype == LB2_F32) return fail(LB2_BAD_ARG, "Float32 gradients are computed by conv_tc_f32_bwd");
   using T = __nv_bfloat16;
   uint8_t* ws = static_cast<uint8_t*>(ws_);
   const ConvGemm f = fwd_gemm(g);

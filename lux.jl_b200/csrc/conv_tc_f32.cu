@@ -16,8 +16,10 @@
 // A is MN-major (s contiguous) straight from kW copies of the input shifted along W (the H shift is
 // a TMA start coordinate, out-of-range rows are zero-filled = the padding), in the 32-byte-atom
 // 128-byte swizzle the tensor core needs to transpose 32-bit elements; the packed filter is K-major.
-// Filter gradient: dw[(tap, ci), co] = sum over (image, 32-position blocks) of x_shifted * dy, both
-// operands K-major, split over CTAs along the contraction, fp32 partials reduced in a fixed order.
+// Filter gradient: sum_s x[s + shift(tap)] * g[s] = sum_s' x[s'] * g[s' - shift(tap)], so it reuses the W-shifted
+// copies of g that the data gradient makes anyway: rows = (tap, co) from those copies, columns = ci from a flat
+// hi/lo split of x, contraction over (image, 32-position blocks), both operands K-major, split over CTAs along
+// the contraction, fp32 partials reduced in a fixed order.
 //
 // Roofline: tensor pipe (tf32 rate, three products per useful one); algorithmic FLOPs =
 // 2*Wo*Ho*N*Cout*Cin*kW*kH per pass.
@@ -465,10 +467,12 @@ conv_tc_f32_wgrad_kernel(const __grid_constant__ CUtensorMap tmXh, const __grid_
   }
 }
 
-// dw[kw,kh,ci,co] = sum over splits (ascending) of partial[z][(tap, chunk, ci % 64)][co]
-__global__ void __launch_bounds__(256) conv_f32_wgrad_reduce_kernel(float* __restrict__ dw, const float* __restrict__ partial,
-                                                                    int kW, int kH, int cin, int cout, int flip, int chunks,
-                                                                    int rows_pad, int n_pad, int splits) {
+// dw[kw,kh,ci,co] = sum over splits (ascending) of partial[z][row][ci]. The filter gradient is formed with the
+// roles swapped (rows = taps of the DATA-gradient geometry x output channels, columns = input channels):
+// row = ((K-1-th)*kW + (K-1-tw)) * chunks * 64 + co, with (tw, th) the forward tap of filter index (kw, kh).
+__global__ void __launch_bounds__(256) conv_f32_wgrad_reduce_swapped_kernel(float* __restrict__ dw, const float* __restrict__ partial,
+                                                                            int kW, int kH, int cin, int cout, int flip,
+                                                                            int chunks, int rows_pad, int n_pad, int splits) {
   const int64_t total = (int64_t)kW * kH * cin * cout;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
     int64_t r = i;
@@ -477,10 +481,11 @@ __global__ void __launch_bounds__(256) conv_f32_wgrad_reduce_kernel(float* __res
     const int ci = (int)(r % cin);
     const int co = (int)(r / cin);
     const int tw = flip ? kw : kW - 1 - kw, th = flip ? kh : kH - 1 - kh;
-    const int rg = (th * kW + tw) * chunks + ci / 64;
-    const int64_t row = (int64_t)rg * 64 + ci % 64;
+    const int twp = kW - 1 - tw, thp = kH - 1 - th;
+    const int rg = (thp * kW + twp) * chunks + co / 64;
+    const int64_t row = (int64_t)rg * 64 + co % 64;
     float s = 0.f;
-    for (int z = 0; z < splits; ++z) s += partial[((int64_t)z * rows_pad + row) * n_pad + co];
+    for (int z = 0; z < splits; ++z) s += partial[((int64_t)z * rows_pad + row) * n_pad + ci];
     dw[i] = s;
   }
 }
@@ -561,14 +566,18 @@ unsigned f32_flat_grid(int64_t total) {
 }
 
 // out = act(implicit GEMM + bias); workspace = copies hi | copies lo | filter hi | filter lo
+void f32_make_copies(float* ch, float* cl, const float* in, const ConvGemmF32& c, cudaStream_t st) {
+  const int64_t rows = (int64_t)c.Hi * c.Ck * c.N;
+  conv_shift_split_kernel<<<f32_flat_grid(rows * (c.W / 4)), 256, 0, st>>>(ch, cl, in, c.W, rows, c.kW, c.pad_w);
+}
+
 int32_t run_f32_gemm(float* out, float* preact, const float* bias, int32_t act, const float* in, const float* w,
-                     const ConvGemmF32& c, const PackGeomF32& pg, uint8_t* ws, cudaStream_t st) {
+                     const ConvGemmF32& c, const PackGeomF32& pg, uint8_t* ws, cudaStream_t st, bool copies_ready = false) {
   float* ch = reinterpret_cast<float*>(ws);
   float* cl = reinterpret_cast<float*>(ws + f32_copy_bytes(c));
   float* wh = reinterpret_cast<float*>(ws + 2 * f32_copy_bytes(c));
   float* wl = reinterpret_cast<float*>(ws + 2 * f32_copy_bytes(c) + f32_packed_bytes(c));
-  const int64_t rows = (int64_t)c.Hi * c.Ck * c.N;
-  conv_shift_split_kernel<<<f32_flat_grid(rows * (c.W / 4)), 256, 0, st>>>(ch, cl, in, c.W, rows, c.kW, c.pad_w);
+  if (!copies_ready) f32_make_copies(ch, cl, in, c, st);
   conv_pack_split_filter_kernel<<<f32_flat_grid((int64_t)pg.n_rows * pg.k_total), 256, 0, st>>>(wh, wl, w, pg);
   LB2_CHECK_LAUNCH("conv_tc_f32 layout passes");
 
@@ -632,16 +641,24 @@ int32_t run_f32_gemm(float* out, float* preact, const float* bias, int32_t act, 
 struct WgPlanF32 {
   int bn, chunks, n_rg, m_tiles, tiles_n, s_blocks, kb_total, splits, kb_per_split, n_pad;
 };
-WgPlanF32 f32_wg_plan(const ConvGeom& g) {
+size_t f32_wg_partial_bytes(const WgPlanF32& w) {
+  return align_up((size_t)w.splits * w.m_tiles * 128 * w.n_pad * sizeof(float), 1024);
+}
+size_t f32_y_bytes(const ConvGeom& g) { return align_up((size_t)g.out[0] * g.out[1] * g.cout * g.batch * 4, 1024); }
+size_t f32_x_bytes(const ConvGeom& g) { return align_up((size_t)g.in[0] * g.in[1] * g.cin * g.batch * 4, 1024); }
+
+// Filter gradient with the roles swapped: rows = (tap of the data-gradient geometry, output channel) from the
+// W-shifted copies of g that the data gradient needs anyway, columns = input channels from a flat split of x.
+WgPlanF32 f32_wg_plan_swapped(const ConvGeom& g) {
   WgPlanF32 w{};
-  w.bn = f32_bn(g.cout);
-  w.chunks = f32_chunks64(g.cin);
+  w.bn = f32_bn(g.cin);
+  w.chunks = f32_chunks64(g.cout);
   w.n_rg = g.k[0] * g.k[1] * w.chunks;
   w.m_tiles = (w.n_rg + 1) / 2;
-  w.tiles_n = (g.cout + w.bn - 1) / w.bn;
+  w.tiles_n = (g.cin + w.bn - 1) / w.bn;
   w.n_pad = w.tiles_n * w.bn;
-  const int S_out = g.out[0] * g.out[1];
-  w.s_blocks = (S_out + 31) / 32;
+  const int S_in = g.in[0] * g.in[1];
+  w.s_blocks = (S_in + 31) / 32;
   w.kb_total = g.batch * w.s_blocks;
   int splits = sm_count() / (w.m_tiles * w.tiles_n);
   if (splits < 1) splits = 1;
@@ -650,10 +667,6 @@ WgPlanF32 f32_wg_plan(const ConvGeom& g) {
   w.splits = (w.kb_total + w.kb_per_split - 1) / w.kb_per_split;
   return w;
 }
-size_t f32_wg_partial_bytes(const WgPlanF32& w) {
-  return align_up((size_t)w.splits * w.m_tiles * 128 * w.n_pad * sizeof(float), 1024);
-}
-size_t f32_y_bytes(const ConvGeom& g) { return align_up((size_t)g.out[0] * g.out[1] * g.cout * g.batch * 4, 1024); }
 
 }  // namespace
 
@@ -663,16 +676,15 @@ bool conv_tc_f32_supported(const ConvGeom& g) {
   if (g.out[0] != g.in[0] || g.out[0] <= 0 || g.out[1] <= 0 || g.batch <= 0 || g.cin <= 0 || g.cout <= 0) return false;
   if (g.pad_lo[0] > g.k[0] - 1 || g.pad_lo[1] > g.k[1] - 1) return false;  // data gradient needs K-1-pad >= 0
   if (!f32_gemm_ok(f32_fwd_gemm(g)) || !f32_gemm_ok(f32_dgrad_gemm(g))) return false;
-  if (g.k[0] * g.k[1] * f32_chunks64(g.cin) > kF32MaxRg) return false;
+  if (g.k[0] * g.k[1] * f32_chunks64(g.cin) > kF32MaxRg || g.k[0] * g.k[1] * f32_chunks64(g.cout) > kF32MaxRg) return false;
   return true;
 }
 
 size_t conv_tc_f32_fwd_workspace_bytes(const ConvGeom& g) { return f32_gemm_bytes(f32_fwd_gemm(g)); }
 
+// backward workspace: g copies hi | lo | packed filter hi | lo (the data-gradient GEMM's layout) | x hi | x lo | partials
 size_t conv_tc_f32_bwd_workspace_bytes(const ConvGeom& g) {
-  const size_t dgrad = f32_gemm_bytes(f32_dgrad_gemm(g));
-  const size_t wgrad = 2 * f32_copy_bytes(f32_fwd_gemm(g)) + 2 * f32_y_bytes(g) + f32_wg_partial_bytes(f32_wg_plan(g));
-  return dgrad > wgrad ? dgrad : wgrad;   // the two gradients run one after the other in the same region
+  return f32_gemm_bytes(f32_dgrad_gemm(g)) + 2 * f32_x_bytes(g) + f32_wg_partial_bytes(f32_wg_plan_swapped(g));
 }
 
 int32_t conv_tc_f32_fwd(void* y, void* preact, const void* x, const void* w, const void* bias, const ConvGeom& g,
@@ -682,66 +694,70 @@ int32_t conv_tc_f32_fwd(void* y, void* preact, const void* x, const void* w, con
                       f32_pack_geom(g, c, 0), static_cast<uint8_t*>(ws), st);
 }
 
-int32_t conv_tc_f32_dgrad(void* dx, const void* gy, const void* w, const ConvGeom& g, void* ws, cudaStream_t st) {
-  const ConvGemmF32 c = f32_dgrad_gemm(g);
-  return run_f32_gemm((float*)dx, nullptr, nullptr, LB2_ACT_IDENTITY, (const float*)gy, (const float*)w, c,
-                      f32_pack_geom(g, c, 1), static_cast<uint8_t*>(ws), st);
-}
-
-int32_t conv_tc_f32_wgrad(void* dw, const void* x, const void* gy, const ConvGeom& g, void* ws_, cudaStream_t st) {
+// Both gradients from ONE set of W-shifted hi/lo copies of g: the data gradient reads them as its A operand;
+// the filter gradient sum_s x[s + shift(tap)] * g[s] is rewritten as sum_s' x[s'] * g[s' - shift(tap)], which is
+// the same copies at the data-gradient tap (K-1-tw, K-1-th), stacked along M, against a flat split of x.
+int32_t conv_tc_f32_bwd(void* dw, void* dx, const void* x, const void* gy, const void* w, const ConvGeom& g, void* ws_,
+                        cudaStream_t st) {
   uint8_t* ws = static_cast<uint8_t*>(ws_);
-  const ConvGemmF32 f = f32_fwd_gemm(g);
-  const WgPlanF32 w = f32_wg_plan(g);
+  const ConvGemmF32 d = f32_dgrad_gemm(g);
   float* ch = reinterpret_cast<float*>(ws);
-  float* cl = reinterpret_cast<float*>(ws + f32_copy_bytes(f));
-  float* gh = reinterpret_cast<float*>(ws + 2 * f32_copy_bytes(f));
-  float* gl = reinterpret_cast<float*>(ws + 2 * f32_copy_bytes(f) + f32_y_bytes(g));
-  float* partial = reinterpret_cast<float*>(ws + 2 * f32_copy_bytes(f) + 2 * f32_y_bytes(g));
-  const int64_t rows = (int64_t)f.Hi * f.Ck * f.N;
-  const int64_t ny = (int64_t)g.out[0] * g.out[1] * g.cout * g.batch;
-  conv_shift_split_kernel<<<f32_flat_grid(rows * (f.W / 4)), 256, 0, st>>>(ch, cl, (const float*)x, f.W, rows, f.kW, f.pad_w);
-  conv_split_flat_kernel<<<f32_flat_grid(ny / 4 + 1), 256, 0, st>>>(gh, gl, (const float*)gy, ny);
-  LB2_CHECK_LAUNCH("conv_tc_f32 layout passes");
+  float* cl = reinterpret_cast<float*>(ws + f32_copy_bytes(d));
+  f32_make_copies(ch, cl, (const float*)gy, d, st);
+  LB2_CHECK_LAUNCH("conv_tc_f32 shifted copies");
+  if (dx != nullptr) {
+    int32_t rc = run_f32_gemm((float*)dx, nullptr, nullptr, LB2_ACT_IDENTITY, (const float*)gy, (const float*)w, d,
+                              f32_pack_geom(g, d, 1), ws, st, true);
+    if (rc != LB2_OK) return rc;
+  }
+  if (dw == nullptr) return LB2_OK;
+  const WgPlanF32 w_ = f32_wg_plan_swapped(g);
+  float* xh = reinterpret_cast<float*>(ws + f32_gemm_bytes(d));
+  float* xl = reinterpret_cast<float*>(ws + f32_gemm_bytes(d) + f32_x_bytes(g));
+  float* partial = reinterpret_cast<float*>(ws + f32_gemm_bytes(d) + 2 * f32_x_bytes(g));
+  const int64_t nx = (int64_t)g.in[0] * g.in[1] * g.cin * g.batch;
+  conv_split_flat_kernel<<<f32_flat_grid(nx / 4 + 1), 256, 0, st>>>(xh, xl, (const float*)x, nx);
+  LB2_CHECK_LAUNCH("conv_tc_f32 split of x");
   ConvF32WgParams p{};
-  p.S_out = g.out[0] * g.out[1];
-  p.n_img = g.batch; p.n_out = g.cout;
-  p.s_blocks = w.s_blocks; p.m_tiles = w.m_tiles; p.tiles_n = w.tiles_n; p.splits = w.splits;
-  p.kb_total = w.kb_total; p.kb_per_split = w.kb_per_split; p.n_rg = w.n_rg;
-  p.idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(w.bn >> 3) << 17) | ((uint32_t)(kF32BM >> 4) << 24);
-  p.idesc_wide = (p.idesc & ~(0x3Fu << 17)) | ((uint32_t)((2 * w.bn) >> 3) << 17);
+  p.S_out = g.in[0] * g.in[1];          // contraction extent: input positions
+  p.n_img = g.batch; p.n_out = g.cin;
+  p.s_blocks = w_.s_blocks; p.m_tiles = w_.m_tiles; p.tiles_n = w_.tiles_n; p.splits = w_.splits;
+  p.kb_total = w_.kb_total; p.kb_per_split = w_.kb_per_split; p.n_rg = w_.n_rg;
+  p.idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(w_.bn >> 3) << 17) | ((uint32_t)(kF32BM >> 4) << 24);
+  p.idesc_wide = (p.idesc & ~(0x3Fu << 17)) | ((uint32_t)((2 * w_.bn) >> 3) << 17);
   p.desc_hi = (uint32_t)((1024u >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
   p.desc_lbo = 1u << 16;
   p.k_advance = 32u >> 4;
-  p.partial = partial; p.n_pad = w.n_pad;
+  p.partial = partial; p.n_pad = w_.n_pad;
   p.status = device_status_word();
   LB2_REQUIRE(p.status != nullptr, LB2_LAUNCH_FAIL, "conv_tc_f32: device status word unavailable");
-  for (int rg = 0; rg < w.n_rg; ++rg) {
-    const int tap = rg / w.chunks, tw = tap % f.kW, th = tap / f.kW;
-    p.rg_shift[rg] = (int16_t)((th - f.pad_h) * f.W);
-    p.rg_chan[rg] = (int16_t)((rg % w.chunks) * 64);
-    p.rg_copy[rg] = (int8_t)tw;
+  for (int rg = 0; rg < w_.n_rg; ++rg) {
+    const int tap = rg / w_.chunks, twp = tap % d.kW, thp = tap / d.kW;   // tap of the data-gradient geometry
+    p.rg_shift[rg] = (int16_t)((thp - d.pad_h) * d.W);
+    p.rg_chan[rg] = (int16_t)((rg % w_.chunks) * 64);
+    p.rg_copy[rg] = (int8_t)twp;
   }
-  CUtensorMap mXh, mXl, mGh, mGl;
-  if (!f32_map_4d(&mXh, ch, (int64_t)f.W * f.Hi, f.Ck, f.N, f.kW, 32, 64, false) ||
-      !f32_map_4d(&mXl, cl, (int64_t)f.W * f.Hi, f.Ck, f.N, f.kW, 32, 64, false) ||
-      !f32_map_4d(&mGh, gh, (int64_t)p.S_out, g.cout, g.batch, 1, 32, w.bn, false) ||
-      !f32_map_4d(&mGl, gl, (int64_t)p.S_out, g.cout, g.batch, 1, 32, w.bn, false))
+  CUtensorMap mGh, mGl, mXh, mXl;
+  if (!f32_map_4d(&mGh, ch, (int64_t)d.W * d.Hi, d.Ck, d.N, d.kW, 32, 64, false) ||
+      !f32_map_4d(&mGl, cl, (int64_t)d.W * d.Hi, d.Ck, d.N, d.kW, 32, 64, false) ||
+      !f32_map_4d(&mXh, xh, (int64_t)p.S_out, g.cin, g.batch, 1, 32, w_.bn, false) ||
+      !f32_map_4d(&mXl, xl, (int64_t)p.S_out, g.cin, g.batch, 1, 32, w_.bn, false))
     return fail(LB2_LAUNCH_FAIL, "conv_tc_f32: cuTensorMapEncodeTiled failed");
-  const int items = w.m_tiles * w.tiles_n * w.splits;
+  const int items = w_.m_tiles * w_.tiles_n * w_.splits;
   const int grid = items < sm_count() ? items : sm_count();
   auto launch = [&](auto kernel, int smem) -> int32_t {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return fail(LB2_LAUNCH_FAIL, "conv_tc_f32: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
-    kernel<<<grid, kF32Threads, smem, st>>>(mXh, mXl, mGh, mGl, p);
+    kernel<<<grid, kF32Threads, smem, st>>>(mGh, mGl, mXh, mXl, p);
     LB2_CHECK_LAUNCH("conv_tc_f32_wgrad");
     return LB2_OK;
   };
-  int32_t rc = w.bn == 64 ? launch(conv_tc_f32_wgrad_kernel<64>, ConvF32Cfg<64>::SMEM_BYTES)
-                          : launch(conv_tc_f32_wgrad_kernel<128>, ConvF32Cfg<128>::SMEM_BYTES);
+  int32_t rc = w_.bn == 64 ? launch(conv_tc_f32_wgrad_kernel<64>, ConvF32Cfg<64>::SMEM_BYTES)
+                           : launch(conv_tc_f32_wgrad_kernel<128>, ConvF32Cfg<128>::SMEM_BYTES);
   if (rc != LB2_OK) return rc;
   const int64_t nw = (int64_t)g.k[0] * g.k[1] * g.cin * g.cout;
-  conv_f32_wgrad_reduce_kernel<<<f32_flat_grid(nw), 256, 0, st>>>((float*)dw, partial, g.k[0], g.k[1], g.cin, g.cout, g.flip,
-                                                                  w.chunks, w.m_tiles * 128, w.n_pad, w.splits);
+  conv_f32_wgrad_reduce_swapped_kernel<<<f32_flat_grid(nw), 256, 0, st>>>((float*)dw, partial, g.k[0], g.k[1], g.cin, g.cout, g.flip,
+                                                                          w_.chunks, w_.m_tiles * 128, w_.n_pad, w_.splits);
   LB2_CHECK_LAUNCH("conv_f32_wgrad_reduce");
   return LB2_OK;
 }
