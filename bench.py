@@ -453,18 +453,145 @@ def run_secondary(args):
     return 0
 
 
+def run_convnet(args):
+    """--workload convnet: a data-parallel training step of the stride-1 stage of a ResNet-18-style network
+    (two basic blocks of conv3x3-BN-relu / conv3x3-BN / residual-add-relu on 56x56x64, global mean pool,
+    Dense 64 -> 1000, mean-squared error against one-hot labels), bf16, per-GPU batch 256, momentum SGD.
+    Every rank holds the same parameters and its own synthetic batch; parameter gradients go through one flat
+    sum all-reduce per bucket and one lb2_optimizer_step launch (1/world folded in). Reports samples/s over all
+    ranks. The strided stages of the full network are not included (their convolutions have no tensor-core
+    path yet)."""
+    import torch
+    import luxlib_b200 as L
+    from luxlib_b200 import distributed as D
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        D.initialize(D.NCCLBackend)
+        import torch.distributed as dist
+    bf = torch.bfloat16
+    Bsz, C, H, NCLS = 256, 64, 56, 1000
+    gp = torch.Generator(device="cuda").manual_seed(5)               # parameters: same on every rank
+    gd = torch.Generator(device="cuda").manual_seed(100 + rank)      # data: one shard per rank
+    cm = lambda t: t.permute(*reversed(range(t.dim()))) if t.dim() > 1 else t   # row-major bytes -> Julia shape
+    rnp = lambda *sh: torch.randn(*sh, device=device, generator=gp)
+    convs = [cm((rnp(C, C, 3, 3) * (2.0 / (9 * C)) ** 0.5).to(bf)) for _ in range(4)]       # kaiming_normal
+    cbias = [torch.zeros(C, device=device, dtype=bf) for _ in range(4)]
+    gam = [torch.ones(C, device=device, dtype=bf) for _ in range(4)]
+    bet = [torch.zeros(C, device=device, dtype=bf) for _ in range(4)]
+    rmean = [torch.zeros(C, device=device, dtype=bf) for _ in range(4)]
+    rvar = [torch.ones(C, device=device, dtype=bf) for _ in range(4)]
+    lim = (24.0 / (C + NCLS)) ** 0.5
+    Wd = cm(((torch.rand(C, NCLS, device=device, generator=gp) - 0.5) * lim).to(bf))        # (1000, 64) glorot_uniform
+    bd = torch.zeros(NCLS, device=device, dtype=bf)
+    x = cm(torch.randn(Bsz, C, H, H, device=device, generator=gd).to(bf))
+    labels = torch.randint(0, NCLS, (Bsz,), device=device, generator=gd)
+    target = cm(torch.nn.functional.one_hot(labels, NCLS).to(bf))                           # (1000, B)
+    params = convs + cbias + gam + bet + [Wd, bd]
+    opt = D.FusedOptimizer(D.NCCLBackend, "momentum", eta=1e-3, rho=0.9)
+    states = opt.init(params)
+    cd = L.ConvDims.make(2, 1, 1, 1, 1, False)
+
+    def step():
+        h, tape = x, []
+        for blk in range(2):
+            skip = h
+            i0, i1 = 2 * blk, 2 * blk + 1
+            c0, pc0 = L.rrule_fused_conv("identity", convs[i0], h, cbias[i0], cd)
+            n0, (rmean[i0], rvar[i0]), pn0 = L.rrule_batchnorm(c0, gam[i0], bet[i0], rmean[i0], rvar[i0], True, "relu", 0.1, 1e-5)
+            c1, pc1 = L.rrule_fused_conv("identity", convs[i1], n0, cbias[i1], cd)
+            n1, (rmean[i1], rvar[i1]), pn1 = L.rrule_batchnorm(c1, gam[i1], bet[i1], rmean[i1], rvar[i1], True, "identity", 0.1, 1e-5)
+            h, padd = L.rrule_add_activation("relu", n1, skip)
+            tape.append((pc0, pn0, pc1, pn1, padd))
+        pooled, ppool = L.rrule_meanpool(h, L.PoolDims.global_(h))          # (1, 1, 64, B)
+        feat = pooled.reshape(C, Bsz)                                        # same bytes, Julia shape (64, B)
+        y, pdense = L.rrule_fused_dense("identity", Wd, feat, bd)
+        # loss glue (tiny, 1000 x B): mean-squared error and its gradient
+        diff = y - target
+        loss = (diff.float() ** 2).mean()
+        dy = diff * (2.0 / diff.numel())
+        grads = [None] * len(params)
+        dWd, dfeat, dbd = pdense(dy)
+        grads[16], grads[17] = dWd, dbd
+        dh = ppool(dfeat.reshape(1, 1, C, Bsz))
+        for blk in (1, 0):
+            pc0, pn0, pc1, pn1, padd = tape[blk]
+            i0, i1 = 2 * blk, 2 * blk + 1
+            dn1, dskip = padd(dh)
+            dc1, grads[8 + i1], grads[12 + i1] = pn1(dn1)
+            grads[i1], dn0, grads[4 + i1] = pc1(dc1)
+            dc0, grads[8 + i0], grads[12 + i0] = pn0(dn0)
+            grads[i0], dx0, grads[4 + i0] = pc0(dc0)
+            dh = L.add_activation("identity", dx0, dskip)
+        opt.update(states, params, grads)
+        return loss
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    warm = max(args.warmup, 3)
+    for _ in range(warm):
+        step()
+    barrier()
+    sampler = ClockSampler(local)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    sampler.start()
+    e0.record()
+    for _ in range(args.steps):
+        loss = step()
+    e1.record()
+    barrier()
+    clocks = sampler.stop()
+    t = torch.tensor([e0.elapsed_time(e1)], device=device)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item()) / args.steps
+    rc = L._cabi.load().lb2_poll_device_status(None)
+    if rc != 0:
+        raise SystemExit(f"device status {rc}")
+    if rank == 0:
+        flop = 4 * 3 * 2.0 * H * H * Bsz * C * C * 9 + 3 * 2.0 * NCLS * C * Bsz
+        sustained, burst, which = measured_peaks()
+        tf = world * flop / (ms * 1e-3) / 1e12
+        line = {"metric": "data-parallel conv-net step samples/s", "value": world * Bsz / (ms * 1e-3), "unit": "samples/s",
+                "n_gpus": world, "steps": args.steps, "warmup": warm, "ms_per_step": ms, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "config": {"workload": "ResNet-18-style stride-1 stage: 2 basic blocks (conv3x3-BN-relu, conv3x3-BN, add-relu) on "
+                                       "56x56x64, global mean pool, Dense 64->1000, MSE; per-GPU batch 256; momentum SGD fused with the "
+                                       "gradient all-reduce bucket",
+                           "parallelism": f"dp{world}", "final_loss": float(loss)},
+                "clocks": clocks, "gpu_launches": None,
+                "roofline": {"bound": "tensor", "achieved": tf, "peak": world * sustained, "unit": "TFLOP/s", "frac": tf / (world * sustained),
+                             "traffic": None, "peak_source": f"{which}: bf16_tflops_sustained x n_gpus; conv + dense FLOPs of the whole step"}}
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="dense", choices=["dense", "ln", "gn", "bn", "conv"],
-                    help="dense = the headline configuration (default); the others are single-GPU secondary rows")
+    ap.add_argument("--workload", default="dense", choices=["dense", "ln", "gn", "bn", "conv", "convnet"],
+                    help="dense = the headline configuration (default); ln/gn/bn/conv are single-GPU secondary rows; "
+                         "convnet = data-parallel conv-net stage step (any --gpus, under torchrun for N > 1)")
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "f32"], help="storage type of the secondary workloads")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)
+    if args.workload == "convnet":
+        return run_convnet(args)
     if args.workload != "dense":
         return run_secondary(args)
     return run_gpu_arm(args)

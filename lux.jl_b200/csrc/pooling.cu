@@ -49,6 +49,56 @@ __global__ void __launch_bounds__(256) pool_fwd_kernel(T* __restrict__ y, const 
   }
 }
 
+// Global pooling (window == whole unpadded input): one warp per (channel, sample) plane, lanes stride through
+// the plane's contiguous elements, then a butterfly - a fixed order, so deterministic.
+template <typename T, bool MAX>
+__global__ void __launch_bounds__(256) pool_global_fwd_kernel(T* __restrict__ y, const T* __restrict__ x, int64_t S, int64_t planes) {
+  const int lane = threadIdx.x & 31;
+  const int64_t wstride = (int64_t)gridDim.x * 8;
+  for (int64_t plane = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); plane < planes; plane += wstride) {
+    const T* xp = x + plane * S;
+    float acc = MAX ? -INFINITY : 0.f;
+    for (int64_t i = lane; i < S; i += 32) {
+      const float v = to_f32(xp[i]);
+      if (MAX) acc = fmaxf(acc, v); else acc += v;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float other = __shfl_xor_sync(0xffffffffu, acc, o);
+      if (MAX) acc = fmaxf(acc, other); else acc += other;
+    }
+    if (lane == 0) y[plane] = from_f32<T>(MAX ? acc : acc / (float)S);
+  }
+}
+
+// Global pooling backward: the mean spreads dy / S over the plane; the max gives dy to the first maximal element.
+template <typename T, bool MAX>
+__global__ void __launch_bounds__(256) pool_global_bwd_kernel(T* __restrict__ dx, const T* __restrict__ dy, const T* __restrict__ y,
+                                                              const T* __restrict__ x, int64_t S, int64_t planes) {
+  const int lane = threadIdx.x & 31;
+  const int64_t wstride = (int64_t)gridDim.x * 8;
+  for (int64_t plane = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); plane < planes; plane += wstride) {
+    const float g = to_f32(dy[plane]);
+    T* dxp = dx + plane * S;
+    if (MAX) {
+      const T* xp = x + plane * S;
+      const float ymax = to_f32(y[plane]);
+      long long first = S;
+      for (int64_t i = lane; i < S && first == S; i += 32)
+        if (to_f32(xp[i]) == ymax) first = i;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const long long other = __shfl_xor_sync(0xffffffffu, first, o);
+        first = other < first ? other : first;
+      }
+      for (int64_t i = lane; i < S; i += 32) dxp[i] = from_f32<T>(i == first ? g : 0.f);
+    } else {
+      const T v = from_f32<T>(g / (float)S);
+      for (int64_t i = lane; i < S; i += 32) dxp[i] = v;
+    }
+  }
+}
+
 // Does the window of output (ow, oh, od) give its max-pool gradient to input (w, h, d)? True when that
 // input is the first element, in (kw fastest, kh, kd) order, equal to the window maximum ymax.
 template <typename T>
@@ -87,22 +137,23 @@ __global__ void __launch_bounds__(256) pool_bwd_kernel(T* __restrict__ dx, const
     const T* yp = y + plane * out_sp;
     const T* dyp = dy + plane * out_sp;
     float acc = 0.f;
-    // outputs whose window holds this input: o*stride - pad + kk*dil == coordinate, kk in [0, k)
-    for (int kd = 0; kd < g.k[2]; ++kd) {
-      const int nd = d + g.pad[2] - kd * g.dil[2];
-      if (nd < 0 || nd % g.stride[2] != 0) continue;
-      const int od = nd / g.stride[2];
-      if (od >= g.out[2]) continue;
-      for (int kh = 0; kh < g.k[1]; ++kh) {
-        const int nh = h + g.pad[1] - kh * g.dil[1];
-        if (nh < 0 || nh % g.stride[1] != 0) continue;
-        const int oh = nh / g.stride[1];
-        if (oh >= g.out[1]) continue;
-        for (int kw = 0; kw < g.k[0]; ++kw) {
-          const int nw = w + g.pad[0] - kw * g.dil[0];
-          if (nw < 0 || nw % g.stride[0] != 0) continue;
-          const int ow = nw / g.stride[0];
-          if (ow >= g.out[0]) continue;
+    // outputs whose window holds this input: o*stride - pad + kk*dil == coordinate with kk in [0, k), i.e.
+    // o in [ceil((coordinate + pad - (k-1)*dil) / stride), floor((coordinate + pad) / stride)], dil | remainder
+    int lo[3], hi[3];
+    const int coord[3] = {w, h, d};
+#pragma unroll
+    for (int a = 0; a < 3; ++a) {
+      const int top = coord[a] + g.pad[a];
+      const int bot = top - (g.k[a] - 1) * g.dil[a];
+      lo[a] = bot <= 0 ? 0 : (bot + g.stride[a] - 1) / g.stride[a];
+      hi[a] = min(g.out[a] - 1, top / g.stride[a]);
+    }
+    for (int od = lo[2]; od <= hi[2]; ++od) {
+      if ((d + g.pad[2] - od * g.stride[2]) % g.dil[2] != 0) continue;
+      for (int oh = lo[1]; oh <= hi[1]; ++oh) {
+        if ((h + g.pad[1] - oh * g.stride[1]) % g.dil[1] != 0) continue;
+        for (int ow = lo[0]; ow <= hi[0]; ++ow) {
+          if ((w + g.pad[0] - ow * g.stride[0]) % g.dil[0] != 0) continue;
           const int64_t o = ((int64_t)od * g.out[1] + oh) * g.out[0] + ow;
           if (MAX) {
             if (first_max_is(xp, g, ow, oh, od, to_f32(yp[o]), w, h, d)) acc += to_f32(dyp[o]);
@@ -168,6 +219,17 @@ int32_t lb2_pool_fwd(void* y, const void* x, const lb2_pool_desc* d, int32_t kin
   LB2_REQUIRE(y && x, LB2_BAD_ARG, "null tensor pointer");
   LB2_REQUIRE(aligned_to(y, dtype_size(dtype)) && aligned_to(x, dtype_size(dtype)), LB2_BAD_ALIGN, "pointer not aligned to the element size");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  bool global = true;
+  for (int i = 0; i < 3; ++i) global = global && g.out[i] == 1 && g.pad[i] == 0 && g.dil[i] == 1 && g.k[i] == g.in[i];
+  if (global) {
+    const int64_t S = (int64_t)g.in[0] * g.in[1] * g.in[2];
+    LB2_DISPATCH_DTYPE(dtype, {
+      if (kind == LB2_POOL_MAX) pool_global_fwd_kernel<T, true><<<pool_grid(g.planes * 32), 256, 0, st>>>((T*)y, (const T*)x, S, g.planes);
+      else pool_global_fwd_kernel<T, false><<<pool_grid(g.planes * 32), 256, 0, st>>>((T*)y, (const T*)x, S, g.planes);
+    });
+    LB2_CHECK_LAUNCH("pool_global_fwd");
+    return LB2_OK;
+  }
   LB2_DISPATCH_DTYPE(dtype, {
     if (kind == LB2_POOL_MAX) pool_fwd_kernel<T, true><<<pool_grid(total), 256, 0, st>>>((T*)y, (const T*)x, g);
     else pool_fwd_kernel<T, false><<<pool_grid(total), 256, 0, st>>>((T*)y, (const T*)x, g);
@@ -197,6 +259,17 @@ int32_t lb2_pool_bwd(void* dx, const void* dy, const void* y, const void* x, con
   const size_t es = dtype_size(dtype);
   LB2_REQUIRE(aligned_to(dx, es) && aligned_to(dy, es) && aligned_to(y, es) && aligned_to(x, es), LB2_BAD_ALIGN,
               "pointer not aligned to the element size");
+  bool global = true;
+  for (int i = 0; i < 3; ++i) global = global && g.out[i] == 1 && g.pad[i] == 0 && g.dil[i] == 1 && g.k[i] == g.in[i];
+  if (global) {
+    const int64_t S = (int64_t)g.in[0] * g.in[1] * g.in[2];
+    LB2_DISPATCH_DTYPE(dtype, {
+      if (kind == LB2_POOL_MAX) pool_global_bwd_kernel<T, true><<<pool_grid(g.planes * 32), 256, 0, st>>>((T*)dx, (const T*)dy, (const T*)y, (const T*)x, S, g.planes);
+      else pool_global_bwd_kernel<T, false><<<pool_grid(g.planes * 32), 256, 0, st>>>((T*)dx, (const T*)dy, nullptr, nullptr, S, g.planes);
+    });
+    LB2_CHECK_LAUNCH("pool_global_bwd");
+    return LB2_OK;
+  }
   LB2_DISPATCH_DTYPE(dtype, {
     if (kind == LB2_POOL_MAX) pool_bwd_kernel<T, true><<<pool_grid(total), 256, 0, st>>>((T*)dx, (const T*)dy, (const T*)y, (const T*)x, g);
     else pool_bwd_kernel<T, false><<<pool_grid(total), 256, 0, st>>>((T*)dx, (const T*)dy, nullptr, nullptr, g);
