@@ -182,6 +182,9 @@ def run_gpu_arm(args):
     device = torch.device("cuda", local)
     dist = None
     if world > 1:
+        # The persistent GEMM kernels occupy every SM; NCCL's in-switch (NVLS) all-reduce kernels compete with them
+        # for SMs and measured slower here at 8 GPUs (5.0-5.4 PFLOP/s against 5.9 with plain ring / tree kernels).
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         import torch.distributed as dist_mod
         dist = dist_mod
         dist.init_process_group("nccl", device_id=device)
@@ -211,15 +214,24 @@ def run_gpu_arm(args):
         pending.append(dist.all_reduce(dW.T, op=dist.ReduceOp.AVG, async_op=True))
         pending.append(dist.all_reduce(db, op=dist.ReduceOp.AVG, async_op=True))
 
+    overlap = os.environ.get("LB2_BENCH_OVERLAP", "1") != "0"   # experiment switch: 0 = all-reduce after the whole pullback
+
+    def backward(pullback):
+        if dist is None:
+            return pullback(dy)
+        if overlap:
+            dW, dx, db = pullback(dy, on_param_grads=start_allreduce)
+        else:
+            dW, dx, db = pullback(dy)
+            start_allreduce(dW, db)
+        for h in pending:
+            h.wait()          # stream-level wait: the next step's work is ordered after the reduced gradients
+        pending.clear()
+        return dW, dx, db
+
     def step():
         y, pullback = L.rrule_fused_dense(ACT, W, x, b)
-        if dist is None:
-            dW, dx, db = pullback(dy)
-        else:
-            dW, dx, db = pullback(dy, on_param_grads=start_allreduce)
-            for h in pending:
-                h.wait()          # stream-level wait: the next step's work is ordered after the reduced gradients
-            pending.clear()
+        dW, dx, db = backward(pullback)
         return y, dW, dx, db
 
     def barrier():
@@ -247,13 +259,7 @@ def run_gpu_arm(args):
         fwd_ev[i][0].record()
         y, pullback = L.rrule_fused_dense(ACT, W, x, b)
         fwd_ev[i][1].record()
-        if dist is None:
-            dW, dx, db = pullback(dy)
-        else:
-            dW, dx, db = pullback(dy, on_param_grads=start_allreduce)
-            for h in pending:
-                h.wait()
-            pending.clear()
+        dW, dx, db = backward(pullback)
     e1.record()
     barrier()
     clocks = sampler.stop()
