@@ -3,18 +3,21 @@
 //
 //   D[Mm x Nn] = A[Mm x Kc] * B[Nn x Kc]^T      (D column-major, Mm contiguous)
 //
-// One persistent CTA per SM, 256 threads, warp-specialised:
+// One persistent CTA per SM, 384 threads, warp-specialised:
 //   warp 0      TMA producer (one elected lane): fills a ring of STAGES {A,B} k-blocks
 //   warp 1      MMA issuer  (one elected lane): 4 tcgen05.mma (K=16 bf16 / K=8 tf32) per k-block,
 //               tcgen05.commit releases the smem stage / publishes the accumulator
 //   warp 2      TMEM allocator (512 columns = two 128 x BN fp32 accumulators, so the epilogue of
 //               tile i overlaps the main loop of tile i+1)
-//   warps 4-7   epilogue: tcgen05.ld 32 lanes x 32 columns -> +bias -> activation -> global
+//   warps 4-11  epilogue, two warps per TMEM lane quarter, each taking half of the tile's columns:
+//               tcgen05.ld 32 lanes x 32 columns -> +bias -> activation -> global
 //               (lane = output row = contiguous index of D, so every warp store is a 64/128-byte run)
 // Operands may be K-major or MN-major in global memory; both are fetched with tiled TMA boxes
 // of 128-byte rows (SWIZZLE_128B) and described to the MMA through the matching shared-memory
 // matrix descriptor, so no transposition pass ever runs. fp32 storage uses kind::tf32, by default
-// as an error-compensated 3-product split (hi*hi + lo*hi + hi*lo) that restores ~fp32 accuracy.
+// as an error-compensated 3-product split (hi*hi + lo*hi + hi*lo) with per-k-block accumulation in
+// registers (gemm_tc_f32acc_kernel) that restores fp32 accuracy. A CTA-pair (cta_group::2) variant
+// of the bf16 / single-pass tf32 kernel is opt-in (gemm_tc_pair_kernel).
 // No TMA multicast is used anywhere. Every mbarrier wait is bounded; on expiry the kernel sets
 // a status word, drains and returns, and the host reports LB2_TIMEOUT from lb2_poll_device_status.
 //

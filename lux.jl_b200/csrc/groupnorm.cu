@@ -1,14 +1,14 @@
-// LayerNorm and GroupNorm, forward and backward: bandwidth-bound kernels that normalise
-// contiguous "rows" (a LayerNorm row of D features; a GroupNorm group of S*C/G elements).
+// GroupNorm (and, with one channel per group, InstanceNorm), forward and backward: bandwidth-bound
+// kernels that normalise contiguous rows = one (group, sample) block of S*C/G elements of the
+// column-major (S, C/G, G, B) view.
 //
-// HBM layout: Julia column-major, so the normalised extent is contiguous. Fast path: the whole
-// row is read ONCE with 128-bit loads into registers (NV vectors per thread), statistics are
-// taken with a two-pass (mean, then centred sum of squares) reduction over registers through
-// warp shuffles / shared memory, and the result is written with 128-bit stores — algorithmic
-// traffic only (read x, write y; backward: read x, dy, write dx). The backward fuses both of its
-// reductions (sum g, sum g*xhat) in one pass and accumulates the affine gradients on the side.
-// A generic multi-pass path (second and third reads served by L2) covers shapes the fast path
-// cannot take. All cross-CTA reductions are two-stage in a fixed order: deterministic.
+// Forward: the row is read ONCE with 128-bit loads into registers (NV vectors per thread),
+// two-pass variance over registers, 128-bit stores. Backward: a chunk-streaming kernel for rows of
+// any length (producer warp + shared-memory ring; the second pass over a row is served by L2), with
+// register-cached and scalar generic kernels for short or unaligned rows. The backward forms
+// per-channel sums first (they are also the affine-gradient contributions of the sample) and
+// derives the two group reductions from them; everything is reduced in a fixed order:
+// deterministic. HBM traffic is the algorithmic figure: read x, write y; read x, dy, write dx.
 //
 // Algorithmic bytes per element: forward 2*sizeof(T), backward 3*sizeof(T).
 #include <stdlib.h>

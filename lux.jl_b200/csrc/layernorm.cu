@@ -1,14 +1,15 @@
-// LayerNorm and GroupNorm, forward and backward: bandwidth-bound kernels that normalise
-// contiguous "rows" (a LayerNorm row of D features; a GroupNorm group of S*C/G elements).
+// LayerNorm, forward and backward: bandwidth-bound kernels that normalise contiguous rows of D
+// features (Julia column-major, so the normalised extent is contiguous).
 //
-// HBM layout: Julia column-major, so the normalised extent is contiguous. Fast path: the whole
-// row is read ONCE with 128-bit loads into registers (NV vectors per thread), statistics are
-// taken with a two-pass (mean, then centred sum of squares) reduction over registers through
-// warp shuffles / shared memory, and the result is written with 128-bit stores — algorithmic
-// traffic only (read x, write y; backward: read x, dy, write dx). The backward fuses both of its
-// reductions (sum g, sum g*xhat) in one pass and accumulates the affine gradients on the side.
-// A generic multi-pass path (second and third reads served by L2) covers shapes the fast path
-// cannot take. All cross-CTA reductions are two-stage in a fixed order: deterministic.
+// Three tiers. Ring kernels (the common case, rows of a few KB to ~100 KB): a producer warp streams
+// whole rows into a shared-memory ring with 1-D bulk copies several rows ahead of 256 compute
+// threads; the forward takes a two-pass (mean, then centred sum of squares) variance over
+// registers, the backward keeps the row in its ring stage through both of its passes. Cached
+// kernels (short rows): the row is read ONCE with 128-bit loads into registers. Generic kernels:
+// scalar, multi-pass (second and third reads served by L2) for shapes the others cannot take.
+// The backward fuses both of its reductions (sum g, sum g*xhat) in one pass and accumulates the
+// affine gradients per thread across rows; all cross-CTA reductions are two-stage in a fixed
+// order: deterministic. HBM traffic is the algorithmic figure: read x, write y; read x, dy, write dx.
 //
 // Algorithmic bytes per element: forward 2*sizeof(T), backward 3*sizeof(T).
 #include "norm_common.cuh"
