@@ -326,7 +326,7 @@ def run_gpu_arm(args):
             "bound": "tensor", "kernel": "gemm_tc_kernel (forward GEMM, bias+gelu epilogue)", "achieved": achieved,
             "peak": sustained, "unit": "TFLOP/s", "frac": achieved / sustained,
             # dram__bytes_read.sum + dram__bytes_write.sum of one forward launch, from the ncu launch-list pass
-            # summarised in profiles/gemm_tc_kernel_dense_c2_bf16.md (132.1 MB + 103.3 MB)
+            # (132.1 MB read + 103.3 MB written, Nsight Compute launch-list pass on this workload)
             "traffic": 235.4e6, "traffic_unit": "bytes per launch",
             "peak_source": f"{which}: bf16_tflops_sustained (kernel timed inside a long step); burst figure {burst}",
             "launch_ms": fwd_ms,
