@@ -217,12 +217,15 @@ def run_gpu_arm(args):
     overlap = os.environ.get("LB2_BENCH_OVERLAP", "1") != "0"   # experiment switch: 0 = all-reduce after the whole pullback
 
     def backward(pullback):
+        return backward_from(pullback, dy)
+
+    def backward_from(pullback, dy_):
         if dist is None:
-            return pullback(dy)
+            return pullback(dy_)
         if overlap:
-            dW, dx, db = pullback(dy, on_param_grads=start_allreduce)
+            dW, dx, db = pullback(dy_, on_param_grads=start_allreduce)
         else:
-            dW, dx, db = pullback(dy)
+            dW, dx, db = pullback(dy_)
             start_allreduce(dW, db)
         for h in pending:
             h.wait()          # stream-level wait: the next step's work is ordered after the reduced gradients
@@ -277,30 +280,45 @@ def run_gpu_arm(args):
 
     # ---- end to end through the public API with HOST buffers (pinned): per step copy this step's
     # inputs (x, dy) to the device, run, and read every result (y, dW, dx, db) back.
-    e2e_steps = max(3, min(args.steps, 10))
+    e2e_steps = max(3, min(args.steps, 20))
     hx = torch.from_numpy(np.ascontiguousarray(xn.T)).to(bf).pin_memory()      # column-major bytes of x
     hdy = torch.from_numpy(np.ascontiguousarray(dyn.T)).to(bf).pin_memory()
-    dxbuf, dybuf = torch.empty_like(hx, device=device), torch.empty_like(hdy, device=device)
-    hy = torch.empty((N, M), dtype=bf).pin_memory()
-    hdW = torch.empty((K, M), dtype=bf).pin_memory()
-    hdx = torch.empty((N, K), dtype=bf).pin_memory()
-    hdb = torch.empty((M,), dtype=bf).pin_memory()
+    # Three streams: uploads, compute, downloads. Device inputs and host outputs are double-buffered so that the
+    # upload of step i+1 and the download of step i-1 run under the compute of step i (PCIe is full duplex).
+    s_in, s_out = torch.cuda.Stream(device=device), torch.cuda.Stream(device=device)
+    in_bufs = [(torch.empty_like(hx, device=device), torch.empty_like(hdy, device=device)) for _ in range(2)]
+    in_ready = [torch.cuda.Event() for _ in range(2)]
+    in_free = [torch.cuda.Event() for _ in range(2)]
+    houts = [(torch.empty((N, M), dtype=bf).pin_memory(), torch.empty((K, M), dtype=bf).pin_memory(),
+              torch.empty((N, K), dtype=bf).pin_memory(), torch.empty((M,), dtype=bf).pin_memory()) for _ in range(2)]
+    hy, hdW, hdx, hdb = houts[0]
+    cur = torch.cuda.current_stream(device)
+    e2e_count = [0]
 
     def e2e_step():
-        dxbuf.copy_(hx, non_blocking=True)
-        dybuf.copy_(hdy, non_blocking=True)
+        k = e2e_count[0] % 2
+        e2e_count[0] += 1
+        dxbuf, dybuf = in_bufs[k]
+        with torch.cuda.stream(s_in):
+            s_in.wait_event(in_free[k])            # the step that last read this buffer pair has finished
+            dxbuf.copy_(hx, non_blocking=True)
+            dybuf.copy_(hdy, non_blocking=True)
+            in_ready[k].record(s_in)
+        cur.wait_event(in_ready[k])
         y, pullback = L.rrule_fused_dense(ACT, W, dxbuf.T, b)
-        if dist is None:
-            dW, dx, db = pullback(dybuf.T)
-        else:
-            dW, dx, db = pullback(dybuf.T, on_param_grads=start_allreduce)
-            for h in pending:
-                h.wait()
-            pending.clear()
-        hy.copy_(y.T, non_blocking=True)
-        hdW.copy_(dW.T, non_blocking=True)
-        hdx.copy_(dx.T, non_blocking=True)
-        hdb.copy_(db, non_blocking=True)
+        dW, dx, db = backward_from(pullback, dybuf.T)
+        in_free[k].record(cur)
+        done = torch.cuda.Event()
+        done.record(cur)
+        oy, odW, odx, odb = houts[k]
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(done)
+            oy.copy_(y.T, non_blocking=True)
+            odW.copy_(dW.T, non_blocking=True)
+            odx.copy_(dx.T, non_blocking=True)
+            odb.copy_(db, non_blocking=True)
+        for t_ in (y, dW, dx, db):
+            t_.record_stream(s_out)                # keep the results alive until their download has run
 
     for _ in range(2):
         e2e_step()
@@ -349,7 +367,8 @@ def run_gpu_arm(args):
                        "parallelism": f"dp{world}: replicated W, per-GPU batch {N}, NCCL allreduce(avg) of dW and db" if world > 1 else "single GPU"},
             "clocks": clocks,
             "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": e2e_s * 1e3, "steps": e2e_steps},
+                    "ms_per_step": e2e_s * 1e3, "steps": e2e_steps,
+                    "pipeline": "uploads, compute and downloads on three streams, double-buffered; wall clock over all steps"},
             "gpu_launches": 5 * args.steps,   # fwd GEMM, g = dy*act' (+db partials), db finish, dW GEMM, dX GEMM
             "roofline": roofline,
             "cpu_baseline": cpu,
