@@ -354,6 +354,7 @@ struct ConvTc2Params {
   int32_t W, S_out, n_img, n_out;
   int32_t tiles_m, tiles_n, kW, kH, chunks, pad_w;
   int32_t stages;
+  int32_t out_stage_stride;   // bytes of output staging per epilogue group (one tile, or two with a pre-activation)
   uint32_t idesc;
   uint32_t a_desc_hi, a_desc_lbo, a_k_advance;
   uint32_t b_desc_hi, b_desc_lbo, b_k_advance;
@@ -367,10 +368,14 @@ struct ConvTc2Params {
 };
 
 constexpr int kHalo = 8;
+// warps 0-2: TMA / MMA / TMEM; warps 4-11 and 12-19: two epilogue groups of eight warps. Group g owns TMEM
+// accumulator g and every second tile, with its own edge rows, staging buffers and named barrier, so one
+// group's TMEM reads, shuffles and store run under the other's (the epilogue of a tile takes longer than its MMAs).
+constexpr int kConv2Threads = 640;
 constexpr int kTileOut = kConvBM - 2 * kHalo;   // 112 outputs per tile
 
 template <int KW, int ACT>
-__global__ void __launch_bounds__(kConvThreads, 1)
+__global__ void __launch_bounds__(kConv2Threads, 1)
 conv_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
                     const __grid_constant__ CUtensorMap tmY, const __grid_constant__ CUtensorMap tmP,
                     const __grid_constant__ ConvTc2Params p) {
@@ -392,11 +397,11 @@ conv_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
   uint64_t* acc_empty = acc_full + 2;
   uint64_t* b_full = acc_empty + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(b_full + 1);
-  // accumulator rows that cross a warp boundary: edge[parity][half][quarter][tw][3 rows][32 cols]
+  // accumulator rows that cross a warp boundary: edge[group][half][quarter][tw][3 rows][32 cols]
   float* edge = reinterpret_cast<float*>(after + 512);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(after + 448);
-  constexpr int EDGE_Q = KW * 3 * 32;   // floats per (parity, half, quarter)
-  // output staging for the TMA store: [64 channels][112 positions] bf16, one tile for y and one for the
+  constexpr int EDGE_Q = KW * 3 * 32;   // floats per (group, half, quarter)
+  // output staging for the TMA store: per group [64 channels][112 positions] bf16, one tile for y and one for the
   // pre-activation. Rows of a tile start 16 bytes off a 32-byte sector in global memory, so direct
   // 2-byte stores from registers would leave half-written sectors; the tiled store writes whole runs.
   constexpr int STAGE_OUT = BN * kTileOut * 2;
@@ -492,13 +497,17 @@ conv_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
       }
     }
   } else if (warp >= 4) {
-    const int q = warp & 3, half = (warp - 4) >> 2;   // lane quarter; which 32 of the 64 channels
+    const int grp = (warp - 4) >> 3;                  // epilogue group = TMEM accumulator it drains
+    const int q = warp & 3, half = ((warp - 4) >> 2) & 1;   // lane quarter; which 32 of the 64 channels
     const int r = q * 32 + lane;                      // MMA row of this thread
-    uint32_t acc = 0, acc_phase = 0;
+    const uint32_t acc = (uint32_t)grp;
+    uint32_t acc_phase = 0;
+    uint8_t* my_stage = out_stage + grp * p.out_stage_stride;
+    const bool leader = (warp == 4 + 8 * grp) && lane == 0;
     const __nv_bfloat16* P = reinterpret_cast<const __nv_bfloat16*>(p.preact);   // only tested for null here
     const float* sb = sbias + half * 32;
-    uint32_t parity = 0;
-    for (int t = first; t < tiles_per_n; t += step, parity ^= 1u) {
+    const uint32_t parity = (uint32_t)grp;           // edge-row buffer of this group
+    for (int t = first + grp * step; t < tiles_per_n; t += 2 * step) {
       const int s0 = (t % p.tiles_m) * kTileOut - kHalo, img = t / p.tiles_m;
       if (!mbar_wait_warp(&acc_full[acc], acc_phase, p.status, 0x10000u)) *abort_flag = 1;
       tc_fence_after();
@@ -506,7 +515,7 @@ conv_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&acc_empty[acc]);
-        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+        acc_phase ^= 1u;
         continue;
       }
       const int s = s0 + r;
@@ -531,10 +540,10 @@ conv_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
           }
         }
       }
-      // one barrier over all eight epilogue warps: edge rows are published, the previous tile's store has
-      // finished reading the staging buffers, and an expired wait is seen by everyone at the same point
-      if (warp == 4 && lane == 0) tma_store_wait_read<0>();
-      asm volatile("bar.sync 4, 256;" ::: "memory");
+      // one barrier over the group's eight warps: edge rows are published, the group's previous store has
+      // finished reading its staging buffers, and an expired wait is seen by everyone at the same point
+      if (leader) tma_store_wait_read<0>();
+      if (grp == 0) asm volatile("bar.sync 4, 256;" ::: "memory"); else asm volatile("bar.sync 5, 256;" ::: "memory");
       if (*abort_flag) break;
       // pass 2: combine the taps
       float out[32];
@@ -574,7 +583,7 @@ conv_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
       // stage the tile in shared memory ([channel][position]) and let one thread issue the tiled store
       const bool valid = r >= kHalo && r < kConvBM - kHalo;
       if (valid && !(p.debug & 8u)) {
-        __nv_bfloat16* so = reinterpret_cast<__nv_bfloat16*>(out_stage) + (half * 32) * kTileOut + (r - kHalo);
+        __nv_bfloat16* so = reinterpret_cast<__nv_bfloat16*>(my_stage) + (half * 32) * kTileOut + (r - kHalo);
         __nv_bfloat16* sp = so + BN * kTileOut;
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
@@ -583,16 +592,16 @@ conv_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
         }
       }
       fence_proxy_async_smem();
-      asm volatile("bar.sync 4, 256;" ::: "memory");
-      if (warp == 4 && lane == 0 && !(p.debug & 8u)) {
+      if (grp == 0) asm volatile("bar.sync 4, 256;" ::: "memory"); else asm volatile("bar.sync 5, 256;" ::: "memory");
+      if (leader && !(p.debug & 8u)) {
         const int so0 = (t % p.tiles_m) * kTileOut;
-        tma_store_3d(&tmY, smem_u32(out_stage), so0, n0, img);
-        if (P != nullptr) tma_store_3d(&tmP, smem_u32(out_stage + STAGE_OUT), so0, n0, img);
+        tma_store_3d(&tmY, smem_u32(my_stage), so0, n0, img);
+        if (P != nullptr) tma_store_3d(&tmP, smem_u32(my_stage + STAGE_OUT), so0, n0, img);
         tma_store_commit();
       }
-      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      acc_phase ^= 1u;
     }
-    if (warp == 4 && lane == 0) tma_store_wait_all<0>();
+    if (leader) tma_store_wait_all<0>();
   }
 
   tc_fence_before();
@@ -840,10 +849,11 @@ static int conv_fwd_stages(const ConvGemm& c) {
 }
 
 // shift-in-epilogue kernel: kernel width <= 4, filter resident next to at least 3 A stages and the edge buffers
-static int conv_fwd2_stages(const ConvGemm& c) {
+// A-ring depth; `with_preact` = the launch also stages a pre-activation tile per epilogue group
+static int conv_fwd2_stages(const ConvGemm& c, bool with_preact = true) {
   if (c.kW > 4 || c.kH > 16) return 0;
   const int resident = c.kW * c.kH * conv_chunks(c.Ck) * 64 * 128;
-  const int edges = 2 * 2 * 4 * c.kW * 3 * 32 * 4 + 2 * 64 * (kConvBM - 16) * 2;   // edge rows + output staging
+  const int edges = 2 * 2 * 4 * c.kW * 3 * 32 * 4 + 2 * (with_preact ? 2 : 1) * 64 * (kConvBM - 16) * 2;   // edge rows + output staging of both epilogue groups
   int st = (198 * 1024 - resident - edges) / (kConvBM * 128);
   return st > 8 ? 8 : st;
 }
@@ -901,7 +911,8 @@ static int32_t run_conv_gemm(void* out, void* preact, const void* bias, int32_t 
     q.tiles_m = (q.S_out + kTileOut - 1) / kTileOut;
     q.tiles_n = (c.Cn + 63) / 64;
     q.kW = c.kW; q.kH = c.kH; q.chunks = conv_chunks(c.Ck); q.pad_w = c.pad_w;
-    q.stages = conv_fwd2_stages(c);
+    q.stages = conv_fwd2_stages(c, preact != nullptr);
+    q.out_stage_stride = (preact != nullptr ? 2 : 1) * 64 * kTileOut * 2;
     for (int th = 0; th < c.kH; ++th) q.row_shift[th] = (int16_t)((th - c.pad_h) * c.W);
     q.a_desc_hi = (uint32_t)((1024u >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
     q.a_desc_lbo = ((8192u >> 4) & 0x3FFFu) << 16;
@@ -922,7 +933,7 @@ static int32_t run_conv_gemm(void* out, void* preact, const void* bias, int32_t 
         !bf16_map_out(&mY2, out, q.S_out, c.Cn, c.N) || !bf16_map_out(&mP2, preact != nullptr ? preact : out, q.S_out, c.Cn, c.N))
       return fail(LB2_LAUNCH_FAIL, "conv_tc: cuTensorMapEncodeTiled failed");
     const int num_b = c.kW * c.kH * q.chunks;
-    const int smem2 = num_b * 64 * 128 + q.stages * kConvBM * 128 + 512 + 2 * 2 * 4 * c.kW * 3 * 32 * 4 + 2 * 64 * kTileOut * 2 + 1024 + 256;
+    const int smem2 = num_b * 64 * 128 + q.stages * kConvBM * 128 + 512 + 2 * 2 * 4 * c.kW * 3 * 32 * 4 + 2 * q.out_stage_stride + 1024 + 256;
     const int tiles_per_n2 = q.tiles_m * q.n_img;
     int per_n2 = sm_count() / q.tiles_n;
     if (per_n2 > tiles_per_n2) per_n2 = tiles_per_n2;
@@ -931,7 +942,7 @@ static int32_t run_conv_gemm(void* out, void* preact, const void* bias, int32_t 
     auto launch2 = [&](auto kernel) -> int32_t {
       cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2);
       if (e != cudaSuccess) return fail(LB2_LAUNCH_FAIL, "conv_tc: cannot reserve %d bytes of shared memory: %s", smem2, cudaGetErrorString(e));
-      kernel<<<grid2, kConvThreads, smem2, st>>>(mX2, mW2, mY2, mP2, q);
+      kernel<<<grid2, kConv2Threads, smem2, st>>>(mX2, mW2, mY2, mP2, q);
       LB2_CHECK_LAUNCH("conv_tc_fwd2");
       return LB2_OK;
     };
