@@ -70,8 +70,21 @@ def cpu_step(W, x, b, dy):
     return y, pb(dy)
 
 
+def use_all_host_threads() -> int:
+    """torchrun exports OMP_NUM_THREADS=1; the CPU arms are meant to use every host core, so the BLAS pool is
+    widened again at run time. Returns the thread count in effect."""
+    cores = os.cpu_count() or 1
+    try:
+        from threadpoolctl import threadpool_limits
+        threadpool_limits(limits=cores)
+    except Exception:
+        pass
+    return cores
+
+
 def cpu_tflops(n_cols: int, reps: int, seed: int = 1):
     from oracle import luxlib_oracle as O
+    use_all_host_threads()
     W, x, b, dy = make_inputs(seed, n_cols)
     W, x, b, dy = (O.round_bf16(a) for a in (W, x, b, dy))
     cpu_step(W, x, b, dy)  # warm the BLAS threads

@@ -65,6 +65,35 @@ def test_status_codes_for_bad_arguments():
     assert lib.lb2_status_string(_cabi.TIMEOUT) == b"device-side wait timed out"
 
 
+def test_status_codes_of_the_pooling_optimizer_and_instancenorm_entry_points():
+    import ctypes as C
+    lib = _cabi.load()
+    d = _cabi.PoolDesc()
+    d.ndim, d.channels, d.batch = 2, 3, 2
+    for i in range(3):
+        d.in_[i], d.k[i], d.stride[i], d.dilation[i] = (8, 2, 2, 1) if i < 2 else (1, 1, 1, 1)
+    out = (C.c_int32 * 3)()
+    assert lib.lb2_pool_output_size(C.byref(d), out) == _cabi.OK and (out[0], out[1]) == (4, 4)
+    assert lib.lb2_pool_fwd(None, None, C.byref(d), _cabi.POOL_MAX, _cabi.F32, None) == _cabi.BAD_ARG      # null tensors
+    assert lib.lb2_pool_fwd(None, None, C.byref(d), 7, _cabi.F32, None) == _cabi.BAD_ARG                   # unknown kind
+    assert lib.lb2_pool_fwd(None, None, C.byref(d), _cabi.POOL_MAX, 9, None) == _cabi.UNSUPPORTED_DTYPE
+    assert lib.lb2_pool_bwd(16, 16, None, None, C.byref(d), _cabi.POOL_MAX, _cabi.F32, None) == _cabi.BAD_ARG  # max needs y, x
+    d.stride[0] = 0
+    assert lib.lb2_pool_output_size(C.byref(d), out) == _cabi.BAD_SHAPE
+    d.stride[0], d.batch = 2, 0
+    assert lib.lb2_pool_fwd(None, None, C.byref(d), _cabi.POOL_MEAN, _cabi.F32, None) == _cabi.OK          # empty batch
+    leaf = (_cabi.OptLeaf * 1)()
+    leaf[0].param, leaf[0].grad, leaf[0].n = 16, 32, 4
+    assert lib.lb2_optimizer_step(leaf, 1, 5, 0.1, 0.9, 0.999, 1e-8, 1, 1.0, _cabi.F32, None) == _cabi.BAD_ARG      # unknown rule
+    assert lib.lb2_optimizer_step(leaf, 1, _cabi.OPT_ADAM, 0.1, 0.9, 0.999, 1e-8, 1, 1.0, _cabi.F32, None) == _cabi.BAD_ARG   # no state
+    assert lib.lb2_optimizer_step(leaf, 1, _cabi.OPT_DESCENT, 0.1, 0.9, 0.999, 1e-8, 0, 1.0, _cabi.F32, None) == _cabi.BAD_ARG  # step from 1
+    leaf[0].param = 18
+    assert lib.lb2_optimizer_step(leaf, 1, _cabi.OPT_DESCENT, 0.1, 0.0, 0.0, 0.0, 1, 1.0, _cabi.F32, None) == _cabi.BAD_ALIGN
+    assert lib.lb2_optimizer_step(None, 0, _cabi.OPT_DESCENT, 0.1, 0.0, 0.0, 0.0, 1, 1.0, _cabi.F32, None) == _cabi.OK         # nothing to do
+    assert lib.lb2_instancenorm_update_stats(None, None, None, None, None, None, 4, 3, 2, 0.1, 1e-5, _cabi.F32, None) == _cabi.BAD_ARG
+    assert lib.lb2_instancenorm_update_stats(None, None, None, None, None, None, 4, 0, 2, 0.1, 1e-5, _cabi.F32, None) == _cabi.OK
+
+
 def test_static_scratch_entry_point_rejects_oversized_problems_before_touching_the_gpu():
     lib = _cabi.load()
     S, C, B = 1, 1 << 18, 2
