@@ -772,6 +772,177 @@ conv_tc_wgrad_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
   }
 }
 
+// ----------------------------------------------------------------------------------------------
+// filter-gradient kernel, wide-N variant (kernel width <= 4)
+// ----------------------------------------------------------------------------------------------
+// The cost of a tcgen05.mma here depends little on its width, so the narrow (N = 64) MMAs of the kernel above are
+// bound by their count. This variant turns the problem around: M = 128 output channels (rows of g), N = kW * 64 =
+// the kW taps of one kernel row x 64 input channels (the kW shifted copies of x side by side), so one MMA covers
+// what kW of the narrow ones did. A work item is (kernel row, 64-channel chunk, 128-channel output tile, K split);
+// partial[z][group][co_local][tw*64 + ci_local] in fp32, reduced in a fixed order afterwards.
+struct ConvWg2Params {
+  int32_t n_img;
+  int32_t s_blocks;                 // 64-position blocks per image
+  int32_t kW, kH, chunks, co_tiles; // groups = kH * chunks * co_tiles
+  int32_t splits, kb_total, kb_per_split;
+  uint32_t idesc;
+  uint32_t desc_hi, desc_lbo, k_advance;   // both operands K-major SW128
+  float* partial;
+  unsigned int* status;
+  int16_t row_shift[16];            // per kernel row th: (th - pad_h) * W
+};
+
+template <int KW>
+__global__ void __launch_bounds__(kConvThreads, 1)
+conv_tc_wgrad2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmG,
+                      const __grid_constant__ ConvWg2Params p) {
+  constexpr int BN = KW * 64;
+  constexpr int A_BYTES = kConvBM * 128;      // 128 output channels x 64 positions
+  constexpr int B_BYTES = BN * 128;           // kW taps x 64 input channels x 64 positions
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr int STAGES = (200 * 1024) / STAGE_BYTES > 8 ? 8 : (200 * 1024) / STAGE_BYTES;
+  constexpr uint32_t TMEM_COLS = 2 * BN > 256 ? 512u : (2 * BN > 128 ? 256u : 128u);
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + STAGES * STAGE_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + STAGES;
+  uint64_t* acc_full = bars + 2 * STAGES;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int groups = p.kH * p.chunks * p.co_tiles;
+  const int num_items = groups * p.splits;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 8); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 2) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // item -> (group fastest, split); group -> (co tile fastest, chunk, kernel row)
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tmX);
+      tma_prefetch_desc(&tmG);
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+        const int grp = item % groups, z = item / groups;
+        const int ct = grp % p.co_tiles, chunk = (grp / p.co_tiles) % p.chunks, th = grp / (p.co_tiles * p.chunks);
+        const int kb_lo = z * p.kb_per_split, kb_hi = min(p.kb_total, kb_lo + p.kb_per_split);
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1u, p.status, 0x20000u)) { ok = false; break; }
+          const int img = kb / p.s_blocks, s0 = (kb % p.s_blocks) * 64;
+          const uint32_t sA = smem_base + stage * STAGE_BYTES, sB = sA + A_BYTES;
+          mbar_expect_tx(&full[stage], (uint32_t)STAGE_BYTES);
+          tma_load_4d(sA, &tmG, s0, ct * 128, img, 0, &full[stage]);
+          tma_load_4d(sA + A_BYTES / 2, &tmG, s0, ct * 128 + 64, img, 0, &full[stage]);   // rows past the last channel are zero-filled
+#pragma unroll
+          for (int tw = 0; tw < KW; ++tw)
+            tma_load_4d(sB + tw * (64 * 128), &tmX, s0 + p.row_shift[th], chunk * 64, img, tw, &full[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+        const int z = item / groups;
+        const int kb_lo = z * p.kb_per_split, kb_hi = min(p.kb_total, kb_lo + p.kb_per_split);
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1u, p.status, 0x40000u)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {
+          if (!mbar_wait(&full[stage], phase, p.status, 0x80000u)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sA = smem_base + stage * STAGE_BYTES, sB = sA + A_BYTES;
+          const uint32_t a_lo32 = ((sA >> 4) & 0x3FFFu) | p.desc_lbo;
+          const uint32_t b_lo32 = ((sB >> 4) & 0x3FFFu) | p.desc_lbo;
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) {
+            const uint64_t ad = ((uint64_t)p.desc_hi << 32) | (uint64_t)(a_lo32 + ks * p.k_advance);
+            const uint64_t bd = ((uint64_t)p.desc_hi << 32) | (uint64_t)(b_lo32 + ks * p.k_advance);
+            umma<false>(d_tmem, ad, bd, p.idesc, (kb > kb_lo || ks != 0) ? 1u : 0u);
+          }
+          umma_commit(&empty[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) umma_commit(&acc_full[acc]);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  } else if (warp >= 4) {
+    const int q = warp & 3, half = (warp - 4) >> 2;   // lane quarter; which half of the BN columns
+    constexpr int COLS = BN / 2;
+    uint32_t acc = 0, acc_phase = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+      const int grp = item % groups, z = item / groups;
+      if (!mbar_wait_warp(&acc_full[acc], acc_phase, p.status, 0x100000u)) { ok = false; break; }
+      tc_fence_after();
+      const int row = q * 32 + lane;
+      float* dst = p.partial + (((int64_t)z * groups + grp) * 128 + row) * BN + half * COLS;
+#pragma unroll 1
+      for (int c = 0; c < COLS / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + half * COLS + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) dst[c * 32 + j] = __uint_as_float(r[j]);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    if (*reinterpret_cast<volatile unsigned int*>(p.status) != 0) {
+      for (int i = 0; i < 64; ++i) __nanosleep(2000);
+    }
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// dw[kw,kh,ci,co] = sum over splits (ascending) of partial[z][(th, chunk, co tile)][co % 128][tw*64 + ci % 64]
+template <typename T>
+__global__ void __launch_bounds__(256) conv_wgrad2_reduce_kernel(T* __restrict__ dw, const float* __restrict__ partial,
+                                                                 int kW, int kH, int cin, int cout, int flip, int chunks,
+                                                                 int co_tiles, int splits) {
+  const int64_t total = (int64_t)kW * kH * cin * cout;
+  const int groups = kH * chunks * co_tiles, bn = kW * 64;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t r = i;
+    const int kw = (int)(r % kW); r /= kW;
+    const int kh = (int)(r % kH); r /= kH;
+    const int ci = (int)(r % cin);
+    const int co = (int)(r / cin);
+    const int tw = flip ? kw : kW - 1 - kw, th = flip ? kh : kH - 1 - kh;
+    const int grp = (th * chunks + ci / 64) * co_tiles + co / 128;
+    const int64_t off = ((int64_t)grp * 128 + co % 128) * bn + tw * 64 + ci % 64;
+    float s = 0.f;
+    for (int z = 0; z < splits; ++z) s += partial[(int64_t)z * groups * 128 * bn + off];
+    dw[i] = from_f32<T>(s);
+  }
+}
+
 // dw[kw,kh,ci,co] = sum over splits (ascending) of partial[z][(tap, chunk, ci % 64)][co]
 template <typename T>
 __global__ void __launch_bounds__(256) conv_wgrad_reduce_kernel(T* __restrict__ dw, const float* __restrict__ partial,
@@ -1088,11 +1259,42 @@ static size_t wg_partial_bytes(const WgPlan& w) {
   return align_up((size_t)w.splits * w.m_tiles * 128 * w.n_pad * sizeof(float), 1024);
 }
 
+// wide-N variant: kernel width <= 4 (N = kW * 64 <= 256), kH <= 16
+struct Wg2Plan {
+  bool ok;
+  int chunks, co_tiles, groups, s_blocks, kb_total, splits, kb_per_split;
+};
+static Wg2Plan wg2_plan(const ConvGeom& g) {
+  Wg2Plan w{};
+  static const int enabled = getenv("LB2_CONV_WGRAD_WIDE") ? atoi(getenv("LB2_CONV_WGRAD_WIDE")) : 1;
+  if (!enabled || g.k[0] > 4 || g.k[1] > 16) return w;
+  w.ok = true;
+  w.chunks = conv_chunks(g.cin);
+  w.co_tiles = (g.cout + 127) / 128;
+  w.groups = g.k[1] * w.chunks * w.co_tiles;
+  const int S_out = g.out[0] * g.out[1];
+  w.s_blocks = (S_out + 63) / 64;
+  w.kb_total = g.batch * w.s_blocks;
+  int splits = sm_count() / w.groups;
+  if (splits < 1) splits = 1;
+  if (splits > w.kb_total) splits = w.kb_total;
+  w.kb_per_split = (w.kb_total + splits - 1) / splits;
+  w.splits = (w.kb_total + w.kb_per_split - 1) / w.kb_per_split;
+  return w;
+}
+static size_t wg2_partial_bytes(const ConvGeom& g, const Wg2Plan& w) {
+  return align_up((size_t)w.splits * w.groups * 128 * (g.k[0] * 64) * sizeof(float), 1024);
+}
+static size_t wg_any_partial_bytes(const ConvGeom& g) {
+  const Wg2Plan w2 = wg2_plan(g);
+  return w2.ok ? wg2_partial_bytes(g, w2) : wg_partial_bytes(wg_plan(g));
+}
+
 size_t conv_tc_bwd_workspace_bytes(const ConvGeom& g, int32_t dtype) {
   if (dtype == LB2_F32) return conv_tc_f32_bwd_workspace_bytes(g);
   const ConvGemm d = dgrad_gemm(g), f = fwd_gemm(g);
   const size_t dgrad = gemm_copies_bytes(d) + packed_bytes(d);
-  const size_t wgrad = copies_bytes(f) + wg_partial_bytes(wg_plan(g));
+  const size_t wgrad = copies_bytes(f) + wg_any_partial_bytes(g);
   return dgrad > wgrad ? dgrad : wgrad;   // the two gradients run one after the other in the same region
 }
 
@@ -1114,6 +1316,46 @@ int32_t conv_tc_wgrad(void* dw, const void* x, const void* gy, const ConvGeom& g
   if (!launch_shift_copies_vec(copies, x, f.W, rows, f.kW, f.pad_w, flat_grid_tc(rows * (f.W / 8)), st))
     conv_shift_copies_kernel<T><<<flat_grid_tc(rows * ((f.W + 7) / 8)), 256, 0, st>>>(copies, (const T*)x, f.W, rows, f.kW, f.pad_w);
   LB2_CHECK_LAUNCH("conv_tc shifted copies");
+  const Wg2Plan w2 = wg2_plan(g);
+  if (w2.ok) {
+    ConvWg2Params q{};
+    q.n_img = g.batch; q.s_blocks = w2.s_blocks;
+    q.kW = f.kW; q.kH = f.kH; q.chunks = w2.chunks; q.co_tiles = w2.co_tiles;
+    q.splits = w2.splits; q.kb_total = w2.kb_total; q.kb_per_split = w2.kb_per_split;
+    q.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)((f.kW * 64) >> 3) << 17) | ((uint32_t)(kConvBM >> 4) << 24);
+    q.desc_hi = (uint32_t)((1024u >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
+    q.desc_lbo = 1u << 16;
+    q.k_advance = 32u >> 4;
+    q.partial = partial;
+    q.status = device_status_word();
+    LB2_REQUIRE(q.status != nullptr, LB2_LAUNCH_FAIL, "conv_tc: device status word unavailable");
+    for (int th = 0; th < f.kH; ++th) q.row_shift[th] = (int16_t)((th - f.pad_h) * f.W);
+    CUtensorMap mX2, mG2;
+    if (!bf16_map_4d(&mX2, copies, (int64_t)f.W * f.Hi, f.Ck, f.N, f.kW, 64, 64) ||
+        !bf16_map_4d(&mG2, gy, (int64_t)g.out[0] * g.out[1], g.cout, g.batch, 1, 64, 64))
+      return fail(LB2_LAUNCH_FAIL, "conv_tc: cuTensorMapEncodeTiled failed");
+    const int stage_bytes = kConvBM * 128 + f.kW * 64 * 128;
+    int nst = (200 * 1024) / stage_bytes;
+    if (nst > 8) nst = 8;
+    const int smem2 = nst * stage_bytes + 1024 + 256 + 64 * 8;
+    const int items2 = w2.groups * w2.splits;
+    const int grid2 = items2 < sm_count() ? items2 : sm_count();
+    auto launch2 = [&](auto kernel) -> int32_t {
+      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2);
+      if (e != cudaSuccess) return fail(LB2_LAUNCH_FAIL, "conv_tc: cannot reserve %d bytes of shared memory: %s", smem2, cudaGetErrorString(e));
+      kernel<<<grid2, kConvThreads, smem2, st>>>(mX2, mG2, q);
+      LB2_CHECK_LAUNCH("conv_tc_wgrad2");
+      return LB2_OK;
+    };
+    int32_t rc2 = f.kW == 1 ? launch2(conv_tc_wgrad2_kernel<1>) : f.kW == 2 ? launch2(conv_tc_wgrad2_kernel<2>)
+                : f.kW == 3 ? launch2(conv_tc_wgrad2_kernel<3>) : launch2(conv_tc_wgrad2_kernel<4>);
+    if (rc2 != LB2_OK) return rc2;
+    const int64_t nw2 = (int64_t)g.k[0] * g.k[1] * g.cin * g.cout;
+    conv_wgrad2_reduce_kernel<T><<<flat_grid_tc(nw2), 256, 0, st>>>((T*)dw, partial, g.k[0], g.k[1], g.cin, g.cout, g.flip, w2.chunks,
+                                                                 w2.co_tiles, w2.splits);
+    LB2_CHECK_LAUNCH("conv_wgrad2_reduce");
+    return LB2_OK;
+  }
   ConvWgParams p{};
   p.S_out = g.out[0] * g.out[1];
   p.n_img = g.batch; p.n_out = g.cout;
