@@ -37,7 +37,7 @@ constexpr int kMaxKb = 96;
 // out[t][n][c][h][w] = in[n][c][h][w + t - pad_w]  (0 outside the row), t = 0..kW-1
 template <typename T>
 __global__ void __launch_bounds__(256) conv_shift_copies_kernel(T* __restrict__ out, const T* __restrict__ in,
-                                                                int W, int64_t rows, int kW, int pad_w) {
+                                                                int W, int64_t rows, int kW, int pad_w, int skip) {
   // one thread per 8-element group of a row; rows = H*C*N
   const int groups = (W + 7) / 8;
   const int64_t total = rows * groups;
@@ -54,6 +54,7 @@ __global__ void __launch_bounds__(256) conv_shift_copies_kernel(T* __restrict__ 
       win[j] = (j < 8 + kW - 1 && w >= 0 && w < W) ? src[w] : from_f32<T>(0.f);
     }
     for (int t = 0; t < kW; ++t) {
+      if (t == skip) continue;   // the caller reads this copy (shift 0) from the input itself
       T* dst = out + ((int64_t)t * rows + row) * W + w0;
 #pragma unroll
       for (int j = 0; j < 8; ++j)
@@ -67,7 +68,7 @@ __global__ void __launch_bounds__(256) conv_shift_copies_kernel(T* __restrict__ 
 // cut out of the three aligned vectors around it with static funnel shifts.
 template <int KW, int PAD>
 __global__ void __launch_bounds__(256) conv_shift_copies_vec_kernel(uint16_t* __restrict__ out, const uint16_t* __restrict__ in,
-                                                                    int W, int64_t rows) {
+                                                                    int W, int64_t rows, int skip) {
   const int groups = W / 8;
   const int64_t total = rows * groups;
   const int64_t copy_stride = rows * W;
@@ -82,6 +83,7 @@ __global__ void __launch_bounds__(256) conv_shift_copies_vec_kernel(uint16_t* __
     const uint32_t win[12] = {vm.x, vm.y, vm.z, vm.w, v0.x, v0.y, v0.z, v0.w, vp.x, vp.y, vp.z, vp.w};  // 24 elements, ours at 8..15
 #pragma unroll
     for (int t = 0; t < KW; ++t) {
+      if (t == skip) continue;              // the caller reads this copy (shift 0) from the input itself
       constexpr int BASE = 8 - PAD;         // element index of output 0 of copy 0 inside the window
       const int e = BASE + t;               // compile-time after unrolling
       uint32_t o[4];
@@ -96,12 +98,12 @@ __global__ void __launch_bounds__(256) conv_shift_copies_vec_kernel(uint16_t* __
 }
 
 static bool launch_shift_copies_vec(void* out, const void* in, int W, int64_t rows, int kW, int pad_w, unsigned grid,
-                                    cudaStream_t st) {
+                                    cudaStream_t st, int skip = -1) {
   uint16_t* o = static_cast<uint16_t*>(out);
   const uint16_t* i = static_cast<const uint16_t*>(in);
 #define LB2_SHIFT_CASE(KW_, PAD_)                                                         \
   if (kW == KW_ && pad_w == PAD_) {                                                       \
-    conv_shift_copies_vec_kernel<KW_, PAD_><<<grid, 256, 0, st>>>(o, i, W, rows);         \
+    conv_shift_copies_vec_kernel<KW_, PAD_><<<grid, 256, 0, st>>>(o, i, W, rows, skip);   \
     return true;                                                                          \
   }
   LB2_SHIFT_CASE(1, 0)
@@ -789,13 +791,14 @@ struct ConvWg2Params {
   uint32_t desc_hi, desc_lbo, k_advance;   // both operands K-major SW128
   float* partial;
   unsigned int* status;
+  int32_t center_tw;                // tap whose shift along W is zero: read from x itself (-1: none)
   int16_t row_shift[16];            // per kernel row th: (th - pad_h) * W
 };
 
 template <int KW>
 __global__ void __launch_bounds__(kConvThreads, 1)
-conv_tc_wgrad2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmG,
-                      const __grid_constant__ ConvWg2Params p) {
+conv_tc_wgrad2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmX0,
+                      const __grid_constant__ CUtensorMap tmG, const __grid_constant__ ConvWg2Params p) {
   constexpr int BN = KW * 64;
   constexpr int A_BYTES = kConvBM * 128;      // 128 output channels x 64 positions
   constexpr int B_BYTES = BN * 128;           // kW taps x 64 input channels x 64 positions
@@ -834,6 +837,7 @@ conv_tc_wgrad2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
   if (warp == 0) {
     if (lane == 0) {
       tma_prefetch_desc(&tmX);
+      tma_prefetch_desc(&tmX0);
       tma_prefetch_desc(&tmG);
       uint32_t stage = 0, phase = 0;
       bool ok = true;
@@ -849,8 +853,10 @@ conv_tc_wgrad2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
           tma_load_4d(sA, &tmG, s0, ct * 128, img, 0, &full[stage]);
           tma_load_4d(sA + A_BYTES / 2, &tmG, s0, ct * 128 + 64, img, 0, &full[stage]);   // rows past the last channel are zero-filled
 #pragma unroll
-          for (int tw = 0; tw < KW; ++tw)
-            tma_load_4d(sB + tw * (64 * 128), &tmX, s0 + p.row_shift[th], chunk * 64, img, tw, &full[stage]);
+          for (int tw = 0; tw < KW; ++tw) {
+            if (tw == p.center_tw) tma_load_4d(sB + tw * (64 * 128), &tmX0, s0 + p.row_shift[th], chunk * 64, img, 0, &full[stage]);
+            else tma_load_4d(sB + tw * (64 * 128), &tmX, s0 + p.row_shift[th], chunk * 64, img, tw, &full[stage]);
+          }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
@@ -1135,7 +1141,7 @@ static int32_t run_conv_gemm(void* out, void* preact, const void* bias, int32_t 
   T* wp = reinterpret_cast<T*>(ws + copies_bytes(c));
   const int64_t rows = (int64_t)c.Hi * c.Ck * c.N;
   if (!launch_shift_copies_vec(copies, in, c.W, rows, c.kW, c.pad_w, flat_grid_tc(rows * (c.W / 8)), st))
-    conv_shift_copies_kernel<T><<<flat_grid_tc(rows * ((c.W + 7) / 8)), 256, 0, st>>>(copies, (const T*)in, c.W, rows, c.kW, c.pad_w);
+    conv_shift_copies_kernel<T><<<flat_grid_tc(rows * ((c.W + 7) / 8)), 256, 0, st>>>(copies, (const T*)in, c.W, rows, c.kW, c.pad_w, -1);
   conv_pack_filter_kernel<T><<<flat_grid_tc((int64_t)pg.n_rows * pg.k_total), 256, 0, st>>>(wp, (const T*)w, pg);
   LB2_CHECK_LAUNCH("conv_tc layout passes");
 
@@ -1313,10 +1319,12 @@ int32_t conv_tc_wgrad(void* dw, const void* x, const void* gy, const ConvGeom& g
   T* copies = reinterpret_cast<T*>(ws);
   float* partial = reinterpret_cast<float*>(ws + copies_bytes(f));
   const int64_t rows = (int64_t)f.Hi * f.Ck * f.N;
-  if (!launch_shift_copies_vec(copies, x, f.W, rows, f.kW, f.pad_w, flat_grid_tc(rows * (f.W / 8)), st))
-    conv_shift_copies_kernel<T><<<flat_grid_tc(rows * ((f.W + 7) / 8)), 256, 0, st>>>(copies, (const T*)x, f.W, rows, f.kW, f.pad_w);
-  LB2_CHECK_LAUNCH("conv_tc shifted copies");
   const Wg2Plan w2 = wg2_plan(g);
+  // the wide-N kernel reads the unshifted tap straight from x, so that copy is not made
+  const int skip = (w2.ok && f.pad_w >= 0 && f.pad_w < f.kW) ? f.pad_w : -1;
+  if (!launch_shift_copies_vec(copies, x, f.W, rows, f.kW, f.pad_w, flat_grid_tc(rows * (f.W / 8)), st, skip))
+    conv_shift_copies_kernel<T><<<flat_grid_tc(rows * ((f.W + 7) / 8)), 256, 0, st>>>(copies, (const T*)x, f.W, rows, f.kW, f.pad_w, skip);
+  LB2_CHECK_LAUNCH("conv_tc shifted copies");
   if (w2.ok) {
     ConvWg2Params q{};
     q.n_img = g.batch; q.s_blocks = w2.s_blocks;
@@ -1330,8 +1338,10 @@ int32_t conv_tc_wgrad(void* dw, const void* x, const void* gy, const ConvGeom& g
     q.status = device_status_word();
     LB2_REQUIRE(q.status != nullptr, LB2_LAUNCH_FAIL, "conv_tc: device status word unavailable");
     for (int th = 0; th < f.kH; ++th) q.row_shift[th] = (int16_t)((th - f.pad_h) * f.W);
-    CUtensorMap mX2, mG2;
+    q.center_tw = skip;
+    CUtensorMap mX2, mX0, mG2;
     if (!bf16_map_4d(&mX2, copies, (int64_t)f.W * f.Hi, f.Ck, f.N, f.kW, 64, 64) ||
+        !bf16_map_4d(&mX0, x, (int64_t)f.W * f.Hi, f.Ck, f.N, 1, 64, 64) ||
         !bf16_map_4d(&mG2, gy, (int64_t)g.out[0] * g.out[1], g.cout, g.batch, 1, 64, 64))
       return fail(LB2_LAUNCH_FAIL, "conv_tc: cuTensorMapEncodeTiled failed");
     const int stage_bytes = kConvBM * 128 + f.kW * 64 * 128;
@@ -1343,7 +1353,7 @@ int32_t conv_tc_wgrad(void* dw, const void* x, const void* gy, const ConvGeom& g
     auto launch2 = [&](auto kernel) -> int32_t {
       cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2);
       if (e != cudaSuccess) return fail(LB2_LAUNCH_FAIL, "conv_tc: cannot reserve %d bytes of shared memory: %s", smem2, cudaGetErrorString(e));
-      kernel<<<grid2, kConvThreads, smem2, st>>>(mX2, mG2, q);
+      kernel<<<grid2, kConvThreads, smem2, st>>>(mX2, mX0, mG2, q);
       LB2_CHECK_LAUNCH("conv_tc_wgrad2");
       return LB2_OK;
     };
