@@ -203,7 +203,7 @@ def run_gpu_arm(args):
         dist.init_process_group("nccl", device_id=device)
     lib = _cabi.load()
     if world > 1:   # leave a few SMs to the NCCL all-reduce that runs under the dX GEMM
-        lib.lb2_set_reserved_sms(int(os.environ.get("LB2_BENCH_RESERVED_SMS", "0")))
+        pass
 
     # every rank holds the same parameters and its own batch shard
     Wn, xn, bn, dyn = make_inputs(1, N)

@@ -66,16 +66,17 @@ typedef enum {
 #define LB2_FLAG_TF32_1X 1u /* fp32 GEMM/conv: single-pass TF32 (rel err ~1e-3) instead of the
                                default error-compensated 3xTF32 split (rel err ~1e-6) */
 #define LB2_FLAG_FORCE_SIMT 2u /* route a contraction through the CUDA-core kernel (debug / odd shapes) */
-#define LB2_FLAG_CTA_PAIR 4u /* tensor-core GEMM: use the CTA-pair (cta_group::2, 256x256 tile) kernel when the problem is large enough */
+#define LB2_FLAG_CTA_PAIR 4u /* tensor-core GEMM: take the CTA-pair kernel (cta_group::2, 256x256 tiles) already for problems
+                                that occupy an eighth of the SM pairs (default: from about three quarters on) */
+#define LB2_FLAG_NO_CTA_PAIR 8u /* tensor-core GEMM: never take the CTA-pair kernel */
+/* Per call: the persistent tensor-core GEMM of this call leaves n SMs (0..127) unoccupied, for a kernel the caller
+ * runs beside it on another stream — e.g. the NCCL all-reduce of parameter gradients that Lux's DistributedOptimizer
+ * issues (src/distributed/public_api.jl:275-278) under the remaining backward GEMM. */
+#define LB2_FLAG_RESERVE_SMS(n) (((uint32_t)(n) & 0x7Fu) << 16)
 
 /* ---- library ------------------------------------------------------------------------- */
 LB2_API int32_t lb2_version(void);
 LB2_API const char* lb2_status_string(int32_t status);
-/* Process-wide: the persistent tensor-core GEMM launches at most (SM count - n) CTAs, leaving n SMs
- * free for a kernel that runs beside it — the NCCL all-reduce of parameter gradients that Lux's
- * DistributedOptimizer issues (src/distributed/public_api.jl:275-278) can then overlap with the
- * remaining backward GEMM. n = 0 (default) uses every SM. */
-LB2_API int32_t lb2_set_reserved_sms(int32_t n);
 /* Thread-local description of the last non-OK status returned on this thread. Mirrors the
  * 0 / -1 + warning convention of cublaslt_matmul_fused!
  * (lib/LuxLib/ext/CUDAExt/cublaslt.jl:184-185,292), without its fallback (:386-402). */
@@ -117,7 +118,9 @@ LB2_API int32_t lb2_dense_fwd(void* y, void* preact, const void* W, const void* 
  *   g  = dy .* act'(out, preact)          (out and/or preact as for lb2_act_bwd; ld = ldy)
  *   dW = g * x'   dx = W' * g   db = sum over columns of g
  * Any of dW, dx, db may be NULL (not computed). accumulate != 0 adds into dW, dx, db instead of
- * overwriting them — the Enzyme shadow contract (lib/LuxLib/src/impl/dense.jl:253-283). */
+ * overwriting them — the Enzyme shadow contract (lib/LuxLib/src/impl/dense.jl:253-283:
+ *   mul!(dW, g, x', true, true); mul!(dx, W', g, true, true); db .+= sum(g)). The last step of that rule,
+ * zeroing the output shadow dy (impl/dense.jl:281), is left to the caller: dy is read-only here. */
 LB2_API size_t lb2_dense_bwd_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t dtype, int32_t act,
                                      uint32_t flags);
 LB2_API int32_t lb2_dense_bwd(void* dW, void* dx, void* db, const void* dy, const void* out,
@@ -188,9 +191,14 @@ LB2_API int32_t lb2_batchnorm_fwd_train(void* y, float* save_mean, float* save_i
  * inside the library (LB2_BATCHNORM_STATIC_SCRATCH_BYTES per GPU, held from library load until
  * process exit); the call allocates nothing and calls no allocating routine. Problems whose scratch
  * need (lb2_batchnorm_workspace_bytes) exceeds that size are rejected with
- * LB2_WORKSPACE_TOO_SMALL. The first call on each device looks up the array's device address;
- * make that first call before any stream capture. All calls on a device share the one array:
- * two calls whose kernels may overlap on the GPU (different streams) race on it — serialise them. */
+ * LB2_WORKSPACE_TOO_SMALL (argument errors and empty problems are answered before the device is
+ * touched). The first call on each device looks up the array's device address, and the first call
+ * of each kernel variant (storage type x activation x small-tensor / single-launch path) makes the
+ * CUDA runtime load that kernel's code, which may allocate and synchronise inside the driver: make
+ * one call of every variant you will use before any stream capture and before entering a context
+ * where that is not allowed. All calls on a device share the one array, which keeps the previous
+ * call's contents (the call clears the words that must start at zero): two calls whose kernels may
+ * overlap on the GPU (different streams) race on it — serialise them. */
 #define LB2_BATCHNORM_STATIC_SCRATCH_BYTES (4u << 20)
 LB2_API int32_t lb2_batchnorm_fwd_train_static(void* y, float* save_mean, float* save_invstd,
                                                void* new_rmean, void* new_rvar, const void* x,
@@ -210,6 +218,16 @@ LB2_API int32_t lb2_batchnorm_bwd(void* dx, void* dgamma, void* dbeta, const voi
                           const void* gamma, const void* beta, const float* save_mean,
                           const float* save_invstd, int64_t S, int64_t C, int64_t B, int32_t dtype,
                           int32_t act, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Backward of the forward with GIVEN statistics (inference mode, "frozen" BatchNorm): the rrule of
+ * batchnorm_affine_normalize_internal (lib/LuxLib/src/impl/batchnorm.jl:405-443) differentiates for whatever mean
+ * and variance it is handed; statistics that did not come from the batch carry no gradient, so
+ *   dx = dy*act' * gamma/sqrt(rvar+eps),  dgamma = sum(dy*act' * (x-rmean)/sqrt(rvar+eps)),  dbeta = sum(dy*act').
+ * Workspace: lb2_batchnorm_workspace_bytes(S, C, B). */
+LB2_API int32_t lb2_batchnorm_bwd_infer(void* dx, void* dgamma, void* dbeta, const void* dy, const void* x,
+                                const void* gamma, const void* beta, const void* rmean, const void* rvar,
+                                int64_t S, int64_t C, int64_t B, double eps, int32_t dtype, int32_t act,
+                                void* workspace, size_t workspace_bytes, void* stream);
 
 /* ---- pooling ------------------------------------------------------------------------------- */
 /* Max / mean pooling on WHCN arrays: x (in..., channels, batch) -> y (out..., channels, batch). Backs the

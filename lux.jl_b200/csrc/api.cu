@@ -43,13 +43,6 @@ int sm_count() {
   return g_sm_count[dev];
 }
 
-// SMs the persistent tensor-core kernels leave free (for a collective running beside them).
-static int g_reserved_sms = 0;
-int persistent_sm_budget() {
-  int n = sm_count() - g_reserved_sms;
-  return n < 1 ? 1 : n;
-}
-
 // One status word per device, living in the module's own global memory (no allocation).
 __device__ unsigned int g_device_status = 0;
 
@@ -64,12 +57,6 @@ unsigned int* device_status_word() {
 extern "C" {
 
 int32_t lb2_version(void) { return 100; }
-
-int32_t lb2_set_reserved_sms(int32_t n) {
-  if (n < 0 || n >= lb2::sm_count()) return lb2::fail(LB2_BAD_ARG, "reserved SM count %d out of range", (int)n);
-  lb2::g_reserved_sms = n;
-  return LB2_OK;
-}
 
 const char* lb2_status_string(int32_t s) {
   switch (s) {

@@ -54,10 +54,10 @@ struct BnFusedPlan {
 constexpr int kBnFusedMaxGc = 64;
 static BnFusedPlan bn_fused_plan(int64_t S, int64_t C, int64_t B, size_t es);
 
-// workspace (fp32): partial[chunks][C][2] | coef[C][4] | fused path: 32 barrier counters 128 B apart (4 KB) | cta_partial[2][grid][kBnFusedMaxGc][2]
+// workspace (fp32): partial[chunks][C][2] | coef[C][4] | frozen-statistics backward: mean[C], invstd[C] | fused path: 32 barrier counters 128 B apart (4 KB) | cta_partial[2][grid][kBnFusedMaxGc][2]
 static size_t bn_classic_ws_bytes(int64_t S, int64_t C, int64_t B) {
   // upper bound on chunks over both regimes
-  return align_up(((size_t)bn_plan(S, C, B).chunks * (size_t)C * 2 + (size_t)C * 4) * sizeof(float), 256);
+  return align_up(((size_t)bn_plan(S, C, B).chunks * (size_t)C * 2 + (size_t)C * 6) * sizeof(float), 256);
 }
 static size_t bn_fused_ws_bytes(const BnFusedPlan& f) {
   return f.ok ? 4096 + align_up((size_t)2 * f.grid * kBnFusedMaxGc * 2 * sizeof(float), 256) : 0;   // 32 counters, 128 B apart
@@ -252,7 +252,7 @@ template <typename T>
 __global__ void bn_finalize_bwd_kernel(T* __restrict__ dgamma, T* __restrict__ dbeta, float* __restrict__ coef,
                                        const T* __restrict__ gamma, const float* __restrict__ save_mean,
                                        const float* __restrict__ save_inv, const float* __restrict__ partial,
-                                       int64_t S, int64_t C, int64_t B, int chunks) {
+                                       int64_t S, int64_t C, int64_t B, int chunks, int frozen) {
   const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= C) return;
   double a = 0.0, q = 0.0;
@@ -269,6 +269,8 @@ __global__ void bn_finalize_bwd_kernel(T* __restrict__ dgamma, T* __restrict__ d
   }
   const float gp = gamma ? to_f32(gamma[c]) * inv : inv;
   // dx = gp * (d - sd/n - (x-mean) * inv^2 * sdx/n) = gp*d + cx*x + c0
+  // statistics that did not come from this batch (frozen running statistics) carry no gradient: dx = gp*d
+  if (frozen) { coef[c * 4 + 0] = gp; coef[c * 4 + 1] = 0.f; coef[c * 4 + 2] = 0.f; return; }
   const float k2 = inv * inv * sdx / n;
   coef[c * 4 + 0] = gp;
   coef[c * 4 + 1] = -gp * k2;                      // multiplies x
@@ -671,30 +673,20 @@ __global__ void __launch_bounds__(256) bn_fused_kernel(const BnFusedArgs a) {
   }
 }
 
-// Experiment switches (environment): LB2_BN_FUSED is a bit mask (1 = forward, 2 = backward may take the fused
-// path; 0 keeps the three-kernel path everywhere; unset = see bn_fused_mask); LB2_BN_L2_MB sets the bytes all subsets' channel groups may
-// occupy together (default 40); LB2_BN_NSUB the number of CTA subsets.
-static int bn_env_int(const char* name, int dflt) {
-  const char* e = getenv(name);
-  return e ? atoi(e) : dflt;
-}
-
 // Default: the fused path for 4-byte elements only. Measured on the 56x56x64x256 tensor: Float32 3844 GB/s fused
 // against 3577 GB/s with three kernels; bf16 (a 103 MB tensor, most of which the three-kernel path already finds
 // in L2 by walking backwards) 2865 against 3250.
-static int bn_fused_mask(size_t es) {
-  static const int m = bn_env_int("LB2_BN_FUSED", -1);
-  return m >= 0 ? m : (es == 4 ? 3 : 0);
-}
+// Bit 0 = forward, bit 1 = backward may take the fused single-launch path.
+static int bn_fused_mask(size_t es) { return es == 4 ? 3 : 0; }
 
 static BnFusedPlan bn_fused_plan(int64_t S, int64_t C, int64_t B, size_t es) {
-  static const int l2_mb = bn_env_int("LB2_BN_L2_MB", 40);
+  constexpr int l2_mb = 40;   // bytes (MiB) all subsets' channel groups may occupy together in L2
   BnFusedPlan f{};
   const int64_t V = (int64_t)(16 / es);
   if (S <= 1 || S % V != 0) return f;
   const double plane_set = (double)S * (double)B * (double)es;           // one channel, all samples
   if ((double)C * plane_set < 16.0 * 1024 * 1024) return f;              // small tensors live in L2 anyway
-  static const int nsub_env = bn_env_int("LB2_BN_NSUB", 16);
+  constexpr int nsub_env = 16;   // CTA subsets, each with its own channel group and barrier
   int nsub = nsub_env < 1 ? 1 : (nsub_env > 32 ? 32 : nsub_env);
   if (nsub > C) nsub = (int)C;
   const double budget = (double)l2_mb * 1024 * 1024 / nsub;
@@ -857,10 +849,13 @@ int32_t lb2_batchnorm_fwd_infer(void* y, const void* x, const void* gamma, const
   return LB2_OK;
 }
 
-int32_t lb2_batchnorm_bwd(void* dx, void* dgamma, void* dbeta, const void* dy, const void* x, const void* gamma,
-                          const void* beta, const float* save_mean, const float* save_invstd, int64_t S, int64_t C,
-                          int64_t B, int32_t dtype, int32_t act, void* workspace, size_t workspace_bytes,
-                          void* stream) {
+}  // extern "C"
+
+// frozen != 0: save_mean / save_invstd are given statistics, not this batch's, so no gradient flows through them
+static int32_t bn_bwd_impl(void* dx, void* dgamma, void* dbeta, const void* dy, const void* x, const void* gamma,
+                           const void* beta, const float* save_mean, const float* save_invstd, int64_t S, int64_t C,
+                           int64_t B, int32_t dtype, int32_t act, void* workspace, size_t workspace_bytes,
+                           void* stream, int frozen) {
   int32_t rc = check_bn(dx, x, gamma, beta, S, C, B, dtype, act);
   if (rc != LB2_OK) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -879,7 +874,7 @@ int32_t lb2_batchnorm_bwd(void* dx, void* dgamma, void* dbeta, const void* dy, c
   float* partial = (float*)workspace;
   float* coef = partial + (size_t)p.chunks * C * 2;
   const BnFusedPlan fp = bn_fused_plan(S, C, B, dtype_size(dtype));
-  if (fp.ok && (bn_fused_mask(dtype_size(dtype)) & 2) && aligned_to(dx, 16) && aligned_to(x, 16) && aligned_to(dy, 16)) {
+  if (!frozen && fp.ok && (bn_fused_mask(dtype_size(dtype)) & 2) && aligned_to(dx, 16) && aligned_to(x, 16) && aligned_to(dy, 16)) {
     uint8_t* fw = static_cast<uint8_t*>(workspace) + bn_classic_ws_bytes(S, C, B);
     BnFusedArgs a{};
     a.out = dx; a.x = x; a.dy = dy; a.gamma = gamma; a.beta = beta;
@@ -903,7 +898,7 @@ int32_t lb2_batchnorm_bwd(void* dx, void* dgamma, void* dbeta, const void* dy, c
       else bn_reduce_launch<T, 1, ACT, false>(partial, (const T*)x, (const T*)dy, nullptr, nullptr, save_mean, save_invstd, S, C, B, p, act, st);
     });
     LB2_CHECK_LAUNCH("batchnorm backward reduction");
-    bn_finalize_bwd_kernel<T><<<(unsigned)((C + 127) / 128), 128, 0, st>>>((T*)dgamma, (T*)dbeta, coef, (const T*)gamma, save_mean, save_invstd, partial, S, C, B, p.chunks);
+    bn_finalize_bwd_kernel<T><<<(unsigned)((C + 127) / 128), 128, 0, st>>>((T*)dgamma, (T*)dbeta, coef, (const T*)gamma, save_mean, save_invstd, partial, S, C, B, p.chunks, frozen);
     LB2_CHECK_LAUNCH("batchnorm backward finalise");
     LB2_DISPATCH_ACT3(act, {
       if (gamma) bn_apply_launch<T, 2, ACT, true>((T*)dx, (const T*)x, (const T*)dy, coef, (const T*)gamma, (const T*)beta, nullptr, nullptr, save_mean, save_invstd, S, C, B, 0.f, act, st);
@@ -914,19 +909,63 @@ int32_t lb2_batchnorm_bwd(void* dx, void* dgamma, void* dbeta, const void* dy, c
   return LB2_OK;
 }
 
+template <typename T>
+__global__ void bn_given_stats_kernel(float* __restrict__ mean, float* __restrict__ inv, const T* __restrict__ rmean,
+                                      const T* __restrict__ rvar, int64_t C, float eps) {
+  const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  mean[c] = to_f32(rmean[c]);
+  inv[c] = 1.f / sqrtf(to_f32(rvar[c]) + eps);
+}
+
+extern "C" {
+
+int32_t lb2_batchnorm_bwd(void* dx, void* dgamma, void* dbeta, const void* dy, const void* x, const void* gamma,
+                          const void* beta, const float* save_mean, const float* save_invstd, int64_t S, int64_t C,
+                          int64_t B, int32_t dtype, int32_t act, void* workspace, size_t workspace_bytes,
+                          void* stream) {
+  return bn_bwd_impl(dx, dgamma, dbeta, dy, x, gamma, beta, save_mean, save_invstd, S, C, B, dtype, act, workspace,
+                     workspace_bytes, stream, 0);
+}
+
+int32_t lb2_batchnorm_bwd_infer(void* dx, void* dgamma, void* dbeta, const void* dy, const void* x, const void* gamma,
+                                const void* beta, const void* rmean, const void* rvar, int64_t S, int64_t C, int64_t B,
+                                double eps, int32_t dtype, int32_t act, void* workspace, size_t workspace_bytes,
+                                void* stream) {
+  int32_t rc = check_bn(dx, x, gamma, beta, S, C, B, dtype, act);
+  if (rc != LB2_OK) return rc;
+  if (S > 0 && C > 0 && B > 0) {
+    LB2_REQUIRE(rmean && rvar, LB2_BAD_ARG, "running statistics are required");
+    LB2_REQUIRE(workspace && workspace_bytes >= bn_ws_bytes(S, C, B), LB2_WORKSPACE_TOO_SMALL, "workspace of %zu bytes needed", bn_ws_bytes(S, C, B));
+    LB2_REQUIRE(aligned_to(workspace, 16), LB2_BAD_ALIGN, "workspace must be 16-byte aligned");
+    const BnPlan p = bn_plan(S, C, B);
+    float* mean = (float*)workspace + (size_t)p.chunks * C * 2 + (size_t)C * 4;
+    float* inv = mean + C;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    LB2_DISPATCH_DTYPE(dtype, {
+      bn_given_stats_kernel<T><<<(unsigned)((C + 127) / 128), 128, 0, st>>>(mean, inv, (const T*)rmean, (const T*)rvar, C, (float)eps);
+    });
+    LB2_CHECK_LAUNCH("batchnorm given statistics");
+    return bn_bwd_impl(dx, dgamma, dbeta, dy, x, gamma, beta, mean, inv, S, C, B, dtype, act, workspace, workspace_bytes, stream, 1);
+  }
+  return bn_bwd_impl(dx, dgamma, dbeta, dy, x, gamma, beta, nullptr, nullptr, S, C, B, dtype, act, workspace, workspace_bytes, stream, 1);
+}
+
 int32_t lb2_batchnorm_fwd_train_static(void* y, float* save_mean, float* save_invstd, void* new_rmean,
                                        void* new_rvar, const void* x, const void* gamma, const void* beta,
                                        const void* rmean, const void* rvar, int64_t S, int64_t C, int64_t B,
                                        double momentum, double eps, int32_t dtype, int32_t act, void* stream) {
-  if (S > 0 && C > 0 && B > 0) {
-    const size_t need = bn_ws_bytes(S, C, B);
-    LB2_REQUIRE(need <= (size_t)LB2_BATCHNORM_STATIC_SCRATCH_BYTES, LB2_WORKSPACE_TOO_SMALL,
-                "this problem needs %zu bytes of scratch; the built-in scratch holds %zu (use lb2_batchnorm_fwd_train "
-                "with a caller workspace instead)",
-                need, (size_t)LB2_BATCHNORM_STATIC_SCRATCH_BYTES);
-  }
+  // argument errors and empty problems are settled before the device is touched at all
+  int32_t rc = check_bn(y, x, gamma, beta, S, C, B, dtype, act);
+  if (rc != LB2_OK) return rc;
+  if (S == 0 || C == 0 || B == 0) return LB2_OK;
+  const size_t need = bn_ws_bytes(S, C, B);
+  LB2_REQUIRE(need <= (size_t)LB2_BATCHNORM_STATIC_SCRATCH_BYTES, LB2_WORKSPACE_TOO_SMALL,
+              "this problem needs %zu bytes of scratch; the built-in scratch holds %zu (use lb2_batchnorm_fwd_train "
+              "with a caller workspace instead)",
+              need, (size_t)LB2_BATCHNORM_STATIC_SCRATCH_BYTES);
   float* scratch = nullptr;
-  int32_t rc = bn_static_scratch_ptr(&scratch);
+  rc = bn_static_scratch_ptr(&scratch);
   if (rc != LB2_OK) return rc;
   return lb2_batchnorm_fwd_train(y, save_mean, save_invstd, new_rmean, new_rvar, x, gamma, beta, rmean, rvar, S, C, B,
                                  momentum, eps, dtype, act, scratch, (size_t)LB2_BATCHNORM_STATIC_SCRATCH_BYTES, stream);

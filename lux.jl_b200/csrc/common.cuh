@@ -14,7 +14,6 @@ namespace lb2 {
 void set_error(const char* fmt, ...);  // thread-local message, defined in api.cu
 int32_t fail(int32_t status, const char* fmt, ...);
 int sm_count();                        // cached per device
-int persistent_sm_budget();            // sm_count() minus the SMs reserved through lb2_set_reserved_sms
 unsigned int* device_status_word();    // per-device status word written by bounded waits
 
 #define LB2_REQUIRE(cond, status, ...)                      \

@@ -85,10 +85,14 @@ int32_t lb2_conv_fwd(void* y, void* preact, const void* x, const void* w, const 
   const size_t es = dtype_size(dtype);
   LB2_REQUIRE(aligned_to(y, es) && aligned_to(preact, es) && aligned_to(x, es) && aligned_to(w, es) && aligned_to(b, es),
               LB2_BAD_ALIGN, "pointer not aligned to the element size");
-  if (!(flags & LB2_FLAG_FORCE_SIMT) && conv_tc_supported(g, dtype)) {
+  // The tensor-core kernels move x, y and the pre-activation with TMA (16-byte aligned bases); an offset view of a
+  // larger array that breaks that rule is served by the direct kernels instead of being rejected.
+  const bool tc = !(flags & LB2_FLAG_FORCE_SIMT) && conv_tc_supported(g, dtype) && aligned_to(x, 16) && aligned_to(y, 16) &&
+                  aligned_to(preact, 16);
+  if (tc) {
     const size_t need = conv_tc_fwd_workspace_bytes(g, dtype);
     LB2_REQUIRE(workspace != nullptr && workspace_bytes >= need, LB2_WORKSPACE_TOO_SMALL, "workspace of %zu bytes needed", need);
-    LB2_REQUIRE(aligned_to(workspace, 256) && aligned_to(x, 16) && aligned_to(y, 2), LB2_BAD_ALIGN, "workspace must be 256-byte aligned");
+    LB2_REQUIRE(aligned_to(workspace, 256), LB2_BAD_ALIGN, "workspace must be 256-byte aligned");
     return conv_tc_fwd(y, preact, x, w, b, g, dtype, act, workspace, static_cast<cudaStream_t>(stream));
   }
   return conv_fwd_direct(y, preact, x, w, b, g, dtype, act, static_cast<cudaStream_t>(stream));
@@ -139,7 +143,9 @@ int32_t lb2_conv_bwd(void* dw, void* dx, void* db, const void* dy, const void* o
     rc = launch_act_bwd(nullptr, db, dy, nullptr, nullptr, S, g.cout, g.batch, g.cout, g.cout, g.cout, dtype, act, 0, red, st);
     if (rc != LB2_OK) return rc;
   }
-  const bool tc = !(flags & LB2_FLAG_FORCE_SIMT) && lay.tc_bytes > 0 && aligned_to(gptr, 16) && aligned_to(x, 16);
+  // TMA needs 16-byte aligned bases for everything it loads (g, x) or stores (dx); other views go to the direct kernels
+  const bool tc = !(flags & LB2_FLAG_FORCE_SIMT) && lay.tc_bytes > 0 && aligned_to(gptr, 16) && aligned_to(x, 16) &&
+                  aligned_to(dx, 16);
   void* tc_ws = ws + lay.g_bytes + lay.red_bytes;
   if (tc && dtype == LB2_F32) {   // both gradients share one set of shifted copies of g
     return conv_tc_f32_bwd(dw, (dx && nx > 0) ? dx : nullptr, x, gptr, w, g, tc_ws, st);

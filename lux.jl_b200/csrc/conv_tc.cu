@@ -20,8 +20,6 @@
 // K-split in the workspace and a fixed-order reduction — deterministic.
 //
 // Roofline: tensor pipe; algorithmic FLOPs = 2*Wo*Ho*N*Cout*Cin*kW*kH per pass.
-#include <stdlib.h>
-
 #include "conv.cuh"
 #include "tc_ptx.cuh"
 
@@ -171,7 +169,6 @@ struct ConvTcParams {
   int16_t a_shift[kMaxKb];   // start-coordinate offset along s (multiple of 8 elements)
   int16_t a_chan[kMaxKb];    // first contracted channel of the k-block
   int8_t a_copy[kMaxKb];     // which W-shifted copy
-  uint32_t debug;            // experiment switches (LB2_GEMM_DEBUG): 1 skip epilogue work, 2 skip MMAs, 4 skip A loads
 };
 
 template <int BN, int ACT>
@@ -241,7 +238,6 @@ conv_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
         const int m0 = (t % p.tiles_m) * kConvBM, img = t / p.tiles_m;
         for (int kb = 0; kb < p.num_kb; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, p.status, 0x1000u)) { ok = false; break; }
-          if (p.debug & 4u) { mbar_arrive(&full[stage]); if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; } continue; }
           mbar_expect_tx(&full[stage], A_BYTES);
           const uint32_t sA = sA0 + stage * A_BYTES;
           const int c0 = m0 + p.a_shift[kb];
@@ -261,7 +257,7 @@ conv_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < p.num_kb; ++kb) {
           if (!mbar_wait(&full[stage], phase, p.status, 0x8000u)) { ok = false; break; }
-          if (!(p.debug & 8u)) tc_fence_after();
+          tc_fence_after();
           const uint32_t sA = sA0 + stage * A_BYTES;
           const uint32_t sB = sB0 + kb * B_BYTES;
           const uint32_t a_lo32 = ((sA >> 4) & 0x3FFFu) | p.a_desc_lbo;
@@ -270,10 +266,9 @@ conv_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
           for (int ks = 0; ks < 4; ++ks) {
             const uint64_t ad = ((uint64_t)p.a_desc_hi << 32) | (uint64_t)(a_lo32 + ks * p.a_k_advance);
             const uint64_t bd = ((uint64_t)p.b_desc_hi << 32) | (uint64_t)(b_lo32 + ks * p.b_k_advance);
-            if (p.debug & 2u) continue;
             umma<false>(d_tmem, ad, bd, p.idesc, (kb | ks) != 0 ? 1u : 0u);
           }
-          if (p.debug & 16u) mbar_arrive(&empty[stage]); else umma_commit(&empty[stage]);
+          umma_commit(&empty[stage]);
           if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
         }
         if (ok) umma_commit(&acc_full[acc]);
@@ -302,7 +297,7 @@ conv_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
       __nv_bfloat16* yp = Y + base;
       __nv_bfloat16* pp = P != nullptr ? P + base : nullptr;
 #pragma unroll 1
-      for (int c = 0; c < ((p.debug & 1u) ? 0 : COLS / 32); ++c) {
+      for (int c = 0; c < COLS / 32; ++c) {
         uint32_t r[32];
         tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + half * COLS + c * 32, r);
         tmem_ld_wait();
@@ -366,7 +361,6 @@ struct ConvTc2Params {
   int32_t act;
   unsigned int* status;
   int16_t row_shift[16];   // per kernel row th: (th - pad_h) * W
-  uint32_t debug;          // experiment switches (LB2_GEMM_DEBUG)
 };
 
 constexpr int kHalo = 8;
@@ -401,6 +395,8 @@ conv_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(b_full + 1);
   // accumulator rows that cross a warp boundary: edge[group][half][quarter][tw][3 rows][32 cols]
   float* edge = reinterpret_cast<float*>(after + 512);
+  // one flag per epilogue group, written and read only by that group's warps around the group's own barrier (the
+  // other group learns of a failure through its own bounded waits)
   volatile int* abort_flag = reinterpret_cast<volatile int*>(after + 448);
   constexpr int EDGE_Q = KW * 3 * 32;   // floats per (group, half, quarter)
   // output staging for the TMA store: per group [64 channels][112 positions] bf16, one tile for y and one for the
@@ -422,7 +418,8 @@ conv_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
     for (int s = 0; s < stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 8); }
     mbar_init(b_full, 1);
-    *abort_flag = 0;
+    abort_flag[0] = 0;
+    abort_flag[1] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   {
@@ -456,7 +453,6 @@ conv_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
         const int s0 = (t % p.tiles_m) * kTileOut - kHalo, img = t / p.tiles_m;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, p.status, 0x1000u)) { ok = false; break; }
-          if (p.debug & 4u) { mbar_arrive(&full[stage]); if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; } continue; }
           mbar_expect_tx(&full[stage], A_BYTES);
           const uint32_t sA = sA0 + stage * A_BYTES;
           const int th = kb / p.chunks, chunk = kb % p.chunks;
@@ -488,7 +484,6 @@ conv_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
           for (int ks = 0; ks < 4; ++ks) {
             const uint64_t ad = ((uint64_t)p.a_desc_hi << 32) | (uint64_t)(a_lo32 + ks * p.a_k_advance);
             const uint64_t bd = ((uint64_t)p.b_desc_hi << 32) | (uint64_t)(b_lo32 + ks * p.b_k_advance);
-            if (p.debug & 2u) continue;
             umma<false>(d0, ad, bd, p.idesc, (kb | ks) != 0 ? 1u : 0u);
           }
           umma_commit(&empty[stage]);
@@ -511,15 +506,8 @@ conv_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
     const uint32_t parity = (uint32_t)grp;           // edge-row buffer of this group
     for (int t = first + grp * step; t < tiles_per_n; t += 2 * step) {
       const int s0 = (t % p.tiles_m) * kTileOut - kHalo, img = t / p.tiles_m;
-      if (!mbar_wait_warp(&acc_full[acc], acc_phase, p.status, 0x10000u)) *abort_flag = 1;
+      if (!mbar_wait_warp(&acc_full[acc], acc_phase, p.status, 0x10000u)) abort_flag[grp] = 1;
       tc_fence_after();
-      if (p.debug & 1u) {
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&acc_empty[acc]);
-        acc_phase ^= 1u;
-        continue;
-      }
       const int s = s0 + r;
       const int w = ((s % p.W) + p.W) % p.W;   // column inside the image row (s is negative in the first halo)
       const uint32_t t_acc = tmem_base + ((uint32_t)(q * 32) << 16) + acc * (KW * BN) + half * 32;
@@ -528,7 +516,7 @@ conv_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
 #pragma unroll
       for (int tw = 0; tw < KW; ++tw) {
         const int d = tw - p.pad_w;
-        if (d != 0 && !(p.debug & 32u)) {
+        if (d != 0) {
           uint32_t rt[32];
           tmem_ld32(t_acc + tw * BN, rt);
           tmem_ld_wait();
@@ -546,7 +534,7 @@ conv_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
       // finished reading its staging buffers, and an expired wait is seen by everyone at the same point
       if (leader) tma_store_wait_read<0>();
       if (grp == 0) asm volatile("bar.sync 4, 256;" ::: "memory"); else asm volatile("bar.sync 5, 256;" ::: "memory");
-      if (*abort_flag) break;
+      if (abort_flag[grp]) break;
       // pass 2: combine the taps
       float out[32];
 #pragma unroll
@@ -554,7 +542,6 @@ conv_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
 #pragma unroll
       for (int tw = 0; tw < KW; ++tw) {
         const int d = tw - p.pad_w;
-        if ((p.debug & 16u) && d != 0) continue;
         uint32_t rt[32];
         tmem_ld32(t_acc + tw * BN, rt);
         tmem_ld_wait();
@@ -584,7 +571,7 @@ conv_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
       if (lane == 0) mbar_arrive(&acc_empty[acc]);
       // stage the tile in shared memory ([channel][position]) and let one thread issue the tiled store
       const bool valid = r >= kHalo && r < kConvBM - kHalo;
-      if (valid && !(p.debug & 8u)) {
+      if (valid) {
         __nv_bfloat16* so = reinterpret_cast<__nv_bfloat16*>(my_stage) + (half * 32) * kTileOut + (r - kHalo);
         __nv_bfloat16* sp = so + BN * kTileOut;
 #pragma unroll
@@ -595,7 +582,7 @@ conv_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
       }
       fence_proxy_async_smem();
       if (grp == 0) asm volatile("bar.sync 4, 256;" ::: "memory"); else asm volatile("bar.sync 5, 256;" ::: "memory");
-      if (leader && !(p.debug & 8u)) {
+      if (leader) {
         const int so0 = (t % p.tiles_m) * kTileOut;
         tma_store_3d(&tmY, smem_u32(my_stage), so0, n0, img);
         if (P != nullptr) tma_store_3d(&tmP, smem_u32(my_stage + STAGE_OUT), so0, n0, img);
@@ -1099,10 +1086,6 @@ static int32_t run_conv_gemm(void* out, void* preact, const void* bias, int32_t 
     q.b_k_advance = 32u >> 4;
     q.idesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | ((uint32_t)((c.kW * 64) >> 3) << 17) | ((uint32_t)(kConvBM >> 4) << 24);
     q.y = out; q.preact = preact; q.bias = bias; q.act = act;
-    {
-      static const uint32_t dbg2 = getenv("LB2_GEMM_DEBUG") ? (uint32_t)atoi(getenv("LB2_GEMM_DEBUG")) : 0u;
-      q.debug = dbg2;
-    }
     q.status = device_status_word();
     LB2_REQUIRE(q.status != nullptr, LB2_LAUNCH_FAIL, "conv_tc: device status word unavailable");
     CUtensorMap mX2, mW2, mY2, mP2;
@@ -1171,10 +1154,6 @@ static int32_t run_conv_gemm(void* out, void* preact, const void* bias, int32_t 
   p.b_k_advance = 32u >> 4;
   p.idesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | (0u << 16) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(kConvBM >> 4) << 24);
   p.y = out; p.preact = preact; p.bias = bias; p.act = act;
-  {
-    static const uint32_t dbg = getenv("LB2_GEMM_DEBUG") ? (uint32_t)atoi(getenv("LB2_GEMM_DEBUG")) : 0u;
-    p.debug = dbg;
-  }
   p.status = device_status_word();
   LB2_REQUIRE(p.status != nullptr, LB2_LAUNCH_FAIL, "conv_tc: device status word unavailable");
   CUtensorMap mX, mW;
@@ -1272,8 +1251,7 @@ struct Wg2Plan {
 };
 static Wg2Plan wg2_plan(const ConvGeom& g) {
   Wg2Plan w{};
-  static const int enabled = getenv("LB2_CONV_WGRAD_WIDE") ? atoi(getenv("LB2_CONV_WGRAD_WIDE")) : 1;
-  if (!enabled || g.k[0] > 4 || g.k[1] > 16) return w;
+  if (g.k[0] > 4 || g.k[1] > 16) return w;
   w.ok = true;
   w.chunks = conv_chunks(g.cin);
   w.co_tiles = (g.cout + 127) / 128;

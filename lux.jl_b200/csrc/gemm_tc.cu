@@ -16,14 +16,13 @@
 // of 128-byte rows (SWIZZLE_128B) and described to the MMA through the matching shared-memory
 // matrix descriptor, so no transposition pass ever runs. fp32 storage uses kind::tf32, by default
 // as an error-compensated 3-product split (hi*hi + lo*hi + hi*lo) with per-k-block accumulation in
-// registers (gemm_tc_f32acc_kernel) that restores fp32 accuracy. A CTA-pair (cta_group::2) variant
-// of the bf16 / single-pass tf32 kernel is opt-in (gemm_tc_pair_kernel).
-// No TMA multicast is used anywhere. Every mbarrier wait is bounded; on expiry the kernel sets
+// registers (gemm_tc_f32acc_kernel) that restores fp32 accuracy. Large bf16 / single-pass tf32 problems
+// run on the CTA-pair kernel (gemm_tc_pair_kernel: cta_group::2, one 256 x 256 tile per pair of SMs).
+// No TMA load uses multicast. Every mbarrier wait is bounded; on expiry the kernel sets
 // a status word, drains and returns, and the host reports LB2_TIMEOUT from lb2_poll_device_status.
 //
 // Roofline: tensor-pipe bound; algorithmic FLOPs = 2*Mm*Nn*Kc per launch.
 #include <cuda.h>
-#include <stdlib.h>
 
 #include <mutex>
 
@@ -58,11 +57,24 @@ struct TcParams {
   void* preact;
   int32_t act, accumulate;
   unsigned int* status;
-  uint32_t debug;  // experiment switches (LB2_GEMM_DEBUG): 1 skip epilogue work, 2 skip MMAs, 4 skip TMA loads
+  int32_t raster_h;     // tiles are walked in bands of this many tile rows (see tile_coords)
 };
 
+// Tile order. Walking all tile rows of one tile column before the next makes the CTAs that run at the same time
+// share one B panel but touch every A panel; for long contractions that working set falls out of L2 between
+// waves. Tiles are walked in bands of `raster_h` tile rows instead (row index fastest inside a band), so the
+// tiles in flight cover a roughly square block of the output and consecutive waves reuse the band's A panels.
+__device__ __forceinline__ void tile_coords(const TcParams& p, int tile, int* tm, int* tn) {
+  const int band_tiles = p.raster_h * p.tiles_n;
+  const int band = tile / band_tiles;
+  const int in_band = tile - band * band_tiles;
+  const int rows_left = p.tiles_m - band * p.raster_h;
+  const int h = rows_left < p.raster_h ? rows_left : p.raster_h;
+  *tm = band * p.raster_h + in_band % h;
+  *tn = in_band / h;
+}
+
 constexpr int kBM = 128;
-constexpr int kThreads = 256;
 constexpr int kKSteps = 4;  // MMA k-steps per k-block (128 bytes of K per row / 32 bytes per step)
 
 template <int BN, bool TF32, bool SPLIT3> struct TcCfg {
@@ -120,10 +132,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % p.tiles_m) * kBM, n0 = (tile / p.tiles_m) * BN;
+        int tm, tn;
+        tile_coords(p, tile, &tm, &tn);
+        const int m0 = tm * kBM, n0 = tn * BN;
         for (int kb = 0; kb < p.num_kb; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, p.status, 0x1u)) { ok = false; break; }
-          if (p.debug & 4u) { mbar_arrive(&full[stage]); if (++stage == STAGES) { stage = 0; phase ^= 1u; } continue; }
           mbar_expect_tx(&full[stage], Cfg::STAGE_BYTES);
           const uint32_t sA = smem_base + stage * Cfg::STAGE_BYTES;
           const uint32_t sB = sA + Cfg::A_BYTES;
@@ -165,11 +178,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           for (int ks = 0; ks < kKSteps; ++ks) {
             const uint64_t ad = ((uint64_t)p.a.desc_hi << 32) | (uint64_t)(a_lo32 + ks * p.a.k_advance);
             const uint64_t bd = ((uint64_t)p.b.desc_hi << 32) | (uint64_t)(b_lo32 + ks * p.b.k_advance);
-            if (p.debug & 2u) continue;
-            if (p.debug & 32u) {  // experiment: alternate between the two accumulators (two independent chains)
-              umma<TF32>(tmem_base + ((ks & 1) ? BN : 0), ad, bd, p.idesc, 1u);
-              continue;
-            }
             umma<TF32>(d_tmem, ad, bd, p.idesc, (kb | ks) != 0 ? 1u : 0u);
             if constexpr (SPLIT3) {
               umma<TF32>(d_tmem, ad + LO_OFF, bd, p.idesc, 1u);  // lo(A) * hi(B)
@@ -197,7 +205,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const bool accumulate = p.accumulate != 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-      const int m0 = (tile % p.tiles_m) * kBM, n0 = (tile / p.tiles_m) * BN + half * COLS;
+      int tm, tn;
+      tile_coords(p, tile, &tm, &tn);
+      const int m0 = tm * kBM, n0 = tn * BN + half * COLS;
       if (!mbar_wait_warp(&acc_full[acc], acc_phase, p.status, 0x8u)) { ok = false; break; }
       tc_fence_after();
       const int64_t m = (int64_t)m0 + q * 32 + lane;
@@ -209,7 +219,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       OutT* dp = D + (int64_t)n0 * ldd + m;
       OutT* pp = P != nullptr ? P + (int64_t)n0 * ldd + m : nullptr;
 #pragma unroll 1
-      for (int c = 0; c < ((p.debug & 1u) ? 0 : COLS / 32); ++c) {
+      for (int c = 0; c < COLS / 32; ++c) {
         uint32_t r[32];
         tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + half * COLS + c * 32, r);
         tmem_ld_wait();
@@ -302,7 +312,9 @@ gemm_tc_f32acc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % p.tiles_m) * kBM, n0 = (tile / p.tiles_m) * BN;
+        int tm, tn;
+        tile_coords(p, tile, &tm, &tn);
+        const int m0 = tm * kBM, n0 = tn * BN;
         for (int kb = 0; kb < p.num_kb; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, p.status, 0x100u)) { ok = false; break; }
           mbar_expect_tx(&full[stage], Cfg::STAGE_BYTES);
@@ -371,7 +383,9 @@ gemm_tc_f32acc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     const float* bias = reinterpret_cast<const float*>(p.bias);
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-      const int m0 = (tile % p.tiles_m) * kBM, n0 = (tile / p.tiles_m) * BN;
+      int tm, tn;
+      tile_coords(p, tile, &tm, &tn);
+      const int m0 = tm * kBM, n0 = tn * BN;
       float sum[64];
 #pragma unroll
       for (int j = 0; j < 64; ++j) sum[j] = 0.f;
@@ -422,33 +436,39 @@ gemm_tc_f32acc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 }
 
 // ----------------------------------------------------------------------------------------------
-// CTA-pair kernel: two CTAs on the two SMs of a TPC work on one 256 x 256 tile with
-// tcgen05.mma.cta_group::2. Each CTA loads its own 128 rows of A and its own 128 rows of B per
-// k-block (32 KB instead of the 48 KB a lone CTA needs for half the MMA work), so operand ingest
-// per tensor-pipe cycle drops from 96 to 64 bytes; each CTA keeps its 128 x 256 half of the
-// accumulator in its own TMEM (double-buffered) and runs its own epilogue. The leader CTA (cluster
-// rank 0) issues all MMAs. Synchronisation: the leader's `full` barriers count both CTAs' TMA
-// bytes (the partner's loads carry cta_group::2 and name the leader's barrier); stage release and
-// accumulator hand-over are tcgen05.commit arrivals sent to each CTA's own barrier (two commits,
-// one per CTA — no multicast anywhere); the partner's epilogue reports back with remote mbarrier
-// arrivals. All waits are time-bounded as in the single-CTA kernel.
+// CTA-pair kernel: the two CTAs of a cluster (two SMs of one TPC) work on one 256 x 256 tile with
+// tcgen05.mma.cta_group::2. Per 64-deep k-block each CTA loads its own 128 rows of A and its own 128 of the
+// tile's 256 B rows: 32 KB for 512 tensor-pipe cycles of work, where a lone CTA on a 128 x 256 tile needs
+// 48 KB, and the tensor core of each SM reads only half of B from its own shared memory. Operand fill plus
+// operand reads then fit the shared-memory bandwidth of an SM, which is what bounds the single-CTA kernel.
+// Each CTA keeps its 128 x 256 half of the accumulator in its own TMEM (two buffers, so the epilogue of
+// tile i runs under the main loop of tile i+1) and runs its own eight-warp epilogue.
+// The leader CTA (cluster rank 0) issues every MMA. Synchronisation per stage:
+//   full[s]   (the leader's)  one arrive.expect_tx by the leader's producer for BOTH CTAs' bytes; the
+//             partner's TMA loads carry cta_group::2 and complete their bytes on the leader's barrier
+//   empty[s]  (one per CTA)   ONE tcgen05.commit with a cluster-multicast mask arrives on both CTAs' barriers
+//             once the MMAs that read the stage have finished
+//   acc_full  (one per CTA)   the same multicast commit after a tile's last MMA
+//   acc_empty (the leader's)  one arrival per CTA, sent by one thread after that CTA's epilogue warps have
+//             met at a named barrier (the partner's arrival is a remote mbarrier arrive)
+// The multicast here is an mbarrier arrival, not a load. All waits are time-bounded.
 // ----------------------------------------------------------------------------------------------
 constexpr int kPairBN = 256;
+constexpr int kPairThreads = 384;   // warps 0-2: TMA / MMA / TMEM; warps 4-11: epilogue
 
-template <bool TF32, bool SPLIT3> struct PairCfg {
+struct PairCfg {
   static constexpr int A_BYTES = kBM * 128;       // this CTA's 128 rows of A
   static constexpr int B_BYTES = kBM * 128;       // this CTA's 128 of the tile's 256 B rows
-  static constexpr int STAGE_BYTES = (A_BYTES + B_BYTES) * (SPLIT3 ? 2 : 1);
-  static constexpr int STAGES = (192 * 1024) / STAGE_BYTES;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = 7;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
-template <bool TF32, bool SPLIT3, int ACT, typename OutT>
-__global__ void __launch_bounds__(kThreads, 1)
+template <bool TF32, int ACT, typename OutT>
+__global__ void __launch_bounds__(kPairThreads, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    const __grid_constant__ CUtensorMap tmA_lo, const __grid_constant__ CUtensorMap tmB_lo,
                     const __grid_constant__ TcParams p) {
-  using Cfg = PairCfg<TF32, SPLIT3>;
+  using Cfg = PairCfg;
   constexpr int STAGES = Cfg::STAGES;
   constexpr int BN = kPairBN;
   constexpr bool FAST = sizeof(OutT) == 2;
@@ -456,10 +476,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + STAGES * Cfg::STAGE_BYTES);
-  uint64_t* full = bars;                    // [STAGES]  both CTAs' TMA -> leader's MMA (leader's copy is used)
+  uint64_t* full = bars;                    // [STAGES]  both CTAs' TMA -> leader's MMA (the leader's copy is used)
   uint64_t* empty = bars + STAGES;          // [STAGES]  MMA -> this CTA's TMA producer
   uint64_t* acc_full = bars + 2 * STAGES;   // [2]       MMA -> this CTA's epilogue
-  uint64_t* acc_empty = acc_full + 2;       // [2]       both CTAs' epilogues -> leader's MMA
+  uint64_t* acc_empty = acc_full + 2;       // [2]       both CTAs' epilogues -> leader's MMA (the leader's copy)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -468,8 +488,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 2); mbar_init(&empty[s], 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 8); }
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 2); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 2) {
@@ -486,22 +506,19 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     if (lane == 0) {
       tma_prefetch_desc(&tmA);
       tma_prefetch_desc(&tmB);
-      if constexpr (SPLIT3) { tma_prefetch_desc(&tmA_lo); tma_prefetch_desc(&tmB_lo); }
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
-        const int m0 = (tile % p.tiles_m) * (2 * kBM) + (int)rank * kBM;
-        const int n0 = (tile / p.tiles_m) * BN + (int)rank * (BN / 2);
+        int tm, tn;
+        tile_coords(p, tile, &tm, &tn);
+        const int m0 = tm * (2 * kBM) + (int)rank * kBM;
+        const int n0 = tn * BN + (int)rank * (BN / 2);
         for (int kb = 0; kb < p.num_kb; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, p.status, 0x10u)) { ok = false; break; }
           const uint32_t leader_full = map_to_cta(smem_u32(&full[stage]), 0);
-          if (p.debug & 4u) {
-            if (rank == 0) mbar_arrive(&full[stage]); else mbar_arrive_cluster(leader_full);
-            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
-            continue;
-          }
-          if (rank == 0) mbar_expect_tx(&full[stage], Cfg::STAGE_BYTES);
-          else mbar_expect_tx_cluster(leader_full, Cfg::STAGE_BYTES);
+          // The partner's bytes may be counted before this arrive (the transaction count then goes negative for
+          // a moment); the phase cannot complete before it, because it is the barrier's only pending arrival.
+          if (rank == 0) mbar_expect_tx(&full[stage], 2 * Cfg::STAGE_BYTES);
           const uint32_t sA = smem_base + stage * Cfg::STAGE_BYTES;
           const uint32_t sB = sA + Cfg::A_BYTES;
           const int k0 = kb * p.bk;
@@ -509,13 +526,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             const int32_t c0 = p.a.mn_major ? m0 + bx * p.a.mn_step : k0;
             const int32_t c1 = p.a.mn_major ? k0 : m0;
             tma_load_2d_pair(sA + bx * p.a.box_bytes, &tmA, c0, c1, leader_full);
-            if constexpr (SPLIT3) tma_load_2d_pair(sA + Cfg::A_BYTES + Cfg::B_BYTES + bx * p.a.box_bytes, &tmA_lo, c0, c1, leader_full);
           }
           for (int bx = 0; bx < p.b.boxes; ++bx) {
             const int32_t c0 = p.b.mn_major ? n0 + bx * p.b.mn_step : k0;
             const int32_t c1 = p.b.mn_major ? k0 : n0;
             tma_load_2d_pair(sB + bx * p.b.box_bytes, &tmB, c0, c1, leader_full);
-            if constexpr (SPLIT3) tma_load_2d_pair(sB + Cfg::A_BYTES + Cfg::B_BYTES + bx * p.b.box_bytes, &tmB_lo, c0, c1, leader_full);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -537,84 +552,72 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           const uint32_t sB = sA + Cfg::A_BYTES;
           const uint32_t a_lo32 = ((sA >> 4) & 0x3FFFu) | p.a.desc_lbo;
           const uint32_t b_lo32 = ((sB >> 4) & 0x3FFFu) | p.b.desc_lbo;
-          constexpr uint32_t LO_OFF = (Cfg::A_BYTES + Cfg::B_BYTES) >> 4;
 #pragma unroll
           for (int ks = 0; ks < kKSteps; ++ks) {
             const uint64_t ad = ((uint64_t)p.a.desc_hi << 32) | (uint64_t)(a_lo32 + ks * p.a.k_advance);
             const uint64_t bd = ((uint64_t)p.b.desc_hi << 32) | (uint64_t)(b_lo32 + ks * p.b.k_advance);
-            if (p.debug & 2u) continue;
-            if (p.debug & 32u) {
-              umma_pair<TF32>(tmem_base + ((ks & 1) ? BN : 0), ad, bd, p.idesc, 1u);
-              continue;
-            }
             umma_pair<TF32>(d_tmem, ad, bd, p.idesc, (kb | ks) != 0 ? 1u : 0u);
-            if constexpr (SPLIT3) {
-              umma_pair<TF32>(d_tmem, ad + LO_OFF, bd, p.idesc, 1u);
-              umma_pair<TF32>(d_tmem, ad, bd + LO_OFF, p.idesc, 1u);
-            }
           }
-          // release this stage in both CTAs once the MMAs above have read it
-          if (p.debug & 8u) {
-            umma_commit_pair_both(smem_u32(&empty[stage]));
-          } else {
-            umma_commit_pair(smem_u32(&empty[stage]));
-            umma_commit_pair(map_to_cta(smem_u32(&empty[stage]), 1));
-          }
+          umma_commit_pair_both(smem_u32(&empty[stage]));   // frees this stage in both CTAs
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
-        if (ok) {
-          if (p.debug & 8u) {
-            umma_commit_pair_both(smem_u32(&acc_full[acc]));
-          } else {
-            umma_commit_pair(smem_u32(&acc_full[acc]));
-            umma_commit_pair(map_to_cta(smem_u32(&acc_full[acc]), 1));
-          }
-        }
+        if (ok) umma_commit_pair_both(smem_u32(&acc_full[acc]));
         if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
       }
     }
   } else if (warp >= 4) {
     // ---------------- epilogue (both CTAs, each on its own 128 rows) ----------------
-    const int q = warp & 3;
+    const int q = warp & 3, half = (warp - 4) >> 2;
+    constexpr int COLS = BN / 2;
     uint32_t acc = 0, acc_phase = 0;
     OutT* D = reinterpret_cast<OutT*>(p.D);
     OutT* P = reinterpret_cast<OutT*>(p.preact);
     const OutT* bias = reinterpret_cast<const OutT*>(p.bias);
+    const int64_t ldd = p.ldd;
+    const bool accumulate = p.accumulate != 0;
+    const uint32_t leader_acc_empty0 = map_to_cta(smem_u32(&acc_empty[0]), 0);
     bool ok = true;
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
-      const int m0 = (tile % p.tiles_m) * (2 * kBM) + (int)rank * kBM;
-      const int n0 = (tile / p.tiles_m) * BN;
+      int tm, tn;
+      tile_coords(p, tile, &tm, &tn);
+      const int m0 = tm * (2 * kBM) + (int)rank * kBM;
+      const int n0 = tn * BN + half * COLS;
       if (!mbar_wait_warp(&acc_full[acc], acc_phase, p.status, 0x80u)) { ok = false; break; }
       tc_fence_after();
       const int64_t m = (int64_t)m0 + q * 32 + lane;
       const bool m_ok = m < p.Mm;
       float bv = 0.f;
       if (bias != nullptr && m_ok) bv = to_f32(bias[m]);
+      const int64_t rem = p.Nn - n0;
+      const int lim = rem < COLS ? (int)rem : COLS;   // live columns (may be <= 0)
+      OutT* dp = D + (int64_t)n0 * ldd + m;
+      OutT* pp = P != nullptr ? P + (int64_t)n0 * ldd + m : nullptr;
 #pragma unroll 1
-      for (int c = 0; c < ((p.debug & 1u) ? 0 : BN / 32); ++c) {
+      for (int c = 0; c < COLS / 32; ++c) {
         uint32_t r[32];
-        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c * 32, r);
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + half * COLS + c * 32, r);
         tmem_ld_wait();
         if (m_ok) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
-            const int64_t n = (int64_t)n0 + c * 32 + j;
-            if (n < p.Nn) {
+            if (c * 32 + j < lim) {
               float v = __uint_as_float(r[j]) + bv;
-              const int64_t off = n * p.ldd + m;
-              if (P != nullptr) P[off] = from_f32<OutT>(v);
+              if (pp != nullptr) pp[j * ldd] = from_f32<OutT>(v);
               v = act_apply_any<ACT, FAST>(p.act, v);
-              if (p.accumulate) v += to_f32(D[off]);
-              D[off] = from_f32<OutT>(v);
+              if (accumulate) v += to_f32(dp[j * ldd]);
+              dp[j * ldd] = from_f32<OutT>(v);
             }
           }
         }
+        dp += 32 * ldd;
+        if (pp != nullptr) pp += 32 * ldd;
       }
+      // this CTA's eight epilogue warps have all read their part of the accumulator: one arrival for the CTA
       tc_fence_before();
-      __syncwarp();
-      if (lane == 0) {
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      if (warp == 4 && lane == 0) {
         if (rank == 0) mbar_arrive(&acc_empty[acc]);
-        else mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[acc]), 0));
+        else mbar_arrive_cluster(leader_acc_empty0 + acc * 8u);
       }
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
     }
@@ -741,12 +744,14 @@ size_t gemm_tc_split_workspace_bytes(GemmOperand A, GemmOperand B, int64_t Mm, i
   return 2 * operand_bytes(A, Mm, Kc) + 2 * operand_bytes(B, Nn, Kc);
 }
 
+static int reserved_sms(uint32_t flags) { return (int)((flags >> 16) & 0x7Fu); }
+
 template <int BN, bool TF32, bool SPLIT3, typename OutT>
 static int32_t tc_launch_cfg(const CUtensorMap& mA, const CUtensorMap& mB, const CUtensorMap& mAl, const CUtensorMap& mBl,
-                             const TcParams& p, cudaStream_t st) {
+                             const TcParams& p, int max_ctas, cudaStream_t st) {
   using Cfg = TcCfg<BN, TF32, SPLIT3>;
   const int tiles = p.tiles_m * p.tiles_n;
-  const int grid = tiles < persistent_sm_budget() ? tiles : persistent_sm_budget();
+  const int grid = tiles < max_ctas ? tiles : max_ctas;
   auto launch = [&](auto kernel) -> int32_t {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return fail(LB2_LAUNCH_FAIL, "gemm_tc: cannot reserve %d bytes of shared memory: %s", Cfg::SMEM_BYTES, cudaGetErrorString(e));
@@ -763,10 +768,10 @@ static int32_t tc_launch_cfg(const CUtensorMap& mA, const CUtensorMap& mB, const
 }
 
 static int32_t tc_launch_f32acc(const CUtensorMap& mA, const CUtensorMap& mB, const CUtensorMap& mAl, const CUtensorMap& mBl,
-                                const TcParams& p, cudaStream_t st) {
+                                const TcParams& p, int max_ctas, cudaStream_t st) {
   using Cfg = TcCfg<kAccBN, true, true>;
   const int tiles = p.tiles_m * p.tiles_n;
-  const int grid = tiles < sm_count() ? tiles : sm_count();
+  const int grid = tiles < max_ctas ? tiles : max_ctas;
   auto launch = [&](auto kernel) -> int32_t {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return fail(LB2_LAUNCH_FAIL, "gemm_tc_f32acc: cannot reserve %d bytes of shared memory: %s", Cfg::SMEM_BYTES, cudaGetErrorString(e));
@@ -781,17 +786,37 @@ static int32_t tc_launch_f32acc(const CUtensorMap& mA, const CUtensorMap& mB, co
   }
 }
 
-template <bool TF32, bool SPLIT3, typename OutT>
-static int32_t tc_launch_pair(const CUtensorMap& mA, const CUtensorMap& mB, const CUtensorMap& mAl, const CUtensorMap& mBl,
-                              const TcParams& p, cudaStream_t st) {
-  using Cfg = PairCfg<TF32, SPLIT3>;
+// CTA pairs the device can hold at once (GPC boundaries can leave a few SMs unpaired). Tiles are dealt
+// round-robin to the clusters, so every cluster of a launch must be resident from the start. Cached per device.
+template <typename Kernel>
+static int resident_pairs(Kernel kernel, cudaLaunchConfig_t* cfg) {
+  static std::mutex mu;
+  static int resident[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return sm_count() / 2;
+  std::lock_guard<std::mutex> lk(mu);
+  if (resident[dev] == 0) {
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, cfg) != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      n = sm_count() / 2;
+    }
+    resident[dev] = n;
+  }
+  return resident[dev];
+}
+
+template <bool TF32, typename OutT>
+static int32_t tc_launch_pair(const CUtensorMap& mA, const CUtensorMap& mB, const TcParams& p, int reserve, cudaStream_t st) {
+  using Cfg = PairCfg;
   const int tiles = p.tiles_m * p.tiles_n;
   auto launch = [&](auto kernel) -> int32_t {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return fail(LB2_LAUNCH_FAIL, "gemm_tc_pair: cannot reserve %d bytes of shared memory: %s", Cfg::SMEM_BYTES, cudaGetErrorString(e));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(sm_count() & ~1, 1, 1);
-    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.blockDim = dim3(kPairThreads, 1, 1);
     cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
@@ -801,39 +826,19 @@ static int32_t tc_launch_pair(const CUtensorMap& mA, const CUtensorMap& mB, cons
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    // Tiles are dealt round-robin to the clusters, so every cluster must be resident from the
-    // start: launch exactly as many CTA pairs as the device can hold at once (GPC boundaries can
-    // leave a few SMs unpaired). Cached per device.
-    static std::mutex mu;
-    static int resident[64] = {0};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    int clusters = 0;
-    {
-      std::lock_guard<std::mutex> lk(mu);
-      if (dev >= 0 && dev < 64 && resident[dev] == 0) {
-        int n = 0;
-        e = cudaOccupancyMaxActiveClusters(&n, kernel, &cfg);
-        if (e != cudaSuccess || n <= 0) {
-          cudaGetLastError();
-          n = sm_count() / 2;
-        }
-        resident[dev] = n;
-        if (getenv("LB2_DEBUG")) fprintf(stderr, "[lb2] gemm_tc_pair: %d resident CTA pairs on device %d\n", n, dev);
-      }
-      clusters = (dev >= 0 && dev < 64) ? resident[dev] : sm_count() / 2;
-    }
+    int clusters = resident_pairs(kernel, &cfg) - (reserve + 1) / 2;
+    if (clusters < 1) clusters = 1;
     if (tiles < clusters) clusters = tiles;
     cfg.gridDim = dim3(2 * clusters, 1, 1);
-    e = cudaLaunchKernelEx(&cfg, kernel, mA, mB, mAl, mBl, p);
+    e = cudaLaunchKernelEx(&cfg, kernel, mA, mB, p);
     if (e != cudaSuccess) return fail(LB2_LAUNCH_FAIL, "gemm_tc_pair: %s", cudaGetErrorString(e));
     return LB2_OK;
   };
   switch (p.act) {
-    case LB2_ACT_IDENTITY: return launch(gemm_tc_pair_kernel<TF32, SPLIT3, LB2_ACT_IDENTITY, OutT>);
-    case LB2_ACT_RELU: return launch(gemm_tc_pair_kernel<TF32, SPLIT3, LB2_ACT_RELU, OutT>);
-    case LB2_ACT_GELU_TANH: return launch(gemm_tc_pair_kernel<TF32, SPLIT3, LB2_ACT_GELU_TANH, OutT>);
-    default: return launch(gemm_tc_pair_kernel<TF32, SPLIT3, -1, OutT>);
+    case LB2_ACT_IDENTITY: return launch(gemm_tc_pair_kernel<TF32, LB2_ACT_IDENTITY, OutT>);
+    case LB2_ACT_RELU: return launch(gemm_tc_pair_kernel<TF32, LB2_ACT_RELU, OutT>);
+    case LB2_ACT_GELU_TANH: return launch(gemm_tc_pair_kernel<TF32, LB2_ACT_GELU_TANH, OutT>);
+    default: return launch(gemm_tc_pair_kernel<TF32, -1, OutT>);
   }
 }
 
@@ -843,14 +848,14 @@ int32_t gemm_tc_launch(void* D, int64_t ldd, GemmOperand A, GemmOperand B, int64
   const bool tf32 = dtype == LB2_F32;
   const int es = tf32 ? 4 : 2;
   const int bk = 128 / es;
-  // BN = 256 halves the A-operand traffic per FLOP; BN = 128 keeps more tiles for small problems and
-  // leaves room for the doubled 3xTF32 stages.
   const bool split = tf32 && split3;
-  // Default: the single-CTA kernel (BN = 128 when that is what it takes to fill the machine). The
-  // CTA-pair kernel is opt-in (LB2_FLAG_CTA_PAIR): it moves a third fewer operand bytes but its
-  // cta_group::2 MMA stream measured no faster on the dense benchmark shape.
+  // Kernel choice. bf16 / single-pass tf32 problems with enough 256 x 256 tiles to occupy most CTA pairs run on the
+  // CTA-pair kernel (LB2_FLAG_CTA_PAIR asks for it from a quarter of the pairs on). Otherwise the single-CTA kernel
+  // with 128 x 256 tiles, or 128 x 128 when that is what it takes to fill the machine or to fit the doubled
+  // 3xTF32 stages.
   const int64_t pair_tiles = ((Mm + 2 * kBM - 1) / (2 * kBM)) * ((Nn + kPairBN - 1) / kPairBN);
-  const bool pair = !split && (flags & LB2_FLAG_CTA_PAIR) && pair_tiles >= sm_count() / 4;
+  const int64_t pair_min = (flags & LB2_FLAG_CTA_PAIR) ? sm_count() / 8 : sm_count() / 2 - 16;
+  const bool pair = !split && !(flags & LB2_FLAG_NO_CTA_PAIR) && pair_tiles >= pair_min;
   int bn = 256;
   if (pair) bn = kPairBN / 2;  // rows of B each CTA of a pair loads
   else if (split) bn = 128;
@@ -890,6 +895,15 @@ int32_t gemm_tc_launch(void* D, int64_t ldd, GemmOperand A, GemmOperand B, int64
   p.tiles_m = (int)((Mm + tile_m - 1) / tile_m);
   p.tiles_n = (int)((Nn + tile_n - 1) / tile_n);
   p.num_kb = (int)((Kc + bk - 1) / bk);
+  // Band height of the tile order: the tiles in flight (one per CTA or CTA pair) should cover a roughly square
+  // block of the output, i.e. about sqrt(workers * tile_n / tile_m) tile rows.
+  {
+    const int workers = pair ? sm_count() / 2 : sm_count();
+    int h = 1;
+    while ((h + 1) * (h + 1) * tile_m <= workers * tile_n) ++h;
+    p.raster_h = h < p.tiles_m ? h : p.tiles_m;
+    if (p.raster_h < 1) p.raster_h = 1;
+  }
   // instruction descriptor: D = f32 (bit 4), A/B format (bits 7-9 / 10-12: 1 = bf16, 2 = tf32),
   // A/B major (bits 15 / 16: 1 = MN-major), N >> 3 (bits 17-22), M >> 4 (bits 24-28)
   const uint32_t fmt = tf32 ? 2u : 1u;
@@ -899,21 +913,20 @@ int32_t gemm_tc_launch(void* D, int64_t ldd, GemmOperand A, GemmOperand B, int64
   p.bias = epi.bias; p.preact = epi.preact; p.act = epi.act; p.accumulate = epi.accumulate;
   p.status = device_status_word();
   LB2_REQUIRE(p.status != nullptr, LB2_LAUNCH_FAIL, "gemm_tc: device status word unavailable");
-  {
-    static const uint32_t dbg = getenv("LB2_GEMM_DEBUG") ? (uint32_t)atoi(getenv("LB2_GEMM_DEBUG")) : 0u;
-    p.debug = dbg;
-  }
+  const int reserve = reserved_sms(flags);
+  int max_ctas = sm_count() - reserve;
+  if (max_ctas < 1) max_ctas = 1;
   if (pair) {
-    if (tf32) return tc_launch_pair<true, false, float>(mA, mB, mAl, mBl, p, st);
-    return tc_launch_pair<false, false, __nv_bfloat16>(mA, mB, mAl, mBl, p, st);
+    if (tf32) return tc_launch_pair<true, float>(mA, mB, p, reserve, st);
+    return tc_launch_pair<false, __nv_bfloat16>(mA, mB, p, reserve, st);
   }
   if (tf32) {
-    if (split) return tc_launch_f32acc(mA, mB, mAl, mBl, p, st);
-    if (bn == 256) return tc_launch_cfg<256, true, false, float>(mA, mB, mAl, mBl, p, st);
-    return tc_launch_cfg<128, true, false, float>(mA, mB, mAl, mBl, p, st);
+    if (split) return tc_launch_f32acc(mA, mB, mAl, mBl, p, max_ctas, st);
+    if (bn == 256) return tc_launch_cfg<256, true, false, float>(mA, mB, mAl, mBl, p, max_ctas, st);
+    return tc_launch_cfg<128, true, false, float>(mA, mB, mAl, mBl, p, max_ctas, st);
   }
-  if (bn == 256) return tc_launch_cfg<256, false, false, __nv_bfloat16>(mA, mB, mAl, mBl, p, st);
-  return tc_launch_cfg<128, false, false, __nv_bfloat16>(mA, mB, mAl, mBl, p, st);
+  if (bn == 256) return tc_launch_cfg<256, false, false, __nv_bfloat16>(mA, mB, mAl, mBl, p, max_ctas, st);
+  return tc_launch_cfg<128, false, false, __nv_bfloat16>(mA, mB, mAl, mBl, p, max_ctas, st);
 }
 
 // ----------------------------------------------------------------------------------------------

@@ -375,14 +375,14 @@ gn_fwd_stream_kernel(T* __restrict__ y, float* __restrict__ mean_out, float* __r
       for (int j = 0; j < V; ++j) s += v.get(j);
     });
     const float mean = group_sum(s, red, kGnCompute) * invL;
-    if (*abort_flag) break;
+    if (*abort_flag) { drain_after_abort(); break; }
     float q = 0.f;
     sweep([&](const Vec16<T>& v, uint32_t) {
 #pragma unroll
       for (int j = 0; j < V; ++j) { const float d = v.get(j) - mean; q = fmaf(d, d, q); }
     });
     const float var = group_sum(q, red, kGnCompute) * invL;
-    if (*abort_flag) break;
+    if (*abort_flag) { drain_after_abort(); break; }
     const float inv = 1.f / sqrtf(var + eps);
     if (t == 0) { mean_out[row] = mean; inv_out[row] = inv; }
     T* yr = y + row * (int64_t)L;
@@ -535,7 +535,7 @@ gn_bwd_stream_kernel(T* __restrict__ dx, float* __restrict__ chan_out, const T* 
       s2 = fmaf(gm, ds[j], s2);
     }
     const float2 m12 = group_sum2(s1, s2, red, kGnCompute);
-    if (*abort_flag) break;
+    if (*abort_flag) { drain_after_abort(); break; }
     const float m1 = m12.x * invL, m2 = m12.y * invL;
     T* dxr = dx + row * (int64_t)L;
     // pass 2: dx = inv * (d*gamma - m1 - xh*m2)
@@ -566,15 +566,9 @@ gn_bwd_stream_kernel(T* __restrict__ dx, float* __restrict__ chan_out, const T* 
   }
 }
 
-// Experiment switch: environment variable LB2_GN_STREAM, bit 0 = forward, bit 1 = backward
-// streaming kernels allowed (default: backward only; the cached forward is faster wherever it applies).
-static int gn_stream_mask() {
-  static const int m = [] {
-    const char* e = getenv("LB2_GN_STREAM");
-    return e ? atoi(e) : 2;
-  }();
-  return m;
-}
+// Which directions may take the chunk-streaming kernels: bit 0 = forward, bit 1 = backward. The cached forward is
+// faster wherever it applies, so only the backward streams.
+static constexpr int gn_stream_mask() { return 2; }
 
 // dgamma[c] = sum_n chan[n][c][0], dbeta[c] = sum_n chan[n][c][1]   (n ascending)
 template <typename T>

@@ -158,7 +158,7 @@ ln_fwd_ring_kernel(T* __restrict__ y, float* __restrict__ mean_out, float* __res
     __syncwarp();
     if (lane == 0) mbar_arrive(&empty[st]);
     const float mean = group_sum(s, red, kRingCompute) * invD;
-    if (*abort_flag) break;
+    if (*abort_flag) { drain_after_abort(); break; }
     float q = 0.f;
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
@@ -272,7 +272,7 @@ ln_bwd_ring_kernel(T* __restrict__ dx, float* __restrict__ partial, const T* __r
       }
     }
     const float2 m12 = group_sum2(s1, s2, red, kRingCompute);
-    if (*abort_flag) break;
+    if (*abort_flag) { drain_after_abort(); break; }
     const float m1 = m12.x * invD, m2 = m12.y * invD;
     // dx = inv * (g - m1 - xh * m2)
     const float c0 = -inv * m1, c1 = -inv * m2;

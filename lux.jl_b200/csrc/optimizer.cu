@@ -83,18 +83,21 @@ int32_t lb2_optimizer_step(const lb2_opt_leaf* leaves, int32_t n_leaves, int32_t
   LB2_REQUIRE(step >= 1, LB2_BAD_ARG, "step counts from 1");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const size_t es = dtype_size(dtype);
+  // Adam: 1 - beta^t, with beta^t built up as a running float product the way Optimisers.jl carries it in its
+  // state. Computed once per call; the loop stops as soon as both products have underflowed to zero (about 1e5
+  // steps for beta = 0.999), so its cost does not grow with the step count.
+  float bc1 = 1.f, bc2 = 1.f;
+  if (rule == LB2_OPT_ADAM) {
+    float b1t = 1.f, b2t = 1.f;
+    for (int64_t k = 0; k < step && (b1t != 0.f || b2t != 0.f); ++k) { b1t *= (float)rho_or_beta1; b2t *= (float)beta2; }
+    bc1 = 1.f - b1t; bc2 = 1.f - b2t;
+  }
   int32_t done = 0;
   while (done < n_leaves) {
     OptBucket bk{};
     bk.rule = rule;
     bk.eta = (float)eta; bk.rho = (float)rho_or_beta1; bk.beta1 = (float)rho_or_beta1; bk.beta2 = (float)beta2; bk.eps = (float)eps;
-    bk.bc1 = 1.f; bk.bc2 = 1.f;
-    if (rule == LB2_OPT_ADAM) {
-      // 1 - beta^t, with beta^t accumulated in the parameter precision the way Optimisers.jl carries it
-      float b1t = 1.f, b2t = 1.f;
-      for (int64_t k = 0; k < step; ++k) { b1t *= (float)rho_or_beta1; b2t *= (float)beta2; }
-      bk.bc1 = 1.f - b1t; bk.bc2 = 1.f - b2t;
-    }
+    bk.bc1 = bc1; bk.bc2 = bc2;
     bk.grad_scale = (float)grad_scale;
     int32_t blocks = 0, k = 0;
     for (; k < kOptMaxLeaves && done + k < n_leaves; ++k) {

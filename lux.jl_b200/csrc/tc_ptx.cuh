@@ -221,6 +221,12 @@ __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint
                : "memory");
 }
 
+// After a bounded wait has expired, bulk copies issued earlier may still be landing in this CTA's shared memory:
+// give them a bounded moment (about 128 microseconds) before the CTA exits and its shared memory is handed on.
+__device__ __forceinline__ void drain_after_abort() {
+  for (int i = 0; i < 64; ++i) __nanosleep(2000);
+}
+
 // Sum over the first `nthreads` threads of the CTA (a multiple of 32, they must all call) through named
 // barrier 1, so that other warps of the CTA (a copy-producer warp) need not take part.
 __device__ __forceinline__ float group_sum(float v, float* smem, int nthreads) {

@@ -12,7 +12,12 @@ LIB_PATH = os.path.join(os.path.dirname(_HERE), "lib", "libluxlib_b200.so")
 OK, BAD_ARG, BAD_SHAPE, BAD_ALIGN, UNSUPPORTED_DTYPE, LAUNCH_FAIL, TIMEOUT, WORKSPACE_TOO_SMALL = 0, -1, -2, -3, -4, -5, -6, -7
 F32, BF16 = 0, 1
 ACT_IDENTITY, ACT_RELU, ACT_GELU_TANH, ACT_GELU_ERF, ACT_TANH, ACT_SIGMOID, ACT_SWISH = range(7)
-FLAG_TF32_1X, FLAG_FORCE_SIMT, FLAG_CTA_PAIR = 1, 2, 4
+FLAG_TF32_1X, FLAG_FORCE_SIMT, FLAG_CTA_PAIR, FLAG_NO_CTA_PAIR = 1, 2, 4, 8
+
+
+def flag_reserve_sms(n: int) -> int:
+    """LB2_FLAG_RESERVE_SMS(n): the persistent GEMM of the call leaves n SMs free for a kernel running beside it."""
+    return (int(n) & 0x7F) << 16
 
 
 class ConvDesc(C.Structure):
@@ -51,7 +56,6 @@ _fp = C.c_void_p  # float* passed as raw device pointers
 PROTOTYPES = {
     "lb2_version": (_i32, []),
     "lb2_status_string": (C.c_char_p, [_i32]),
-    "lb2_set_reserved_sms": (_i32, [_i32]),
     "lb2_last_error_string": (C.c_char_p, []),
     "lb2_poll_device_status": (_i32, [_p]),
     "lb2_act_fwd": (_i32, [_p, _p, _i64, _i32, _i32, _p]),
@@ -75,6 +79,7 @@ PROTOTYPES = {
     "lb2_batchnorm_fwd_train_static": (_i32, [_p, _fp, _fp, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _dbl, _dbl, _i32, _i32, _p]),
     "lb2_batchnorm_fwd_infer": (_i32, [_p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _dbl, _i32, _i32, _p]),
     "lb2_batchnorm_bwd": (_i32, [_p, _p, _p, _p, _p, _p, _p, _fp, _fp, _i64, _i64, _i64, _i32, _i32, _p, _sz, _p]),
+    "lb2_batchnorm_bwd_infer": (_i32, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _dbl, _i32, _i32, _p, _sz, _p]),
     "lb2_groupnorm_fwd": (_i32, [_p, _fp, _fp, _p, _p, _p, _i64, _i64, _i64, _i64, _dbl, _i32, _i32, _p]),
     "lb2_groupnorm_bwd_workspace_bytes": (_sz, [_i64, _i64, _i64, _i64]),
     "lb2_groupnorm_bwd": (_i32, [_p, _p, _p, _p, _p, _p, _p, _fp, _fp, _i64, _i64, _i64, _i64, _i32, _i32, _p, _sz, _p]),

@@ -133,10 +133,12 @@ def rrule_fused_dense(act: str, weight, x, b=None, *, flags: int = 0):
     y, pre, (W, ldw, X, ldx, bb, M, N, K, dt) = _dense_fwd(act, weight, x, b, keep_pre, flags)
     code = act_code(act)
 
-    def pullback(delta, on_param_grads=None):
+    def pullback(delta, on_param_grads=None, shadows=None):
         """Δ -> (∂weight, ∂x, ∂b). `on_param_grads(dW, db)`, when given, is called as soon as the
         parameter gradients are enqueued and before ∂x is computed, so a data-parallel caller can
-        start their all-reduce underneath the remaining GEMM (same kernels, three C calls instead of one)."""
+        start their all-reduce underneath the remaining GEMM (same kernels, three C calls instead of one).
+        `shadows = (dW, dx, db)` switches to the accumulate contract of the Enzyme rules: the gradients are added
+        to those arrays in place and Δ is zeroed."""
         if on_param_grads is not None:
             d = as_colmajor(delta.reshape(M, N).to(W.dtype))
             g = jl_empty((M, N), W.dtype, W.device)
@@ -150,21 +152,36 @@ def rrule_fused_dense(act: str, weight, x, b=None, *, flags: int = 0):
             dx = matmul(W, g, transA=True, flags=flags)      # W' * g
             return dW, (dx.reshape(x.shape) if x.dim() == 1 else dx), db
         d = as_colmajor(delta.reshape(M, N).to(W.dtype))
-        dW = jl_empty((M, K), W.dtype, W.device)
-        dx = jl_empty((K, N), W.dtype, W.device)
-        db = jl_empty((M,), W.dtype, W.device) if bb is not None else None
+        if shadows is not None:
+            # Enzyme's reverse pass (lib/LuxLib/src/impl/dense.jl:253-283): the gradients are ADDED to the caller's
+            # shadow arrays (mul!(dW, g, x', true, true); db .+= ...) and the output shadow is zeroed afterwards.
+            dW, dx, db = shadows
+            dW, ldw_s = _matrix_ld(dW)
+            dx2, ldx_s = _matrix_ld(dx.reshape(K, N))
+            if (ldw_s, ldx_s) != (ldw, ldx):
+                raise DimensionMismatch("shadow arrays must have the layout of weight and x")
+        else:
+            dW = jl_empty((M, K), W.dtype, W.device)
+            dx = dx2 = jl_empty((K, N), W.dtype, W.device)
+            db = jl_empty((M,), W.dtype, W.device) if bb is not None else None
         y2, pre2 = y.reshape(M, N), (None if pre is None else pre.reshape(M, N))
         _, wsp, wsn = _ws(lib.lb2_dense_bwd_workspace_bytes(M, N, K, dt, code, flags), W.device)
-        _cabi.check(lib.lb2_dense_bwd(ptr(dW), ptr(dx), ptr(db), ptr(d), None if keep_pre else ptr(y2), ptr(pre2),
-                                      ptr(W), ptr(X), M, N, K, ldw, ldx, max(M, 1), dt, code, 0, flags, wsp, wsn,
-                                      current_stream(W.device)))
+        _cabi.check(lib.lb2_dense_bwd(ptr(dW), ptr(dx2), ptr(db), ptr(d), None if keep_pre else ptr(y2), ptr(pre2),
+                                      ptr(W), ptr(X), M, N, K, ldw, ldx, max(M, 1), dt, code, int(shadows is not None),
+                                      flags, wsp, wsn, current_stream(W.device)))
+        if shadows is not None:
+            if delta.dtype == W.dtype:
+                delta.zero_()      # dy .= 0 is the caller-side half of the contract (impl/dense.jl:281)
+            return dW, dx, db
         return dW, (dx.reshape(x.shape) if x.dim() == 1 else dx), db
 
     return y, pullback
 
 
-def matmul(A, B, *, transA=False, transB=False, flags: int = 0):
-    """op(A) * op(B) on column-major matrices — matmul! (lib/LuxLib/src/impl/matmul.jl:96-125)."""
+def matmul(A, B, *, transA=False, transB=False, flags: int = 0, out=None, accumulate=False):
+    """op(A) * op(B) on column-major matrices — matmul! (lib/LuxLib/src/impl/matmul.jl:96-125).
+    `out` names the destination; with `accumulate` the product is added to it (mul!(C, A, B, true, true), the form
+    the Enzyme rules of matmuladd! use, lib/LuxLib/src/impl/matmul.jl:254-347)."""
     lib = _cabi.load()
     A, B = _promote(A, B)
     A2, lda = _matrix_ld(A)
@@ -174,10 +191,19 @@ def matmul(A, B, *, transA=False, transB=False, flags: int = 0):
     if K != Kb:
         raise DimensionMismatch(f"inner dimensions differ: {K} vs {Kb}")
     dt = dtype_code(A2.dtype)
-    Cm = jl_empty((M, N), A2.dtype, A2.device)
+    if out is None:
+        if accumulate:
+            raise ArgumentError("accumulate needs the destination `out`")
+        Cm, ldc = jl_empty((M, N), A2.dtype, A2.device), max(M, 1)
+    else:
+        if tuple(out.shape) != (M, N) or out.dtype != A2.dtype:
+            raise DimensionMismatch(f"out must be a {M} x {N} matrix of {A2.dtype}")
+        Cm, ldc = _matrix_ld(out)
+        if Cm is not out:
+            raise ArgumentError("out must be column-major with a contiguous first index")
     _, wsp, wsn = _ws(lib.lb2_matmul_workspace_bytes(M, N, K, dt, flags), A2.device)
-    _cabi.check(lib.lb2_matmul(ptr(Cm), ptr(A2), ptr(B2), M, N, K, lda, ldb, max(M, 1), int(transA), int(transB), dt, 0,
-                               flags, wsp, wsn, current_stream(A2.device)))
+    _cabi.check(lib.lb2_matmul(ptr(Cm), ptr(A2), ptr(B2), M, N, K, lda, ldb, ldc, int(transA), int(transB), dt,
+                               int(bool(accumulate)), flags, wsp, wsn, current_stream(A2.device)))
     return Cm
 
 
@@ -430,19 +456,19 @@ def _batchnorm_fwd(x, scale, bias, rmean, rvar, training, act, momentum, epsilon
         return y, stats, (X, scale_c, bias_c, save_mean, save_inv, S, Cc, B, dt, code, True)
     _cabi.check(lib.lb2_batchnorm_fwd_infer(ptr(y), ptr(X), ptr(scale_c), ptr(bias_c), ptr(rmean_c), ptr(rvar_c), S, Cc, B,
                                             eps, dt, code, current_stream(dev)))
-    return y, (rmean, rvar), (X, scale_c, bias_c, None, None, S, Cc, B, dt, code, False)
+    return y, (rmean, rvar), (X, scale_c, bias_c, (rmean_c, eps), rvar_c, S, Cc, B, dt, code, False)
 
 
 def rrule_batchnorm(x, scale, bias, running_mean, running_var, training: bool, act: str = "identity",
                     momentum: float = 0.1, epsilon: Optional[float] = None):
-    """Forward + pullback Δ -> (∂x, ∂scale, ∂bias) of batchnorm with batch statistics:
-    rrule(batchnorm_affine_normalize_internal) (lib/LuxLib/src/impl/batchnorm.jl:405-443) chained
-    through the mean_var rule (lib/LuxLib/src/impl/common_ops.jl:45-61)."""
+    """Forward + pullback Δ -> (∂x, ∂scale, ∂bias) of batchnorm:
+    rrule(batchnorm_affine_normalize_internal) (lib/LuxLib/src/impl/batchnorm.jl:405-443), chained through the
+    mean_var rule (lib/LuxLib/src/impl/common_ops.jl:45-61) when the statistics came from the batch. With
+    training = False and running statistics given (a frozen BatchNorm being fine-tuned around) the statistics are
+    constants and only the affine-normalise step is differentiated, as the reference's rule does."""
     lib = _cabi.load()
     y, stats, (X, sc, bi, save_mean, save_inv, S, Cc, B, dt, code, batch_stats) = _batchnorm_fwd(
         x, scale, bias, running_mean, running_var, training, act, momentum, epsilon)
-    if not batch_stats:
-        raise ArgumentError("the fused batchnorm pullback covers batch statistics (training mode)")
 
     def pullback(delta):
         d = as_colmajor(delta.to(X.dtype))
@@ -450,8 +476,13 @@ def rrule_batchnorm(x, scale, bias, running_mean, running_var, training: bool, a
         dg = torch.empty(Cc, dtype=X.dtype, device=X.device) if sc is not None else None
         db = torch.empty(Cc, dtype=X.dtype, device=X.device) if sc is not None else None
         _, wsp, wsn = _ws(lib.lb2_batchnorm_workspace_bytes(S, Cc, B), X.device)
-        _cabi.check(lib.lb2_batchnorm_bwd(ptr(dx), ptr(dg), ptr(db), ptr(d), ptr(X), ptr(sc), ptr(bi), ptr(save_mean),
-                                          ptr(save_inv), S, Cc, B, dt, code, wsp, wsn, current_stream(X.device)))
+        if batch_stats:
+            _cabi.check(lib.lb2_batchnorm_bwd(ptr(dx), ptr(dg), ptr(db), ptr(d), ptr(X), ptr(sc), ptr(bi), ptr(save_mean),
+                                              ptr(save_inv), S, Cc, B, dt, code, wsp, wsn, current_stream(X.device)))
+        else:
+            (rm, eps), rv = save_mean, save_inv
+            _cabi.check(lib.lb2_batchnorm_bwd_infer(ptr(dx), ptr(dg), ptr(db), ptr(d), ptr(X), ptr(sc), ptr(bi), ptr(rm), ptr(rv),
+                                                    S, Cc, B, eps, dt, code, wsp, wsn, current_stream(X.device)))
         return dx, dg, db
 
     return y, stats, pullback

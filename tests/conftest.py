@@ -26,3 +26,15 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+def pytest_terminal_summary(terminalreporter, exitstatus, config):
+    """Write the measured parity errors and print the worst one per (test, tensor, dtype)."""
+    import parity_report
+    path = parity_report.write()
+    if path is None:
+        return
+    tr = terminalreporter
+    tr.write_sep("-", f"parity errors measured ({len(parity_report.RECORDS)} comparisons, written to {path})")
+    for (fn, tensor, dt), r in sorted(parity_report.worst_by_function().items()):
+        tr.write_line(f"{fn:62s} {tensor:28s} {dt:5s} rel-L2 {r['rel_l2']:.3e}  (tol {r['tol']:.0e})")

@@ -28,15 +28,24 @@ def test_oracle_reproduces_the_committed_vectors():
 def test_cuda_path_matches_the_committed_vectors():
     import torch
     import luxlib_b200 as L
+    import parity_report
     f = lambda shp: L.from_numpy(O.generate_fixed_array(shp, np.float32))
     seed = lambda y: L.from_numpy(np.ones(y.shape, np.float32) * 0.5 + L.to_numpy(y) * 0.25)
 
     def cmp(name, got: dict, denom_floor=None):
+        # denom_floor = norm of the terms that cancel inside a normalisation dx; it replaces the plain denominator
+        # only where the expected value is more than 20 times smaller than those terms (these ramps make dx
+        # cancel almost exactly, so any fp32 evaluation loses that factor)
         for k, v in got.items():
             want = GOLD[f"{name}/{k}"].astype(np.float64)
             g = L.to_numpy(v).astype(np.float64)
-            den = max(np.linalg.norm(want), denom_floor or 0.0)
+            den = np.linalg.norm(want)
+            extra = {}
+            if denom_floor is not None and denom_floor > 20.0 * den:
+                extra = {"cancellation": float(denom_floor / den) if den > 0 else float("inf"), "judged": "against cancelling terms"}
+                den = denom_floor
             err = np.linalg.norm(g - want) / den if den > 0 else np.linalg.norm(g)
+            parity_report.record(f"{name}/{k}", "f32", err, 1e-5, **extra)
             assert err <= 1e-5, f"{name}/{k}: rel-L2 {err:.3e}"
 
     for i, (k, pad, stride, groups) in enumerate(make_golden.CONV):
@@ -67,11 +76,11 @@ def test_cuda_path_matches_the_committed_vectors():
         dx, dg, dbt = pb(d)
         name = f"ln{'x'.join(map(str, shp))}"
         cmp(name, dict(y=z, dgamma=dg, dbeta=dbt))
-        cmp(name, dict(dx=dx), denom_floor=np.linalg.norm(L.to_numpy(d)) * 10)
+        cmp(name, dict(dx=dx), denom_floor=np.linalg.norm(L.to_numpy(d)))
     for shp, groups in (((4, 4, 6, 2), 3), ((6, 2), 2)):
         z, pb = L.rrule_groupnorm(f(shp), f((6,)), f((6,)), groups, "identity", 1e-5)
         d = seed(z)
         dx, dg, dbt = pb(d)
         name = f"gn{'x'.join(map(str, shp))}_g{groups}"
         cmp(name, dict(y=z, dgamma=dg, dbeta=dbt))
-        cmp(name, dict(dx=dx), denom_floor=np.linalg.norm(L.to_numpy(d)) * 10)
+        cmp(name, dict(dx=dx), denom_floor=np.linalg.norm(L.to_numpy(d)))

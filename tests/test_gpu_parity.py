@@ -9,6 +9,7 @@ import pytest
 import torch
 
 import luxlib_b200 as L
+import parity_report
 from oracle import luxlib_oracle as O
 
 pytestmark = pytest.mark.gpu
@@ -30,10 +31,17 @@ def prep(a, dt):
     return O.round_bf16(a) if dt == "bf16" else a
 
 
+CANCEL_LIMIT = 20.0
+
+
 def check(got, want, dt, what, tol=None, scale=None):
-    """rel-L2 of got against want. `scale` (an array) widens the denominator to the norm of the
-    terms that cancel inside `want` — used for the normalisation dx, which is a difference of
-    quantities of that size and can be arbitrarily small itself (e.g. BatchNorm over 2 samples)."""
+    """rel-L2 of got against want, asserted against the contract's tolerance and recorded in the parity report.
+
+    `scale` (an array) names the terms that cancel inside `want` (the normalisation dx is a difference of
+    quantities of dy's size). It only matters for degenerate cases: when `want` is more than CANCEL_LIMIT times
+    smaller than those terms (BatchNorm over 2 samples, ramps whose gradient cancels exactly) any fp32
+    evaluation, the reference's included, loses that factor, and the error is judged against the terms.
+    Everywhere else the plain rel-L2 is what is asserted."""
     if want is None:
         assert got is None
         return
@@ -41,11 +49,20 @@ def check(got, want, dt, what, tol=None, scale=None):
     w = np.asarray(want, dtype=np.float64)
     assert g.shape == w.shape, f"{what}: shape {g.shape} vs {w.shape}"
     assert np.isfinite(g).all(), f"{what}: non-finite values"
+    limit = tol or TOL[dt]
     denom = np.linalg.norm(w.ravel())
+    diff = np.linalg.norm((g - w).ravel())
+    err = diff / denom if denom > 0 else np.linalg.norm(g.ravel())
+    extra = {}
     if scale is not None:
-        denom = max(denom, np.linalg.norm(np.asarray(scale, dtype=np.float64).ravel()))
-    err = np.linalg.norm((g - w).ravel()) / denom if denom > 0 else np.linalg.norm(g.ravel())
-    assert err <= (tol or TOL[dt]), f"{what}: rel-L2 {err:.3e} > {(tol or TOL[dt]):.1e}"
+        terms = np.linalg.norm(np.asarray(scale, dtype=np.float64).ravel())
+        extra["cancellation"] = float(terms / denom) if denom > 0 else float("inf")
+        if denom == 0 or terms > CANCEL_LIMIT * denom:
+            extra["rel_l2_plain"] = float(err)
+            err = diff / terms if terms > 0 else diff
+            extra["judged"] = "against cancelling terms"
+    parity_report.record(what, dt, err, limit, **extra)
+    assert err <= limit, f"{what}: rel-L2 {err:.3e} > {limit:.1e} {extra}"
 
 
 # ------------------------------------------------------------------------------------------
@@ -180,6 +197,69 @@ def test_dense_tf32_single_pass_flag_is_looser_but_close():
     assert O.rel_l2(L.to_numpy(y), W @ x) < 2e-3
     y3 = L.fused_dense_bias_activation("identity", dev(W, "f32"), dev(x, "f32"), None)
     assert O.rel_l2(L.to_numpy(y3), W.astype(np.float64) @ x.astype(np.float64)) < 1e-5
+
+
+ACCUMULATE_CASES = [
+    # (M, N, K), flags: CUDA-core route (tiny), tensor-core single-CTA route with ragged tiles, forced CUDA-core
+    # route, single-pass tf32, CTA-pair route (needs enough 256 x 256 tiles in all three GEMMs)
+    ((20, 33, 17), 0), ((130, 300, 72), 0), ((256, 512, 512), 0), ((256, 512, 512), 2), ((256, 512, 512), 1),
+    ((1792, 1800, 1792), 4),
+]
+
+
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("act", ["identity", "relu", "gelu"])
+@pytest.mark.parametrize("mnk,flags", ACCUMULATE_CASES)
+def test_dense_pullback_accumulates_into_shadows(dt, act, mnk, flags):
+    # Enzyme's reverse rule for fused_dense! (lib/LuxLib/src/impl/dense.jl:253-283): dW, dx and db are ADDED to the
+    # shadows that already hold other contributions, and the output shadow is zeroed afterwards
+    M, N, K = mnk
+    if flags == 1 and dt == "bf16":
+        pytest.skip("the single-pass tf32 flag only concerns Float32 storage")
+    rng = np.random.default_rng(M + N + K + flags)
+    W = prep(O.glorot_uniform(rng, (M, K)), dt)
+    x = prep(rng.standard_normal((K, N)), dt)
+    b = prep(rng.uniform(-0.1, 0.1, M), dt)
+    delta = prep(rng.standard_normal((M, N)), dt)
+    old = [prep(rng.standard_normal(shp) * s, dt) for shp, s in (((M, K), 3.0), ((K, N), 2.0), ((M,), 5.0))]
+    _, pb_ref = O.fused_dense_rrule(act, W, x, b)
+    grads = pb_ref(delta)
+    y, pb = L.rrule_fused_dense(act, dev(W, dt), dev(x, dt), dev(b, dt), flags=flags)
+    shadows = tuple(dev(o, dt) for o in old)
+    d = dev(delta, dt)
+    dW, dx, db = pb(d, shadows=shadows)
+    assert dW.data_ptr() == shadows[0].data_ptr() and dx.data_ptr() == shadows[1].data_ptr()
+    tol = 2e-3 if flags == 1 else None
+    for name, got, o, g in zip(("dW", "dx", "db"), (dW, dx, db), old, grads):
+        check(got, o.astype(np.float64) + np.asarray(g, np.float64), dt, f"{name} (accumulated)", tol=tol)
+    assert float(d.abs().max()) == 0.0          # the output shadow is zeroed
+    # a second pass adds once more
+    d2 = dev(delta, dt)
+    pb(d2, shadows=shadows)
+    for name, got, o, g in zip(("dW", "dx", "db"), shadows, old, grads):
+        check(got, o.astype(np.float64) + 2 * np.asarray(g, np.float64), dt, f"{name} (accumulated twice)", tol=tol)
+    assert L._cabi.load().lb2_poll_device_status(None) == 0
+
+
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("ta", [False, True])
+@pytest.mark.parametrize("tb", [False, True])
+@pytest.mark.parametrize("mnk,flags", [((192, 264, 160), 0), ((9, 5, 30), 0), ((2304, 2250, 328), 4)])
+def test_matmul_accumulates_into_a_strided_destination(dt, ta, tb, mnk, flags):
+    # mul!(C, A, B, true, true) (lib/LuxLib/src/impl/matmul.jl:254-347) with C a column block view of a taller
+    # matrix: the rows below the block must stay untouched
+    M, N, K = mnk
+    rng = np.random.default_rng(23)
+    A = prep(rng.standard_normal((K, M) if ta else (M, K)), dt)
+    B = prep(rng.standard_normal((N, K) if tb else (K, N)), dt)
+    big = prep(rng.standard_normal((M + 8, N)), dt)
+    ref = big.astype(np.float64).copy()
+    ref[:M] += (A.T if ta else A).astype(np.float64) @ (B.T if tb else B).astype(np.float64)
+    Cbig = dev(big, dt)
+    out = L.matmul(dev(A, dt), dev(B, dt), transA=ta, transB=tb, flags=flags, out=Cbig[:M], accumulate=True)
+    assert out.data_ptr() == Cbig.data_ptr()
+    check(Cbig, ref, dt, "C (accumulated, ld > M)")
+    assert L._cabi.load().lb2_poll_device_status(None) == 0
 
 
 # ------------------------------------------------------------------------------------------
@@ -344,6 +424,31 @@ def test_batchnorm_inference(dt):
     y_ref, _ = O.batchnorm(x, g, b, rm, rv, False, "relu", 0.1, 1e-5)
     y, _ = L.batchnorm(dev(x, dt), dev(g, dt), dev(b, dt), dev(rm, dt), dev(rv, dt), False, "relu", 0.1, 1e-5)
     check(y, y_ref, dt, "y")
+
+
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("act", ["identity", "relu", "gelu"])
+@pytest.mark.parametrize("shape", [(6, 5, 8, 3), (32, 40), (14, 14, 24, 16)])
+@pytest.mark.parametrize("affine", [True, False])
+def test_batchnorm_pullback_with_given_statistics(dt, act, shape, affine):
+    # frozen BatchNorm (training = false, running statistics given): the reference's rrule
+    # (lib/LuxLib/src/impl/batchnorm.jl:405-443) differentiates the affine-normalise step for the statistics it is handed
+    rng = np.random.default_rng(19)
+    c = shape[-2]
+    x = prep(rng.standard_normal(shape) * 1.4 + 0.3, dt)
+    g = prep(rng.uniform(0.5, 1.5, c), dt) if affine else None
+    b = prep(rng.standard_normal(c) * 0.1, dt) if affine else None
+    rm, rv = prep(rng.standard_normal(c) * 0.2, dt), prep(rng.uniform(0.5, 2, c), dt)
+    z_ref, _, pb_ref = O.batchnorm_rrule(x, g, b, rm, rv, False, act, 0.1, 1e-5)
+    z, (srm, srv), pb = L.rrule_batchnorm(dev(x, dt), dev(g, dt), dev(b, dt), dev(rm, dt), dev(rv, dt), False, act, 0.1, 1e-5)
+    check(z, z_ref, dt, "y")
+    check(srm, rm, dt, "running_mean unchanged")
+    delta = prep(rng.standard_normal(shape), dt)
+    dx_ref, dg_ref, db_ref = pb_ref(delta)
+    dx, dg, db = pb(dev(delta, dt))
+    check(dx, dx_ref, dt, "dx")
+    check(dg, dg_ref, dt, "dgamma")
+    check(db, db_ref, dt, "dbeta")
 
 
 # ------------------------------------------------------------------------------------------
@@ -569,7 +674,7 @@ def test_fused_optimizer_matches_the_rule_definitions(dt, rule):
             ostates[i], oparams[i] = O.optimiser_apply(rule, ostates[i], oparams[i], g.astype(np.float64), 0.05, 0.9,
                                                        (0.9, 0.999), 1e-8)
     for i in (0, 1, 2, 3, 4, 30, 64):
-        check(dparams[i], oparams[i], dt, f"param {i}", tol=None if dt == "f32" else 2e-2)
+        check(dparams[i], oparams[i], dt, f"param {i}")
 
 
 def test_fused_optimizer_master_copy_keeps_small_updates():
