@@ -36,6 +36,14 @@ int32_t make_geom(const lb2_conv_desc* d, ConvGeom* g) {
   return LB2_OK;
 }
 
+// Which kernels serve a geometry: 1 = tensor-core path on the WHCN bytes (conv_tc*.cu), 2 = general bf16 tensor-core
+// path on channel-innermost copies (conv_cw.cu), 0 = CUDA-core direct kernels.
+int conv_route(const ConvGeom& g, int32_t dtype) {
+  if (conv_tc_supported(g, dtype)) return 1;
+  if (conv_cw_supported(g, dtype)) return 2;
+  return 0;
+}
+
 int64_t y_numel(const ConvGeom& g) { return (int64_t)g.out[0] * g.out[1] * g.out[2] * g.cout * g.batch; }
 int64_t y_spatial(const ConvGeom& g) { return (int64_t)g.out[0] * g.out[1] * g.out[2]; }
 
@@ -49,7 +57,8 @@ ConvBwdLayout conv_bwd_layout(const ConvGeom& g, int32_t dtype, int32_t act) {
   if (n <= 0) return l;
   l.g_bytes = act == LB2_ACT_IDENTITY ? 0 : align_up((size_t)n * dtype_size(dtype), 1024);
   l.red_bytes = align_up(act_bwd_workspace_bytes(y_spatial(g), g.cout, g.batch), 1024);
-  l.tc_bytes = conv_tc_supported(g, dtype) ? conv_tc_bwd_workspace_bytes(g, dtype) : 0;
+  const int route = conv_route(g, dtype);
+  l.tc_bytes = route == 1 ? conv_tc_bwd_workspace_bytes(g, dtype) : (route == 2 ? conv_cw_bwd_workspace_bytes(g) : 0);
   return l;
 }
 
@@ -69,7 +78,8 @@ int32_t lb2_conv_output_size(const lb2_conv_desc* d, int32_t* out) {
 size_t lb2_conv_fwd_workspace_bytes(const lb2_conv_desc* d, int32_t dtype) {
   ConvGeom g;
   if (!valid_dtype(dtype) || make_geom(d, &g) != LB2_OK || y_numel(g) == 0) return 0;
-  return conv_tc_supported(g, dtype) ? conv_tc_fwd_workspace_bytes(g, dtype) : 0;
+  const int route = conv_route(g, dtype);
+  return route == 1 ? conv_tc_fwd_workspace_bytes(g, dtype) : (route == 2 ? conv_cw_fwd_workspace_bytes(g) : 0);
 }
 
 int32_t lb2_conv_fwd(void* y, void* preact, const void* x, const void* w, const void* b, const lb2_conv_desc* d,
@@ -85,15 +95,18 @@ int32_t lb2_conv_fwd(void* y, void* preact, const void* x, const void* w, const 
   const size_t es = dtype_size(dtype);
   LB2_REQUIRE(aligned_to(y, es) && aligned_to(preact, es) && aligned_to(x, es) && aligned_to(w, es) && aligned_to(b, es),
               LB2_BAD_ALIGN, "pointer not aligned to the element size");
-  // The tensor-core kernels move x, y and the pre-activation with TMA (16-byte aligned bases); an offset view of a
-  // larger array that breaks that rule is served by the direct kernels instead of being rejected.
-  const bool tc = !(flags & LB2_FLAG_FORCE_SIMT) && conv_tc_supported(g, dtype) && aligned_to(x, 16) && aligned_to(y, 16) &&
-                  aligned_to(preact, 16);
-  if (tc) {
-    const size_t need = conv_tc_fwd_workspace_bytes(g, dtype);
+  // The tensor-core kernels on the WHCN bytes move x, y and the pre-activation with TMA (16-byte aligned bases); an
+  // offset view of a larger array that breaks that rule goes to the general path (which copies its input) or to the
+  // direct kernels instead of being rejected.
+  int route = (flags & LB2_FLAG_FORCE_SIMT) ? 0 : conv_route(g, dtype);
+  if (route == 1 && !(aligned_to(x, 16) && aligned_to(y, 16) && aligned_to(preact, 16)))
+    route = (conv_cw_supported(g, dtype) && conv_cw_fwd_workspace_bytes(g) <= workspace_bytes) ? 2 : 0;
+  if (route != 0) {
+    const size_t need = route == 1 ? conv_tc_fwd_workspace_bytes(g, dtype) : conv_cw_fwd_workspace_bytes(g);
     LB2_REQUIRE(workspace != nullptr && workspace_bytes >= need, LB2_WORKSPACE_TOO_SMALL, "workspace of %zu bytes needed", need);
     LB2_REQUIRE(aligned_to(workspace, 256), LB2_BAD_ALIGN, "workspace must be 256-byte aligned");
-    return conv_tc_fwd(y, preact, x, w, b, g, dtype, act, workspace, static_cast<cudaStream_t>(stream));
+    if (route == 1) return conv_tc_fwd(y, preact, x, w, b, g, dtype, act, workspace, static_cast<cudaStream_t>(stream));
+    return conv_cw_fwd(y, preact, x, w, b, g, act, workspace, static_cast<cudaStream_t>(stream));
   }
   return conv_fwd_direct(y, preact, x, w, b, g, dtype, act, static_cast<cudaStream_t>(stream));
 }
@@ -143,10 +156,11 @@ int32_t lb2_conv_bwd(void* dw, void* dx, void* db, const void* dy, const void* o
     rc = launch_act_bwd(nullptr, db, dy, nullptr, nullptr, S, g.cout, g.batch, g.cout, g.cout, g.cout, dtype, act, 0, red, st);
     if (rc != LB2_OK) return rc;
   }
-  // TMA needs 16-byte aligned bases for everything it loads (g, x) or stores (dx); other views go to the direct kernels
-  const bool tc = !(flags & LB2_FLAG_FORCE_SIMT) && lay.tc_bytes > 0 && aligned_to(gptr, 16) && aligned_to(x, 16) &&
-                  aligned_to(dx, 16);
+  const int route = (flags & LB2_FLAG_FORCE_SIMT) ? 0 : (lay.tc_bytes > 0 ? conv_route(g, dtype) : 0);
   void* tc_ws = ws + lay.g_bytes + lay.red_bytes;
+  if (route == 2) return conv_cw_bwd(dw, (dx && nx > 0) ? dx : nullptr, x, gptr, w, g, tc_ws, st);
+  // TMA needs 16-byte aligned bases for everything it loads (g, x) or stores (dx); other views go to the direct kernels
+  const bool tc = route == 1 && aligned_to(gptr, 16) && aligned_to(x, 16) && aligned_to(dx, 16);
   if (tc && dtype == LB2_F32) {   // both gradients share one set of shifted copies of g
     return conv_tc_f32_bwd(dw, (dx && nx > 0) ? dx : nullptr, x, gptr, w, g, tc_ws, st);
   }

@@ -1044,7 +1044,9 @@ bool conv_tc_supported(const ConvGeom& g, int32_t dtype) {
   if (g.pad_lo[0] > g.k[0] - 1 || g.pad_lo[1] > g.k[1] - 1) return false;  // data gradient needs K-1-pad >= 0
   const ConvGemm f{g.in[0], g.in[1], g.out[1], g.cin, g.cout, g.batch, g.k[0], g.k[1], g.pad_lo[0], g.pad_lo[1]};
   const ConvGemm d{g.in[0], g.out[1], g.in[1], g.cout, g.cin, g.batch, g.k[0], g.k[1], g.k[0] - 1 - g.pad_lo[0], g.k[1] - 1 - g.pad_lo[1]};
-  if (!conv_gemm_ok(f) || !conv_gemm_ok(d)) return false;
+  // only the fast case stays here (filter resident in shared memory, shift-in-epilogue kernels in both directions);
+  // every other bf16 geometry is served by the general path of conv_cw.cu
+  if (!conv_gemm_ok(f) || !conv_gemm_ok(d) || !conv_use_fwd2(f) || !conv_use_fwd2(d)) return false;
   if (g.k[0] * g.k[1] * conv_chunks(g.cin) > 2 * kMaxKb) return false;
   return true;
 }

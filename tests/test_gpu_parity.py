@@ -300,6 +300,48 @@ def test_fused_conv_fwd_bwd(dt, act, case):
     check(db, db_ref, dt, "db")
 
 
+GENERAL_CONV_CASES = [
+    # spatial, k, cin, cout, stride, pad, dilation, flip, batch — the geometries of a ResNet-18 beyond its stride-1
+    # 64-channel stage, plus odd ones; bf16 storage takes the general tensor-core path (channel-innermost copies)
+    ((32, 32), (7, 7), 3, 64, 2, 3, 1, False, 3),              # stem: kW taps folded into the channel index
+    ((28, 28), (3, 3), 64, 128, 2, 1, 1, False, 3),            # strided 3x3 at a stage entry
+    ((28, 28), (1, 1), 64, 128, 2, 0, 1, False, 3),            # 1x1 stride-2 projection (dx has untouched classes)
+    ((14, 14), (3, 3), 128, 128, 1, 1, 1, False, 3),
+    ((14, 14), (3, 3), 128, 256, 2, 1, 1, False, 2),
+    ((7, 7), (3, 3), 256, 512, 1, 1, 1, False, 5),             # several images per tile, 256-wide N tiles
+    ((7, 7), (3, 3), 512, 512, 1, 1, 1, True, 2),
+    ((16, 12), (3, 3), 32, 48, 1, 2, 2, False, 2),             # dilation
+    ((17, 13), (3, 2), 40, 24, (3, 2), (1, 0, 2, 1), 1, True, 2),   # odd strides, asymmetric padding
+    ((150, 6), (3, 3), 16, 16, 1, 1, 1, False, 2),             # rows longer than a tile
+    ((9, 9), (5, 5), 8, 8, 2, 2, 1, False, 2),
+]
+
+
+@pytest.mark.parametrize("act", ["identity", "relu", "gelu"])
+@pytest.mark.parametrize("dt", ["bf16", "f32"])
+@pytest.mark.parametrize("case", GENERAL_CONV_CASES)
+def test_fused_conv_general_geometries(case, dt, act):
+    sp, k, cin, cout, stride, pad, dil, flip, batch = case
+    if dt == "f32" and act != "relu":
+        pytest.skip("Float32 storage takes the direct kernels here; one activation is enough")
+    rng = np.random.default_rng(29)
+    x = prep(rng.standard_normal(sp + (cin, batch)), dt)
+    w = prep(O.kaiming_normal(rng, k + (cin, cout)), dt)
+    b = prep(rng.uniform(-0.1, 0.1, cout), dt)
+    ocd = O.ConvDims.make(2, stride, pad, dil, 1, flip)
+    lcd = L.ConvDims.make(2, stride, pad, dil, 1, flip)
+    y_ref, pb_ref = O.fused_conv_rrule(act, w, x, b, ocd)
+    y, pb = L.rrule_fused_conv(act, dev(w, dt), dev(x, dt), dev(b, dt), lcd)
+    check(y, y_ref, dt, "y")
+    delta = prep(rng.standard_normal(y_ref.shape), dt)
+    dw_ref, dx_ref, db_ref = pb_ref(delta)
+    dw, dx, db = pb(dev(delta, dt))
+    check(dw, dw_ref, dt, "dw")
+    check(dx, dx_ref, dt, "dx")
+    check(db, db_ref, dt, "db")
+    assert L._cabi.load().lb2_poll_device_status(None) == 0
+
+
 TC_CONV_CASES = [
     # spatial, k, cin, cout, pad, flip  — shapes the tensor-core implicit-GEMM path takes (bf16, stride 1, W % 8 == 0)
     ((16, 8), (3, 3), 16, 16, 1, False),
