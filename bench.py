@@ -1,24 +1,34 @@
 #!/usr/bin/env python
-"""Benchmark of the fused dense layer hot path (forward + pullback) on B200.
+"""Benchmark of LuxLib's fused-layer hot path on B200.
 
-Workload (the configuration the headline metric is quoted on): one fused dense layer,
-W 4096x4096, x 4096x8192 (features x batch), bias 4096, bf16 storage / fp32 accumulate, gelu;
-W ~ glorot_uniform, x ~ N(0,1), b ~ U(-0.1,0.1), upstream gradient ~ N(0,1), seed 1.
-A step = forward + dX + dW + db. Algorithmic work = 6*M*N*K FLOP per step per GPU.
+Headline workload (the configuration the metric is quoted on): one fused dense layer, W 4096x4096, x 4096x8192
+(features x batch), bias 4096, bf16 storage / fp32 accumulate, gelu; W ~ glorot_uniform, x ~ N(0,1),
+b ~ U(-0.1,0.1), upstream gradient ~ N(0,1), seed 1. A step = forward + dX + dW + db = 6*M*N*K FLOP per GPU.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload ...] [--no-secondary]
 
-For N > 1 launch under torchrun: every rank runs the layer on its own batch shard of the same
-size (weak scaling, replicated weights) and the parameter gradients dW, db are all-reduced (avg)
-with NCCL, like Lux's DistributedOptimizer does per leaf.
+For N > 1 launch under torchrun: every rank runs the layer on its own batch shard of the same size (weak scaling,
+replicated weights) and the parameter gradients dW, db are all-reduced (avg) with NCCL, as Lux's DistributedOptimizer
+does per leaf; dW travels in column panels so that a panel's all-reduce runs under the next panel's GEMM.
 
-Prints ONE JSON line (rank 0).
+How a number is taken: the step is captured once into a CUDA graph (so that the host's launch path is outside the
+measurement), replayed untimed for a fixed wall time (`ramp_s`; a GPU that was idle when the process started needs
+it to reach its running clocks), then W warm-up replays, then exactly K timed replays between two CUDA events
+bracketed by barrier + synchronize; max over ranks. Every step is also bracketed by its own events (median / min /
+max are reported), SM clocks and throttle reasons are sampled every millisecond during the timed region. The launch
+durations of the individual kernels come from an eager replay of the same K steps directly afterwards, with event
+pairs around each launch.
+
+The same JSON line carries the other configurations of the path as `secondary` records (conv C3, LayerNorm /
+GroupNorm C4, BatchNorm C3, the small MLP C1, one ResNet-18 data-parallel training step), each with its own
+roofline and clocks. Prints ONE JSON line (rank 0).
 """
 from __future__ import annotations
 
 import argparse
 import json
 import os
+import re
 import sys
 import threading
 import time
@@ -35,6 +45,9 @@ ACT = "gelu"
 METRIC = "fused dense+bias+act fwd+bwd TFLOP/s"
 UNIT = "TFLOP/s"
 WORKLOAD = "dense W 4096x4096 * x 4096x8192 + b, gelu(tanh), bf16 storage / fp32 accumulate; fwd + dX + dW + db"
+RAMP_S = 1.5
+DW_PANELS = 4
+TRAFFIC_PROFILE = os.path.join("profiles", "gemm_tc_kernel_dense_c2_bf16.md")
 
 
 def flops_per_step() -> float:
@@ -52,13 +65,38 @@ def make_inputs(seed: int, n_cols: int):
     return W, x, b, dy
 
 
-def measured_peaks():
+def _peaks_file():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         with open(path) as f:
-            d = json.load(f)
+            return json.load(f)
+    return None
+
+
+def measured_peaks():
+    d = _peaks_file()
+    if d is not None:
         return d.get("bf16_tflops_sustained", 1430.0), d.get("bf16_tflops", 1699.0), "measured"
     return 1400.0, 1590.0, "fallback"
+
+
+def hbm_peak():
+    d = _peaks_file()
+    if d is not None:
+        return d.get("hbm_gbs", 6552.0), "measured"
+    return 6650.0, "fallback"
+
+
+def recorded_traffic():
+    """DRAM bytes of one forward launch as recorded in the committed ncu summary (a line
+    `roofline_traffic_bytes: <n>` in profiles/gemm_tc_kernel_dense_c2_bf16.md); None when the file has no such line."""
+    path = os.path.join(ROOT, TRAFFIC_PROFILE)
+    try:
+        with open(path) as f:
+            m = re.search(r"roofline_traffic_bytes:\s*([0-9.eE+]+)", f.read())
+        return float(m.group(1)) if m else None
+    except OSError:
+        return None
 
 
 # ---------------------------------------------------------------------------------------------
@@ -96,9 +134,9 @@ def cpu_tflops(n_cols: int, reps: int, seed: int = 1):
 
 
 def run_reference_arm(args):
-    """`--impl reference`: the CPU implementation of the path on the host cores. Julia is not
-    available, so this is the numpy restatement of LuxLib's CPU code (kind "port"), BLAS-threaded
-    over all host cores. Each step is a bounded sample (a column block of the batch)."""
+    """`--impl reference`: the CPU implementation of the path on the host cores. Julia is not available, so this is
+    the numpy restatement of LuxLib's CPU code (kind "port"), BLAS-threaded over all host cores. Each step is a
+    bounded sample (a column block of the batch)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
@@ -139,8 +177,9 @@ class ClockSampler:
         0x80: "hw_power_brake_slowdown", 0x2: "applications_clocks_setting", 0x100: "display_clock_setting",
     }
 
-    def __init__(self, index: int):
+    def __init__(self, index: int, period_s: float = 0.001):
         self.samples, self.reasons, self.max_mhz = [], set(), None
+        self.period = period_s
         self._stop = threading.Event()
         self._thread = None
         try:
@@ -163,12 +202,13 @@ class ClockSampler:
                         self.reasons.add(name)
             except Exception:
                 pass
-            time.sleep(0.01)
+            time.sleep(self.period)
 
     def start(self):
         if self.nv is not None:
             self._thread = threading.Thread(target=self._run, daemon=True)
             self._thread.start()
+        return self
 
     def stop(self):
         self._stop.set()
@@ -179,7 +219,71 @@ class ClockSampler:
 
 
 # ---------------------------------------------------------------------------------------------
-# GPU arm
+# measurement helpers
+# ---------------------------------------------------------------------------------------------
+def capture(step, torch, device):
+    """The step as a CUDA graph replay (None when capture is not possible: the caller then times eager launches)."""
+    try:
+        torch.cuda.synchronize(device)
+        g = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream(device=device)
+        side.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(side):
+            step()                                   # allocator and library caches warm on the capture stream
+        torch.cuda.current_stream(device).wait_stream(side)
+        torch.cuda.synchronize(device)
+        with torch.cuda.graph(g):
+            out = step()
+        torch.cuda.synchronize(device)
+        return g, out
+    except Exception as e:                           # noqa: BLE001 - any capture failure falls back to eager timing
+        sys.stderr.write(f"[bench] CUDA graph capture failed ({type(e).__name__}: {e}); timing eager launches\n")
+        try:
+            torch.cuda.synchronize(device)
+        except Exception:
+            pass
+        return None, None
+
+
+def ramp(run, torch, seconds: float, barrier=None):
+    """Untimed repetitions of the step for a fixed wall time (clocks, caches, NCCL first-use set-up)."""
+    t0 = time.perf_counter()
+    n = 0
+    while True:
+        for _ in range(8):
+            run()
+        n += 8
+        torch.cuda.synchronize()
+        if time.perf_counter() - t0 >= seconds:
+            break
+    if barrier is not None:
+        barrier()
+    return time.perf_counter() - t0, n
+
+
+def timed(run, torch, steps: int, barrier, device_index: int):
+    """Exactly `steps` runs between two events, each run also bracketed by its own event; clocks sampled meanwhile.
+    Returns (total ms, per-step ms list, clocks)."""
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+    barrier()
+    sampler = ClockSampler(device_index).start()
+    ev[0].record()
+    for i in range(steps):
+        run()
+        ev[i + 1].record()
+    barrier()
+    clocks = sampler.stop()
+    per = [ev[i].elapsed_time(ev[i + 1]) for i in range(steps)]
+    return ev[0].elapsed_time(ev[steps]), per, clocks
+
+
+def stats(per):
+    a = np.asarray(per, dtype=np.float64)
+    return {"median": float(np.median(a)), "min": float(a.min()), "max": float(a.max())}
+
+
+# ---------------------------------------------------------------------------------------------
+# GPU arm: the dense layer
 # ---------------------------------------------------------------------------------------------
 def run_gpu_arm(args):
     import torch
@@ -195,15 +299,10 @@ def run_gpu_arm(args):
     device = torch.device("cuda", local)
     dist = None
     if world > 1:
-        # The persistent GEMM kernels occupy every SM; NCCL's in-switch (NVLS) all-reduce kernels compete with them
-        # for SMs and measured slower here at 8 GPUs (5.0-5.4 PFLOP/s against 5.9 with plain ring / tree kernels).
-        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         import torch.distributed as dist_mod
         dist = dist_mod
         dist.init_process_group("nccl", device_id=device)
     lib = _cabi.load()
-    if world > 1:   # leave a few SMs to the NCCL all-reduce that runs under the dX GEMM
-        pass
 
     # every rank holds the same parameters and its own batch shard
     Wn, xn, bn, dyn = make_inputs(1, N)
@@ -218,81 +317,109 @@ def run_gpu_arm(args):
     dy = L.from_numpy(dyn, device, bf)
     del Wn, bn
 
-    pending = []
+    def reduce_panel(dW_panel, db):
+        # DistributedOptimizer's all-reduce(avg) of the parameter-gradient leaves, issued per column panel of dW as soon
+        # as the panel exists, so that it runs underneath the next panel's GEMM. A column panel of the column-major dW
+        # is contiguous: .T is the contiguous view of the same memory.
+        works = [dist.all_reduce(dW_panel.T, op=dist.ReduceOp.AVG, async_op=True)]
+        if db is not None:
+            works.append(dist.all_reduce(db, op=dist.ReduceOp.AVG, async_op=True))
+        return works
 
-    def start_allreduce(dW, db):
-        # DistributedOptimizer's all-reduce(avg) of every parameter-gradient leaf, started as soon as the
-        # leaves exist so that it runs underneath the dX GEMM. dW is column-major: .T is the contiguous
-        # view of the same memory.
-        pending.append(dist.all_reduce(dW.T, op=dist.ReduceOp.AVG, async_op=True))
-        pending.append(dist.all_reduce(db, op=dist.ReduceOp.AVG, async_op=True))
-
-    overlap = os.environ.get("LB2_BENCH_OVERLAP", "1") != "0"   # experiment switch: 0 = all-reduce after the whole pullback
-
-    def backward(pullback):
-        return backward_from(pullback, dy)
-
-    def backward_from(pullback, dy_):
-        if dist is None:
-            return pullback(dy_)
-        if overlap:
-            dW, dx, db = pullback(dy_, on_param_grads=start_allreduce)
-        else:
+    def step_from(x_, dy_, collectives=True):
+        y, pullback = L.rrule_fused_dense(ACT, W, x_, b)
+        if dist is None or not collectives:
             dW, dx, db = pullback(dy_)
-            start_allreduce(dW, db)
+            return y, dW, dx, db
+        pending = []
+        dW, dx, db = pullback(dy_, on_param_grads=lambda p, d: pending.extend(reduce_panel(p, d)), param_panels=DW_PANELS)
         for h in pending:
-            h.wait()          # stream-level wait: the next step's work is ordered after the reduced gradients
-        pending.clear()
-        return dW, dx, db
+            h.wait()          # stream-level wait: later work is ordered after the reduced gradients
+        return y, dW, dx, db
 
     def step():
-        y, pullback = L.rrule_fused_dense(ACT, W, x, b)
-        dW, dx, db = backward(pullback)
-        return y, dW, dx, db
+        return step_from(x, dy)
 
     def barrier():
         if dist is not None:
             dist.barrier()
         torch.cuda.synchronize()
 
-    warm = max(args.warmup, 3)
-    for _ in range(warm):
+    for _ in range(3):
         step()
     barrier()
     rc = lib.lb2_poll_device_status(None)
     if rc != 0:
-        raise SystemExit(f"device status after warm-up: {rc} {lib.lb2_last_error_string()}")
+        raise SystemExit(f"device status after the first steps: {rc} {lib.lb2_last_error_string()}")
 
-    # ---- timed region: K steps, CUDA events on the launching stream; the forward GEMM launch is
-    # additionally bracketed by its own event pair to get the dominant kernel's launch duration.
-    sampler = ClockSampler(local)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    fwd_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
-    barrier()
-    sampler.start()
-    e0.record()
-    for i in range(args.steps):
-        fwd_ev[i][0].record()
-        y, pullback = L.rrule_fused_dense(ACT, W, x, b)
-        fwd_ev[i][1].record()
-        dW, dx, db = backward(pullback)
-    e1.record()
-    barrier()
-    clocks = sampler.stop()
-    ms_total = e0.elapsed_time(e1)
+    graph, _ = capture(step, torch, device)
+    run = graph.replay if graph is not None else step
+    mode = "cuda_graph_replay" if graph is not None else "eager"
+    ramp_s, ramp_steps = ramp(run, torch, RAMP_S, barrier)
+    warm = max(args.warmup, 3)
+    for _ in range(warm):
+        run()
+    ms_total, per, clocks = timed(run, torch, args.steps, barrier, local)
     t = torch.tensor([ms_total], device=device)
     if dist is not None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_total = float(t.item())
     ms_step = ms_total / args.steps
     value = world * flops_per_step() / (ms_step * 1e-3) / 1e12
-    fwd_ms = float(np.mean([a.elapsed_time(b_) for a, b_ in fwd_ev]))
     rc = lib.lb2_poll_device_status(None)
     if rc != 0:
         raise SystemExit(f"device status after the timed region: {rc} {lib.lb2_last_error_string()}")
 
-    # ---- end to end through the public API with HOST buffers (pinned): per step copy this step's
-    # inputs (x, dy) to the device, run, and read every result (y, dW, dx, db) back.
+    # ---- per-launch durations: eager replay of the same K steps, an event pair around every launch
+    names = ["forward GEMM (bias+gelu epilogue, pre-activation store)", "g = dy*gelu'(pre) and db partials + db finish",
+             "dX GEMM", "dW GEMM"]
+    kern = {n_: [] for n_ in names}
+    sampler2 = ClockSampler(local).start()
+    for _ in range(args.steps):
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
+        e[0].record()
+        y, pullback = L.rrule_fused_dense(ACT, W, x, b)
+        e[1].record()
+        marks = []
+        pullback(dy, on_param_grads=lambda p, d: None, param_panels=1,
+                 mark=lambda: (marks.append(torch.cuda.Event(enable_timing=True)), marks[-1].record()))
+        torch.cuda.synchronize()
+        kern[names[0]].append(e[0].elapsed_time(e[1]))
+        pts = [e[1]] + marks      # marks: after g/db, after dX, after dW
+        for nm, a_, b_ in zip(names[1:], pts[:-1], pts[1:]):
+            kern[nm].append(a_.elapsed_time(b_))
+    clocks2 = sampler2.stop()
+    fwd_ms = float(np.median(kern[names[0]]))
+    launches = {n_: stats(v) for n_, v in kern.items()}
+
+    # ---- collectives alone and the step without them (N > 1): how much of the all-reduce time is hidden
+    comm = None
+    if dist is not None:
+        dWbuf = L.jl_empty((M, K), bf, device)
+        dbbuf = torch.zeros(M, device=device, dtype=bf)
+        cols = K // DW_PANELS
+
+        def comm_only():
+            hs = []
+            for p_ in range(DW_PANELS):
+                hs += reduce_panel(dWbuf[:, p_ * cols:(p_ + 1) * cols], dbbuf if p_ == DW_PANELS - 1 else None)
+            for h in hs:
+                h.wait()
+        for _ in range(5):
+            comm_only()
+        comm_total, _, _ = timed(comm_only, torch, args.steps, barrier, local)
+        nocomm_total, _, _ = timed(lambda: step_from(x, dy, collectives=False), torch, args.steps, barrier, local)
+        tt = torch.tensor([comm_total / args.steps, nocomm_total / args.steps], device=device)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        comm_ms, nocomm_ms = float(tt[0]), float(tt[1])
+        exposed = max(0.0, ms_step - nocomm_ms)
+        comm = {"comm_ms": comm_ms, "step_without_collectives_ms": nocomm_ms, "exposed_ms": exposed,
+                "overlap_frac": max(0.0, min(1.0, 1.0 - exposed / comm_ms)) if comm_ms > 0 else None,
+                "payload_bytes": (M * K + M) * 2, "panels": DW_PANELS,
+                "nvls": os.environ.get("NCCL_NVLS_ENABLE", "default")}
+
+    # ---- end to end through the public API with HOST buffers (pinned): per step copy this step's inputs (x, dy) to
+    # the device, run, and read every result (y, dW, dx, db) back.
     e2e_steps = max(3, min(args.steps, 20))
     hx = torch.from_numpy(np.ascontiguousarray(xn.T)).to(bf).pin_memory()      # column-major bytes of x
     hdy = torch.from_numpy(np.ascontiguousarray(dyn.T)).to(bf).pin_memory()
@@ -318,8 +445,7 @@ def run_gpu_arm(args):
             dybuf.copy_(hdy, non_blocking=True)
             in_ready[k].record(s_in)
         cur.wait_event(in_ready[k])
-        y, pullback = L.rrule_fused_dense(ACT, W, dxbuf.T, b)
-        dW, dx, db = backward_from(pullback, dybuf.T)
+        y, dW, dx, db = step_from(dxbuf.T, dybuf.T)
         in_free[k].record(cur)
         done = torch.cuda.Event()
         done.record(cur)
@@ -333,7 +459,7 @@ def run_gpu_arm(args):
         for t_ in (y, dW, dx, db):
             t_.record_stream(s_out)                # keep the results alive until their download has run
 
-    for _ in range(2):
+    for _ in range(3):
         e2e_step()
     barrier()
     t0 = time.perf_counter()
@@ -348,19 +474,41 @@ def run_gpu_arm(args):
     e2e_val = world * flops_per_step() / e2e_s / 1e12
     h2d = hx.numel() * 2 + hdy.numel() * 2
     d2h = (hy.numel() + hdW.numel() + hdx.numel() + hdb.numel()) * 2
+    del in_bufs, houts, hx, hdy
 
-    line = None
+    # ---- the other configurations of the path, in the same line
+    secondary = None
+    if not args.no_secondary:
+        del graph
+        torch.cuda.empty_cache()
+        secondary = {}
+        if world == 1:
+            for wl, dts in (("conv", ("bf16", "f32")), ("ln", ("bf16", "f32")), ("gn", ("bf16", "f32")), ("bn", ("bf16", "f32")),
+                            ("mlp", ("f32",))):
+                for dt_ in dts:
+                    try:
+                        secondary[f"{wl}_{dt_}"] = measure_secondary(wl, dt_, steps=max(args.steps, 30), warm=warm, quiet=True)
+                    except Exception as e:   # noqa: BLE001 - a failing secondary row must not lose the headline
+                        secondary[f"{wl}_{dt_}"] = {"error": f"{type(e).__name__}: {e}"}
+                    torch.cuda.empty_cache()
+        try:
+            secondary["convnet"] = measure_convnet(max(5, min(args.steps, 20)), warm, dist, world, rank, local)
+        except Exception as e:               # noqa: BLE001
+            secondary["convnet"] = {"error": f"{type(e).__name__}: {e}"}
+
     if rank == 0:
         sustained, burst, which = measured_peaks()
         achieved = 2.0 * M * N * K / (fwd_ms * 1e-3) / 1e12
+        traffic = recorded_traffic()
         roofline = {
-            "bound": "tensor", "kernel": "gemm_tc_kernel (forward GEMM, bias+gelu epilogue)", "achieved": achieved,
+            "bound": "tensor", "kernel": "forward GEMM (bias+gelu epilogue, pre-activation store)", "achieved": achieved,
             "peak": sustained, "unit": "TFLOP/s", "frac": achieved / sustained,
-            # dram__bytes_read.sum + dram__bytes_write.sum of one forward launch, from the ncu launch-list pass
-            # (132.1 MB read + 103.3 MB written, Nsight Compute launch-list pass on this workload)
-            "traffic": 235.4e6, "traffic_unit": "bytes per launch",
+            "traffic": traffic, "traffic_unit": "bytes per launch",
+            "traffic_source": f"recorded constant: dram__bytes_read.sum + dram__bytes_write.sum of one forward launch in {TRAFFIC_PROFILE}",
             "peak_source": f"{which}: bf16_tflops_sustained (kernel timed inside a long step); burst figure {burst}",
             "launch_ms": fwd_ms,
+            "launch_timing": "event pair around each launch, eager replay of the same steps directly after the timed region",
+            "launches": launches, "clocks_during_launch_timing": clocks2,
         }
         cpu = None
         if world == 1:
@@ -371,22 +519,30 @@ def run_gpu_arm(args):
             val, dt_cpu = cpu_tflops(n_cols, reps)
             cpu = {"value": val, "unit": UNIT, "cores": cores, "kind": "port",
                    "sample": f"{n_cols} of {N} batch columns x {reps} repetitions, numpy/BLAS restatement of LuxLib's CPU path"}
+        st = stats(per)
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warm,
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": WORKLOAD, "M": M, "N_per_gpu": N, "K": K, "gelu": L.ops.GELU_VARIANT,
                        "l2": "inputs larger than L2 (704 MB touched per step vs 126 MB L2)",
-                       "parallelism": f"dp{world}: replicated W, per-GPU batch {N}, NCCL allreduce(avg) of dW and db" if world > 1 else "single GPU"},
+                       "parallelism": (f"dp{world}: replicated W, per-GPU batch {N}, NCCL allreduce(avg) of dW in {DW_PANELS} column "
+                                       "panels (each under the next panel's GEMM) and of db") if world > 1 else "single GPU"},
+            "timing": {"mode": mode, "ramp_s": ramp_s, "ramp_steps": ramp_steps, "step_ms": st,
+                       "ms_x_sm_mhz": ms_step * clocks["sm_mhz"] if clocks.get("sm_mhz") else None},
             "clocks": clocks,
             "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_s * 1e3, "steps": e2e_steps,
                     "pipeline": "uploads, compute and downloads on three streams, double-buffered; wall clock over all steps"},
-            "gpu_launches": 5 * args.steps,   # fwd GEMM, g = dy*act' (+db partials), db finish, dW GEMM, dX GEMM
+            "gpu_launches": (5 if world == 1 else 4 + DW_PANELS) * args.steps,   # fwd GEMM, g/db pass, db finish, dX GEMM, dW GEMM(s)
             "roofline": roofline,
             "cpu_baseline": cpu,
             "pct_of_measured_peak": {"sustained": value / world / sustained, "burst": value / world / burst},
         }
+        if comm is not None:
+            line["collectives"] = comm
+        if secondary is not None:
+            line["secondary"] = secondary
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()
@@ -395,29 +551,20 @@ def run_gpu_arm(args):
 
 
 # ---------------------------------------------------------------------------------------------
-# secondary workloads (the other configurations of the path): one JSON line each, single GPU
+# secondary workloads (the other configurations of the path), single GPU
 # ---------------------------------------------------------------------------------------------
-def hbm_peak():
-    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    if os.path.exists(path):
-        with open(path) as f:
-            return json.load(f).get("hbm_gbs", 6552.0), "measured"
-    return 6650.0, "fallback"
-
-
-def run_secondary(args):
-    """--workload ln | gn | bn | conv  [--dtype f32|bf16]: norm rows report algorithmic GB/s
-    (5*numel*sizeof(T) per fwd+bwd step) against the measured HBM copy bandwidth; conv reports
-    TFLOP/s (3 x 2*Wo*Ho*N*Cout*Cin*kW*kH per step) against the measured bf16 tensor peak."""
+def measure_secondary(wl: str, dtype: str, steps: int, warm: int, quiet: bool = False):
+    """ln | gn | bn: algorithmic GB/s (5*numel*sizeof(T) per fwd+bwd step) against the measured HBM copy bandwidth;
+    conv: TFLOP/s (3 x 2*Wo*Ho*N*Cout*Cin*kW*kH per step) against the measured bf16 tensor peak; mlp: microseconds
+    per forward + backward of the small MLP (latency-bound: time, not a fraction)."""
     import torch
     import luxlib_b200 as L
-    torch.cuda.set_device(0)
-    tdt = torch.float32 if args.dtype == "f32" else torch.bfloat16
-    es = 4 if args.dtype == "f32" else 2
+    dev_index = torch.cuda.current_device()
+    tdt = torch.float32 if dtype == "f32" else torch.bfloat16
+    es = 4 if dtype == "f32" else 2
     g = torch.Generator(device="cuda").manual_seed(3)
     rn = lambda *shape: torch.randn(*shape, device="cuda", generator=g)
     cm = lambda t: t.permute(*reversed(range(t.dim()))) if t.dim() > 1 else t  # row-major bytes -> Julia shape
-    wl = args.workload
     if wl == "ln":
         D, R = 4096, 16384
         x = cm((rn(R, D) * 1.3).to(tdt)); dy = cm(rn(R, D).to(tdt))
@@ -425,7 +572,7 @@ def run_secondary(args):
         def step():
             y, pb = L.rrule_layernorm(x, gam, bet, "identity", None, 1e-5)
             return pb(dy)
-        numel, launches, name = D * R, 3, "LayerNorm 4096x16384 (rows of 4096), affine, fwd+bwd"
+        numel, name = D * R, "LayerNorm 4096x16384 (rows of 4096), affine, fwd+bwd"
     elif wl == "gn":
         shape = (128, 512, 32, 32)  # N, C, H, W row-major == WHCN column-major
         x = cm((rn(*shape) * (torch.rand(1, 512, 1, 1, device="cuda", generator=g) * 1.5 + 0.5)).to(tdt)); dy = cm(rn(*shape).to(tdt))
@@ -433,7 +580,7 @@ def run_secondary(args):
         def step():
             y, pb = L.rrule_groupnorm(x, gam, bet, 32, "identity", 1e-5)
             return pb(dy)
-        numel, launches, name = 128 * 512 * 32 * 32, 3, "GroupNorm(32 groups) 32x32x512x128, affine, fwd+bwd"
+        numel, name = 128 * 512 * 32 * 32, "GroupNorm(32 groups) 32x32x512x128, affine, fwd+bwd"
     elif wl == "bn":
         shape = (256, 64, 56, 56)
         x = cm(rn(*shape).to(tdt)); dy = cm(rn(*shape).to(tdt))
@@ -442,7 +589,7 @@ def run_secondary(args):
         def step():
             y, st, pb = L.rrule_batchnorm(x, gam, bet, rm, rv, True, "relu", 0.1, 1e-5)
             return pb(dy)
-        numel, launches, name = 256 * 64 * 56 * 56, 6, "BatchNorm(64)+relu 56x56x64x256 training, running stats, fwd+bwd"
+        numel, name = 256 * 64 * 56 * 56, "BatchNorm(64)+relu 56x56x64x256 training, running stats, fwd+bwd"
     elif wl == "conv":
         x = cm(rn(256, 64, 56, 56).to(tdt)); dy = cm(rn(256, 64, 56, 56).to(tdt))
         w = cm((rn(64, 64, 3, 3) * (2.0 / 576) ** 0.5).to(tdt)); b = torch.zeros(64, device="cuda", dtype=tdt)
@@ -450,122 +597,180 @@ def run_secondary(args):
         def step():
             y, pb = L.rrule_fused_conv("identity", w, x, b, cd)
             return pb(dy)
-        numel, launches, name = 256 * 64 * 56 * 56, 0, "Conv 3x3 64->64 s1 p1 on 56x56x64x256, fwd + dx + dw + db"
+        numel, name = 256 * 64 * 56 * 56, "Conv 3x3 64->64 s1 p1 on 56x56x64x256, fwd + dx + dw + db"
+    elif wl == "mlp":
+        # Dense(784 -> 256, relu) -> Dense(256 -> 10), batch 128, Float32: forward + pullback of the mean-squared error
+        W1 = cm(((torch.rand(784, 256, device="cuda", generator=g) - 0.5) * (24.0 / (784 + 256)) ** 0.5))
+        W2 = cm(((torch.rand(256, 10, device="cuda", generator=g) - 0.5) * (24.0 / (256 + 10)) ** 0.5))
+        b1, b2 = torch.zeros(256, device="cuda"), torch.zeros(10, device="cuda")
+        x = cm(rn(128, 784)); tgt = cm(torch.nn.functional.one_hot(torch.randint(0, 10, (128,), device="cuda", generator=g), 10).float())
+        def step():
+            h, pb1 = L.rrule_fused_dense("relu", W1, x, b1)
+            y, pb2 = L.rrule_fused_dense("identity", W2, h, b2)
+            d = (y - tgt) * (2.0 / y.numel())
+            dW2, dh, db2 = pb2(d)
+            return pb1(dh)
+        numel, name = 0, "MLP Dense(784->256, relu) -> Dense(256->10), batch 128, Float32: forward + pullback of MSE"
     else:
         raise SystemExit(f"unknown workload {wl}")
-    warm = max(args.warmup, 3)
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    graph, _ = capture(step, torch, torch.device("cuda", dev_index))
+    run = graph.replay if graph is not None else step
+    ramp(run, torch, 0.4)
     for _ in range(warm):
-        step()
-    torch.cuda.synchronize()
-    sampler = ClockSampler(0)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sampler.start()
-    e0.record()
-    for _ in range(args.steps):
-        step()
-    e1.record()
-    torch.cuda.synchronize()
-    clocks = sampler.stop()
-    ms = e0.elapsed_time(e1) / args.steps
+        run()
+    total, per, clocks = timed(run, torch, steps, torch.cuda.synchronize, dev_index)
+    ms = total / steps
     rc = L._cabi.load().lb2_poll_device_status(None)
     if rc != 0:
         raise SystemExit(f"device status {rc}")
+    common = {"ms_per_step": ms, "step_ms": stats(per), "steps": steps, "dtype": dtype, "workload": name, "clocks": clocks,
+              "mode": "cuda_graph_replay" if graph is not None else "eager"}
     if wl == "conv":
         flop = 3 * 2.0 * 56 * 56 * 256 * 64 * 64 * 9
         sustained, burst, which = measured_peaks()
         val = flop / (ms * 1e-3) / 1e12
-        line = {"metric": "fused conv+bias+act fwd+bwd TFLOP/s", "value": val, "unit": "TFLOP/s",
-                "roofline": {"bound": "tensor", "achieved": val, "peak": sustained, "unit": "TFLOP/s", "frac": val / sustained,
-                             "traffic": None, "peak_source": f"{which}: bf16_tflops_sustained; whole step (layout passes, 3 GEMM-like kernels, reductions)"}}
+        rec = {"metric": "fused conv+bias+act fwd+bwd TFLOP/s", "value": val, "unit": "TFLOP/s",
+               "roofline": {"bound": "tensor", "achieved": val, "peak": sustained, "unit": "TFLOP/s", "frac": val / sustained,
+                            "traffic": None, "peak_source": f"{which}: bf16_tflops_sustained; whole step (layout passes, 3 GEMM-like kernels, reductions)"}}
+    elif wl == "mlp":
+        rec = {"metric": "MLP forward+backward time", "value": ms * 1e3, "unit": "us", "higher_is_better": False,
+               "flop": 6.0 * 128 * (784 * 256 + 256 * 10)}
     else:
         byts = 5.0 * numel * es
         peak, which = hbm_peak()
         val = byts / (ms * 1e-3) / 1e9
-        line = {"metric": "norm fwd+bwd HBM GB/s", "value": val, "unit": "GB/s",
-                "roofline": {"bound": "hbm", "achieved": val, "peak": peak, "unit": "GB/s", "frac": val / peak, "traffic": None,
-                             "peak_source": f"{which}: hbm_gbs; algorithmic bytes 5*numel*sizeof(T) over the whole fwd+bwd step"}}
-    line.update({"n_gpus": 1, "steps": args.steps, "warmup": warm, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
-                 "vs_baseline": None, "dtype": args.dtype, "data": "synthetic", "config": {"workload": name}, "clocks": clocks,
-                 "gpu_launches": launches * args.steps if launches else None})
-    print(json.dumps(line), flush=True)
+        rec = {"metric": "norm fwd+bwd HBM GB/s", "value": val, "unit": "GB/s",
+               "roofline": {"bound": "hbm", "achieved": val, "peak": peak, "unit": "GB/s", "frac": val / peak, "traffic": None,
+                            "peak_source": f"{which}: hbm_gbs; algorithmic bytes 5*numel*sizeof(T) over the whole fwd+bwd step"}}
+    rec.update(common)
+    return rec
+
+
+def run_secondary(args):
+    import torch
+    torch.cuda.set_device(0)
+    rec = measure_secondary(args.workload, args.dtype, args.steps, max(args.warmup, 3))
+    rec.update({"n_gpus": 1, "warmup": max(args.warmup, 3), "higher_is_better": rec.get("higher_is_better", True), "scaling": "weak",
+                "vs_baseline": None, "data": "synthetic", "config": {"workload": rec["workload"]}})
+    print(json.dumps(rec), flush=True)
     return 0
 
 
-def run_convnet(args):
-    """--workload convnet: a data-parallel training step of the stride-1 stage of a ResNet-18-style network
-    (two basic blocks of conv3x3-BN-relu / conv3x3-BN / residual-add-relu on 56x56x64, global mean pool,
-    Dense 64 -> 1000, mean-squared error against one-hot labels), bf16, per-GPU batch 256, momentum SGD.
-    Every rank holds the same parameters and its own synthetic batch; parameter gradients go through one flat
-    sum all-reduce per bucket and one lb2_optimizer_step launch (1/world folded in). Reports samples/s over all
-    ranks. The strided stages of the full network are not included (their convolutions have no tensor-core
-    path yet)."""
-    import torch
-    import luxlib_b200 as L
-    from luxlib_b200 import distributed as D
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    device = torch.device("cuda", local)
-    dist = None
-    if world > 1:
-        D.initialize(D.NCCLBackend)
-        import torch.distributed as dist
-    bf = torch.bfloat16
-    Bsz, C, H, NCLS = 256, 64, 56, 1000
+# ---------------------------------------------------------------------------------------------
+# ResNet-18 data-parallel training step (perf/resnet/resnet.jl:9-107)
+# ---------------------------------------------------------------------------------------------
+def build_resnet18(L, torch, device, rank, batch, dtype):
+    """Parameters (identical on every rank) and the training step of ResNet(18) as perf/resnet/resnet.jl builds it:
+    7x7/2 stem conv + BatchNorm(relu) + 3x3/2 max pool (SamePad), four stages of two basic blocks (conv3x3-BN(relu)-
+    conv3x3-BN(relu, scale initialised to zero), projection conv1x1/2-BN on the first block of stages 2-4, joined
+    by relu.(main .+ skip)), global mean pool, Dense 512 -> 1000. Convolutions carry no bias. Loss: mean-squared error
+    against one-hot labels."""
     gp = torch.Generator(device="cuda").manual_seed(5)               # parameters: same on every rank
     gd = torch.Generator(device="cuda").manual_seed(100 + rank)      # data: one shard per rank
     cm = lambda t: t.permute(*reversed(range(t.dim()))) if t.dim() > 1 else t   # row-major bytes -> Julia shape
-    rnp = lambda *sh: torch.randn(*sh, device=device, generator=gp)
-    convs = [cm((rnp(C, C, 3, 3) * (2.0 / (9 * C)) ** 0.5).to(bf)) for _ in range(4)]       # kaiming_normal
-    cbias = [torch.zeros(C, device=device, dtype=bf) for _ in range(4)]
-    gam = [torch.ones(C, device=device, dtype=bf) for _ in range(4)]
-    bet = [torch.zeros(C, device=device, dtype=bf) for _ in range(4)]
-    rmean = [torch.zeros(C, device=device, dtype=bf) for _ in range(4)]
-    rvar = [torch.ones(C, device=device, dtype=bf) for _ in range(4)]
-    lim = (24.0 / (C + NCLS)) ** 0.5
-    Wd = cm(((torch.rand(C, NCLS, device=device, generator=gp) - 0.5) * lim).to(bf))        # (1000, 64) glorot_uniform
-    bd = torch.zeros(NCLS, device=device, dtype=bf)
-    x = cm(torch.randn(Bsz, C, H, H, device=device, generator=gd).to(bf))
-    labels = torch.randint(0, NCLS, (Bsz,), device=device, generator=gd)
-    target = cm(torch.nn.functional.one_hot(labels, NCLS).to(bf))                           # (1000, B)
-    params = convs + cbias + gam + bet + [Wd, bd]
-    opt = D.FusedOptimizer(D.NCCLBackend, "momentum", eta=1e-3, rho=0.9)
-    states = opt.init(params)
-    cd = L.ConvDims.make(2, 1, 1, 1, 1, False)
+    params, names = [], []
 
-    def step():
-        h, tape = x, []
-        for blk in range(2):
+    def conv_w(k, cin, cout):
+        w = cm((torch.randn(cout, cin, k, k, device=device, generator=gp) * (2.0 / (k * k * cin)) ** 0.5).to(dtype))   # kaiming_normal
+        params.append(w); names.append(f"conv{k}x{k}_{cin}_{cout}")
+        return len(params) - 1
+
+    def bn_p(c, zero_scale=False):
+        g_ = torch.zeros(c, device=device, dtype=dtype) if zero_scale else torch.ones(c, device=device, dtype=dtype)
+        params.append(g_); params.append(torch.zeros(c, device=device, dtype=dtype)); names.extend([f"bn_scale_{c}", f"bn_bias_{c}"])
+        return len(params) - 2
+
+    stem = (conv_w(7, 3, 64), bn_p(64))
+    blocks = []
+    cin = 64
+    for stage, cout in enumerate((64, 128, 256, 512)):
+        for j in range(2):
+            stride = 2 if (stage > 0 and j == 0) else 1
+            blk = {"stride": stride, "c1": conv_w(3, cin, cout), "n1": bn_p(cout), "c2": conv_w(3, cout, cout), "n2": bn_p(cout, True)}
+            if stride != 1 or cin != cout:
+                blk["cp"], blk["np"] = conv_w(1, cin, cout), bn_p(cout)
+            blocks.append(blk)
+            cin = cout
+    lim = (24.0 / (512 + 1000)) ** 0.5
+    params.append(cm(((torch.rand(512, 1000, device=device, generator=gp) - 0.5) * lim).to(dtype)))   # (1000, 512) glorot_uniform
+    params.append(torch.zeros(1000, device=device, dtype=dtype))
+    iWd, ibd = len(params) - 2, len(params) - 1
+    n_bn = sum(1 for n_ in names if n_.startswith("bn_scale"))
+    rstats = {}
+
+    def bn(i, h, act):
+        c = params[i].shape[0]
+        rm, rv = rstats.setdefault(i, (torch.zeros(c, device=device, dtype=dtype), torch.ones(c, device=device, dtype=dtype)))
+        y, new, pb = L.rrule_batchnorm(h, params[i], params[i + 1], rm, rv, True, act, 0.1, 1e-5)
+        rstats[i] = new
+        return y, pb
+
+    x = cm(torch.randn(batch, 3, 224, 224, device=device, generator=gd).to(dtype))
+    labels = torch.randint(0, 1000, (batch,), device=device, generator=gd)
+    target = cm(torch.nn.functional.one_hot(labels, 1000).to(dtype))                            # (1000, B)
+    cd = lambda s, p: L.ConvDims.make(2, s, p, 1, 1, False)
+
+    def forward_backward():
+        grads = [None] * len(params)
+        h, pc = L.rrule_fused_conv("identity", params[stem[0]], x, None, cd(2, 3))
+        h, pn = bn(stem[1], h, "relu")
+        h, pp = L.rrule_maxpool(h, L.PoolDims.make((3, 3), (2, 2), (1, 1, 1, 1)))
+        tape = []
+        for blk in blocks:
             skip = h
-            i0, i1 = 2 * blk, 2 * blk + 1
-            c0, pc0 = L.rrule_fused_conv("identity", convs[i0], h, cbias[i0], cd)
-            n0, (rmean[i0], rvar[i0]), pn0 = L.rrule_batchnorm(c0, gam[i0], bet[i0], rmean[i0], rvar[i0], True, "relu", 0.1, 1e-5)
-            c1, pc1 = L.rrule_fused_conv("identity", convs[i1], n0, cbias[i1], cd)
-            n1, (rmean[i1], rvar[i1]), pn1 = L.rrule_batchnorm(c1, gam[i1], bet[i1], rmean[i1], rvar[i1], True, "identity", 0.1, 1e-5)
-            h, padd = L.rrule_add_activation("relu", n1, skip)
-            tape.append((pc0, pn0, pc1, pn1, padd))
-        pooled, ppool = L.rrule_meanpool(h, L.PoolDims.global_(h))          # (1, 1, 64, B)
-        feat = pooled.reshape(C, Bsz)                                        # same bytes, Julia shape (64, B)
-        y, pdense = L.rrule_fused_dense("identity", Wd, feat, bd)
-        # loss glue (tiny, 1000 x B): mean-squared error and its gradient
-        diff = y - target
+            a, pc1 = L.rrule_fused_conv("identity", params[blk["c1"]], h, None, cd(blk["stride"], 1))
+            a, pn1 = bn(blk["n1"], a, "relu")
+            a, pc2 = L.rrule_fused_conv("identity", params[blk["c2"]], a, None, cd(1, 1))
+            a, pn2 = bn(blk["n2"], a, "relu")
+            pcp = pnp = None
+            if "cp" in blk:
+                skip, pcp = L.rrule_fused_conv("identity", params[blk["cp"]], h, None, cd(blk["stride"], 0))
+                skip, pnp = bn(blk["np"], skip, "identity")
+            h, padd = L.rrule_add_activation("relu", a, skip)
+            tape.append((blk, pc1, pn1, pc2, pn2, pcp, pnp, padd))
+        pooled, ppool = L.rrule_meanpool(h, L.PoolDims.global_(h))          # (1, 1, 512, B)
+        feat = pooled.reshape(512, batch)                                    # same bytes, Julia shape (512, B)
+        y, pdense = L.rrule_fused_dense("identity", params[iWd], feat, params[ibd])
+        diff = y - target                                                    # loss glue (1000 x B)
         loss = (diff.float() ** 2).mean()
         dy = diff * (2.0 / diff.numel())
-        grads = [None] * len(params)
-        dWd, dfeat, dbd = pdense(dy)
-        grads[16], grads[17] = dWd, dbd
-        dh = ppool(dfeat.reshape(1, 1, C, Bsz))
-        for blk in (1, 0):
-            pc0, pn0, pc1, pn1, padd = tape[blk]
-            i0, i1 = 2 * blk, 2 * blk + 1
-            dn1, dskip = padd(dh)
-            dc1, grads[8 + i1], grads[12 + i1] = pn1(dn1)
-            grads[i1], dn0, grads[4 + i1] = pc1(dc1)
-            dc0, grads[8 + i0], grads[12 + i0] = pn0(dn0)
-            grads[i0], dx0, grads[4 + i0] = pc0(dc0)
-            dh = L.add_activation("identity", dx0, dskip)
-        opt.update(states, params, grads)
+        grads[iWd], dfeat, grads[ibd] = pdense(dy)
+        dh = ppool(dfeat.reshape(1, 1, 512, batch))
+        for blk, pc1, pn1, pc2, pn2, pcp, pnp, padd in reversed(tape):
+            da, dskip = padd(dh)
+            da, grads[blk["n2"]], grads[blk["n2"] + 1] = pn2(da)
+            grads[blk["c2"]], da, _ = pc2(da)
+            da, grads[blk["n1"]], grads[blk["n1"] + 1] = pn1(da)
+            grads[blk["c1"]], dmain, _ = pc1(da)
+            if pcp is not None:
+                ds, grads[blk["np"]], grads[blk["np"] + 1] = pnp(dskip)
+                grads[blk["cp"]], dskip, _ = pcp(ds)
+            dh = L.add_activation("identity", dmain, dskip)
+        dh = pp(dh)
+        dh, grads[stem[1]], grads[stem[1] + 1] = pn(dh)
+        grads[stem[0]], _, _ = pc(dh, need_dx=False)
+        return loss, grads
+
+    return params, forward_backward, n_bn
+
+
+def measure_convnet(steps, warm, dist, world, rank, local, batch=256):
+    import torch
+    import luxlib_b200 as L
+    from luxlib_b200 import distributed as D
+    device = torch.device("cuda", local)
+    bf = torch.bfloat16
+    params, forward_backward, n_bn = build_resnet18(L, torch, device, rank, batch, bf)
+    opt = D.FusedOptimizer(D.NCCLBackend, "momentum", eta=1e-3, rho=0.9)
+    states = opt.init(params)
+    n_params = sum(p.numel() for p in params)
+
+    def step():
+        loss, grads = forward_backward()
+        opt.update(states, params, grads)       # one flat sum all-reduce per bucket + one optimiser launch (1/world folded in)
         return loss
 
     def barrier():
@@ -573,42 +778,56 @@ def run_convnet(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    warm = max(args.warmup, 3)
-    for _ in range(warm):
-        step()
-    barrier()
-    sampler = ClockSampler(local)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    sampler.start()
-    e0.record()
-    for _ in range(args.steps):
+    for _ in range(2):
         loss = step()
-    e1.record()
     barrier()
-    clocks = sampler.stop()
-    t = torch.tensor([e0.elapsed_time(e1)], device=device)
+    rc = L._cabi.load().lb2_poll_device_status(None)
+    if rc != 0:
+        raise SystemExit(f"device status {rc}: {L._cabi.load().lb2_last_error_string()}")
+    graph, gloss = capture(step, torch, device)
+    run = graph.replay if graph is not None else step
+    ramp(run, torch, 0.5, barrier)
+    for _ in range(warm):
+        run()
+    total, per, clocks = timed(run, torch, steps, barrier, local)
+    t = torch.tensor([total], device=device)
     if dist is not None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item()) / args.steps
+    ms = float(t.item()) / steps
     rc = L._cabi.load().lb2_poll_device_status(None)
     if rc != 0:
         raise SystemExit(f"device status {rc}")
+    flop = 10.88e9 * batch                           # 3 x (3.627 GFLOP conv + 0.001 GFLOP dense) per image
+    sustained, burst, which = measured_peaks()
+    tf = world * flop / (ms * 1e-3) / 1e12
+    final_loss = float(gloss if graph is not None else loss)
+    return {"metric": "data-parallel conv-net step samples/s", "value": world * batch / (ms * 1e-3), "unit": "samples/s",
+            "n_gpus": world, "steps": steps, "ms_per_step": ms, "step_ms": stats(per), "dtype": "bf16",
+            "workload": ("ResNet-18 (7x7/2 stem, 3x3/2 max pool, stages [2,2,2,2] of basic blocks at 64/128/256/512 with 1x1/2 projections, "
+                         f"global mean pool, Dense 512->1000), 224x224x3 input, per-GPU batch {batch}, MSE loss, momentum SGD fused with the "
+                         "gradient all-reduce bucket"),
+            "parameters": n_params, "allreduce_bytes": n_params * 2, "parallelism": f"dp{world}", "final_loss": final_loss,
+            "mode": "cuda_graph_replay" if graph is not None else "eager", "clocks": clocks,
+            "roofline": {"bound": "tensor", "achieved": tf, "peak": world * sustained, "unit": "TFLOP/s", "frac": tf / (world * sustained),
+                         "traffic": None, "peak_source": f"{which}: bf16_tflops_sustained x n_gpus; 10.88 GFLOP per image (conv + dense, fwd + both gradients)"}}
+
+
+def run_convnet(args):
+    import torch
+    from luxlib_b200 import distributed as D
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        D.initialize(D.NCCLBackend)
+        import torch.distributed as dist
+    rec = measure_convnet(args.steps, max(args.warmup, 3), dist, world, rank, local, batch=args.batch)
     if rank == 0:
-        flop = 4 * 3 * 2.0 * H * H * Bsz * C * C * 9 + 3 * 2.0 * NCLS * C * Bsz
-        sustained, burst, which = measured_peaks()
-        tf = world * flop / (ms * 1e-3) / 1e12
-        line = {"metric": "data-parallel conv-net step samples/s", "value": world * Bsz / (ms * 1e-3), "unit": "samples/s",
-                "n_gpus": world, "steps": args.steps, "warmup": warm, "ms_per_step": ms, "higher_is_better": True,
-                "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-                "config": {"workload": "ResNet-18-style stride-1 stage: 2 basic blocks (conv3x3-BN-relu, conv3x3-BN, add-relu) on "
-                                       "56x56x64, global mean pool, Dense 64->1000, MSE; per-GPU batch 256; momentum SGD fused with the "
-                                       "gradient all-reduce bucket",
-                           "parallelism": f"dp{world}", "final_loss": float(loss)},
-                "clocks": clocks, "gpu_launches": None,
-                "roofline": {"bound": "tensor", "achieved": tf, "peak": world * sustained, "unit": "TFLOP/s", "frac": tf / (world * sustained),
-                             "traffic": None, "peak_source": f"{which}: bf16_tflops_sustained x n_gpus; conv + dense FLOPs of the whole step"}}
-        print(json.dumps(line), flush=True)
+        rec.update({"warmup": max(args.warmup, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "data": "synthetic",
+                    "config": {"workload": rec["workload"], "parallelism": rec["parallelism"]}, "gpu_launches": None})
+        print(json.dumps(rec), flush=True)
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
@@ -618,13 +837,16 @@ def run_convnet(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="dense", choices=["dense", "ln", "gn", "bn", "conv", "convnet"],
-                    help="dense = the headline configuration (default); ln/gn/bn/conv are single-GPU secondary rows; "
-                         "convnet = data-parallel conv-net stage step (any --gpus, under torchrun for N > 1)")
+    ap.add_argument("--workload", default="dense", choices=["dense", "ln", "gn", "bn", "conv", "mlp", "convnet"],
+                    help="dense = the headline configuration (default; its line also carries the others as `secondary`); "
+                         "ln/gn/bn/conv/mlp print one single-GPU row; convnet = the ResNet-18 data-parallel step (any --gpus, "
+                         "under torchrun for N > 1)")
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "f32"], help="storage type of the secondary workloads")
+    ap.add_argument("--batch", type=int, default=256, help="per-GPU batch of the convnet workload")
+    ap.add_argument("--no-secondary", action="store_true", help="dense workload only: leave the `secondary` records out")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)

@@ -66,8 +66,8 @@ typedef enum {
 #define LB2_FLAG_TF32_1X 1u /* fp32 GEMM/conv: single-pass TF32 (rel err ~1e-3) instead of the
                                default error-compensated 3xTF32 split (rel err ~1e-6) */
 #define LB2_FLAG_FORCE_SIMT 2u /* route a contraction through the CUDA-core kernel (debug / odd shapes) */
-#define LB2_FLAG_CTA_PAIR 4u /* tensor-core GEMM: take the CTA-pair kernel (cta_group::2, 256x256 tiles) already for problems
-                                that occupy an eighth of the SM pairs (default: from about three quarters on) */
+#define LB2_FLAG_CTA_PAIR 4u /* tensor-core GEMM: take the CTA-pair kernel (cta_group::2, 256x256 tiles) for any operand layout
+                                once the problem occupies an eighth of the SM pairs (default: only for two MN-major operands) */
 #define LB2_FLAG_NO_CTA_PAIR 8u /* tensor-core GEMM: never take the CTA-pair kernel */
 /* Per call: the persistent tensor-core GEMM of this call leaves n SMs (0..127) unoccupied, for a kernel the caller
  * runs beside it on another stream — e.g. the NCCL all-reduce of parameter gradients that Lux's DistributedOptimizer

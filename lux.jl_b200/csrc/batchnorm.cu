@@ -92,8 +92,10 @@ __global__ void __launch_bounds__(256) bn_reduce_kernel(float* __restrict__ part
     mean = mean_in[c];
     if constexpr (ACT != LB2_ACT_IDENTITY) {
       const float inv = inv_in[c];
-      gp = inv; bp = -mean * inv;
-      if constexpr (AFFINE) { gp = to_f32(gamma[c]) * inv; bp = to_f32(beta[c]) - mean * gp; }
+      // the pre-activation is rebuilt from the CENTRED value, (x - mean)*gp + beta, as the reference forms it: with
+      // given (storage-precision) statistics x can equal the mean exactly, and relu' must then see exactly beta
+      gp = inv; bp = 0.f;
+      if constexpr (AFFINE) { gp = to_f32(gamma[c]) * inv; bp = to_f32(beta[c]); }
     }
   }
   float a = 0.f, q = 0.f;
@@ -126,9 +128,10 @@ __global__ void __launch_bounds__(256) bn_reduce_kernel(float* __restrict__ part
 #pragma unroll
             for (int j = 0; j < V; ++j) {
               float d = gv[k].get(j);
-              if constexpr (ACT != LB2_ACT_IDENTITY) d *= act_grad_pre_any<ACT, FAST>(act_rt, fmaf(xv[k].get(j), gp, bp));
+              const float xm = xv[k].get(j) - mean;
+              if constexpr (ACT != LB2_ACT_IDENTITY) d *= act_grad_pre_any<ACT, FAST>(act_rt, fmaf(xm, gp, bp));
               a += d;
-              q = fmaf(d, xv[k].get(j) - mean, q);
+              q = fmaf(d, xm, q);
             }
           }
         }
@@ -144,9 +147,10 @@ __global__ void __launch_bounds__(256) bn_reduce_kernel(float* __restrict__ part
         float d = xv - K; a += d; q += d * d;
       } else {
         float d = to_f32(dy[e]);
-        if constexpr (ACT != LB2_ACT_IDENTITY) d *= act_grad_pre_any<ACT, FAST>(act_rt, fmaf(xv, gp, bp));
+        const float xm = xv - mean;
+        if constexpr (ACT != LB2_ACT_IDENTITY) d *= act_grad_pre_any<ACT, FAST>(act_rt, fmaf(xm, gp, bp));
         a += d;
-        q += d * (xv - mean);
+        q += d * xm;
       }
     }
   }
@@ -180,8 +184,8 @@ __global__ void __launch_bounds__(256) bn_reduce_s1_kernel(float* __restrict__ p
       mean = mean_in[c];
       if constexpr (ACT != LB2_ACT_IDENTITY) {
         const float inv = inv_in[c];
-        gp = inv; bp = -mean * inv;
-        if constexpr (AFFINE) { gp = to_f32(gamma[c]) * inv; bp = to_f32(beta[c]) - mean * gp; }
+        gp = inv; bp = 0.f;
+        if constexpr (AFFINE) { gp = to_f32(gamma[c]) * inv; bp = to_f32(beta[c]); }
       }
     }
     for (int64_t b = b_begin + threadIdx.y; b < b_end; b += 8) {
@@ -190,9 +194,10 @@ __global__ void __launch_bounds__(256) bn_reduce_s1_kernel(float* __restrict__ p
         float d = xv - K; a += d; q += d * d;
       } else {
         float d = to_f32(dy[b * C + c]);
-        if constexpr (ACT != LB2_ACT_IDENTITY) d *= act_grad_pre_any<ACT, FAST>(act_rt, fmaf(xv, gp, bp));
+        const float xm = xv - mean;
+        if constexpr (ACT != LB2_ACT_IDENTITY) d *= act_grad_pre_any<ACT, FAST>(act_rt, fmaf(xm, gp, bp));
         a += d;
-        q += d * (xv - mean);
+        q += d * xm;
       }
     }
   }
@@ -296,11 +301,12 @@ __device__ __forceinline__ void bn_channel_coefs(int64_t c, const float* __restr
     gp = inv; bp = -mean * inv;
     if constexpr (AFFINE) { gp = to_f32(gamma[c]) * inv; bp = to_f32(beta[c]) - mean * gp; }
   } else {
+    // the activation derivative is taken at (x - mean)*gp + bp with bp = beta (see bn_reduce_kernel)
     gp = 1.f; bp = 0.f;
     if constexpr (ACT != LB2_ACT_IDENTITY) {
-      const float inv = inv_in[c], mean = mean_in[c];
-      gp = inv; bp = -mean * inv;
-      if constexpr (AFFINE) { gp = to_f32(gamma[c]) * inv; bp = to_f32(beta[c]) - mean * gp; }
+      const float inv = inv_in[c];
+      gp = inv;
+      if constexpr (AFFINE) { gp = to_f32(gamma[c]) * inv; bp = to_f32(beta[c]); }
     }
   }
 }
@@ -344,13 +350,15 @@ __global__ void __launch_bounds__(256) bn_apply_kernel(T* __restrict__ out, cons
       }
       if constexpr (MODE == 2) {
         const float c0 = coef[c * 4], c1 = coef[c * 4 + 1], c2 = coef[c * 4 + 2];
+        float mu = 0.f;
+        if constexpr (ACT != LB2_ACT_IDENTITY) mu = mean_in[c];
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
           const int64_t v = v0 + k * 32;
           if (v < sv) {
             store16_stream(outr + v * V, vec_from<T>([&](int j) {
               float d = gv[k].get(j);
-              if constexpr (ACT != LB2_ACT_IDENTITY) d *= act_grad_pre_any<ACT, FAST>(act_rt, fmaf(xv[k].get(j), gp, bp));
+              if constexpr (ACT != LB2_ACT_IDENTITY) d *= act_grad_pre_any<ACT, FAST>(act_rt, fmaf(xv[k].get(j) - mu, gp, bp));
               return fmaf(c0, d, fmaf(c1, xv[k].get(j), c2));
             }));
           }
@@ -375,7 +383,7 @@ __global__ void __launch_bounds__(256) bn_apply_kernel(T* __restrict__ out, cons
         const float c0 = coef[c * 4], c1 = coef[c * 4 + 1], c2 = coef[c * 4 + 2];
         const float xv = to_f32(x[e]);
         float d = to_f32(dy[e]);
-        if constexpr (ACT != LB2_ACT_IDENTITY) d *= act_grad_pre_any<ACT, FAST>(act_rt, fmaf(xv, gp, bp));
+        if constexpr (ACT != LB2_ACT_IDENTITY) d *= act_grad_pre_any<ACT, FAST>(act_rt, fmaf(xv - mean_in[c], gp, bp));
         out[e] = from_f32<T>(fmaf(c0, d, fmaf(c1, xv, c2)));
       } else {
         out[e] = from_f32<T>(act_apply_any<ACT, FAST>(act_rt, fmaf(to_f32(x[e]), gp, bp)));

@@ -849,13 +849,17 @@ int32_t gemm_tc_launch(void* D, int64_t ldd, GemmOperand A, GemmOperand B, int64
   const int es = tf32 ? 4 : 2;
   const int bk = 128 / es;
   const bool split = tf32 && split3;
-  // Kernel choice. bf16 / single-pass tf32 problems with enough 256 x 256 tiles to occupy most CTA pairs run on the
-  // CTA-pair kernel (LB2_FLAG_CTA_PAIR asks for it from a quarter of the pairs on). Otherwise the single-CTA kernel
-  // with 128 x 256 tiles, or 128 x 128 when that is what it takes to fill the machine or to fit the doubled
-  // 3xTF32 stages.
+  // Kernel choice. Under the board's power limit the single-CTA kernel with 128 x 256 tiles is as fast as the
+  // CTA-pair kernel for K-major operands (forward and dX of a dense layer: 1131 / 1151 against 1100 / 1136 TFLOP/s
+  // on 4096 x 8192 x 4096), while the pair kernel wins when both operands are MN-major (dW: 981 against 933), whose
+  // tiles arrive as several 64-wide boxes per k-block. So the pair kernel is the default for that layout when the
+  // problem has enough 256 x 256 tiles to occupy most SM pairs; LB2_FLAG_CTA_PAIR asks for it for any layout (from an
+  // eighth of the pairs on), LB2_FLAG_NO_CTA_PAIR rules it out. 128 x 128 tiles when that is what it takes to fill
+  // the machine or to fit the doubled 3xTF32 stages.
   const int64_t pair_tiles = ((Mm + 2 * kBM - 1) / (2 * kBM)) * ((Nn + kPairBN - 1) / kPairBN);
-  const int64_t pair_min = (flags & LB2_FLAG_CTA_PAIR) ? sm_count() / 8 : sm_count() / 2 - 16;
-  const bool pair = !split && !(flags & LB2_FLAG_NO_CTA_PAIR) && pair_tiles >= pair_min;
+  const bool want_pair = (flags & LB2_FLAG_CTA_PAIR) ? pair_tiles >= sm_count() / 8
+                                                     : (A.mn_major && B.mn_major && pair_tiles >= sm_count() / 2 - 16);
+  const bool pair = !split && !(flags & LB2_FLAG_NO_CTA_PAIR) && want_pair;
   int bn = 256;
   if (pair) bn = kPairBN / 2;  // rows of B each CTA of a pair loads
   else if (split) bn = 128;

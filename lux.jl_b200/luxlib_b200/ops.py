@@ -133,10 +133,14 @@ def rrule_fused_dense(act: str, weight, x, b=None, *, flags: int = 0):
     y, pre, (W, ldw, X, ldx, bb, M, N, K, dt) = _dense_fwd(act, weight, x, b, keep_pre, flags)
     code = act_code(act)
 
-    def pullback(delta, on_param_grads=None, shadows=None):
-        """Δ -> (∂weight, ∂x, ∂b). `on_param_grads(dW, db)`, when given, is called as soon as the
-        parameter gradients are enqueued and before ∂x is computed, so a data-parallel caller can
-        start their all-reduce underneath the remaining GEMM (same kernels, three C calls instead of one).
+    def pullback(delta, on_param_grads=None, shadows=None, param_panels=1, mark=None):
+        """Δ -> (∂weight, ∂x, ∂b).
+
+        `on_param_grads(dW_panel, db_or_None)` switches to the data-parallel order of work: g = Δ .* act' and ∂b first,
+        then ∂x, then ∂weight in `param_panels` column panels; the callback runs as soon as a panel is enqueued (∂b
+        comes with the last one), so the caller's all-reduce of panel i runs underneath the GEMM of panel i+1 — a
+        panel of 1024 columns is one wave of 256 x 256 tiles on 64 of the 74 SM pairs, which leaves SMs to the
+        collective. Same kernels, more C calls. `mark()`, when given, is called after each phase (profiling hooks).
         `shadows = (dW, dx, db)` switches to the accumulate contract of the Enzyme rules: the gradients are added
         to those arrays in place and Δ is zeroed."""
         if on_param_grads is not None:
@@ -147,9 +151,20 @@ def rrule_fused_dense(act: str, weight, x, b=None, *, flags: int = 0):
             _, wsp, wsn = _ws(lib.lb2_bias_act_bwd_workspace_bytes(1, M, N), W.device)
             _cabi.check(lib.lb2_bias_act_bwd(ptr(g), ptr(db), ptr(d), None if keep_pre else ptr(y2), ptr(pre2), 1, M, N, dt,
                                              code, wsp, wsn, current_stream(W.device)))
-            dW = matmul(g, X, transB=True, flags=flags)      # g * x'
-            on_param_grads(dW, db)
+            if mark is not None:
+                mark()
             dx = matmul(W, g, transA=True, flags=flags)      # W' * g
+            if mark is not None:
+                mark()
+            dW = jl_empty((M, K), W.dtype, W.device)
+            panels = max(1, min(int(param_panels), K))
+            bounds = [K * i // panels for i in range(panels + 1)]
+            for i in range(panels):
+                k0, k1 = bounds[i], bounds[i + 1]
+                matmul(g, X[k0:k1, :], transB=True, flags=flags, out=dW[:, k0:k1])      # g * x[k0:k1, :]'
+                on_param_grads(dW[:, k0:k1], db if i == panels - 1 else None)
+            if mark is not None:
+                mark()
             return dW, (dx.reshape(x.shape) if x.dim() == 1 else dx), db
         d = as_colmajor(delta.reshape(M, N).to(W.dtype))
         if shadows is not None:
@@ -384,10 +399,11 @@ def rrule_fused_conv(act: str, weight, x, b, cdims: ConvDims, *, flags: int = 0)
     y, pre, (Wt, X, bb, d, dt) = _conv_fwd(act, weight, x, b, cdims, keep_pre, flags)
     code = act_code(act)
 
-    def pullback(delta):
+    def pullback(delta, need_dx=True):
+        """Δ -> (∂weight, ∂x, ∂b); `need_dx=False` (a network's first layer) skips the data gradient and returns None for it."""
         dl = as_colmajor(delta.to(X.dtype))  # NNlib.colmajor(Δ): impl/conv.jl:263
         dw = jl_empty(Wt.shape, X.dtype, X.device)
-        dx = jl_empty(X.shape, X.dtype, X.device)
+        dx = jl_empty(X.shape, X.dtype, X.device) if need_dx else None
         db = jl_empty((d.cout,), X.dtype, X.device) if bb is not None else None
         _, wsp, wsn = _ws(lib.lb2_conv_bwd_workspace_bytes(C.byref(d), dt, code), X.device)
         _cabi.check(lib.lb2_conv_bwd(ptr(dw), ptr(dx), ptr(db), ptr(dl), None if keep_pre else ptr(y), ptr(pre), ptr(X),
