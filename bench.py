@@ -221,8 +221,13 @@ class ClockSampler:
 # ---------------------------------------------------------------------------------------------
 # measurement helpers
 # ---------------------------------------------------------------------------------------------
+EAGER = False   # --eager: time plain launches (no graph capture, no ramp); used when profiling the launch list
+
+
 def capture(step, torch, device):
     """The step as a CUDA graph replay (None when capture is not possible: the caller then times eager launches)."""
+    if EAGER:
+        return None, None
     try:
         torch.cuda.synchronize(device)
         g = torch.cuda.CUDAGraph()
@@ -249,6 +254,8 @@ def ramp(run, torch, seconds: float, barrier=None):
     """Untimed repetitions of the step for a fixed wall time (clocks, caches, NCCL first-use set-up)."""
     t0 = time.perf_counter()
     n = 0
+    if EAGER:
+        return 0.0, 0
     while True:
         for _ in range(8):
             run()
@@ -847,7 +854,10 @@ def main():
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "f32"], help="storage type of the secondary workloads")
     ap.add_argument("--batch", type=int, default=256, help="per-GPU batch of the convnet workload")
     ap.add_argument("--no-secondary", action="store_true", help="dense workload only: leave the `secondary` records out")
+    ap.add_argument("--eager", action="store_true", help="plain launches, no CUDA graph and no ramp (for kernel-list profiling)")
     args = ap.parse_args()
+    global EAGER
+    EAGER = args.eager
     if args.impl == "reference":
         return run_reference_arm(args)
     if args.workload == "convnet":

@@ -85,6 +85,12 @@ LB2_API const char* lb2_last_error_string(void);
  * wait expires. Synchronises `stream`. Returns LB2_OK or LB2_TIMEOUT. */
 LB2_API int32_t lb2_poll_device_status(void* stream);
 
+/* Self-test of the bounded device-side waits (no counterpart in the reference): launches one thread that waits, with
+ * the given limit (1 us .. 100 ms), on a barrier nothing arrives at — the wait routine of the tensor-core kernels. The
+ * wait expires, the kernel records it and returns; lb2_poll_device_status then reports LB2_TIMEOUT once and the
+ * device stays usable. */
+LB2_API int32_t lb2_selftest_bounded_wait(uint64_t limit_ns, void* stream);
+
 /* ---- activation / bias-activation ------------------------------------------------------ */
 /* y = act.(x) over n elements.  Replaces activation!  (lib/LuxLib/src/impl/activation.jl:103-133). */
 LB2_API int32_t lb2_act_fwd(void* y, const void* x, int64_t n, int32_t dtype, int32_t act, void* stream);

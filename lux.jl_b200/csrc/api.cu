@@ -6,6 +6,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "tc_ptx.cuh"
 
 namespace lb2 {
 
@@ -52,11 +53,32 @@ unsigned int* device_status_word() {
   return p;
 }
 
+// One thread waits, with the given limit, on an mbarrier that nothing ever arrives at: the same wait routine the
+// tensor-core kernels use, so its expiry path (status word set, kernel returns, context intact) can be exercised
+// without any kernel having to hang.
+__global__ void selftest_bounded_wait_kernel(unsigned int* status, uint64_t limit_ns) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    mbar_wait_limit(&bar, 0, status, 0x40000000u, limit_ns);
+  }
+}
+
 }  // namespace lb2
 
 extern "C" {
 
-int32_t lb2_version(void) { return 100; }
+int32_t lb2_version(void) { return 101; }
+
+int32_t lb2_selftest_bounded_wait(uint64_t limit_ns, void* stream) {
+  LB2_REQUIRE(limit_ns >= 1000 && limit_ns <= 100000000ull, LB2_BAD_ARG, "limit must be between 1 microsecond and 100 milliseconds");
+  unsigned int* st = lb2::device_status_word();
+  LB2_REQUIRE(st != nullptr, LB2_LAUNCH_FAIL, "status word unavailable");
+  lb2::selftest_bounded_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(st, limit_ns);
+  LB2_CHECK_LAUNCH("selftest_bounded_wait");
+  return LB2_OK;
+}
 
 const char* lb2_status_string(int32_t s) {
   switch (s) {

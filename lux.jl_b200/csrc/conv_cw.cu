@@ -36,36 +36,68 @@ namespace {
 constexpr int kCwThreads = 384;
 constexpr int kCwBM = 128;
 constexpr int kCwMaxKb = 160;     // k-blocks (tap x 64-channel chunk) per launch
-constexpr int kCwMaxPairs = 4;    // column groups of one filter-gradient MMA
 
 inline int round_up(int v, int a) { return (v + a - 1) / a * a; }
 
 // ----------------------------------------------------------------------------------------------
 // layout passes
 // ----------------------------------------------------------------------------------------------
-// out[n][h][w][c] (c contiguous, Cp channels, zero beyond C)  <-  in[n][c][h][w] (w contiguous)
+// out[n][s][c] (c contiguous, Cp channels, zero beyond C)  <-  in[n][c][s] (s = w + W*h contiguous): per image a
+// C x S matrix is transposed in 64 x 64 tiles through shared memory. VW = elements per global load (8: 16-byte
+// loads when the planes are 16-byte aligned, i.e. S % 8 == 0; 4 for S % 4 == 0; 1 otherwise); stores are always
+// 16 bytes wide along c (Cp is a multiple of 8).
+template <int VW>
 __global__ void __launch_bounds__(256) cw_transpose_kernel(uint16_t* __restrict__ out, const uint16_t* __restrict__ in,
-                                                           int W, int H, int C, int Cp, int N) {
-  __shared__ uint16_t tile[64][66];
-  const int wt = (W + 63) / 64, ct = (Cp + 63) / 64;
-  const int64_t blocks = (int64_t)N * H * wt * ct;
-  const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;   // 64 x 4
+                                                           int S, int C, int Cp, int N) {
+  constexpr int PITCH = 66;                         // elements per tile row: 33 words, odd, spreads the banks
+  __shared__ uint16_t tile[64 * PITCH];
+  const int st = (S + 63) / 64, ct = (Cp + 63) / 64;
+  const int64_t blocks = (int64_t)N * st * ct;
   for (int64_t b = blockIdx.x; b < blocks; b += gridDim.x) {
     int64_t r = b;
     const int ci = (int)(r % ct); r /= ct;
-    const int wi = (int)(r % wt); r /= wt;
-    const int h = (int)(r % H);
-    const int n = (int)(r / H);
-    const int w0 = wi * 64, c0 = ci * 64;
+    const int si = (int)(r % st);
+    const int n = (int)(r / st);
+    const int s0 = si * 64, c0 = ci * 64;
     __syncthreads();
-    for (int j = ty; j < 64; j += 4) {   // rows of the tile = channels; tx walks w
-      const int c = c0 + j, w = w0 + tx;
-      tile[j][tx] = (c < C && w < W) ? in[(((int64_t)n * C + c) * H + h) * W + w] : (uint16_t)0;
+    // load: rows of the tile = channels, VW consecutive s per thread
+    constexpr int VPR = 64 / VW;                    // vectors per row
+    for (int v = threadIdx.x; v < 64 * VPR; v += 256) {
+      const int j = v / VPR, q = (v % VPR) * VW;
+      const int c = c0 + j, sx = s0 + q;
+      uint16_t e[VW];
+      if (c < C && sx + VW <= S) {
+        const uint16_t* src = in + ((int64_t)n * C + c) * S + sx;
+        if constexpr (VW == 8) {
+          const uint4 u = __ldg(reinterpret_cast<const uint4*>(src));
+          const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+          for (int k = 0; k < 4; ++k) { e[2 * k] = (uint16_t)(w[k] & 0xFFFFu); e[2 * k + 1] = (uint16_t)(w[k] >> 16); }
+        } else if constexpr (VW == 4) {
+          const uint2 u = __ldg(reinterpret_cast<const uint2*>(src));
+          e[0] = (uint16_t)(u.x & 0xFFFFu); e[1] = (uint16_t)(u.x >> 16); e[2] = (uint16_t)(u.y & 0xFFFFu); e[3] = (uint16_t)(u.y >> 16);
+        } else {
+          e[0] = src[0];
+        }
+      } else {
+#pragma unroll
+        for (int k = 0; k < VW; ++k) e[k] = (c < C && sx + k < S) ? in[((int64_t)n * C + c) * S + sx + k] : (uint16_t)0;
+      }
+#pragma unroll
+      for (int k = 0; k < VW; ++k) tile[j * PITCH + q + k] = e[k];
     }
     __syncthreads();
-    for (int j = ty; j < 64; j += 4) {   // rows = w; tx walks channels
-      const int w = w0 + j, c = c0 + tx;
-      if (w < W && c < Cp) out[(((int64_t)n * H + h) * W + w) * Cp + c] = tile[tx][j];
+    // store: rows = positions, 8 consecutive channels (16 bytes) per thread
+    for (int v = threadIdx.x; v < 64 * 8; v += 256) {
+      const int j = v / 8, q = (v % 8) * 8;
+      const int sx = s0 + j, c = c0 + q;
+      if (sx < S && c < Cp) {
+        uint32_t w[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          w[k] = (uint32_t)tile[(q + 2 * k) * PITCH + j] | ((uint32_t)tile[(q + 2 * k + 1) * PITCH + j] << 16);
+        *reinterpret_cast<uint4*>(out + ((int64_t)n * S + sx) * Cp + c) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
     }
   }
 }
@@ -75,20 +107,29 @@ __global__ void __launch_bounds__(256) cw_transpose_kernel(uint16_t* __restrict_
 __global__ void __launch_bounds__(256) cw_transpose_fold_kernel(uint16_t* __restrict__ out, const uint16_t* __restrict__ in,
                                                                 int W, int H, int C, int Cp, int N, int OW, int kW,
                                                                 int s, int dil, int pad) {
-  const int64_t total = (int64_t)N * H * OW * Cp;
+  // one thread per group of 8 output channels (one 16-byte store)
+  const int groups = Cp / 8;
+  const int64_t total = (int64_t)N * H * OW * groups;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
     int64_t r = i;
-    const int j = (int)(r % Cp); r /= Cp;
+    const int q = (int)(r % groups); r /= groups;
     const int ow = (int)(r % OW); r /= OW;
     const int h = (int)(r % H);
     const int n = (int)(r / H);
-    uint16_t v = 0;
-    if (j < kW * C) {
-      const int tw = j / C, c = j % C;
-      const int w = ow * s + tw * dil - pad;
-      if (w >= 0 && w < W) v = in[(((int64_t)n * C + c) * H + h) * W + w];
+    uint16_t e[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int j = q * 8 + k;
+      uint16_t v = 0;
+      if (j < kW * C) {
+        const int tw = j / C, c = j % C;
+        const int w = ow * s + tw * dil - pad;
+        if (w >= 0 && w < W) v = __ldg(in + (((int64_t)n * C + c) * H + h) * W + w);
+      }
+      e[k] = v;
     }
-    out[i] = v;
+    *reinterpret_cast<uint4*>(out + i * 8) = make_uint4((uint32_t)e[0] | ((uint32_t)e[1] << 16), (uint32_t)e[2] | ((uint32_t)e[3] << 16),
+                                                      (uint32_t)e[4] | ((uint32_t)e[5] << 16), (uint32_t)e[6] | ((uint32_t)e[7] << 16));
   }
 }
 
@@ -569,16 +610,22 @@ void cw_tile_box(int OW, int OH, int NI, int* BW, int* BH, int* BI) {
 }
 
 int32_t cw_transpose(void* out, const void* in, int W, int H, int C, int Cp, int N, cudaStream_t st) {
-  const int64_t blocks = (int64_t)N * H * ((W + 63) / 64) * ((Cp + 63) / 64);
+  const int S = W * H;
+  const int64_t blocks = (int64_t)N * ((S + 63) / 64) * ((Cp + 63) / 64);
   const int64_t cap = (int64_t)sm_count() * 8;
-  cw_transpose_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, st>>>((uint16_t*)out, (const uint16_t*)in, W, H, C, Cp, N);
+  const unsigned grid = (unsigned)(blocks < cap ? blocks : cap);
+  uint16_t* o = (uint16_t*)out;
+  const uint16_t* i = (const uint16_t*)in;
+  if (S % 8 == 0 && aligned_to(in, 16)) cw_transpose_kernel<8><<<grid, 256, 0, st>>>(o, i, S, C, Cp, N);
+  else if (S % 4 == 0 && aligned_to(in, 8)) cw_transpose_kernel<4><<<grid, 256, 0, st>>>(o, i, S, C, Cp, N);
+  else cw_transpose_kernel<1><<<grid, 256, 0, st>>>(o, i, S, C, Cp, N);
   LB2_CHECK_LAUNCH("conv_cw transpose");
   return LB2_OK;
 }
 
 int32_t cw_copy_x(void* xc, const void* x, const ConvGeom& g, const CwCopy& c, cudaStream_t st) {
   if (cw_fold(g)) {
-    cw_transpose_fold_kernel<<<flat_grid((int64_t)c.Cp * c.W * c.H * g.batch), 256, 0, st>>>(
+    cw_transpose_fold_kernel<<<flat_grid((int64_t)(c.Cp / 8) * c.W * c.H * g.batch), 256, 0, st>>>(
         (uint16_t*)xc, (const uint16_t*)x, g.in[0], g.in[1], g.cin, c.Cp, g.batch, g.out[0], g.k[0], g.stride[0], g.dil[0], g.pad_lo[0]);
     LB2_CHECK_LAUNCH("conv_cw folded copy");
     return LB2_OK;

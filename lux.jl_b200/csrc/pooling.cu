@@ -6,8 +6,8 @@
 // vendored): windows are clipped to the input (padding never wins a max), the mean always divides
 // by the full window size, and the max-pool gradient goes to the FIRST element of the window that
 // equals the maximum, scanning kw fastest, then kh, then kd.
-// Bandwidth-bound: one thread per output (forward) / per input (backward, a gather over the windows
-// that cover it, so the sums are formed in a fixed order: deterministic, no atomics).
+// Bandwidth-bound: a CTA walks whole (channel, sample) planes, one thread per output (forward) / per input (backward,
+// a gather over the windows that cover it, so the sums are formed in a fixed order: deterministic, no atomics).
 #include "common.cuh"
 
 namespace lb2 {
@@ -17,35 +17,39 @@ struct PoolGeom {
   int64_t planes;   // channels * batch
 };
 
+// One CTA walks whole (channel, sample) planes, so all index arithmetic inside a plane is 32-bit and the plane's
+// rows stay in L1 / L2 while the windows that share them are evaluated.
 template <typename T, bool MAX>
 __global__ void __launch_bounds__(256) pool_fwd_kernel(T* __restrict__ y, const T* __restrict__ x, const PoolGeom g) {
-  const int64_t out_sp = (int64_t)g.out[0] * g.out[1] * g.out[2];
-  const int64_t in_sp = (int64_t)g.in[0] * g.in[1] * g.in[2];
-  const int64_t total = out_sp * g.planes;
+  const int out_sp = g.out[0] * g.out[1] * g.out[2];
+  const int in_sp = g.in[0] * g.in[1] * g.in[2];
   const float inv_win = 1.f / (float)(g.k[0] * g.k[1] * g.k[2]);
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    int64_t r = i;
-    const int ow = (int)(r % g.out[0]); r /= g.out[0];
-    const int oh = (int)(r % g.out[1]); r /= g.out[1];
-    const int od = (int)(r % g.out[2]);
-    const int64_t plane = r / g.out[2];
+  for (int64_t plane = blockIdx.x; plane < g.planes; plane += gridDim.x) {
     const T* xp = x + plane * in_sp;
-    float acc = MAX ? -INFINITY : 0.f;
-    for (int kd = 0; kd < g.k[2]; ++kd) {
-      const int d = od * g.stride[2] - g.pad[2] + kd * g.dil[2];
-      if (d < 0 || d >= g.in[2]) continue;
-      for (int kh = 0; kh < g.k[1]; ++kh) {
-        const int h = oh * g.stride[1] - g.pad[1] + kh * g.dil[1];
-        if (h < 0 || h >= g.in[1]) continue;
-        for (int kw = 0; kw < g.k[0]; ++kw) {
-          const int w = ow * g.stride[0] - g.pad[0] + kw * g.dil[0];
-          if (w < 0 || w >= g.in[0]) continue;
-          const float v = to_f32(xp[((int64_t)d * g.in[1] + h) * g.in[0] + w]);
-          if (MAX) acc = fmaxf(acc, v); else acc += v;
+    T* yp = y + plane * out_sp;
+    for (int i = threadIdx.x; i < out_sp; i += blockDim.x) {
+      int r = i;
+      const int ow = r % g.out[0]; r /= g.out[0];
+      const int oh = r % g.out[1];
+      const int od = r / g.out[1];
+      float acc = MAX ? -INFINITY : 0.f;
+      for (int kd = 0; kd < g.k[2]; ++kd) {
+        const int d = od * g.stride[2] - g.pad[2] + kd * g.dil[2];
+        if (d < 0 || d >= g.in[2]) continue;
+        for (int kh = 0; kh < g.k[1]; ++kh) {
+          const int h = oh * g.stride[1] - g.pad[1] + kh * g.dil[1];
+          if (h < 0 || h >= g.in[1]) continue;
+          const T* row = xp + (d * g.in[1] + h) * g.in[0];
+          for (int kw = 0; kw < g.k[0]; ++kw) {
+            const int w = ow * g.stride[0] - g.pad[0] + kw * g.dil[0];
+            if (w < 0 || w >= g.in[0]) continue;
+            const float v = to_f32(row[w]);
+            if (MAX) acc = fmaxf(acc, v); else acc += v;
+          }
         }
       }
+      yp[i] = from_f32<T>(MAX ? acc : acc * inv_win);
     }
-    y[i] = from_f32<T>(MAX ? acc : acc * inv_win);
   }
 }
 
@@ -123,47 +127,52 @@ __device__ __forceinline__ bool first_max_is(const T* xp, const PoolGeom& g, int
 template <typename T, bool MAX>
 __global__ void __launch_bounds__(256) pool_bwd_kernel(T* __restrict__ dx, const T* __restrict__ dy, const T* __restrict__ y,
                                                        const T* __restrict__ x, const PoolGeom g) {
-  const int64_t out_sp = (int64_t)g.out[0] * g.out[1] * g.out[2];
-  const int64_t in_sp = (int64_t)g.in[0] * g.in[1] * g.in[2];
-  const int64_t total = in_sp * g.planes;
+  const int out_sp = g.out[0] * g.out[1] * g.out[2];
+  const int in_sp = g.in[0] * g.in[1] * g.in[2];
   const float inv_win = 1.f / (float)(g.k[0] * g.k[1] * g.k[2]);
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    int64_t r = i;
-    const int w = (int)(r % g.in[0]); r /= g.in[0];
-    const int h = (int)(r % g.in[1]); r /= g.in[1];
-    const int d = (int)(r % g.in[2]);
-    const int64_t plane = r / g.in[2];
-    const T* xp = x + plane * in_sp;
-    const T* yp = y + plane * out_sp;
+  for (int64_t plane = blockIdx.x; plane < g.planes; plane += gridDim.x) {
+    const T* xp = MAX ? x + plane * in_sp : nullptr;
+    const T* yp = MAX ? y + plane * out_sp : nullptr;
     const T* dyp = dy + plane * out_sp;
-    float acc = 0.f;
-    // outputs whose window holds this input: o*stride - pad + kk*dil == coordinate with kk in [0, k), i.e.
-    // o in [ceil((coordinate + pad - (k-1)*dil) / stride), floor((coordinate + pad) / stride)], dil | remainder
-    int lo[3], hi[3];
-    const int coord[3] = {w, h, d};
+    T* dxp = dx + plane * in_sp;
+    for (int i = threadIdx.x; i < in_sp; i += blockDim.x) {
+      int r = i;
+      const int w = r % g.in[0]; r /= g.in[0];
+      const int h = r % g.in[1];
+      const int d = r / g.in[1];
+      const float xv = MAX ? to_f32(xp[i]) : 0.f;
+      float acc = 0.f;
+      // outputs whose window holds this input: o*stride - pad + kk*dil == coordinate with kk in [0, k), i.e.
+      // o in [ceil((coordinate + pad - (k-1)*dil) / stride), floor((coordinate + pad) / stride)], dil | remainder
+      int lo[3], hi[3];
+      const int coord[3] = {w, h, d};
 #pragma unroll
-    for (int a = 0; a < 3; ++a) {
-      const int top = coord[a] + g.pad[a];
-      const int bot = top - (g.k[a] - 1) * g.dil[a];
-      lo[a] = bot <= 0 ? 0 : (bot + g.stride[a] - 1) / g.stride[a];
-      hi[a] = min(g.out[a] - 1, top / g.stride[a]);
-    }
-    for (int od = lo[2]; od <= hi[2]; ++od) {
-      if ((d + g.pad[2] - od * g.stride[2]) % g.dil[2] != 0) continue;
-      for (int oh = lo[1]; oh <= hi[1]; ++oh) {
-        if ((h + g.pad[1] - oh * g.stride[1]) % g.dil[1] != 0) continue;
-        for (int ow = lo[0]; ow <= hi[0]; ++ow) {
-          if ((w + g.pad[0] - ow * g.stride[0]) % g.dil[0] != 0) continue;
-          const int64_t o = ((int64_t)od * g.out[1] + oh) * g.out[0] + ow;
-          if (MAX) {
-            if (first_max_is(xp, g, ow, oh, od, to_f32(yp[o]), w, h, d)) acc += to_f32(dyp[o]);
-          } else {
-            acc += to_f32(dyp[o]) * inv_win;
+      for (int a = 0; a < 3; ++a) {
+        const int top = coord[a] + g.pad[a];
+        const int bot = top - (g.k[a] - 1) * g.dil[a];
+        lo[a] = bot <= 0 ? 0 : (bot + g.stride[a] - 1) / g.stride[a];
+        hi[a] = min(g.out[a] - 1, top / g.stride[a]);
+      }
+      for (int od = lo[2]; od <= hi[2]; ++od) {
+        if ((d + g.pad[2] - od * g.stride[2]) % g.dil[2] != 0) continue;
+        for (int oh = lo[1]; oh <= hi[1]; ++oh) {
+          if ((h + g.pad[1] - oh * g.stride[1]) % g.dil[1] != 0) continue;
+          for (int ow = lo[0]; ow <= hi[0]; ++ow) {
+            if ((w + g.pad[0] - ow * g.stride[0]) % g.dil[0] != 0) continue;
+            const int o = (od * g.out[1] + oh) * g.out[0] + ow;
+            if (MAX) {
+              // only an element equal to the window's maximum can receive its gradient; the scan for an earlier
+              // equal element (the tie rule) runs for those alone
+              const float ym = to_f32(yp[o]);
+              if (xv == ym && first_max_is(xp, g, ow, oh, od, ym, w, h, d)) acc += to_f32(dyp[o]);
+            } else {
+              acc += to_f32(dyp[o]) * inv_win;
+            }
           }
         }
       }
+      dxp[i] = from_f32<T>(acc);
     }
-    dx[i] = from_f32<T>(acc);
   }
 }
 
@@ -185,7 +194,13 @@ static int32_t make_pool_geom(const lb2_pool_desc* d, PoolGeom* g) {
     g->out[i] = span < 0 ? 0 : span / g->stride[i] + 1;
   }
   g->planes = (int64_t)d->channels * d->batch;
+  LB2_REQUIRE((int64_t)g->in[0] * g->in[1] * g->in[2] < ((int64_t)1 << 31), LB2_BAD_SHAPE, "a (channel, sample) plane must hold fewer than 2^31 elements");
   return LB2_OK;
+}
+
+static unsigned plane_grid(int64_t planes) {
+  const int64_t cap = (int64_t)sm_count() * 16;
+  return (unsigned)(planes < 1 ? 1 : (planes > cap ? cap : planes));
 }
 
 static unsigned pool_grid(int64_t total) {
@@ -231,8 +246,8 @@ int32_t lb2_pool_fwd(void* y, const void* x, const lb2_pool_desc* d, int32_t kin
     return LB2_OK;
   }
   LB2_DISPATCH_DTYPE(dtype, {
-    if (kind == LB2_POOL_MAX) pool_fwd_kernel<T, true><<<pool_grid(total), 256, 0, st>>>((T*)y, (const T*)x, g);
-    else pool_fwd_kernel<T, false><<<pool_grid(total), 256, 0, st>>>((T*)y, (const T*)x, g);
+    if (kind == LB2_POOL_MAX) pool_fwd_kernel<T, true><<<plane_grid(g.planes), 256, 0, st>>>((T*)y, (const T*)x, g);
+    else pool_fwd_kernel<T, false><<<plane_grid(g.planes), 256, 0, st>>>((T*)y, (const T*)x, g);
   });
   LB2_CHECK_LAUNCH("pool_fwd");
   return LB2_OK;
@@ -271,8 +286,8 @@ int32_t lb2_pool_bwd(void* dx, const void* dy, const void* y, const void* x, con
     return LB2_OK;
   }
   LB2_DISPATCH_DTYPE(dtype, {
-    if (kind == LB2_POOL_MAX) pool_bwd_kernel<T, true><<<pool_grid(total), 256, 0, st>>>((T*)dx, (const T*)dy, (const T*)y, (const T*)x, g);
-    else pool_bwd_kernel<T, false><<<pool_grid(total), 256, 0, st>>>((T*)dx, (const T*)dy, nullptr, nullptr, g);
+    if (kind == LB2_POOL_MAX) pool_bwd_kernel<T, true><<<plane_grid(g.planes), 256, 0, st>>>((T*)dx, (const T*)dy, (const T*)y, (const T*)x, g);
+    else pool_bwd_kernel<T, false><<<plane_grid(g.planes), 256, 0, st>>>((T*)dx, (const T*)dy, nullptr, nullptr, g);
   });
   LB2_CHECK_LAUNCH("pool_bwd");
   return LB2_OK;

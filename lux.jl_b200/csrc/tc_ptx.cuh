@@ -42,7 +42,8 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
 // Bounded wait: gives up after kWaitLimitNs of wall time (checked every 256 polls), records `code`
 // in the status word and returns false.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned int* status, unsigned int code) {
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, unsigned int* status, unsigned int code,
+                                                uint64_t limit_ns) {
   uint32_t spins = 0;
   uint64_t t0 = 0;
   while (!mbar_try_wait(bar, parity)) {
@@ -50,13 +51,16 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsign
       const uint64_t now = globaltimer_ns();
       if (t0 == 0) {
         t0 = now;
-      } else if (now - t0 > kWaitLimitNs) {
+      } else if (now - t0 > limit_ns) {
         atomicOr(status, code);
         return false;
       }
     }
   }
   return true;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned int* status, unsigned int code) {
+  return mbar_wait_limit(bar, parity, status, code, kWaitLimitNs);
 }
 
 // Warp-collective wait: only lane 0 polls the barrier (32x fewer shared-memory requests than a whole

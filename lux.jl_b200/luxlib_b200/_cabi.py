@@ -58,6 +58,7 @@ PROTOTYPES = {
     "lb2_status_string": (C.c_char_p, [_i32]),
     "lb2_last_error_string": (C.c_char_p, []),
     "lb2_poll_device_status": (_i32, [_p]),
+    "lb2_selftest_bounded_wait": (_i32, [C.c_uint64, _p]),
     "lb2_act_fwd": (_i32, [_p, _p, _i64, _i32, _i32, _p]),
     "lb2_act_bwd": (_i32, [_p, _p, _p, _p, _i64, _i32, _i32, _p]),
     "lb2_bias_act_fwd": (_i32, [_p, _p, _p, _i64, _i64, _i64, _i32, _i32, _p]),

@@ -151,3 +151,15 @@ def test_host_mirror_argument_errors_need_no_gpu():
     a = np.arange(24, dtype=np.float32).reshape(2, 3, 4)
     j = L.from_numpy(a, "cpu")
     assert L.is_colmajor(j) and (L.to_numpy(j) == a).all()
+
+
+def test_the_library_reads_no_environment_variable():
+    # a drop-in library must not change its arithmetic on an inherited environment: every switch is an argument
+    import glob
+    csrc = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "lux.jl_b200", "csrc")
+    files = sorted(glob.glob(os.path.join(csrc, "*.cu")) + glob.glob(os.path.join(csrc, "*.cuh")))
+    assert files
+    for f in files:
+        with open(f) as fh:
+            text = fh.read()
+        assert "getenv" not in text, f

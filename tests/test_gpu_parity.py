@@ -778,3 +778,26 @@ def test_residual_add_activation(dt, act):
     ref = O.grad_activation(delta, prep(z_ref, dt), act, s.astype(np.float32))
     check(dx, ref, dt, "dx")
     check(dy, ref, dt, "dy")
+
+
+# ------------------------------------------------------------------------------------------
+# bounded device-side waits
+# ------------------------------------------------------------------------------------------
+def test_an_expired_device_side_wait_is_reported_and_leaves_the_device_usable():
+    # Every mbarrier wait of the tensor-core kernels goes through one bounded wait routine. The self-test kernel runs
+    # that routine on a barrier nothing arrives at, with a 1 ms limit: it must return (not hang), the status poll
+    # must report the timeout exactly once, and the next operation must work.
+    lib = L._cabi.load()
+    assert lib.lb2_poll_device_status(None) == 0
+    t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    assert lib.lb2_selftest_bounded_wait(1_000_000, torch.cuda.current_stream().cuda_stream) == 0
+    t1.record()
+    torch.cuda.synchronize()
+    assert 0.5 <= t0.elapsed_time(t1) <= 50.0          # the wait ran for about its limit, then gave up
+    assert lib.lb2_poll_device_status(None) == L._cabi.TIMEOUT
+    assert b"0x40000000" in lib.lb2_last_error_string()
+    assert lib.lb2_poll_device_status(None) == 0        # the poll cleared the word
+    assert lib.lb2_selftest_bounded_wait(10, None) == L._cabi.BAD_ARG      # limits outside 1 us .. 100 ms are refused
+    x = np.arange(12, dtype=np.float32).reshape(3, 4)
+    check(L.fast_activation("relu", dev(x - 5, "f32")), np.maximum(x - 5, 0), "f32", "relu after the timeout")
