@@ -614,8 +614,8 @@ def measure_secondary(wl: str, dtype: str, steps: int, warm: int, quiet: bool = 
         def step():
             h, pb1 = L.rrule_fused_dense("relu", W1, x, b1)
             y, pb2 = L.rrule_fused_dense("identity", W2, h, b2)
-            d = (y - tgt) * (2.0 / y.numel())
-            dW2, dh, db2 = pb2(d)
+            loss, pl = L.rrule_mse_loss(y, tgt)
+            dW2, dh, db2 = pb2(pl())
             return pb1(dh)
         numel, name = 0, "MLP Dense(784->256, relu) -> Dense(256->10), batch 128, Float32: forward + pullback of MSE"
     else:
@@ -741,10 +741,8 @@ def build_resnet18(L, torch, device, rank, batch, dtype):
         pooled, ppool = L.rrule_meanpool(h, L.PoolDims.global_(h))          # (1, 1, 512, B)
         feat = pooled.reshape(512, batch)                                    # same bytes, Julia shape (512, B)
         y, pdense = L.rrule_fused_dense("identity", params[iWd], feat, params[ibd])
-        diff = y - target                                                    # loss glue (1000 x B)
-        loss = (diff.float() ** 2).mean()
-        dy = diff * (2.0 / diff.numel())
-        grads[iWd], dfeat, grads[ibd] = pdense(dy)
+        loss, ploss = L.rrule_mse_loss(y, target)
+        grads[iWd], dfeat, grads[ibd] = pdense(ploss())
         dh = ppool(dfeat.reshape(1, 1, 512, batch))
         for blk, pc1, pn1, pc2, pn2, pcp, pnp, padd in reversed(tape):
             da, dskip = padd(dh)

@@ -258,6 +258,14 @@ LB2_API int32_t lb2_pool_fwd(void* y, const void* x, const lb2_pool_desc* desc, 
 LB2_API int32_t lb2_pool_bwd(void* dx, const void* dy, const void* y, const void* x, const lb2_pool_desc* desc,
                           int32_t kind, int32_t dtype, void* stream);
 
+/* ---- loss ---------------------------------------------------------------------------------------- */
+/* MSELoss() (src/helpers/losses.jl:659: GenericLossFunction(l2_distance_loss; agg = mean), derivative 2(x - y) at
+ * :121-125) and its gradient in one pass over n elements: *loss = mean((yhat - y)^2) (fp32, device scalar),
+ * dyhat = 2 (yhat - y) / n (may be NULL, may alias yhat). */
+LB2_API size_t lb2_mse_loss_workspace_bytes(int64_t n);
+LB2_API int32_t lb2_mse_loss(float* loss, void* dyhat, const void* yhat, const void* y, int64_t n, int32_t dtype,
+                             void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---- optimiser step for a bucket of leaves ------------------------------------------------ */
 /* The leaf loop that Optimisers.update! runs under DistributedOptimizer
  * (src/distributed/public_api.jl:270-278: allreduce!(backend, grad, avg) then apply! of the wrapped rule;

@@ -176,6 +176,99 @@ __global__ void __launch_bounds__(256) pool_bwd_kernel(T* __restrict__ dx, const
   }
 }
 
+// ---- 2-D windows without dilation (the pooling layers of a conv net): no runtime divisions per element ----------
+// Threads are laid out as 128 columns x 2 rows over a plane; STRIDE is a compile-time constant for the common
+// strides (0 = read it from the geometry), so the window ranges are shifts and compares.
+template <int STRIDE> __device__ __forceinline__ int div_stride(int v, int s) {   // floor(v / stride), v >= 0
+  if constexpr (STRIDE == 1) return v;
+  else if constexpr (STRIDE == 2) return v >> 1;
+  else return v / s;
+}
+
+template <typename T, bool MAX, int STRIDE>
+__global__ void __launch_bounds__(256) pool2d_fwd_kernel(T* __restrict__ y, const T* __restrict__ x, const PoolGeom g) {
+  const int W = g.in[0], H = g.in[1], OW = g.out[0], OH = g.out[1];
+  const int sw = STRIDE ? STRIDE : g.stride[0], sh = STRIDE ? STRIDE : g.stride[1];
+  const int tx = threadIdx.x & 127, ty = threadIdx.x >> 7;
+  const float inv_win = 1.f / (float)(g.k[0] * g.k[1]);
+  for (int64_t plane = blockIdx.x; plane < g.planes; plane += gridDim.x) {
+    const T* xp = x + plane * (int64_t)(W * H);
+    T* yp = y + plane * (int64_t)(OW * OH);
+    for (int oh = ty; oh < OH; oh += 2) {
+      const int h0 = oh * sh - g.pad[1];
+      const int kh_lo = h0 < 0 ? -h0 : 0, kh_hi = min(g.k[1], H - h0);
+      for (int ow = tx; ow < OW; ow += 128) {
+        const int w0 = ow * sw - g.pad[0];
+        const int kw_lo = w0 < 0 ? -w0 : 0, kw_hi = min(g.k[0], W - w0);
+        float acc = MAX ? -INFINITY : 0.f;
+        for (int kh = kh_lo; kh < kh_hi; ++kh) {
+          const T* row = xp + (h0 + kh) * W + w0;
+          for (int kw = kw_lo; kw < kw_hi; ++kw) {
+            const float v = to_f32(row[kw]);
+            if (MAX) acc = fmaxf(acc, v); else acc += v;
+          }
+        }
+        yp[oh * OW + ow] = from_f32<T>(MAX ? acc : acc * inv_win);
+      }
+    }
+  }
+}
+
+template <typename T, bool MAX, int STRIDE>
+__global__ void __launch_bounds__(256) pool2d_bwd_kernel(T* __restrict__ dx, const T* __restrict__ dy, const T* __restrict__ y,
+                                                         const T* __restrict__ x, const PoolGeom g) {
+  const int W = g.in[0], H = g.in[1], OW = g.out[0], OH = g.out[1], kW = g.k[0], kH = g.k[1];
+  const int sw = STRIDE ? STRIDE : g.stride[0], sh = STRIDE ? STRIDE : g.stride[1];
+  const int tx = threadIdx.x & 127, ty = threadIdx.x >> 7;
+  const float inv_win = 1.f / (float)(kW * kH);
+  for (int64_t plane = blockIdx.x; plane < g.planes; plane += gridDim.x) {
+    const T* xp = MAX ? x + plane * (int64_t)(W * H) : nullptr;
+    const T* yp = MAX ? y + plane * (int64_t)(OW * OH) : nullptr;
+    const T* dyp = dy + plane * (int64_t)(OW * OH);
+    T* dxp = dx + plane * (int64_t)(W * H);
+    for (int h = ty; h < H; h += 2) {
+      // outputs whose window holds row h: oh*sh - pad <= h <= oh*sh - pad + kH - 1
+      const int top = h + g.pad[1], bot = top - (kH - 1);
+      const int oh_lo = bot <= 0 ? 0 : div_stride<STRIDE>(bot + sh - 1, sh);
+      const int oh_hi = min(OH - 1, div_stride<STRIDE>(top, sh));
+      for (int w = tx; w < W; w += 128) {
+        const int topw = w + g.pad[0], botw = topw - (kW - 1);
+        const int ow_lo = botw <= 0 ? 0 : div_stride<STRIDE>(botw + sw - 1, sw);
+        const int ow_hi = min(OW - 1, div_stride<STRIDE>(topw, sw));
+        const float xv = MAX ? to_f32(xp[h * W + w]) : 0.f;
+        float acc = 0.f;
+        for (int oh = oh_lo; oh <= oh_hi; ++oh) {
+          for (int ow = ow_lo; ow <= ow_hi; ++ow) {
+            const int o = oh * OW + ow;
+            if (MAX) {
+              const float ym = to_f32(yp[o]);
+              if (xv == ym) {
+                // the gradient goes to the FIRST element of the window equal to its maximum (kw fastest, then kh)
+                const int h0 = oh * sh - g.pad[1], w0 = ow * sw - g.pad[0];
+                bool first = true;
+                for (int kh = max(0, -h0); first && h0 + kh <= h; ++kh) {
+                  const int kw_end = (h0 + kh == h) ? (w - w0) : min(kW, W - w0);
+                  for (int kw = max(0, -w0); kw < kw_end; ++kw)
+                    if (to_f32(xp[(h0 + kh) * W + w0 + kw]) == ym) { first = false; break; }
+                }
+                if (first) acc += to_f32(dyp[o]);
+              }
+            } else {
+              acc += to_f32(dyp[o]) * inv_win;
+            }
+          }
+        }
+        dxp[h * W + w] = from_f32<T>(acc);
+      }
+    }
+  }
+}
+
+static bool pool_is_2d_plain(const PoolGeom& g) {
+  return g.in[2] == 1 && g.k[2] == 1 && g.out[2] == 1 && g.dil[0] == 1 && g.dil[1] == 1 && g.pad[2] == 0 &&
+         (int64_t)g.in[0] * g.in[1] < ((int64_t)1 << 30);
+}
+
 static int32_t make_pool_geom(const lb2_pool_desc* d, PoolGeom* g) {
   LB2_REQUIRE(d != nullptr, LB2_BAD_ARG, "pool descriptor is null");
   LB2_REQUIRE(d->ndim >= 1 && d->ndim <= 3, LB2_BAD_SHAPE, "spatial rank %d not in 1..3", (int)d->ndim);
@@ -245,6 +338,22 @@ int32_t lb2_pool_fwd(void* y, const void* x, const lb2_pool_desc* d, int32_t kin
     LB2_CHECK_LAUNCH("pool_global_fwd");
     return LB2_OK;
   }
+  if (pool_is_2d_plain(g)) {
+    const bool same = g.stride[0] == g.stride[1];
+    LB2_DISPATCH_DTYPE(dtype, {
+      if (kind == LB2_POOL_MAX) {
+        if (same && g.stride[0] == 1) pool2d_fwd_kernel<T, true, 1><<<plane_grid(g.planes), 256, 0, st>>>((T*)y, (const T*)x, g);
+        else if (same && g.stride[0] == 2) pool2d_fwd_kernel<T, true, 2><<<plane_grid(g.planes), 256, 0, st>>>((T*)y, (const T*)x, g);
+        else pool2d_fwd_kernel<T, true, 0><<<plane_grid(g.planes), 256, 0, st>>>((T*)y, (const T*)x, g);
+      } else {
+        if (same && g.stride[0] == 1) pool2d_fwd_kernel<T, false, 1><<<plane_grid(g.planes), 256, 0, st>>>((T*)y, (const T*)x, g);
+        else if (same && g.stride[0] == 2) pool2d_fwd_kernel<T, false, 2><<<plane_grid(g.planes), 256, 0, st>>>((T*)y, (const T*)x, g);
+        else pool2d_fwd_kernel<T, false, 0><<<plane_grid(g.planes), 256, 0, st>>>((T*)y, (const T*)x, g);
+      }
+    });
+    LB2_CHECK_LAUNCH("pool2d_fwd");
+    return LB2_OK;
+  }
   LB2_DISPATCH_DTYPE(dtype, {
     if (kind == LB2_POOL_MAX) pool_fwd_kernel<T, true><<<plane_grid(g.planes), 256, 0, st>>>((T*)y, (const T*)x, g);
     else pool_fwd_kernel<T, false><<<plane_grid(g.planes), 256, 0, st>>>((T*)y, (const T*)x, g);
@@ -283,6 +392,22 @@ int32_t lb2_pool_bwd(void* dx, const void* dy, const void* y, const void* x, con
       else pool_global_bwd_kernel<T, false><<<pool_grid(g.planes * 32), 256, 0, st>>>((T*)dx, (const T*)dy, nullptr, nullptr, S, g.planes);
     });
     LB2_CHECK_LAUNCH("pool_global_bwd");
+    return LB2_OK;
+  }
+  if (pool_is_2d_plain(g)) {
+    const bool same = g.stride[0] == g.stride[1];
+    LB2_DISPATCH_DTYPE(dtype, {
+      if (kind == LB2_POOL_MAX) {
+        if (same && g.stride[0] == 1) pool2d_bwd_kernel<T, true, 1><<<plane_grid(g.planes), 256, 0, st>>>((T*)dx, (const T*)dy, (const T*)y, (const T*)x, g);
+        else if (same && g.stride[0] == 2) pool2d_bwd_kernel<T, true, 2><<<plane_grid(g.planes), 256, 0, st>>>((T*)dx, (const T*)dy, (const T*)y, (const T*)x, g);
+        else pool2d_bwd_kernel<T, true, 0><<<plane_grid(g.planes), 256, 0, st>>>((T*)dx, (const T*)dy, (const T*)y, (const T*)x, g);
+      } else {
+        if (same && g.stride[0] == 1) pool2d_bwd_kernel<T, false, 1><<<plane_grid(g.planes), 256, 0, st>>>((T*)dx, (const T*)dy, nullptr, nullptr, g);
+        else if (same && g.stride[0] == 2) pool2d_bwd_kernel<T, false, 2><<<plane_grid(g.planes), 256, 0, st>>>((T*)dx, (const T*)dy, nullptr, nullptr, g);
+        else pool2d_bwd_kernel<T, false, 0><<<plane_grid(g.planes), 256, 0, st>>>((T*)dx, (const T*)dy, nullptr, nullptr, g);
+      }
+    });
+    LB2_CHECK_LAUNCH("pool2d_bwd");
     return LB2_OK;
   }
   LB2_DISPATCH_DTYPE(dtype, {

@@ -87,6 +87,8 @@ PROTOTYPES = {
     "lb2_pool_output_size": (_i32, [C.POINTER(PoolDesc), C.POINTER(C.c_int32)]),
     "lb2_pool_fwd": (_i32, [_p, _p, C.POINTER(PoolDesc), _i32, _i32, _p]),
     "lb2_pool_bwd": (_i32, [_p, _p, _p, _p, C.POINTER(PoolDesc), _i32, _i32, _p]),
+    "lb2_mse_loss_workspace_bytes": (_sz, [_i64]),
+    "lb2_mse_loss": (_i32, [_fp, _p, _p, _p, _i64, _i32, _p, _sz, _p]),
     "lb2_optimizer_step": (_i32, [C.POINTER(OptLeaf), _i32, _i32, _dbl, _dbl, _dbl, _dbl, _i64, _dbl, _i32, _p]),
     "lb2_instancenorm_update_stats": (_i32, [_p, _p, _p, _p, _fp, _fp, _i64, _i64, _i64, _dbl, _dbl, _i32, _p]),
     "lb2_layernorm_fwd": (_i32, [_p, _fp, _fp, _p, _p, _p, _i64, _i64, _dbl, _i32, _i32, _p]),

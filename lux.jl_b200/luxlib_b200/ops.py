@@ -759,3 +759,32 @@ def rrule_layernorm(x, scale=None, bias=None, act: str = "identity", dims=None, 
         return dx, dg, db
 
     return y, pullback
+
+
+# --------------------------------------------------------------------------------------------
+# loss
+# --------------------------------------------------------------------------------------------
+def rrule_mse_loss(yhat, y):
+    """MSELoss()(ŷ, y) = mean(abs2.(ŷ .- y)) (src/helpers/losses.jl:659, l2_distance_loss and its derivative at
+    :121-125) with its pullback: returns (loss, Δ -> ∂ŷ). Loss and gradient come from ONE pass; the loss is a
+    Float32 device scalar (no synchronisation)."""
+    lib = _cabi.load()
+    if tuple(yhat.shape) != tuple(y.shape):
+        raise DimensionMismatch("ŷ and y must have the same shape")
+    yhat, y = _promote(yhat, y)
+    Yh, Y = as_colmajor(yhat), as_colmajor(y)
+    n = Yh.numel()
+    loss = torch.empty(1, dtype=torch.float32, device=Yh.device)
+    d = jl_empty(Yh.shape, Yh.dtype, Yh.device)
+    _, wsp, wsn = _ws(lib.lb2_mse_loss_workspace_bytes(n), Yh.device)
+    _cabi.check(lib.lb2_mse_loss(ptr(loss), ptr(d), ptr(Yh), ptr(Y), n, dtype_code(Yh.dtype), wsp, wsn, current_stream(Yh.device)))
+
+    def pullback(delta=None):
+        return d if delta is None else d * delta
+
+    return loss, pullback
+
+
+def mse_loss(yhat, y):
+    """MSELoss()(ŷ, y) as a Float32 device scalar."""
+    return rrule_mse_loss(yhat, y)[0]

@@ -824,3 +824,20 @@ def rel_l2(a: np.ndarray, b: np.ndarray) -> float:
     denom = np.linalg.norm(b.ravel())
     num = np.linalg.norm((a - b).ravel())
     return float(num / denom) if denom > 0 else float(num)
+
+
+# --------------------------------------------------------------------------- #
+# loss
+# --------------------------------------------------------------------------- #
+def mse_loss_rrule(yhat, y):
+    """MSELoss() — src/helpers/losses.jl:659: GenericLossFunction(l2_distance_loss; agg = mean) with
+    l2_distance_loss(x, y) = abs2(x - y) and derivative 2 (x - y) (src/helpers/losses.jl:121-125).
+    Returns (loss, Δ -> ∂ŷ)."""
+    d = yhat - y
+    n = d.size
+    loss = (d * d).sum(dtype=d.dtype) / d.dtype.type(n) if n else np.float32("nan")
+
+    def pullback(delta=1.0):
+        return (2.0 * d / n * delta).astype(d.dtype)
+
+    return loss, pullback

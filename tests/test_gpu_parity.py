@@ -801,3 +801,17 @@ def test_an_expired_device_side_wait_is_reported_and_leaves_the_device_usable():
     assert lib.lb2_selftest_bounded_wait(10, None) == L._cabi.BAD_ARG      # limits outside 1 us .. 100 ms are refused
     x = np.arange(12, dtype=np.float32).reshape(3, 4)
     check(L.fast_activation("relu", dev(x - 5, "f32")), np.maximum(x - 5, 0), "f32", "relu after the timeout")
+
+
+# ------------------------------------------------------------------------------------------
+# loss
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("shape", [(10, 128), (1000, 256), (7,), (3, 5, 2)])
+def test_mse_loss_and_gradient(dt, shape):
+    rng = np.random.default_rng(41)
+    yh, y = prep(rng.standard_normal(shape), dt), prep(rng.standard_normal(shape), dt)
+    l_ref, pb_ref = O.mse_loss_rrule(yh.astype(np.float64), y.astype(np.float64))
+    l, pb = L.rrule_mse_loss(dev(yh, dt), dev(y, dt))
+    check(l, np.array([l_ref]), "f32", "loss")          # the loss is a Float32 scalar for either storage type
+    check(pb(), pb_ref(), dt, "dyhat")

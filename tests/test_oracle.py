@@ -332,3 +332,18 @@ def test_gelu_variants_match_torch():
     np.testing.assert_allclose(O.act_fn("gelu", x, "tanh"), F.gelu(torch.from_numpy(x), approximate="tanh").numpy(), atol=1e-12)
     np.testing.assert_allclose(O.act_fn("gelu", x, "erf"), F.gelu(torch.from_numpy(x)).numpy(), atol=1e-12)
     np.testing.assert_allclose(O.act_fn("swish", x), F.silu(torch.from_numpy(x)).numpy(), atol=1e-12)
+
+
+def test_mse_loss_against_torch_and_the_reference_docstring_example():
+    # src/helpers/losses.jl:650-656: loss([1.1, 1.9, 3.1], 1:3) ≈ 0.01
+    l, _ = O.mse_loss_rrule(np.array([1.1, 1.9, 3.1]), np.array([1.0, 2.0, 3.0]))
+    assert abs(l - 0.01) < 1e-12
+    import torch
+    rng = np.random.default_rng(40)
+    a, b = rng.standard_normal((10, 7)), rng.standard_normal((10, 7))
+    ta = torch.tensor(a, requires_grad=True)
+    lt = torch.nn.functional.mse_loss(ta, torch.tensor(b))
+    lt.backward()
+    l, pb = O.mse_loss_rrule(a, b)
+    np.testing.assert_allclose(l, lt.item(), rtol=1e-12)
+    np.testing.assert_allclose(pb(), ta.grad.numpy(), rtol=1e-12)
