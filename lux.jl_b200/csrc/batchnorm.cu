@@ -138,19 +138,36 @@ __global__ void __launch_bounds__(256) bn_reduce_kernel(float* __restrict__ part
       }
     }
   } else {
-    const int64_t items = (b_end - b_begin) * sv;
-    for (int64_t it = threadIdx.x; it < items; it += blockDim.x) {
-      const int64_t b = b_begin + it / sv;
-      const int64_t e = (b * C + c) * S + (it % sv) * V;
-      const float xv = to_f32(x[e]);
+    // Planes whose length or alignment rules out 16-byte vectors (14 x 14 and 7 x 7 feature maps): a warp walks one
+    // (sample, channel) plane at a time, two 2-byte elements per load where the plane allows it. No per-element
+    // index arithmetic.
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int Si = (int)S;
+    const bool pairs = sizeof(T) == 2 && (Si & 1) == 0 && aligned_to_dev(x, 4) && (MODE == 0 || aligned_to_dev(dy, 4));
+    auto one = [&](float xv, float gvv) {
       if constexpr (MODE == 0) {
-        float d = xv - K; a += d; q += d * d;
+        const float d = xv - K; a += d; q = fmaf(d, d, q);
       } else {
-        float d = to_f32(dy[e]);
+        float d = gvv;
         const float xm = xv - mean;
         if constexpr (ACT != LB2_ACT_IDENTITY) d *= act_grad_pre_any<ACT, FAST>(act_rt, fmaf(xm, gp, bp));
         a += d;
-        q += d * xm;
+        q = fmaf(d, xm, q);
+      }
+    };
+    for (int64_t b = b_begin + warp; b < b_end; b += 8) {
+      const T* xr = x + (b * C + c) * S;
+      const T* gr = MODE == 1 ? dy + (b * C + c) * S : nullptr;
+      if (pairs) {
+        for (int i = lane * 2; i < Si; i += 64) {
+          const uint32_t ux = *reinterpret_cast<const uint32_t*>(xr + i);
+          uint32_t ug = 0;
+          if constexpr (MODE == 1) ug = *reinterpret_cast<const uint32_t*>(gr + i);
+          one(__uint_as_float(ux << 16), __uint_as_float(ug << 16));
+          one(__uint_as_float(ux & 0xFFFF0000u), __uint_as_float(ug & 0xFFFF0000u));
+        }
+      } else {
+        for (int i = lane; i < Si; i += 32) one(to_f32(xr[i]), MODE == 1 ? to_f32(gr[i]) : 0.f);
       }
     }
   }
@@ -373,20 +390,48 @@ __global__ void __launch_bounds__(256) bn_apply_kernel(T* __restrict__ out, cons
       }
     }
   } else {
-    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-    for (int64_t i0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i0 < n; i0 += stride) {
-      const int64_t e = n - 1 - i0;
-      const int64_t c = (e / S) % C;
+    // planes that cannot take 16-byte vectors: a warp per (sample, channel) plane, last plane first, pairs of
+    // 2-byte elements where the plane allows it
+    const int lane = threadIdx.x & 31;
+    const int Si = (int)S;
+    const int64_t planes = n / S;
+    const int64_t wstride = (int64_t)gridDim.x * (blockDim.x >> 5);
+    const bool pairs = sizeof(T) == 2 && (Si & 1) == 0 && aligned_to_dev(x, 4) && aligned_to_dev(out, 4) && (MODE != 2 || aligned_to_dev(dy, 4));
+    for (int64_t p0 = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); p0 < planes; p0 += wstride) {
+      const int64_t plane = planes - 1 - p0;
+      const int64_t c = plane % C;
       float gp, bp;
       bn_channel_coefs<T, MODE, ACT, AFFINE>(c, coef, gamma, beta, rmean, rvar, mean_in, inv_in, eps, gp, bp);
+      float c0 = 0.f, c1 = 0.f, c2 = 0.f, mu = 0.f;
       if constexpr (MODE == 2) {
-        const float c0 = coef[c * 4], c1 = coef[c * 4 + 1], c2 = coef[c * 4 + 2];
-        const float xv = to_f32(x[e]);
-        float d = to_f32(dy[e]);
-        if constexpr (ACT != LB2_ACT_IDENTITY) d *= act_grad_pre_any<ACT, FAST>(act_rt, fmaf(xv - mean_in[c], gp, bp));
-        out[e] = from_f32<T>(fmaf(c0, d, fmaf(c1, xv, c2)));
+        c0 = coef[c * 4]; c1 = coef[c * 4 + 1]; c2 = coef[c * 4 + 2];
+        if constexpr (ACT != LB2_ACT_IDENTITY) mu = mean_in[c];
+      }
+      const T* xr = x + plane * S;
+      const T* gr = MODE == 2 ? dy + plane * S : nullptr;
+      T* outr = out + plane * S;
+      auto one = [&](float xv, float gvv) -> float {
+        if constexpr (MODE == 2) {
+          float d = gvv;
+          if constexpr (ACT != LB2_ACT_IDENTITY) d *= act_grad_pre_any<ACT, FAST>(act_rt, fmaf(xv - mu, gp, bp));
+          return fmaf(c0, d, fmaf(c1, xv, c2));
+        } else {
+          return act_apply_any<ACT, FAST>(act_rt, fmaf(xv, gp, bp));
+        }
+      };
+      if (pairs) {
+        for (int i = lane * 2; i < Si; i += 64) {
+          const uint32_t ux = *reinterpret_cast<const uint32_t*>(xr + i);
+          uint32_t ug = 0;
+          if constexpr (MODE == 2) ug = *reinterpret_cast<const uint32_t*>(gr + i);
+          const float r0 = one(__uint_as_float(ux << 16), __uint_as_float(ug << 16));
+          const float r1 = one(__uint_as_float(ux & 0xFFFF0000u), __uint_as_float(ug & 0xFFFF0000u));
+          uint32_t u;
+          asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(u) : "f"(r1), "f"(r0));
+          *reinterpret_cast<uint32_t*>(outr + i) = u;
+        }
       } else {
-        out[e] = from_f32<T>(act_apply_any<ACT, FAST>(act_rt, fmaf(to_f32(x[e]), gp, bp)));
+        for (int i = lane; i < Si; i += 32) outr[i] = from_f32<T>(one(to_f32(xr[i]), MODE == 2 ? to_f32(gr[i]) : 0.f));
       }
     }
   }
@@ -421,7 +466,7 @@ static void bn_apply_launch(T* out, const T* x, const T* dy, const float* coef, 
   const bool vec = aligned_to(out, 16) && aligned_to(x, 16) && (!dy || aligned_to(dy, 16)) && S % V == 0;
   const int64_t units = (n / S) * ((S / V + 127) / 128);   // one warp per unit, 8 warps per CTA
   if (vec) bn_apply_kernel<T, MODE, ACT, AFFINE, true><<<apply_grid(units * 32), 256, 0, st>>>(out, x, dy, coef, g, b, rm, rv, sm, si, S, C, n, eps, act);
-  else bn_apply_kernel<T, MODE, ACT, AFFINE, false><<<apply_grid(n), 256, 0, st>>>(out, x, dy, coef, g, b, rm, rv, sm, si, S, C, n, eps, act);
+  else bn_apply_kernel<T, MODE, ACT, AFFINE, false><<<apply_grid((n / S) * 32), 256, 0, st>>>(out, x, dy, coef, g, b, rm, rv, sm, si, S, C, n, eps, act);
 }
 
 // ---------------------------------------------------------------------------------------------

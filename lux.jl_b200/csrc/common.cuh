@@ -32,6 +32,7 @@ inline bool valid_dtype(int32_t d) { return d == LB2_F32 || d == LB2_BF16; }
 inline bool valid_act(int32_t a) { return a >= LB2_ACT_IDENTITY && a <= LB2_ACT_SWISH; }
 inline size_t dtype_size(int32_t d) { return d == LB2_BF16 ? 2 : 4; }
 inline bool aligned_to(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+__device__ __forceinline__ bool aligned_to_dev(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 // sigma' computable from the output alone (lib/LuxLib/src/traits.jl:59-65)
 inline bool act_grad_from_output(int32_t a) {
   return a == LB2_ACT_IDENTITY || a == LB2_ACT_RELU || a == LB2_ACT_TANH || a == LB2_ACT_SIGMOID;

@@ -21,7 +21,9 @@
 //                  own TMA box), contraction over 64-position blocks split over CTAs; fp32 partials per split and a
 //                  fixed-order reduction (deterministic)
 // A small-channel input whose kW taps fit one 64-channel chunk together (the 3-channel stem) is copied with the kW
-// taps folded into the channel index, so a kernel row costs one k-block instead of kW.
+// taps folded into the channel index, so a kernel row costs one k-block instead of kW; when the stride along H is
+// s >= 2 and s kernel rows fit the chunk as well, s rows are folded too (row s*q - pad + d of the input becomes
+// channel group d of row q of the copy), which turns the kH taps into ceil(kH / s) stride-1 taps along q.
 //
 // All kernels are persistent, warp-specialised (TMA producer, MMA issuer, TMEM allocator, eight epilogue warps) with
 // bounded mbarrier waits, like the GEMM kernels. Roofline: tensor pipe; algorithmic FLOPs = 2*Wo*Ho*N*Cout*Cin*kW*kH
@@ -102,29 +104,31 @@ __global__ void __launch_bounds__(256) cw_transpose_kernel(uint16_t* __restrict_
   }
 }
 
-// Folded copy for small channel counts: out[n][h][ow][tw*C + c] = in[n][c][h][ow*s + tw*dil - pad] (0 outside),
-// channels padded with zeros to Cp.
+// Folded copy for small channel counts: out[n][q][ow][(d*kW + tw)*C + c] = in[n][c][hq][ow*s + tw*dil - pad] (0 outside),
+// hq = q when only the kW taps are folded (FR = 1, d = 0), hq = sh*q - pad_h + d when FR = sh kernel rows are folded
+// too. Channels padded with zeros to Cp. One thread per group of 8 output channels (one 16-byte store).
 __global__ void __launch_bounds__(256) cw_transpose_fold_kernel(uint16_t* __restrict__ out, const uint16_t* __restrict__ in,
-                                                                int W, int H, int C, int Cp, int N, int OW, int kW,
-                                                                int s, int dil, int pad) {
-  // one thread per group of 8 output channels (one 16-byte store)
+                                                                int W, int H, int C, int Cp, int N, int OW, int HQ, int kW,
+                                                                int s, int dil, int pad, int FR, int sh, int pad_h) {
   const int groups = Cp / 8;
-  const int64_t total = (int64_t)N * H * OW * groups;
+  const int64_t total = (int64_t)N * HQ * OW * groups;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
     int64_t r = i;
-    const int q = (int)(r % groups); r /= groups;
+    const int qg = (int)(r % groups); r /= groups;
     const int ow = (int)(r % OW); r /= OW;
-    const int h = (int)(r % H);
-    const int n = (int)(r / H);
+    const int q = (int)(r % HQ);
+    const int n = (int)(r / HQ);
     uint16_t e[8];
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
-      const int j = q * 8 + k;
+      const int j = qg * 8 + k;
       uint16_t v = 0;
-      if (j < kW * C) {
-        const int tw = j / C, c = j % C;
+      const int d = j / (kW * C), rem = j % (kW * C);
+      if (d < FR) {
+        const int tw = rem / C, c = rem % C;
         const int w = ow * s + tw * dil - pad;
-        if (w >= 0 && w < W) v = __ldg(in + (((int64_t)n * C + c) * H + h) * W + w);
+        const int h = FR >= 2 ? sh * q - pad_h + d : q;
+        if (w >= 0 && w < W && h >= 0 && h < H) v = __ldg(in + (((int64_t)n * C + c) * H + h) * W + w);
       }
       e[k] = v;
     }
@@ -135,7 +139,8 @@ __global__ void __launch_bounds__(256) cw_transpose_fold_kernel(uint16_t* __rest
 
 // Packed filter Wp[row][tap][chunk][64]. Forward: row = co, contracted channel = ci. Data gradient (transpose): row =
 // ci, contracted channel = co. tap = th*kW + tw in tap positions (filter index = flip ? t : K-1-t per dim).
-// fold: the contracted index of a kernel row is (tw, ci) in ONE chunk (taps run over th only).
+// fold >= 1: the contracted index of a tap is (d, tw, ci) in ONE chunk, d < fold kernel rows per tap (fold = 1: taps
+// run over th; fold = s >= 2: tap p covers kernel rows s*p .. s*p + s - 1).
 struct CwPack {
   int kW, kH, cin, cout, flip, transpose, fold, chunks, n_rows, k_total;
 };
@@ -153,8 +158,10 @@ __global__ void __launch_bounds__(256) cw_pack_filter_kernel(__nv_bfloat16* __re
       int tw, th, c;
       bool live;
       if (g.fold) {
-        th = kb; tw = j / g.cin; c = j % g.cin;
-        live = tw < g.kW;
+        const int d = j / (g.kW * g.cin), rem = j % (g.kW * g.cin);
+        th = g.fold >= 2 ? g.fold * kb + d : kb;
+        tw = rem / g.cin; c = rem % g.cin;
+        live = d < g.fold && th < g.kH;
       } else {
         const int tap = kb / g.chunks;
         tw = tap % g.kW; th = tap / g.kW;
@@ -530,7 +537,8 @@ __global__ void __launch_bounds__(256) conv_cw_wgrad_reduce_kernel(T* __restrict
     const int co = (int)(r / g.cin);
     const int tw = g.flip ? kw : g.kW - 1 - kw, th = g.flip ? kh : g.kH - 1 - kh;
     int pair, col;
-    if (g.fold) { pair = th; col = tw * g.cin + ci; }
+    if (g.fold >= 2) { pair = th / g.fold; col = ((th % g.fold) * g.kW + tw) * g.cin + ci; }
+    else if (g.fold) { pair = th; col = tw * g.cin + ci; }
     else { pair = (th * g.kW + tw) * g.chunks + ci / 64; col = ci % 64; }
     const int grp = pair / g.pairs_per_group, slot = pair % g.pairs_per_group;
     const int64_t off = (((int64_t)(grp * g.co_tiles + co / 128)) * 128 + co % 128) * bn + slot * 64 + col;
@@ -575,8 +583,16 @@ unsigned flat_grid(int64_t total) {
 
 int cw_bn(int n_out) { return n_out <= 64 ? 64 : (n_out <= 128 ? 128 : 256); }
 
-// kW taps folded into the channel index of the input copy (forward and filter gradient of small-channel inputs)
-bool cw_fold(const ConvGeom& g) { return g.k[0] > 1 && g.k[0] * g.cin <= 64; }
+// Kernel rows folded into the channel index of the input copy together with the kW taps (forward and filter gradient
+// of small-channel inputs): 0 = no folding, 1 = the kW taps only, s >= 2 = the s rows a stride-s step spans as well.
+int cw_fold(const ConvGeom& g) {
+  if (g.k[0] <= 1 || g.k[0] * g.cin > 64) return 0;
+  const int sh = g.stride[1];
+  if (sh >= 2 && g.dil[1] == 1 && g.k[1] > 1 && sh * g.k[0] * g.cin <= 64) return sh;
+  return 1;
+}
+// taps (k-blocks per output tile) of a folded problem
+int cw_fold_taps(const ConvGeom& g, int fold) { return fold >= 2 ? (g.k[1] + fold - 1) / fold : g.k[1]; }
 
 struct CwCopy {      // channel-innermost copy of an activation array
   int Cp, W, H;      // padded channels, spatial extents of the copy (W = output width when folded)
@@ -584,9 +600,10 @@ struct CwCopy {      // channel-innermost copy of an activation array
 };
 CwCopy cw_copy_of_x(const ConvGeom& g) {
   CwCopy c{};
-  if (cw_fold(g)) { c.Cp = round_up(g.k[0] * g.cin, 8); c.W = g.out[0]; }
+  const int fold = cw_fold(g);
+  if (fold) { c.Cp = round_up(fold * g.k[0] * g.cin, 8); c.W = g.out[0]; }
   else { c.Cp = round_up(g.cin, 8); c.W = g.in[0]; }
-  c.H = g.in[1];
+  c.H = fold >= 2 ? g.out[1] + cw_fold_taps(g, fold) - 1 : g.in[1];
   c.bytes = align_up((size_t)c.Cp * c.W * c.H * g.batch * 2, 1024);
   return c;
 }
@@ -624,9 +641,11 @@ int32_t cw_transpose(void* out, const void* in, int W, int H, int C, int Cp, int
 }
 
 int32_t cw_copy_x(void* xc, const void* x, const ConvGeom& g, const CwCopy& c, cudaStream_t st) {
-  if (cw_fold(g)) {
+  const int fold = cw_fold(g);
+  if (fold) {
     cw_transpose_fold_kernel<<<flat_grid((int64_t)(c.Cp / 8) * c.W * c.H * g.batch), 256, 0, st>>>(
-        (uint16_t*)xc, (const uint16_t*)x, g.in[0], g.in[1], g.cin, c.Cp, g.batch, g.out[0], g.k[0], g.stride[0], g.dil[0], g.pad_lo[0]);
+        (uint16_t*)xc, (const uint16_t*)x, g.in[0], g.in[1], g.cin, c.Cp, g.batch, g.out[0], c.H, g.k[0], g.stride[0], g.dil[0], g.pad_lo[0],
+        fold, g.stride[1], g.pad_lo[1]);
     LB2_CHECK_LAUNCH("conv_cw folded copy");
     return LB2_OK;
   }
@@ -696,7 +715,8 @@ bool conv_cw_supported(const ConvGeom& g, int32_t dtype) {
   if (dtype != LB2_BF16 || g.ndim != 2 || g.groups != 1) return false;
   if (g.out[0] <= 0 || g.out[1] <= 0 || g.batch <= 0 || g.cin <= 0 || g.cout <= 0) return false;
   if (g.stride[0] > 4 || g.stride[1] > 4) return false;               // box extent = positions x stride must stay <= 256
-  const int chunks = cw_fold(g) ? 1 : (g.cin + 63) / 64, taps = cw_fold(g) ? g.k[1] : g.k[0] * g.k[1];
+  const int fold0 = cw_fold(g);
+  const int chunks = fold0 ? 1 : (g.cin + 63) / 64, taps = fold0 ? cw_fold_taps(g, fold0) : g.k[0] * g.k[1];
   if (taps * chunks > kCwMaxKb) return false;
   if (g.k[0] * g.k[1] * ((g.cout + 63) / 64) > kCwMaxKb) return false;   // data gradient contracts over output channels
   if (g.k[0] * g.dil[0] > 120 || g.k[1] * g.dil[1] > 120) return false;
@@ -708,33 +728,34 @@ bool conv_cw_supported(const ConvGeom& g, int32_t dtype) {
 }
 
 size_t conv_cw_fwd_workspace_bytes(const ConvGeom& g) {
-  const bool fold = cw_fold(g);
-  return cw_copy_of_x(g).bytes + cw_packed_bytes(g.cout, fold ? g.k[1] : g.k[0] * g.k[1], fold ? 1 : (g.cin + 63) / 64);
+  const int fold = cw_fold(g);
+  return cw_copy_of_x(g).bytes + cw_packed_bytes(g.cout, fold ? cw_fold_taps(g, fold) : g.k[0] * g.k[1], fold ? 1 : (g.cin + 63) / 64);
 }
 
 int32_t conv_cw_fwd(void* y, void* preact, const void* x, const void* w, const void* bias, const ConvGeom& g, int32_t act,
                     void* ws_, cudaStream_t st) {
   uint8_t* ws = static_cast<uint8_t*>(ws_);
-  const bool fold = cw_fold(g);
+  const int fold = cw_fold(g);
   const CwCopy xc = cw_copy_of_x(g);
   int32_t rc = cw_copy_x(ws, x, g, xc, st);
   if (rc != LB2_OK) return rc;
   __nv_bfloat16* wp = reinterpret_cast<__nv_bfloat16*>(ws + xc.bytes);
   CwPack pk{};
-  pk.kW = g.k[0]; pk.kH = g.k[1]; pk.cin = g.cin; pk.cout = g.cout; pk.flip = g.flip; pk.transpose = 0; pk.fold = fold ? 1 : 0;
+  pk.kW = g.k[0]; pk.kH = g.k[1]; pk.cin = g.cin; pk.cout = g.cout; pk.flip = g.flip; pk.transpose = 0; pk.fold = fold;
   pk.chunks = fold ? 1 : (g.cin + 63) / 64;
-  const int n_taps = fold ? g.k[1] : g.k[0] * g.k[1];
+  const int n_taps = fold ? cw_fold_taps(g, fold) : g.k[0] * g.k[1];
   pk.n_rows = round_up(g.cout, cw_bn(g.cout));
   pk.k_total = n_taps * pk.chunks * 64;
   cw_pack_filter_kernel<<<flat_grid((int64_t)pk.n_rows * pk.k_total), 256, 0, st>>>(wp, (const __nv_bfloat16*)w, pk);
   LB2_CHECK_LAUNCH("conv_cw filter packing");
   CwTap taps[kCwMaxKb];
   for (int t = 0; t < n_taps; ++t) {
-    if (fold) taps[t] = CwTap{0, t * g.dil[1] - g.pad_lo[1], t};
+    if (fold >= 2) taps[t] = CwTap{0, t, t};                                        // rows of the copy: q = oh + t
+    else if (fold) taps[t] = CwTap{0, t * g.dil[1] - g.pad_lo[1], t};
     else taps[t] = CwTap{(t % g.k[0]) * g.dil[0] - g.pad_lo[0], (t / g.k[0]) * g.dil[1] - g.pad_lo[1], t};
   }
   return cw_run_gemm(y, preact, bias, act, ws, xc.Cp, xc.W, xc.H, g.batch, pk.chunks, wp, pk.n_rows, pk.k_total, taps, n_taps,
-                     g.out[0], g.out[1], fold ? 1 : g.stride[0], g.stride[1], g.cout, g.out[0], g.out[1], 1, 0, 1, 0, st);
+                     g.out[0], g.out[1], fold ? 1 : g.stride[0], fold >= 2 ? 1 : g.stride[1], g.cout, g.out[0], g.out[1], 1, 0, 1, 0, st);
 }
 
 // ---- backward ---------------------------------------------------------------------------------------
@@ -747,9 +768,9 @@ struct CwWgPlan {
 };
 CwWgPlan cw_wg_plan(const ConvGeom& g) {
   CwWgPlan w{};
-  const bool fold = cw_fold(g);
+  const int fold = cw_fold(g);
   w.chunks = fold ? 1 : (g.cin + 63) / 64;
-  w.n_pairs = (fold ? g.k[1] : g.k[0] * g.k[1]) * w.chunks;
+  w.n_pairs = (fold ? cw_fold_taps(g, fold) : g.k[0] * g.k[1]) * w.chunks;
   // column groups per MMA: the largest of 4, 3, 2 that divides the pair count, else 4 with filler groups
   w.ppg = w.n_pairs >= 4 ? 4 : w.n_pairs;
   for (int c = 4; c >= 2; --c)
@@ -793,7 +814,7 @@ int32_t conv_cw_bwd(void* dw, void* dx, const void* x, const void* gy, const voi
   uint8_t* rest = ws + yc.bytes;
 
   if (dw != nullptr) {
-    const bool fold = cw_fold(g);
+    const int fold = cw_fold(g);
     const CwCopy xc = cw_copy_of_x(g);
     rc = cw_copy_x(rest, x, g, xc, st);
     if (rc != LB2_OK) return rc;
@@ -801,7 +822,7 @@ int32_t conv_cw_bwd(void* dw, void* dx, const void* x, const void* gy, const voi
     CwWgParams q{};
     q.OW = g.out[0]; q.OH = g.out[1]; q.NI = g.batch;
     q.KW_ = pl.KW_; q.KH_ = pl.KH_; q.KI_ = pl.KI_; q.kbw = pl.kbw; q.kbh = pl.kbh; q.kbi = pl.kbi;
-    q.sw = fold ? 1 : g.stride[0]; q.sh = g.stride[1];
+    q.sw = fold ? 1 : g.stride[0]; q.sh = fold >= 2 ? 1 : g.stride[1];
     q.co_tiles = pl.co_tiles; q.groups = pl.groups; q.pairs_per_group = pl.ppg; q.n_pairs = pl.n_pairs;
     q.splits = pl.splits; q.kb_total = pl.kb_total; q.kb_per_split = pl.kb_per_split;
     // A (gy copy) and B (x copy) both MN-major: bits 15 and 16
@@ -809,12 +830,12 @@ int32_t conv_cw_bwd(void* dw, void* dx, const void* x, const void* gy, const voi
     q.partial = reinterpret_cast<float*>(rest + xc.bytes);
     q.status = device_status_word();
     LB2_REQUIRE(q.status != nullptr, LB2_LAUNCH_FAIL, "conv_cw: device status word unavailable");
-    const int n_taps = fold ? g.k[1] : g.k[0] * g.k[1];
+    const int n_taps = fold ? cw_fold_taps(g, fold) : g.k[0] * g.k[1];
     for (int t = 0; t < n_taps; ++t)
       for (int ch = 0; ch < pl.chunks; ++ch) {
         const int pr = t * pl.chunks + ch;
         q.pr_dw[pr] = (int16_t)(fold ? 0 : (t % g.k[0]) * g.dil[0] - g.pad_lo[0]);
-        q.pr_dh[pr] = (int16_t)((fold ? t : t / g.k[0]) * g.dil[1] - g.pad_lo[1]);
+        q.pr_dh[pr] = (int16_t)(fold >= 2 ? t : (fold ? t : t / g.k[0]) * g.dil[1] - g.pad_lo[1]);
         q.pr_c0[pr] = (int16_t)(ch * 64);
       }
     CUtensorMap mG, mX;
@@ -837,7 +858,7 @@ int32_t conv_cw_bwd(void* dw, void* dx, const void* x, const void* gy, const voi
     rc = pl.ppg == 1 ? launch(conv_cw_wgrad_kernel<1>, 1) : pl.ppg == 2 ? launch(conv_cw_wgrad_kernel<2>, 2)
        : pl.ppg == 3 ? launch(conv_cw_wgrad_kernel<3>, 3) : launch(conv_cw_wgrad_kernel<4>, 4);
     if (rc != LB2_OK) return rc;
-    CwReduce rd{g.k[0], g.k[1], g.cin, g.cout, g.flip, fold ? 1 : 0, pl.chunks, pl.co_tiles, pl.groups, pl.ppg, pl.splits};
+    CwReduce rd{g.k[0], g.k[1], g.cin, g.cout, g.flip, fold, pl.chunks, pl.co_tiles, pl.groups, pl.ppg, pl.splits};
     conv_cw_wgrad_reduce_kernel<__nv_bfloat16><<<flat_grid((int64_t)g.k[0] * g.k[1] * g.cin * g.cout), 256, 0, st>>>(
         (__nv_bfloat16*)dw, q.partial, rd);
     LB2_CHECK_LAUNCH("conv_cw_wgrad_reduce");
