@@ -119,18 +119,20 @@ __global__ void __launch_bounds__(256) cw_transpose_fold_kernel(uint16_t* __rest
     const int q = (int)(r % HQ);
     const int n = (int)(r / HQ);
     uint16_t e[8];
+    // (d, tw, c) of the group's first channel by division, of the following seven by carrying
+    int d = (qg * 8) / (kW * C), rem = (qg * 8) % (kW * C);
+    int tw = rem / C, c = rem % C;
+    const uint16_t* plane0 = in + (int64_t)n * C * H * W;
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
-      const int j = qg * 8 + k;
       uint16_t v = 0;
-      const int d = j / (kW * C), rem = j % (kW * C);
       if (d < FR) {
-        const int tw = rem / C, c = rem % C;
         const int w = ow * s + tw * dil - pad;
         const int h = FR >= 2 ? sh * q - pad_h + d : q;
-        if (w >= 0 && w < W && h >= 0 && h < H) v = __ldg(in + (((int64_t)n * C + c) * H + h) * W + w);
+        if (w >= 0 && w < W && h >= 0 && h < H) v = __ldg(plane0 + ((int64_t)c * H + h) * W + w);
       }
       e[k] = v;
+      if (++c == C) { c = 0; if (++tw == kW) { tw = 0; ++d; } }
     }
     *reinterpret_cast<uint4*>(out + i * 8) = make_uint4((uint32_t)e[0] | ((uint32_t)e[1] << 16), (uint32_t)e[2] | ((uint32_t)e[3] << 16),
                                                       (uint32_t)e[4] | ((uint32_t)e[5] << 16), (uint32_t)e[6] | ((uint32_t)e[7] << 16));

@@ -1,23 +1,22 @@
-// Tensor-core convolution for sm_100a (bf16 storage, fp32 accumulation in TMEM): implicit GEMM on
-// the WHCN (column-major) layout without an im2col buffer.
+// Tensor-core convolution for sm_100a (bf16 storage, fp32 accumulation in TMEM), fast case: implicit GEMM on the
+// WHCN (column-major) bytes themselves, no copy of the input for the forward and the data gradient.
 //
-// Shapes taken: 2-D, stride 1, dilation 1, groups 1, output width == input width ("same" along W),
-// W*sizeof(T) a multiple of 16 bytes. Everything else stays on the direct kernels.
+// Shapes taken: 2-D, stride 1, dilation 1, groups 1, output width == input width ("same" along W), W a multiple of 8,
+// kernel width <= 4 and a filter small enough to stay RESIDENT in shared memory next to the operand ring (the
+// 64-channel 3x3 stage of a ResNet). Every other bf16 geometry is served by the general path of conv_cw.cu.
 //
-// Formulation. With s = w + W*h the flattened spatial index of one image, a kernel tap (tw, th) reads
-// x at s + (tw - pad_w) + (th - pad_h)*W. The H part of that shift is a multiple of 16 bytes and is
-// applied as a TMA start coordinate on a 4-D tensor map (s, channel, image, copy) whose out-of-range
-// rows are zero-filled — that is the top/bottom padding. The W part is a single-element shift, which
-// TMA cannot start on, so a bandwidth pass first writes kW copies of the input, copy t shifted by
-// t - pad_w along W with zeros at the row ends (the left/right padding). The GEMM then is
-//   y[s, co] (+)= sum over k-blocks (tap, 64 input channels) of  A_kb[s, ci] * Wp[co, kb*64 + ci]
-// with A MN-major (s contiguous) straight from the shifted copies, the packed filter Wp K-major and
-// RESIDENT in shared memory for the whole persistent CTA (it is the same for every tile), M = 128
-// spatial positions, N = 64 or 128 output channels, fp32 accumulators double-buffered in TMEM.
+// Formulation. With s = w + W*h the flattened spatial index of one image, a kernel tap (tw, th) reads x at
+// s + (tw - pad_w) + (th - pad_h)*W. The H part of that shift is a multiple of 16 bytes and is applied as a TMA start
+// coordinate on a tensor map (s, channel, image) whose out-of-range rows are zero-filled — the top/bottom padding.
+// The W part is a single-element shift, which a TMA tile cannot start on; it is applied in the EPILOGUE instead
+// (conv_tc_fwd2_kernel): per k-step ONE MMA of width kW*64 multiplies the A tile (128 positions x 64 channels,
+// MN-major) with the kW taps of a kernel row side by side, giving kW accumulators that the epilogue adds shifted by one
+// row each (warp shuffles plus a few rows exchanged through shared memory), masked at the image-row ends.
 // The data gradient is the same kernel on dy with the filter packed flipped and transposed.
-// The filter gradient contracts over (s, image): per CTA a K-range of 64-position blocks, A = two
-// taps' shifted input rows stacked to M = 128 (K-major), B = dy rows (K-major), fp32 partials per
-// K-split in the workspace and a fixed-order reduction — deterministic.
+// The filter gradient (conv_tc_wgrad2_kernel) contracts over (s, image): M = 128 output channels (rows of dy),
+// N = kW*64 = the kW taps of a kernel row x 64 input channels, read from kW-1 W-shifted copies of x made by one
+// bandwidth pass (the unshifted tap comes from x itself); fp32 partials per K-split in the workspace and a
+// fixed-order reduction — deterministic.
 //
 // Roofline: tensor pipe; algorithmic FLOPs = 2*Wo*Ho*N*Cout*Cin*kW*kH per pass.
 #include "conv.cuh"
@@ -27,7 +26,6 @@ namespace lb2 {
 
 constexpr int kConvThreads = 384;   // warps 0-2: TMA / MMA / TMEM, warps 4-11: epilogue (two per TMEM lane quarter)
 constexpr int kConvBM = 128;
-constexpr int kMaxKb = 96;
 
 // ----------------------------------------------------------------------------------------------
 // layout passes
@@ -149,190 +147,6 @@ __global__ void __launch_bounds__(256) conv_pack_filter_kernel(T* __restrict__ w
     wp[i] = from_f32<T>(v);
   }
 }
-
-// ----------------------------------------------------------------------------------------------
-// forward / data-gradient kernel
-// ----------------------------------------------------------------------------------------------
-struct ConvTcParams {
-  int32_t S_out;          // flattened output positions per image (W * Ho)
-  int32_t n_img, n_out;   // images, GEMM output channels
-  int32_t tiles_m, tiles_n, num_kb;
-  int32_t stages;         // A-operand ring depth
-  uint32_t idesc;
-  uint32_t a_desc_hi, a_desc_lbo, a_k_advance;
-  uint32_t b_desc_hi, b_desc_lbo, b_k_advance;
-  void* y;
-  void* preact;
-  const void* bias;       // per GEMM output channel, or null
-  int32_t act;
-  unsigned int* status;
-  int16_t a_shift[kMaxKb];   // start-coordinate offset along s (multiple of 8 elements)
-  int16_t a_chan[kMaxKb];    // first contracted channel of the k-block
-  int8_t a_copy[kMaxKb];     // which W-shifted copy
-};
-
-template <int BN, int ACT>
-__global__ void __launch_bounds__(kConvThreads, 1)
-conv_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
-                   const __grid_constant__ ConvTcParams p) {
-  constexpr int A_BYTES = kConvBM * 128;   // 128 positions x 64 channels bf16
-  constexpr int B_BYTES = BN * 128;        // BN output channels x 64 contracted channels
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-  const uint32_t sB0 = smem_base;                                // resident filter: num_kb tiles
-  const uint32_t sA0 = smem_base + p.num_kb * B_BYTES;           // A ring
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + p.num_kb * B_BYTES + p.stages * A_BYTES);
-  uint64_t* full = bars;                       // [stages]
-  uint64_t* empty = bars + p.stages;           // [stages]
-  uint64_t* acc_full = bars + 2 * p.stages;    // [2]
-  uint64_t* acc_empty = acc_full + 2;          // [2]
-  uint64_t* b_full = acc_empty + 2;            // [1] resident filter landed
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(b_full + 1);
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tiles_per_n = p.tiles_m * p.n_img;
-  const int num_tiles = tiles_per_n * p.tiles_n;
-  const int stages = p.stages;
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 8); }
-    mbar_init(b_full, 1);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  __shared__ float sbias[BN];
-  {
-    const int nt_ = blockIdx.x % p.tiles_n;
-    const __nv_bfloat16* bias = reinterpret_cast<const __nv_bfloat16*>(p.bias);
-    for (int c = threadIdx.x; c < BN; c += blockDim.x) {
-      const int co = nt_ * BN + c;
-      sbias[c] = (bias != nullptr && co < p.n_out) ? __bfloat162float(bias[co]) : 0.f;
-    }
-  }
-  if (warp == 2) {
-    tmem_alloc(tmem_slot, 2 * BN);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-
-  // This CTA's tiles all use the same n-tile when tiles_n == 1 (the common case); with several
-  // n-tiles the resident filter would differ per tile, so the grid is partitioned by n-tile instead:
-  // CTA b works on n-tile (b % tiles_n) and strides over the (m, image) tiles of that n-tile.
-  const int nt = blockIdx.x % p.tiles_n;
-  const int first = blockIdx.x / p.tiles_n, step = gridDim.x / p.tiles_n;
-  const int n0 = nt * BN;
-
-  if (warp == 0) {
-    if (lane == 0) {
-      tma_prefetch_desc(&tmX);
-      tma_prefetch_desc(&tmW);
-      mbar_expect_tx(b_full, (uint32_t)(p.num_kb * B_BYTES));
-      for (int kb = 0; kb < p.num_kb; ++kb) tma_load_2d(sB0 + kb * B_BYTES, &tmW, kb * 64, n0, b_full);
-      uint32_t stage = 0, phase = 0;
-      bool ok = true;
-      for (int t = first; t < tiles_per_n && ok; t += step) {
-        const int m0 = (t % p.tiles_m) * kConvBM, img = t / p.tiles_m;
-        for (int kb = 0; kb < p.num_kb; ++kb) {
-          if (!mbar_wait(&empty[stage], phase ^ 1u, p.status, 0x1000u)) { ok = false; break; }
-          mbar_expect_tx(&full[stage], A_BYTES);
-          const uint32_t sA = sA0 + stage * A_BYTES;
-          const int c0 = m0 + p.a_shift[kb];
-          tma_load_4d(sA, &tmX, c0, p.a_chan[kb], img, p.a_copy[kb], &full[stage]);
-          tma_load_4d(sA + A_BYTES / 2, &tmX, c0 + 64, p.a_chan[kb], img, p.a_copy[kb], &full[stage]);
-          if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
-        }
-      }
-    }
-  } else if (warp == 1) {
-    if (lane == 0) {
-      uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
-      bool ok = mbar_wait(b_full, 0, p.status, 0x2000u);
-      for (int t = first; t < tiles_per_n && ok; t += step) {
-        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1u, p.status, 0x4000u)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < p.num_kb; ++kb) {
-          if (!mbar_wait(&full[stage], phase, p.status, 0x8000u)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t sA = sA0 + stage * A_BYTES;
-          const uint32_t sB = sB0 + kb * B_BYTES;
-          const uint32_t a_lo32 = ((sA >> 4) & 0x3FFFu) | p.a_desc_lbo;
-          const uint32_t b_lo32 = ((sB >> 4) & 0x3FFFu) | p.b_desc_lbo;
-#pragma unroll
-          for (int ks = 0; ks < 4; ++ks) {
-            const uint64_t ad = ((uint64_t)p.a_desc_hi << 32) | (uint64_t)(a_lo32 + ks * p.a_k_advance);
-            const uint64_t bd = ((uint64_t)p.b_desc_hi << 32) | (uint64_t)(b_lo32 + ks * p.b_k_advance);
-            umma<false>(d_tmem, ad, bd, p.idesc, (kb | ks) != 0 ? 1u : 0u);
-          }
-          umma_commit(&empty[stage]);
-          if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
-        }
-        if (ok) umma_commit(&acc_full[acc]);
-        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
-      }
-    }
-  } else if (warp >= 4) {
-    // Two warps share each TMEM lane quarter and split the tile's columns. A thread owns one output
-    // position s and walks its channels with a pointer stride of S_out (channel planes of y).
-    const int q = warp & 3, half = (warp - 4) >> 2;
-    constexpr int COLS = BN / 2;
-    uint32_t acc = 0, acc_phase = 0;
-    __nv_bfloat16* Y = reinterpret_cast<__nv_bfloat16*>(p.y);
-    __nv_bfloat16* P = reinterpret_cast<__nv_bfloat16*>(p.preact);
-    const int64_t cs = p.S_out;
-    const int col0 = n0 + half * COLS;
-    const int lim = min(COLS, p.n_out - col0);   // live columns of this warp (may be <= 0)
-    bool ok = true;
-    for (int t = first; t < tiles_per_n && ok; t += step) {
-      const int m0 = (t % p.tiles_m) * kConvBM, img = t / p.tiles_m;
-      if (!mbar_wait_warp(&acc_full[acc], acc_phase, p.status, 0x10000u)) { ok = false; break; }
-      tc_fence_after();
-      const int s = m0 + q * 32 + lane;
-      const bool s_ok = s < p.S_out;
-      const int64_t base = (int64_t)s + cs * ((int64_t)p.n_out * img + col0);
-      __nv_bfloat16* yp = Y + base;
-      __nv_bfloat16* pp = P != nullptr ? P + base : nullptr;
-#pragma unroll 1
-      for (int c = 0; c < COLS / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + half * COLS + c * 32, r);
-        tmem_ld_wait();
-        if (s_ok) {
-          const float* sb = sbias + half * COLS + c * 32;
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            if (c * 32 + j < lim) {
-              const float v = __uint_as_float(r[j]) + sb[j];
-              if (pp != nullptr) pp[j * cs] = __float2bfloat16_rn(v);
-              yp[j * cs] = __float2bfloat16_rn(act_apply_any<ACT, true>(p.act, v));
-            }
-          }
-        }
-        yp += 32 * cs;
-        if (pp != nullptr) pp += 32 * cs;
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[acc]);
-      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
-    }
-  }
-
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 2) {
-    if (*reinterpret_cast<volatile unsigned int*>(p.status) != 0) {
-      for (int i = 0; i < 64; ++i) __nanosleep(2000);
-    }
-    tc_fence_after();
-    tmem_dealloc(tmem_base, 2 * BN);
-  }
-}
-
 
 // ----------------------------------------------------------------------------------------------
 // forward / data-gradient kernel, shift-in-epilogue variant (kernel width <= 4, 64-channel N tiles)
@@ -605,163 +419,6 @@ conv_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
 }
 
 // ----------------------------------------------------------------------------------------------
-// filter-gradient kernel
-// ----------------------------------------------------------------------------------------------
-// Row groups of 64 rows each: rg = tap * chunks + chunk. An M tile stacks row groups 2j and 2j+1.
-struct ConvWgParams {
-  int32_t S_out, n_img, n_out;       // contraction extent per image, images, dy channels (GEMM N)
-  int32_t s_blocks;                  // 64-position blocks per image
-  int32_t m_tiles, tiles_n, splits;  // work item = (m tile, n tile, K split)
-  int32_t kb_total, kb_per_split;
-  int32_t n_rg;                      // number of row groups
-  int32_t stages;
-  uint32_t idesc;
-  uint32_t desc_hi, desc_lbo, k_advance;   // both operands K-major SW128
-  float* partial;                    // [splits][m_tiles*128][n_pad]
-  int32_t n_pad;
-  unsigned int* status;
-  int16_t rg_shift[2 * kMaxKb];      // per row group: start offset along s, first channel, copy
-  int16_t rg_chan[2 * kMaxKb];
-  int8_t rg_copy[2 * kMaxKb];
-};
-
-template <int BN>
-__global__ void __launch_bounds__(kConvThreads, 1)
-conv_tc_wgrad_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmG,
-                     const __grid_constant__ ConvWgParams p) {
-  constexpr int A_BYTES = kConvBM * 128;
-  constexpr int B_BYTES = BN * 128;
-  constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + p.stages * STAGE_BYTES);
-  uint64_t* full = bars;
-  uint64_t* empty = bars + p.stages;
-  uint64_t* acc_full = bars + 2 * p.stages;
-  uint64_t* acc_empty = acc_full + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int stages = p.stages;
-  const int num_items = p.m_tiles * p.tiles_n * p.splits;
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 8); }
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  if (warp == 2) {
-    tmem_alloc(tmem_slot, 2 * BN);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-
-  // item -> (m tile fastest, n tile, split)
-  if (warp == 0) {
-    if (lane == 0) {
-      tma_prefetch_desc(&tmX);
-      tma_prefetch_desc(&tmG);
-      uint32_t stage = 0, phase = 0;
-      bool ok = true;
-      for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
-        const int mt = item % p.m_tiles, nt = (item / p.m_tiles) % p.tiles_n, z = item / (p.m_tiles * p.tiles_n);
-        const int kb_lo = z * p.kb_per_split, kb_hi = min(p.kb_total, kb_lo + p.kb_per_split);
-        const int rg0 = 2 * mt, rg1 = 2 * mt + 1;
-        for (int kb = kb_lo; kb < kb_hi; ++kb) {
-          if (!mbar_wait(&empty[stage], phase ^ 1u, p.status, 0x20000u)) { ok = false; break; }
-          const int img = kb / p.s_blocks, s0 = (kb % p.s_blocks) * 64;
-          const uint32_t sA = smem_base + stage * STAGE_BYTES, sB = sA + A_BYTES;
-          const bool two = rg1 < p.n_rg;
-          mbar_expect_tx(&full[stage], (uint32_t)(B_BYTES + (two ? A_BYTES : A_BYTES / 2)));
-          tma_load_4d(sA, &tmX, s0 + p.rg_shift[rg0], p.rg_chan[rg0], img, p.rg_copy[rg0], &full[stage]);
-          if (two) tma_load_4d(sA + A_BYTES / 2, &tmX, s0 + p.rg_shift[rg1], p.rg_chan[rg1], img, p.rg_copy[rg1], &full[stage]);
-          tma_load_4d(sB, &tmG, s0, nt * BN, img, 0, &full[stage]);
-          if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
-        }
-      }
-    }
-  } else if (warp == 1) {
-    if (lane == 0) {
-      uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
-      bool ok = true;
-      for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
-        const int z = item / (p.m_tiles * p.tiles_n);
-        const int kb_lo = z * p.kb_per_split, kb_hi = min(p.kb_total, kb_lo + p.kb_per_split);
-        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1u, p.status, 0x40000u)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = kb_lo; kb < kb_hi; ++kb) {
-          if (!mbar_wait(&full[stage], phase, p.status, 0x80000u)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t sA = smem_base + stage * STAGE_BYTES, sB = sA + A_BYTES;
-          const uint32_t a_lo32 = ((sA >> 4) & 0x3FFFu) | p.desc_lbo;
-          const uint32_t b_lo32 = ((sB >> 4) & 0x3FFFu) | p.desc_lbo;
-#pragma unroll
-          for (int ks = 0; ks < 4; ++ks) {
-            const uint64_t ad = ((uint64_t)p.desc_hi << 32) | (uint64_t)(a_lo32 + ks * p.k_advance);
-            const uint64_t bd = ((uint64_t)p.desc_hi << 32) | (uint64_t)(b_lo32 + ks * p.k_advance);
-            umma<false>(d_tmem, ad, bd, p.idesc, (kb > kb_lo || ks != 0) ? 1u : 0u);
-          }
-          umma_commit(&empty[stage]);
-          if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
-        }
-        if (ok) umma_commit(&acc_full[acc]);
-        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
-      }
-    }
-  } else if (warp >= 4) {
-    const int q = warp & 3;
-    uint32_t acc = 0, acc_phase = 0;
-    bool ok = true;
-    for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
-      const int mt = item % p.m_tiles, nt = (item / p.m_tiles) % p.tiles_n, z = item / (p.m_tiles * p.tiles_n);
-      const int kb_lo = z * p.kb_per_split;
-      const bool empty_range = kb_lo >= p.kb_total;   // a split with no k-blocks contributes zeros
-      if (!empty_range) {
-        if (!mbar_wait_warp(&acc_full[acc], acc_phase, p.status, 0x100000u)) { ok = false; break; }
-        tc_fence_after();
-      }
-      const int row = mt * 128 + q * 32 + lane;
-      float* dst = p.partial + ((int64_t)z * p.m_tiles * 128 + row) * p.n_pad + nt * BN;
-      // A row group that was not loaded (odd tail) leaves stale shared memory under the MMA: its rows
-      // are never read by the reduction, but they are written as zeros to keep the buffer defined.
-      const bool live = (row / 64) < p.n_rg;
-      const int half = (warp - 4) >> 2;   // two warps per lane quarter split the columns
-#pragma unroll 1
-      for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
-        uint32_t r[32];
-        if (!empty_range) {
-          tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c * 32, r);
-          tmem_ld_wait();
-        }
-#pragma unroll
-        for (int j = 0; j < 32; ++j) dst[c * 32 + j] = (live && !empty_range) ? __uint_as_float(r[j]) : 0.f;
-      }
-      if (!empty_range) {
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&acc_empty[acc]);
-        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
-      }
-    }
-  }
-
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 2) {
-    if (*reinterpret_cast<volatile unsigned int*>(p.status) != 0) {
-      for (int i = 0; i < 64; ++i) __nanosleep(2000);
-    }
-    tc_fence_after();
-    tmem_dealloc(tmem_base, 2 * BN);
-  }
-}
-
-// ----------------------------------------------------------------------------------------------
 // filter-gradient kernel, wide-N variant (kernel width <= 4)
 // ----------------------------------------------------------------------------------------------
 // The cost of a tcgen05.mma here depends little on its width, so the narrow (N = 64) MMAs of the kernel above are
@@ -936,27 +593,6 @@ __global__ void __launch_bounds__(256) conv_wgrad2_reduce_kernel(T* __restrict__
   }
 }
 
-// dw[kw,kh,ci,co] = sum over splits (ascending) of partial[z][(tap, chunk, ci % 64)][co]
-template <typename T>
-__global__ void __launch_bounds__(256) conv_wgrad_reduce_kernel(T* __restrict__ dw, const float* __restrict__ partial,
-                                                                int kW, int kH, int cin, int cout, int flip, int chunks,
-                                                                int rows_pad, int n_pad, int splits) {
-  const int64_t total = (int64_t)kW * kH * cin * cout;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    int64_t r = i;
-    const int kw = (int)(r % kW); r /= kW;
-    const int kh = (int)(r % kH); r /= kH;
-    const int ci = (int)(r % cin);
-    const int co = (int)(r / cin);
-    const int tw = flip ? kw : kW - 1 - kw, th = flip ? kh : kH - 1 - kh;
-    const int rg = (th * kW + tw) * chunks + ci / 64;
-    const int64_t row = (int64_t)rg * 64 + ci % 64;
-    float s = 0.f;
-    for (int z = 0; z < splits; ++z) s += partial[((int64_t)z * rows_pad + row) * n_pad + co];
-    dw[i] = from_f32<T>(s);
-  }
-}
-
 
 // ----------------------------------------------------------------------------------------------
 // host side
@@ -1003,14 +639,7 @@ static bool bf16_map_out(CUtensorMap* map, const void* ptr, int64_t s_out, int64
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-static int conv_bn(int cn) { return cn <= 64 ? 64 : 128; }
 static int conv_chunks(int ck) { return (ck + 63) / 64; }
-static int conv_fwd_stages(const ConvGemm& c) {
-  const int num_kb = c.kW * c.kH * conv_chunks(c.Ck);
-  const int resident = num_kb * conv_bn(c.Cn) * 128;
-  int st = (200 * 1024 - resident) / (kConvBM * 128);
-  return st > 8 ? 8 : st;
-}
 
 // shift-in-epilogue kernel: kernel width <= 4, filter resident next to at least 3 A stages and the edge buffers
 // A-ring depth; `with_preact` = the launch also stages a pre-activation tile per epilogue group
@@ -1027,13 +656,7 @@ static bool conv_gemm_ok(const ConvGemm& c) {
   if (c.W % 8 == 0 && c.kW >= 1 && c.kH >= 1 && conv_use_fwd2(c) && (int64_t)(c.kH + c.pad_h) * c.W <= 32000 &&
       (int64_t)c.W * c.Hi < (1 << 30) && (int64_t)c.W * c.Ho < (1 << 30))
     return tensor_map_encoder() != nullptr;
-  if (c.W % 8 != 0 || c.kW > 8 || c.kW < 1 || c.kH < 1) return false;
-  const int num_kb = c.kW * c.kH * conv_chunks(c.Ck);
-  if (num_kb > kMaxKb) return false;
-  if ((int64_t)(c.kH + c.pad_h) * c.W > 32000) return false;
-  if (conv_fwd_stages(c) < 3) return false;
-  if ((int64_t)c.W * c.Hi >= (1 << 30) || (int64_t)c.W * c.Ho >= (1 << 30)) return false;
-  return tensor_map_encoder() != nullptr;
+  return false;
 }
 
 bool conv_tc_supported(const ConvGeom& g, int32_t dtype) {
@@ -1047,14 +670,12 @@ bool conv_tc_supported(const ConvGeom& g, int32_t dtype) {
   // only the fast case stays here (filter resident in shared memory, shift-in-epilogue kernels in both directions);
   // every other bf16 geometry is served by the general path of conv_cw.cu
   if (!conv_gemm_ok(f) || !conv_gemm_ok(d) || !conv_use_fwd2(f) || !conv_use_fwd2(d)) return false;
-  if (g.k[0] * g.k[1] * conv_chunks(g.cin) > 2 * kMaxKb) return false;
   return true;
 }
 
 static size_t copies_bytes(const ConvGemm& c) { return align_up((size_t)c.kW * c.W * c.Hi * c.Ck * c.N * 2, 1024); }
-static size_t gemm_copies_bytes(const ConvGemm& c) { return conv_use_fwd2(c) ? 0 : copies_bytes(c); }
 static size_t packed_bytes(const ConvGemm& c) {
-  const int bn = conv_use_fwd2(c) ? 64 : conv_bn(c.Cn);
+  const int bn = 64;
   const size_t rows = (size_t)((c.Cn + bn - 1) / bn) * bn;
   return align_up(rows * (size_t)(c.kW * c.kH * conv_chunks(c.Ck) * 64) * 2, 1024);
 }
@@ -1122,71 +743,7 @@ static int32_t run_conv_gemm(void* out, void* preact, const void* bias, int32_t 
     }
 #undef LB2_FWD2_ACT
   }
-  T* copies = reinterpret_cast<T*>(ws);
-  T* wp = reinterpret_cast<T*>(ws + copies_bytes(c));
-  const int64_t rows = (int64_t)c.Hi * c.Ck * c.N;
-  if (!launch_shift_copies_vec(copies, in, c.W, rows, c.kW, c.pad_w, flat_grid_tc(rows * (c.W / 8)), st))
-    conv_shift_copies_kernel<T><<<flat_grid_tc(rows * ((c.W + 7) / 8)), 256, 0, st>>>(copies, (const T*)in, c.W, rows, c.kW, c.pad_w, -1);
-  conv_pack_filter_kernel<T><<<flat_grid_tc((int64_t)pg.n_rows * pg.k_total), 256, 0, st>>>(wp, (const T*)w, pg);
-  LB2_CHECK_LAUNCH("conv_tc layout passes");
-
-  const int bn = conv_bn(c.Cn);
-  ConvTcParams p{};
-  p.S_out = c.W * c.Ho;
-  p.n_img = c.N;
-  p.n_out = c.Cn;
-  p.tiles_m = (p.S_out + kConvBM - 1) / kConvBM;
-  p.tiles_n = (c.Cn + bn - 1) / bn;
-  const int chunks = conv_chunks(c.Ck);
-  p.num_kb = c.kW * c.kH * chunks;
-  p.stages = conv_fwd_stages(c);
-  for (int kb = 0; kb < p.num_kb; ++kb) {
-    const int tap = kb / chunks, tw = tap % c.kW, th = tap / c.kW;
-    p.a_shift[kb] = (int16_t)((th - c.pad_h) * c.W);
-    p.a_chan[kb] = (int16_t)((kb % chunks) * 64);
-    p.a_copy[kb] = (int8_t)tw;
-  }
-  // A: bf16, MN-major, two boxes of (64 positions x 64 channels): LBO = 8192, SBO = 1024, 16 channels (2048 B) per MMA
-  p.a_desc_hi = (uint32_t)((1024u >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
-  p.a_desc_lbo = ((8192u >> 4) & 0x3FFFu) << 16;
-  p.a_k_advance = 2048u >> 4;
-  // B: bf16, K-major rows of 128 bytes: SBO = 1024, 32 bytes per MMA
-  p.b_desc_hi = p.a_desc_hi;
-  p.b_desc_lbo = 1u << 16;
-  p.b_k_advance = 32u >> 4;
-  p.idesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | (0u << 16) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(kConvBM >> 4) << 24);
-  p.y = out; p.preact = preact; p.bias = bias; p.act = act;
-  p.status = device_status_word();
-  LB2_REQUIRE(p.status != nullptr, LB2_LAUNCH_FAIL, "conv_tc: device status word unavailable");
-  CUtensorMap mX, mW;
-  if (!bf16_map_4d(&mX, copies, (int64_t)c.W * c.Hi, c.Ck, c.N, c.kW, 64, 64) ||
-      !bf16_map_2d(&mW, wp, pg.k_total, pg.n_rows, 64, bn))
-    return fail(LB2_LAUNCH_FAIL, "conv_tc: cuTensorMapEncodeTiled failed");
-  const int smem = p.num_kb * bn * 128 + p.stages * kConvBM * 128 + 1024 + 256 + 64 * 8;
-  const int tiles_per_n = p.tiles_m * p.n_img;
-  int per_n = sm_count() / p.tiles_n;
-  if (per_n > tiles_per_n) per_n = tiles_per_n;
-  if (per_n < 1) per_n = 1;
-  const int grid = per_n * p.tiles_n;
-  auto launch = [&](auto kernel) -> int32_t {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return fail(LB2_LAUNCH_FAIL, "conv_tc: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
-    kernel<<<grid, kConvThreads, smem, st>>>(mX, mW, p);
-    LB2_CHECK_LAUNCH("conv_tc_fwd");
-    return LB2_OK;
-  };
-  if (bn == 64) {
-    switch (act) {
-      case LB2_ACT_IDENTITY: return launch(conv_tc_fwd_kernel<64, LB2_ACT_IDENTITY>);
-      case LB2_ACT_RELU: return launch(conv_tc_fwd_kernel<64, LB2_ACT_RELU>);
-      default: return launch(conv_tc_fwd_kernel<64, -1>);
-    }
-  }
-  switch (act) {
-    case LB2_ACT_IDENTITY: return launch(conv_tc_fwd_kernel<128, LB2_ACT_IDENTITY>);
-    case LB2_ACT_RELU: return launch(conv_tc_fwd_kernel<128, LB2_ACT_RELU>);
-    default: return launch(conv_tc_fwd_kernel<128, -1>);
-  }
+  return fail(LB2_BAD_SHAPE, "conv_tc: geometry outside the resident-filter fast case");
 }
 
 static ConvGemm fwd_gemm(const ConvGeom& g) {
@@ -1199,7 +756,7 @@ static PackGeom pack_geom(const ConvGeom& g, const ConvGemm& c, int transpose) {
   PackGeom pg{};
   pg.kW = g.k[0]; pg.kH = g.k[1]; pg.cin = g.cin; pg.cout = g.cout; pg.flip = g.flip; pg.transpose = transpose;
   pg.chunks = conv_chunks(c.Ck);
-  const int bn = conv_use_fwd2(c) ? 64 : conv_bn(c.Cn);
+  const int bn = 64;
   pg.n_rows = ((c.Cn + bn - 1) / bn) * bn;
   pg.k_total = c.kW * c.kH * pg.chunks * 64;
   return pg;
@@ -1208,7 +765,7 @@ static PackGeom pack_geom(const ConvGeom& g, const ConvGemm& c, int transpose) {
 size_t conv_tc_fwd_workspace_bytes(const ConvGeom& g, int32_t dtype) {
   if (dtype == LB2_F32) return conv_tc_f32_fwd_workspace_bytes(g);
   const ConvGemm c = fwd_gemm(g);
-  return gemm_copies_bytes(c) + packed_bytes(c);
+  return packed_bytes(c);
 }
 
 int32_t conv_tc_fwd(void* y, void* preact, const void* x, const void* w, const void* bias, const ConvGeom& g,
@@ -1219,33 +776,6 @@ int32_t conv_tc_fwd(void* y, void* preact, const void* x, const void* w, const v
 }
 
 // ---- filter gradient plan
-struct WgPlan {
-  int bn, chunks, n_rg, m_tiles, tiles_n, s_blocks, kb_total, splits, kb_per_split, stages, n_pad;
-};
-static WgPlan wg_plan(const ConvGeom& g) {
-  WgPlan w{};
-  w.bn = conv_bn(g.cout);
-  w.chunks = conv_chunks(g.cin);
-  w.n_rg = g.k[0] * g.k[1] * w.chunks;
-  w.m_tiles = (w.n_rg + 1) / 2;
-  w.tiles_n = (g.cout + w.bn - 1) / w.bn;
-  w.n_pad = w.tiles_n * w.bn;
-  const int S_out = g.out[0] * g.out[1];
-  w.s_blocks = (S_out + 63) / 64;
-  w.kb_total = g.batch * w.s_blocks;
-  int splits = sm_count() / (w.m_tiles * w.tiles_n);
-  if (splits < 1) splits = 1;
-  if (splits > w.kb_total) splits = w.kb_total;
-  w.kb_per_split = (w.kb_total + splits - 1) / splits;
-  w.splits = (w.kb_total + w.kb_per_split - 1) / w.kb_per_split;
-  w.stages = (200 * 1024) / (kConvBM * 128 + w.bn * 128);
-  if (w.stages > 8) w.stages = 8;
-  return w;
-}
-static size_t wg_partial_bytes(const WgPlan& w) {
-  return align_up((size_t)w.splits * w.m_tiles * 128 * w.n_pad * sizeof(float), 1024);
-}
-
 // wide-N variant: kernel width <= 4 (N = kW * 64 <= 256), kH <= 16
 struct Wg2Plan {
   bool ok;
@@ -1271,15 +801,12 @@ static Wg2Plan wg2_plan(const ConvGeom& g) {
 static size_t wg2_partial_bytes(const ConvGeom& g, const Wg2Plan& w) {
   return align_up((size_t)w.splits * w.groups * 128 * (g.k[0] * 64) * sizeof(float), 1024);
 }
-static size_t wg_any_partial_bytes(const ConvGeom& g) {
-  const Wg2Plan w2 = wg2_plan(g);
-  return w2.ok ? wg2_partial_bytes(g, w2) : wg_partial_bytes(wg_plan(g));
-}
+static size_t wg_any_partial_bytes(const ConvGeom& g) { return wg2_partial_bytes(g, wg2_plan(g)); }
 
 size_t conv_tc_bwd_workspace_bytes(const ConvGeom& g, int32_t dtype) {
   if (dtype == LB2_F32) return conv_tc_f32_bwd_workspace_bytes(g);
   const ConvGemm d = dgrad_gemm(g), f = fwd_gemm(g);
-  const size_t dgrad = gemm_copies_bytes(d) + packed_bytes(d);
+  const size_t dgrad = packed_bytes(d);
   const size_t wgrad = copies_bytes(f) + wg_any_partial_bytes(g);
   return dgrad > wgrad ? dgrad : wgrad;   // the two gradients run one after the other in the same region
 }
@@ -1295,7 +822,6 @@ int32_t conv_tc_wgrad(void* dw, const void* x, const void* gy, const ConvGeom& g
   using T = __nv_bfloat16;
   uint8_t* ws = static_cast<uint8_t*>(ws_);
   const ConvGemm f = fwd_gemm(g);
-  const WgPlan w = wg_plan(g);
   T* copies = reinterpret_cast<T*>(ws);
   float* partial = reinterpret_cast<float*>(ws + copies_bytes(f));
   const int64_t rows = (int64_t)f.Hi * f.Ck * f.N;
@@ -1346,45 +872,7 @@ int32_t conv_tc_wgrad(void* dw, const void* x, const void* gy, const ConvGeom& g
     LB2_CHECK_LAUNCH("conv_wgrad2_reduce");
     return LB2_OK;
   }
-  ConvWgParams p{};
-  p.S_out = g.out[0] * g.out[1];
-  p.n_img = g.batch; p.n_out = g.cout;
-  p.s_blocks = w.s_blocks; p.m_tiles = w.m_tiles; p.tiles_n = w.tiles_n; p.splits = w.splits;
-  p.kb_total = w.kb_total; p.kb_per_split = w.kb_per_split; p.n_rg = w.n_rg; p.stages = w.stages;
-  p.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(w.bn >> 3) << 17) | ((uint32_t)(kConvBM >> 4) << 24);
-  p.desc_hi = (uint32_t)((1024u >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
-  p.desc_lbo = 1u << 16;
-  p.k_advance = 32u >> 4;
-  p.partial = partial; p.n_pad = w.n_pad;
-  p.status = device_status_word();
-  LB2_REQUIRE(p.status != nullptr, LB2_LAUNCH_FAIL, "conv_tc: device status word unavailable");
-  for (int rg = 0; rg < w.n_rg; ++rg) {
-    const int tap = rg / w.chunks, tw = tap % f.kW, th = tap / f.kW;
-    p.rg_shift[rg] = (int16_t)((th - f.pad_h) * f.W);
-    p.rg_chan[rg] = (int16_t)((rg % w.chunks) * 64);
-    p.rg_copy[rg] = (int8_t)tw;
-  }
-  CUtensorMap mX, mG;
-  if (!bf16_map_4d(&mX, copies, (int64_t)f.W * f.Hi, f.Ck, f.N, f.kW, 64, 64) ||
-      !bf16_map_4d(&mG, gy, (int64_t)p.S_out, g.cout, g.batch, 1, 64, w.bn))
-    return fail(LB2_LAUNCH_FAIL, "conv_tc: cuTensorMapEncodeTiled failed");
-  const int smem = w.stages * (kConvBM * 128 + w.bn * 128) + 1024 + 256 + 64 * 8;
-  const int items = w.m_tiles * w.tiles_n * w.splits;
-  const int grid = items < sm_count() ? items : sm_count();
-  auto launch = [&](auto kernel) -> int32_t {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return fail(LB2_LAUNCH_FAIL, "conv_tc: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
-    kernel<<<grid, kConvThreads, smem, st>>>(mX, mG, p);
-    LB2_CHECK_LAUNCH("conv_tc_wgrad");
-    return LB2_OK;
-  };
-  int32_t rc = w.bn == 64 ? launch(conv_tc_wgrad_kernel<64>) : launch(conv_tc_wgrad_kernel<128>);
-  if (rc != LB2_OK) return rc;
-  const int64_t nw = (int64_t)g.k[0] * g.k[1] * g.cin * g.cout;
-  conv_wgrad_reduce_kernel<T><<<flat_grid_tc(nw), 256, 0, st>>>((T*)dw, partial, g.k[0], g.k[1], g.cin, g.cout, g.flip, w.chunks,
-                                                              w.m_tiles * 128, w.n_pad, w.splits);
-  LB2_CHECK_LAUNCH("conv_wgrad_reduce");
-  return LB2_OK;
+  return fail(LB2_BAD_SHAPE, "conv_tc: geometry outside the resident-filter fast case");
 }
 
 }  // namespace lb2

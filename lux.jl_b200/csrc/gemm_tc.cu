@@ -899,12 +899,17 @@ int32_t gemm_tc_launch(void* D, int64_t ldd, GemmOperand A, GemmOperand B, int64
   p.tiles_m = (int)((Mm + tile_m - 1) / tile_m);
   p.tiles_n = (int)((Nn + tile_n - 1) / tile_n);
   p.num_kb = (int)((Kc + bk - 1) / bk);
-  // Band height of the tile order: the tiles in flight (one per CTA or CTA pair) should cover a roughly square
-  // block of the output, i.e. about sqrt(workers * tile_n / tile_m) tile rows.
+  // Band height of the tile order. If the A panels of all tile rows fit a third of L2 together, walk all of them per
+  // tile column (A stays resident, B streams through once). Otherwise take as many tile rows as fit that budget, but
+  // not fewer than what makes the tiles in flight (one per CTA or CTA pair) cover a roughly square block of the
+  // output, i.e. about sqrt(workers * tile_n / tile_m) tile rows.
   {
     const int workers = pair ? sm_count() / 2 : sm_count();
-    int h = 1;
-    while ((h + 1) * (h + 1) * tile_m <= workers * tile_n) ++h;
+    int h_sq = 1;
+    while ((h_sq + 1) * (h_sq + 1) * tile_m <= workers * tile_n) ++h_sq;
+    const double panel_bytes = (double)tile_m * (double)Kc * es;
+    int h = (int)(48.0 * 1024 * 1024 / panel_bytes);
+    if (h < h_sq) h = h_sq;
     p.raster_h = h < p.tiles_m ? h : p.tiles_m;
     if (p.raster_h < 1) p.raster_h = 1;
   }

@@ -264,6 +264,131 @@ __global__ void __launch_bounds__(256) pool2d_bwd_kernel(T* __restrict__ dx, con
   }
 }
 
+// ---- 2-D windows, planes staged in shared memory ------------------------------------------------------------------
+// The direct kernels above issue chains of dependent 2-byte global loads per element (x, then the y of each window,
+// then possibly a scan of the window) and are latency-bound. When a plane of x together with its y and dy planes fits
+// in shared memory, a CTA stages them with 16-byte loads, evaluates every window from shared memory and writes the
+// result rows coalesced. Threads form (256 / Wp) rows of Wp columns, Wp = the row length rounded up to a power of two.
+template <typename T>
+__device__ __forceinline__ void pool_stage(T* dst, const T* src, int n, bool vec) {
+  if (vec) {
+    const int nv = (int)((size_t)n * sizeof(T) / 16);
+    for (int i = threadIdx.x; i < nv; i += blockDim.x) reinterpret_cast<uint4*>(dst)[i] = __ldg(reinterpret_cast<const uint4*>(src) + i);
+  } else {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) dst[i] = src[i];
+  }
+}
+
+template <typename T, bool MAX, int STRIDE>
+__global__ void __launch_bounds__(256) pool2d_fwd_smem_kernel(T* __restrict__ y, const T* __restrict__ x, const PoolGeom g, int lw,
+                                                              int vec) {
+  extern __shared__ __align__(16) uint8_t pool_smem[];
+  T* sx = reinterpret_cast<T*>(pool_smem);
+  const int W = g.in[0], H = g.in[1], OW = g.out[0], OH = g.out[1];
+  const int sw = STRIDE ? STRIDE : g.stride[0], sh = STRIDE ? STRIDE : g.stride[1];
+  const int tx = threadIdx.x & ((1 << lw) - 1), ty = threadIdx.x >> lw, rows = 256 >> lw;
+  const float inv_win = 1.f / (float)(g.k[0] * g.k[1]);
+  for (int64_t plane = blockIdx.x; plane < g.planes; plane += gridDim.x) {
+    __syncthreads();
+    pool_stage(sx, x + plane * (int64_t)(W * H), W * H, vec != 0);
+    __syncthreads();
+    T* yp = y + plane * (int64_t)(OW * OH);
+    if (tx < OW) {
+      const int w0 = tx * sw - g.pad[0];
+      const int kw_lo = w0 < 0 ? -w0 : 0, kw_hi = min(g.k[0], W - w0);
+      for (int oh = ty; oh < OH; oh += rows) {
+        const int h0 = oh * sh - g.pad[1];
+        const int kh_lo = h0 < 0 ? -h0 : 0, kh_hi = min(g.k[1], H - h0);
+        float acc = MAX ? -INFINITY : 0.f;
+        for (int kh = kh_lo; kh < kh_hi; ++kh) {
+          const T* row = sx + (h0 + kh) * W + w0;
+          for (int kw = kw_lo; kw < kw_hi; ++kw) {
+            const float v = to_f32(row[kw]);
+            if (MAX) acc = fmaxf(acc, v); else acc += v;
+          }
+        }
+        yp[oh * OW + tx] = from_f32<T>(MAX ? acc : acc * inv_win);
+      }
+    }
+  }
+}
+
+template <typename T, bool MAX, int STRIDE>
+__global__ void __launch_bounds__(256) pool2d_bwd_smem_kernel(T* __restrict__ dx, const T* __restrict__ dy, const T* __restrict__ y,
+                                                              const T* __restrict__ x, const PoolGeom g, int lw, int vec_in, int vec_out,
+                                                              int off_y, int off_dy) {
+  extern __shared__ __align__(16) uint8_t pool_smem[];
+  T* sx = reinterpret_cast<T*>(pool_smem);
+  T* sy = reinterpret_cast<T*>(pool_smem + off_y);
+  T* sdy = reinterpret_cast<T*>(pool_smem + off_dy);
+  const int W = g.in[0], H = g.in[1], OW = g.out[0], OH = g.out[1], kW = g.k[0], kH = g.k[1];
+  const int sw = STRIDE ? STRIDE : g.stride[0], sh = STRIDE ? STRIDE : g.stride[1];
+  const int tx = threadIdx.x & ((1 << lw) - 1), ty = threadIdx.x >> lw, rows = 256 >> lw;
+  const float inv_win = 1.f / (float)(kW * kH);
+  for (int64_t plane = blockIdx.x; plane < g.planes; plane += gridDim.x) {
+    __syncthreads();
+    if (MAX) {
+      pool_stage(sx, x + plane * (int64_t)(W * H), W * H, vec_in != 0);
+      pool_stage(sy, y + plane * (int64_t)(OW * OH), OW * OH, vec_out != 0);
+    }
+    pool_stage(sdy, dy + plane * (int64_t)(OW * OH), OW * OH, vec_out != 0);
+    __syncthreads();
+    T* dxp = dx + plane * (int64_t)(W * H);
+    if (tx < W) {
+      const int w = tx;
+      const int topw = w + g.pad[0], botw = topw - (kW - 1);
+      const int ow_lo = botw <= 0 ? 0 : div_stride<STRIDE>(botw + sw - 1, sw);
+      const int ow_hi = min(OW - 1, div_stride<STRIDE>(topw, sw));
+      for (int h = ty; h < H; h += rows) {
+        const int top = h + g.pad[1], bot = top - (kH - 1);
+        const int oh_lo = bot <= 0 ? 0 : div_stride<STRIDE>(bot + sh - 1, sh);
+        const int oh_hi = min(OH - 1, div_stride<STRIDE>(top, sh));
+        const float xv = MAX ? to_f32(sx[h * W + w]) : 0.f;
+        float acc = 0.f;
+        for (int oh = oh_lo; oh <= oh_hi; ++oh) {
+          for (int ow = ow_lo; ow <= ow_hi; ++ow) {
+            const int o = oh * OW + ow;
+            if (MAX) {
+              const float ym = to_f32(sy[o]);
+              if (xv == ym) {
+                // the gradient goes to the FIRST element of the window equal to its maximum (kw fastest, then kh)
+                const int h0 = oh * sh - g.pad[1], w0 = ow * sw - g.pad[0];
+                bool first = true;
+                for (int kh = max(0, -h0); first && h0 + kh <= h; ++kh) {
+                  const int kw_end = (h0 + kh == h) ? (w - w0) : min(kW, W - w0);
+                  for (int kw = max(0, -w0); kw < kw_end; ++kw)
+                    if (to_f32(sx[(h0 + kh) * W + w0 + kw]) == ym) { first = false; break; }
+                }
+                if (first) acc += to_f32(sdy[o]);
+              }
+            } else {
+              acc += to_f32(sdy[o]) * inv_win;
+            }
+          }
+        }
+        dxp[h * W + w] = from_f32<T>(acc);
+      }
+    }
+  }
+}
+
+// pointer types of a staged kernel's output / input parameters (so one generic launcher serves both storage types)
+template <typename T, typename... R> T* pool_arg_y(void (*)(T*, const T*, R...));
+template <typename T, typename... R> const T* pool_arg_x(void (*)(T*, const T*, R...));
+
+// shared-memory layout of the staged kernels: x plane | y plane | dy plane, each starting on 16 bytes
+struct PoolSmem { int off_y, off_dy, bytes, lw_in, lw_out; bool ok; };
+static PoolSmem pool_smem_plan(const PoolGeom& g, size_t es, bool bwd) {
+  PoolSmem p{};
+  const size_t xb = align_up((size_t)g.in[0] * g.in[1] * es, 16), yb = align_up((size_t)g.out[0] * g.out[1] * es, 16);
+  p.off_y = (int)xb; p.off_dy = (int)(xb + yb);
+  p.bytes = (int)(bwd ? xb + 2 * yb : xb);
+  auto lg = [](int v) { int l = 5; while ((1 << l) < v) ++l; return l; };
+  p.lw_in = lg(g.in[0]); p.lw_out = lg(g.out[0]);
+  p.ok = p.bytes <= 96 * 1024 && p.lw_in <= 8 && p.lw_out <= 8 && g.out[0] >= 1 && g.out[1] >= 1;
+  return p;
+}
+
 static bool pool_is_2d_plain(const PoolGeom& g) {
   return g.in[2] == 1 && g.k[2] == 1 && g.out[2] == 1 && g.dil[0] == 1 && g.dil[1] == 1 && g.pad[2] == 0 &&
          (int64_t)g.in[0] * g.in[1] < ((int64_t)1 << 30);
@@ -340,6 +465,24 @@ int32_t lb2_pool_fwd(void* y, const void* x, const lb2_pool_desc* d, int32_t kin
   }
   if (pool_is_2d_plain(g)) {
     const bool same = g.stride[0] == g.stride[1];
+    const PoolSmem sp = pool_smem_plan(g, dtype_size(dtype), false);
+    if (sp.ok) {
+      const int vec = (aligned_to(x, 16) && ((size_t)g.in[0] * g.in[1] * dtype_size(dtype)) % 16 == 0) ? 1 : 0;
+      const int st2 = same && g.stride[0] <= 2 ? g.stride[0] : 0;
+      auto launch = [&](auto kernel) -> int32_t {
+        if (sp.bytes > 48 * 1024) {
+          cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, sp.bytes);
+          if (e != cudaSuccess) return fail(LB2_LAUNCH_FAIL, "pool2d_fwd: cannot reserve %d bytes of shared memory: %s", sp.bytes, cudaGetErrorString(e));
+        }
+        kernel<<<plane_grid(g.planes), 256, sp.bytes, st>>>((decltype(pool_arg_y(kernel)))y, (decltype(pool_arg_x(kernel)))x, g, sp.lw_out, vec);
+        LB2_CHECK_LAUNCH("pool2d_fwd (staged)");
+        return LB2_OK;
+      };
+      LB2_DISPATCH_DTYPE(dtype, {
+        if (kind == LB2_POOL_MAX) return st2 == 1 ? launch(pool2d_fwd_smem_kernel<T, true, 1>) : st2 == 2 ? launch(pool2d_fwd_smem_kernel<T, true, 2>) : launch(pool2d_fwd_smem_kernel<T, true, 0>);
+        return st2 == 1 ? launch(pool2d_fwd_smem_kernel<T, false, 1>) : st2 == 2 ? launch(pool2d_fwd_smem_kernel<T, false, 2>) : launch(pool2d_fwd_smem_kernel<T, false, 0>);
+      });
+    }
     LB2_DISPATCH_DTYPE(dtype, {
       if (kind == LB2_POOL_MAX) {
         if (same && g.stride[0] == 1) pool2d_fwd_kernel<T, true, 1><<<plane_grid(g.planes), 256, 0, st>>>((T*)y, (const T*)x, g);
@@ -396,6 +539,26 @@ int32_t lb2_pool_bwd(void* dx, const void* dy, const void* y, const void* x, con
   }
   if (pool_is_2d_plain(g)) {
     const bool same = g.stride[0] == g.stride[1];
+    const PoolSmem sp = pool_smem_plan(g, es, true);
+    if (sp.ok) {
+      const int vec_in = (aligned_to(x, 16) && ((size_t)g.in[0] * g.in[1] * es) % 16 == 0) ? 1 : 0;
+      const int vec_out = (aligned_to(dy, 16) && aligned_to(y, 16) && ((size_t)g.out[0] * g.out[1] * es) % 16 == 0) ? 1 : 0;
+      const int st2 = same && g.stride[0] <= 2 ? g.stride[0] : 0;
+      auto launch = [&](auto kernel) -> int32_t {
+        if (sp.bytes > 48 * 1024) {
+          cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, sp.bytes);
+          if (e != cudaSuccess) return fail(LB2_LAUNCH_FAIL, "pool2d_bwd: cannot reserve %d bytes of shared memory: %s", sp.bytes, cudaGetErrorString(e));
+        }
+        kernel<<<plane_grid(g.planes), 256, sp.bytes, st>>>((decltype(pool_arg_y(kernel)))dx, (decltype(pool_arg_x(kernel)))dy, (decltype(pool_arg_x(kernel)))y,
+                                                            (decltype(pool_arg_x(kernel)))x, g, sp.lw_in, vec_in, vec_out, sp.off_y, sp.off_dy);
+        LB2_CHECK_LAUNCH("pool2d_bwd (staged)");
+        return LB2_OK;
+      };
+      LB2_DISPATCH_DTYPE(dtype, {
+        if (kind == LB2_POOL_MAX) return st2 == 1 ? launch(pool2d_bwd_smem_kernel<T, true, 1>) : st2 == 2 ? launch(pool2d_bwd_smem_kernel<T, true, 2>) : launch(pool2d_bwd_smem_kernel<T, true, 0>);
+        return st2 == 1 ? launch(pool2d_bwd_smem_kernel<T, false, 1>) : st2 == 2 ? launch(pool2d_bwd_smem_kernel<T, false, 2>) : launch(pool2d_bwd_smem_kernel<T, false, 0>);
+      });
+    }
     LB2_DISPATCH_DTYPE(dtype, {
       if (kind == LB2_POOL_MAX) {
         if (same && g.stride[0] == 1) pool2d_bwd_kernel<T, true, 1><<<plane_grid(g.planes), 256, 0, st>>>((T*)dx, (const T*)dy, (const T*)y, (const T*)x, g);
