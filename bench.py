@@ -237,7 +237,8 @@ def capture(step, torch, device):
             step()                                   # allocator and library caches warm on the capture stream
         torch.cuda.current_stream(device).wait_stream(side)
         torch.cuda.synchronize(device)
-        with torch.cuda.graph(g):
+        # thread_local: the NCCL watchdog and the clock sampler are other threads of this process
+        with torch.cuda.graph(g, capture_error_mode="thread_local"):
             out = step()
         torch.cuda.synchronize(device)
         return g, out
@@ -306,9 +307,10 @@ def run_gpu_arm(args):
     device = torch.device("cuda", local)
     dist = None
     if world > 1:
+        from luxlib_b200 import distributed as D
+        D.initialize(D.NCCLBackend)            # DistributedUtils.initialize: process group from the launcher's environment
         import torch.distributed as dist_mod
         dist = dist_mod
-        dist.init_process_group("nccl", device_id=device)
     lib = _cabi.load()
 
     # every rank holds the same parameters and its own batch shard

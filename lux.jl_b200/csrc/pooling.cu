@@ -269,15 +269,21 @@ __global__ void __launch_bounds__(256) pool2d_bwd_kernel(T* __restrict__ dx, con
 // then possibly a scan of the window) and are latency-bound. When a plane of x together with its y and dy planes fits
 // in shared memory, a CTA stages them with 16-byte loads, evaluates every window from shared memory and writes the
 // result rows coalesced. Threads form (256 / Wp) rows of Wp columns, Wp = the row length rounded up to a power of two.
+// Stages n elements into shared memory. With `vec` (16-byte aligned source, n*sizeof(T) a multiple of 16) the copies
+// are asynchronous 16-byte global->shared copies, all in flight at once; pool_stage_wait() must precede the barrier
+// that publishes them.
 template <typename T>
 __device__ __forceinline__ void pool_stage(T* dst, const T* src, int n, bool vec) {
   if (vec) {
     const int nv = (int)((size_t)n * sizeof(T) / 16);
-    for (int i = threadIdx.x; i < nv; i += blockDim.x) reinterpret_cast<uint4*>(dst)[i] = __ldg(reinterpret_cast<const uint4*>(src) + i);
+    const uint32_t d0 = (uint32_t)__cvta_generic_to_shared(dst);
+    for (int i = threadIdx.x; i < nv; i += blockDim.x)
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d0 + 16u * (uint32_t)i), "l"(reinterpret_cast<const uint4*>(src) + i) : "memory");
   } else {
     for (int i = threadIdx.x; i < n; i += blockDim.x) dst[i] = src[i];
   }
 }
+__device__ __forceinline__ void pool_stage_wait() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
 template <typename T, bool MAX, int STRIDE>
 __global__ void __launch_bounds__(256) pool2d_fwd_smem_kernel(T* __restrict__ y, const T* __restrict__ x, const PoolGeom g, int lw,
@@ -291,6 +297,7 @@ __global__ void __launch_bounds__(256) pool2d_fwd_smem_kernel(T* __restrict__ y,
   for (int64_t plane = blockIdx.x; plane < g.planes; plane += gridDim.x) {
     __syncthreads();
     pool_stage(sx, x + plane * (int64_t)(W * H), W * H, vec != 0);
+    pool_stage_wait();
     __syncthreads();
     T* yp = y + plane * (int64_t)(OW * OH);
     if (tx < OW) {
@@ -313,26 +320,45 @@ __global__ void __launch_bounds__(256) pool2d_fwd_smem_kernel(T* __restrict__ y,
   }
 }
 
+// Backward. Max pooling: a first pass, one thread per OUTPUT, finds the position of each window's first maximal
+// element (scan in kw-fastest order with a strict comparison, NNlib's tie rule) and leaves it in shared memory; the
+// second pass, one thread per INPUT, adds dy of the covering windows whose recorded position it is. Both passes are
+// free of data-dependent branches, so warps do not serialise on ties. The forward result y is not needed.
 template <typename T, bool MAX, int STRIDE>
 __global__ void __launch_bounds__(256) pool2d_bwd_smem_kernel(T* __restrict__ dx, const T* __restrict__ dy, const T* __restrict__ y,
                                                               const T* __restrict__ x, const PoolGeom g, int lw, int vec_in, int vec_out,
-                                                              int off_y, int off_dy) {
+                                                              int off_idx, int off_dy) {
   extern __shared__ __align__(16) uint8_t pool_smem[];
   T* sx = reinterpret_cast<T*>(pool_smem);
-  T* sy = reinterpret_cast<T*>(pool_smem + off_y);
+  int* sidx = reinterpret_cast<int*>(pool_smem + off_idx);
   T* sdy = reinterpret_cast<T*>(pool_smem + off_dy);
+  (void)y;
   const int W = g.in[0], H = g.in[1], OW = g.out[0], OH = g.out[1], kW = g.k[0], kH = g.k[1];
   const int sw = STRIDE ? STRIDE : g.stride[0], sh = STRIDE ? STRIDE : g.stride[1];
   const int tx = threadIdx.x & ((1 << lw) - 1), ty = threadIdx.x >> lw, rows = 256 >> lw;
   const float inv_win = 1.f / (float)(kW * kH);
   for (int64_t plane = blockIdx.x; plane < g.planes; plane += gridDim.x) {
     __syncthreads();
-    if (MAX) {
-      pool_stage(sx, x + plane * (int64_t)(W * H), W * H, vec_in != 0);
-      pool_stage(sy, y + plane * (int64_t)(OW * OH), OW * OH, vec_out != 0);
-    }
+    if (MAX) pool_stage(sx, x + plane * (int64_t)(W * H), W * H, vec_in != 0);
     pool_stage(sdy, dy + plane * (int64_t)(OW * OH), OW * OH, vec_out != 0);
+    pool_stage_wait();
     __syncthreads();
+    if (MAX) {
+      for (int o = threadIdx.x; o < OW * OH; o += blockDim.x) {
+        const int oh = o / OW, ow = o - oh * OW;
+        const int h0 = oh * sh - g.pad[1], w0 = ow * sw - g.pad[0];
+        float best = -INFINITY;
+        int where = -1;
+        for (int kh = max(0, -h0); kh < min(kH, H - h0); ++kh)
+          for (int kw = max(0, -w0); kw < min(kW, W - w0); ++kw) {
+            const int i = (h0 + kh) * W + w0 + kw;
+            const float v = to_f32(sx[i]);
+            if (v > best || where < 0) { best = v; where = i; }
+          }
+        sidx[o] = where;
+      }
+      __syncthreads();
+    }
     T* dxp = dx + plane * (int64_t)(W * H);
     if (tx < W) {
       const int w = tx;
@@ -343,30 +369,15 @@ __global__ void __launch_bounds__(256) pool2d_bwd_smem_kernel(T* __restrict__ dx
         const int top = h + g.pad[1], bot = top - (kH - 1);
         const int oh_lo = bot <= 0 ? 0 : div_stride<STRIDE>(bot + sh - 1, sh);
         const int oh_hi = min(OH - 1, div_stride<STRIDE>(top, sh));
-        const float xv = MAX ? to_f32(sx[h * W + w]) : 0.f;
+        const int i = h * W + w;
         float acc = 0.f;
-        for (int oh = oh_lo; oh <= oh_hi; ++oh) {
+        for (int oh = oh_lo; oh <= oh_hi; ++oh)
           for (int ow = ow_lo; ow <= ow_hi; ++ow) {
             const int o = oh * OW + ow;
-            if (MAX) {
-              const float ym = to_f32(sy[o]);
-              if (xv == ym) {
-                // the gradient goes to the FIRST element of the window equal to its maximum (kw fastest, then kh)
-                const int h0 = oh * sh - g.pad[1], w0 = ow * sw - g.pad[0];
-                bool first = true;
-                for (int kh = max(0, -h0); first && h0 + kh <= h; ++kh) {
-                  const int kw_end = (h0 + kh == h) ? (w - w0) : min(kW, W - w0);
-                  for (int kw = max(0, -w0); kw < kw_end; ++kw)
-                    if (to_f32(sx[(h0 + kh) * W + w0 + kw]) == ym) { first = false; break; }
-                }
-                if (first) acc += to_f32(sdy[o]);
-              }
-            } else {
-              acc += to_f32(sdy[o]) * inv_win;
-            }
+            const float d = to_f32(sdy[o]);
+            if (MAX) acc += (sidx[o] == i) ? d : 0.f; else acc += d * inv_win;
           }
-        }
-        dxp[h * W + w] = from_f32<T>(acc);
+        dxp[i] = from_f32<T>(acc);
       }
     }
   }
@@ -376,13 +387,14 @@ __global__ void __launch_bounds__(256) pool2d_bwd_smem_kernel(T* __restrict__ dx
 template <typename T, typename... R> T* pool_arg_y(void (*)(T*, const T*, R...));
 template <typename T, typename... R> const T* pool_arg_x(void (*)(T*, const T*, R...));
 
-// shared-memory layout of the staged kernels: x plane | y plane | dy plane, each starting on 16 bytes
-struct PoolSmem { int off_y, off_dy, bytes, lw_in, lw_out; bool ok; };
+// shared-memory layout of the staged kernels: x plane | first-maximum positions | dy plane, each starting on 16 bytes
+struct PoolSmem { int off_idx, off_dy, bytes, lw_in, lw_out; bool ok; };
 static PoolSmem pool_smem_plan(const PoolGeom& g, size_t es, bool bwd) {
   PoolSmem p{};
   const size_t xb = align_up((size_t)g.in[0] * g.in[1] * es, 16), yb = align_up((size_t)g.out[0] * g.out[1] * es, 16);
-  p.off_y = (int)xb; p.off_dy = (int)(xb + yb);
-  p.bytes = (int)(bwd ? xb + 2 * yb : xb);
+  const size_t ib = align_up((size_t)g.out[0] * g.out[1] * sizeof(int), 16);   // first-maximum positions, one per window
+  p.off_idx = (int)xb; p.off_dy = (int)(xb + ib);
+  p.bytes = (int)(bwd ? xb + ib + yb : xb);
   auto lg = [](int v) { int l = 5; while ((1 << l) < v) ++l; return l; };
   p.lw_in = lg(g.in[0]); p.lw_out = lg(g.out[0]);
   p.ok = p.bytes <= 96 * 1024 && p.lw_in <= 8 && p.lw_out <= 8 && g.out[0] >= 1 && g.out[1] >= 1;
@@ -542,7 +554,7 @@ int32_t lb2_pool_bwd(void* dx, const void* dy, const void* y, const void* x, con
     const PoolSmem sp = pool_smem_plan(g, es, true);
     if (sp.ok) {
       const int vec_in = (aligned_to(x, 16) && ((size_t)g.in[0] * g.in[1] * es) % 16 == 0) ? 1 : 0;
-      const int vec_out = (aligned_to(dy, 16) && aligned_to(y, 16) && ((size_t)g.out[0] * g.out[1] * es) % 16 == 0) ? 1 : 0;
+      const int vec_out = (aligned_to(dy, 16) && ((size_t)g.out[0] * g.out[1] * es) % 16 == 0) ? 1 : 0;
       const int st2 = same && g.stride[0] <= 2 ? g.stride[0] : 0;
       auto launch = [&](auto kernel) -> int32_t {
         if (sp.bytes > 48 * 1024) {
@@ -550,7 +562,7 @@ int32_t lb2_pool_bwd(void* dx, const void* dy, const void* y, const void* x, con
           if (e != cudaSuccess) return fail(LB2_LAUNCH_FAIL, "pool2d_bwd: cannot reserve %d bytes of shared memory: %s", sp.bytes, cudaGetErrorString(e));
         }
         kernel<<<plane_grid(g.planes), 256, sp.bytes, st>>>((decltype(pool_arg_y(kernel)))dx, (decltype(pool_arg_x(kernel)))dy, (decltype(pool_arg_x(kernel)))y,
-                                                            (decltype(pool_arg_x(kernel)))x, g, sp.lw_in, vec_in, vec_out, sp.off_y, sp.off_dy);
+                                                            (decltype(pool_arg_x(kernel)))x, g, sp.lw_in, vec_in, vec_out, sp.off_idx, sp.off_dy);
         LB2_CHECK_LAUNCH("pool2d_bwd (staged)");
         return LB2_OK;
       };
