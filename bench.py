@@ -251,8 +251,11 @@ def capture(step, torch, device):
         return None, None
 
 
-def ramp(run, torch, seconds: float, barrier=None):
-    """Untimed repetitions of the step for a fixed wall time (clocks, caches, NCCL first-use set-up)."""
+def ramp(run, torch, seconds: float, barrier=None, dist=None):
+    """Untimed repetitions of the step for a fixed wall time (clocks, caches, NCCL first-use set-up). With several
+    ranks the decision to stop is shared (an all-reduce of the "time is up" flag after every batch of 8), so that
+    every rank runs the same number of steps: a step holds collectives, and ranks that disagreed on the count would
+    wait for each other for ever."""
     t0 = time.perf_counter()
     n = 0
     if EAGER:
@@ -262,7 +265,12 @@ def ramp(run, torch, seconds: float, barrier=None):
             run()
         n += 8
         torch.cuda.synchronize()
-        if time.perf_counter() - t0 >= seconds:
+        done = time.perf_counter() - t0 >= seconds
+        if dist is not None:
+            flag = torch.tensor([1.0 if done else 0.0], device="cuda")
+            dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+            done = bool(flag.item() > 0)
+        if done or n >= 100000:
             break
     if barrier is not None:
         barrier()
@@ -364,7 +372,7 @@ def run_gpu_arm(args):
     graph, _ = capture(step, torch, device)
     run = graph.replay if graph is not None else step
     mode = "cuda_graph_replay" if graph is not None else "eager"
-    ramp_s, ramp_steps = ramp(run, torch, RAMP_S, barrier)
+    ramp_s, ramp_steps = ramp(run, torch, RAMP_S, barrier, dist)
     warm = max(args.warmup, 3)
     for _ in range(warm):
         run()
@@ -793,7 +801,7 @@ def measure_convnet(steps, warm, dist, world, rank, local, batch=256):
         raise SystemExit(f"device status {rc}: {L._cabi.load().lb2_last_error_string()}")
     graph, gloss = capture(step, torch, device)
     run = graph.replay if graph is not None else step
-    ramp(run, torch, 0.5, barrier)
+    ramp(run, torch, 0.5, barrier, dist)
     for _ in range(warm):
         run()
     total, per, clocks = timed(run, torch, steps, barrier, local)

@@ -343,28 +343,35 @@ class ConvDims:
         return ConvDims(s, p, d, int(groups), bool(flipkernel))
 
 
-def _conv_desc(weight, x, cd: ConvDims) -> _cabi.ConvDesc:
-    nd = x.dim() - 2
-    if weight.dim() != x.dim() or nd < 1 or nd > 3:
+def _conv_desc_from(wshape, spatial, cin: int, batch: int, cd: ConvDims) -> _cabi.ConvDesc:
+    """lb2_conv_desc of the convolution that maps an input of spatial extents `spatial` with `cin` channels through a
+    filter of shape `wshape` = (k..., cin / groups, cout)."""
+    nd = len(spatial)
+    if len(wshape) != nd + 2 or nd < 1 or nd > 3:
         raise DimensionMismatch("weight and x must have the same rank (3 to 5)")
     if len(cd.stride) != nd:
         raise DimensionMismatch("ConvDims rank does not match the arrays")
-    cin, n = x.shape[-2], x.shape[-1]
-    cin_g, cout = weight.shape[-2], weight.shape[-1]
+    cin_g, cout = wshape[-2], wshape[-1]
     if cin_g * cd.groups != cin or cout % cd.groups != 0:
         raise DimensionMismatch(f"channels: x has {cin}, weight expects {cin_g} x {cd.groups} groups -> {cout}")
     d = _cabi.ConvDesc()
     d.ndim = nd
     for i in range(3):
         live = i < nd
-        d.in_[i] = x.shape[i] if live else 1
-        d.k[i] = weight.shape[i] if live else 1
+        d.in_[i] = spatial[i] if live else 1
+        d.k[i] = wshape[i] if live else 1
         d.stride[i] = cd.stride[i] if live else 1
         d.pad_lo[i] = cd.padding[2 * i] if live else 0
         d.pad_hi[i] = cd.padding[2 * i + 1] if live else 0
         d.dilation[i] = cd.dilation[i] if live else 1
-    d.groups, d.flipkernel, d.cin, d.cout, d.batch = cd.groups, int(cd.flipkernel), cin, cout, n
+    d.groups, d.flipkernel, d.cin, d.cout, d.batch = cd.groups, int(cd.flipkernel), cin, cout, batch
     return d
+
+
+def _conv_desc(weight, x, cd: ConvDims) -> _cabi.ConvDesc:
+    if weight.dim() != x.dim():
+        raise DimensionMismatch("weight and x must have the same rank (3 to 5)")
+    return _conv_desc_from(tuple(weight.shape), tuple(x.shape[:-2]), x.shape[-2], x.shape[-1], cd)
 
 
 def _conv_fwd(act, weight, x, b, cd, want_preact, flags=0):
@@ -411,6 +418,65 @@ def rrule_fused_conv(act: str, weight, x, b, cdims: ConvDims, *, flags: int = 0)
         return dw, dx, db
 
     return y, pullback
+
+
+def conv_transpose_output_size(in_sz, k, cd: ConvDims, outpad=0):
+    """Spatial size of conv_transpose's result (conv_transpose_dims, src/layers/conv.jl:19-45): the input size of the
+    convolution whose output has size `in_sz`: (in - 1)*stride + 1 + (k - 1)*dilation - pad_lo - pad_hi + outpad."""
+    nd = len(in_sz)
+    op = tuple(outpad) if isinstance(outpad, (tuple, list)) else (int(outpad),) * nd
+    return tuple((in_sz[i] - 1) * cd.stride[i] + 1 + (k[i] - 1) * cd.dilation[i] - cd.padding[2 * i] - cd.padding[2 * i + 1] + op[i]
+                 for i in range(nd))
+
+
+def rrule_conv_transpose(act: str, weight, x, b, cdims: ConvDims, outpad=0, *, flags: int = 0):
+    """The ConvTranspose layer's computation (src/layers/conv.jl:428-434): act.(conv_transpose(x, weight, cdims) .+ b) with
+    NNlib.conv_transpose(x, w, cdims) = ∇conv_data(x, w, cdims), and its pullback Δ -> (∂weight, ∂x, ∂b). `weight` is
+    (k..., C_out / groups, C_in) — the filter of the convolution that maps the RESULT back onto x. Everything runs on the
+    convolution entry points: forward = the data-gradient kernels + the bias-activation kernel; pullback: ∂x = conv(g, w),
+    ∂weight = ∇conv_filter(g, x) with g = Δ .* act'."""
+    lib = _cabi.load()
+    weight, x, b = _promote(weight, x, b)
+    if weight.dim() != x.dim():
+        raise DimensionMismatch("weight and x must have the same rank (3 to 5)")
+    Wt, X = as_colmajor(weight), as_colmajor(x)
+    nd = X.dim() - 2
+    if Wt.shape[-1] != X.shape[-2]:
+        raise DimensionMismatch(f"x has {X.shape[-2]} channels, weight expects {Wt.shape[-1]}")
+    cu = Wt.shape[-2] * cdims.groups
+    usz = conv_transpose_output_size(tuple(X.shape[:nd]), tuple(Wt.shape[:nd]), cdims, outpad)
+    d = _conv_desc_from(tuple(Wt.shape), usz, cu, X.shape[-1], cdims)
+    osz = (C.c_int32 * 3)()
+    _cabi.check(lib.lb2_conv_output_size(C.byref(d), osz))
+    if tuple(osz[i] for i in range(nd)) != tuple(X.shape[:nd]):
+        raise DimensionMismatch("outpad does not fit the stride: the convolution of the result does not reproduce size(x)")
+    if b is not None and b.shape[0] != cu:
+        raise DimensionMismatch("length(bias) must equal the number of output channels")
+    dt = dtype_code(X.dtype)
+    ident = act_code("identity")
+    u = jl_empty(usz + (cu, X.shape[-1]), X.dtype, X.device)
+    _, wsp, wsn = _ws(lib.lb2_conv_bwd_workspace_bytes(C.byref(d), dt, ident), X.device)
+    _cabi.check(lib.lb2_conv_bwd(None, ptr(u), None, ptr(X), None, None, None, ptr(Wt), C.byref(d), dt, ident, flags, wsp, wsn,
+                                 current_stream(X.device)))
+    y, pb_act = rrule_bias_activation(act, u, b)
+
+    def pullback(delta):
+        g, db = pb_act(delta)
+        dx = jl_empty(X.shape, X.dtype, X.device)
+        _, w1, n1 = _ws(lib.lb2_conv_fwd_workspace_bytes(C.byref(d), dt), X.device)
+        _cabi.check(lib.lb2_conv_fwd(ptr(dx), None, ptr(g), ptr(Wt), None, C.byref(d), dt, ident, flags, w1, n1, current_stream(X.device)))
+        dw = jl_empty(Wt.shape, X.dtype, X.device)
+        _, w2, n2 = _ws(lib.lb2_conv_bwd_workspace_bytes(C.byref(d), dt, ident), X.device)
+        _cabi.check(lib.lb2_conv_bwd(ptr(dw), None, None, ptr(X), None, None, ptr(g), None, C.byref(d), dt, ident, flags, w2, n2,
+                                     current_stream(X.device)))
+        return dw, dx, db
+
+    return y, pullback
+
+
+def conv_transpose_bias_activation(act: str, weight, x, b, cdims: ConvDims, outpad=0, *, flags: int = 0):
+    """act.(conv_transpose(x, weight, cdims) .+ b) — the ConvTranspose layer (src/layers/conv.jl:428-434)."""
+    return rrule_conv_transpose(act, weight, x, b, cdims, outpad, flags=flags)[0]
 
 
 # --------------------------------------------------------------------------------------------

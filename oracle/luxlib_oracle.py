@@ -384,6 +384,36 @@ def fused_conv_rrule(act: str, w, x, b, cd: ConvDims, gelu="tanh"):
     return z, pullback
 
 
+def conv_transpose_output_size(in_sz, k, cd: ConvDims, outpad=0):
+    """conv_transpose_dims (src/layers/conv.jl:19-45): (in - 1)*stride + 1 + (k - 1)*dil - pad_lo - pad_hi + outpad."""
+    nd = len(in_sz)
+    op = tuple(outpad) if isinstance(outpad, (tuple, list)) else (int(outpad),) * nd
+    return tuple((in_sz[i] - 1) * cd.stride[i] + 1 + (k[i] - 1) * cd.dilation[i] - cd.pad[2 * i] - cd.pad[2 * i + 1] + op[i]
+                 for i in range(nd))
+
+
+def conv_transpose_rrule(act: str, w, x, b, cd: ConvDims, outpad=0, gelu="tanh"):
+    """ConvTranspose (src/layers/conv.jl:428-434): bias_activation!!(σ, conv_transpose(x, w, cdims), bias) with
+    NNlib.conv_transpose(x, w, cdims) = ∇conv_data(x, w, cdims); w is (k..., C_out / groups, C_in).
+    Pullback Δ -> (∂w, ∂x, ∂b): ∂x = conv(g, w), ∂w = ∇conv_filter(g, x)."""
+    nd = x.ndim - 2
+    usz = conv_transpose_output_size(x.shape[:nd], w.shape[:nd], cd, outpad)
+    u_shape = usz + (w.shape[nd] * cd.groups, x.shape[nd + 1])
+    pre = grad_conv_data(x, w, cd, u_shape)
+    if b is not None:
+        pre = pre + b.reshape(_bias_shape(pre, b))
+    z = act_fn(act, pre, gelu)
+
+    def pullback(delta):
+        g = grad_activation(delta, z, act, pre if needs_preactivation(act) else None, gelu)
+        dx = conv(g, w, cd)
+        dw = grad_conv_filter(g, x, cd, w.shape)
+        db = grad_bias_add(b, g)
+        return dw, dx, db
+
+    return z, pullback
+
+
 # --------------------------------------------------------------------------- #
 # statistics
 # --------------------------------------------------------------------------- #

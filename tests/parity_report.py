@@ -44,3 +44,31 @@ def write(path=None):
         for r in RECORDS:
             f.write(json.dumps(r) + "\n")
     return path
+
+
+def summarize(path):
+    """Markdown summary of a report file: the worst comparison per (test function, tensor, dtype)."""
+    global RECORDS
+    with open(path) as f:
+        RECORDS = [json.loads(line) for line in f if line.strip()]
+    rows = ["| test | tensor | dtype | worst rel-L2 | tolerance | note |", "|---|---|---|---|---|---|"]
+    for (fn, tensor, dt), r in sorted(worst_by_function().items()):
+        note = r.get("judged", "")
+        if "rel_l2_plain" in r:
+            note += f" (plain {r['rel_l2_plain']:.2e}, cancellation {r.get('cancellation', float('nan')):.3g})"
+        rows.append(f"| {fn} | {tensor} | {dt} | {r['rel_l2']:.2e} | {r['tol']:.0e} | {note} |")
+    head = f"{len(RECORDS)} comparisons; worst over all Float32 comparisons relative to their tolerance: "
+    f32 = [r for r in RECORDS if r["dtype"] == "f32"]
+    bf = [r for r in RECORDS if r["dtype"] == "bf16"]
+    w32 = max(f32, key=lambda r: r["rel_l2"] / r["tol"]) if f32 else None
+    wbf = max(bf, key=lambda r: r["rel_l2"] / r["tol"]) if bf else None
+    if w32:
+        head += f"{w32['rel_l2']:.2e} of {w32['tol']:.0e} ({w32['test'].split('::')[-1]}, {w32['tensor']})"
+    if wbf:
+        head += f"; bf16: {wbf['rel_l2']:.2e} of {wbf['tol']:.0e} ({wbf['test'].split('::')[-1]}, {wbf['tensor']})"
+    return head + "\n\n" + "\n".join(rows) + "\n"
+
+
+if __name__ == "__main__":
+    import sys
+    print(summarize(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("LB2_PARITY_REPORT", "parity_report.jsonl")))

@@ -815,3 +815,35 @@ def test_mse_loss_and_gradient(dt, shape):
     l, pb = L.rrule_mse_loss(dev(yh, dt), dev(y, dt))
     check(l, np.array([l_ref]), "f32", "loss")          # the loss is a Float32 scalar for either storage type
     check(pb(), pb_ref(), dt, "dyhat")
+
+
+# ------------------------------------------------------------------------------------------
+# ConvTranspose (the data-gradient kernels as a forward operator)
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("act", ["identity", "relu", "gelu"])
+@pytest.mark.parametrize("case", [
+    # spatial, k, C_in, C_out, stride, pad, dilation, outpad, groups, flip, batch
+    ((5, 4), (3, 3), 4, 6, 1, 0, 1, 0, 1, False, 2),
+    ((7, 7), (3, 3), 64, 32, 2, 1, 1, 1, 1, False, 3),        # a decoder's 2x upsampling step (general tensor-core path)
+    ((6, 5), (2, 2), 8, 8, 2, 0, 1, 0, 2, True, 2),           # groups: direct kernels
+    ((14, 14), (3, 3), 128, 64, 1, 1, 1, 0, 1, False, 2),
+])
+def test_conv_transpose_fwd_bwd(dt, act, case):
+    sp, k, cin, cu, stride, pad, dil, outpad, groups, flip, batch = case
+    rng = np.random.default_rng(43)
+    x = prep(rng.standard_normal(sp + (cin, batch)), dt)
+    w = prep(O.kaiming_normal(rng, k + (cu // groups, cin)), dt)
+    b = prep(rng.uniform(-0.1, 0.1, cu), dt)
+    ocd = O.ConvDims.make(2, stride, pad, dil, groups, flip)
+    lcd = L.ConvDims.make(2, stride, pad, dil, groups, flip)
+    z_ref, pb_ref = O.conv_transpose_rrule(act, w, x, b, ocd, outpad)
+    z, pb = L.rrule_conv_transpose(act, dev(w, dt), dev(x, dt), dev(b, dt), lcd, outpad)
+    check(z, z_ref, dt, "y")
+    delta = prep(rng.standard_normal(z_ref.shape), dt)
+    dw_ref, dx_ref, db_ref = pb_ref(delta)
+    dw, dx, db = pb(dev(delta, dt))
+    check(dw, dw_ref, dt, "dw")
+    check(dx, dx_ref, dt, "dx")
+    check(db, db_ref, dt, "db")
+    assert L._cabi.load().lb2_poll_device_status(None) == 0

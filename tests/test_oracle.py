@@ -347,3 +347,28 @@ def test_mse_loss_against_torch_and_the_reference_docstring_example():
     l, pb = O.mse_loss_rrule(a, b)
     np.testing.assert_allclose(l, lt.item(), rtol=1e-12)
     np.testing.assert_allclose(pb(), ta.grad.numpy(), rtol=1e-12)
+
+
+def test_conv_transpose_against_torch():
+    # NNlib.conv_transpose = ∇conv_data (the ConvTranspose layer, src/layers/conv.jl:428-434); torch's
+    # conv_transpose2d is the data gradient of a cross-correlation, i.e. the flipkernel = true case
+    import torch
+    rng = np.random.default_rng(42)
+    for stride, pad, dil, outpad, groups in ((1, 0, 1, 0, 1), (2, 1, 1, 1, 1), (2, 1, 1, 0, 2), (3, 2, 2, 1, 1)):
+        cin, cu = 4, 6
+        x = rng.standard_normal((5, 4, cin, 2))
+        w = rng.standard_normal((3, 3, cu // groups, cin))
+        b = rng.standard_normal(cu)
+        cd = O.ConvDims.make(2, stride, pad, dil, groups, True)
+        z, pb = O.conv_transpose_rrule("identity", w, x, b, cd, outpad)
+        tx = torch.tensor(np.ascontiguousarray(x.transpose(3, 2, 1, 0)), requires_grad=True)       # N, C, H, W
+        tw = torch.tensor(np.ascontiguousarray(w.transpose(3, 2, 1, 0)), requires_grad=True)       # Cin, Cu/g, kH, kW
+        tb = torch.tensor(b, requires_grad=True)
+        tz = torch.nn.functional.conv_transpose2d(tx, tw, tb, stride=stride, padding=pad, output_padding=outpad, groups=groups, dilation=dil)
+        np.testing.assert_allclose(z, tz.detach().numpy().transpose(3, 2, 1, 0), rtol=1e-10, atol=1e-10)
+        delta = rng.standard_normal(z.shape)
+        tz.backward(torch.tensor(np.ascontiguousarray(delta.transpose(3, 2, 1, 0))))
+        dw, dx, db = pb(delta)
+        np.testing.assert_allclose(dx, tx.grad.numpy().transpose(3, 2, 1, 0), rtol=1e-10, atol=1e-10)
+        np.testing.assert_allclose(dw, tw.grad.numpy().transpose(3, 2, 1, 0), rtol=1e-10, atol=1e-10)
+        np.testing.assert_allclose(db, tb.grad.numpy(), rtol=1e-10, atol=1e-10)
