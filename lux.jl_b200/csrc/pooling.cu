@@ -285,9 +285,51 @@ __device__ __forceinline__ void pool_stage(T* dst, const T* src, int n, bool vec
 }
 __device__ __forceinline__ void pool_stage_wait() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
-template <typename T, bool MAX, int STRIDE>
+// Window scans with the window extent K known at compile time (K x K taps, fully unrolled). Taps that fall into the
+// padding are ALIASED onto the window's first valid row / column instead of being skipped: a padded row above the
+// plane reads the first valid row (the same elements, met again later at their true place, where a strict comparison
+// cannot replace them), a padded row below reads it after every true tap (and cannot win either); columns likewise.
+// The recorded position is computed from the aliased coordinates and is therefore always the true position of the
+// element read. The scan is then free of predicates and of loop overhead. Needs a window with at least one valid row
+// and column (pool_fixed_window() checks that on the host). cofs[kw] = the aliased column of tap kw.
+template <int K>
+__device__ __forceinline__ void pool_alias_columns(int (&cofs)[K], int w0, int W) {
+  const int wfirst = max(w0, 0);
+#pragma unroll
+  for (int kw = 0; kw < K; ++kw) cofs[kw] = (unsigned)(w0 + kw) < (unsigned)W ? w0 + kw : wfirst;
+}
+template <typename T, int K>
+__device__ __forceinline__ void pool_window_argmax(const T* __restrict__ sx, int W, int H, int h0, const int (&cofs)[K], float& best, int& where) {
+  const int hfirst = max(h0, 0);
+#pragma unroll
+  for (int kh = 0; kh < K; ++kh) {
+    const int rb = ((unsigned)(h0 + kh) < (unsigned)H ? h0 + kh : hfirst) * W;
+#pragma unroll
+    for (int kw = 0; kw < K; ++kw) {
+      const int i = rb + cofs[kw];
+      const float v = to_f32(sx[i]);
+      if (kh == 0 && kw == 0) { best = v; where = i; }        // the first valid element is taken unconditionally
+      else { const bool take = v > best; best = take ? v : best; where = take ? i : where; }
+    }
+  }
+}
+template <typename T, int K>
+__device__ __forceinline__ float pool_window_max(const T* __restrict__ sx, int W, int H, int h0, const int (&cofs)[K]) {
+  const int hfirst = max(h0, 0);
+  float best = -INFINITY;
+#pragma unroll
+  for (int kh = 0; kh < K; ++kh) {
+    const int rb = ((unsigned)(h0 + kh) < (unsigned)H ? h0 + kh : hfirst) * W;
+#pragma unroll
+    for (int kw = 0; kw < K; ++kw) best = fmaxf(best, to_f32(sx[rb + cofs[kw]]));
+  }
+  return best;
+}
+
+template <typename T, bool MAX, int STRIDE, int K>
 __global__ void __launch_bounds__(256) pool2d_fwd_smem_kernel(T* __restrict__ y, const T* __restrict__ x, const PoolGeom g, int lw,
                                                               int vec) {
+  static_assert(K == 0 || MAX, "the unrolled scan is the max scan");
   extern __shared__ __align__(16) uint8_t pool_smem[];
   T* sx = reinterpret_cast<T*>(pool_smem);
   const int W = g.in[0], H = g.in[1], OW = g.out[0], OH = g.out[1];
@@ -302,63 +344,45 @@ __global__ void __launch_bounds__(256) pool2d_fwd_smem_kernel(T* __restrict__ y,
     T* yp = y + plane * (int64_t)(OW * OH);
     if (tx < OW) {
       const int w0 = tx * sw - g.pad[0];
-      const int kw_lo = w0 < 0 ? -w0 : 0, kw_hi = min(g.k[0], W - w0);
-      for (int oh = ty; oh < OH; oh += rows) {
-        const int h0 = oh * sh - g.pad[1];
-        const int kh_lo = h0 < 0 ? -h0 : 0, kh_hi = min(g.k[1], H - h0);
-        float acc = MAX ? -INFINITY : 0.f;
-        for (int kh = kh_lo; kh < kh_hi; ++kh) {
-          const T* row = sx + (h0 + kh) * W + w0;
-          for (int kw = kw_lo; kw < kw_hi; ++kw) {
-            const float v = to_f32(row[kw]);
-            if (MAX) acc = fmaxf(acc, v); else acc += v;
+      if constexpr (K > 0) {
+        int cofs[K];
+        pool_alias_columns<K>(cofs, w0, W);
+        for (int oh = ty; oh < OH; oh += rows) yp[oh * OW + tx] = from_f32<T>(pool_window_max<T, K>(sx, W, H, oh * sh - g.pad[1], cofs));
+      } else {
+        const int kw_lo = w0 < 0 ? -w0 : 0, kw_hi = min(g.k[0], W - w0);
+        for (int oh = ty; oh < OH; oh += rows) {
+          const int h0 = oh * sh - g.pad[1];
+          const int kh_lo = h0 < 0 ? -h0 : 0, kh_hi = min(g.k[1], H - h0);
+          float acc = MAX ? -INFINITY : 0.f;
+          for (int kh = kh_lo; kh < kh_hi; ++kh) {
+            const T* row = sx + (h0 + kh) * W + w0;
+            for (int kw = kw_lo; kw < kw_hi; ++kw) {
+              const float v = to_f32(row[kw]);
+              if (MAX) acc = fmaxf(acc, v); else acc += v;
+            }
           }
+          yp[oh * OW + tx] = from_f32<T>(MAX ? acc : acc * inv_win);
         }
-        yp[oh * OW + tx] = from_f32<T>(MAX ? acc : acc * inv_win);
       }
     }
   }
 }
 
-// Backward. Max pooling: a first pass, one thread per OUTPUT, finds the position of each window's first maximal
-// element (scan in kw-fastest order with a strict comparison, NNlib's tie rule) and leaves it in shared memory; the
-// second pass, one thread per INPUT, adds dy of the covering windows whose recorded position it is. Both passes are
-// free of data-dependent branches, so warps do not serialise on ties. The forward result y is not needed.
-template <typename T, bool MAX, int STRIDE>
-__global__ void __launch_bounds__(256) pool2d_bwd_smem_kernel(T* __restrict__ dx, const T* __restrict__ dy, const T* __restrict__ y,
-                                                              const T* __restrict__ x, const PoolGeom g, int lw, int vec_in, int vec_out,
-                                                              int off_idx, int off_dy) {
+// Backward of mean pooling: one thread per INPUT element adds dy of the covering windows.
+template <typename T, int STRIDE>
+__global__ void __launch_bounds__(256) pool2d_meanbwd_smem_kernel(T* __restrict__ dx, const T* __restrict__ dy, const PoolGeom g, int lw,
+                                                                  int vec_out) {
   extern __shared__ __align__(16) uint8_t pool_smem[];
-  T* sx = reinterpret_cast<T*>(pool_smem);
-  int* sidx = reinterpret_cast<int*>(pool_smem + off_idx);
-  T* sdy = reinterpret_cast<T*>(pool_smem + off_dy);
-  (void)y;
+  T* sdy = reinterpret_cast<T*>(pool_smem);
   const int W = g.in[0], H = g.in[1], OW = g.out[0], OH = g.out[1], kW = g.k[0], kH = g.k[1];
   const int sw = STRIDE ? STRIDE : g.stride[0], sh = STRIDE ? STRIDE : g.stride[1];
   const int tx = threadIdx.x & ((1 << lw) - 1), ty = threadIdx.x >> lw, rows = 256 >> lw;
   const float inv_win = 1.f / (float)(kW * kH);
   for (int64_t plane = blockIdx.x; plane < g.planes; plane += gridDim.x) {
     __syncthreads();
-    if (MAX) pool_stage(sx, x + plane * (int64_t)(W * H), W * H, vec_in != 0);
     pool_stage(sdy, dy + plane * (int64_t)(OW * OH), OW * OH, vec_out != 0);
     pool_stage_wait();
     __syncthreads();
-    if (MAX) {
-      for (int o = threadIdx.x; o < OW * OH; o += blockDim.x) {
-        const int oh = o / OW, ow = o - oh * OW;
-        const int h0 = oh * sh - g.pad[1], w0 = ow * sw - g.pad[0];
-        float best = -INFINITY;
-        int where = -1;
-        for (int kh = max(0, -h0); kh < min(kH, H - h0); ++kh)
-          for (int kw = max(0, -w0); kw < min(kW, W - w0); ++kw) {
-            const int i = (h0 + kh) * W + w0 + kw;
-            const float v = to_f32(sx[i]);
-            if (v > best || where < 0) { best = v; where = i; }
-          }
-        sidx[o] = where;
-      }
-      __syncthreads();
-    }
     T* dxp = dx + plane * (int64_t)(W * H);
     if (tx < W) {
       const int w = tx;
@@ -369,16 +393,92 @@ __global__ void __launch_bounds__(256) pool2d_bwd_smem_kernel(T* __restrict__ dx
         const int top = h + g.pad[1], bot = top - (kH - 1);
         const int oh_lo = bot <= 0 ? 0 : div_stride<STRIDE>(bot + sh - 1, sh);
         const int oh_hi = min(OH - 1, div_stride<STRIDE>(top, sh));
-        const int i = h * W + w;
         float acc = 0.f;
         for (int oh = oh_lo; oh <= oh_hi; ++oh)
-          for (int ow = ow_lo; ow <= ow_hi; ++ow) {
-            const int o = oh * OW + ow;
-            const float d = to_f32(sdy[o]);
-            if (MAX) acc += (sidx[o] == i) ? d : 0.f; else acc += d * inv_win;
-          }
-        dxp[i] = from_f32<T>(acc);
+          for (int ow = ow_lo; ow <= ow_hi; ++ow) acc += to_f32(sdy[oh * OW + ow]);
+        dxp[h * W + w] = from_f32<T>(acc * inv_win);
       }
+    }
+  }
+}
+
+// Backward of max pooling, window-centric: a thread owns a window, finds its first maximal element (scan in
+// kw-fastest order with a strict comparison, NNlib's tie rule) and adds the window's dy to that element's fp32
+// accumulator in shared memory. Windows are visited in ceil(kW/sw) x ceil(kH/sh) classes of equal (ow mod cw,
+// oh mod ch): two windows of one class do not overlap, so the additions within a class touch distinct accumulators
+// and need no atomics, and the order of additions into one accumulator is fixed (class order): the result is
+// deterministic. The plane of accumulators is then rounded and written with 16-byte stores. The per-element work of
+// the input-centric form (bounds of the covering windows for each of W*H elements) is gone; what is left is one scan
+// per window. The forward result y is not needed.
+template <typename T, int STRIDE, int K>
+__global__ void __launch_bounds__(1024, 2) pool2d_maxbwd_smem_kernel(T* __restrict__ dx, const T* __restrict__ dy, const T* __restrict__ x,
+                                                                 const PoolGeom g, int lw, int vec_in, int vec_out, int off_acc, int off_dy,
+                                                                 int cw, int ch) {
+  extern __shared__ __align__(16) uint8_t pool_smem[];
+  T* sx = reinterpret_cast<T*>(pool_smem);
+  float* sacc = reinterpret_cast<float*>(pool_smem + off_acc);
+  T* sdy = reinterpret_cast<T*>(pool_smem + off_dy);
+  const int W = g.in[0], H = g.in[1], OW = g.out[0], OH = g.out[1], kW = g.k[0], kH = g.k[1];
+  const int sw = STRIDE ? STRIDE : g.stride[0], sh = STRIDE ? STRIDE : g.stride[1];
+  const int tx = threadIdx.x & ((1 << lw) - 1), ty = threadIdx.x >> lw, rows = (int)blockDim.x >> lw;
+  const int n = W * H, n4 = (n + 3) >> 2;
+  for (int64_t plane = blockIdx.x; plane < g.planes; plane += gridDim.x) {
+    __syncthreads();
+    pool_stage(sx, x + plane * (int64_t)n, n, vec_in != 0);
+    pool_stage(sdy, dy + plane * (int64_t)(OW * OH), OW * OH, vec_out != 0);
+    for (int i = threadIdx.x; i < n4; i += blockDim.x) reinterpret_cast<float4*>(sacc)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    pool_stage_wait();
+    __syncthreads();
+    for (int ci = 0; ci < ch; ++ci)
+      for (int cj = 0; cj < cw; ++cj) {
+        const int ow = cj + tx * cw;
+        if (ow < OW) {
+          const int w0 = ow * sw - g.pad[0];
+          if constexpr (K > 0) {
+            int cofs[K];
+            pool_alias_columns<K>(cofs, w0, W);
+            for (int oh = ci + ty * ch; oh < OH; oh += rows * ch) {
+              float best;
+              int where;
+              pool_window_argmax<T, K>(sx, W, H, oh * sh - g.pad[1], cofs, best, where);
+              sacc[where] += to_f32(sdy[oh * OW + ow]);
+            }
+          } else {
+            const int kw_lo = w0 < 0 ? -w0 : 0, kw_hi = min(kW, W - w0);
+            for (int oh = ci + ty * ch; oh < OH; oh += rows * ch) {
+              const int h0 = oh * sh - g.pad[1];
+              const int kh_lo = h0 < 0 ? -h0 : 0, kh_hi = min(kH, H - h0);
+              float best = -INFINITY;
+              int where = -1;
+              for (int kh = kh_lo; kh < kh_hi; ++kh) {
+                const int r = (h0 + kh) * W + w0;
+                for (int kw = kw_lo; kw < kw_hi; ++kw) {
+                  const float v = to_f32(sx[r + kw]);
+                  const bool take = v > best || where < 0;
+                  best = take ? v : best;
+                  where = take ? r + kw : where;
+                }
+              }
+              if (where >= 0) sacc[where] += to_f32(sdy[oh * OW + ow]);
+            }
+          }
+        }
+        __syncthreads();
+      }
+    T* dxp = dx + plane * (int64_t)n;
+    if (vec_in) {      // n * sizeof(T) is a multiple of 16 and the plane starts on 16 bytes
+      constexpr int PER = 16 / (int)sizeof(T);
+      for (int i = threadIdx.x; i < n / PER; i += blockDim.x) {
+        alignas(16) T out[PER];
+#pragma unroll
+        for (int j = 0; j < PER; j += 4) {
+          const float4 a = reinterpret_cast<const float4*>(sacc)[(i * PER + j) >> 2];
+          out[j] = from_f32<T>(a.x); out[j + 1] = from_f32<T>(a.y); out[j + 2] = from_f32<T>(a.z); out[j + 3] = from_f32<T>(a.w);
+        }
+        reinterpret_cast<uint4*>(dxp)[i] = *reinterpret_cast<const uint4*>(out);
+      }
+    } else {
+      for (int i = threadIdx.x; i < n; i += blockDim.x) dxp[i] = from_f32<T>(sacc[i]);
     }
   }
 }
@@ -387,18 +487,35 @@ __global__ void __launch_bounds__(256) pool2d_bwd_smem_kernel(T* __restrict__ dx
 template <typename T, typename... R> T* pool_arg_y(void (*)(T*, const T*, R...));
 template <typename T, typename... R> const T* pool_arg_x(void (*)(T*, const T*, R...));
 
-// shared-memory layout of the staged kernels: x plane | first-maximum positions | dy plane, each starting on 16 bytes
-struct PoolSmem { int off_idx, off_dy, bytes, lw_in, lw_out; bool ok; };
-static PoolSmem pool_smem_plan(const PoolGeom& g, size_t es, bool bwd) {
+// shared-memory layout of the staged kernels. Forward: the x plane. Mean backward: the dy plane. Max backward:
+// x plane | fp32 accumulators of dx (a multiple of four) | dy plane, each starting on 16 bytes; two CTAs of 256
+// threads per SM while that is at most 112 KB, one up to 200 KB.
+struct PoolSmem { int off_acc, off_dy, bytes, lw_in, lw_out, lw_cls, cw, ch; bool ok; };
+static PoolSmem pool_smem_plan(const PoolGeom& g, size_t es, int what /*0 fwd, 1 mean bwd, 2 max bwd*/) {
   PoolSmem p{};
-  const size_t xb = align_up((size_t)g.in[0] * g.in[1] * es, 16), yb = align_up((size_t)g.out[0] * g.out[1] * es, 16);
-  const size_t ib = align_up((size_t)g.out[0] * g.out[1] * sizeof(int), 16);   // first-maximum positions, one per window
-  p.off_idx = (int)xb; p.off_dy = (int)(xb + ib);
-  p.bytes = (int)(bwd ? xb + ib + yb : xb);
+  const size_t n = (size_t)g.in[0] * g.in[1], no = (size_t)g.out[0] * g.out[1];
+  const size_t xb = align_up(n * es, 16), yb = align_up(no * es, 16), ab = align_up(n * sizeof(float), 16);
+  p.off_acc = (int)xb; p.off_dy = (int)(xb + ab);
+  p.bytes = (int)(what == 0 ? xb : what == 1 ? yb : xb + ab + yb);
   auto lg = [](int v) { int l = 5; while ((1 << l) < v) ++l; return l; };
-  p.lw_in = lg(g.in[0]); p.lw_out = lg(g.out[0]);
-  p.ok = p.bytes <= 96 * 1024 && p.lw_in <= 8 && p.lw_out <= 8 && g.out[0] >= 1 && g.out[1] >= 1;
+  p.cw = (g.k[0] + g.stride[0] - 1) / g.stride[0];
+  p.ch = (g.k[1] + g.stride[1] - 1) / g.stride[1];
+  p.lw_in = lg(g.in[0]); p.lw_out = lg(g.out[0]); p.lw_cls = lg((g.out[0] + p.cw - 1) / p.cw);
+  p.ok = (size_t)p.bytes <= (what == 2 ? 200u : 96u) * 1024 && xb + ab + yb < ((size_t)1 << 30) && p.lw_in <= 8 && p.lw_out <= 8 &&
+         g.out[0] >= 1 && g.out[1] >= 1 && p.cw * p.ch <= 64;
   return p;
+}
+
+// 2 or 3 when the window is K x K and every window holds at least one valid row and column (the condition of the
+// unrolled scans with aliased padding taps), else 0.
+static int pool_fixed_window(const PoolGeom& g) {
+  if (g.k[0] != g.k[1] || (g.k[0] != 2 && g.k[0] != 3)) return 0;
+  for (int i = 0; i < 2; ++i) {
+    if (g.out[i] < 1 || g.in[i] < 1) return 0;
+    const int last0 = (g.out[i] - 1) * g.stride[i] - g.pad[i];     // first tap of the last window
+    if (g.pad[i] >= g.k[i] || last0 >= g.in[i]) return 0;
+  }
+  return g.k[0];
 }
 
 static bool pool_is_2d_plain(const PoolGeom& g) {
@@ -477,7 +594,7 @@ int32_t lb2_pool_fwd(void* y, const void* x, const lb2_pool_desc* d, int32_t kin
   }
   if (pool_is_2d_plain(g)) {
     const bool same = g.stride[0] == g.stride[1];
-    const PoolSmem sp = pool_smem_plan(g, dtype_size(dtype), false);
+    const PoolSmem sp = pool_smem_plan(g, dtype_size(dtype), 0);
     if (sp.ok) {
       const int vec = (aligned_to(x, 16) && ((size_t)g.in[0] * g.in[1] * dtype_size(dtype)) % 16 == 0) ? 1 : 0;
       const int st2 = same && g.stride[0] <= 2 ? g.stride[0] : 0;
@@ -490,9 +607,14 @@ int32_t lb2_pool_fwd(void* y, const void* x, const lb2_pool_desc* d, int32_t kin
         LB2_CHECK_LAUNCH("pool2d_fwd (staged)");
         return LB2_OK;
       };
+      const int kfix = kind == LB2_POOL_MAX ? pool_fixed_window(g) : 0;
       LB2_DISPATCH_DTYPE(dtype, {
-        if (kind == LB2_POOL_MAX) return st2 == 1 ? launch(pool2d_fwd_smem_kernel<T, true, 1>) : st2 == 2 ? launch(pool2d_fwd_smem_kernel<T, true, 2>) : launch(pool2d_fwd_smem_kernel<T, true, 0>);
-        return st2 == 1 ? launch(pool2d_fwd_smem_kernel<T, false, 1>) : st2 == 2 ? launch(pool2d_fwd_smem_kernel<T, false, 2>) : launch(pool2d_fwd_smem_kernel<T, false, 0>);
+        if (kind == LB2_POOL_MAX) {
+          if (kfix == 3) return st2 == 1 ? launch(pool2d_fwd_smem_kernel<T, true, 1, 3>) : st2 == 2 ? launch(pool2d_fwd_smem_kernel<T, true, 2, 3>) : launch(pool2d_fwd_smem_kernel<T, true, 0, 3>);
+          if (kfix == 2) return st2 == 1 ? launch(pool2d_fwd_smem_kernel<T, true, 1, 2>) : st2 == 2 ? launch(pool2d_fwd_smem_kernel<T, true, 2, 2>) : launch(pool2d_fwd_smem_kernel<T, true, 0, 2>);
+          return st2 == 1 ? launch(pool2d_fwd_smem_kernel<T, true, 1, 0>) : st2 == 2 ? launch(pool2d_fwd_smem_kernel<T, true, 2, 0>) : launch(pool2d_fwd_smem_kernel<T, true, 0, 0>);
+        }
+        return st2 == 1 ? launch(pool2d_fwd_smem_kernel<T, false, 1, 0>) : st2 == 2 ? launch(pool2d_fwd_smem_kernel<T, false, 2, 0>) : launch(pool2d_fwd_smem_kernel<T, false, 0, 0>);
       });
     }
     LB2_DISPATCH_DTYPE(dtype, {
@@ -551,24 +673,42 @@ int32_t lb2_pool_bwd(void* dx, const void* dy, const void* y, const void* x, con
   }
   if (pool_is_2d_plain(g)) {
     const bool same = g.stride[0] == g.stride[1];
-    const PoolSmem sp = pool_smem_plan(g, es, true);
+    const PoolSmem sp = pool_smem_plan(g, es, kind == LB2_POOL_MAX ? 2 : 1);
     if (sp.ok) {
-      const int vec_in = (aligned_to(x, 16) && ((size_t)g.in[0] * g.in[1] * es) % 16 == 0) ? 1 : 0;
+      const int vec_in = (aligned_to(x, 16) && aligned_to(dx, 16) && ((size_t)g.in[0] * g.in[1] * es) % 16 == 0) ? 1 : 0;
       const int vec_out = (aligned_to(dy, 16) && ((size_t)g.out[0] * g.out[1] * es) % 16 == 0) ? 1 : 0;
       const int st2 = same && g.stride[0] <= 2 ? g.stride[0] : 0;
-      auto launch = [&](auto kernel) -> int32_t {
+      auto reserve = [&](auto kernel) -> int32_t {
         if (sp.bytes > 48 * 1024) {
           cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, sp.bytes);
           if (e != cudaSuccess) return fail(LB2_LAUNCH_FAIL, "pool2d_bwd: cannot reserve %d bytes of shared memory: %s", sp.bytes, cudaGetErrorString(e));
         }
-        kernel<<<plane_grid(g.planes), 256, sp.bytes, st>>>((decltype(pool_arg_y(kernel)))dx, (decltype(pool_arg_x(kernel)))dy, (decltype(pool_arg_x(kernel)))y,
-                                                            (decltype(pool_arg_x(kernel)))x, g, sp.lw_in, vec_in, vec_out, sp.off_idx, sp.off_dy);
-        LB2_CHECK_LAUNCH("pool2d_bwd (staged)");
+        return LB2_OK;
+      };
+      auto launch_max = [&](auto kernel) -> int32_t {
+        if (int32_t rc = reserve(kernel)) return rc;
+        // a class of windows is one pass of 1024 threads for planes up to about 64 x 64 outputs; small planes take fewer
+        const int per_class = ((g.out[1] + sp.ch - 1) / sp.ch) << sp.lw_cls;
+        const int threads = per_class > 512 ? 1024 : per_class > 256 ? 512 : 256;
+        kernel<<<plane_grid(g.planes), threads, sp.bytes, st>>>((decltype(pool_arg_y(kernel)))dx, (decltype(pool_arg_x(kernel)))dy,
+                                                            (decltype(pool_arg_x(kernel)))x, g, sp.lw_cls, vec_in, vec_out, sp.off_acc, sp.off_dy, sp.cw, sp.ch);
+        LB2_CHECK_LAUNCH("pool2d_bwd (max, staged)");
+        return LB2_OK;
+      };
+      auto launch_mean = [&](auto kernel) -> int32_t {
+        if (int32_t rc = reserve(kernel)) return rc;
+        kernel<<<plane_grid(g.planes), 256, sp.bytes, st>>>((decltype(pool_arg_y(kernel)))dx, (decltype(pool_arg_x(kernel)))dy, g, sp.lw_in, vec_out);
+        LB2_CHECK_LAUNCH("pool2d_bwd (mean, staged)");
         return LB2_OK;
       };
       LB2_DISPATCH_DTYPE(dtype, {
-        if (kind == LB2_POOL_MAX) return st2 == 1 ? launch(pool2d_bwd_smem_kernel<T, true, 1>) : st2 == 2 ? launch(pool2d_bwd_smem_kernel<T, true, 2>) : launch(pool2d_bwd_smem_kernel<T, true, 0>);
-        return st2 == 1 ? launch(pool2d_bwd_smem_kernel<T, false, 1>) : st2 == 2 ? launch(pool2d_bwd_smem_kernel<T, false, 2>) : launch(pool2d_bwd_smem_kernel<T, false, 0>);
+        if (kind == LB2_POOL_MAX) {
+          const int kfix = pool_fixed_window(g);
+          if (kfix == 3) return st2 == 1 ? launch_max(pool2d_maxbwd_smem_kernel<T, 1, 3>) : st2 == 2 ? launch_max(pool2d_maxbwd_smem_kernel<T, 2, 3>) : launch_max(pool2d_maxbwd_smem_kernel<T, 0, 3>);
+          if (kfix == 2) return st2 == 1 ? launch_max(pool2d_maxbwd_smem_kernel<T, 1, 2>) : st2 == 2 ? launch_max(pool2d_maxbwd_smem_kernel<T, 2, 2>) : launch_max(pool2d_maxbwd_smem_kernel<T, 0, 2>);
+          return st2 == 1 ? launch_max(pool2d_maxbwd_smem_kernel<T, 1, 0>) : st2 == 2 ? launch_max(pool2d_maxbwd_smem_kernel<T, 2, 0>) : launch_max(pool2d_maxbwd_smem_kernel<T, 0, 0>);
+        }
+        return st2 == 1 ? launch_mean(pool2d_meanbwd_smem_kernel<T, 1>) : st2 == 2 ? launch_mean(pool2d_meanbwd_smem_kernel<T, 2>) : launch_mean(pool2d_meanbwd_smem_kernel<T, 0>);
       });
     }
     LB2_DISPATCH_DTYPE(dtype, {

@@ -392,20 +392,24 @@ def conv_transpose_output_size(in_sz, k, cd: ConvDims, outpad=0):
                  for i in range(nd))
 
 
-def conv_transpose_rrule(act: str, w, x, b, cd: ConvDims, outpad=0, gelu="tanh"):
+def conv_transpose_rrule(act: str, w, x, b, cd: ConvDims, outpad=0, gelu="tanh", store=None):
     """ConvTranspose (src/layers/conv.jl:428-434): bias_activation!!(σ, conv_transpose(x, w, cdims), bias) with
     NNlib.conv_transpose(x, w, cdims) = ∇conv_data(x, w, cdims); w is (k..., C_out / groups, C_in).
-    Pullback Δ -> (∂w, ∂x, ∂b): ∂x = conv(g, w), ∂w = ∇conv_filter(g, x)."""
+    Pullback Δ -> (∂w, ∂x, ∂b): ∂x = conv(g, w), ∂w = ∇conv_filter(g, x).
+    The layer is a composition of separate array operations, so the reference materialises conv_transpose's result and
+    g = Δ .* act' in the arrays' element type before the next operation reads them; `store` is that rounding
+    (round_bf16 for BFloat16 arrays, None for no rounding)."""
+    store = store or (lambda a: a)
     nd = x.ndim - 2
     usz = conv_transpose_output_size(x.shape[:nd], w.shape[:nd], cd, outpad)
     u_shape = usz + (w.shape[nd] * cd.groups, x.shape[nd + 1])
-    pre = grad_conv_data(x, w, cd, u_shape)
+    pre = store(grad_conv_data(x, w, cd, u_shape))
     if b is not None:
         pre = pre + b.reshape(_bias_shape(pre, b))
     z = act_fn(act, pre, gelu)
 
     def pullback(delta):
-        g = grad_activation(delta, z, act, pre if needs_preactivation(act) else None, gelu)
+        g = store(grad_activation(delta, z, act, pre if needs_preactivation(act) else None, gelu))
         dx = conv(g, w, cd)
         dw = grad_conv_filter(g, x, cd, w.shape)
         db = grad_bias_add(b, g)
