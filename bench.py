@@ -224,6 +224,40 @@ class ClockSampler:
 EAGER = False   # --eager: time plain launches (no graph capture, no ramp); used when profiling the launch list
 
 
+GRAPHS = []      # every captured graph, so that shutdown() can release them before the process group goes
+
+
+def shutdown(dist, torch):
+    """Ends a multi-rank run. Captured graphs that hold collectives are released first and the communicator is
+    destroyed after a barrier; because a rank must not outlive its result by minutes whatever a library does on
+    the way out, the destruction runs beside a 20 s watch that ends the process (the JSON line is out by then)."""
+    import gc
+    import threading
+    torch.cuda.synchronize()
+    for g in GRAPHS:
+        try:
+            g.reset()                # frees the captured graph even while a caller's variable still names the object
+        except Exception:            # noqa: BLE001
+            pass
+    GRAPHS.clear()
+    gc.collect()
+    torch.cuda.synchronize()
+    sys.stdout.flush()
+    sys.stderr.flush()
+    if dist is None:
+        return
+
+    def watch():
+        time.sleep(20.0)
+        sys.stderr.write("[bench] process-group shutdown did not return within 20 s; leaving\n")
+        sys.stderr.flush()
+        os._exit(0)
+    threading.Thread(target=watch, daemon=True).start()
+    dist.barrier()
+    torch.cuda.synchronize()
+    dist.destroy_process_group()
+
+
 def capture(step, torch, device):
     """The step as a CUDA graph replay (None when capture is not possible: the caller then times eager launches)."""
     if EAGER:
@@ -241,6 +275,7 @@ def capture(step, torch, device):
         with torch.cuda.graph(g, capture_error_mode="thread_local"):
             out = step()
         torch.cuda.synchronize(device)
+        GRAPHS.append(g)
         return g, out
     except Exception as e:                           # noqa: BLE001 - any capture failure falls back to eager timing
         sys.stderr.write(f"[bench] CUDA graph capture failed ({type(e).__name__}: {e}); timing eager launches\n")
@@ -561,9 +596,7 @@ def run_gpu_arm(args):
         if secondary is not None:
             line["secondary"] = secondary
         print(json.dumps(line), flush=True)
-    if dist is not None:
-        dist.barrier()
-        dist.destroy_process_group()
+    shutdown(dist, torch)
     return 0
 
 
@@ -843,9 +876,7 @@ def run_convnet(args):
         rec.update({"warmup": max(args.warmup, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "data": "synthetic",
                     "config": {"workload": rec["workload"], "parallelism": rec["parallelism"]}, "gpu_launches": None})
         print(json.dumps(rec), flush=True)
-    if dist is not None:
-        dist.barrier()
-        dist.destroy_process_group()
+    shutdown(dist, torch)
     return 0
 
 
