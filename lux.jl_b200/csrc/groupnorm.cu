@@ -570,19 +570,34 @@ gn_bwd_stream_kernel(T* __restrict__ dx, float* __restrict__ chan_out, const T* 
 // faster wherever it applies, so only the backward streams.
 static constexpr int gn_stream_mask() { return 2; }
 
-// dgamma[c] = sum_n chan[n][c][0], dbeta[c] = sum_n chan[n][c][1]   (n ascending)
+// dgamma[c] = sum_n chan[n][c][0], dbeta[c] = sum_n chan[n][c][1]. block (32 channels, 32 slices): slice y adds
+// samples y, y+32, ... in ascending order, then the slice sums are added in slice order: a fixed order, deterministic,
+// and a chain of B/32 loads per thread instead of B.
+constexpr int kGnFinishSlices = 32;
 template <typename T>
-__global__ void gn_finish_kernel(T* __restrict__ dgamma, T* __restrict__ dbeta, const float* __restrict__ chan,
-                                 int64_t C, int64_t B) {
-  const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= C) return;
-  float sg = 0.f, sb = 0.f;
-  for (int64_t n = 0; n < B; ++n) {
-    sg += chan[(n * C + c) * 2];
-    sb += chan[(n * C + c) * 2 + 1];
+__global__ void __launch_bounds__(32 * kGnFinishSlices) gn_finish_kernel(T* __restrict__ dgamma, T* __restrict__ dbeta,
+                                                                        const float* __restrict__ chan, int64_t C, int64_t B) {
+  __shared__ float sg[kGnFinishSlices][33], sb[kGnFinishSlices][33];
+  const int64_t c = (int64_t)blockIdx.x * 32 + threadIdx.x;
+  float ag = 0.f, ab = 0.f;
+  if (c < C) {
+#pragma unroll 4
+    for (int64_t n = threadIdx.y; n < B; n += kGnFinishSlices) {
+      const float2 v = __ldcs(reinterpret_cast<const float2*>(chan) + n * C + c);
+      ag += v.x;
+      ab += v.y;
+    }
   }
-  dgamma[c] = from_f32<T>(sg);
-  dbeta[c] = from_f32<T>(sb);
+  sg[threadIdx.y][threadIdx.x] = ag;
+  sb[threadIdx.y][threadIdx.x] = ab;
+  __syncthreads();
+  if (threadIdx.y == 0 && c < C) {
+    float tg = 0.f, tb = 0.f;
+#pragma unroll
+    for (int r = 0; r < kGnFinishSlices; ++r) { tg += sg[r][threadIdx.x]; tb += sb[r][threadIdx.x]; }
+    dgamma[c] = from_f32<T>(tg);
+    dbeta[c] = from_f32<T>(tb);
+  }
 }
 
 template <typename T, int ACT, bool AFFINE>
@@ -659,7 +674,7 @@ static int32_t gn_bwd_launch(T* dx, T* dg, T* db, const T* dy, const T* x, const
   }
   LB2_CHECK_LAUNCH("groupnorm_bwd");
   if constexpr (AFFINE) {
-    gn_finish_kernel<T><<<(unsigned)((C + 127) / 128), 128, 0, st>>>(dg, db, ws, C, B);
+    gn_finish_kernel<T><<<(unsigned)((C + 31) / 32), dim3(32, kGnFinishSlices), 0, st>>>(dg, db, ws, C, B);
     LB2_CHECK_LAUNCH("groupnorm_bwd_finish");
   }
   return LB2_OK;

@@ -501,18 +501,21 @@ __global__ void __launch_bounds__(256) ln_bwd_generic_kernel(T* __restrict__ dx,
   }
 }
 
-// out[i] = sum_k partial[k][which][i]. block (32 features, 8 slices): slice y adds parts y, y+8, ... in
-// ascending order, then the eight slice sums are added in slice order: a fixed order, deterministic.
+// out[i] = sum_k partial[k][which][i]. block (32 features, 32 slices): slice y adds parts y, y+32, ... in
+// ascending order (a short chain of independent loads: the kernel is latency-bound, not bandwidth-bound), then the
+// slice sums are added in slice order: a fixed order, deterministic.
+constexpr int kLnFinishSlices = 32;
 template <typename T>
-__global__ void __launch_bounds__(256) ln_finish_kernel(T* __restrict__ dgamma, T* __restrict__ dbeta,
-                                                        const float* __restrict__ partial, int64_t D, int parts) {
-  __shared__ float sg[8][33], sb[8][33];
+__global__ void __launch_bounds__(32 * kLnFinishSlices) ln_finish_kernel(T* __restrict__ dgamma, T* __restrict__ dbeta,
+                                                                        const float* __restrict__ partial, int64_t D, int parts) {
+  __shared__ float sg[kLnFinishSlices][33], sb[kLnFinishSlices][33];
   const int64_t i = (int64_t)blockIdx.x * 32 + threadIdx.x;
   float ag = 0.f, ab = 0.f;
   if (i < D) {
-    for (int k = threadIdx.y; k < parts; k += 8) {
-      ag += partial[((int64_t)k * 2) * D + i];
-      ab += partial[((int64_t)k * 2 + 1) * D + i];
+#pragma unroll 4
+    for (int k = threadIdx.y; k < parts; k += kLnFinishSlices) {
+      ag += __ldcs(partial + ((int64_t)k * 2) * D + i);
+      ab += __ldcs(partial + ((int64_t)k * 2 + 1) * D + i);
     }
   }
   sg[threadIdx.y][threadIdx.x] = ag;
@@ -521,7 +524,7 @@ __global__ void __launch_bounds__(256) ln_finish_kernel(T* __restrict__ dgamma, 
   if (threadIdx.y == 0 && i < D) {
     float tg = 0.f, tb = 0.f;
 #pragma unroll
-    for (int r = 0; r < 8; ++r) { tg += sg[r][threadIdx.x]; tb += sb[r][threadIdx.x]; }
+    for (int r = 0; r < kLnFinishSlices; ++r) { tg += sg[r][threadIdx.x]; tb += sb[r][threadIdx.x]; }
     dgamma[i] = from_f32<T>(tg);
     dbeta[i] = from_f32<T>(tb);
   }
@@ -669,7 +672,7 @@ static int32_t ln_bwd_launch(T* dx, T* dg, T* db, const T* dy, const T* x, const
   }
   LB2_CHECK_LAUNCH("layernorm_bwd");
   if constexpr (AFFINE) {
-    ln_finish_kernel<T><<<(unsigned)((D + 31) / 32), dim3(32, 8), 0, st>>>(dg, db, ws, D, p.grid);
+    ln_finish_kernel<T><<<(unsigned)((D + 31) / 32), dim3(32, kLnFinishSlices), 0, st>>>(dg, db, ws, D, p.grid);
     LB2_CHECK_LAUNCH("layernorm_bwd_finish");
   }
   return LB2_OK;
