@@ -47,16 +47,21 @@ def write(path=None):
 
 
 def summarize(path):
-    """Markdown summary of a report file: the worst comparison per (test function, tensor, dtype)."""
+    """Markdown summary of a report file: per (test function, dtype) the number of comparisons and the worst one."""
     global RECORDS
     with open(path) as f:
         RECORDS = [json.loads(line) for line in f if line.strip()]
-    rows = ["| test | tensor | dtype | worst rel-L2 | tolerance | note |", "|---|---|---|---|---|---|"]
-    for (fn, tensor, dt), r in sorted(worst_by_function().items()):
+    groups = {}
+    for r in RECORDS:
+        fn = r["test"].split("::")[-1].split("[")[0]
+        groups.setdefault((fn, r["dtype"]), []).append(r)
+    rows = ["| test | dtype | comparisons | worst rel-L2 | tolerance | worst tensor | note |", "|---|---|---|---|---|---|---|"]
+    for (fn, dt), rs in sorted(groups.items()):
+        r = max(rs, key=lambda q: q["rel_l2"] / q["tol"])
         note = r.get("judged", "")
         if "rel_l2_plain" in r:
             note += f" (plain {r['rel_l2_plain']:.2e}, cancellation {r.get('cancellation', float('nan')):.3g})"
-        rows.append(f"| {fn} | {tensor} | {dt} | {r['rel_l2']:.2e} | {r['tol']:.0e} | {note} |")
+        rows.append(f"| {fn} | {dt} | {len(rs)} | {r['rel_l2']:.2e} | {r['tol']:.0e} | {r['tensor']} | {note} |")
     head = f"{len(RECORDS)} comparisons; worst over all Float32 comparisons relative to their tolerance: "
     f32 = [r for r in RECORDS if r["dtype"] == "f32"]
     bf = [r for r in RECORDS if r["dtype"] == "bf16"]
