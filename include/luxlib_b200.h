@@ -69,6 +69,11 @@ typedef enum {
 #define LB2_FLAG_CTA_PAIR 4u /* tensor-core GEMM: take the CTA-pair kernel (cta_group::2, 256x256 tiles) for any operand layout
                                 once the problem occupies an eighth of the SM pairs (default: only for two MN-major operands) */
 #define LB2_FLAG_NO_CTA_PAIR 8u /* tensor-core GEMM: never take the CTA-pair kernel */
+/* lb2_conv_bwd only: the `x` argument is not x but the start of the workspace that lb2_conv_fwd was given for the same
+ * descriptor and x (and that the caller has kept untouched since): the general tensor-core path leaves its
+ * channel-innermost copy of x there and the filter gradient then reads that copy instead of making it again. Valid
+ * only where lb2_conv_fwd_leaves_x_copy() returns 1; refused (LB2_BAD_ARG) elsewhere. */
+#define LB2_FLAG_X_COPY_GIVEN 16u
 /* Per call: the persistent tensor-core GEMM of this call leaves n SMs (0..127) unoccupied, for a kernel the caller
  * runs beside it on another stream — e.g. the NCCL all-reduce of parameter gradients that Lux's DistributedOptimizer
  * issues (src/distributed/public_api.jl:275-278) under the remaining backward GEMM. */
@@ -89,6 +94,10 @@ LB2_API int32_t lb2_poll_device_status(void* stream);
  * the given limit (1 us .. 100 ms), on a barrier nothing arrives at — the wait routine of the tensor-core kernels. The
  * wait expires, the kernel records it and returns; lb2_poll_device_status then reports LB2_TIMEOUT once and the
  * device stays usable. */
+/* Diagnostics: the calling thread's last tensor-core GEMM launch (dense, matmul): out[0] kernel (1 single-CTA,
+ * 2 CTA pair; 0 none yet), out[1], out[2] tile rows and columns, out[3] tiles, out[4] CTAs or CTA pairs launched,
+ * out[5], out[6] whole-tile and total work slots (they differ when the tiles of a thin last wave are halved). */
+LB2_API int32_t lb2_last_gemm_plan(int32_t* out, int32_t n);
 LB2_API int32_t lb2_selftest_bounded_wait(uint64_t limit_ns, void* stream);
 
 /* ---- activation / bias-activation ------------------------------------------------------ */
@@ -168,6 +177,9 @@ LB2_API int32_t lb2_conv_fwd(void* y, void* preact, const void* x, const void* w
                      void* workspace, size_t workspace_bytes, void* stream);
 /* Pullback ∇fused_conv (lib/LuxLib/src/impl/conv.jl:261-275): g = dy .* act'(out, preact);
  * dw = ∇conv_filter(x, g); dx = ∇conv_data(g, w); db = sum_{spatial,N} g. Outputs may be NULL. */
+/* 1 when lb2_conv_fwd (without LB2_FLAG_FORCE_SIMT, on 16-byte aligned arrays) leaves a reusable copy of x at the
+ * start of its workspace for this geometry (see LB2_FLAG_X_COPY_GIVEN), else 0. */
+LB2_API int32_t lb2_conv_fwd_leaves_x_copy(const lb2_conv_desc* d, int32_t dtype);
 LB2_API size_t lb2_conv_bwd_workspace_bytes(const lb2_conv_desc* d, int32_t dtype, int32_t act);
 LB2_API int32_t lb2_conv_bwd(void* dw, void* dx, void* db, const void* dy, const void* out,
                      const void* preact, const void* x, const void* w, const lb2_conv_desc* d,
@@ -257,6 +269,19 @@ LB2_API int32_t lb2_pool_output_size(const lb2_pool_desc* desc, int32_t* out);
 LB2_API int32_t lb2_pool_fwd(void* y, const void* x, const lb2_pool_desc* desc, int32_t kind, int32_t dtype, void* stream);
 LB2_API int32_t lb2_pool_bwd(void* dx, const void* dy, const void* y, const void* x, const lb2_pool_desc* desc,
                           int32_t kind, int32_t dtype, void* stream);
+
+/* ---- Scale layer ------------------------------------------------------------------------------- */
+/* y = act.(x .* weight .+ bias) (src/layers/basic.jl:452-461; the {False} method has no bias: bias = NULL) with
+ * weight / bias of the layer's dims and x of shape (dims..., batch...): a (D, B) column-major view, D = prod(dims).
+ * Backward: g = dy .* act'(x .* weight .+ bias) (the pre-activation is rebuilt from x), dx = g .* weight,
+ * dweight = sum over the batch of g .* x, dbias = sum over the batch of g (fixed summation order).
+ * dbias is NULL exactly when bias is NULL. */
+LB2_API int32_t lb2_scale_fwd(void* y, const void* x, const void* weight, const void* bias, int64_t D, int64_t B,
+                              int32_t dtype, int32_t act, void* stream);
+LB2_API size_t lb2_scale_bwd_workspace_bytes(int64_t D, int64_t B);
+LB2_API int32_t lb2_scale_bwd(void* dx, void* dweight, void* dbias, const void* dy, const void* x, const void* weight,
+                              const void* bias, int64_t D, int64_t B, int32_t dtype, int32_t act, void* workspace,
+                              size_t workspace_bytes, void* stream);
 
 /* ---- loss ---------------------------------------------------------------------------------------- */
 /* MSELoss() (src/helpers/losses.jl:659: GenericLossFunction(l2_distance_loss; agg = mean), derivative 2(x - y) at

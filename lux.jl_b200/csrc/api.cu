@@ -6,6 +6,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "gemm.cuh"
 #include "tc_ptx.cuh"
 
 namespace lb2 {
@@ -69,7 +70,13 @@ __global__ void selftest_bounded_wait_kernel(unsigned int* status, uint64_t limi
 
 extern "C" {
 
-int32_t lb2_version(void) { return 101; }
+int32_t lb2_version(void) { return 102; }
+
+int32_t lb2_last_gemm_plan(int32_t* out, int32_t n) {
+  LB2_REQUIRE(out != nullptr && n >= 0, LB2_BAD_ARG, "out is null");
+  for (int i = 0; i < n && i < 8; ++i) out[i] = lb2::g_last_gemm_plan[i];
+  return LB2_OK;
+}
 
 int32_t lb2_selftest_bounded_wait(uint64_t limit_ns, void* stream) {
   LB2_REQUIRE(limit_ns >= 1000 && limit_ns <= 100000000ull, LB2_BAD_ARG, "limit must be between 1 microsecond and 100 milliseconds");

@@ -111,6 +111,12 @@ int32_t lb2_conv_fwd(void* y, void* preact, const void* x, const void* w, const 
   return conv_fwd_direct(y, preact, x, w, b, g, dtype, act, static_cast<cudaStream_t>(stream));
 }
 
+int32_t lb2_conv_fwd_leaves_x_copy(const lb2_conv_desc* d, int32_t dtype) {
+  ConvGeom g;
+  if (!valid_dtype(dtype) || make_geom(d, &g) != LB2_OK || y_numel(g) == 0) return 0;
+  return conv_route(g, dtype) == 2 ? 1 : 0;
+}
+
 size_t lb2_conv_bwd_workspace_bytes(const lb2_conv_desc* d, int32_t dtype, int32_t act) {
   ConvGeom g;
   if (!valid_dtype(dtype) || make_geom(d, &g) != LB2_OK) return 0;
@@ -157,8 +163,11 @@ int32_t lb2_conv_bwd(void* dw, void* dx, void* db, const void* dy, const void* o
     if (rc != LB2_OK) return rc;
   }
   const int route = (flags & LB2_FLAG_FORCE_SIMT) ? 0 : (lay.tc_bytes > 0 ? conv_route(g, dtype) : 0);
+  const bool x_is_copy = (flags & LB2_FLAG_X_COPY_GIVEN) != 0;
+  LB2_REQUIRE(!x_is_copy || (route == 2 && aligned_to(x, 256)), LB2_BAD_ARG,
+              "LB2_FLAG_X_COPY_GIVEN: this geometry does not run on the path that leaves a copy of x (or the pointer is not a workspace start)");
   void* tc_ws = ws + lay.g_bytes + lay.red_bytes;
-  if (route == 2) return conv_cw_bwd(dw, (dx && nx > 0) ? dx : nullptr, x, gptr, w, g, tc_ws, st);
+  if (route == 2) return conv_cw_bwd(dw, (dx && nx > 0) ? dx : nullptr, x, gptr, w, g, tc_ws, st, x_is_copy);
   // TMA needs 16-byte aligned bases for everything it loads (g, x) or stores (dx); other views go to the direct kernels
   const bool tc = route == 1 && aligned_to(gptr, 16) && aligned_to(x, 16) && aligned_to(dx, 16);
   if (tc && dtype == LB2_F32) {   // both gradients share one set of shifted copies of g

@@ -35,7 +35,7 @@ int32_t conv_cw_fwd(void* y, void* preact, const void* x, const void* w, const v
                     void* ws, cudaStream_t st);
 // both gradients (either of dw, dx may be null) from one channel-innermost copy of gy
 int32_t conv_cw_bwd(void* dw, void* dx, const void* x, const void* gy, const void* w, const ConvGeom& g, void* ws,
-                    cudaStream_t st);
+                    cudaStream_t st, bool x_is_copy = false);
 
 bool conv_tc_f32_supported(const ConvGeom& g);
 size_t conv_tc_f32_fwd_workspace_bytes(const ConvGeom& g);

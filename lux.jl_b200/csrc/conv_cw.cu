@@ -807,8 +807,10 @@ size_t conv_cw_bwd_workspace_bytes(const ConvGeom& g) {
   return gy + (dgrad > wgrad ? dgrad : wgrad);
 }
 
-// both gradients (either output may be null) from one channel-innermost copy of gy
-int32_t conv_cw_bwd(void* dw, void* dx, const void* x, const void* gy, const void* w, const ConvGeom& g, void* ws_, cudaStream_t st) {
+// both gradients (either output may be null) from one channel-innermost copy of gy. With `x_is_copy`, x points at the
+// channel-innermost copy that conv_cw_fwd left at the start of its workspace (same geometry, same x).
+int32_t conv_cw_bwd(void* dw, void* dx, const void* x, const void* gy, const void* w, const ConvGeom& g, void* ws_, cudaStream_t st,
+                    bool x_is_copy) {
   uint8_t* ws = static_cast<uint8_t*>(ws_);
   const CwCopy yc = cw_copy_of_y(g);
   int32_t rc = cw_transpose(ws, gy, g.out[0], g.out[1], g.cout, yc.Cp, g.batch, st);
@@ -818,8 +820,13 @@ int32_t conv_cw_bwd(void* dw, void* dx, const void* x, const void* gy, const voi
   if (dw != nullptr) {
     const int fold = cw_fold(g);
     const CwCopy xc = cw_copy_of_x(g);
-    rc = cw_copy_x(rest, x, g, xc, st);
-    if (rc != LB2_OK) return rc;
+    uint8_t* xcopy = rest;
+    if (x_is_copy) {
+      xcopy = static_cast<uint8_t*>(const_cast<void*>(x));
+    } else {
+      rc = cw_copy_x(rest, x, g, xc, st);
+      if (rc != LB2_OK) return rc;
+    }
     const CwWgPlan pl = cw_wg_plan(g);
     CwWgParams q{};
     q.OW = g.out[0]; q.OH = g.out[1]; q.NI = g.batch;
@@ -829,7 +836,7 @@ int32_t conv_cw_bwd(void* dw, void* dx, const void* x, const void* gy, const voi
     q.splits = pl.splits; q.kb_total = pl.kb_total; q.kb_per_split = pl.kb_per_split;
     // A (gy copy) and B (x copy) both MN-major: bits 15 and 16
     q.idesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | (1u << 16) | ((uint32_t)((pl.ppg * 64) >> 3) << 17) | ((uint32_t)(kCwBM >> 4) << 24);
-    q.partial = reinterpret_cast<float*>(rest + xc.bytes);
+    q.partial = reinterpret_cast<float*>(rest + (x_is_copy ? 0 : xc.bytes));
     q.status = device_status_word();
     LB2_REQUIRE(q.status != nullptr, LB2_LAUNCH_FAIL, "conv_cw: device status word unavailable");
     const int n_taps = fold ? cw_fold_taps(g, fold) : g.k[0] * g.k[1];
@@ -842,7 +849,7 @@ int32_t conv_cw_bwd(void* dw, void* dx, const void* x, const void* gy, const voi
       }
     CUtensorMap mG, mX;
     if (!cw_map(&mG, ws, yc.Cp, yc.W, yc.H, g.batch, pl.KW_, pl.KH_, pl.KI_, 1, 1) ||
-        !cw_map(&mX, rest, xc.Cp, xc.W, xc.H, g.batch, pl.KW_, pl.KH_, pl.KI_, q.sw, q.sh))
+        !cw_map(&mX, xcopy, xc.Cp, xc.W, xc.H, g.batch, pl.KW_, pl.KH_, pl.KI_, q.sw, q.sh))
       return fail(LB2_LAUNCH_FAIL, "conv_cw: cuTensorMapEncodeTiled failed");
     const int items = pl.co_tiles * pl.groups * pl.splits;
     const int grid = items < sm_count() ? items : sm_count();

@@ -45,4 +45,6 @@ int32_t gemm_dispatch(void* D, int64_t ldd, GemmOperand A, GemmOperand B, int64_
                       int32_t dtype, uint32_t flags, const GemmEpilogue& epi, void* ws, size_t ws_bytes,
                       cudaStream_t st);
 
+extern thread_local int32_t g_last_gemm_plan[8];   // see gemm_tc.cu
+
 }  // namespace lb2

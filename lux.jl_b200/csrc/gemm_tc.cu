@@ -58,6 +58,10 @@ struct TcParams {
   int32_t act, accumulate;
   unsigned int* status;
   int32_t raster_h;     // tiles are walked in bands of this many tile rows (see tile_coords)
+  // CTA-pair kernel only: work slots [0, full_slots) are whole 256 x 256 tiles; slots [full_slots, total_slots) are the
+  // two 128-column halves of the tiles that would otherwise form a partly filled last wave (see pair_slot)
+  int32_t full_slots, total_slots;
+  uint32_t idesc_half;  // instruction descriptor of a half tile (N = 128)
 };
 
 // Tile order. Walking all tile rows of one tile column before the next makes the CTAs that run at the same time
@@ -72,6 +76,19 @@ __device__ __forceinline__ void tile_coords(const TcParams& p, int tile, int* tm
   const int h = rows_left < p.raster_h ? rows_left : p.raster_h;
   *tm = band * p.raster_h + in_band % h;
   *tn = in_band / h;
+}
+
+// Work slot of the CTA-pair kernel -> (tile, half). A persistent grid of C pairs walks T tiles in ceil(T / C) waves,
+// and the last wave is as long as the others however few tiles it holds (256 tiles on 74 pairs: 3.46 waves of work in
+// the time of 4). When the T mod C leftover tiles are at most C / 2, each of them is issued as two 128-column halves to
+// two different pairs instead: the last wave then takes half the time. A half tile loads all of A and half of the B
+// boxes (which is why this needs an MN-major B, whose tile arrives as several 64-wide boxes) and issues MMAs of N = 128.
+__device__ __forceinline__ void pair_slot(const TcParams& p, int slot, int* tile, int* halved, int* which) {
+  if (slot < p.full_slots) { *tile = slot; *halved = 0; *which = 0; return; }
+  const int h = slot - p.full_slots;
+  *tile = p.full_slots + (h >> 1);
+  *halved = 1;
+  *which = h & 1;
 }
 
 constexpr int kBM = 128;
@@ -484,7 +501,6 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_cta_rank();        // 0 = leader
-  const int num_tiles = p.tiles_m * p.tiles_n;     // 256 x 256 tiles
   const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
 
   if (threadIdx.x == 0) {
@@ -508,17 +524,21 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       tma_prefetch_desc(&tmB);
       uint32_t stage = 0, phase = 0;
       bool ok = true;
-      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
-        int tm, tn;
+      for (int slot = cluster_id; slot < p.total_slots && ok; slot += num_clusters) {
+        int tile, halved, which, tm, tn;
+        pair_slot(p, slot, &tile, &halved, &which);
         tile_coords(p, tile, &tm, &tn);
+        const int bn_eff = halved ? BN / 2 : BN;                 // columns of this work item
+        const int b_boxes = halved ? p.b.boxes / 2 : p.b.boxes;  // B boxes this CTA loads per k-block
         const int m0 = tm * (2 * kBM) + (int)rank * kBM;
-        const int n0 = tn * BN + (int)rank * (BN / 2);
+        const int n0 = tn * BN + which * (BN / 2) + (int)rank * (bn_eff / 2);
+        const uint32_t stage_tx = 2u * (uint32_t)(Cfg::A_BYTES + b_boxes * p.b.box_bytes);
         for (int kb = 0; kb < p.num_kb; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, p.status, 0x10u)) { ok = false; break; }
           const uint32_t leader_full = map_to_cta(smem_u32(&full[stage]), 0);
           // The partner's bytes may be counted before this arrive (the transaction count then goes negative for
           // a moment); the phase cannot complete before it, because it is the barrier's only pending arrival.
-          if (rank == 0) mbar_expect_tx(&full[stage], 2 * Cfg::STAGE_BYTES);
+          if (rank == 0) mbar_expect_tx(&full[stage], stage_tx);
           const uint32_t sA = smem_base + stage * Cfg::STAGE_BYTES;
           const uint32_t sB = sA + Cfg::A_BYTES;
           const int k0 = kb * p.bk;
@@ -527,7 +547,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             const int32_t c1 = p.a.mn_major ? k0 : m0;
             tma_load_2d_pair(sA + bx * p.a.box_bytes, &tmA, c0, c1, leader_full);
           }
-          for (int bx = 0; bx < p.b.boxes; ++bx) {
+          for (int bx = 0; bx < b_boxes; ++bx) {
             const int32_t c0 = p.b.mn_major ? n0 + bx * p.b.mn_step : k0;
             const int32_t c1 = p.b.mn_major ? k0 : n0;
             tma_load_2d_pair(sB + bx * p.b.box_bytes, &tmB, c0, c1, leader_full);
@@ -541,7 +561,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     if (lane == 0 && rank == 0) {
       uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
       bool ok = true;
-      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+      for (int slot = cluster_id; slot < p.total_slots && ok; slot += num_clusters) {
+        const uint32_t idesc = slot < p.full_slots ? p.idesc : p.idesc_half;
         if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1u, p.status, 0x20u)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
@@ -556,7 +577,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           for (int ks = 0; ks < kKSteps; ++ks) {
             const uint64_t ad = ((uint64_t)p.a.desc_hi << 32) | (uint64_t)(a_lo32 + ks * p.a.k_advance);
             const uint64_t bd = ((uint64_t)p.b.desc_hi << 32) | (uint64_t)(b_lo32 + ks * p.b.k_advance);
-            umma_pair<TF32>(d_tmem, ad, bd, p.idesc, (kb | ks) != 0 ? 1u : 0u);
+            umma_pair<TF32>(d_tmem, ad, bd, idesc, (kb | ks) != 0 ? 1u : 0u);
           }
           umma_commit_pair_both(smem_u32(&empty[stage]));   // frees this stage in both CTAs
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -568,7 +589,6 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   } else if (warp >= 4) {
     // ---------------- epilogue (both CTAs, each on its own 128 rows) ----------------
     const int q = warp & 3, half = (warp - 4) >> 2;
-    constexpr int COLS = BN / 2;
     uint32_t acc = 0, acc_phase = 0;
     OutT* D = reinterpret_cast<OutT*>(p.D);
     OutT* P = reinterpret_cast<OutT*>(p.preact);
@@ -577,11 +597,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const bool accumulate = p.accumulate != 0;
     const uint32_t leader_acc_empty0 = map_to_cta(smem_u32(&acc_empty[0]), 0);
     bool ok = true;
-    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
-      int tm, tn;
+    for (int slot = cluster_id; slot < p.total_slots && ok; slot += num_clusters) {
+      int tile, halved, which, tm, tn;
+      pair_slot(p, slot, &tile, &halved, &which);
       tile_coords(p, tile, &tm, &tn);
+      const int COLS = halved ? BN / 4 : BN / 2;      // columns per epilogue warp group
       const int m0 = tm * (2 * kBM) + (int)rank * kBM;
-      const int n0 = tn * BN + half * COLS;
+      const int n0 = tn * BN + which * (BN / 2) + half * COLS;
       if (!mbar_wait_warp(&acc_full[acc], acc_phase, p.status, 0x80u)) { ok = false; break; }
       tc_fence_after();
       const int64_t m = (int64_t)m0 + q * 32 + lane;
@@ -638,6 +660,14 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 // ----------------------------------------------------------------------------------------------
 // host side
 // ----------------------------------------------------------------------------------------------
+// What the calling thread's last tensor-core GEMM launch looked like (read by lb2_last_gemm_plan; tests use it to
+// assert which kernel and which tile schedule a shape takes): kernel (1 single-CTA, 2 CTA pair), tile_m, tile_n,
+// tiles, workers (CTAs or CTA pairs), full_slots, total_slots.
+thread_local int32_t g_last_gemm_plan[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+void record_gemm_plan(int kernel, int tile_m, int tile_n, int tiles, int workers, int full_slots, int total_slots) {
+  int32_t* r = g_last_gemm_plan;
+  r[0] = kernel; r[1] = tile_m; r[2] = tile_n; r[3] = tiles; r[4] = workers; r[5] = full_slots; r[6] = total_slots; r[7] = 0;
+}
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -755,6 +785,7 @@ static int32_t tc_launch_cfg(const CUtensorMap& mA, const CUtensorMap& mB, const
   auto launch = [&](auto kernel) -> int32_t {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return fail(LB2_LAUNCH_FAIL, "gemm_tc: cannot reserve %d bytes of shared memory: %s", Cfg::SMEM_BYTES, cudaGetErrorString(e));
+    record_gemm_plan(1, kBM, BN, tiles, grid, tiles, tiles);
     kernel<<<grid, kThreadsSingle, Cfg::SMEM_BYTES, st>>>(mA, mB, mAl, mBl, p);
     LB2_CHECK_LAUNCH("gemm_tc");
     return LB2_OK;
@@ -830,7 +861,15 @@ static int32_t tc_launch_pair(const CUtensorMap& mA, const CUtensorMap& mB, cons
     if (clusters < 1) clusters = 1;
     if (tiles < clusters) clusters = tiles;
     cfg.gridDim = dim3(2 * clusters, 1, 1);
-    e = cudaLaunchKernelEx(&cfg, kernel, mA, mB, p);
+    TcParams q = p;
+    q.full_slots = q.total_slots = tiles;
+    const int rem = tiles % clusters;
+    if (rem > 0 && 2 * rem <= clusters && q.b.mn_major && q.b.boxes % 2 == 0) {   // halve the tiles of a thin last wave
+      q.full_slots = tiles - rem;
+      q.total_slots = tiles + rem;
+    }
+    record_gemm_plan(2, 2 * kBM, kPairBN, tiles, clusters, q.full_slots, q.total_slots);
+    e = cudaLaunchKernelEx(&cfg, kernel, mA, mB, q);
     if (e != cudaSuccess) return fail(LB2_LAUNCH_FAIL, "gemm_tc_pair: %s", cudaGetErrorString(e));
     return LB2_OK;
   };
@@ -918,6 +957,7 @@ int32_t gemm_tc_launch(void* D, int64_t ldd, GemmOperand A, GemmOperand B, int64
   const uint32_t fmt = tf32 ? 2u : 1u;
   p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((A.mn_major ? 1u : 0u) << 15) | ((B.mn_major ? 1u : 0u) << 16) |
             ((uint32_t)(tile_n >> 3) << 17) | ((uint32_t)(tile_m >> 4) << 24);
+  p.idesc_half = (p.idesc & ~(0x3Fu << 17)) | ((uint32_t)((tile_n / 2) >> 3) << 17);
   p.D = D; p.ldd = ldd;
   p.bias = epi.bias; p.preact = epi.preact; p.act = epi.act; p.accumulate = epi.accumulate;
   p.status = device_status_word();

@@ -129,12 +129,17 @@ ln_fwd_ring_kernel(T* __restrict__ y, float* __restrict__ mean_out, float* __res
     }
     return;
   }
-  Vec16<T> gv[NV], bv[NV];
+  // scale and shift of this thread's features, unpacked once (the per-row work is then free of conversions)
+  float gf[NV][V], bf[NV][V];
   if constexpr (AFFINE) {
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
       const int64_t i = ((int64_t)k * kRingCompute + t) * V;
-      if (i < D) { gv[k] = load16(gamma + i); bv[k] = load16(beta + i); }
+      if (i < D) {
+        const Vec16<T> gv = load16(gamma + i), bv = load16(beta + i);
+#pragma unroll
+        for (int j = 0; j < V; ++j) { gf[k][j] = gv.get(j); bf[k][j] = bv.get(j); }
+      }
     }
   }
   const float invD = 1.f / (float)D;
@@ -144,42 +149,43 @@ ln_fwd_ring_kernel(T* __restrict__ y, float* __restrict__ mean_out, float* __res
     const int64_t row = blockIdx.x + it * gridDim.x;
     if (!mbar_wait_warp(&full[st], ph, status, 0x400000u)) *abort_flag = 1;
     const T* sx = reinterpret_cast<const T*>(data + (size_t)st * row_bytes);
-    Vec16<T> xv[NV];
-    float s = 0.f;
+    // One pass over the row: sums of d = x - K and of d^2 with K = the row's first element (a sample of the row, so
+    // |mean - K| is of the order of the deviation and var = E[d^2] - E[d]^2 does not cancel), reduced together.
+    const float K0 = to_f32(sx[0]);
+    float df[NV][V];
+    float s = 0.f, q = 0.f;
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
       const int64_t i = ((int64_t)k * kRingCompute + t) * V;
       if (i < D) {
-        xv[k] = load16(sx + i);
+        const Vec16<T> xv = load16(sx + i);
 #pragma unroll
-        for (int j = 0; j < V; ++j) s += xv[k].get(j);
+        for (int j = 0; j < V; ++j) {
+          const float d = xv.get(j) - K0;
+          df[k][j] = d;
+          s += d;
+          q = fmaf(d, d, q);
+        }
       }
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(&empty[st]);
-    const float mean = group_sum(s, red, kRingCompute) * invD;
+    const float2 sq = group_sum2(s, q, red, kRingCompute);
     if (*abort_flag) { drain_after_abort(); break; }
-    float q = 0.f;
-#pragma unroll
-    for (int k = 0; k < NV; ++k) {
-      const int64_t i = ((int64_t)k * kRingCompute + t) * V;
-      if (i < D) {
-#pragma unroll
-        for (int j = 0; j < V; ++j) { float d = xv[k].get(j) - mean; q += d * d; }
-      }
-    }
-    const float var = group_sum(q, red, kRingCompute) * invD;
+    const float dm = sq.x * invD;                                  // mean - K
+    const float var = fmaxf(fmaf(-dm, dm, sq.y * invD), 0.f);
     const float inv = 1.f / sqrtf(var + eps);
-    if (t == 0) { mean_out[row] = mean; inv_out[row] = inv; }
+    const float nmi = -dm * inv;
+    if (t == 0) { mean_out[row] = K0 + dm; inv_out[row] = inv; }
     T* yr = y + row * D;
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
       const int64_t i = ((int64_t)k * kRingCompute + t) * V;
       if (i < D) {
         store16_stream(yr + i, vec_from<T>([&](int j) {
-          float gp = inv, bp = -mean * inv;
-          if constexpr (AFFINE) { gp = gv[k].get(j) * inv; bp = bv[k].get(j) - mean * gp; }
-          return act_apply_any<ACT, FAST>(act_rt, fmaf(xv[k].get(j), gp, bp));
+          float v = fmaf(df[k][j], inv, nmi);                      // (x - mean) * inv
+          if constexpr (AFFINE) v = fmaf(v, gf[k][j], bf[k][j]);
+          return act_apply_any<ACT, FAST>(act_rt, v);
         }));
       }
     }
@@ -222,13 +228,20 @@ ln_bwd_ring_kernel(T* __restrict__ dx, float* __restrict__ partial, const T* __r
     }
     return;
   }
-  Vec16<T> gv[NV], bv[NV];
+  // the scale of this thread's features unpacked once; the shift is needed only to rebuild a pre-activation
+  float gf[NV][V];
+  Vec16<T> bv[NV];
   float adg[NV][V], adb[NV][V];
   if constexpr (AFFINE) {
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
       const int64_t i = ((int64_t)k * kRingCompute + t) * V;
-      if (i < D) { gv[k] = load16(gamma + i); bv[k] = load16(beta + i); }
+      if (i < D) {
+        const Vec16<T> gv = load16(gamma + i);
+#pragma unroll
+        for (int j = 0; j < V; ++j) gf[k][j] = gv.get(j);
+        if constexpr (ACT != LB2_ACT_IDENTITY) bv[k] = load16(beta + i);
+      }
 #pragma unroll
       for (int j = 0; j < V; ++j) { adg[k][j] = 0.f; adb[k][j] = 0.f; }
     }
@@ -244,7 +257,15 @@ ln_bwd_ring_kernel(T* __restrict__ dx, float* __restrict__ partial, const T* __r
     const T* sdy = reinterpret_cast<const T*>(data + (size_t)st * 2 * row_bytes + row_bytes);
     // The row stays in its ring stage through both passes (registers hold only the dgamma/dbeta
     // accumulators), so two CTAs fit on an SM and one reduces while the other streams.
-    const float nmi = -mean * inv;
+    // d = dy * act'(pre-activation), the pre-activation rebuilt as ((x - mean) * inv) * gamma + beta
+    auto act_scaled = [&](float d, float xh, int k, int j) {
+      if constexpr (ACT != LB2_ACT_IDENTITY) {
+        float pre = xh;
+        if constexpr (AFFINE) pre = fmaf(xh, gf[k][j], bv[k].get(j));
+        d *= act_grad_pre_any<ACT, FAST>(act_rt, pre);
+      }
+      return d;
+    };
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
@@ -254,17 +275,12 @@ ln_bwd_ring_kernel(T* __restrict__ dx, float* __restrict__ partial, const T* __r
 #pragma unroll
         for (int j = 0; j < V; ++j) {
           const float xh = (xv.get(j) - mean) * inv;
-          float d = gy.get(j);
-          if constexpr (ACT != LB2_ACT_IDENTITY) {
-            float gp = inv, bp = nmi;
-            if constexpr (AFFINE) { gp = gv[k].get(j) * inv; bp = bv[k].get(j) - mean * gp; }
-            d *= act_grad_pre_any<ACT, FAST>(act_rt, fmaf(xv.get(j), gp, bp));
-          }
+          const float d = act_scaled(gy.get(j), xh, k, j);
           float g = d;
           if constexpr (AFFINE) {
             adg[k][j] = fmaf(d, xh, adg[k][j]);
             adb[k][j] += d;
-            g = d * gv[k].get(j);
+            g = d * gf[k][j];
           }
           s1 += g;
           s2 = fmaf(g, xh, s2);
@@ -274,8 +290,9 @@ ln_bwd_ring_kernel(T* __restrict__ dx, float* __restrict__ partial, const T* __r
     const float2 m12 = group_sum2(s1, s2, red, kRingCompute);
     if (*abort_flag) { drain_after_abort(); break; }
     const float m1 = m12.x * invD, m2 = m12.y * invD;
-    // dx = inv * (g - m1 - xh * m2)
-    const float c0 = -inv * m1, c1 = -inv * m2;
+    // dx = inv * (g - m1 - xh * m2) = g * inv + (x * c1i + c0m): the xh term folded into one multiply-add on x
+    const float c1i = -inv * m2 * inv;
+    const float c0m = fmaf(-mean, c1i, -inv * m1);
     T* dxr = dx + row * D;
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
@@ -283,16 +300,11 @@ ln_bwd_ring_kernel(T* __restrict__ dx, float* __restrict__ partial, const T* __r
       if (i < D) {
         const Vec16<T> xv = load16(sx + i), gy = load16(sdy + i);
         store16_stream(dxr + i, vec_from<T>([&](int j) {
-          const float xh = (xv.get(j) - mean) * inv;
+          const float xf = xv.get(j);
           float d = gy.get(j);
-          if constexpr (ACT != LB2_ACT_IDENTITY) {
-            float gp = inv, bp = nmi;
-            if constexpr (AFFINE) { gp = gv[k].get(j) * inv; bp = bv[k].get(j) - mean * gp; }
-            d *= act_grad_pre_any<ACT, FAST>(act_rt, fmaf(xv.get(j), gp, bp));
-          }
-          float gi = d * inv;
-          if constexpr (AFFINE) gi *= gv[k].get(j);
-          return fmaf(xh, c1, gi + c0);
+          if constexpr (ACT != LB2_ACT_IDENTITY) d = act_scaled(d, (xf - mean) * inv, k, j);
+          if constexpr (AFFINE) d *= gf[k][j];
+          return fmaf(d, inv, fmaf(xf, c1i, c0m));
         }));
       }
     }

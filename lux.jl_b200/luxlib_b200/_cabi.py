@@ -12,7 +12,7 @@ LIB_PATH = os.path.join(os.path.dirname(_HERE), "lib", "libluxlib_b200.so")
 OK, BAD_ARG, BAD_SHAPE, BAD_ALIGN, UNSUPPORTED_DTYPE, LAUNCH_FAIL, TIMEOUT, WORKSPACE_TOO_SMALL = 0, -1, -2, -3, -4, -5, -6, -7
 F32, BF16 = 0, 1
 ACT_IDENTITY, ACT_RELU, ACT_GELU_TANH, ACT_GELU_ERF, ACT_TANH, ACT_SIGMOID, ACT_SWISH = range(7)
-FLAG_TF32_1X, FLAG_FORCE_SIMT, FLAG_CTA_PAIR, FLAG_NO_CTA_PAIR = 1, 2, 4, 8
+FLAG_TF32_1X, FLAG_FORCE_SIMT, FLAG_CTA_PAIR, FLAG_NO_CTA_PAIR, FLAG_X_COPY_GIVEN = 1, 2, 4, 8, 16
 
 
 def flag_reserve_sms(n: int) -> int:
@@ -87,6 +87,11 @@ PROTOTYPES = {
     "lb2_pool_output_size": (_i32, [C.POINTER(PoolDesc), C.POINTER(C.c_int32)]),
     "lb2_pool_fwd": (_i32, [_p, _p, C.POINTER(PoolDesc), _i32, _i32, _p]),
     "lb2_pool_bwd": (_i32, [_p, _p, _p, _p, C.POINTER(PoolDesc), _i32, _i32, _p]),
+    "lb2_conv_fwd_leaves_x_copy": (_i32, [_p, _i32]),
+    "lb2_last_gemm_plan": (_i32, [C.POINTER(C.c_int32), _i32]),
+    "lb2_scale_fwd": (_i32, [_p, _p, _p, _p, _i64, _i64, _i32, _i32, _p]),
+    "lb2_scale_bwd_workspace_bytes": (_sz, [_i64, _i64]),
+    "lb2_scale_bwd": (_i32, [_p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i32, _i32, _p, _sz, _p]),
     "lb2_mse_loss_workspace_bytes": (_sz, [_i64]),
     "lb2_mse_loss": (_i32, [_fp, _p, _p, _p, _i64, _i32, _p, _sz, _p]),
     "lb2_optimizer_step": (_i32, [C.POINTER(OptLeaf), _i32, _i32, _dbl, _dbl, _dbl, _dbl, _i64, _dbl, _i32, _p]),

@@ -277,6 +277,42 @@ def rrule_bias_activation(act: str, x, bias=None):
     return y, pullback
 
 
+def rrule_scale(act: str, weight, x, bias=None):
+    """The Scale layer (src/layers/basic.jl:452-461): y = act.(x .* weight .+ bias), weight / bias of the layer's dims,
+    x of shape (dims..., batch...); pullback Δ -> (∂weight, ∂x, ∂bias) of the broadcast."""
+    lib = _cabi.load()
+    weight, x, bias = _promote(weight, x, bias)
+    nd = weight.dim()
+    if x.dim() < nd or tuple(x.shape[:nd]) != tuple(weight.shape):
+        raise DimensionMismatch(f"x of size {tuple(x.shape)} does not start with the layer's dims {tuple(weight.shape)}")
+    if bias is not None and tuple(bias.shape) != tuple(weight.shape):
+        raise DimensionMismatch("weight and bias must have the same shape")
+    X, Wt = as_colmajor(x), as_colmajor(weight)
+    Bs = as_colmajor(bias) if bias is not None else None
+    D = Wt.numel()
+    B = X.numel() // D if D else 0
+    code, dt = act_code(act), dtype_code(X.dtype)
+    y = jl_empty(X.shape, X.dtype, X.device)
+    _cabi.check(lib.lb2_scale_fwd(ptr(y), ptr(X), ptr(Wt), ptr(Bs), D, B, dt, code, current_stream(X.device)))
+
+    def pullback(delta):
+        d = as_colmajor(delta.to(X.dtype))
+        dx = jl_empty(X.shape, X.dtype, X.device)
+        dw = jl_empty(Wt.shape, X.dtype, X.device)
+        db = jl_empty(Wt.shape, X.dtype, X.device) if Bs is not None else None
+        _, wsp, wsn = _ws(lib.lb2_scale_bwd_workspace_bytes(D, B), X.device)
+        _cabi.check(lib.lb2_scale_bwd(ptr(dx), ptr(dw), ptr(db), ptr(d), ptr(X), ptr(Wt), ptr(Bs), D, B, dt, code, wsp, wsn,
+                                      current_stream(X.device)))
+        return dw, dx, db
+
+    return y, pullback
+
+
+def scale(act: str, weight, x, bias=None):
+    """act.(x .* weight .+ bias) — the Scale layer (src/layers/basic.jl:452-461)."""
+    return rrule_scale(act, weight, x, bias)[0]
+
+
 def _add_act(code: int, X, Y):
     lib = _cabi.load()
     z = jl_empty(X.shape, X.dtype, X.device)
@@ -374,7 +410,7 @@ def _conv_desc(weight, x, cd: ConvDims) -> _cabi.ConvDesc:
     return _conv_desc_from(tuple(weight.shape), tuple(x.shape[:-2]), x.shape[-2], x.shape[-1], cd)
 
 
-def _conv_fwd(act, weight, x, b, cd, want_preact, flags=0):
+def _conv_fwd(act, weight, x, b, cd, want_preact, flags=0, want_ws=False):
     lib = _cabi.load()
     weight, x, b = _promote(weight, x, b)
     d = _conv_desc(weight, x, cd)
@@ -387,10 +423,14 @@ def _conv_fwd(act, weight, x, b, cd, want_preact, flags=0):
     y = jl_empty(yshape, X.dtype, X.device)
     pre = jl_empty(yshape, X.dtype, X.device) if want_preact else None
     dt = dtype_code(X.dtype)
-    _, wsp, wsn = _ws(lib.lb2_conv_fwd_workspace_bytes(C.byref(d), dt), X.device)
+    ws, wsp, wsn = _ws(lib.lb2_conv_fwd_workspace_bytes(C.byref(d), dt), X.device)
     _cabi.check(lib.lb2_conv_fwd(ptr(y), ptr(pre), ptr(X), ptr(Wt), ptr(b), C.byref(d), dt, act_code(act), flags, wsp, wsn,
                                  current_stream(X.device)))
-    return y, pre, (Wt, X, b, d, dt)
+    # the general tensor-core path leaves its channel-innermost copy of x at the start of the workspace; a pullback
+    # that keeps the workspace alive hands it back instead of having the copy made again
+    keep = ws if (want_ws and ws is not None and not (flags & _cabi.FLAG_FORCE_SIMT) and X.data_ptr() % 16 == 0 and
+                  lib.lb2_conv_fwd_leaves_x_copy(C.byref(d), dt) == 1) else None
+    return y, pre, (Wt, X, b, d, dt, keep)
 
 
 def fused_conv_bias_activation(act: str, weight, x, b, cdims: ConvDims, *, flags: int = 0):
@@ -403,7 +443,7 @@ def rrule_fused_conv(act: str, weight, x, b, cdims: ConvDims, *, flags: int = 0)
     Pullback Δ -> (∂weight, ∂x, ∂b)."""
     lib = _cabi.load()
     keep_pre = needs_preactivation(act)
-    y, pre, (Wt, X, bb, d, dt) = _conv_fwd(act, weight, x, b, cdims, keep_pre, flags)
+    y, pre, (Wt, X, bb, d, dt, xcopy) = _conv_fwd(act, weight, x, b, cdims, keep_pre, flags, want_ws=True)
     code = act_code(act)
 
     def pullback(delta, need_dx=True):
@@ -413,8 +453,9 @@ def rrule_fused_conv(act: str, weight, x, b, cdims: ConvDims, *, flags: int = 0)
         dx = jl_empty(X.shape, X.dtype, X.device) if need_dx else None
         db = jl_empty((d.cout,), X.dtype, X.device) if bb is not None else None
         _, wsp, wsn = _ws(lib.lb2_conv_bwd_workspace_bytes(C.byref(d), dt, code), X.device)
-        _cabi.check(lib.lb2_conv_bwd(ptr(dw), ptr(dx), ptr(db), ptr(dl), None if keep_pre else ptr(y), ptr(pre), ptr(X),
-                                     ptr(Wt), C.byref(d), dt, code, flags, wsp, wsn, current_stream(X.device)))
+        xarg, xflag = (ptr(xcopy), _cabi.FLAG_X_COPY_GIVEN) if xcopy is not None else (ptr(X), 0)
+        _cabi.check(lib.lb2_conv_bwd(ptr(dw), ptr(dx), ptr(db), ptr(dl), None if keep_pre else ptr(y), ptr(pre), xarg,
+                                     ptr(Wt), C.byref(d), dt, code, flags | xflag, wsp, wsn, current_stream(X.device)))
         return dw, dx, db
 
     return y, pullback

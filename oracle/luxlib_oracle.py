@@ -384,6 +384,27 @@ def fused_conv_rrule(act: str, w, x, b, cd: ConvDims, gelu="tanh"):
     return z, pullback
 
 
+def scale_rrule(act: str, w, x, b=None, gelu="tanh"):
+    """Scale layer (src/layers/basic.jl:452-461): σ.(x .* weight .+ bias), weight / bias broadcast over the trailing
+    batch dimensions of x. Pullback Δ -> (∂w, ∂x, ∂b) by the broadcast rule: g = Δ·σ′, ∂x = g·w, ∂w = Σ_batch g·x,
+    ∂b = Σ_batch g."""
+    nd = w.ndim
+    wb = w.reshape(w.shape + (1,) * (x.ndim - nd))
+    pre = x * wb
+    if b is not None:
+        pre = pre + b.reshape(wb.shape)
+    z = act_fn(act, pre, gelu)
+
+    def pullback(delta):
+        g = grad_activation(delta, z, act, pre if needs_preactivation(act) else None, gelu)
+        axes = tuple(range(nd, x.ndim))
+        dw = (g * x).sum(axis=axes) if axes else g * x
+        db = None if b is None else (g.sum(axis=axes) if axes else g)
+        return dw, g * wb, db
+
+    return z, pullback
+
+
 def conv_transpose_output_size(in_sz, k, cd: ConvDims, outpad=0):
     """conv_transpose_dims (src/layers/conv.jl:19-45): (in - 1)*stride + 1 + (k - 1)*dil - pad_lo - pad_hi + outpad."""
     nd = len(in_sz)

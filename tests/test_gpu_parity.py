@@ -847,3 +847,30 @@ def test_conv_transpose_fwd_bwd(dt, act, case):
     check(dx, dx_ref, dt, "dx")
     check(db, db_ref, dt, "db")
     assert L._cabi.load().lb2_poll_device_status(None) == 0
+
+
+# ------------------------------------------------------------------------------------------
+# Scale layer
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("act", ["identity", "relu", "gelu", "tanh", "swish"])
+@pytest.mark.parametrize("shape", [((5,), (5, 7)), ((8, 3), (8, 3, 33)), ((256,), (256, 130)), ((6, 4), (6, 4)), ((40, 8), (40, 8, 3, 70))])
+@pytest.mark.parametrize("use_bias", [True, False])
+def test_scale_layer_fwd_bwd(dt, act, shape, use_bias):
+    dims, xs = shape
+    rng = np.random.default_rng(45)
+    x = prep(rng.standard_normal(xs), dt)
+    w = prep(rng.uniform(0.5, 1.5, dims), dt)
+    b = prep(rng.uniform(-0.3, 0.3, dims), dt) if use_bias else None
+    z_ref, pb_ref = O.scale_rrule(act, w, x, b)
+    z, pb = L.rrule_scale(act, dev(w, dt), dev(x, dt), dev(b, dt) if use_bias else None)
+    check(z, z_ref, dt, "y")
+    delta = prep(rng.standard_normal(xs), dt)
+    dw_ref, dx_ref, db_ref = pb_ref(delta)
+    dw, dx, db = pb(dev(delta, dt))
+    check(dw, dw_ref, dt, "dw")
+    check(dx, dx_ref, dt, "dx")
+    if use_bias:
+        check(db, db_ref, dt, "db")
+    else:
+        assert db is None

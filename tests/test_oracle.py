@@ -372,3 +372,22 @@ def test_conv_transpose_against_torch():
         np.testing.assert_allclose(dx, tx.grad.numpy().transpose(3, 2, 1, 0), rtol=1e-10, atol=1e-10)
         np.testing.assert_allclose(dw, tw.grad.numpy().transpose(3, 2, 1, 0), rtol=1e-10, atol=1e-10)
         np.testing.assert_allclose(db, tb.grad.numpy(), rtol=1e-10, atol=1e-10)
+
+
+def test_scale_against_torch_autograd():
+    import torch
+    rng = np.random.default_rng(44)
+    x, w, b = rng.standard_normal((5, 3, 7)), rng.standard_normal((5, 3)), rng.standard_normal((5, 3))
+    delta = rng.standard_normal(x.shape)
+    for act, tact in (("identity", lambda t: t), ("tanh", torch.tanh), ("relu", torch.relu), ("sigmoid", torch.sigmoid)):
+        z, pb = O.scale_rrule(act, w, x, b)
+        tx, tw, tb = (torch.tensor(a, requires_grad=True) for a in (x, w, b))
+        tz = tact(tx * tw[..., None] + tb[..., None])
+        tz.backward(torch.tensor(delta))
+        dw, dx, db = pb(delta)
+        np.testing.assert_allclose(z, tz.detach().numpy(), rtol=1e-12, atol=1e-12)
+        np.testing.assert_allclose(dx, tx.grad.numpy(), rtol=1e-10, atol=1e-12)
+        np.testing.assert_allclose(dw, tw.grad.numpy(), rtol=1e-10, atol=1e-12)
+        np.testing.assert_allclose(db, tb.grad.numpy(), rtol=1e-10, atol=1e-12)
+    z, pb = O.scale_rrule("identity", w, x, None)
+    assert pb(delta)[2] is None and np.allclose(z, x * w[..., None])
