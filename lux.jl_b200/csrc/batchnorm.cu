@@ -28,19 +28,53 @@ struct BnPlan {
   int64_t rows_per_chunk;
 };
 
+// Upper bound of the batch chunks of the reduction passes (sizes the workspace; the launch picks its own count, at
+// most this one: bn_plan_fit).
+constexpr int kBnMaxChunks = 64;
 static BnPlan bn_plan(int64_t S, int64_t C, int64_t B) {
-  const int64_t target = (int64_t)sm_count() * 4;
-  int64_t per_chunk_ctas = (S == 1) ? (C + 31) / 32 : C;
-  if (per_chunk_ctas < 1) per_chunk_ctas = 1;
-  int64_t chunks = (target + per_chunk_ctas - 1) / per_chunk_ctas;
-  const int64_t max_chunks = (S == 1) ? (B + 31) / 32 : B;
-  if (chunks > max_chunks) chunks = max_chunks;
-  if (chunks < 1) chunks = 1;
-  if (chunks > 512) chunks = 512;
   BnPlan p;
+  if (S == 1) {
+    const int64_t target = (int64_t)sm_count() * 4;
+    int64_t per_chunk_ctas = (C + 31) / 32;
+    if (per_chunk_ctas < 1) per_chunk_ctas = 1;
+    int64_t chunks = (target + per_chunk_ctas - 1) / per_chunk_ctas;
+    const int64_t max_chunks = (B + 31) / 32;
+    if (chunks > max_chunks) chunks = max_chunks;
+    if (chunks < 1) chunks = 1;
+    if (chunks > 512) chunks = 512;
+    p.rows_per_chunk = (B + chunks - 1) / chunks;
+    p.chunks = (int)((B + p.rows_per_chunk - 1) / p.rows_per_chunk);
+    return p;
+  }
+  int64_t chunks = B < kBnMaxChunks ? (B < 1 ? 1 : B) : kBnMaxChunks;
   p.rows_per_chunk = (B + chunks - 1) / chunks;
   p.chunks = (int)((B + p.rows_per_chunk - 1) / p.rows_per_chunk);
   return p;
+}
+
+// Chunks for a reduction kernel of which `ctas_per_sm` CTAs are resident per SM: a CTA's time is a fixed part (start-up,
+// block reduction, tail: worth about 16 KB of streaming) plus its batch rows' bytes, and the launch takes
+// ceil(CTAs / resident CTAs) rounds of that, so the count that minimises rounds x (rows x plane_bytes + 16 KB) is taken
+// (the fewest chunks among equals). A grid a little larger than what is resident would otherwise run a second, nearly
+// empty round and double the launch's duration.
+static BnPlan bn_plan_fit(int64_t C, int64_t B, int ctas_per_sm, int64_t plane_bytes) {
+  const int64_t capacity = (int64_t)sm_count() * (ctas_per_sm < 1 ? 1 : ctas_per_sm);
+  BnPlan best{1, B < 1 ? 1 : B};
+  int64_t best_cost = -1;
+  const int64_t max_chunks = B < kBnMaxChunks ? (B < 1 ? 1 : B) : kBnMaxChunks;
+  for (int64_t ch = 1; ch <= max_chunks; ++ch) {
+    const int64_t rows = (B + ch - 1) / ch, used = (B + rows - 1) / rows;
+    const int64_t rounds = (C * used + capacity - 1) / capacity;
+    const int64_t cost = rounds * (rows * plane_bytes + 16384);
+    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best.chunks = (int)used; best.rows_per_chunk = rows; }
+  }
+  return best;
+}
+
+template <typename K> static int bn_resident_ctas(K kernel) {
+  int n = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, 256, 0) != cudaSuccess || n < 1) { cudaGetLastError(); n = 4; }
+  return n;
 }
 
 // Plan of the fused (single cooperative launch) path; see bn_fused_kernel.
@@ -442,19 +476,23 @@ static unsigned apply_grid(int64_t items) {
   return (unsigned)(g < 1 ? 1 : (g > cap ? cap : g));
 }
 
+// launches the reduction pass and returns the number of batch chunks (rows of `partial`) it wrote
 template <typename T, int MODE, int ACT, bool AFFINE>
-static void bn_reduce_launch(float* partial, const T* x, const T* dy, const T* g, const T* b, const float* sm,
-                             const float* si, int64_t S, int64_t C, int64_t B, const BnPlan& p, int act, cudaStream_t st) {
+static int bn_reduce_launch(float* partial, const T* x, const T* dy, const T* g, const T* b, const float* sm,
+                            const float* si, int64_t S, int64_t C, int64_t B, const BnPlan& p, int act, cudaStream_t st) {
   constexpr int V = Vec16<T>::N;
   if (S == 1) {
     dim3 grid((unsigned)((C + 31) / 32), p.chunks), block(32, 8);
     bn_reduce_s1_kernel<T, MODE, ACT, AFFINE><<<grid, block, 0, st>>>(partial, x, dy, g, b, sm, si, C, B, p.rows_per_chunk, act);
-  } else {
-    dim3 grid((unsigned)C, p.chunks);
-    const bool vec = aligned_to(x, 16) && (!dy || aligned_to(dy, 16)) && S % V == 0;
-    if (vec) bn_reduce_kernel<T, MODE, ACT, AFFINE, true><<<grid, 256, 0, st>>>(partial, x, dy, g, b, sm, si, S, C, B, p.rows_per_chunk, act);
-    else bn_reduce_kernel<T, MODE, ACT, AFFINE, false><<<grid, 256, 0, st>>>(partial, x, dy, g, b, sm, si, S, C, B, p.rows_per_chunk, act);
+    return p.chunks;
   }
+  const bool vec = aligned_to(x, 16) && (!dy || aligned_to(dy, 16)) && S % V == 0;
+  const int occ = vec ? bn_resident_ctas(bn_reduce_kernel<T, MODE, ACT, AFFINE, true>) : bn_resident_ctas(bn_reduce_kernel<T, MODE, ACT, AFFINE, false>);
+  const BnPlan f = bn_plan_fit(C, B, occ, S * (int64_t)sizeof(T) * (dy ? 2 : 1));      // f.chunks <= p.chunks: both are capped by kBnMaxChunks and B
+  dim3 grid((unsigned)C, f.chunks);
+  if (vec) bn_reduce_kernel<T, MODE, ACT, AFFINE, true><<<grid, 256, 0, st>>>(partial, x, dy, g, b, sm, si, S, C, B, f.rows_per_chunk, act);
+  else bn_reduce_kernel<T, MODE, ACT, AFFINE, false><<<grid, 256, 0, st>>>(partial, x, dy, g, b, sm, si, S, C, B, f.rows_per_chunk, act);
+  return f.chunks;
 }
 
 template <typename T, int MODE, int ACT, bool AFFINE>
@@ -870,11 +908,11 @@ int32_t lb2_batchnorm_fwd_train(void* y, float* save_mean, float* save_invstd, v
     });
   }
   LB2_DISPATCH_DTYPE(dtype, {
-    bn_reduce_launch<T, 0, LB2_ACT_IDENTITY, false>(partial, (const T*)x, nullptr, nullptr, nullptr, nullptr, nullptr, S, C, B, p, act, st);
+    const int used = bn_reduce_launch<T, 0, LB2_ACT_IDENTITY, false>(partial, (const T*)x, nullptr, nullptr, nullptr, nullptr, nullptr, S, C, B, p, act, st);
     LB2_CHECK_LAUNCH("batchnorm statistics");
     bn_finalize_fwd_kernel<T><<<(unsigned)((C + 127) / 128), 128, 0, st>>>(
         save_mean, save_invstd, coef, (T*)new_rmean, (T*)new_rvar, (const T*)rmean, (const T*)rvar, (const T*)gamma,
-        (const T*)beta, (const T*)x, partial, S, C, B, p.chunks, (float)momentum, (float)eps);
+        (const T*)beta, (const T*)x, partial, S, C, B, used, (float)momentum, (float)eps);
     LB2_CHECK_LAUNCH("batchnorm finalise");
     LB2_DISPATCH_ACT3(act, {
       bn_apply_launch<T, 0, ACT, false>((T*)y, (const T*)x, nullptr, coef, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, S, C, B, (float)eps, act, st);
@@ -946,12 +984,13 @@ static int32_t bn_bwd_impl(void* dx, void* dgamma, void* dbeta, const void* dy, 
     });
   }
   LB2_DISPATCH_DTYPE(dtype, {
+    int used = p.chunks;
     LB2_DISPATCH_ACT3(act, {
-      if (gamma) bn_reduce_launch<T, 1, ACT, true>(partial, (const T*)x, (const T*)dy, (const T*)gamma, (const T*)beta, save_mean, save_invstd, S, C, B, p, act, st);
-      else bn_reduce_launch<T, 1, ACT, false>(partial, (const T*)x, (const T*)dy, nullptr, nullptr, save_mean, save_invstd, S, C, B, p, act, st);
+      if (gamma) used = bn_reduce_launch<T, 1, ACT, true>(partial, (const T*)x, (const T*)dy, (const T*)gamma, (const T*)beta, save_mean, save_invstd, S, C, B, p, act, st);
+      else used = bn_reduce_launch<T, 1, ACT, false>(partial, (const T*)x, (const T*)dy, nullptr, nullptr, save_mean, save_invstd, S, C, B, p, act, st);
     });
     LB2_CHECK_LAUNCH("batchnorm backward reduction");
-    bn_finalize_bwd_kernel<T><<<(unsigned)((C + 127) / 128), 128, 0, st>>>((T*)dgamma, (T*)dbeta, coef, (const T*)gamma, save_mean, save_invstd, partial, S, C, B, p.chunks, frozen);
+    bn_finalize_bwd_kernel<T><<<(unsigned)((C + 127) / 128), 128, 0, st>>>((T*)dgamma, (T*)dbeta, coef, (const T*)gamma, save_mean, save_invstd, partial, S, C, B, used, frozen);
     LB2_CHECK_LAUNCH("batchnorm backward finalise");
     LB2_DISPATCH_ACT3(act, {
       if (gamma) bn_apply_launch<T, 2, ACT, true>((T*)dx, (const T*)x, (const T*)dy, coef, (const T*)gamma, (const T*)beta, nullptr, nullptr, save_mean, save_invstd, S, C, B, 0.f, act, st);
