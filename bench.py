@@ -546,7 +546,7 @@ def run_gpu_arm(args):
         secondary = {}
         if world == 1:
             for wl, dts in (("conv", ("bf16", "f32")), ("ln", ("bf16", "f32")), ("gn", ("bf16", "f32")), ("bn", ("bf16", "f32")),
-                            ("mlp", ("f32",))):
+                            ("mlp", ("f32",)), ("pool", ("bf16",))):
                 for dt_ in dts:
                     try:
                         secondary[f"{wl}_{dt_}"] = measure_secondary(wl, dt_, steps=max(args.steps, 30), warm=warm, quiet=True)
@@ -671,6 +671,16 @@ def measure_secondary(wl: str, dtype: str, steps: int, warm: int, quiet: bool = 
             dW2, dh, db2 = pb2(pl())
             return pb1(dh)
         numel, name = 0, "MLP Dense(784->256, relu) -> Dense(256->10), batch 128, Float32: forward + pullback of MSE"
+    elif wl == "pool":
+        # the stem's pooling of ResNet-18 at batch 256: MaxPool 3x3, stride 2, SamePad on 112x112x64x256, fwd + pullback
+        x = cm(rn(256, 64, 112, 112).to(tdt))
+        pd = L.PoolDims.make((3, 3), 2, 1)
+        y0, _ = L.rrule_maxpool(x, pd)
+        dy = torch.randn(y0.shape, device="cuda", generator=g).to(tdt)
+        def step():
+            y, pb = L.rrule_maxpool(x, pd)
+            return pb(dy)
+        numel, name = 256 * 64 * 112 * 112, "MaxPool 3x3 / 2 (pad 1) on 112x112x64x256, forward + pullback"
     else:
         raise SystemExit(f"unknown workload {wl}")
     for _ in range(3):
@@ -698,6 +708,13 @@ def measure_secondary(wl: str, dtype: str, steps: int, warm: int, quiet: bool = 
     elif wl == "mlp":
         rec = {"metric": "MLP forward+backward time", "value": ms * 1e3, "unit": "us", "higher_is_better": False,
                "flop": 6.0 * 128 * (784 * 256 + 256 * 10)}
+    elif wl == "pool":
+        byts = 3.5 * numel * es      # forward: read x, write y (a quarter of x); pullback: read x and dy, write dx
+        peak, which = hbm_peak()
+        val = byts / (ms * 1e-3) / 1e9
+        rec = {"metric": "pooling fwd+bwd HBM GB/s", "value": val, "unit": "GB/s",
+               "roofline": {"bound": "hbm", "achieved": val, "peak": peak, "unit": "GB/s", "frac": val / peak, "traffic": None,
+                            "peak_source": f"{which}: hbm_gbs; algorithmic bytes 3.5*numel*sizeof(T) over the whole fwd+bwd step"}}
     else:
         byts = 5.0 * numel * es
         peak, which = hbm_peak()
@@ -897,9 +914,9 @@ def main():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="dense", choices=["dense", "ln", "gn", "bn", "conv", "mlp", "convnet"],
+    ap.add_argument("--workload", default="dense", choices=["dense", "ln", "gn", "bn", "conv", "mlp", "pool", "convnet"],
                     help="dense = the headline configuration (default; its line also carries the others as `secondary`); "
-                         "ln/gn/bn/conv/mlp print one single-GPU row; convnet = the ResNet-18 data-parallel step (any --gpus, "
+                         "ln/gn/bn/conv/mlp/pool print one single-GPU row; convnet = the ResNet-18 data-parallel step (any --gpus, "
                          "under torchrun for N > 1)")
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "f32"], help="storage type of the secondary workloads")
     ap.add_argument("--batch", type=int, default=256, help="per-GPU batch of the convnet workload")
