@@ -270,6 +270,26 @@ LB2_API int32_t lb2_pool_fwd(void* y, const void* x, const lb2_pool_desc* desc, 
 LB2_API int32_t lb2_pool_bwd(void* dx, const void* dy, const void* y, const void* x, const lb2_pool_desc* desc,
                           int32_t kind, int32_t dtype, void* stream);
 
+/* ---- batched matrix product, attention softmax ----------------------------------------------------- */
+/* batched_matmul (lib/LuxLib/src/api/batched_mul.jl:56-70, impl/batched_mul.jl:1-60 after its reshape to 3-D):
+ * C[:, :, i] = op(A[:, :, i]) * op(B[:, :, i]), i < batch, column-major with leading dimensions and batch strides in
+ * elements; a stride of 0 repeats an operand (batch dimension of size 1). accumulate = 1: C += ... */
+LB2_API size_t lb2_batched_matmul_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t dtype, uint32_t flags);
+LB2_API int32_t lb2_batched_matmul(void* C, const void* A, const void* B, int64_t M, int64_t N, int64_t K, int64_t batch,
+                                   int64_t lda, int64_t ldb, int64_t ldc, int64_t stride_a, int64_t stride_b,
+                                   int64_t stride_c, int32_t transA, int32_t transB, int32_t dtype, int32_t accumulate,
+                                   uint32_t flags, void* workspace, size_t workspace_bytes, void* stream);
+/* The softmax step of scaled_dot_product_attention (lib/LuxLib/src/impl/attention.jl:76-131) on logits[S, L, HB]
+ * (key index first): y = softmax over s of (keep ? scale * logits + bias : -inf), keep = mask (bytes, nonzero = keep;
+ * NULL = all) and, with causal = 1, s <= l (make_causal_mask = triu(trues(S, L)), :131-137). bias / mask have the shape
+ * [S, L] (batch stride 0) or [S, L, HB] (batch stride S*L). Backward: dlogits = scale * y .* (dy - sum_s y .* dy) and /
+ * or dbias = y .* (dy - sum_s y .* dy) (either may be NULL). */
+LB2_API int32_t lb2_attention_softmax_fwd(void* y, const void* logits, const void* bias, int64_t bias_batch_stride,
+                                          const uint8_t* mask, int64_t mask_batch_stride, int32_t causal, double scale,
+                                          int64_t S, int64_t L, int64_t HB, int32_t dtype, void* stream);
+LB2_API int32_t lb2_attention_softmax_bwd(void* dlogits, void* dbias, const void* dy, const void* y, double scale,
+                                          int64_t S, int64_t L, int64_t HB, int32_t dtype, void* stream);
+
 /* ---- Scale layer ------------------------------------------------------------------------------- */
 /* y = act.(x .* weight .+ bias) (src/layers/basic.jl:452-461; the {False} method has no bias: bias = NULL) with
  * weight / bias of the layer's dims and x of shape (dims..., batch...): a (D, B) column-major view, D = prod(dims).
@@ -290,6 +310,16 @@ LB2_API int32_t lb2_scale_bwd(void* dx, void* dweight, void* dbias, const void* 
 LB2_API size_t lb2_mse_loss_workspace_bytes(int64_t n);
 LB2_API int32_t lb2_mse_loss(float* loss, void* dyhat, const void* yhat, const void* y, int64_t n, int32_t dtype,
                              void* workspace, size_t workspace_bytes, void* stream);
+
+/* CrossEntropyLoss(; dims = 1, agg = mean, logits, label_smoothing, epsilon) (src/helpers/losses.jl:383-416) on
+ * (K classes, B columns) column-major arrays: *loss (fp32 device scalar) and, unless NULL, its gradient dyhat.
+ * from_logits = 1: -sum(yt .* logsoftmax(yhat; dims = 1)) per column (:408-412); from_logits = 0:
+ * -sum(xlogy.(yt, yhat .+ epsilon)) (:414-416), epsilon = eps(T) in the reference when not given.
+ * yt = (1 - label_smoothing) * y + label_smoothing / K (:172-177). Workspace: one float per column. */
+LB2_API size_t lb2_cross_entropy_workspace_bytes(int64_t K, int64_t B);
+LB2_API int32_t lb2_cross_entropy(float* loss, void* dyhat, const void* yhat, const void* y, int64_t K, int64_t B,
+                                  int32_t from_logits, double label_smoothing, double epsilon, int32_t dtype,
+                                  void* workspace, size_t workspace_bytes, void* stream);
 
 /* ---- optimiser step for a bucket of leaves ------------------------------------------------ */
 /* The leaf loop that Optimisers.update! runs under DistributedOptimizer

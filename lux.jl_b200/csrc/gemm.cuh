@@ -25,7 +25,8 @@ struct GemmEpilogue {
 
 // CUDA-core tiled GEMM: any shape, any leading dimension, exact fp32 accumulation.
 int32_t gemm_simt_launch(void* D, int64_t ldd, GemmOperand A, GemmOperand B, int64_t Mm, int64_t Nn, int64_t Kc,
-                         int32_t dtype, const GemmEpilogue& epi, cudaStream_t st);
+                         int32_t dtype, const GemmEpilogue& epi, cudaStream_t st, int batch = 1, int64_t bs_a = 0, int64_t bs_b = 0,
+                         int64_t bs_d = 0);
 
 // tcgen05 / TMEM / TMA GEMM. `tc_supported` tells whether the pointers and leading dimensions
 // satisfy the TMA rules (16-byte aligned bases, strides multiple of 16 bytes).

@@ -11,9 +11,13 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(T* __restrict__ D, int64
                                                         int64_t sa_m, int64_t sa_k, const T* __restrict__ B,
                                                         int64_t sb_n, int64_t sb_k, int64_t Mm, int64_t Nn, int64_t Kc,
                                                         const T* __restrict__ bias, T* __restrict__ preact,
-                                                        int accumulate) {
+                                                        int accumulate, int64_t bs_a, int64_t bs_b, int64_t bs_d) {
   constexpr bool FAST = sizeof(T) == 2;
   constexpr int TM = 64, TN = 64, TK = 16;
+  // blockIdx.z = batch element (strides in elements; 0 repeats an operand)
+  A += (int64_t)blockIdx.z * bs_a;
+  B += (int64_t)blockIdx.z * bs_b;
+  D += (int64_t)blockIdx.z * bs_d;
   __shared__ float As[TK][TM + 4];
   __shared__ float Bs[TK][TN + 4];
   const int tid = threadIdx.x;
@@ -74,9 +78,11 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(T* __restrict__ D, int64
 }
 
 int32_t gemm_simt_launch(void* D, int64_t ldd, GemmOperand A, GemmOperand B, int64_t Mm, int64_t Nn, int64_t Kc,
-                         int32_t dtype, const GemmEpilogue& epi, cudaStream_t st) {
-  if (Mm == 0 || Nn == 0) return LB2_OK;
-  dim3 grid((unsigned)((Mm + 63) / 64), (unsigned)((Nn + 63) / 64));
+                         int32_t dtype, const GemmEpilogue& epi, cudaStream_t st, int batch, int64_t bs_a, int64_t bs_b,
+                         int64_t bs_d) {
+  if (Mm == 0 || Nn == 0 || batch <= 0) return LB2_OK;
+  LB2_REQUIRE(batch <= 65535, LB2_BAD_SHAPE, "CUDA-core GEMM: more than 65535 batch elements in one launch");
+  dim3 grid((unsigned)((Mm + 63) / 64), (unsigned)((Nn + 63) / 64), (unsigned)batch);
   LB2_REQUIRE(grid.y <= 65535, LB2_BAD_SHAPE, "CUDA-core GEMM: N extent too large (%lld)", (long long)Nn);
   const int64_t sa_m = A.mn_major ? 1 : A.ld, sa_k = A.mn_major ? A.ld : 1;
   const int64_t sb_n = B.mn_major ? 1 : B.ld, sb_k = B.mn_major ? B.ld : 1;
@@ -84,7 +90,7 @@ int32_t gemm_simt_launch(void* D, int64_t ldd, GemmOperand A, GemmOperand B, int
     LB2_DISPATCH_ACT(epi.act, {
       gemm_simt_kernel<T, ACT><<<grid, 256, 0, st>>>((T*)D, ldd, (const T*)A.ptr, sa_m, sa_k, (const T*)B.ptr, sb_n,
                                                      sb_k, Mm, Nn, Kc, (const T*)epi.bias, (T*)epi.preact,
-                                                     epi.accumulate);
+                                                     epi.accumulate, bs_a, bs_b, bs_d);
     });
   });
   LB2_CHECK_LAUNCH("gemm_simt");

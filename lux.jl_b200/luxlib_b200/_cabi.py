@@ -89,6 +89,13 @@ PROTOTYPES = {
     "lb2_pool_bwd": (_i32, [_p, _p, _p, _p, C.POINTER(PoolDesc), _i32, _i32, _p]),
     "lb2_conv_fwd_leaves_x_copy": (_i32, [_p, _i32]),
     "lb2_last_gemm_plan": (_i32, [C.POINTER(C.c_int32), _i32]),
+    "lb2_cross_entropy_workspace_bytes": (_sz, [_i64, _i64]),
+    "lb2_cross_entropy": (_i32, [_fp, _p, _p, _p, _i64, _i64, _i32, C.c_double, C.c_double, _i32, _p, _sz, _p]),
+    "lb2_batched_matmul_workspace_bytes": (_sz, [_i64, _i64, _i64, _i32, C.c_uint32]),
+    "lb2_batched_matmul": (_i32, [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _i32,
+                                  C.c_uint32, _p, _sz, _p]),
+    "lb2_attention_softmax_fwd": (_i32, [_p, _p, _p, _i64, _p, _i64, _i32, C.c_double, _i64, _i64, _i64, _i32, _p]),
+    "lb2_attention_softmax_bwd": (_i32, [_p, _p, _p, _p, C.c_double, _i64, _i64, _i64, _i32, _p]),
     "lb2_scale_fwd": (_i32, [_p, _p, _p, _p, _i64, _i64, _i32, _i32, _p]),
     "lb2_scale_bwd_workspace_bytes": (_sz, [_i64, _i64]),
     "lb2_scale_bwd": (_i32, [_p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i32, _i32, _p, _sz, _p]),

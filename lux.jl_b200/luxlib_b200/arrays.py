@@ -50,6 +50,13 @@ def as_colmajor(t: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def jl_reshape(t: torch.Tensor, shape: Sequence[int]) -> torch.Tensor:
+    """Julia's reshape: the same column-major memory under a new shape (torch's own reshape walks indices in row-major
+    order and would permute the elements of a column-major tensor)."""
+    t = as_colmajor(t)
+    return torch.as_strided(t, tuple(shape), colmajor_strides(tuple(shape)), t.storage_offset())
+
+
 def from_numpy(a: np.ndarray, device="cuda", dtype: torch.dtype | None = None) -> torch.Tensor:
     """Host numpy array (any layout, Julia index order) -> column-major device array."""
     a = np.asarray(a)

@@ -11,6 +11,7 @@ Arrays are column-major device arrays (see arrays.py); activations are named by 
 from __future__ import annotations
 
 import ctypes as C
+import math
 import warnings
 from dataclasses import dataclass
 from typing import Optional, Sequence, Tuple
@@ -19,7 +20,7 @@ import torch
 
 from . import _cabi
 from ._cabi import ArgumentError, DimensionMismatch
-from .arrays import as_colmajor, current_stream, dtype_code, jl_empty, ptr, workspace
+from .arrays import as_colmajor, current_stream, dtype_code, jl_empty, jl_reshape, ptr, workspace
 
 # --------------------------------------------------------------------------------------------
 # activations
@@ -521,6 +522,202 @@ def conv_transpose_bias_activation(act: str, weight, x, b, cdims: ConvDims, outp
 
 
 # --------------------------------------------------------------------------------------------
+# batched matrix product, attention
+# --------------------------------------------------------------------------------------------
+def _bmm(lib, Cp, Ap, Bp, M, N, K, batch, lda, ldb, ldc, sa, sb, sc, ta, tb, dt, device, accumulate=0, flags=0):
+    """One lb2_batched_matmul call on raw pointers (integers)."""
+    _, wsp, wsn = _ws(lib.lb2_batched_matmul_workspace_bytes(M, N, K, dt, flags), device)
+    _cabi.check(lib.lb2_batched_matmul(Cp, Ap, Bp, M, N, K, batch, lda, ldb, ldc, sa, sb, sc, int(ta), int(tb), dt, accumulate, flags,
+                                       wsp, wsn, current_stream(device)))
+
+
+def batched_matmul(x, y, *, flags: int = 0):
+    """LuxLib.batched_matmul(x, y) (lib/LuxLib/src/api/batched_mul.jl:56-70) for the default dimension roles:
+    x (M, K, Bx), y (K, N, By) -> (M, N, max(Bx, By)); a matrix counts as batch size 1 and a batch dimension of size 1
+    is repeated. Batch dimensions beyond the third are flattened like the reference does."""
+    lib = _cabi.load()
+    x, y = _promote(x, y)
+    if x.dim() == 2:
+        x = jl_reshape(x, (x.shape[0], x.shape[1], 1))
+    if y.dim() == 2:
+        y = jl_reshape(y, (y.shape[0], y.shape[1], 1))
+    if x.dim() != y.dim() or x.dim() < 3:
+        raise DimensionMismatch("batched_matmul needs two arrays of the same rank (>= 3) or a matrix and a 3-D array")
+    X, Y = as_colmajor(x), as_colmajor(y)
+    bx, by = tuple(X.shape[2:]), tuple(Y.shape[2:])
+    if any(p != q and p != 1 and q != 1 for p, q in zip(bx, by)):
+        raise DimensionMismatch(f"batch dimensions {bx} and {by} do not match")
+    if len(bx) > 1 and bx != by:      # mixed repeats over several batch dimensions: materialise them like Utils.maybe_repeat
+        full = tuple(max(p, q) for p, q in zip(bx, by))
+        X = as_colmajor(X.expand(*X.shape[:2], *full))
+        Y = as_colmajor(Y.expand(*Y.shape[:2], *full))
+        bx = by = full
+    M, K = X.shape[0], X.shape[1]
+    if Y.shape[0] != K:
+        raise DimensionMismatch(f"size(x, 2) = {K} does not match size(y, 1) = {Y.shape[0]}")
+    N = Y.shape[1]
+    nbx, nby = math.prod(bx), math.prod(by)
+    nb = max(nbx, nby)
+    out = jl_empty((M, N) + tuple(max(p, q) for p, q in zip(bx, by)), X.dtype, X.device)
+    _bmm(lib, ptr(out), ptr(X), ptr(Y), M, N, K, nb, max(M, 1), max(K, 1), max(M, 1), 0 if nbx == 1 else M * K, 0 if nby == 1 else K * N,
+         M * N, 0, 0, dtype_code(X.dtype), X.device, flags=flags)
+    return out
+
+
+def rrule_batched_matmul(x, y, *, flags: int = 0):
+    """batched_matmul with its pullback Δ -> (∂x, ∂y): ∂x = Δ ⊠ yᵀ, ∂y = xᵀ ⊠ Δ (summed over a repeated batch)."""
+    lib = _cabi.load()
+    z = batched_matmul(x, y, flags=flags)
+    x, y = _promote(x, y)
+    X3 = jl_reshape(x, (x.shape[0], x.shape[1], math.prod(x.shape[2:])))
+    Y3 = jl_reshape(y, (y.shape[0], y.shape[1], math.prod(y.shape[2:])))
+    M, K, nbx = X3.shape
+    N, nby = Y3.shape[1], Y3.shape[2]
+    nb = max(nbx, nby)
+    if x.dim() > 3 and tuple(x.shape[2:]) != tuple(y.shape[2:]):
+        raise NotImplementedError("pullback with mixed repeats over several batch dimensions")
+    dt, es = dtype_code(X3.dtype), X3.element_size()
+
+    def pullback(delta):
+        D = as_colmajor(delta.to(X3.dtype))
+        dx = jl_empty(tuple(x.shape), X3.dtype, X3.device)
+        dy = jl_empty(tuple(y.shape), X3.dtype, X3.device)
+        # a repeated operand's gradient is the sum over the batch: accumulate element by element in a fixed order
+        if nbx == nb:
+            _bmm(lib, ptr(dx), ptr(D), ptr(Y3), M, K, N, nb, M, K, M, M * N, 0 if nby == 1 else K * N, M * K, 0, 1, dt, X3.device, flags=flags)
+        else:
+            for i in range(nb):
+                _bmm(lib, ptr(dx), D.data_ptr() + i * M * N * es, Y3.data_ptr() + (0 if nby == 1 else i * K * N * es), M, K, N, 1, M, K, M,
+                     0, 0, M * K, 0, 1, dt, X3.device, accumulate=1 if i else 0, flags=flags)
+        if nby == nb:
+            _bmm(lib, ptr(dy), ptr(X3), ptr(D), K, N, M, nb, M, M, K, 0 if nbx == 1 else M * K, M * N, K * N, 1, 0, dt, X3.device, flags=flags)
+        else:
+            for i in range(nb):
+                _bmm(lib, ptr(dy), X3.data_ptr() + (0 if nbx == 1 else i * M * K * es), D.data_ptr() + i * M * N * es, K, N, M, 1, M, M, K,
+                     0, 0, K * N, 1, 0, dt, X3.device, accumulate=1 if i else 0, flags=flags)
+        return dx, dy
+
+    return z, pullback
+
+
+def rrule_scaled_dot_product_attention(q, k, v, *, scale=None, mask=None, is_causal=None, bias=None, flags: int = 0):
+    """LuxLib.scaled_dot_product_attention (lib/LuxLib/src/api/attention.jl, impl/attention.jl:5-118) for the default
+    dimension roles head_dim = 1, token_dim = 3: q (D, H, L, B...), k (D, Hkv, S, B...), v (E, Hkv, S, B...) ->
+    (x (E, H, L, B...), weights (S, L, H, B...)), and the pullback (Δx) -> (∂q, ∂k, ∂v, ∂bias). Logits =
+    batched k'q / scale (default scale sqrt(D)), + bias, masked (mask true = keep, or is_causal), softmax over the key
+    index. H must be a multiple of Hkv (grouped keys / values are shared by consecutive query heads)."""
+    lib = _cabi.load()
+    if q.dim() < 4 or k.dim() != q.dim() or v.dim() != q.dim():
+        raise AssertionError("N must be at least 4")
+    if mask is not None and is_causal is not None:
+        raise AssertionError("`mask` and `is_causal` cannot both be specified")
+    q, k, v = _promote(q, k, v)
+    Q, Kx, V = as_colmajor(q), as_colmajor(k), as_colmajor(v)
+    D, H, Lq = Q.shape[:3]
+    Hkv, S = Kx.shape[1], Kx.shape[2]
+    E = V.shape[0]
+    if Kx.shape[0] != D:
+        raise AssertionError("`q` and `k` must have the same head dimension")
+    if tuple(Q.shape[3:]) != tuple(Kx.shape[3:]) or tuple(Q.shape[3:]) != tuple(V.shape[3:]):
+        raise DimensionMismatch("All dimensions (except first 3) of q, k, v must be the same")
+    if V.shape[2] != S or V.shape[1] != Hkv:
+        raise AssertionError("`v` and `k` must have the same number of tokens and heads")
+    if H % Hkv != 0:
+        raise AssertionError("num_heads must be divisible by num_kv_groups")
+    gs = H // Hkv
+    batch_shape = tuple(Q.shape[3:])
+    Bn = math.prod(batch_shape)
+    sc = 1.0 / (float(scale) if scale is not None else float(D) ** 0.5)
+    dt, es, device = dtype_code(Q.dtype), Q.element_size(), Q.device
+    logits = jl_empty((S, Lq, H) + batch_shape, Q.dtype, device)
+
+    def per_group(fn):
+        for b in range(Bn):
+            for g in range(Hkv):
+                fn(b, g)
+
+    # logits[:, :, h, b] = k[:, g, :, b]' * q[:, h, :, b] for the gs heads h of group g: one batched call, k repeated
+    def fwd_logits(b, g):
+        _bmm(lib, logits.data_ptr() + ((g * gs + H * b) * S * Lq) * es, Kx.data_ptr() + (g * D + b * D * Hkv * S) * es,
+             Q.data_ptr() + (g * gs * D + b * D * H * Lq) * es, S, Lq, D, gs, D * Hkv, D * H, S, 0, D, S * Lq, 1, 0, dt, device, flags=flags)
+    per_group(fwd_logits)
+
+    bias_c = mask_c = None
+    bias_bs = mask_bs = 0
+    if bias is not None:
+        bias_c = as_colmajor(bias.to(Q.dtype))
+        if tuple(bias_c.shape) == (S, Lq):
+            bias_bs = 0
+        elif tuple(bias_c.shape) == (S, Lq, H) + batch_shape:
+            bias_bs = S * Lq
+        else:
+            raise DimensionMismatch("bias must have the shape (S, L) or (S, L, H, B...)")
+    if mask is not None:
+        mask_c = as_colmajor(mask.to(torch.uint8))
+        if tuple(mask_c.shape) == (S, Lq):
+            mask_bs = 0
+        elif tuple(mask_c.shape) == (S, Lq, H) + batch_shape:
+            mask_bs = S * Lq
+        else:
+            raise DimensionMismatch("mask must have the shape (S, L) or (S, L, H, B...)")
+    w = jl_empty(tuple(logits.shape), Q.dtype, device)
+    _cabi.check(lib.lb2_attention_softmax_fwd(ptr(w), ptr(logits), ptr(bias_c), bias_bs, ptr(mask_c), mask_bs, 1 if is_causal else 0, sc,
+                                              S, Lq, H * Bn, dt, current_stream(device)))
+    out = jl_empty((E, H, Lq) + batch_shape, Q.dtype, device)
+
+    # x[:, h, :, b] = v[:, g, :, b] * w[:, :, h, b]
+    def fwd_out(b, g):
+        _bmm(lib, out.data_ptr() + (g * gs * E + b * E * H * Lq) * es, V.data_ptr() + (g * E + b * E * Hkv * S) * es,
+             w.data_ptr() + ((g * gs + H * b) * S * Lq) * es, E, Lq, S, gs, E * Hkv, S, E * H, 0, S * Lq, E, 0, 0, dt, device, flags=flags)
+    per_group(fwd_out)
+
+    def pullback(dx):
+        G = as_colmajor(dx.to(Q.dtype))
+        dw = jl_empty(tuple(w.shape), Q.dtype, device)
+        dq, dk, dv = (jl_empty(tuple(t.shape), Q.dtype, device) for t in (Q, Kx, V))
+
+        # dw[:, :, h, b] = v[:, g, :, b]' * dx[:, h, :, b]
+        def bwd_dw(b, g):
+            _bmm(lib, dw.data_ptr() + ((g * gs + H * b) * S * Lq) * es, V.data_ptr() + (g * E + b * E * Hkv * S) * es,
+                 G.data_ptr() + (g * gs * E + b * E * H * Lq) * es, S, Lq, E, gs, E * Hkv, E * H, S, 0, E, S * Lq, 1, 0, dt, device, flags=flags)
+        per_group(bwd_dw)
+        dl = jl_empty(tuple(w.shape), Q.dtype, device)
+        db = jl_empty(tuple(w.shape), Q.dtype, device) if bias_c is not None else None
+        _cabi.check(lib.lb2_attention_softmax_bwd(ptr(dl), ptr(db), ptr(dw), ptr(w), sc, S, Lq, H * Bn, dt, current_stream(device)))
+
+        # per head (the heads of a group add into the same dk / dv, so they run one after the other, in order):
+        # dv[:, g, :, b] += dx[:, h, :, b] * w[:, :, h, b]';  dk[:, g, :, b] += q[:, h, :, b] * dl[:, :, h, b]'
+        # dq[:, h, :, b] = k[:, g, :, b] * dl[:, :, h, b]
+        def bwd_rest(b, g):
+            _bmm(lib, dq.data_ptr() + (g * gs * D + b * D * H * Lq) * es, Kx.data_ptr() + (g * D + b * D * Hkv * S) * es,
+                 dl.data_ptr() + ((g * gs + H * b) * S * Lq) * es, D, Lq, S, gs, D * Hkv, S, D * H, 0, S * Lq, D, 0, 0, dt, device, flags=flags)
+            for j in range(gs):
+                h = g * gs + j
+                _bmm(lib, dv.data_ptr() + (g * E + b * E * Hkv * S) * es, G.data_ptr() + (h * E + b * E * H * Lq) * es,
+                     w.data_ptr() + ((h + H * b) * S * Lq) * es, E, S, Lq, 1, E * H, S, E * Hkv, 0, 0, E * S, 0, 1, dt, device,
+                     accumulate=1 if j else 0, flags=flags)
+                _bmm(lib, dk.data_ptr() + (g * D + b * D * Hkv * S) * es, Q.data_ptr() + (h * D + b * D * H * Lq) * es,
+                     dl.data_ptr() + ((h + H * b) * S * Lq) * es, D, S, Lq, 1, D * H, S, D * Hkv, 0, 0, D * S, 0, 1, dt, device,
+                     accumulate=1 if j else 0, flags=flags)
+        per_group(bwd_rest)
+        if db is not None and bias_bs == 0:
+            # a bias shared by all heads and samples: its gradient is the sum over them — the bias-gradient reduction on
+            # the (1, S*L, H*B) view
+            full, db = db, jl_empty((S, Lq), Q.dtype, device)
+            _, wsp, wsn = _ws(lib.lb2_bias_act_bwd_workspace_bytes(1, S * Lq, H * Bn), device)
+            _cabi.check(lib.lb2_bias_act_bwd(None, ptr(db), ptr(full), None, None, 1, S * Lq, H * Bn, dt, act_code("identity"), wsp, wsn,
+                                             current_stream(device)))
+        return dq, dk, dv, db
+
+    return (out, w), pullback
+
+
+def scaled_dot_product_attention(q, k, v, **kw):
+    """(x, attention weights) of LuxLib.scaled_dot_product_attention for head_dim = 1, token_dim = 3."""
+    return rrule_scaled_dot_product_attention(q, k, v, **kw)[0]
+
+
+# --------------------------------------------------------------------------------------------
 # normalisation
 # --------------------------------------------------------------------------------------------
 def default_epsilon(dtype: torch.dtype) -> float:
@@ -890,6 +1087,37 @@ def rrule_mse_loss(yhat, y):
         return d if delta is None else d * delta
 
     return loss, pullback
+
+
+def rrule_cross_entropy_loss(yhat, y, *, logits: bool = False, label_smoothing=None, epsilon=None):
+    """CrossEntropyLoss(; dims = 1, agg = mean, logits, label_smoothing, epsilon)(ŷ, y) (src/helpers/losses.jl:383-416)
+    with its pullback: returns (loss, Δ -> ∂ŷ). The class dimension is the first one; all others are columns.
+    `epsilon` defaults to eps(T) of the arrays' element type (src/helpers/losses.jl:104-105)."""
+    lib = _cabi.load()
+    if tuple(yhat.shape) != tuple(y.shape):
+        raise DimensionMismatch("ŷ and y must have the same shape")
+    if label_smoothing is not None and not (0 <= label_smoothing <= 1):
+        raise AssertionError("0 <= label_smoothing <= 1")
+    yhat, y = _promote(yhat, y)
+    Yh, Y = as_colmajor(yhat), as_colmajor(y)
+    K = Yh.shape[0] if Yh.dim() else 1
+    B = Yh.numel() // K if K else 0
+    eps = float(epsilon) if epsilon is not None else float(torch.finfo(Yh.dtype).eps)
+    loss = torch.empty(1, dtype=torch.float32, device=Yh.device)
+    d = jl_empty(Yh.shape, Yh.dtype, Yh.device)
+    _, wsp, wsn = _ws(lib.lb2_cross_entropy_workspace_bytes(K, B), Yh.device)
+    _cabi.check(lib.lb2_cross_entropy(ptr(loss), ptr(d), ptr(Yh), ptr(Y), K, B, 1 if logits else 0, float(label_smoothing or 0.0), eps,
+                                      dtype_code(Yh.dtype), wsp, wsn, current_stream(Yh.device)))
+
+    def pullback(delta=None):
+        return d if delta is None else d * delta
+
+    return loss, pullback
+
+
+def cross_entropy_loss(yhat, y, **kw):
+    """CrossEntropyLoss(...)(ŷ, y) as a Float32 device scalar."""
+    return rrule_cross_entropy_loss(yhat, y, **kw)[0]
 
 
 def mse_loss(yhat, y):

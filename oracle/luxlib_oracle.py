@@ -884,6 +884,98 @@ def rel_l2(a: np.ndarray, b: np.ndarray) -> float:
 # --------------------------------------------------------------------------- #
 # loss
 # --------------------------------------------------------------------------- #
+def batched_matmul_rrule(x, y):
+    """batched_matmul for the default dimension roles (lib/LuxLib/src/api/batched_mul.jl:56-70): x (M, K, Bx...),
+    y (K, N, By...) -> (M, N, B...), batch dimensions of size 1 repeated; matrices count as batch size 1.
+    Pullback Δ -> (∂x, ∂y), summed over a repeated batch dimension."""
+    x3 = x.reshape(x.shape + (1,)) if x.ndim == 2 else x
+    y3 = y.reshape(y.shape + (1,)) if y.ndim == 2 else y
+    z = np.einsum("mk...,kn...->mn...", x3, y3)
+
+    def pullback(delta):
+        dx = np.einsum("mn...,kn...->mk...", delta, np.broadcast_to(y3, y3.shape[:2] + delta.shape[2:]))
+        dy = np.einsum("mk...,mn...->kn...", np.broadcast_to(x3, x3.shape[:2] + delta.shape[2:]), delta)
+        for ax in range(2, delta.ndim):
+            if x3.shape[ax] == 1 and delta.shape[ax] != 1:
+                dx = dx.sum(axis=ax, keepdims=True)
+            if y3.shape[ax] == 1 and delta.shape[ax] != 1:
+                dy = dy.sum(axis=ax, keepdims=True)
+        return dx.reshape(x.shape), dy.reshape(y.shape)
+
+    return z, pullback
+
+
+def attention_rrule(q, k, v, scale=None, mask=None, is_causal=None, bias=None):
+    """scaled_dot_product_attention for head_dim = 1, token_dim = 3 (lib/LuxLib/src/impl/attention.jl:5-137):
+    q (D, H, L, B), k (D, Hkv, S, B), v (E, Hkv, S, B); grouped keys / values repeated along the heads (repeat inner,
+    :1-3, :47-51); logits[s, l, h, b] = sum_d k[d, h, s, b] * (q[d, h, l, b] / scale) (+ bias, masked with typemin:
+    :120-128; causal mask = triu(trues(S, L)), :131-137); weights = softmax over s; x[e, h, l, b] = sum_s v[e, h, s, b] *
+    weights[s, l, h, b]. Returns ((x, weights), Δx -> (∂q, ∂k, ∂v, ∂bias))."""
+    D, H, L = q.shape[:3]
+    Hkv, S = k.shape[1], k.shape[2]
+    gs = H // Hkv
+    kr, vr = np.repeat(k, gs, axis=1), np.repeat(v, gs, axis=1)
+    sc = 1.0 / (np.sqrt(D) if scale is None else scale)
+    logits = np.einsum("dhsb,dhlb->slhb", kr, q * sc)
+    if bias is not None:
+        logits = logits + (bias if bias.ndim == 4 else bias[:, :, None, None])
+    keep = None
+    if is_causal:
+        keep = np.triu(np.ones((S, L), dtype=bool))[:, :, None, None]
+    elif mask is not None:
+        keep = mask.astype(bool) if mask.ndim == 4 else mask.astype(bool)[:, :, None, None]
+    if keep is not None:
+        logits = np.where(keep, logits, -np.inf)
+    m = logits.max(axis=0, keepdims=True)
+    e = np.exp(logits - m)
+    w = e / e.sum(axis=0, keepdims=True)
+    x = np.einsum("ehsb,slhb->ehlb", vr, w)
+
+    def pullback(dx):
+        dw = np.einsum("ehsb,ehlb->slhb", vr, dx)
+        dvr = np.einsum("ehlb,slhb->ehsb", dx, w)
+        dpre = w * (dw - (w * dw).sum(axis=0, keepdims=True))
+        dq = np.einsum("dhsb,slhb->dhlb", kr, dpre) * sc
+        dkr = np.einsum("dhlb,slhb->dhsb", q * sc, dpre)
+        dk = dkr.reshape(D, Hkv, gs, S, -1).sum(axis=2)
+        dv = dvr.reshape(v.shape[0], Hkv, gs, S, -1).sum(axis=2)
+        db = None
+        if bias is not None:
+            db = dpre if bias.ndim == 4 else dpre.sum(axis=(2, 3))
+        return dq, dk, dv, db
+
+    return (x, w), pullback
+
+
+def cross_entropy_rrule(yhat, y, logits=False, label_smoothing=None, epsilon=None):
+    """CrossEntropyLoss(; dims = 1, agg = mean) — src/helpers/losses.jl:383-416. logits = true:
+    mean(-sum(ỹ .* logsoftmax(ŷ; dims = 1); dims = 1)) (:408-412); logits = false: mean(-sum(xlogy.(ỹ, ŷ .+ ϵ); dims = 1))
+    (:414-416) with ϵ = eps(T) unless given (:104-105); ỹ = (1 - α) y + α / size(y, 1) (label_smoothing, :172-177).
+    Returns (loss, Δ -> ∂ŷ)."""
+    K = yhat.shape[0]
+    B = yhat.size // K
+    yt = y if label_smoothing is None else (1 - label_smoothing) * y + label_smoothing / K
+    yt = yt.astype(yhat.dtype)
+    if logits:
+        m = yhat.max(axis=0, keepdims=True)
+        z = yhat - m
+        lse = np.log(np.exp(z).sum(axis=0, keepdims=True))
+        loss = -(yt * (z - lse)).sum() / B
+        grad = (np.exp(z - lse) * yt.sum(axis=0, keepdims=True) - yt) / B
+    else:
+        eps = np.finfo(yhat.dtype).eps if epsilon is None else epsilon
+        p = yhat + yhat.dtype.type(eps)
+        with np.errstate(divide="ignore", invalid="ignore"):
+            terms = np.where(yt == 0, 0.0, yt * np.log(p))
+        loss = -terms.sum() / B
+        grad = -yt / p / B
+
+    def pullback(delta=1.0):
+        return (grad * delta).astype(yhat.dtype)
+
+    return yhat.dtype.type(loss), pullback
+
+
 def mse_loss_rrule(yhat, y):
     """MSELoss() — src/helpers/losses.jl:659: GenericLossFunction(l2_distance_loss; agg = mean) with
     l2_distance_loss(x, y) = abs2(x - y) and derivative 2 (x - y) (src/helpers/losses.jl:121-125).

@@ -874,3 +874,91 @@ def test_scale_layer_fwd_bwd(dt, act, shape, use_bias):
         check(db, db_ref, dt, "db")
     else:
         assert db is None
+
+
+# ------------------------------------------------------------------------------------------
+# cross-entropy loss
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("logits", [True, False])
+@pytest.mark.parametrize("ls", [None, 0.15])
+@pytest.mark.parametrize("shape", [(3, 5), (10, 128), (1000, 256), (37, 4, 6)])
+def test_cross_entropy_loss_and_gradient(dt, logits, ls, shape):
+    rng = np.random.default_rng(47)
+    K = shape[0]
+    cols = int(np.prod(shape[1:]))
+    y = np.eye(K, dtype=np.float32)[:, rng.integers(0, K, cols)].reshape(shape)
+    if logits:
+        yhat = prep(rng.standard_normal(shape) * 2.0, dt)
+    else:
+        e = np.exp(rng.standard_normal(shape))
+        yhat = prep(e / e.sum(axis=0, keepdims=True), dt)
+    y = prep(y, dt)
+    eps = float(np.finfo(np.float32).eps) if dt == "f32" else 2.0 ** -7      # eps(Float32) / eps(BFloat16)
+    loss_ref, pb_ref = O.cross_entropy_rrule(yhat.astype(np.float64), y.astype(np.float64), logits=logits, label_smoothing=ls, epsilon=eps)
+    loss, pb = L.rrule_cross_entropy_loss(dev(yhat, dt), dev(y, dt), logits=logits, label_smoothing=ls)
+    got = float(loss.item())
+    tol = 1e-5 if dt == "f32" else 1e-2
+    err = abs(got - float(loss_ref)) / max(abs(float(loss_ref)), 1e-30)
+    parity_report.record("loss", dt, err, tol)
+    assert err <= tol, (got, float(loss_ref))
+    check(pb(), pb_ref(), dt, "dyhat")
+
+
+# ------------------------------------------------------------------------------------------
+# batched matmul, scaled dot-product attention
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("shapes", [((4, 5, 6), (5, 3, 6)), ((70, 33, 5), (33, 130, 1)), ((64, 64), (64, 32, 9)), ((16, 8, 3, 2), (8, 12, 3, 2)),
+                                    ((320, 300, 2), (300, 280, 2))])
+def test_batched_matmul_fwd_bwd(dt, shapes):
+    xs, ys = shapes
+    rng = np.random.default_rng(49)
+    x, y = prep(rng.standard_normal(xs), dt), prep(rng.standard_normal(ys), dt)
+    z_ref, pb_ref = O.batched_matmul_rrule(x.astype(np.float64), y.astype(np.float64))
+    z, pb = L.rrule_batched_matmul(dev(x, dt), dev(y, dt))
+    check(z, z_ref, dt, "z")
+    dz = prep(rng.standard_normal(z_ref.shape), dt)
+    dx_ref, dy_ref = pb_ref(dz.astype(np.float64))
+    dx, dy = pb(dev(dz, dt))
+    check(dx, dx_ref, dt, "dx")
+    check(dy, dy_ref, dt, "dy")
+
+
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("variant", ["plain", "causal", "mask", "bias", "mask+bias4"])
+@pytest.mark.parametrize("dims", [(8, 4, 2, 5, 7, 6, 3), (64, 8, 8, 128, 128, 64, 2), (32, 6, 2, 33, 65, 16, 1)])
+def test_scaled_dot_product_attention_fwd_bwd(dt, variant, dims):
+    D, H, Hkv, Lq, S, E, B = dims
+    rng = np.random.default_rng(50)
+    q = prep(rng.standard_normal((D, H, Lq, B)), dt)
+    k = prep(rng.standard_normal((D, Hkv, S, B)), dt)
+    v = prep(rng.standard_normal((E, Hkv, S, B)), dt)
+    mask = bias = None
+    causal = None
+    if variant == "causal":
+        causal = True
+    if "mask" in variant:
+        mask = rng.random((S, Lq)) > 0.3
+        mask[0, :] = True                      # no column fully masked
+    if variant == "bias":
+        bias = prep(rng.standard_normal((S, Lq)) * 0.5, dt)
+    if variant == "mask+bias4":
+        bias = prep(rng.standard_normal((S, Lq, H, B)) * 0.5, dt)
+    f64 = lambda a: None if a is None else a.astype(np.float64)
+    (x_ref, w_ref), pb_ref = O.attention_rrule(f64(q), f64(k), f64(v), mask=mask, is_causal=causal, bias=f64(bias))
+    tmask = None if mask is None else L.from_numpy(mask.astype(np.uint8), "cuda", torch.uint8)
+    (x, w), pb = L.rrule_scaled_dot_product_attention(dev(q, dt), dev(k, dt), dev(v, dt), mask=tmask, is_causal=causal,
+                                                       bias=None if bias is None else dev(bias, dt))
+    check(w, w_ref, dt, "weights")
+    check(x, x_ref, dt, "x")
+    dx = prep(rng.standard_normal(x_ref.shape), dt)
+    dq_ref, dk_ref, dv_ref, db_ref = pb_ref(f64(dx))
+    dq, dk, dv, db = pb(dev(dx, dt))
+    # bf16: the weights and the logits gradient are stored in bf16 between the launches, as the reference's arrays would be
+    check(dq, dq_ref, dt, "dq")
+    check(dk, dk_ref, dt, "dk")
+    check(dv, dv_ref, dt, "dv")
+    if bias is not None:
+        check(db, db_ref, dt, "dbias")
+    assert L._cabi.load().lb2_poll_device_status(None) == 0

@@ -391,3 +391,69 @@ def test_scale_against_torch_autograd():
         np.testing.assert_allclose(db, tb.grad.numpy(), rtol=1e-10, atol=1e-12)
     z, pb = O.scale_rrule("identity", w, x, None)
     assert pb(delta)[2] is None and np.allclose(z, x * w[..., None])
+
+
+def test_cross_entropy_known_answers_of_the_reference_docstring():
+    # src/helpers/losses.jl:355-381: y one-hot 3x5, y_model = softmax(reshape(-7:7, 3, 5)); CrossEntropyLoss()(y_model, y)
+    # ≈ 1.6076053, with label_smoothing = 0.15 ≈ 1.5776052, agg = sum gives 5x the mean
+    z = np.arange(-7, 8, dtype=np.float32).reshape(5, 3).T          # Julia's column-major reshape
+    y = np.array([[1, 0, 0, 0, 1], [0, 1, 0, 1, 0], [0, 0, 1, 0, 0]], dtype=np.float32)
+    e = np.exp(z - z.max(axis=0, keepdims=True))
+    y_model = (e / e.sum(axis=0, keepdims=True)).astype(np.float32)
+    assert abs(float(y_model[0, 0]) - 0.0900306) < 1e-6 and abs(float(y_model[2, 0]) - 0.665241) < 1e-6
+    assert abs(float(O.cross_entropy_rrule(y_model, y)[0]) - 1.6076053) < 2e-6
+    assert abs(float(O.cross_entropy_rrule(y_model, y, label_smoothing=0.15)[0]) - 1.5776052) < 2e-6
+    # the logits form on the logits themselves is the same loss (up to the epsilon of the probability form)
+    assert abs(float(O.cross_entropy_rrule(z, y, logits=True)[0]) - 1.6076053) < 2e-6
+    # gradients against torch autograd
+    import torch
+    rng = np.random.default_rng(46)
+    zz = rng.standard_normal((7, 9))
+    yy = np.eye(7)[:, rng.integers(0, 7, 9)]
+    for ls in (None, 0.2):
+        loss, pb = O.cross_entropy_rrule(zz, yy, logits=True, label_smoothing=ls)
+        tz = torch.tensor(zz, requires_grad=True)
+        yt = torch.tensor(yy if ls is None else (1 - ls) * yy + ls / 7)
+        tl = -(yt * torch.log_softmax(tz, dim=0)).sum(dim=0).mean()
+        tl.backward()
+        assert abs(float(loss) - float(tl)) < 1e-12
+        np.testing.assert_allclose(pb(), tz.grad.numpy(), rtol=1e-10, atol=1e-12)
+    pp = np.abs(rng.standard_normal((7, 9))) + 0.1
+    loss, pb = O.cross_entropy_rrule(pp, yy, logits=False, label_smoothing=0.1)
+    tp = torch.tensor(pp, requires_grad=True)
+    yt = torch.tensor(0.9 * yy + 0.1 / 7)
+    tl = -(yt * torch.log(tp + np.finfo(np.float64).eps)).sum(dim=0).mean()
+    tl.backward()
+    assert abs(float(loss) - float(tl)) < 1e-12
+    np.testing.assert_allclose(pb(), tp.grad.numpy(), rtol=1e-10, atol=1e-12)
+
+
+def test_attention_and_batched_matmul_against_torch():
+    import torch
+    rng = np.random.default_rng(48)
+    D, H, Hkv, L, S, E, B = 8, 4, 2, 5, 7, 6, 3
+    q, k, v = rng.standard_normal((D, H, L, B)), rng.standard_normal((D, Hkv, S, B)), rng.standard_normal((E, Hkv, S, B))
+    dx = rng.standard_normal((E, H, L, B))
+    for causal in (False, True):
+        (x, w), pb = O.attention_rrule(q, k, v, is_causal=causal or None)
+        tq, tk, tv = (torch.tensor(np.ascontiguousarray(a.transpose(3, 1, 2, 0)), requires_grad=True) for a in (q, k, v))   # B, H, T, D
+        kr, vr = tk.repeat_interleave(H // Hkv, dim=1), tv.repeat_interleave(H // Hkv, dim=1)
+        am = torch.tensor(np.triu(np.ones((S, L), dtype=bool)).T) if causal else None                                      # (L, S): key s <= query l
+        tx = torch.nn.functional.scaled_dot_product_attention(tq, kr, vr, attn_mask=am)
+        tx.backward(torch.tensor(np.ascontiguousarray(dx.transpose(3, 1, 2, 0))))
+        np.testing.assert_allclose(x, tx.detach().numpy().transpose(3, 1, 2, 0), rtol=1e-10, atol=1e-12)
+        dq, dk, dv, _ = pb(dx)
+        np.testing.assert_allclose(dq, tq.grad.numpy().transpose(3, 1, 2, 0), rtol=1e-9, atol=1e-12)
+        np.testing.assert_allclose(dk, tk.grad.numpy().transpose(3, 1, 2, 0), rtol=1e-9, atol=1e-12)
+        np.testing.assert_allclose(dv, tv.grad.numpy().transpose(3, 1, 2, 0), rtol=1e-9, atol=1e-12)
+        assert np.allclose(w.sum(axis=0), 1.0)
+    x3, y3 = rng.standard_normal((4, 5, 6)), rng.standard_normal((5, 3, 1))
+    z, pb = O.batched_matmul_rrule(x3, y3)
+    tx, ty = torch.tensor(x3.transpose(2, 0, 1).copy(), requires_grad=True), torch.tensor(y3.transpose(2, 0, 1).copy(), requires_grad=True)
+    tz = torch.matmul(tx, ty)
+    dz = rng.standard_normal(z.shape)
+    tz.backward(torch.tensor(dz.transpose(2, 0, 1).copy()))
+    np.testing.assert_allclose(z, tz.detach().numpy().transpose(1, 2, 0), rtol=1e-12)
+    gx, gy = pb(dz)
+    np.testing.assert_allclose(gx, tx.grad.numpy().transpose(1, 2, 0), rtol=1e-10)
+    np.testing.assert_allclose(gy, ty.grad.numpy().transpose(1, 2, 0), rtol=1e-10)
