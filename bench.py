@@ -676,7 +676,7 @@ def measure_secondary(wl: str, dtype: str, steps: int, warm: int, quiet: bool = 
         x = cm(rn(256, 64, 112, 112).to(tdt))
         pd = L.PoolDims.make((3, 3), 2, 1)
         y0, _ = L.rrule_maxpool(x, pd)
-        dy = torch.randn(y0.shape, device="cuda", generator=g).to(tdt)
+        dy = torch.empty_like(y0).normal_(generator=g)       # same (column-major) strides as y: no layout copy in the step
         def step():
             y, pb = L.rrule_maxpool(x, pd)
             return pb(dy)
