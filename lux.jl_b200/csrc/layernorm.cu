@@ -82,6 +82,77 @@ __global__ void __launch_bounds__(BT) ln_fwd_cached_kernel(T* __restrict__ y, fl
 }
 
 // ---------------------------------------------------------------------------------------------
+// Warp-per-row forward for 2-byte elements: a lane keeps NV 16-byte vectors of the row PACKED in registers (a row of
+// 4096 bf16 is 16 vectors = 64 registers per lane), so both passes read registers, the only reduction is a warp
+// butterfly (no block barrier, no shared-memory ring, no spin on an mbarrier) and the warps of an SM are in different
+// phases of their rows at any time, which is what keeps loads in flight. Scale and shift are staged in shared memory
+// once per CTA and read per use. Statistics in one pass over d = x - K, K = the row's first element.
+// ---------------------------------------------------------------------------------------------
+template <typename T, int ACT, bool AFFINE, int NV>
+__global__ void __launch_bounds__(256, 2) ln_fwd_warp_kernel(T* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ inv_out,
+                                                             const T* __restrict__ x, const T* __restrict__ gamma,
+                                                             const T* __restrict__ beta, int64_t D, int64_t R, float eps, int act_rt) {
+  constexpr bool FAST = sizeof(T) == 2;
+  constexpr int V = Vec16<T>::N;
+  extern __shared__ __align__(16) uint8_t ln_warp_smem[];
+  T* sg = reinterpret_cast<T*>(ln_warp_smem);
+  T* sb = sg + D;
+  if constexpr (AFFINE) {
+    for (int64_t i = (int64_t)threadIdx.x * V; i < D; i += (int64_t)blockDim.x * V) {
+      store16(sg + i, load16(gamma + i));
+      store16(sb + i, load16(beta + i));
+    }
+    __syncthreads();
+  }
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  const float invD = 1.f / (float)D;
+  for (int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < R; row += warps) {
+    const T* xr = x + row * D;
+    Vec16<T> xv[NV];
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int64_t i = ((int64_t)k * 32 + lane) * V;
+      if (i < D) xv[k] = load16_stream(xr + i);
+    }
+    const float K0 = __shfl_sync(0xffffffffu, xv[0].get(0), 0);
+    float s = 0.f, q = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      if (((int64_t)k * 32 + lane) * V < D) {
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          const float d = xv[k].get(j) - K0;
+          s += d;
+          q = fmaf(d, d, q);
+        }
+      }
+    }
+    s = warp_sum(s);
+    q = warp_sum(q);
+    const float dm = s * invD;                                   // mean - K
+    const float var = fmaxf(fmaf(-dm, dm, q * invD), 0.f);
+    const float inv = 1.f / sqrtf(var + eps);
+    const float nmi = -dm * inv;
+    if (lane == 0) { mean_out[row] = K0 + dm; inv_out[row] = inv; }
+    T* yr = y + row * D;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int64_t i = ((int64_t)k * 32 + lane) * V;
+      if (i < D) {
+        Vec16<T> gv, bv;
+        if constexpr (AFFINE) { gv = load16(sg + i); bv = load16(sb + i); }
+        store16_stream(yr + i, vec_from<T>([&](int j) {
+          float v = fmaf(xv[k].get(j) - K0, inv, nmi);             // (x - mean) * inv
+          if constexpr (AFFINE) v = fmaf(v, gv.get(j), bv.get(j));
+          return act_apply_any<ACT, FAST>(act_rt, v);
+        }));
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
 // Ring-buffered variants (one CTA per row, 256 compute threads + one copy-producer warp).
 // The phases of a row (load, two reductions, store) leave the memory system idle while a CTA
 // reduces, and with rows held in registers only a couple of CTAs fit per SM. Here a producer
@@ -143,52 +214,73 @@ ln_fwd_ring_kernel(T* __restrict__ y, float* __restrict__ mean_out, float* __res
     }
   }
   const float invD = 1.f / (float)D;
-  for (int64_t it = 0; it < nrows; ++it) {
-    const int st = (int)(it % stages);
-    const uint32_t ph = (uint32_t)((it / stages) & 1);
-    const int64_t row = blockIdx.x + it * gridDim.x;
-    if (!mbar_wait_warp(&full[st], ph, status, 0x400000u)) *abort_flag = 1;
-    const T* sx = reinterpret_cast<const T*>(data + (size_t)st * row_bytes);
-    // One pass over the row: sums of d = x - K and of d^2 with K = the row's first element (a sample of the row, so
+  // Two rows per round: a round costs a fixed chain (wait, pass, block reduction with two barriers, pass) that does not
+  // depend on the row length, so short rows (2-byte elements) are bound by rounds per second, not by bytes; two rows
+  // share one reduction (four sums) and halve the number of rounds.
+  constexpr int kRowsPerRound = sizeof(T) == 2 ? 2 : 1;   // 4-byte rows are long enough to be bandwidth-bound one at a time
+  for (int64_t it = 0; it < nrows; it += kRowsPerRound) {
+    const bool two = kRowsPerRound == 2 && it + 1 < nrows;
+    const int st0 = (int)(it % stages), st1 = (int)((it + 1) % stages);
+    const uint32_t ph0 = (uint32_t)((it / stages) & 1), ph1 = (uint32_t)(((it + 1) / stages) & 1);
+    const int64_t row0 = blockIdx.x + it * gridDim.x, row1 = row0 + gridDim.x;
+    if (!mbar_wait_warp(&full[st0], ph0, status, 0x400000u)) *abort_flag = 1;
+    if (two && !mbar_wait_warp(&full[st1], ph1, status, 0x400000u)) *abort_flag = 1;
+    const T* sx0 = reinterpret_cast<const T*>(data + (size_t)st0 * row_bytes);
+    const T* sx1 = reinterpret_cast<const T*>(data + (size_t)st1 * row_bytes);
+    // One pass over a row: sums of d = x - K and of d^2 with K = the row's first element (a sample of the row, so
     // |mean - K| is of the order of the deviation and var = E[d^2] - E[d]^2 does not cancel), reduced together.
-    const float K0 = to_f32(sx[0]);
-    float df[NV][V];
-    float s = 0.f, q = 0.f;
+    const float K0 = to_f32(sx0[0]), K1 = two ? to_f32(sx1[0]) : 0.f;
+    float df0[NV][V], df1[NV][V];
+    float s0 = 0.f, q0 = 0.f, s1 = 0.f, q1 = 0.f;
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
       const int64_t i = ((int64_t)k * kRingCompute + t) * V;
       if (i < D) {
-        const Vec16<T> xv = load16(sx + i);
+        const Vec16<T> xv = load16(sx0 + i);
 #pragma unroll
         for (int j = 0; j < V; ++j) {
           const float d = xv.get(j) - K0;
-          df[k][j] = d;
-          s += d;
-          q = fmaf(d, d, q);
+          df0[k][j] = d;
+          s0 += d;
+          q0 = fmaf(d, d, q0);
+        }
+        if (two) {
+          const Vec16<T> xw = load16(sx1 + i);
+#pragma unroll
+          for (int j = 0; j < V; ++j) {
+            const float d = xw.get(j) - K1;
+            df1[k][j] = d;
+            s1 += d;
+            q1 = fmaf(d, d, q1);
+          }
         }
       }
     }
     __syncwarp();
-    if (lane == 0) mbar_arrive(&empty[st]);
-    const float2 sq = group_sum2(s, q, red, kRingCompute);
+    if (lane == 0) { mbar_arrive(&empty[st0]); if (two) mbar_arrive(&empty[st1]); }
+    const float4 sq = group_sum4(s0, q0, s1, q1, red, kRingCompute);
     if (*abort_flag) { drain_after_abort(); break; }
-    const float dm = sq.x * invD;                                  // mean - K
-    const float var = fmaxf(fmaf(-dm, dm, sq.y * invD), 0.f);
-    const float inv = 1.f / sqrtf(var + eps);
-    const float nmi = -dm * inv;
-    if (t == 0) { mean_out[row] = K0 + dm; inv_out[row] = inv; }
-    T* yr = y + row * D;
+    auto finish = [&](float su, float sq2, float K, int64_t row, float (&df)[NV][V]) {
+      const float dm = su * invD;                                  // mean - K
+      const float var = fmaxf(fmaf(-dm, dm, sq2 * invD), 0.f);
+      const float inv = 1.f / sqrtf(var + eps);
+      const float nmi = -dm * inv;
+      if (t == 0) { mean_out[row] = K + dm; inv_out[row] = inv; }
+      T* yr = y + row * D;
 #pragma unroll
-    for (int k = 0; k < NV; ++k) {
-      const int64_t i = ((int64_t)k * kRingCompute + t) * V;
-      if (i < D) {
-        store16_stream(yr + i, vec_from<T>([&](int j) {
-          float v = fmaf(df[k][j], inv, nmi);                      // (x - mean) * inv
-          if constexpr (AFFINE) v = fmaf(v, gf[k][j], bf[k][j]);
-          return act_apply_any<ACT, FAST>(act_rt, v);
-        }));
+      for (int k = 0; k < NV; ++k) {
+        const int64_t i = ((int64_t)k * kRingCompute + t) * V;
+        if (i < D) {
+          store16_stream(yr + i, vec_from<T>([&](int j) {
+            float v = fmaf(df[k][j], inv, nmi);                      // (x - mean) * inv
+            if constexpr (AFFINE) v = fmaf(v, gf[k][j], bf[k][j]);
+            return act_apply_any<ACT, FAST>(act_rt, v);
+          }));
+        }
       }
-    }
+    };
+    finish(sq.x, sq.y, K0, row0, df0);
+    if (two) finish(sq.z, sq.w, K1, row1, df1);
   }
 }
 
@@ -247,16 +339,19 @@ ln_bwd_ring_kernel(T* __restrict__ dx, float* __restrict__ partial, const T* __r
     }
   }
   const float invD = 1.f / (float)D;
-  for (int64_t it = 0; it < nrows; ++it) {
-    const int st = (int)(it % stages);
-    const uint32_t ph = (uint32_t)((it / stages) & 1);
-    const int64_t row = blockIdx.x + it * gridDim.x;
-    const float mean = mean_in[row], inv = inv_in[row];
-    if (!mbar_wait_warp(&full[st], ph, status, 0x1000000u)) *abort_flag = 1;
-    const T* sx = reinterpret_cast<const T*>(data + (size_t)st * 2 * row_bytes);
-    const T* sdy = reinterpret_cast<const T*>(data + (size_t)st * 2 * row_bytes + row_bytes);
-    // The row stays in its ring stage through both passes (registers hold only the dgamma/dbeta
-    // accumulators), so two CTAs fit on an SM and one reduces while the other streams.
+  // Two rows per round (see the forward kernel): the rows stay in their ring stages through both passes, the
+  // dgamma / dbeta accumulators are per feature and therefore shared by the two rows (row order kept), and one
+  // reduction of four sums serves both.
+  constexpr int kRowsPerRound = sizeof(T) == 2 ? 2 : 1;   // 4-byte rows are long enough to be bandwidth-bound one at a time
+  for (int64_t it = 0; it < nrows; it += kRowsPerRound) {
+    const bool two = kRowsPerRound == 2 && it + 1 < nrows;
+    const int st0 = (int)(it % stages), st1 = (int)((it + 1) % stages);
+    const uint32_t ph0 = (uint32_t)((it / stages) & 1), ph1 = (uint32_t)(((it + 1) / stages) & 1);
+    const int64_t row0 = blockIdx.x + it * gridDim.x, row1 = row0 + gridDim.x;
+    const float mean0 = mean_in[row0], inv0 = inv_in[row0];
+    const float mean1 = two ? mean_in[row1] : 0.f, inv1 = two ? inv_in[row1] : 0.f;
+    if (!mbar_wait_warp(&full[st0], ph0, status, 0x1000000u)) *abort_flag = 1;
+    if (two && !mbar_wait_warp(&full[st1], ph1, status, 0x1000000u)) *abort_flag = 1;
     // d = dy * act'(pre-activation), the pre-activation rebuilt as ((x - mean) * inv) * gamma + beta
     auto act_scaled = [&](float d, float xh, int k, int j) {
       if constexpr (ACT != LB2_ACT_IDENTITY) {
@@ -266,50 +361,62 @@ ln_bwd_ring_kernel(T* __restrict__ dx, float* __restrict__ partial, const T* __r
       }
       return d;
     };
-    float s1 = 0.f, s2 = 0.f;
+    auto pass1 = [&](int st, float mean, float inv, float& s1, float& s2) {
+      const T* sx = reinterpret_cast<const T*>(data + (size_t)st * 2 * row_bytes);
+      const T* sdy = reinterpret_cast<const T*>(data + (size_t)st * 2 * row_bytes + row_bytes);
 #pragma unroll
-    for (int k = 0; k < NV; ++k) {
-      const int64_t i = ((int64_t)k * kRingCompute + t) * V;
-      if (i < D) {
-        const Vec16<T> xv = load16(sx + i), gy = load16(sdy + i);
+      for (int k = 0; k < NV; ++k) {
+        const int64_t i = ((int64_t)k * kRingCompute + t) * V;
+        if (i < D) {
+          const Vec16<T> xv = load16(sx + i), gy = load16(sdy + i);
 #pragma unroll
-        for (int j = 0; j < V; ++j) {
-          const float xh = (xv.get(j) - mean) * inv;
-          const float d = act_scaled(gy.get(j), xh, k, j);
-          float g = d;
-          if constexpr (AFFINE) {
-            adg[k][j] = fmaf(d, xh, adg[k][j]);
-            adb[k][j] += d;
-            g = d * gf[k][j];
+          for (int j = 0; j < V; ++j) {
+            const float xh = (xv.get(j) - mean) * inv;
+            const float d = act_scaled(gy.get(j), xh, k, j);
+            float g = d;
+            if constexpr (AFFINE) {
+              adg[k][j] = fmaf(d, xh, adg[k][j]);
+              adb[k][j] += d;
+              g = d * gf[k][j];
+            }
+            s1 += g;
+            s2 = fmaf(g, xh, s2);
           }
-          s1 += g;
-          s2 = fmaf(g, xh, s2);
         }
       }
-    }
-    const float2 m12 = group_sum2(s1, s2, red, kRingCompute);
+    };
+    float s1a = 0.f, s2a = 0.f, s1b = 0.f, s2b = 0.f;
+    pass1(st0, mean0, inv0, s1a, s2a);
+    if (two) pass1(st1, mean1, inv1, s1b, s2b);
+    const float4 m = group_sum4(s1a, s2a, s1b, s2b, red, kRingCompute);
     if (*abort_flag) { drain_after_abort(); break; }
-    const float m1 = m12.x * invD, m2 = m12.y * invD;
     // dx = inv * (g - m1 - xh * m2) = g * inv + (x * c1i + c0m): the xh term folded into one multiply-add on x
-    const float c1i = -inv * m2 * inv;
-    const float c0m = fmaf(-mean, c1i, -inv * m1);
-    T* dxr = dx + row * D;
+    auto pass2 = [&](int st, int64_t row, float mean, float inv, float sum1, float sum2) {
+      const T* sx = reinterpret_cast<const T*>(data + (size_t)st * 2 * row_bytes);
+      const T* sdy = reinterpret_cast<const T*>(data + (size_t)st * 2 * row_bytes + row_bytes);
+      const float m1 = sum1 * invD, m2 = sum2 * invD;
+      const float c1i = -inv * m2 * inv;
+      const float c0m = fmaf(-mean, c1i, -inv * m1);
+      T* dxr = dx + row * D;
 #pragma unroll
-    for (int k = 0; k < NV; ++k) {
-      const int64_t i = ((int64_t)k * kRingCompute + t) * V;
-      if (i < D) {
-        const Vec16<T> xv = load16(sx + i), gy = load16(sdy + i);
-        store16_stream(dxr + i, vec_from<T>([&](int j) {
-          const float xf = xv.get(j);
-          float d = gy.get(j);
-          if constexpr (ACT != LB2_ACT_IDENTITY) d = act_scaled(d, (xf - mean) * inv, k, j);
-          if constexpr (AFFINE) d *= gf[k][j];
-          return fmaf(d, inv, fmaf(xf, c1i, c0m));
-        }));
+      for (int k = 0; k < NV; ++k) {
+        const int64_t i = ((int64_t)k * kRingCompute + t) * V;
+        if (i < D) {
+          const Vec16<T> xv = load16(sx + i), gy = load16(sdy + i);
+          store16_stream(dxr + i, vec_from<T>([&](int j) {
+            const float xf = xv.get(j);
+            float d = gy.get(j);
+            if constexpr (ACT != LB2_ACT_IDENTITY) d = act_scaled(d, (xf - mean) * inv, k, j);
+            if constexpr (AFFINE) d *= gf[k][j];
+            return fmaf(d, inv, fmaf(xf, c1i, c0m));
+          }));
+        }
       }
-    }
-    __syncwarp();
-    if (lane == 0) mbar_arrive(&empty[st]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[st]);
+    };
+    pass2(st0, row0, mean0, inv0, m.x, m.y);
+    if (two) pass2(st1, row1, mean1, inv1, m.z, m.w);
   }
   if constexpr (AFFINE) {
     float* pg = partial + (int64_t)blockIdx.x * 2 * D;
@@ -654,7 +761,15 @@ static int32_t ln_fwd_launch(T* y, float* sm, float* si, const T* x, const T* g,
                              float eps, int32_t act, cudaStream_t st) {
   const bool al = aligned_to(y, 16) && aligned_to(x, 16) && (!g || (aligned_to(g, 16) && aligned_to(b, 16)));
   const LnPlan p = ln_plan<T>(D, R, al, false);
-  if (p.ring) {
+  constexpr int V = Vec16<T>::N;
+  if (sizeof(T) == 2 && p.cached && D % V == 0 && D / V > 32 * 4 && D / V <= 32 * 16 && R >= (int64_t)sm_count() * 16) {
+    // rows of 1025 to 4096 two-byte elements, enough of them to give every resident warp several rows
+    const int smem = AFFINE ? (int)(2 * D * sizeof(T)) : 0;
+    const int grid = sm_count() * 2;
+    const int64_t vecs = D / V;
+    if (vecs <= 32 * 8) ln_fwd_warp_kernel<T, ACT, AFFINE, 8><<<grid, 256, smem, st>>>(y, sm, si, x, g, b, D, R, eps, act);
+    else ln_fwd_warp_kernel<T, ACT, AFFINE, 16><<<grid, 256, smem, st>>>(y, sm, si, x, g, b, D, R, eps, act);
+  } else if (p.ring) {
     unsigned int* status = device_status_word();
     LB2_REQUIRE(status != nullptr, LB2_LAUNCH_FAIL, "layernorm: device status word unavailable");
     LN_RING_SWITCH(ln_fwd_ring_kernel, y, sm, si, x, g, b, D, R, eps, act, p.stages, status)

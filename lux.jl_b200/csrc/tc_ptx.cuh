@@ -254,6 +254,18 @@ __device__ __forceinline__ float2 group_sum2(float a, float b, float* smem, int 
   return make_float2(warp_sum(ta), warp_sum(tb));
 }
 
+// four sums at once (one barrier pair); smem holds 128 floats
+__device__ __forceinline__ float4 group_sum4(float a, float b, float c, float d, float* smem, int nthreads) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = nthreads >> 5;
+  a = warp_sum(a); b = warp_sum(b); c = warp_sum(c); d = warp_sum(d);
+  asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+  if (lane == 0) { smem[w] = a; smem[32 + w] = b; smem[64 + w] = c; smem[96 + w] = d; }
+  asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+  const bool in = lane < nw;
+  const float ta = in ? smem[lane] : 0.f, tb = in ? smem[32 + lane] : 0.f, tc = in ? smem[64 + lane] : 0.f, td = in ? smem[96 + lane] : 0.f;
+  return make_float4(warp_sum(ta), warp_sum(tb), warp_sum(tc), warp_sum(td));
+}
+
 // cuTensorMapEncodeTiled through the runtime's driver entry point (no link-time libcuda dependency).
 typedef CUresult (*TensorMapEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                       const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,

@@ -574,7 +574,9 @@ def test_groupnorm_errors():
 @pytest.mark.parametrize("dt", ["f32", "bf16"])
 @pytest.mark.parametrize("act", ["identity", "tanh"])
 @pytest.mark.parametrize("shape,nd", [((16, 7), 1), ((4096, 9), 1), ((4, 4, 6, 3), 3), ((100, 33), 1), ((6000, 4), 1),
-                                      ((24576, 3), 1), ((1030, 5), 1)])
+                                      ((24576, 3), 1), ((1030, 5), 1),
+                                      # many rows of 2048 / 4096 / 1152 elements: the warp-per-row forward of 2-byte rows
+                                      ((2048, 2400), 1), ((4096, 2500), 1), ((1152, 2377), 1)])
 @pytest.mark.parametrize("affine", [True, False])
 def test_layernorm_fwd_bwd(dt, act, shape, nd, affine):
     rng = np.random.default_rng(18)
