@@ -470,7 +470,15 @@ def run_gpu_arm(args):
         for _ in range(5):
             comm_only()
         comm_total, _, _ = timed(comm_only, torch, args.steps, barrier, local)
-        nocomm_total, _, _ = timed(lambda: step_from(x, dy, collectives=False), torch, args.steps, barrier, local)
+        # the same step without its all-reduces, timed the way the step itself is: a graph replay after an untimed ramp
+        nocomm_step = lambda: step_from(x, dy, collectives=False)
+        for _ in range(3):
+            nocomm_step()
+        torch.cuda.synchronize()
+        g_nc, _ = capture(nocomm_step, torch, device)
+        run_nc = g_nc.replay if g_nc is not None else nocomm_step
+        ramp(run_nc, torch, 0.3, barrier, dist)
+        nocomm_total, _, _ = timed(run_nc, torch, args.steps, barrier, local)
         tt = torch.tensor([comm_total / args.steps, nocomm_total / args.steps], device=device)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         comm_ms, nocomm_ms = float(tt[0]), float(tt[1])
