@@ -406,7 +406,10 @@ __global__ void __launch_bounds__(kGnThreads, 2)
 gn_bwd_stream_kernel(T* __restrict__ dx, float* __restrict__ chan_out, const T* __restrict__ dy,
                      const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
                      const float* __restrict__ mean_in, const float* __restrict__ inv_in, uint32_t S, uint32_t Cg,
-                     uint32_t G, int64_t rows, int act_rt, int stages, uint32_t aux_bytes, unsigned int* status) {
+                     uint32_t G, int64_t rows, int act_rt, int stages, uint32_t aux_bytes, unsigned int* status, int resident) {
+  // resident: the ring has exactly one stage per chunk of a row (stages == nchunks), so the row stays in shared memory
+  // from the first pass to the second: it is fetched once, the second pass waits for nothing, and a stage is released
+  // (to the next row's copy) only after its second use.
   constexpr bool FAST = sizeof(T) == 2;
   constexpr int V = Vec16<T>::N;
   constexpr uint32_t CE = kGnChunkBytes / sizeof(T);
@@ -436,7 +439,7 @@ gn_bwd_stream_kernel(T* __restrict__ dx, float* __restrict__ chan_out, const T* 
       uint32_t st = 0, ph = 0;
       for (int64_t r = 0; r < nrows; ++r) {
         const int64_t base = (blockIdx.x + r * gridDim.x) * (int64_t)L;
-        for (int pass = 0; pass < 2; ++pass) {
+        for (int pass = 0; pass < (resident ? 1 : 2); ++pass) {
           for (uint32_t c = 0; c < nchunks; ++c) {
             if (!mbar_wait(&empty[st], ph ^ 1u, status, 0x8000000u)) return;
             const uint32_t left = (L - c * CE) * (uint32_t)sizeof(T);
@@ -501,7 +504,7 @@ gn_bwd_stream_kernel(T* __restrict__ dx, float* __restrict__ chan_out, const T* 
         const uint32_t sl = c * kSlotsPerChunk + (uint32_t)(k * (kGnCompute / 32) + warp);
         if (lane < 8 && sl < nslots) slots[sl * 8 + lane] = make_float2(a, b);
       }
-      if (!dead) {
+      if (!dead && !resident) {
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[st]);
       }
@@ -540,10 +543,11 @@ gn_bwd_stream_kernel(T* __restrict__ dx, float* __restrict__ chan_out, const T* 
     T* dxr = dx + row * (int64_t)L;
     // pass 2: dx = inv * (d*gamma - m1 - xh*m2)
     for (uint32_t c = 0; c < nchunks; ++c) {
-      if (!dead && !mbar_wait_warp(&full[st], ph, status, 0x20000000u)) { dead = true; *abort_flag = 1; }
+      const uint32_t sc = resident ? c : st;      // resident: chunk c sits in stage c since the first pass
+      if (!resident && !dead && !mbar_wait_warp(&full[st], ph, status, 0x20000000u)) { dead = true; *abort_flag = 1; }
       if (!dead) {
-        const T* sx = reinterpret_cast<const T*>(data + (size_t)st * 2 * kGnChunkBytes);
-        const T* sdy = reinterpret_cast<const T*>(data + (size_t)st * 2 * kGnChunkBytes + kGnChunkBytes);
+        const T* sx = reinterpret_cast<const T*>(data + (size_t)sc * 2 * kGnChunkBytes);
+        const T* sdy = reinterpret_cast<const T*>(data + (size_t)sc * 2 * kGnChunkBytes + kGnChunkBytes);
 #pragma unroll
         for (int k = 0; k < kGnVecsPerChunk; ++k) {
           const uint32_t off = (uint32_t)(k * kGnCompute + t) * V;
@@ -559,9 +563,9 @@ gn_bwd_stream_kernel(T* __restrict__ dx, float* __restrict__ chan_out, const T* 
           }
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(&empty[st]);
+        if (lane == 0) mbar_arrive(&empty[sc]);
       }
-      if (++st == (uint32_t)stages) { st = 0; ph ^= 1u; }
+      if (!resident && ++st == (uint32_t)stages) { st = 0; ph ^= 1u; }
     }
   }
 }
@@ -654,13 +658,16 @@ static int32_t gn_bwd_launch(T* dx, T* dg, T* db, const T* dy, const T* x, const
   if ((gn_stream_mask() & 2) && al && fits32 && aux <= 64 * 1024 && L * (int64_t)sizeof(T) >= 2 * (int64_t)kGnChunkBytes) {
     unsigned int* status = device_status_word();
     LB2_REQUIRE(status != nullptr, LB2_LAUNCH_FAIL, "groupnorm: device status word unavailable");
-    const int stages = 6;
+    // rows of at most four chunks per operand (64 KB of x and dy together) stay resident between the passes
+    const int64_t nchunks = (L * (int64_t)sizeof(T) + kGnChunkBytes - 1) / kGnChunkBytes;
+    const int resident = nchunks <= 4 ? 1 : 0;
+    const int stages = resident ? (int)nchunks : 6;
     const int smem = kGnHeaderBytes + (int)aux + stages * 2 * (int)kGnChunkBytes;
     cudaError_t e = cudaFuncSetAttribute(gn_bwd_stream_kernel<T, ACT, AFFINE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     LB2_REQUIRE(e == cudaSuccess, LB2_LAUNCH_FAIL, "groupnorm: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
     const int per_sm = smem <= 112 * 1024 ? 2 : 1;
     grid = (int)(rows < (int64_t)sms * per_sm ? rows : (int64_t)sms * per_sm);
-    gn_bwd_stream_kernel<T, ACT, AFFINE><<<grid, kGnThreads, smem, st>>>(dx, ws, dy, x, g, b, sm, si, (uint32_t)S, (uint32_t)Cg, (uint32_t)G, rows, act, stages, (uint32_t)aux, status);
+    gn_bwd_stream_kernel<T, ACT, AFFINE><<<grid, kGnThreads, smem, st>>>(dx, ws, dy, x, g, b, sm, si, (uint32_t)S, (uint32_t)Cg, (uint32_t)G, rows, act, stages, (uint32_t)aux, status, resident);
   } else if (al && vecs <= 512 * 4) {
     const int nv = vecs <= 512 ? 1 : (vecs <= 1024 ? 2 : 4);
     if (nv == 1) gn_bwd_cached_kernel<T, ACT, AFFINE, 1, 512><<<grid, 512, dyn, st>>>(dx, ws, dy, x, g, b, sm, si, S, Cg, G, rows, act);
