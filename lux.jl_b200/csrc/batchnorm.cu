@@ -189,19 +189,69 @@ __global__ void __launch_bounds__(256) bn_reduce_kernel(float* __restrict__ part
         q = fmaf(d, xm, q);
       }
     };
-    for (int64_t b = b_begin + warp; b < b_end; b += 8) {
+    // four planes of the channel (samples b, b + 8, b + 16, b + 24) per round, all loads of a round issued before any
+    // is used: planes are short (392 or 98 bytes), so one at a time leaves a lane with a single small load in flight
+    const bool quads = sizeof(T) == 2 && (Si & 3) == 0 && aligned_to_dev(x, 8) && (MODE == 0 || aligned_to_dev(dy, 8));
+    const int64_t plane_stride = C * S;
+    for (int64_t b = b_begin + warp; b < b_end; b += 32) {
       const T* xr = x + (b * C + c) * S;
       const T* gr = MODE == 1 ? dy + (b * C + c) * S : nullptr;
-      if (pairs) {
+      bool live[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) live[u] = b + 8 * u < b_end;
+      if (quads) {
+        for (int i = lane * 4; i < Si; i += 128) {
+          uint2 ux[4], ug[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            if (live[u]) {
+              ux[u] = *reinterpret_cast<const uint2*>(xr + u * 8 * plane_stride + i);
+              if constexpr (MODE == 1) ug[u] = *reinterpret_cast<const uint2*>(gr + u * 8 * plane_stride + i);
+              else ug[u] = make_uint2(0u, 0u);
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            if (live[u]) {
+              one(__uint_as_float(ux[u].x << 16), __uint_as_float(ug[u].x << 16));
+              one(__uint_as_float(ux[u].x & 0xFFFF0000u), __uint_as_float(ug[u].x & 0xFFFF0000u));
+              one(__uint_as_float(ux[u].y << 16), __uint_as_float(ug[u].y << 16));
+              one(__uint_as_float(ux[u].y & 0xFFFF0000u), __uint_as_float(ug[u].y & 0xFFFF0000u));
+            }
+          }
+        }
+      } else if (pairs) {
         for (int i = lane * 2; i < Si; i += 64) {
-          const uint32_t ux = *reinterpret_cast<const uint32_t*>(xr + i);
-          uint32_t ug = 0;
-          if constexpr (MODE == 1) ug = *reinterpret_cast<const uint32_t*>(gr + i);
-          one(__uint_as_float(ux << 16), __uint_as_float(ug << 16));
-          one(__uint_as_float(ux & 0xFFFF0000u), __uint_as_float(ug & 0xFFFF0000u));
+          uint32_t ux[4], ug[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            if (live[u]) {
+              ux[u] = *reinterpret_cast<const uint32_t*>(xr + u * 8 * plane_stride + i);
+              ug[u] = MODE == 1 ? *reinterpret_cast<const uint32_t*>(gr + u * 8 * plane_stride + i) : 0u;
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            if (live[u]) {
+              one(__uint_as_float(ux[u] << 16), __uint_as_float(ug[u] << 16));
+              one(__uint_as_float(ux[u] & 0xFFFF0000u), __uint_as_float(ug[u] & 0xFFFF0000u));
+            }
+          }
         }
       } else {
-        for (int i = lane; i < Si; i += 32) one(to_f32(xr[i]), MODE == 1 ? to_f32(gr[i]) : 0.f);
+        for (int i = lane; i < Si; i += 32) {
+          float fx[4], fg[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            if (live[u]) {
+              fx[u] = to_f32(xr[u * 8 * plane_stride + i]);
+              fg[u] = MODE == 1 ? to_f32(gr[u * 8 * plane_stride + i]) : 0.f;
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            if (live[u]) one(fx[u], fg[u]);
+        }
       }
     }
   }
@@ -471,6 +521,73 @@ __global__ void __launch_bounds__(256) bn_apply_kernel(T* __restrict__ out, cons
   }
 }
 
+// Apply pass for planes that cannot take 16-byte vectors on their own (14 x 14 and 7 x 7 feature maps: 392 and 98
+// bytes per plane): the TENSOR is walked in 16-byte vectors regardless of plane boundaries. A vector starts in plane
+// p0 = e0 / S and may run into the next one (S >= 8 elements, so at most one boundary per vector); the per-channel
+// coefficients of both come from a table in shared memory that every CTA builds once. Divisions are multiply-high by
+// host-made reciprocals. Walks memory backwards like the other apply kernels.
+struct BnFastDiv { uint64_t mul; uint32_t d; };
+static BnFastDiv bn_fastdiv(uint32_t d) { return BnFastDiv{d > 1 ? ~0ull / d + 1 : 0ull, d}; }
+__device__ __forceinline__ uint32_t bn_div(uint32_t n, const BnFastDiv& f) { return f.d > 1 ? (uint32_t)__umul64hi((uint64_t)n, f.mul) : n; }
+
+template <typename T, int MODE, int ACT, bool AFFINE>
+__global__ void __launch_bounds__(256) bn_apply_flat_kernel(T* __restrict__ out, const T* __restrict__ x, const T* __restrict__ dy,
+                                                            const float* __restrict__ coef, const T* __restrict__ gamma,
+                                                            const T* __restrict__ beta, const T* __restrict__ rmean,
+                                                            const T* __restrict__ rvar, const float* __restrict__ mean_in,
+                                                            const float* __restrict__ inv_in, BnFastDiv dS, BnFastDiv dC,
+                                                            uint32_t nvec, float eps, int act_rt) {
+  constexpr bool FAST = sizeof(T) == 2;
+  constexpr int V = Vec16<T>::N;
+  constexpr int NF = MODE == 2 ? 6 : 2;          // gp, bp [, c0, c1, c2, mean]
+  extern __shared__ __align__(16) float bn_flat_tab[];
+  const uint32_t S = dS.d, C = dC.d;
+  for (uint32_t c = threadIdx.x; c < C; c += blockDim.x) {
+    float gp, bp;
+    bn_channel_coefs<T, MODE, ACT, AFFINE>(c, coef, gamma, beta, rmean, rvar, mean_in, inv_in, eps, gp, bp);
+    bn_flat_tab[c * NF] = gp;
+    bn_flat_tab[c * NF + 1] = bp;
+    if constexpr (MODE == 2) {
+      bn_flat_tab[c * NF + 2] = coef[c * 4];
+      bn_flat_tab[c * NF + 3] = coef[c * 4 + 1];
+      bn_flat_tab[c * NF + 4] = coef[c * 4 + 2];
+      bn_flat_tab[c * NF + 5] = ACT != LB2_ACT_IDENTITY ? mean_in[c] : 0.f;
+    }
+  }
+  __syncthreads();
+  const uint32_t stride = gridDim.x * blockDim.x;
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+    const uint32_t vi = nvec - 1 - i;
+    const uint32_t e0 = vi * V;
+    const uint32_t p0 = bn_div(e0, dS);
+    const uint32_t r0 = e0 - p0 * S;
+    const uint32_t ca = p0 - bn_div(p0, dC) * C;
+    const uint32_t cb = ca + 1 == C ? 0 : ca + 1;
+    const int cut = (int)(S - r0);               // elements j >= cut belong to the next plane
+    const float* ta = bn_flat_tab + ca * NF;
+    const float* tb = bn_flat_tab + cb * NF;
+    const Vec16<T> xv = load16_stream(x + e0);
+    Vec16<T> gv;
+    if constexpr (MODE == 2) gv = load16_stream(dy + e0);
+    float fa[NF], fb[NF];
+#pragma unroll
+    for (int k = 0; k < NF; ++k) { fa[k] = ta[k]; fb[k] = tb[k]; }
+    store16_stream(out + e0, vec_from<T>([&](int j) {
+      const bool nxt = j >= cut;
+      const float gp = nxt ? fb[0] : fa[0], bp = nxt ? fb[1] : fa[1];
+      const float xf = xv.get(j);
+      if constexpr (MODE == 2) {
+        float d = gv.get(j);
+        const float mu = nxt ? fb[5] : fa[5];
+        if constexpr (ACT != LB2_ACT_IDENTITY) d *= act_grad_pre_any<ACT, FAST>(act_rt, fmaf(xf - mu, gp, bp));
+        return fmaf(nxt ? fb[2] : fa[2], d, fmaf(nxt ? fb[3] : fa[3], xf, nxt ? fb[4] : fa[4]));
+      } else {
+        return act_apply_any<ACT, FAST>(act_rt, fmaf(xf, gp, bp));
+      }
+    }));
+  }
+}
+
 static unsigned apply_grid(int64_t items) {
   int64_t g = (items + 255) / 256, cap = (int64_t)sm_count() * 16;
   return (unsigned)(g < 1 ? 1 : (g > cap ? cap : g));
@@ -503,8 +620,17 @@ static void bn_apply_launch(T* out, const T* x, const T* dy, const float* coef, 
   const int64_t n = S * C * B;
   const bool vec = aligned_to(out, 16) && aligned_to(x, 16) && (!dy || aligned_to(dy, 16)) && S % V == 0;
   const int64_t units = (n / S) * ((S / V + 127) / 128);   // one warp per unit, 8 warps per CTA
-  if (vec) bn_apply_kernel<T, MODE, ACT, AFFINE, true><<<apply_grid(units * 32), 256, 0, st>>>(out, x, dy, coef, g, b, rm, rv, sm, si, S, C, n, eps, act);
-  else bn_apply_kernel<T, MODE, ACT, AFFINE, false><<<apply_grid((n / S) * 32), 256, 0, st>>>(out, x, dy, coef, g, b, rm, rv, sm, si, S, C, n, eps, act);
+  const bool flat = !vec && S >= V && n % V == 0 && n < ((int64_t)1 << 32) && C <= 2048 && aligned_to(out, 16) && aligned_to(x, 16) &&
+                    (!dy || aligned_to(dy, 16));
+  if (vec) {
+    bn_apply_kernel<T, MODE, ACT, AFFINE, true><<<apply_grid(units * 32), 256, 0, st>>>(out, x, dy, coef, g, b, rm, rv, sm, si, S, C, n, eps, act);
+  } else if (flat) {
+    const size_t tab = (size_t)C * (MODE == 2 ? 6 : 2) * sizeof(float);     // at most 48 KB
+    bn_apply_flat_kernel<T, MODE, ACT, AFFINE><<<apply_grid(n / V), 256, tab, st>>>(out, x, dy, coef, g, b, rm, rv, sm, si, bn_fastdiv((uint32_t)S),
+                                                                                    bn_fastdiv((uint32_t)C), (uint32_t)(n / V), eps, act);
+  } else {
+    bn_apply_kernel<T, MODE, ACT, AFFINE, false><<<apply_grid((n / S) * 32), 256, 0, st>>>(out, x, dy, coef, g, b, rm, rv, sm, si, S, C, n, eps, act);
+  }
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -398,7 +398,10 @@ def test_conv_known_answers():
 # ------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("dt", ["f32", "bf16"])
 @pytest.mark.parametrize("act", ["identity", "relu", "sigmoid"])
-@pytest.mark.parametrize("shape", [(4, 4, 6, 2), (8, 2), (64, 48), (12, 12, 16, 8), (7, 5, 3, 4)])
+@pytest.mark.parametrize("shape", [(4, 4, 6, 2), (8, 2), (64, 48), (12, 12, 16, 8), (7, 5, 3, 4),
+                                   # planes of 392 / 98 bytes: reductions four planes per round (8-byte / 2-byte loads), apply pass
+                                   # in 16-byte vectors across plane boundaries; batch sizes that leave partial rounds
+                                   (14, 14, 16, 4), (7, 7, 32, 6), (7, 7, 8, 41), (14, 14, 24, 37)])
 @pytest.mark.parametrize("affine", [True, False])
 def test_batchnorm_train_fwd_bwd(dt, act, shape, affine):
     _batchnorm_case(dt, act, shape, affine)
