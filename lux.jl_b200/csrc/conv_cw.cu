@@ -525,29 +525,58 @@ conv_cw_wgrad_kernel(const __grid_constant__ CUtensorMap tmG, const __grid_const
 struct CwReduce {
   int kW, kH, cin, cout, flip, fold, chunks, co_tiles, groups, pairs_per_group, splits;
 };
+// Sums the split-K partials and scatters them into dw. A block takes one 64-column slot of one partial row, i.e. one
+// (output channel, (tap, chunk) pair): thread x reads consecutive floats (coalesced, where the old per-output indexing
+// read 4 scattered bytes per split), the four y slices add splits y, y + 4, ... in ascending order and are then added
+// in slice order (a fixed order); the destination index is rebuilt from (pair, column).
+constexpr int kCwReduceSlices = 4;
 template <typename T>
-__global__ void __launch_bounds__(256) conv_cw_wgrad_reduce_kernel(T* __restrict__ dw, const float* __restrict__ partial,
-                                                                   const CwReduce g) {
-  const int64_t total = (int64_t)g.kW * g.kH * g.cin * g.cout;
+__global__ void __launch_bounds__(64 * kCwReduceSlices) conv_cw_wgrad_reduce_kernel(T* __restrict__ dw, const float* __restrict__ partial,
+                                                                                    const CwReduce g) {
+  __shared__ float part[kCwReduceSlices][64];
   const int bn = g.pairs_per_group * 64;
   const int64_t split_stride = (int64_t)g.co_tiles * g.groups * 128 * bn;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    int64_t r = i;
-    const int kw = (int)(r % g.kW); r /= g.kW;
-    const int kh = (int)(r % g.kH); r /= g.kH;
-    const int ci = (int)(r % g.cin);
-    const int co = (int)(r / g.cin);
-    const int tw = g.flip ? kw : g.kW - 1 - kw, th = g.flip ? kh : g.kH - 1 - kh;
-    int pair, col;
-    if (g.fold >= 2) { pair = th / g.fold; col = ((th % g.fold) * g.kW + tw) * g.cin + ci; }
-    else if (g.fold) { pair = th; col = tw * g.cin + ci; }
-    else { pair = (th * g.kW + tw) * g.chunks + ci / 64; col = ci % 64; }
-    const int grp = pair / g.pairs_per_group, slot = pair % g.pairs_per_group;
-    const int64_t off = (((int64_t)(grp * g.co_tiles + co / 128)) * 128 + co % 128) * bn + slot * 64 + col;
-    float s = 0.f;
-    for (int z = 0; z < g.splits; ++z) s += partial[z * split_stride + off];
-    dw[i] = from_f32<T>(s);
+  // blockIdx.x -> (slot, row, co tile, group), slot fastest
+  int64_t r = blockIdx.x;
+  const int slot = (int)(r % g.pairs_per_group); r /= g.pairs_per_group;
+  const int row = (int)(r % 128); r /= 128;
+  const int ct = (int)(r % g.co_tiles);
+  const int grp = (int)(r / g.co_tiles);
+  const int co = ct * 128 + row;
+  const int pair = grp * g.pairs_per_group + slot;
+  const int n_taps = g.fold >= 2 ? (g.kH + g.fold - 1) / g.fold : (g.fold ? g.kH : g.kW * g.kH);
+  if (co >= g.cout || pair >= n_taps * g.chunks) return;
+  const int col = threadIdx.x;
+  const int64_t off = (((int64_t)(grp * g.co_tiles + ct)) * 128 + row) * bn + slot * 64 + col;
+  float s = 0.f;
+  for (int z = threadIdx.y; z < g.splits; z += kCwReduceSlices) s += partial[z * split_stride + off];
+  part[threadIdx.y][col] = s;
+  __syncthreads();
+  if (threadIdx.y != 0) return;
+#pragma unroll
+  for (int y = 1; y < kCwReduceSlices; ++y) s += part[y][col];
+  int tw, th, ci;
+  if (g.fold >= 2) {
+    const int q = col / g.cin;
+    ci = col % g.cin;
+    tw = q % g.kW;
+    const int thm = q / g.kW;
+    th = pair * g.fold + thm;
+    if (thm >= g.fold || th >= g.kH) return;
+  } else if (g.fold) {
+    tw = col / g.cin;
+    ci = col % g.cin;
+    th = pair;
+    if (tw >= g.kW) return;
+  } else {
+    const int tap = pair / g.chunks;
+    ci = (pair % g.chunks) * 64 + col;
+    if (ci >= g.cin) return;
+    th = tap / g.kW;
+    tw = tap % g.kW;
   }
+  const int kw = g.flip ? tw : g.kW - 1 - tw, kh = g.flip ? th : g.kH - 1 - th;
+  dw[kw + (int64_t)g.kW * (kh + (int64_t)g.kH * (ci + (int64_t)g.cin * co))] = from_f32<T>(s);
 }
 
 // ----------------------------------------------------------------------------------------------
@@ -868,7 +897,7 @@ int32_t conv_cw_bwd(void* dw, void* dx, const void* x, const void* gy, const voi
        : pl.ppg == 3 ? launch(conv_cw_wgrad_kernel<3>, 3) : launch(conv_cw_wgrad_kernel<4>, 4);
     if (rc != LB2_OK) return rc;
     CwReduce rd{g.k[0], g.k[1], g.cin, g.cout, g.flip, fold, pl.chunks, pl.co_tiles, pl.groups, pl.ppg, pl.splits};
-    conv_cw_wgrad_reduce_kernel<__nv_bfloat16><<<flat_grid((int64_t)g.k[0] * g.k[1] * g.cin * g.cout), 256, 0, st>>>(
+    conv_cw_wgrad_reduce_kernel<__nv_bfloat16><<<(unsigned)((int64_t)pl.groups * pl.co_tiles * 128 * pl.ppg), dim3(64, kCwReduceSlices), 0, st>>>(
         (__nv_bfloat16*)dw, q.partial, rd);
     LB2_CHECK_LAUNCH("conv_cw_wgrad_reduce");
   }
