@@ -134,18 +134,21 @@ __global__ void __launch_bounds__(256) bn_reduce_kernel(float* __restrict__ part
   }
   float a = 0.f, q = 0.f;
   if constexpr (VEC) {
-    // A warp takes units of 128 vectors (4 per lane, all loads issued before any is used) of one
-    // sample's channel plane; the unit -> (sample, segment) division happens once per unit.
+    // A warp takes units of 32 * KV vectors (KV per lane and tensor, all loads issued before any is used: the pass is
+    // bound by memory latency, eight 16-byte loads per lane in flight either way) of one sample's channel plane; the
+    // unit -> (sample, segment) division happens once per unit, in 32 bits.
+    constexpr int KV = MODE == 0 ? 8 : 4;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const uint32_t upr = (uint32_t)((sv + 127) / 128);   // units per channel plane
+    const uint32_t upr = (uint32_t)((sv + 32 * KV - 1) / (32 * KV));   // units per channel plane
     const int64_t units = (b_end - b_begin) * (int64_t)upr;
     for (int64_t u = warp; u < units; u += 8) {
-      const int64_t b = b_begin + u / upr;
-      const int64_t v0 = (int64_t)(u % upr) * 128 + lane;
+      const uint32_t uq = (uint32_t)u / upr;          // a chunk of 2^32 units would span terabytes
+      const int64_t b = b_begin + uq;
+      const int64_t v0 = (int64_t)((uint32_t)u - uq * upr) * (32 * KV) + lane;
       const T* xr = x + (b * C + c) * S;
-      Vec16<T> xv[4], gv[4];
+      Vec16<T> xv[KV], gv[KV];
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
+      for (int k = 0; k < KV; ++k) {
         const int64_t v = v0 + k * 32;
         if (v < sv) {
           xv[k] = load16(xr + v * V);
@@ -153,7 +156,7 @@ __global__ void __launch_bounds__(256) bn_reduce_kernel(float* __restrict__ part
         }
       }
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
+      for (int k = 0; k < KV; ++k) {
         if (v0 + k * 32 < sv) {
           if constexpr (MODE == 0) {
 #pragma unroll
