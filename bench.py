@@ -786,11 +786,14 @@ def build_resnet18(L, torch, device, rank, batch, dtype):
     n_bn = sum(1 for n_ in names if n_.startswith("bn_scale"))
     rstats = {}
 
-    def bn(i, h, act):
-        c = params[i].shape[0]
-        rm, rv = rstats.setdefault(i, (torch.zeros(c, device=device, dtype=dtype), torch.ones(c, device=device, dtype=dtype)))
-        y, new, pb = L.rrule_batchnorm(h, params[i], params[i + 1], rm, rv, True, act, 0.1, 1e-5)
-        rstats[i] = new
+    def conv_bn(ic, ib, h, cdims, act):
+        """conv_norm of perf/resnet/resnet.jl:17-22: Conv without bias, then BatchNorm carrying the activation; the
+        statistics come from the convolution's epilogue where the general tensor-core path runs it. Pullback
+        Δ -> (∂weight, ∂x, ∂scale, ∂bias)."""
+        c = params[ib].shape[0]
+        rm, rv = rstats.setdefault(ib, (torch.zeros(c, device=device, dtype=dtype), torch.ones(c, device=device, dtype=dtype)))
+        y, new, pb = L.rrule_conv_batchnorm(act, params[ic], h, cdims, params[ib], params[ib + 1], rm, rv, 0.1, 1e-5)
+        rstats[ib] = new
         return y, pb
 
     x = cm(torch.randn(batch, 3, 224, 224, device=device, generator=gd).to(dtype))
@@ -800,41 +803,33 @@ def build_resnet18(L, torch, device, rank, batch, dtype):
 
     def forward_backward():
         grads = [None] * len(params)
-        h, pc = L.rrule_fused_conv("identity", params[stem[0]], x, None, cd(2, 3))
-        h, pn = bn(stem[1], h, "relu")
+        h, pstem = conv_bn(stem[0], stem[1], x, cd(2, 3), "relu")
         h, pp = L.rrule_maxpool(h, L.PoolDims.make((3, 3), (2, 2), (1, 1, 1, 1)))
         tape = []
         for blk in blocks:
             skip = h
-            a, pc1 = L.rrule_fused_conv("identity", params[blk["c1"]], h, None, cd(blk["stride"], 1))
-            a, pn1 = bn(blk["n1"], a, "relu")
-            a, pc2 = L.rrule_fused_conv("identity", params[blk["c2"]], a, None, cd(1, 1))
-            a, pn2 = bn(blk["n2"], a, "relu")
-            pcp = pnp = None
+            a, p1 = conv_bn(blk["c1"], blk["n1"], h, cd(blk["stride"], 1), "relu")
+            a, p2 = conv_bn(blk["c2"], blk["n2"], a, cd(1, 1), "relu")
+            pproj = None
             if "cp" in blk:
-                skip, pcp = L.rrule_fused_conv("identity", params[blk["cp"]], h, None, cd(blk["stride"], 0))
-                skip, pnp = bn(blk["np"], skip, "identity")
+                skip, pproj = conv_bn(blk["cp"], blk["np"], h, cd(blk["stride"], 0), "identity")
             h, padd = L.rrule_add_activation("relu", a, skip)
-            tape.append((blk, pc1, pn1, pc2, pn2, pcp, pnp, padd))
+            tape.append((blk, p1, p2, pproj, padd))
         pooled, ppool = L.rrule_meanpool(h, L.PoolDims.global_(h))          # (1, 1, 512, B)
         feat = pooled.reshape(512, batch)                                    # same bytes, Julia shape (512, B)
         y, pdense = L.rrule_fused_dense("identity", params[iWd], feat, params[ibd])
         loss, ploss = L.rrule_mse_loss(y, target)
         grads[iWd], dfeat, grads[ibd] = pdense(ploss())
         dh = ppool(dfeat.reshape(1, 1, 512, batch))
-        for blk, pc1, pn1, pc2, pn2, pcp, pnp, padd in reversed(tape):
+        for blk, p1, p2, pproj, padd in reversed(tape):
             da, dskip = padd(dh)
-            da, grads[blk["n2"]], grads[blk["n2"] + 1] = pn2(da)
-            grads[blk["c2"]], da, _ = pc2(da)
-            da, grads[blk["n1"]], grads[blk["n1"] + 1] = pn1(da)
-            grads[blk["c1"]], dmain, _ = pc1(da)
-            if pcp is not None:
-                ds, grads[blk["np"]], grads[blk["np"] + 1] = pnp(dskip)
-                grads[blk["cp"]], dskip, _ = pcp(ds)
+            grads[blk["c2"]], da, grads[blk["n2"]], grads[blk["n2"] + 1] = p2(da)
+            grads[blk["c1"]], dmain, grads[blk["n1"]], grads[blk["n1"] + 1] = p1(da)
+            if pproj is not None:
+                grads[blk["cp"]], dskip, grads[blk["np"]], grads[blk["np"] + 1] = pproj(dskip)
             dh = L.add_activation("identity", dmain, dskip)
         dh = pp(dh)
-        dh, grads[stem[1]], grads[stem[1] + 1] = pn(dh)
-        grads[stem[0]], _, _ = pc(dh, need_dx=False)
+        grads[stem[0]], _, grads[stem[1]], grads[stem[1] + 1] = pstem(dh, need_dx=False)
         return loss, grads
 
     return params, forward_backward, n_bn

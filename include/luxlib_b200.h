@@ -180,6 +180,16 @@ LB2_API int32_t lb2_conv_fwd(void* y, void* preact, const void* x, const void* w
 /* 1 when lb2_conv_fwd (without LB2_FLAG_FORCE_SIMT, on 16-byte aligned arrays) leaves a reusable copy of x at the
  * start of its workspace for this geometry (see LB2_FLAG_X_COPY_GIVEN), else 0. */
 LB2_API int32_t lb2_conv_fwd_leaves_x_copy(const lb2_conv_desc* d, int32_t dtype);
+/* conv -> BatchNorm(act) pairs (perf/resnet/resnet.jl:17-22: Conv without bias, then BatchNorm carrying the
+ * activation): the convolution (identity activation, no bias) that also returns per output channel the sums of the
+ * stored y and of y^2 (fp32 [cout][2]) — BatchNorm's statistics pass without reading y back. On the general bf16
+ * tensor-core path the sums are formed in the convolution's epilogue; elsewhere a separate pass over y forms them.
+ * lb2_conv_fwd_sums_is_fused() == 1 says that the epilogue form applies AND pays (a contraction of at least 16
+ * k-blocks of 64 hides it); callers should keep the plain conv + BatchNorm pair otherwise. The workspace keeps lb2_conv_fwd's layout (LB2_FLAG_X_COPY_GIVEN applies). */
+LB2_API int32_t lb2_conv_fwd_sums_is_fused(const lb2_conv_desc* d, int32_t dtype);
+LB2_API size_t lb2_conv_fwd_sums_workspace_bytes(const lb2_conv_desc* d, int32_t dtype);
+LB2_API int32_t lb2_conv_fwd_sums(void* y, float* sums, const void* x, const void* w, const lb2_conv_desc* d, int32_t dtype,
+                                  uint32_t flags, void* workspace, size_t workspace_bytes, void* stream);
 LB2_API size_t lb2_conv_bwd_workspace_bytes(const lb2_conv_desc* d, int32_t dtype, int32_t act);
 LB2_API int32_t lb2_conv_bwd(void* dw, void* dx, void* db, const void* dy, const void* out,
                      const void* preact, const void* x, const void* w, const lb2_conv_desc* d,
@@ -225,6 +235,18 @@ LB2_API int32_t lb2_batchnorm_fwd_train_static(void* y, float* save_mean, float*
                                                double momentum, double eps, int32_t dtype, int32_t act,
                                                void* stream);
 /* Inference forward with given statistics (lib/LuxLib/src/impl/normalization.jl:136-143). */
+/* Per-channel sums of x and x^2 over the (S, C, B) view (fp32 [C][2]), and the training forward that starts from
+ * such sums instead of its own statistics pass: mean = s1/n, var = s2/n - mean^2 (biased), then exactly
+ * lb2_batchnorm_fwd_train's normalisation, saved statistics and running-statistics update. Workspace as for
+ * lb2_batchnorm_fwd_train. */
+LB2_API size_t lb2_channel_sums_workspace_bytes(int64_t S, int64_t C, int64_t B);
+LB2_API int32_t lb2_channel_sums(float* sums, const void* x, int64_t S, int64_t C, int64_t B, int32_t dtype,
+                                 void* workspace, size_t workspace_bytes, void* stream);
+LB2_API int32_t lb2_batchnorm_fwd_train_sums(void* y, float* save_mean, float* save_invstd, void* new_rmean,
+                                             void* new_rvar, const void* x, const void* gamma, const void* beta,
+                                             const void* rmean, const void* rvar, const float* sums, int64_t S,
+                                             int64_t C, int64_t B, double momentum, double eps, int32_t dtype,
+                                             int32_t act, void* workspace, size_t workspace_bytes, void* stream);
 LB2_API int32_t lb2_batchnorm_fwd_infer(void* y, const void* x, const void* gamma, const void* beta,
                                 const void* rmean, const void* rvar, int64_t S, int64_t C, int64_t B,
                                 double eps, int32_t dtype, int32_t act, void* stream);

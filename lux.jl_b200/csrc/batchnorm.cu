@@ -357,6 +357,62 @@ __global__ void bn_finalize_fwd_kernel(float* __restrict__ save_mean, float* __r
   }
 }
 
+// Forward finalise from plain per-channel sums (sum of x, sum of x^2 over S*B elements), as a convolution's epilogue
+// delivers them: mean = s1/n, var = s2/n - mean^2 in fp64 (the sums are of values of a few units at most; a tensor
+// whose mean dwarfs its deviation should take the shifted-sum pass instead).
+template <typename T>
+__global__ void bn_finalize_sums_kernel(float* __restrict__ save_mean, float* __restrict__ save_inv, float* __restrict__ coef,
+                                        T* __restrict__ new_rmean, T* __restrict__ new_rvar, const T* __restrict__ rmean,
+                                        const T* __restrict__ rvar, const T* __restrict__ gamma, const T* __restrict__ beta,
+                                        const float* __restrict__ sums, int64_t S, int64_t C, int64_t B, float momentum, float eps) {
+  const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const double n = (double)S * (double)B;
+  const double mean_d = (double)sums[c * 2] / n;
+  double var_d = (double)sums[c * 2 + 1] / n - mean_d * mean_d;
+  if (var_d < 0.0) var_d = 0.0;
+  const float mean = (float)mean_d, var = (float)var_d;
+  const float inv = 1.f / sqrtf(var + eps);
+  save_mean[c] = mean;
+  save_inv[c] = inv;
+  float gp = inv, bp = -mean * inv;
+  if (gamma) { gp = to_f32(gamma[c]) * inv; bp = to_f32(beta[c]) - mean * gp; }
+  coef[c * 4 + 0] = gp;
+  coef[c * 4 + 1] = bp;
+  if (rmean) {
+    const float nf = (float)n;
+    const float m1 = momentum, m2 = momentum * nf / (nf - 1.f), m3 = 1.f - m1;
+    new_rmean[c] = from_f32<T>(m3 * to_f32(rmean[c]) + m1 * mean);
+    new_rvar[c] = from_f32<T>(m3 * to_f32(rvar[c]) + m2 * var);
+  }
+}
+
+// Plain per-channel sums of x and x^2 (fp32 [C][2]) for callers that have no fused producer of them: grid (C, chunks),
+// block sums, then lb2_channel_sums finishes over the chunks in order.
+template <typename T>
+__global__ void __launch_bounds__(256) channel_sums_kernel(float* __restrict__ partial, const T* __restrict__ x, int64_t S, int64_t C,
+                                                           int64_t B, int64_t rows_per_chunk) {
+  __shared__ float red[32];
+  const int64_t c = blockIdx.x;
+  const int64_t b0 = (int64_t)blockIdx.y * rows_per_chunk, b1 = min(B, b0 + rows_per_chunk);
+  float a = 0.f, q = 0.f;
+  for (int64_t b = b0; b < b1; ++b) {
+    const T* xr = x + (b * C + c) * S;
+    for (int64_t i = threadIdx.x; i < S; i += blockDim.x) { const float v = to_f32(xr[i]); a += v; q = fmaf(v, v, q); }
+  }
+  a = block_sum(a, red);
+  q = block_sum(q, red);
+  if (threadIdx.x == 0) { partial[((int64_t)blockIdx.y * C + c) * 2] = a; partial[((int64_t)blockIdx.y * C + c) * 2 + 1] = q; }
+}
+__global__ void channel_sums_finish_kernel(float* __restrict__ sums, const float* __restrict__ partial, int64_t C, int chunks) {
+  const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  double a = 0.0, q = 0.0;
+  for (int k = 0; k < chunks; ++k) { a += (double)partial[((int64_t)k * C + c) * 2]; q += (double)partial[((int64_t)k * C + c) * 2 + 1]; }
+  sums[c * 2] = (float)a;
+  sums[c * 2 + 1] = (float)q;
+}
+
 template <typename T>
 __global__ void bn_finalize_bwd_kernel(T* __restrict__ dgamma, T* __restrict__ dbeta, float* __restrict__ coef,
                                        const T* __restrict__ gamma, const float* __restrict__ save_mean,
@@ -1043,6 +1099,62 @@ int32_t lb2_batchnorm_fwd_train(void* y, float* save_mean, float* save_invstd, v
         save_mean, save_invstd, coef, (T*)new_rmean, (T*)new_rvar, (const T*)rmean, (const T*)rvar, (const T*)gamma,
         (const T*)beta, (const T*)x, partial, S, C, B, used, (float)momentum, (float)eps);
     LB2_CHECK_LAUNCH("batchnorm finalise");
+    LB2_DISPATCH_ACT3(act, {
+      bn_apply_launch<T, 0, ACT, false>((T*)y, (const T*)x, nullptr, coef, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, S, C, B, (float)eps, act, st);
+    });
+    LB2_CHECK_LAUNCH("batchnorm apply");
+  });
+  return LB2_OK;
+}
+
+size_t lb2_channel_sums_workspace_bytes(int64_t S, int64_t C, int64_t B) { return bn_ws_bytes(S, C, B); }
+
+int32_t lb2_channel_sums(float* sums, const void* x, int64_t S, int64_t C, int64_t B, int32_t dtype, void* workspace,
+                         size_t workspace_bytes, void* stream) {
+  LB2_REQUIRE(S >= 0 && C >= 0 && B >= 0, LB2_BAD_SHAPE, "bad extent");
+  LB2_REQUIRE(valid_dtype(dtype), LB2_UNSUPPORTED_DTYPE, "dtype %d not supported", (int)dtype);
+  if (C == 0) return LB2_OK;
+  LB2_REQUIRE(sums != nullptr, LB2_BAD_ARG, "sums is null");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (S == 0 || B == 0) {
+    cudaError_t e = cudaMemsetAsync(sums, 0, (size_t)C * 2 * sizeof(float), st);
+    LB2_REQUIRE(e == cudaSuccess, LB2_LAUNCH_FAIL, "channel_sums: %s", cudaGetErrorString(e));
+    return LB2_OK;
+  }
+  LB2_REQUIRE(x != nullptr, LB2_BAD_ARG, "x is null");
+  LB2_REQUIRE(workspace && workspace_bytes >= bn_ws_bytes(S, C, B), LB2_WORKSPACE_TOO_SMALL, "workspace of %zu bytes needed", bn_ws_bytes(S, C, B));
+  LB2_REQUIRE(aligned_to(workspace, 16), LB2_BAD_ALIGN, "workspace must be 16-byte aligned");
+  const BnPlan p = bn_plan(S > 1 ? S : 2, C, B);        // the S > 1 plan: chunks over the batch, at most kBnMaxChunks
+  float* partial = static_cast<float*>(workspace);
+  LB2_DISPATCH_DTYPE(dtype, {
+    channel_sums_kernel<T><<<dim3((unsigned)C, (unsigned)p.chunks), 256, 0, st>>>(partial, (const T*)x, S, C, B, p.rows_per_chunk);
+  });
+  LB2_CHECK_LAUNCH("channel_sums");
+  channel_sums_finish_kernel<<<(unsigned)((C + 127) / 128), 128, 0, st>>>(sums, partial, C, p.chunks);
+  LB2_CHECK_LAUNCH("channel_sums finish");
+  return LB2_OK;
+}
+
+int32_t lb2_batchnorm_fwd_train_sums(void* y, float* save_mean, float* save_invstd, void* new_rmean, void* new_rvar, const void* x,
+                                     const void* gamma, const void* beta, const void* rmean, const void* rvar, const float* sums,
+                                     int64_t S, int64_t C, int64_t B, double momentum, double eps, int32_t dtype, int32_t act,
+                                     void* workspace, size_t workspace_bytes, void* stream) {
+  int32_t rc = check_bn(y, x, gamma, beta, S, C, B, dtype, act);
+  if (rc != LB2_OK) return rc;
+  if (S == 0 || C == 0 || B == 0) return LB2_OK;
+  LB2_REQUIRE(save_mean && save_invstd && sums, LB2_BAD_ARG, "save_mean / save_invstd / sums are null");
+  LB2_REQUIRE((rmean == nullptr) == (rvar == nullptr), LB2_BAD_ARG, "running mean and variance must both be given or both be null");
+  LB2_REQUIRE(!rmean || (new_rmean && new_rvar), LB2_BAD_ARG, "outputs for the updated running statistics are null");
+  LB2_REQUIRE(workspace && workspace_bytes >= bn_ws_bytes(S, C, B), LB2_WORKSPACE_TOO_SMALL, "workspace of %zu bytes needed", bn_ws_bytes(S, C, B));
+  LB2_REQUIRE(aligned_to(workspace, 16), LB2_BAD_ALIGN, "workspace must be 16-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const BnPlan p = bn_plan(S, C, B);
+  float* coef = (float*)workspace + (size_t)p.chunks * C * 2;
+  LB2_DISPATCH_DTYPE(dtype, {
+    bn_finalize_sums_kernel<T><<<(unsigned)((C + 127) / 128), 128, 0, st>>>(save_mean, save_invstd, coef, (T*)new_rmean, (T*)new_rvar,
+                                                                            (const T*)rmean, (const T*)rvar, (const T*)gamma, (const T*)beta,
+                                                                            sums, S, C, B, (float)momentum, (float)eps);
+    LB2_CHECK_LAUNCH("batchnorm finalise (from sums)");
     LB2_DISPATCH_ACT3(act, {
       bn_apply_launch<T, 0, ACT, false>((T*)y, (const T*)x, nullptr, coef, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, S, C, B, (float)eps, act, st);
     });

@@ -117,6 +117,53 @@ int32_t lb2_conv_fwd_leaves_x_copy(const lb2_conv_desc* d, int32_t dtype) {
   return conv_route(g, dtype) == 2 ? 1 : 0;
 }
 
+// The epilogue sums cost about a thousand instructions per warp and tile; they disappear behind the tile's MMAs only
+// when the contraction is long enough (16 k-blocks of 64: a 3x3 filter over 128 input channels and up). Shorter
+// contractions (1x1 projections, the folded stem) are faster with BatchNorm's own statistics pass.
+int32_t lb2_conv_fwd_sums_is_fused(const lb2_conv_desc* d, int32_t dtype) {
+  ConvGeom g;
+  if (!valid_dtype(dtype) || make_geom(d, &g) != LB2_OK || y_numel(g) == 0) return 0;
+  if (conv_route(g, dtype) != 2) return 0;
+  return (int64_t)g.k[0] * g.k[1] * ((g.cin + 63) / 64) >= 16 ? 1 : 0;
+}
+
+size_t lb2_conv_fwd_sums_workspace_bytes(const lb2_conv_desc* d, int32_t dtype) {
+  ConvGeom g;
+  if (!valid_dtype(dtype) || make_geom(d, &g) != LB2_OK) return 0;
+  const size_t conv = align_up(lb2_conv_fwd_workspace_bytes(d, dtype), 1024);
+  if (conv_route(g, dtype) == 2) return conv;
+  return conv + lb2_channel_sums_workspace_bytes(y_spatial(g), g.cout, g.batch);
+}
+
+int32_t lb2_conv_fwd_sums(void* y, float* sums, const void* x, const void* w, const lb2_conv_desc* d, int32_t dtype, uint32_t flags,
+                          void* workspace, size_t workspace_bytes, void* stream) {
+  LB2_REQUIRE(valid_dtype(dtype), LB2_UNSUPPORTED_DTYPE, "dtype %d not supported", (int)dtype);
+  LB2_REQUIRE(sums != nullptr, LB2_BAD_ARG, "sums is null");
+  ConvGeom g;
+  int32_t rc = make_geom(d, &g);
+  if (rc != LB2_OK) return rc;
+  if (g.cout == 0) return LB2_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (y_numel(g) == 0) {
+    cudaMemsetAsync(sums, 0, (size_t)g.cout * 2 * sizeof(float), st);
+    return LB2_OK;
+  }
+  LB2_REQUIRE(workspace_bytes >= lb2_conv_fwd_sums_workspace_bytes(d, dtype), LB2_WORKSPACE_TOO_SMALL, "workspace of %zu bytes needed",
+              lb2_conv_fwd_sums_workspace_bytes(d, dtype));
+  const bool fused = !(flags & LB2_FLAG_FORCE_SIMT) && conv_route(g, dtype) == 2;
+  if (fused) {
+    LB2_REQUIRE(y && x && w, LB2_BAD_ARG, "null tensor pointer");
+    LB2_REQUIRE(workspace != nullptr && aligned_to(workspace, 256), LB2_BAD_ALIGN, "workspace must be 256-byte aligned");
+    LB2_REQUIRE(aligned_to(y, 2) && aligned_to(x, 2) && aligned_to(w, 2), LB2_BAD_ALIGN, "pointer not aligned to the element size");
+    return conv_cw_fwd(y, nullptr, x, w, nullptr, g, LB2_ACT_IDENTITY, workspace, st, sums);
+  }
+  const size_t conv = align_up(lb2_conv_fwd_workspace_bytes(d, dtype), 1024);
+  rc = lb2_conv_fwd(y, nullptr, x, w, nullptr, d, dtype, LB2_ACT_IDENTITY, flags, workspace, conv, stream);
+  if (rc != LB2_OK) return rc;
+  uint8_t* rest = static_cast<uint8_t*>(workspace) + conv;
+  return lb2_channel_sums(sums, y, y_spatial(g), g.cout, g.batch, dtype, rest, workspace_bytes - conv, stream);
+}
+
 size_t lb2_conv_bwd_workspace_bytes(const lb2_conv_desc* d, int32_t dtype, int32_t act) {
   ConvGeom g;
   if (!valid_dtype(dtype) || make_geom(d, &g) != LB2_OK) return 0;

@@ -32,7 +32,7 @@ bool conv_cw_supported(const ConvGeom& g, int32_t dtype);
 size_t conv_cw_fwd_workspace_bytes(const ConvGeom& g);
 size_t conv_cw_bwd_workspace_bytes(const ConvGeom& g);
 int32_t conv_cw_fwd(void* y, void* preact, const void* x, const void* w, const void* bias, const ConvGeom& g, int32_t act,
-                    void* ws, cudaStream_t st);
+                    void* ws, cudaStream_t st, float* sums = nullptr);
 // both gradients (either of dw, dx may be null) from one channel-innermost copy of gy
 int32_t conv_cw_bwd(void* dw, void* dx, const void* x, const void* gy, const void* w, const ConvGeom& g, void* ws,
                     cudaStream_t st, bool x_is_copy = false);

@@ -199,6 +199,7 @@ struct CwFwdParams {
   const void* bias;
   int32_t act;
   unsigned int* status;
+  float* sums_partial;         // SUMS kernels: [gridDim.x][BN][2] per-CTA sums of y and y^2 per channel of the CTA's column tile
   int16_t kb_dw[kCwMaxKb], kb_dh[kCwMaxKb];   // input start coordinate offsets of the k-block's tap
   int16_t kb_c0[kCwMaxKb];                    // first contracted channel
   int32_t kb_k0[kCwMaxKb];                    // column of the packed filter
@@ -206,7 +207,28 @@ struct CwFwdParams {
 
 constexpr uint32_t kDescHiSw128 = (uint32_t)((1024u >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
 
-template <int BN, int ACT>
+// Sum over the 32 lanes of a warp of v[j], for each j: lane j ends up with the sum of everybody's v[j] (a butterfly
+// that halves the values a lane carries at every step: 31 shuffles for 32 sums instead of 160; fixed order).
+__device__ __forceinline__ float warp_transpose_sum(float (&v)[32], int lane) {
+#pragma unroll
+  for (int k = 16; k >= 1; k >>= 1) {
+    const bool up = (lane & k) != 0;
+#pragma unroll
+    for (int i = 0; i < k; ++i) {
+      const float send = up ? v[i] : v[i + k];
+      const float keep = up ? v[i + k] : v[i];
+      v[i] = keep + __shfl_xor_sync(0xffffffffu, send, k);
+    }
+  }
+  return v[0];
+}
+
+// SUMS: the epilogue also forms, per output channel, the sums of the STORED values y and of y^2 over every position
+// this CTA writes (what a BatchNorm statistics pass over y would read back from memory). The grid is a multiple of
+// tiles_n, so a CTA always works on the same column tile and a lane can keep "its" channel's running sums in
+// registers (lane j of an epilogue warp owns channel j of each 32-column chunk of the warp's half); at the end the
+// four warps that share the channels (the TMEM lane quarters) are added in order and the CTA writes one partial row.
+template <int BN, int ACT, bool SUMS = false>
 __global__ void __launch_bounds__(kCwThreads, 1)
 conv_cw_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
                    const __grid_constant__ CwFwdParams p) {
@@ -316,6 +338,9 @@ conv_cw_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
     const int pos = q * 32 + lane;
     const int iw = pos % p.BW, ih = (pos / p.BW) % p.BH, ii = pos / (p.BW * p.BH);
     bool ok = true;
+    float run_s[COLS / 32], run_q[COLS / 32];          // SUMS: this lane's channel of every chunk
+#pragma unroll
+    for (int c = 0; c < COLS / 32; ++c) { run_s[c] = 0.f; run_q[c] = 0.f; }
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       int tn, tw, th, ti;
       tile_coords(tile, &tn, &tw, &th, &ti);
@@ -329,34 +354,88 @@ conv_cw_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
                            plane * ((int64_t)p.n_out * img + col0);
       __nv_bfloat16* yp = Y + base;
       __nv_bfloat16* pp = P != nullptr ? P + base : nullptr;
-#pragma unroll 1
-      for (int c = 0; c < COLS / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + half * COLS + c * 32, r);
-        tmem_ld_wait();
-        if (live) {
+      if constexpr (SUMS) {
+#pragma unroll
+        for (int c = 0; c < COLS / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + half * COLS + c * 32, r);
+          tmem_ld_wait();
+          float sv[32], sq[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
-            if (c * 32 + j < lim) {
+            float stored = 0.f;
+            if (live && c * 32 + j < lim) {
               float v = __uint_as_float(r[j]);
               if (bias != nullptr) v += __bfloat162float(bias[col0 + c * 32 + j]);
-              if (pp != nullptr) pp[j * plane] = __float2bfloat16_rn(v);
-              yp[j * plane] = __float2bfloat16_rn(act_apply_any<ACT, true>(p.act, v));
+              const __nv_bfloat16 o = __float2bfloat16_rn(act_apply_any<ACT, true>(p.act, v));
+              yp[j * plane] = o;
+              stored = __bfloat162float(o);
+            }
+            sv[j] = stored;
+            sq[j] = stored * stored;
+          }
+          run_s[c] += warp_transpose_sum(sv, lane);
+          run_q[c] += warp_transpose_sum(sq, lane);
+          yp += 32 * plane;
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < COLS / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + half * COLS + c * 32, r);
+          tmem_ld_wait();
+          if (live) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (c * 32 + j < lim) {
+                float v = __uint_as_float(r[j]);
+                if (bias != nullptr) v += __bfloat162float(bias[col0 + c * 32 + j]);
+                if (pp != nullptr) pp[j * plane] = __float2bfloat16_rn(v);
+                yp[j * plane] = __float2bfloat16_rn(act_apply_any<ACT, true>(p.act, v));
+              }
             }
           }
+          yp += 32 * plane;
+          if (pp != nullptr) pp += 32 * plane;
         }
-        yp += 32 * plane;
-        if (pp != nullptr) pp += 32 * plane;
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[acc]);
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
     }
+    if constexpr (SUMS) {
+      // every tile of this CTA is finished (its loads consumed, its accumulators read), so the operand ring is free:
+      // the eight warps park their sums there, [q][half][chunk][lane] pairs
+      float2* park = reinterpret_cast<float2*>(smem_gen);
+#pragma unroll
+      for (int c = 0; c < COLS / 32; ++c) park[((q * 2 + half) * (COLS / 32) + c) * 32 + lane] = make_float2(run_s[c], run_q[c]);
+    }
   }
 
   tc_fence_before();
   __syncthreads();
+  if constexpr (SUMS) {
+    constexpr int COLS = BN / 2;
+    if (warp >= 4 && (warp & 3) == 0) {          // one warp per half adds the four lane quarters in order
+      const int half = (warp - 4) >> 2;
+      const float2* park = reinterpret_cast<const float2*>(smem_gen);
+      float* out = p.sums_partial + (int64_t)blockIdx.x * BN * 2;
+#pragma unroll
+      for (int c = 0; c < COLS / 32; ++c) {
+        float sum = 0.f, sqs = 0.f;
+#pragma unroll
+        for (int qi = 0; qi < 4; ++qi) {
+          const float2 v = park[((qi * 2 + half) * (COLS / 32) + c) * 32 + lane];
+          sum += v.x;
+          sqs += v.y;
+        }
+        const int ch = half * COLS + c * 32 + lane;
+        out[ch * 2] = sum;
+        out[ch * 2 + 1] = sqs;
+      }
+    }
+  }
   if (warp == 2) {
     if (*reinterpret_cast<volatile unsigned int*>(p.status) != 0) drain_after_abort();
     tc_fence_after();
@@ -684,12 +763,18 @@ int32_t cw_copy_x(void* xc, const void* x, const ConvGeom& g, const CwCopy& c, c
 }
 
 template <int BN>
-int32_t cw_launch_fwd(const CUtensorMap& mX, const CUtensorMap& mW, const CwFwdParams& p, int32_t act, cudaStream_t st) {
+int32_t cw_launch_fwd(const CUtensorMap& mX, const CUtensorMap& mW, const CwFwdParams& p, int32_t act, cudaStream_t st, int* grid_out) {
   constexpr int STAGE_BYTES = kCwBM * 128 + BN * 128;
   constexpr int STAGES = (200 * 1024) / STAGE_BYTES > 8 ? 8 : (200 * 1024) / STAGE_BYTES;
   constexpr int smem = STAGES * STAGE_BYTES + 1024 + 256;
   const int tiles = p.tiles_w * p.tiles_h * p.tiles_i * p.tiles_n;
-  const int grid = tiles < sm_count() ? tiles : sm_count();
+  int grid = tiles < sm_count() ? tiles : sm_count();
+  if (p.sums_partial != nullptr) {
+    // a multiple of tiles_n (tiles is one): blockIdx.x % tiles_n is then the column tile of every tile of the CTA
+    grid = grid / p.tiles_n * p.tiles_n;
+    if (grid < p.tiles_n) grid = p.tiles_n;
+  }
+  if (grid_out != nullptr) *grid_out = grid;
   auto launch = [&](auto kernel) -> int32_t {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return fail(LB2_LAUNCH_FAIL, "conv_cw: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
@@ -697,6 +782,10 @@ int32_t cw_launch_fwd(const CUtensorMap& mX, const CUtensorMap& mW, const CwFwdP
     LB2_CHECK_LAUNCH("conv_cw_fwd");
     return LB2_OK;
   };
+  if (p.sums_partial != nullptr) {
+    if (act == LB2_ACT_IDENTITY) return launch(conv_cw_fwd_kernel<BN, LB2_ACT_IDENTITY, true>);
+    return launch(conv_cw_fwd_kernel<BN, -1, true>);
+  }
   switch (act) {
     case LB2_ACT_IDENTITY: return launch(conv_cw_fwd_kernel<BN, LB2_ACT_IDENTITY>);
     case LB2_ACT_RELU: return launch(conv_cw_fwd_kernel<BN, LB2_ACT_RELU>);
@@ -704,12 +793,27 @@ int32_t cw_launch_fwd(const CUtensorMap& mX, const CUtensorMap& mW, const CwFwdP
   }
 }
 
+// sums[ch][0..1] = sum over the CTAs of column tile ch / bn (ascending block index) of their partial rows
+__global__ void __launch_bounds__(128) cw_sums_finish_kernel(float* __restrict__ sums, const float* __restrict__ partial, int grid, int tiles_n,
+                                                             int bn, int cout) {
+  const int ch = blockIdx.x * blockDim.x + threadIdx.x;
+  if (ch >= cout) return;
+  const int tn = ch / bn, j = ch % bn;
+  double a = 0.0, q = 0.0;
+  for (int k = tn; k < grid; k += tiles_n) {
+    a += (double)partial[((int64_t)k * bn + j) * 2];
+    q += (double)partial[((int64_t)k * bn + j) * 2 + 1];
+  }
+  sums[ch * 2] = (float)a;
+  sums[ch * 2 + 1] = (float)q;
+}
+
 // One implicit-GEMM launch: grid of OW x OH x NI positions, n_out channels, the given taps of the packed filter.
 struct CwTap { int dw, dh, tap_index; };
 int32_t cw_run_gemm(void* out, void* preact, const void* bias, int32_t act, const void* src_c, int Cp_src, int Wsrc, int Hsrc,
                     int NI, int k_chunks, const void* wp, int wp_rows, int wp_cols, const CwTap* taps, int n_taps,
                     int OW, int OH, int sw, int sh, int n_out, int FW, int FH, int ow_step, int ow_off, int oh_step, int oh_off,
-                    cudaStream_t st) {
+                    cudaStream_t st, float* sums = nullptr, float* sums_partial = nullptr) {
   CwFwdParams p{};
   p.OW = OW; p.OH = OH; p.NI = NI;
   cw_tile_box(OW, OH, NI, &p.BW, &p.BH, &p.BI);
@@ -729,14 +833,19 @@ int32_t cw_run_gemm(void* out, void* preact, const void* bias, int32_t act, cons
   p.FW = FW; p.FH = FH; p.ow_step = ow_step; p.ow_off = ow_off; p.oh_step = oh_step; p.oh_off = oh_off;
   p.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(kCwBM >> 4) << 24);
   p.y = out; p.preact = preact; p.bias = bias; p.act = act;
+  p.sums_partial = sums != nullptr ? sums_partial : nullptr;
   p.status = device_status_word();
   LB2_REQUIRE(p.status != nullptr, LB2_LAUNCH_FAIL, "conv_cw: device status word unavailable");
   CUtensorMap mX, mW;
   if (!cw_map(&mX, src_c, Cp_src, Wsrc, Hsrc, NI, p.BW, p.BH, p.BI, sw, sh) || !cw_map_2d(&mW, wp, wp_cols, wp_rows, 64, bn))
     return fail(LB2_LAUNCH_FAIL, "conv_cw: cuTensorMapEncodeTiled failed");
-  if (bn == 64) return cw_launch_fwd<64>(mX, mW, p, act, st);
-  if (bn == 128) return cw_launch_fwd<128>(mX, mW, p, act, st);
-  return cw_launch_fwd<256>(mX, mW, p, act, st);
+  int grid = 0;
+  const int32_t rc = bn == 64 ? cw_launch_fwd<64>(mX, mW, p, act, st, &grid)
+                   : bn == 128 ? cw_launch_fwd<128>(mX, mW, p, act, st, &grid) : cw_launch_fwd<256>(mX, mW, p, act, st, &grid);
+  if (rc != LB2_OK || sums == nullptr) return rc;
+  cw_sums_finish_kernel<<<(unsigned)((n_out + 127) / 128), 128, 0, st>>>(sums, sums_partial, grid, p.tiles_n, bn, n_out);
+  LB2_CHECK_LAUNCH("conv_cw channel sums");
+  return LB2_OK;
 }
 
 }  // namespace
@@ -758,13 +867,18 @@ bool conv_cw_supported(const ConvGeom& g, int32_t dtype) {
   return tensor_map_encoder() != nullptr;
 }
 
+// per-CTA rows of the channel-sum partials: at most one CTA per SM, 256 channels, two floats
+static size_t cw_sums_partial_bytes() { return align_up((size_t)sm_count() * 256 * 2 * sizeof(float), 1024); }
+
 size_t conv_cw_fwd_workspace_bytes(const ConvGeom& g) {
   const int fold = cw_fold(g);
-  return cw_copy_of_x(g).bytes + cw_packed_bytes(g.cout, fold ? cw_fold_taps(g, fold) : g.k[0] * g.k[1], fold ? 1 : (g.cin + 63) / 64);
+  return align_up(cw_copy_of_x(g).bytes + cw_packed_bytes(g.cout, fold ? cw_fold_taps(g, fold) : g.k[0] * g.k[1], fold ? 1 : (g.cin + 63) / 64), 1024) +
+         cw_sums_partial_bytes();
 }
 
+// `sums` (fp32 [cout][2], may be null): per output channel the sums of the stored y and of y^2, formed in the epilogue
 int32_t conv_cw_fwd(void* y, void* preact, const void* x, const void* w, const void* bias, const ConvGeom& g, int32_t act,
-                    void* ws_, cudaStream_t st) {
+                    void* ws_, cudaStream_t st, float* sums) {
   uint8_t* ws = static_cast<uint8_t*>(ws_);
   const int fold = cw_fold(g);
   const CwCopy xc = cw_copy_of_x(g);
@@ -785,8 +899,10 @@ int32_t conv_cw_fwd(void* y, void* preact, const void* x, const void* w, const v
     else if (fold) taps[t] = CwTap{0, t * g.dil[1] - g.pad_lo[1], t};
     else taps[t] = CwTap{(t % g.k[0]) * g.dil[0] - g.pad_lo[0], (t / g.k[0]) * g.dil[1] - g.pad_lo[1], t};
   }
+  float* sums_partial = reinterpret_cast<float*>(ws + align_up(xc.bytes + cw_packed_bytes(g.cout, n_taps, pk.chunks), 1024));
   return cw_run_gemm(y, preact, bias, act, ws, xc.Cp, xc.W, xc.H, g.batch, pk.chunks, wp, pk.n_rows, pk.k_total, taps, n_taps,
-                     g.out[0], g.out[1], fold ? 1 : g.stride[0], fold >= 2 ? 1 : g.stride[1], g.cout, g.out[0], g.out[1], 1, 0, 1, 0, st);
+                     g.out[0], g.out[1], fold ? 1 : g.stride[0], fold >= 2 ? 1 : g.stride[1], g.cout, g.out[0], g.out[1], 1, 0, 1, 0, st,
+                     sums, sums_partial);
 }
 
 // ---- backward ---------------------------------------------------------------------------------------

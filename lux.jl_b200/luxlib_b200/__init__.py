@@ -9,7 +9,7 @@ from .ops import (ConvDims, PoolDims, add_activation, batchnorm, bias_activation
                   needs_preactivation, rrule_add_activation, rrule_batchnorm, rrule_bias_activation, rrule_fused_conv,
                   rrule_fused_dense, rrule_groupnorm, rrule_instancenorm, rrule_layernorm, rrule_maxpool, rrule_meanpool, mse_loss,
                   rrule_mse_loss, conv_transpose_bias_activation, rrule_conv_transpose, conv_transpose_output_size, scale, rrule_scale, cross_entropy_loss, rrule_cross_entropy_loss, batched_matmul, rrule_batched_matmul,
-                  scaled_dot_product_attention, rrule_scaled_dot_product_attention)
+                  scaled_dot_product_attention, rrule_scaled_dot_product_attention, rrule_conv_batchnorm)
 
 __all__ = [
     "ArgumentError", "DimensionMismatch", "LuxLibB200Error", "ConvDims", "PoolDims",
@@ -18,5 +18,5 @@ __all__ = [
     "bias_activation", "add_activation", "rrule_add_activation", "fast_activation", "matmul", "default_epsilon", "needs_preactivation",
     "rrule_fused_dense", "rrule_fused_conv", "rrule_batchnorm", "rrule_groupnorm", "rrule_instancenorm", "rrule_layernorm", "maxpool", "meanpool", "rrule_maxpool", "rrule_meanpool",
     "rrule_bias_activation", "mse_loss", "rrule_mse_loss", "conv_transpose_bias_activation", "rrule_conv_transpose", "conv_transpose_output_size", "scale", "rrule_scale", "cross_entropy_loss", "rrule_cross_entropy_loss", "batched_matmul", "rrule_batched_matmul",
-    "scaled_dot_product_attention", "rrule_scaled_dot_product_attention",
+    "scaled_dot_product_attention", "rrule_scaled_dot_product_attention", "rrule_conv_batchnorm",
 ]

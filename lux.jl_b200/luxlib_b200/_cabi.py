@@ -96,6 +96,12 @@ PROTOTYPES = {
                                   C.c_uint32, _p, _sz, _p]),
     "lb2_attention_softmax_fwd": (_i32, [_p, _p, _p, _i64, _p, _i64, _i32, C.c_double, _i64, _i64, _i64, _i32, _p]),
     "lb2_attention_softmax_bwd": (_i32, [_p, _p, _p, _p, C.c_double, _i64, _i64, _i64, _i32, _p]),
+    "lb2_conv_fwd_sums_is_fused": (_i32, [_p, _i32]),
+    "lb2_conv_fwd_sums_workspace_bytes": (_sz, [_p, _i32]),
+    "lb2_conv_fwd_sums": (_i32, [_p, _fp, _p, _p, _p, _i32, C.c_uint32, _p, _sz, _p]),
+    "lb2_channel_sums_workspace_bytes": (_sz, [_i64, _i64, _i64]),
+    "lb2_channel_sums": (_i32, [_fp, _p, _i64, _i64, _i64, _i32, _p, _sz, _p]),
+    "lb2_batchnorm_fwd_train_sums": (_i32, [_p, _fp, _fp, _p, _p, _p, _p, _p, _p, _p, _fp, _i64, _i64, _i64, _dbl, _dbl, _i32, _i32, _p, _sz, _p]),
     "lb2_scale_fwd": (_i32, [_p, _p, _p, _p, _i64, _i64, _i32, _i32, _p]),
     "lb2_scale_bwd_workspace_bytes": (_sz, [_i64, _i64]),
     "lb2_scale_bwd": (_i32, [_p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i32, _i32, _p, _sz, _p]),

@@ -808,6 +808,81 @@ def rrule_batchnorm(x, scale, bias, running_mean, running_var, training: bool, a
     return y, stats, pullback
 
 
+def rrule_conv_batchnorm(act: str, weight, x, cdims: ConvDims, scale, bias, running_mean, running_var, momentum: float = 0.1,
+                         epsilon: Optional[float] = None, *, flags: int = 0):
+    """A bias-free Conv followed by a training-mode BatchNorm carrying the activation — the pair every block of the
+    reference's ResNet is made of (perf/resnet/resnet.jl:17-22: conv_norm = Chain(Conv(...; use_bias = false),
+    BatchNorm(out, act))) — with BatchNorm's statistics taken from per-channel sums that the convolution's epilogue
+    forms while it writes its result, instead of a pass that reads the result back. Same values as
+    batchnorm(fused_conv_bias_activation(identity, weight, x, nothing, cdims), ...) up to the summation order.
+    Returns (y, (new_running_mean, new_running_var), pullback) with pullback Δ -> (∂weight, ∂x, ∂scale, ∂bias); the
+    pullback is the composition of the two layers' pullbacks."""
+    lib = _cabi.load()
+    weight, x = _promote(weight, x)
+    _check_affine(scale, bias)
+    if (running_mean is None) != (running_var is None):
+        raise ArgumentError("running_mean and running_var must both be given or both be nothing")
+    d = _conv_desc(weight, x, cdims)
+    Wt, X = as_colmajor(weight), as_colmajor(x)
+    osz = (C.c_int32 * 3)()
+    _cabi.check(lib.lb2_conv_output_size(C.byref(d), osz))
+    ushape = tuple(osz[i] for i in range(d.ndim)) + (d.cout, d.batch)
+    for v, name in ((scale, "scale"), (bias, "bias"), (running_mean, "running_mean"), (running_var, "running_var")):
+        if v is not None and v.shape[0] != d.cout:
+            raise DimensionMismatch(f"length({name}) must equal the number of channels {d.cout}")
+    dt, dev = dtype_code(X.dtype), X.device
+    if (flags & _cabi.FLAG_FORCE_SIMT) or lib.lb2_conv_fwd_sums_is_fused(C.byref(d), dt) != 1:
+        # short contractions and the paths without the epilogue sums: the plain pair is the faster form
+        u, pb_conv = rrule_fused_conv("identity", weight, x, None, cdims, flags=flags)
+        y, stats, pb_bn = rrule_batchnorm(u, scale, bias, running_mean, running_var, True, act, momentum, epsilon)
+
+        def pullback_pair(delta, need_dx=True):
+            du, dg, db = pb_bn(delta)
+            dw, dx, _ = pb_conv(du, need_dx=need_dx)
+            return dw, dx, dg, db
+
+        return y, stats, pullback_pair
+    u = jl_empty(ushape, X.dtype, dev)
+    sums = torch.empty(2 * d.cout, dtype=torch.float32, device=dev)
+    ws, wsp, wsn = _ws(lib.lb2_conv_fwd_sums_workspace_bytes(C.byref(d), dt), dev)
+    _cabi.check(lib.lb2_conv_fwd_sums(ptr(u), ptr(sums), ptr(X), ptr(Wt), C.byref(d), dt, flags, wsp, wsn, current_stream(dev)))
+    xcopy = ws if (ws is not None and not (flags & _cabi.FLAG_FORCE_SIMT) and X.data_ptr() % 16 == 0 and
+                   lib.lb2_conv_fwd_leaves_x_copy(C.byref(d), dt) == 1) else None
+    S, Cc, B = _scb(u)
+    eps = default_epsilon(X.dtype) if epsilon is None else float(epsilon)
+    code = act_code(act)
+    cast = lambda v: None if v is None else v.to(X.dtype)
+    sc, bi, rm, rv = cast(scale), cast(bias), cast(running_mean), cast(running_var)
+    y = jl_empty(ushape, X.dtype, dev)
+    save_mean = torch.empty(Cc, dtype=torch.float32, device=dev)
+    save_inv = torch.empty(Cc, dtype=torch.float32, device=dev)
+    new_rm = torch.empty_like(rm) if rm is not None else None
+    new_rv = torch.empty_like(rv) if rv is not None else None
+    _, w2, n2 = _ws(lib.lb2_batchnorm_workspace_bytes(S, Cc, B), dev)
+    _cabi.check(lib.lb2_batchnorm_fwd_train_sums(ptr(y), ptr(save_mean), ptr(save_inv), ptr(new_rm), ptr(new_rv), ptr(u), ptr(sc), ptr(bi),
+                                                 ptr(rm), ptr(rv), ptr(sums), S, Cc, B, float(momentum), eps, dt, code, w2, n2,
+                                                 current_stream(dev)))
+    ident = act_code("identity")
+
+    def pullback(delta, need_dx=True):
+        dl = as_colmajor(delta.to(X.dtype))
+        du = jl_empty(ushape, X.dtype, dev)
+        dg = torch.empty(Cc, dtype=X.dtype, device=dev) if sc is not None else None
+        db = torch.empty(Cc, dtype=X.dtype, device=dev) if sc is not None else None
+        _, w3, n3 = _ws(lib.lb2_batchnorm_workspace_bytes(S, Cc, B), dev)
+        _cabi.check(lib.lb2_batchnorm_bwd(ptr(du), ptr(dg), ptr(db), ptr(dl), ptr(u), ptr(sc), ptr(bi), ptr(save_mean), ptr(save_inv),
+                                          S, Cc, B, dt, code, w3, n3, current_stream(dev)))
+        dw = jl_empty(Wt.shape, X.dtype, dev)
+        dx = jl_empty(X.shape, X.dtype, dev) if need_dx else None
+        _, w4, n4 = _ws(lib.lb2_conv_bwd_workspace_bytes(C.byref(d), dt, ident), dev)
+        xarg, xflag = (ptr(xcopy), _cabi.FLAG_X_COPY_GIVEN) if xcopy is not None else (ptr(X), 0)
+        _cabi.check(lib.lb2_conv_bwd(ptr(dw), ptr(dx), None, ptr(du), None, None, xarg, ptr(Wt), C.byref(d), dt, ident, flags | xflag,
+                                     w4, n4, current_stream(dev)))
+        return dw, dx, dg, db
+
+    return y, ((new_rm, new_rv) if rm is not None else (running_mean, running_var)), pullback
+
+
 @dataclass(frozen=True)
 class PoolDims:
     """The fields of NNlib.PoolDims built by calculate_pool_dims (src/layers/pooling.jl:17-34)."""

@@ -967,3 +967,85 @@ def test_scaled_dot_product_attention_fwd_bwd(dt, variant, dims):
     if bias is not None:
         check(db, db_ref, dt, "dbias")
     assert L._cabi.load().lb2_poll_device_status(None) == 0
+
+
+# ------------------------------------------------------------------------------------------
+# conv -> BatchNorm(act) with the statistics taken from the convolution's epilogue
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dt", ["bf16", "f32"])
+@pytest.mark.parametrize("act", ["identity", "relu"])
+@pytest.mark.parametrize("case", [
+    # spatial, k, C_in, C_out, stride, pad, batch
+    ((14, 14), (3, 3), 128, 128, 1, 1, 8),       # general tensor-core path: sums from the epilogue (bf16)
+    ((28, 28), (3, 3), 128, 128, 2, 1, 6),       # strided; two epilogue halves of 64 channels
+    ((9, 7), (3, 3), 128, 512, 2, 1, 5),         # two column tiles of 256: the grid is a multiple of the tile count
+    ((9, 7), (1, 1), 64, 512, 2, 0, 5),          # short contraction: the plain pair
+    ((30, 30), (7, 7), 3, 64, 2, 3, 4),          # the folded stem geometry: the plain pair
+    ((16, 16), (3, 3), 64, 64, 1, 1, 4),         # the stride-1 64-channel fast case: sums by a separate pass
+    ((6, 5), (3, 3), 4, 6, 1, 1, 3),             # CUDA-core kernels + separate pass
+])
+def test_conv_batchnorm_pair_with_sums_from_the_conv(dt, act, case):
+    sp, k, cin, cout, stride, pad, batch = case
+    rng = np.random.default_rng(51)
+    x = prep(rng.standard_normal(sp + (cin, batch)), dt)
+    w = prep(O.kaiming_normal(rng, k + (cin, cout)), dt)
+    gam = prep(rng.uniform(0.5, 1.5, cout), dt)
+    bet = prep(rng.standard_normal(cout) * 0.1, dt)
+    rm, rv = prep(rng.standard_normal(cout) * 0.1, dt), prep(rng.uniform(0.5, 1.5, cout), dt)
+    ocd, lcd = O.ConvDims.make(2, stride, pad, 1, 1, False), L.ConvDims.make(2, stride, pad, 1, 1, False)
+    store = O.round_bf16 if dt == "bf16" else (lambda a: a)
+    u_ref, pb_conv = O.fused_conv_rrule("identity", w, x, None, ocd)
+    u_ref = store(u_ref)                       # the convolution's result as the arrays' element type holds it
+    y_ref, (nrm_ref, nrv_ref), pb_bn = O.batchnorm_rrule(u_ref, gam, bet, rm, rv, True, act, 0.1, 1e-5)
+    y, (nrm, nrv), pb = L.rrule_conv_batchnorm(act, dev(w, dt), dev(x, dt), lcd, dev(gam, dt), dev(bet, dt), dev(rm, dt), dev(rv, dt), 0.1, 1e-5)
+    check(y, y_ref, dt, "y")
+    check(nrm, nrm_ref, dt, "running_mean")
+    check(nrv, nrv_ref, dt, "running_var")
+    delta = prep(rng.standard_normal(y_ref.shape), dt)
+    du_ref, dg_ref, db_ref = pb_bn(delta)
+    dw_ref, dx_ref, _ = pb_conv(store(du_ref))
+    dw, dx, dg, db = pb(dev(delta, dt))
+    check(dg, dg_ref, dt, "dgamma")
+    check(db, db_ref, dt, "dbeta")
+    check(dw, dw_ref, dt, "dw")
+    check(dx, dx_ref, dt, "dx")
+    assert L._cabi.load().lb2_poll_device_status(None) == 0
+
+
+@pytest.mark.parametrize("dt", ["bf16", "f32"])
+@pytest.mark.parametrize("case", [((14, 14), (3, 3), 128, 128, 1, 1, 8), ((9, 7), (1, 1), 64, 512, 2, 0, 5), ((30, 30), (7, 7), 3, 64, 2, 3, 4),
+                                  ((16, 16), (3, 3), 64, 64, 1, 1, 4), ((6, 5), (3, 3), 4, 6, 1, 1, 3)])
+def test_conv_fwd_sums_entry_point_on_every_route(dt, case):
+    # lb2_conv_fwd_sums itself (the Python pair takes it only where the epilogue form pays): y and the per-channel sums of
+    # the stored y and y^2, from the epilogue on the general bf16 path and from lb2_channel_sums elsewhere
+    import ctypes as C
+    sp, k, cin, cout, stride, pad, batch = case
+    rng = np.random.default_rng(52)
+    x = prep(rng.standard_normal(sp + (cin, batch)), dt)
+    w = prep(O.kaiming_normal(rng, k + (cin, cout)), dt)
+    ocd, lcd = O.ConvDims.make(2, stride, pad, 1, 1, False), L.ConvDims.make(2, stride, pad, 1, 1, False)
+    y_ref = O.conv(x.astype(np.float64), w.astype(np.float64), ocd)
+    y_st = O.round_bf16(y_ref).astype(np.float64) if dt == "bf16" else y_ref.astype(np.float32).astype(np.float64)
+    lib = L._cabi.load()
+    X, W = dev(x, dt), dev(w, dt)
+    from luxlib_b200 import ops as _ops
+    d = _ops._conv_desc(W, X, lcd)
+    y = L.jl_empty(y_ref.shape, X.dtype, "cuda")
+    sums = torch.empty(2 * cout, dtype=torch.float32, device="cuda")
+    dtc = 1 if dt == "bf16" else 0
+    n = lib.lb2_conv_fwd_sums_workspace_bytes(C.byref(d), dtc)
+    ws = torch.empty(max(n, 1), dtype=torch.uint8, device="cuda")
+    rc = lib.lb2_conv_fwd_sums(y.data_ptr(), sums.data_ptr(), X.data_ptr(), W.data_ptr(), C.byref(d), dtc, 0, ws.data_ptr(), n, None)
+    assert rc == 0, lib.lb2_last_error_string()
+    check(y, y_ref, dt, "y")
+    got = sums.cpu().numpy().reshape(cout, 2)
+    # judged against the stored values the library itself produced (rounding of y differs from the oracle's by design)
+    ys = L.to_numpy(y).astype(np.float64)
+    axes = (0, 1, 3)
+    s1, s2 = ys.sum(axis=axes), (ys * ys).sum(axis=axes)
+    err2 = np.linalg.norm(got[:, 1] - s2) / np.linalg.norm(s2)
+    err1 = np.linalg.norm(got[:, 0] - s1) / max(np.linalg.norm(s1), 1e-3 * np.sqrt(np.sum(np.abs(ys).sum(axis=axes) ** 2)))
+    parity_report.record("sum y^2", dt, err2, 1e-5)
+    parity_report.record("sum y", dt, err1, 1e-5, judged="against the sum of magnitudes when the sum cancels")
+    assert err2 <= 1e-5 and err1 <= 1e-5, (err1, err2)
+    del y_st
