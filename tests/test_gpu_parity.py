@@ -432,7 +432,7 @@ def _batchnorm_case(dt, act, shape, affine):
     delta = prep(rng.standard_normal(shape), dt)
     dx_ref, dg_ref, db_ref = pb_ref(delta)
     dx, dg, db = pb(dev(delta, dt))
-    # dx = g' * (d - mean(d) - xhat * mean(d * xhat)) cancels; judge it on the size of its terms
+    # dx = g' * (d - mean(d) - xhat * mean(d * xhat)) cancels; it is measured against the size of its terms
     x3 = x.reshape((-1,) + x.shape[-2:], order="F")
     inv = 1.0 / np.sqrt(x3.var(axis=(0, 2)) + 1e-5)
     gp = (inv if g is None else g * inv).reshape((1,) * (x.ndim - 2) + (c, 1))
@@ -694,7 +694,7 @@ def test_config_conv_batchnorm_relu_block(dt):
     check(dw, dw_ref, dt, "dw")
     check(dx, dx_ref, dt, "dx")
     # BatchNorm's input gradient sums to zero over each channel, so the conv bias gradient is pure cancellation:
-    # judge it on the size of the terms that cancel
+    # measured against the size of the terms that cancel
     check(db, db_ref, dt, "db", scale=np.abs(dc_ref).sum(axis=(0, 1, 3)), degenerate=True)
     assert L._cabi.load().lb2_poll_device_status(None) == 0
 
