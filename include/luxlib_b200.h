@@ -175,13 +175,12 @@ LB2_API size_t lb2_conv_fwd_workspace_bytes(const lb2_conv_desc* d, int32_t dtyp
 LB2_API int32_t lb2_conv_fwd(void* y, void* preact, const void* x, const void* w, const void* b,
                      const lb2_conv_desc* d, int32_t dtype, int32_t act, uint32_t flags,
                      void* workspace, size_t workspace_bytes, void* stream);
-/* Pullback ∇fused_conv (lib/LuxLib/src/impl/conv.jl:261-275): g = dy .* act'(out, preact);
- * dw = ∇conv_filter(x, g); dx = ∇conv_data(g, w); db = sum_{spatial,N} g. Outputs may be NULL. */
 /* 1 when lb2_conv_fwd (without LB2_FLAG_FORCE_SIMT, on 16-byte aligned arrays) leaves a reusable copy of x at the
- * start of its workspace for this geometry (see LB2_FLAG_X_COPY_GIVEN), else 0. */
+ * start of its workspace for this geometry (see LB2_FLAG_X_COPY_GIVEN), else 0. The reference keeps x itself for
+ * ∇conv_filter (lib/LuxLib/src/impl/conv.jl:261-275); no counterpart in the reference for the copy. */
 LB2_API int32_t lb2_conv_fwd_leaves_x_copy(const lb2_conv_desc* d, int32_t dtype);
-/* conv -> BatchNorm(act) pairs (perf/resnet/resnet.jl:17-22: Conv without bias, then BatchNorm carrying the
- * activation): the convolution (identity activation, no bias) that also returns per output channel the sums of the
+/* conv -> BatchNorm(act) pairs (perf/resnet/resnet.jl:17-22: Conv without bias, src/layers/conv.jl:251-260, then
+ * BatchNorm carrying the activation, src/layers/normalize.jl:149-190): the convolution (identity activation, no bias) that also returns per output channel the sums of the
  * stored y and of y^2 (fp32 [cout][2]) — BatchNorm's statistics pass without reading y back. On the general bf16
  * tensor-core path the sums are formed in the convolution's epilogue; elsewhere a separate pass over y forms them.
  * lb2_conv_fwd_sums_is_fused() == 1 says that the epilogue form applies AND pays (a contraction of at least 16
@@ -190,6 +189,8 @@ LB2_API int32_t lb2_conv_fwd_sums_is_fused(const lb2_conv_desc* d, int32_t dtype
 LB2_API size_t lb2_conv_fwd_sums_workspace_bytes(const lb2_conv_desc* d, int32_t dtype);
 LB2_API int32_t lb2_conv_fwd_sums(void* y, float* sums, const void* x, const void* w, const lb2_conv_desc* d, int32_t dtype,
                                   uint32_t flags, void* workspace, size_t workspace_bytes, void* stream);
+/* Pullback ∇fused_conv (lib/LuxLib/src/impl/conv.jl:261-275): g = dy .* act'(out, preact);
+ * dw = ∇conv_filter(x, g); dx = ∇conv_data(g, w); db = sum_{spatial,N} g. Outputs may be NULL. */
 LB2_API size_t lb2_conv_bwd_workspace_bytes(const lb2_conv_desc* d, int32_t dtype, int32_t act);
 LB2_API int32_t lb2_conv_bwd(void* dw, void* dx, void* db, const void* dy, const void* out,
                      const void* preact, const void* x, const void* w, const lb2_conv_desc* d,
