@@ -47,6 +47,7 @@ UNIT = "TFLOP/s"
 WORKLOAD = "dense W 4096x4096 * x 4096x8192 + b, gelu(tanh), bf16 storage / fp32 accumulate; fwd + dX + dW + db"
 RAMP_S = 1.5
 DW_PANELS = 4
+DX_RESERVE_SMS = 16       # SMs kept out of the dX GEMM of a multi-rank step: the last dW panel's all-reduce runs beside it
 TRAFFIC_PROFILE = os.path.join("profiles", "gemm_tc_kernel_dense_c2_bf16.md")
 
 
@@ -394,7 +395,8 @@ def run_gpu_arm(args):
             dW, dx, db = pullback(dy_)
             return y, dW, dx, db
         pending = []
-        dW, dx, db = pullback(dy_, on_param_grads=lambda p, d: pending.extend(reduce_panel(p, d)), param_panels=DW_PANELS)
+        dW, dx, db = pullback(dy_, on_param_grads=lambda p, d: pending.extend(reduce_panel(p, d)), param_panels=DW_PANELS,
+                              dx_reserve_sms=DX_RESERVE_SMS)
         for h in pending:
             h.wait()          # stream-level wait: later work is ordered after the reduced gradients
         return y, dW, dx, db
@@ -434,7 +436,7 @@ def run_gpu_arm(args):
 
     # ---- per-launch durations: eager replay of the same K steps, an event pair around every launch
     names = ["forward GEMM (bias+gelu epilogue, pre-activation store)", "g = dy*gelu'(pre) and db partials + db finish",
-             "dX GEMM", "dW GEMM"]
+             "dW GEMM", "dX GEMM"]
     kern = {n_: [] for n_ in names}
     sampler2 = ClockSampler(local).start()
     for _ in range(args.steps):
@@ -447,7 +449,7 @@ def run_gpu_arm(args):
                  mark=lambda: (marks.append(torch.cuda.Event(enable_timing=True)), marks[-1].record()))
         torch.cuda.synchronize()
         kern[names[0]].append(e[0].elapsed_time(e[1]))
-        pts = [e[1]] + marks      # marks: after g/db, after dX, after dW
+        pts = [e[1]] + marks      # marks: after g/db, after dW, after dX
         for nm, a_, b_ in zip(names[1:], pts[:-1], pts[1:]):
             kern[nm].append(a_.elapsed_time(b_))
     clocks2 = sampler2.stop()

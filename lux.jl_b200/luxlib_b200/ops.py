@@ -134,16 +134,17 @@ def rrule_fused_dense(act: str, weight, x, b=None, *, flags: int = 0):
     y, pre, (W, ldw, X, ldx, bb, M, N, K, dt) = _dense_fwd(act, weight, x, b, keep_pre, flags)
     code = act_code(act)
 
-    def pullback(delta, on_param_grads=None, shadows=None, param_panels=1, mark=None):
+    def pullback(delta, on_param_grads=None, shadows=None, param_panels=1, mark=None, dx_reserve_sms=0):
         """Δ -> (∂weight, ∂x, ∂b).
 
         `on_param_grads(dW_panel, db_or_None)` switches to the data-parallel order of work: g = Δ .* act' and ∂b first,
-        then ∂x, then ∂weight in `param_panels` column panels; the callback runs as soon as a panel is enqueued (∂b
-        comes with the last one), so the caller's all-reduce of panel i runs underneath the GEMM of panel i+1 — a
-        panel of 1024 columns is one wave of 256 x 256 tiles on 64 of the 74 SM pairs, which leaves SMs to the
-        collective. Same kernels, more C calls. `mark()`, when given, is called after each phase (profiling hooks).
-        `shadows = (dW, dx, db)` switches to the accumulate contract of the Enzyme rules: the gradients are added
-        to those arrays in place and Δ is zeroed."""
+        then ∂weight in `param_panels` column panels, then ∂x; the callback runs as soon as a panel is enqueued (∂b
+        comes with the last one), so the caller's all-reduce of panel i runs underneath the GEMM of panel i+1 and the
+        last panel's underneath the ∂x GEMM — a panel of 1024 columns is one wave of 256 x 256 tiles on 64 of the 74
+        SM pairs, which leaves SMs to the collective, and `dx_reserve_sms` keeps that many SMs out of the ∂x GEMM for
+        the same reason. Same kernels, more C calls. `mark()`, when given, is called after each phase (profiling
+        hooks). `shadows = (dW, dx, db)` switches to the accumulate contract of the Enzyme rules: the gradients are
+        added to those arrays in place and Δ is zeroed."""
         if on_param_grads is not None:
             d = as_colmajor(delta.reshape(M, N).to(W.dtype))
             g = jl_empty((M, N), W.dtype, W.device)
@@ -154,9 +155,6 @@ def rrule_fused_dense(act: str, weight, x, b=None, *, flags: int = 0):
                                              code, wsp, wsn, current_stream(W.device)))
             if mark is not None:
                 mark()
-            dx = matmul(W, g, transA=True, flags=flags)      # W' * g
-            if mark is not None:
-                mark()
             dW = jl_empty((M, K), W.dtype, W.device)
             panels = max(1, min(int(param_panels), K))
             bounds = [K * i // panels for i in range(panels + 1)]
@@ -164,6 +162,9 @@ def rrule_fused_dense(act: str, weight, x, b=None, *, flags: int = 0):
                 k0, k1 = bounds[i], bounds[i + 1]
                 matmul(g, X[k0:k1, :], transB=True, flags=flags, out=dW[:, k0:k1])      # g * x[k0:k1, :]'
                 on_param_grads(dW[:, k0:k1], db if i == panels - 1 else None)
+            if mark is not None:
+                mark()
+            dx = matmul(W, g, transA=True, flags=flags | _cabi.flag_reserve_sms(int(dx_reserve_sms)))      # W' * g
             if mark is not None:
                 mark()
             return dW, (dx.reshape(x.shape) if x.dim() == 1 else dx), db
