@@ -595,6 +595,186 @@ __global__ void __launch_bounds__(256) conv_wgrad2_reduce_kernel(T* __restrict__
 
 
 // ----------------------------------------------------------------------------------------------
+// filter-gradient kernel for at most 64 output channels: kernel rows stacked along M
+// ----------------------------------------------------------------------------------------------
+// With 64 output channels the 128 accumulator rows of the kernel above are half empty and every kernel row loads the
+// wide x operand again. Substituting s' = s + (th - pad_h)*W in
+//   dw[tw, th, ci, co] = sum_s dy[co, s] * x_tw[ci, s + (th - pad_h)*W]
+// moves the kernel-row shift onto dy: dw = sum_s' dy[co, s' - (th - pad_h)*W] * x_tw[ci, s']. One stage then holds the kW
+// tap tiles of x at the positions s' ONCE and kH tiles of dy (64 rows each), each fetched at its own start coordinate
+// (out-of-image positions zero-filled by the tensor map); two kernel rows form one A operand of 128 rows, so a 64-position
+// block takes ceil(kH/2) * 4 MMAs for all kernel rows and (kW + kH) * 8 KB of operand traffic instead of kH * 4 MMAs and
+// kH * (kW + 2) * 8 KB. A work item is (64-channel chunk, K split); partial[z][chunk][pair][(th & 1)*64 + co][tw*64 + ci]
+// in fp32, reduced in a fixed order afterwards. For an odd kH the upper half of the last pair multiplies whatever
+// follows the dy tiles in the stage (the first x tile); those accumulator rows are never read.
+struct ConvWg3Params {
+  int32_t n_img;
+  int32_t s_blocks;                 // 64-position blocks per image (input positions)
+  int32_t kW, kH, chunks, pairs;
+  int32_t splits, kb_total, kb_per_split;
+  uint32_t idesc;
+  uint32_t desc_hi, desc_lbo, k_advance;   // both operands K-major SW128
+  float* partial;
+  unsigned int* status;
+  int32_t center_tw;                // tap whose shift along W is zero: read from x itself (-1: none)
+  int16_t row_shift[16];            // per kernel row th: (th - pad_h) * W
+};
+
+template <int KW>
+__global__ void __launch_bounds__(kConvThreads, 1)
+conv_tc_wgrad_rows_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmX0,
+                          const __grid_constant__ CUtensorMap tmG, const __grid_constant__ ConvWg3Params p, int stages,
+                          int stage_bytes, uint32_t tmem_cols) {
+  constexpr int BN = KW * 64;
+  constexpr int TILE = 64 * 128;              // 64 rows x 64 positions
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + stages * stage_bytes);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + stages;
+  uint64_t* acc_full = bars + 2 * stages;
+  uint64_t* acc_empty = acc_full + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_items = p.chunks * p.splits;
+  const int a_bytes = p.kH * TILE;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    mbar_init(acc_full, 1);
+    mbar_init(acc_empty, 8);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 2) {
+    tmem_alloc(tmem_slot, tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // item -> (chunk fastest, split)
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tmX);
+      tma_prefetch_desc(&tmX0);
+      tma_prefetch_desc(&tmG);
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+        const int chunk = item % p.chunks, z = item / p.chunks;
+        const int kb_lo = z * p.kb_per_split, kb_hi = min(p.kb_total, kb_lo + p.kb_per_split);
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1u, p.status, 0x20000u)) { ok = false; break; }
+          const int img = kb / p.s_blocks, s0 = (kb % p.s_blocks) * 64;
+          const uint32_t sA = smem_base + stage * stage_bytes, sB = sA + a_bytes;
+          mbar_expect_tx(&full[stage], (uint32_t)((p.kH + KW) * TILE));
+          for (int th = 0; th < p.kH; ++th) tma_load_4d(sA + th * TILE, &tmG, s0 - p.row_shift[th], 0, img, 0, &full[stage]);
+#pragma unroll
+          for (int tw = 0; tw < KW; ++tw) {
+            if (tw == p.center_tw) tma_load_4d(sB + tw * TILE, &tmX0, s0, chunk * 64, img, 0, &full[stage]);
+            else tma_load_4d(sB + tw * TILE, &tmX, s0, chunk * 64, img, tw, &full[stage]);
+          }
+          if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0, acc_phase = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+        const int z = item / p.chunks;
+        const int kb_lo = z * p.kb_per_split, kb_hi = min(p.kb_total, kb_lo + p.kb_per_split);
+        if (!mbar_wait(acc_empty, acc_phase ^ 1u, p.status, 0x40000u)) { ok = false; break; }
+        tc_fence_after();
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {
+          if (!mbar_wait(&full[stage], phase, p.status, 0x80000u)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sA = smem_base + stage * stage_bytes, sB = sA + a_bytes;
+          const uint32_t b_lo32 = ((sB >> 4) & 0x3FFFu) | p.desc_lbo;
+          for (int pi = 0; pi < p.pairs; ++pi) {
+            const uint32_t a_lo32 = (((sA + pi * 2 * TILE) >> 4) & 0x3FFFu) | p.desc_lbo;
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+              const uint64_t ad = ((uint64_t)p.desc_hi << 32) | (uint64_t)(a_lo32 + ks * p.k_advance);
+              const uint64_t bd = ((uint64_t)p.desc_hi << 32) | (uint64_t)(b_lo32 + ks * p.k_advance);
+              umma<false>(tmem_base + pi * BN, ad, bd, p.idesc, (kb > kb_lo || ks != 0) ? 1u : 0u);
+            }
+          }
+          umma_commit(&empty[stage]);
+          if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) umma_commit(acc_full);
+        acc_phase ^= 1u;
+      }
+    }
+  } else if (warp >= 4) {
+    const int q = warp & 3, half = (warp - 4) >> 2;   // lane quarter; which half of the BN columns
+    constexpr int COLS = BN / 2;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+      if (!mbar_wait_warp(acc_full, acc_phase, p.status, 0x100000u)) { ok = false; break; }
+      tc_fence_after();
+      const int row = q * 32 + lane;
+      for (int pi = 0; pi < p.pairs; ++pi) {
+        if (2 * pi + (q >> 1) >= p.kH) continue;   // upper half of an odd last pair: nothing to keep
+        float* dst = p.partial + (((int64_t)item * p.pairs + pi) * 128 + row) * BN + half * COLS;
+#pragma unroll 1
+        for (int c = 0; c < COLS / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + pi * BN + half * COLS + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) dst[c * 32 + j] = __uint_as_float(r[j]);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty);
+      acc_phase ^= 1u;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    if (*reinterpret_cast<volatile unsigned int*>(p.status) != 0) {
+      for (int i = 0; i < 64; ++i) __nanosleep(2000);
+    }
+    tc_fence_after();
+    tmem_dealloc(tmem_base, tmem_cols);
+  }
+}
+
+// dw[kw,kh,ci,co] = sum over splits (ascending) of partial[z][chunk][th / 2][(th & 1)*64 + co][tw*64 + ci % 64]
+template <typename T>
+__global__ void __launch_bounds__(256) conv_wgrad_rows_reduce_kernel(T* __restrict__ dw, const float* __restrict__ partial,
+                                                                     int kW, int kH, int cin, int cout, int flip, int chunks,
+                                                                     int pairs, int splits) {
+  const int64_t total = (int64_t)kW * kH * cin * cout;
+  const int bn = kW * 64;
+  const int64_t per_split = (int64_t)chunks * pairs * 128 * bn;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t r = i;
+    const int kw = (int)(r % kW); r /= kW;
+    const int kh = (int)(r % kH); r /= kH;
+    const int ci = (int)(r % cin);
+    const int co = (int)(r / cin);
+    const int tw = flip ? kw : kW - 1 - kw, th = flip ? kh : kH - 1 - kh;
+    const int64_t off = ((((int64_t)(ci / 64) * pairs + th / 2) * 128) + (th & 1) * 64 + co) * bn + tw * 64 + ci % 64;
+    float s = 0.f;
+    for (int z = 0; z < splits; ++z) s += partial[(int64_t)z * per_split + off];
+    dw[i] = from_f32<T>(s);
+  }
+}
+
+
+// ----------------------------------------------------------------------------------------------
 // host side
 // ----------------------------------------------------------------------------------------------
 // One implicit-GEMM problem: out (W, Ho, Cn, N) = taps over in (W, Hi, Ck, N)
@@ -801,7 +981,42 @@ static Wg2Plan wg2_plan(const ConvGeom& g) {
 static size_t wg2_partial_bytes(const ConvGeom& g, const Wg2Plan& w) {
   return align_up((size_t)w.splits * w.groups * 128 * (g.k[0] * 64) * sizeof(float), 1024);
 }
-static size_t wg_any_partial_bytes(const ConvGeom& g) { return wg2_partial_bytes(g, wg2_plan(g)); }
+// kernel rows stacked along M: at most 64 output channels, all accumulators (one per pair of kernel rows) in TMEM at once
+struct Wg3Plan {
+  bool ok;
+  int chunks, pairs, s_blocks, kb_total, splits, kb_per_split, stages, stage_bytes;
+  uint32_t tmem_cols;
+};
+static Wg3Plan wg3_plan(const ConvGeom& g) {
+  Wg3Plan w{};
+  if (g.k[0] > 4 || g.k[1] > 16 || g.cout > 64) return w;
+  w.pairs = (g.k[1] + 1) / 2;
+  const int cols = w.pairs * g.k[0] * 64;
+  if (cols > 512) return w;
+  w.tmem_cols = 32;
+  while ((int)w.tmem_cols < cols) w.tmem_cols *= 2;
+  w.stage_bytes = (g.k[1] + g.k[0]) * 64 * 128;
+  w.stages = (200 * 1024) / w.stage_bytes;
+  if (w.stages > 8) w.stages = 8;
+  if (w.stages < 2) return w;
+  w.ok = true;
+  w.chunks = conv_chunks(g.cin);
+  w.s_blocks = (g.in[0] * g.in[1] + 63) / 64;
+  w.kb_total = g.batch * w.s_blocks;
+  int splits = sm_count() / w.chunks;
+  if (splits < 1) splits = 1;
+  if (splits > w.kb_total) splits = w.kb_total;
+  w.kb_per_split = (w.kb_total + splits - 1) / splits;
+  w.splits = (w.kb_total + w.kb_per_split - 1) / w.kb_per_split;
+  return w;
+}
+static size_t wg3_partial_bytes(const ConvGeom& g, const Wg3Plan& w) {
+  return align_up((size_t)w.splits * w.chunks * w.pairs * 128 * (g.k[0] * 64) * sizeof(float), 1024);
+}
+static size_t wg_any_partial_bytes(const ConvGeom& g) {
+  const Wg3Plan w3 = wg3_plan(g);
+  return w3.ok ? wg3_partial_bytes(g, w3) : wg2_partial_bytes(g, wg2_plan(g));
+}
 
 size_t conv_tc_bwd_workspace_bytes(const ConvGeom& g, int32_t dtype) {
   if (dtype == LB2_F32) return conv_tc_f32_bwd_workspace_bytes(g);
@@ -831,6 +1046,45 @@ int32_t conv_tc_wgrad(void* dw, const void* x, const void* gy, const ConvGeom& g
   if (!launch_shift_copies_vec(copies, x, f.W, rows, f.kW, f.pad_w, flat_grid_tc(rows * (f.W / 8)), st, skip))
     conv_shift_copies_kernel<T><<<flat_grid_tc(rows * ((f.W + 7) / 8)), 256, 0, st>>>(copies, (const T*)x, f.W, rows, f.kW, f.pad_w, skip);
   LB2_CHECK_LAUNCH("conv_tc shifted copies");
+  const Wg3Plan w3 = wg3_plan(g);
+  if (w3.ok) {
+    ConvWg3Params q{};
+    q.n_img = g.batch; q.s_blocks = w3.s_blocks;
+    q.kW = f.kW; q.kH = f.kH; q.chunks = w3.chunks; q.pairs = w3.pairs;
+    q.splits = w3.splits; q.kb_total = w3.kb_total; q.kb_per_split = w3.kb_per_split;
+    q.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)((f.kW * 64) >> 3) << 17) | ((uint32_t)(kConvBM >> 4) << 24);
+    q.desc_hi = (uint32_t)((1024u >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
+    q.desc_lbo = 1u << 16;
+    q.k_advance = 32u >> 4;
+    q.partial = partial;
+    q.status = device_status_word();
+    LB2_REQUIRE(q.status != nullptr, LB2_LAUNCH_FAIL, "conv_tc: device status word unavailable");
+    for (int th = 0; th < f.kH; ++th) q.row_shift[th] = (int16_t)((th - f.pad_h) * f.W);
+    q.center_tw = skip;
+    CUtensorMap mX3, mX03, mG3;
+    if (!bf16_map_4d(&mX3, copies, (int64_t)f.W * f.Hi, f.Ck, f.N, f.kW, 64, 64) ||
+        !bf16_map_4d(&mX03, x, (int64_t)f.W * f.Hi, f.Ck, f.N, 1, 64, 64) ||
+        !bf16_map_4d(&mG3, gy, (int64_t)g.out[0] * g.out[1], g.cout, g.batch, 1, 64, 64))
+      return fail(LB2_LAUNCH_FAIL, "conv_tc: cuTensorMapEncodeTiled failed");
+    const int smem3 = w3.stages * w3.stage_bytes + 1024 + 256 + 64 * 8;
+    const int items3 = w3.chunks * w3.splits;
+    const int grid3 = items3 < sm_count() ? items3 : sm_count();
+    auto launch3 = [&](auto kernel) -> int32_t {
+      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem3);
+      if (e != cudaSuccess) return fail(LB2_LAUNCH_FAIL, "conv_tc: cannot reserve %d bytes of shared memory: %s", smem3, cudaGetErrorString(e));
+      kernel<<<grid3, kConvThreads, smem3, st>>>(mX3, mX03, mG3, q, w3.stages, w3.stage_bytes, w3.tmem_cols);
+      LB2_CHECK_LAUNCH("conv_tc_wgrad_rows");
+      return LB2_OK;
+    };
+    int32_t rc3 = f.kW == 1 ? launch3(conv_tc_wgrad_rows_kernel<1>) : f.kW == 2 ? launch3(conv_tc_wgrad_rows_kernel<2>)
+                : f.kW == 3 ? launch3(conv_tc_wgrad_rows_kernel<3>) : launch3(conv_tc_wgrad_rows_kernel<4>);
+    if (rc3 != LB2_OK) return rc3;
+    const int64_t nw3 = (int64_t)g.k[0] * g.k[1] * g.cin * g.cout;
+    conv_wgrad_rows_reduce_kernel<T><<<flat_grid_tc(nw3), 256, 0, st>>>((T*)dw, partial, g.k[0], g.k[1], g.cin, g.cout, g.flip, w3.chunks,
+                                                                      w3.pairs, w3.splits);
+    LB2_CHECK_LAUNCH("conv_wgrad_rows_reduce");
+    return LB2_OK;
+  }
   if (w2.ok) {
     ConvWg2Params q{};
     q.n_img = g.batch; q.s_blocks = w2.s_blocks;
