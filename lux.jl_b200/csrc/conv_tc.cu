@@ -595,7 +595,7 @@ __global__ void __launch_bounds__(256) conv_wgrad2_reduce_kernel(T* __restrict__
 
 
 // ----------------------------------------------------------------------------------------------
-// filter-gradient kernel for at most 64 output channels: kernel rows stacked along M
+// filter-gradient kernel for at most 64 output channels: kernel rows stacked along M, tap shifts made in shared memory
 // ----------------------------------------------------------------------------------------------
 // With 64 output channels the 128 accumulator rows of the kernel above are half empty and every kernel row loads the
 // wide x operand again. Substituting s' = s + (th - pad_h)*W in
@@ -603,37 +603,68 @@ __global__ void __launch_bounds__(256) conv_wgrad2_reduce_kernel(T* __restrict__
 // moves the kernel-row shift onto dy: dw = sum_s' dy[co, s' - (th - pad_h)*W] * x_tw[ci, s']. One stage then holds the kW
 // tap tiles of x at the positions s' ONCE and kH tiles of dy (64 rows each), each fetched at its own start coordinate
 // (out-of-image positions zero-filled by the tensor map); two kernel rows form one A operand of 128 rows, so a 64-position
-// block takes ceil(kH/2) * 4 MMAs for all kernel rows and (kW + kH) * 8 KB of operand traffic instead of kH * 4 MMAs and
-// kH * (kW + 2) * 8 KB. A work item is (64-channel chunk, K split); partial[z][chunk][pair][(th & 1)*64 + co][tw*64 + ci]
-// in fp32, reduced in a fixed order afterwards. For an odd kH the upper half of the last pair multiplies whatever
-// follows the dy tiles in the stage (the first x tile); those accumulator rows are never read.
+// block takes ceil(kH/2) * 4 MMAs for all kernel rows.
+//
+// The tap tiles x_tw[ci, s'] = x[ci, s' + tw - pad_w] (0 where the shift leaves the image row) are not read from shifted
+// copies in global memory: the producer loads the unshifted tile (the tap tw = pad_w, in its final swizzled layout) and
+// the 8 positions either side of it, and the eight epilogue warps, idle during the main loop, cut the other taps out of
+// it: per 16-byte chunk a funnel shift over the chunk and its two neighbours, masked at the image-row ends (W is a
+// multiple of 8 and blocks start on a multiple of 64, so a row end can only fall on a chunk boundary), stored at the
+// chunk's swizzled place in the tap's tile. Operand traffic per block: (kH + 1) * 8 KB + 2 KB.
+//
+// A work item is (64-channel chunk, K split); partial[z][chunk][pair][(th & 1)*64 + co][tw*64 + ci] in fp32, reduced in
+// a fixed order afterwards. For an odd kH the upper half of the last pair multiplies whatever follows the dy tiles in
+// the stage (the first x tile); those accumulator rows are never read.
 struct ConvWg3Params {
   int32_t n_img;
+  int32_t W;
   int32_t s_blocks;                 // 64-position blocks per image (input positions)
-  int32_t kW, kH, chunks, pairs;
+  int32_t kH, chunks, pairs;
   int32_t splits, kb_total, kb_per_split;
   uint32_t idesc;
   uint32_t desc_hi, desc_lbo, k_advance;   // both operands K-major SW128
   float* partial;
   unsigned int* status;
-  int32_t center_tw;                // tap whose shift along W is zero: read from x itself (-1: none)
   int16_t row_shift[16];            // per kernel row th: (th - pad_h) * W
 };
 
-template <int KW>
+// 16-byte chunk of tap shift D cut out of the window [chunk c-1 | chunk c | chunk c+1] (12 words, 24 elements)
+template <int D>
+__device__ __forceinline__ uint4 conv_shifted_chunk(const uint32_t (&win)[12], bool row_start, bool row_end) {
+  constexpr int e = 8 + D;
+  uint32_t o[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    constexpr int q0 = e >> 1;
+    o[k] = (e & 1) ? __funnelshift_r(win[q0 + k], win[q0 + k + 1], 16) : win[q0 + k];
+  }
+  if (D < 0 && row_start) {
+#pragma unroll
+    for (int k = 0; k < -D; ++k) o[k >> 1] &= (k & 1) ? 0x0000FFFFu : 0xFFFF0000u;
+  }
+  if (D > 0 && row_end) {
+#pragma unroll
+    for (int k = 8 - D; k < 8; ++k) o[k >> 1] &= (k & 1) ? 0x0000FFFFu : 0xFFFF0000u;
+  }
+  return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+template <int KW, int PAD>
 __global__ void __launch_bounds__(kConvThreads, 1)
-conv_tc_wgrad_rows_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmX0,
+conv_tc_wgrad_rows_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmXh,
                           const __grid_constant__ CUtensorMap tmG, const __grid_constant__ ConvWg3Params p, int stages,
                           int stage_bytes, uint32_t tmem_cols) {
   constexpr int BN = KW * 64;
   constexpr int TILE = 64 * 128;              // 64 rows x 64 positions
+  constexpr int HALO = 64 * 16;               // 64 rows x 8 positions
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + stages * stage_bytes);
-  uint64_t* full = bars;
-  uint64_t* empty = bars + stages;
-  uint64_t* acc_full = bars + 2 * stages;
+  uint64_t* raw_full = bars;                  // TMA has landed: dy tiles, the unshifted x tile, the two halos
+  uint64_t* full = bars + stages;             // the shifted tap tiles are written (eight warps arrive)
+  uint64_t* empty = bars + 2 * stages;
+  uint64_t* acc_full = bars + 3 * stages;
   uint64_t* acc_empty = acc_full + 1;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 1);
 
@@ -642,7 +673,7 @@ conv_tc_wgrad_rows_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
   const int a_bytes = p.kH * TILE;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int s = 0; s < stages; ++s) { mbar_init(&raw_full[s], 1); mbar_init(&full[s], 8); mbar_init(&empty[s], 1); }
     mbar_init(acc_full, 1);
     mbar_init(acc_empty, 8);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -660,7 +691,7 @@ conv_tc_wgrad_rows_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
   if (warp == 0) {
     if (lane == 0) {
       tma_prefetch_desc(&tmX);
-      tma_prefetch_desc(&tmX0);
+      tma_prefetch_desc(&tmXh);
       tma_prefetch_desc(&tmG);
       uint32_t stage = 0, phase = 0;
       bool ok = true;
@@ -670,14 +701,12 @@ conv_tc_wgrad_rows_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
         for (int kb = kb_lo; kb < kb_hi; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, p.status, 0x20000u)) { ok = false; break; }
           const int img = kb / p.s_blocks, s0 = (kb % p.s_blocks) * 64;
-          const uint32_t sA = smem_base + stage * stage_bytes, sB = sA + a_bytes;
-          mbar_expect_tx(&full[stage], (uint32_t)((p.kH + KW) * TILE));
-          for (int th = 0; th < p.kH; ++th) tma_load_4d(sA + th * TILE, &tmG, s0 - p.row_shift[th], 0, img, 0, &full[stage]);
-#pragma unroll
-          for (int tw = 0; tw < KW; ++tw) {
-            if (tw == p.center_tw) tma_load_4d(sB + tw * TILE, &tmX0, s0, chunk * 64, img, 0, &full[stage]);
-            else tma_load_4d(sB + tw * TILE, &tmX, s0, chunk * 64, img, tw, &full[stage]);
-          }
+          const uint32_t sA = smem_base + stage * stage_bytes, sB = sA + a_bytes, sH = sB + KW * TILE;
+          mbar_expect_tx(&raw_full[stage], (uint32_t)((p.kH + 1) * TILE + 2 * HALO));
+          for (int th = 0; th < p.kH; ++th) tma_load_4d(sA + th * TILE, &tmG, s0 - p.row_shift[th], 0, img, 0, &raw_full[stage]);
+          tma_load_4d(sB + PAD * TILE, &tmX, s0, chunk * 64, img, 0, &raw_full[stage]);
+          tma_load_4d(sH, &tmXh, s0 - 8, chunk * 64, img, 0, &raw_full[stage]);
+          tma_load_4d(sH + HALO, &tmXh, s0 + 64, chunk * 64, img, 0, &raw_full[stage]);
           if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
         }
       }
@@ -692,7 +721,10 @@ conv_tc_wgrad_rows_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
         if (!mbar_wait(acc_empty, acc_phase ^ 1u, p.status, 0x40000u)) { ok = false; break; }
         tc_fence_after();
         for (int kb = kb_lo; kb < kb_hi; ++kb) {
-          if (!mbar_wait(&full[stage], phase, p.status, 0x80000u)) { ok = false; break; }
+          if (!mbar_wait(&raw_full[stage], phase, p.status, 0x80000u) || !mbar_wait(&full[stage], phase, p.status, 0x80000u)) {
+            ok = false;
+            break;
+          }
           tc_fence_after();
           const uint32_t sA = smem_base + stage * stage_bytes, sB = sA + a_bytes;
           const uint32_t b_lo32 = ((sB >> 4) & 0x3FFFu) | p.desc_lbo;
@@ -714,10 +746,60 @@ conv_tc_wgrad_rows_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
     }
   } else if (warp >= 4) {
     const int q = warp & 3, half = (warp - 4) >> 2;   // lane quarter; which half of the BN columns
+    const int tid = threadIdx.x - 128;                // 0..255 over the eight warps
     constexpr int COLS = BN / 2;
-    uint32_t acc_phase = 0;
+    uint32_t stage = 0, phase = 0, acc_phase = 0;
     bool ok = true;
     for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+      const int z = item / p.chunks;
+      const int kb_lo = z * p.kb_per_split, kb_hi = min(p.kb_total, kb_lo + p.kb_per_split);
+      // main loop: the tap tiles of every stage
+      for (int kb = kb_lo; kb < kb_hi; ++kb) {
+        if (!mbar_wait_warp(&raw_full[stage], phase, p.status, 0x200000u)) { ok = false; break; }
+        if (KW > 1) {
+          uint8_t* sB = smem_gen + stage * stage_bytes + a_bytes;
+          const uint8_t* centre = sB + PAD * TILE;
+          const uint8_t* halo = sB + KW * TILE;
+          const int base_w = ((kb % p.s_blocks) * 64) % p.W;
+#pragma unroll
+          for (int i = 0; i < 2; ++i) {
+            const int task = tid + i * 256;
+            const int r = task >> 3, c = task & 7;
+            const int w0 = (base_w + 8 * c) % p.W;
+            const int row_off = (r >> 3) * 1024 + (r & 7) * 128;
+            const int sw = r & 7;
+            const uint4 v0 = *reinterpret_cast<const uint4*>(centre + row_off + ((c ^ sw) << 4));
+            const uint4 vm = c > 0 ? *reinterpret_cast<const uint4*>(centre + row_off + (((c - 1) ^ sw) << 4))
+                                   : *reinterpret_cast<const uint4*>(halo + r * 16);
+            const uint4 vp = c < 7 ? *reinterpret_cast<const uint4*>(centre + row_off + (((c + 1) ^ sw) << 4))
+                                   : *reinterpret_cast<const uint4*>(halo + HALO + r * 16);
+            const uint32_t win[12] = {vm.x, vm.y, vm.z, vm.w, v0.x, v0.y, v0.z, v0.w, vp.x, vp.y, vp.z, vp.w};
+            const bool row_start = w0 == 0, row_end = w0 == p.W - 8;
+            const int dst_off = row_off + ((c ^ sw) << 4);
+#pragma unroll
+            for (int tw = 0; tw < KW; ++tw) {
+              if (tw == PAD) continue;
+              uint4 o;
+              // tw - PAD is a compile-time constant after unrolling; spelled out so that the template argument is one
+              switch (tw - PAD) {
+                case -3: o = conv_shifted_chunk<-3>(win, row_start, row_end); break;
+                case -2: o = conv_shifted_chunk<-2>(win, row_start, row_end); break;
+                case -1: o = conv_shifted_chunk<-1>(win, row_start, row_end); break;
+                case 1: o = conv_shifted_chunk<1>(win, row_start, row_end); break;
+                case 2: o = conv_shifted_chunk<2>(win, row_start, row_end); break;
+                default: o = conv_shifted_chunk<3>(win, row_start, row_end); break;
+              }
+              *reinterpret_cast<uint4*>(sB + tw * TILE + dst_off) = o;
+            }
+          }
+          fence_proxy_async_smem();
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&full[stage]);
+        if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
+      }
+      if (!ok) break;
+      // epilogue: the accumulators of this item
       if (!mbar_wait_warp(acc_full, acc_phase, p.status, 0x100000u)) { ok = false; break; }
       tc_fence_after();
       const int row = q * 32 + lane;
@@ -751,28 +833,40 @@ conv_tc_wgrad_rows_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
   }
 }
 
-// dw[kw,kh,ci,co] = sum over splits (ascending) of partial[z][chunk][th / 2][(th & 1)*64 + co][tw*64 + ci % 64]
+// dw[kw,kh,ci,co] = sum over splits of partial[z][chunk][th / 2][(th & 1)*64 + co][tw*64 + ci % 64]. A block takes 64
+// consecutive columns of the partial layout (coalesced reads) in four slices of the split index; every slice adds its
+// splits in ascending order and the four slice sums are combined in a fixed order.
 template <typename T>
 __global__ void __launch_bounds__(256) conv_wgrad_rows_reduce_kernel(T* __restrict__ dw, const float* __restrict__ partial,
                                                                      int kW, int kH, int cin, int cout, int flip, int chunks,
                                                                      int pairs, int splits) {
-  const int64_t total = (int64_t)kW * kH * cin * cout;
+  __shared__ float part[4][64];
   const int bn = kW * 64;
   const int64_t per_split = (int64_t)chunks * pairs * 128 * bn;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    int64_t r = i;
-    const int kw = (int)(r % kW); r /= kW;
-    const int kh = (int)(r % kH); r /= kH;
-    const int ci = (int)(r % cin);
-    const int co = (int)(r / cin);
-    const int tw = flip ? kw : kW - 1 - kw, th = flip ? kh : kH - 1 - kh;
-    const int64_t off = ((((int64_t)(ci / 64) * pairs + th / 2) * 128) + (th & 1) * 64 + co) * bn + tw * 64 + ci % 64;
+  const int col = threadIdx.x & 63, zs = threadIdx.x >> 6;
+  for (int64_t base = (int64_t)blockIdx.x * 64; base < per_split; base += (int64_t)gridDim.x * 64) {
+    const int64_t off = base + col;
     float s = 0.f;
-    for (int z = 0; z < splits; ++z) s += partial[(int64_t)z * per_split + off];
-    dw[i] = from_f32<T>(s);
+#pragma unroll 4
+    for (int z = zs; z < splits; z += 4) s += __ldcs(partial + (int64_t)z * per_split + off);
+    part[zs][col] = s;
+    __syncthreads();
+    if (zs == 0) {
+      const float total = ((part[0][col] + part[1][col]) + part[2][col]) + part[3][col];
+      const int c = (int)(off % bn);
+      int64_t r = off / bn;
+      const int row = (int)(r % 128); r /= 128;
+      const int pi = (int)(r % pairs);
+      const int chunk = (int)(r / pairs);
+      const int th = 2 * pi + (row >> 6), co = row & 63, tw = c >> 6, ci = chunk * 64 + (c & 63);
+      if (th < kH && co < cout && ci < cin) {
+        const int kw = flip ? tw : kW - 1 - tw, kh = flip ? th : kH - 1 - th;
+        dw[kw + (int64_t)kW * (kh + (int64_t)kH * (ci + (int64_t)cin * co))] = from_f32<T>(total);
+      }
+    }
+    __syncthreads();
   }
 }
-
 
 // ----------------------------------------------------------------------------------------------
 // host side
@@ -783,7 +877,7 @@ struct ConvGemm {
 };
 
 static bool bf16_map_4d(CUtensorMap* map, const void* ptr, int64_t d0, int64_t d1, int64_t d2, int64_t d3,
-                        int box0, int box1) {
+                        int box0, int box1, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
   TensorMapEncodeFn enc = tensor_map_encoder();
   if (!enc) return false;
   cuuint64_t dims[4] = {(cuuint64_t)d0, (cuuint64_t)d1, (cuuint64_t)d2, (cuuint64_t)d3};
@@ -791,7 +885,7 @@ static bool bf16_map_4d(CUtensorMap* map, const void* ptr, int64_t d0, int64_t d
   cuuint32_t box[4] = {(cuuint32_t)box0, (cuuint32_t)box1, 1, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr,
-             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 static bool bf16_map_2d(CUtensorMap* map, const void* ptr, int64_t d0, int64_t d1, int box0, int box1) {
@@ -989,13 +1083,13 @@ struct Wg3Plan {
 };
 static Wg3Plan wg3_plan(const ConvGeom& g) {
   Wg3Plan w{};
-  if (g.k[0] > 4 || g.k[1] > 16 || g.cout > 64) return w;
+  if (g.k[0] > 4 || g.k[1] > 16 || g.cout > 64 || g.pad_lo[0] < 0 || g.pad_lo[0] >= g.k[0] || g.in[0] % 8 != 0) return w;
   w.pairs = (g.k[1] + 1) / 2;
   const int cols = w.pairs * g.k[0] * 64;
   if (cols > 512) return w;
   w.tmem_cols = 32;
   while ((int)w.tmem_cols < cols) w.tmem_cols *= 2;
-  w.stage_bytes = (g.k[1] + g.k[0]) * 64 * 128;
+  w.stage_bytes = (g.k[1] + g.k[0]) * 64 * 128 + 2 * 64 * 16;   // dy tiles, tap tiles, the two 8-position halos of x
   w.stages = (200 * 1024) / w.stage_bytes;
   if (w.stages > 8) w.stages = 8;
   if (w.stages < 2) return w;
@@ -1040,17 +1134,11 @@ int32_t conv_tc_wgrad(void* dw, const void* x, const void* gy, const ConvGeom& g
   T* copies = reinterpret_cast<T*>(ws);
   float* partial = reinterpret_cast<float*>(ws + copies_bytes(f));
   const int64_t rows = (int64_t)f.Hi * f.Ck * f.N;
-  const Wg2Plan w2 = wg2_plan(g);
-  // the wide-N kernel reads the unshifted tap straight from x, so that copy is not made
-  const int skip = (w2.ok && f.pad_w >= 0 && f.pad_w < f.kW) ? f.pad_w : -1;
-  if (!launch_shift_copies_vec(copies, x, f.W, rows, f.kW, f.pad_w, flat_grid_tc(rows * (f.W / 8)), st, skip))
-    conv_shift_copies_kernel<T><<<flat_grid_tc(rows * ((f.W + 7) / 8)), 256, 0, st>>>(copies, (const T*)x, f.W, rows, f.kW, f.pad_w, skip);
-  LB2_CHECK_LAUNCH("conv_tc shifted copies");
   const Wg3Plan w3 = wg3_plan(g);
-  if (w3.ok) {
+  if (w3.ok) {   // no copies of x: the taps are cut out of the unshifted tile in shared memory
     ConvWg3Params q{};
-    q.n_img = g.batch; q.s_blocks = w3.s_blocks;
-    q.kW = f.kW; q.kH = f.kH; q.chunks = w3.chunks; q.pairs = w3.pairs;
+    q.n_img = g.batch; q.W = f.W; q.s_blocks = w3.s_blocks;
+    q.kH = f.kH; q.chunks = w3.chunks; q.pairs = w3.pairs;
     q.splits = w3.splits; q.kb_total = w3.kb_total; q.kb_per_split = w3.kb_per_split;
     q.idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)((f.kW * 64) >> 3) << 17) | ((uint32_t)(kConvBM >> 4) << 24);
     q.desc_hi = (uint32_t)((1024u >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
@@ -1060,10 +1148,9 @@ int32_t conv_tc_wgrad(void* dw, const void* x, const void* gy, const ConvGeom& g
     q.status = device_status_word();
     LB2_REQUIRE(q.status != nullptr, LB2_LAUNCH_FAIL, "conv_tc: device status word unavailable");
     for (int th = 0; th < f.kH; ++th) q.row_shift[th] = (int16_t)((th - f.pad_h) * f.W);
-    q.center_tw = skip;
-    CUtensorMap mX3, mX03, mG3;
-    if (!bf16_map_4d(&mX3, copies, (int64_t)f.W * f.Hi, f.Ck, f.N, f.kW, 64, 64) ||
-        !bf16_map_4d(&mX03, x, (int64_t)f.W * f.Hi, f.Ck, f.N, 1, 64, 64) ||
+    CUtensorMap mX3, mXh3, mG3;
+    if (!bf16_map_4d(&mX3, x, (int64_t)f.W * f.Hi, f.Ck, f.N, 1, 64, 64) ||
+        !bf16_map_4d(&mXh3, x, (int64_t)f.W * f.Hi, f.Ck, f.N, 1, 8, 64, CU_TENSOR_MAP_SWIZZLE_NONE) ||
         !bf16_map_4d(&mG3, gy, (int64_t)g.out[0] * g.out[1], g.cout, g.batch, 1, 64, 64))
       return fail(LB2_LAUNCH_FAIL, "conv_tc: cuTensorMapEncodeTiled failed");
     const int smem3 = w3.stages * w3.stage_bytes + 1024 + 256 + 64 * 8;
@@ -1072,19 +1159,36 @@ int32_t conv_tc_wgrad(void* dw, const void* x, const void* gy, const ConvGeom& g
     auto launch3 = [&](auto kernel) -> int32_t {
       cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem3);
       if (e != cudaSuccess) return fail(LB2_LAUNCH_FAIL, "conv_tc: cannot reserve %d bytes of shared memory: %s", smem3, cudaGetErrorString(e));
-      kernel<<<grid3, kConvThreads, smem3, st>>>(mX3, mX03, mG3, q, w3.stages, w3.stage_bytes, w3.tmem_cols);
+      kernel<<<grid3, kConvThreads, smem3, st>>>(mX3, mXh3, mG3, q, w3.stages, w3.stage_bytes, w3.tmem_cols);
       LB2_CHECK_LAUNCH("conv_tc_wgrad_rows");
       return LB2_OK;
     };
-    int32_t rc3 = f.kW == 1 ? launch3(conv_tc_wgrad_rows_kernel<1>) : f.kW == 2 ? launch3(conv_tc_wgrad_rows_kernel<2>)
-                : f.kW == 3 ? launch3(conv_tc_wgrad_rows_kernel<3>) : launch3(conv_tc_wgrad_rows_kernel<4>);
+    int32_t rc3 = LB2_OK;
+    switch (f.kW * 4 + f.pad_w) {
+      case 1 * 4 + 0: rc3 = launch3(conv_tc_wgrad_rows_kernel<1, 0>); break;
+      case 2 * 4 + 0: rc3 = launch3(conv_tc_wgrad_rows_kernel<2, 0>); break;
+      case 2 * 4 + 1: rc3 = launch3(conv_tc_wgrad_rows_kernel<2, 1>); break;
+      case 3 * 4 + 0: rc3 = launch3(conv_tc_wgrad_rows_kernel<3, 0>); break;
+      case 3 * 4 + 1: rc3 = launch3(conv_tc_wgrad_rows_kernel<3, 1>); break;
+      case 3 * 4 + 2: rc3 = launch3(conv_tc_wgrad_rows_kernel<3, 2>); break;
+      case 4 * 4 + 0: rc3 = launch3(conv_tc_wgrad_rows_kernel<4, 0>); break;
+      case 4 * 4 + 1: rc3 = launch3(conv_tc_wgrad_rows_kernel<4, 1>); break;
+      case 4 * 4 + 2: rc3 = launch3(conv_tc_wgrad_rows_kernel<4, 2>); break;
+      default: rc3 = launch3(conv_tc_wgrad_rows_kernel<4, 3>); break;
+    }
     if (rc3 != LB2_OK) return rc3;
-    const int64_t nw3 = (int64_t)g.k[0] * g.k[1] * g.cin * g.cout;
-    conv_wgrad_rows_reduce_kernel<T><<<flat_grid_tc(nw3), 256, 0, st>>>((T*)dw, partial, g.k[0], g.k[1], g.cin, g.cout, g.flip, w3.chunks,
-                                                                      w3.pairs, w3.splits);
+    const int64_t per_split3 = (int64_t)w3.chunks * w3.pairs * 128 * (f.kW * 64);
+    conv_wgrad_rows_reduce_kernel<T><<<(unsigned)(per_split3 / 64), 256, 0, st>>>((T*)dw, partial, g.k[0], g.k[1], g.cin, g.cout, g.flip,
+                                                                               w3.chunks, w3.pairs, w3.splits);
     LB2_CHECK_LAUNCH("conv_wgrad_rows_reduce");
     return LB2_OK;
   }
+  const Wg2Plan w2 = wg2_plan(g);
+  // the wide-N kernel reads the unshifted tap straight from x, so that copy is not made
+  const int skip = (w2.ok && f.pad_w >= 0 && f.pad_w < f.kW) ? f.pad_w : -1;
+  if (!launch_shift_copies_vec(copies, x, f.W, rows, f.kW, f.pad_w, flat_grid_tc(rows * (f.W / 8)), st, skip))
+    conv_shift_copies_kernel<T><<<flat_grid_tc(rows * ((f.W + 7) / 8)), 256, 0, st>>>(copies, (const T*)x, f.W, rows, f.kW, f.pad_w, skip);
+  LB2_CHECK_LAUNCH("conv_tc shifted copies");
   if (w2.ok) {
     ConvWg2Params q{};
     q.n_img = g.batch; q.s_blocks = w2.s_blocks;

@@ -350,6 +350,18 @@ TC_CONV_CASES = [
     ((16, 6), (3, 3), 64, 96, 1, False),
     ((8, 40), (3, 5), 130, 48, (1, 1, 2, 2), False),
     ((12, 9), (3, 3), 24, 20, 1, False),     # W % 4 == 0 only: Float32 tensor-core path, bf16 direct path
+    # at most 64 output channels: the bf16 filter gradient stacks kernel rows along M and cuts the taps out of the
+    # unshifted tile in shared memory; one case per (kernel width, left padding) kind, odd and even kernel heights,
+    # a row of a single 16-byte chunk, fewer than 64 positions, two channel chunks
+    ((8, 5), (2, 2), 16, 24, (0, 1, 0, 1), False),
+    ((24, 6), (2, 3), 32, 64, (1, 0, 1, 1), True),
+    ((16, 7), (3, 1), 64, 48, (0, 2, 0, 0), False),
+    ((16, 5), (3, 2), 24, 32, (2, 0, 1, 0), False),
+    ((16, 6), (2, 4), 24, 32, (1, 0, 2, 1), False),
+    ((32, 4), (4, 2), 40, 56, (1, 2, 0, 1), False),
+    ((16, 6), (4, 2), 16, 16, (3, 0, 1, 0), True),
+    ((16, 9), (1, 3), 128, 64, (0, 0, 1, 1), False),
+    ((8, 3), (3, 3), 8, 8, 1, False),
 ]
 
 
