@@ -165,6 +165,7 @@ struct ConvTc2Params {
   int32_t W, S_out, n_img, n_out;
   int32_t tiles_m, tiles_n, kW, kH, chunks, pad_w;
   int32_t stages;
+  int32_t edge_rows;          // accumulator rows a neighbouring lane quarter needs per tap: max(pad_w, kW - 1 - pad_w)
   int32_t out_stage_stride;   // bytes of output staging per epilogue group (one tile, or two with a pre-activation)
   uint32_t idesc;
   uint32_t a_desc_hi, a_desc_lbo, a_k_advance;
@@ -207,12 +208,13 @@ conv_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
   uint64_t* acc_empty = acc_full + 2;
   uint64_t* b_full = acc_empty + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(b_full + 1);
-  // accumulator rows that cross a warp boundary: edge[group][half][quarter][tw][3 rows][32 cols]
+  // accumulator rows that cross a warp boundary: edge[group][half][quarter][tw][edge_rows][32 cols]
   float* edge = reinterpret_cast<float*>(after + 512);
   // one flag per epilogue group, written and read only by that group's warps around the group's own barrier (the
   // other group learns of a failure through its own bounded waits)
   volatile int* abort_flag = reinterpret_cast<volatile int*>(after + 448);
-  constexpr int EDGE_Q = KW * 3 * 32;   // floats per (group, half, quarter)
+  const int ER = p.edge_rows;
+  const int EDGE_Q = KW * ER * 32;   // floats per (group, half, quarter)
   // output staging for the TMA store: per group [64 channels][112 positions] bf16, one tile for y and one for the
   // pre-activation. Rows of a tile start 16 bytes off a 32-byte sector in global memory, so direct
   // 2-byte stores from registers would leave half-written sectors; the tiled store writes whole runs.
@@ -338,7 +340,7 @@ conv_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
           if (d < 0 && lane >= 32 + d) idx = lane - (32 + d);
           if (d > 0 && lane < d) idx = lane;
           if (idx >= 0) {
-            float* e = eb + (tw * 3 + idx) * 32;
+            float* e = eb + (tw * ER + idx) * 32;
 #pragma unroll
             for (int j = 0; j < 32; ++j) e[j] = __uint_as_float(rt[j]);
           }
@@ -370,7 +372,7 @@ conv_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
           const float* en = nullptr;
           if (!local && qn >= 0 && qn < 4) {
             const float* nb = edge + (size_t)((parity * 2 + half) * 4 + qn) * EDGE_Q;
-            en = nb + (tw * 3 + (src < 0 ? lane : src - 32)) * 32;
+            en = nb + (tw * ER + (src < 0 ? lane : src - 32)) * 32;
           }
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
@@ -488,8 +490,7 @@ conv_tc_wgrad2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
       for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
         const int grp = item % groups, z = item / groups;
         const int ct = grp % p.co_tiles, chunk = (grp / p.co_tiles) % p.chunks, th = grp / (p.co_tiles * p.chunks);
-        const int kb_lo = z * p.kb_per_split, kb_hi = min(p.kb_total, kb_lo + p.kb_per_split);
-        for (int kb = kb_lo; kb < kb_hi; ++kb) {
+        for (int kb = z; kb < p.kb_total; kb += p.splits) {   // interleaved: concurrent CTAs read neighbouring blocks
           if (!mbar_wait(&empty[stage], phase ^ 1u, p.status, 0x20000u)) { ok = false; break; }
           const int img = kb / p.s_blocks, s0 = (kb % p.s_blocks) * 64;
           const uint32_t sA = smem_base + stage * STAGE_BYTES, sB = sA + A_BYTES;
@@ -511,11 +512,10 @@ conv_tc_wgrad2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
       bool ok = true;
       for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
         const int z = item / groups;
-        const int kb_lo = z * p.kb_per_split, kb_hi = min(p.kb_total, kb_lo + p.kb_per_split);
         if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1u, p.status, 0x40000u)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = kb_lo; kb < kb_hi; ++kb) {
+        for (int kb = z; kb < p.kb_total; kb += p.splits) {   // interleaved: concurrent CTAs read neighbouring blocks
           if (!mbar_wait(&full[stage], phase, p.status, 0x80000u)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sA = smem_base + stage * STAGE_BYTES, sB = sA + A_BYTES;
@@ -525,7 +525,7 @@ conv_tc_wgrad2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
           for (int ks = 0; ks < 4; ++ks) {
             const uint64_t ad = ((uint64_t)p.desc_hi << 32) | (uint64_t)(a_lo32 + ks * p.k_advance);
             const uint64_t bd = ((uint64_t)p.desc_hi << 32) | (uint64_t)(b_lo32 + ks * p.k_advance);
-            umma<false>(d_tmem, ad, bd, p.idesc, (kb > kb_lo || ks != 0) ? 1u : 0u);
+            umma<false>(d_tmem, ad, bd, p.idesc, (kb != z || ks != 0) ? 1u : 0u);
           }
           umma_commit(&empty[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -612,8 +612,10 @@ __global__ void __launch_bounds__(256) conv_wgrad2_reduce_kernel(T* __restrict__
 // multiple of 8 and blocks start on a multiple of 64, so a row end can only fall on a chunk boundary), stored at the
 // chunk's swizzled place in the tap's tile. Operand traffic per block: (kH + 1) * 8 KB + 2 KB.
 //
-// A work item is (64-channel chunk, K split); partial[z][chunk][pair][(th & 1)*64 + co][tw*64 + ci] in fp32, reduced in
-// a fixed order afterwards. For an odd kH the upper half of the last pair multiplies whatever follows the dy tiles in
+// A work item is (64-channel chunk, K split z); split z takes the position blocks z, z + splits, ... so that the CTAs
+// running at the same time read neighbouring blocks of the same channel rows (whole DRAM pages get used while they are
+// open; with one contiguous range per CTA every 128-byte row piece came from a page of its own).
+// partial[z][chunk][pair][(th & 1)*64 + co][tw*64 + ci] in fp32, reduced in a fixed order afterwards. For an odd kH the upper half of the last pair multiplies whatever follows the dy tiles in
 // the stage (the first x tile); those accumulator rows are never read.
 struct ConvWg3Params {
   int32_t n_img;
@@ -697,8 +699,7 @@ conv_tc_wgrad_rows_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
       bool ok = true;
       for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
         const int chunk = item % p.chunks, z = item / p.chunks;
-        const int kb_lo = z * p.kb_per_split, kb_hi = min(p.kb_total, kb_lo + p.kb_per_split);
-        for (int kb = kb_lo; kb < kb_hi; ++kb) {
+        for (int kb = z; kb < p.kb_total; kb += p.splits) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, p.status, 0x20000u)) { ok = false; break; }
           const int img = kb / p.s_blocks, s0 = (kb % p.s_blocks) * 64;
           const uint32_t sA = smem_base + stage * stage_bytes, sB = sA + a_bytes, sH = sB + KW * TILE;
@@ -717,10 +718,9 @@ conv_tc_wgrad_rows_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
       bool ok = true;
       for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
         const int z = item / p.chunks;
-        const int kb_lo = z * p.kb_per_split, kb_hi = min(p.kb_total, kb_lo + p.kb_per_split);
         if (!mbar_wait(acc_empty, acc_phase ^ 1u, p.status, 0x40000u)) { ok = false; break; }
         tc_fence_after();
-        for (int kb = kb_lo; kb < kb_hi; ++kb) {
+        for (int kb = z; kb < p.kb_total; kb += p.splits) {
           if (!mbar_wait(&raw_full[stage], phase, p.status, 0x80000u) || !mbar_wait(&full[stage], phase, p.status, 0x80000u)) {
             ok = false;
             break;
@@ -734,7 +734,7 @@ conv_tc_wgrad_rows_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
             for (int ks = 0; ks < 4; ++ks) {
               const uint64_t ad = ((uint64_t)p.desc_hi << 32) | (uint64_t)(a_lo32 + ks * p.k_advance);
               const uint64_t bd = ((uint64_t)p.desc_hi << 32) | (uint64_t)(b_lo32 + ks * p.k_advance);
-              umma<false>(tmem_base + pi * BN, ad, bd, p.idesc, (kb > kb_lo || ks != 0) ? 1u : 0u);
+              umma<false>(tmem_base + pi * BN, ad, bd, p.idesc, (kb != z || ks != 0) ? 1u : 0u);
             }
           }
           umma_commit(&empty[stage]);
@@ -752,9 +752,8 @@ conv_tc_wgrad_rows_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
     bool ok = true;
     for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
       const int z = item / p.chunks;
-      const int kb_lo = z * p.kb_per_split, kb_hi = min(p.kb_total, kb_lo + p.kb_per_split);
       // main loop: the tap tiles of every stage
-      for (int kb = kb_lo; kb < kb_hi; ++kb) {
+      for (int kb = z; kb < p.kb_total; kb += p.splits) {
         if (!mbar_wait_warp(&raw_full[stage], phase, p.status, 0x200000u)) { ok = false; break; }
         if (KW > 1) {
           uint8_t* sB = smem_gen + stage * stage_bytes + a_bytes;
@@ -917,11 +916,13 @@ static int conv_chunks(int ck) { return (ck + 63) / 64; }
 
 // shift-in-epilogue kernel: kernel width <= 4, filter resident next to at least 3 A stages and the edge buffers
 // A-ring depth; `with_preact` = the launch also stages a pre-activation tile per epilogue group
+static int conv_edge_rows(const ConvGemm& c) { return c.pad_w > c.kW - 1 - c.pad_w ? c.pad_w : c.kW - 1 - c.pad_w; }
+static int conv_edge_bytes(const ConvGemm& c) { return 2 * 2 * 4 * c.kW * conv_edge_rows(c) * 32 * 4; }
 static int conv_fwd2_stages(const ConvGemm& c, bool with_preact = true) {
   if (c.kW > 4 || c.kH > 16) return 0;
   const int resident = c.kW * c.kH * conv_chunks(c.Ck) * 64 * 128;
-  const int edges = 2 * 2 * 4 * c.kW * 3 * 32 * 4 + 2 * (with_preact ? 2 : 1) * 64 * (kConvBM - 16) * 2;   // edge rows + output staging of both epilogue groups
-  int st = (198 * 1024 - resident - edges) / (kConvBM * 128);
+  const int edges = conv_edge_bytes(c) + 2 * (with_preact ? 2 : 1) * 64 * (kConvBM - 16) * 2;   // edge rows + output staging of both epilogue groups
+  int st = (224 * 1024 - resident - edges) / (kConvBM * 128);
   return st > 8 ? 8 : st;
 }
 static bool conv_use_fwd2(const ConvGemm& c) { return conv_fwd2_stages(c) >= 3; }
@@ -973,6 +974,7 @@ static int32_t run_conv_gemm(void* out, void* preact, const void* bias, int32_t 
     q.tiles_n = (c.Cn + 63) / 64;
     q.kW = c.kW; q.kH = c.kH; q.chunks = conv_chunks(c.Ck); q.pad_w = c.pad_w;
     q.stages = conv_fwd2_stages(c, preact != nullptr);
+    q.edge_rows = conv_edge_rows(c);
     q.out_stage_stride = (preact != nullptr ? 2 : 1) * 64 * kTileOut * 2;
     for (int th = 0; th < c.kH; ++th) q.row_shift[th] = (int16_t)((th - c.pad_h) * c.W);
     q.a_desc_hi = (uint32_t)((1024u >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
@@ -990,7 +992,7 @@ static int32_t run_conv_gemm(void* out, void* preact, const void* bias, int32_t 
         !bf16_map_out(&mY2, out, q.S_out, c.Cn, c.N) || !bf16_map_out(&mP2, preact != nullptr ? preact : out, q.S_out, c.Cn, c.N))
       return fail(LB2_LAUNCH_FAIL, "conv_tc: cuTensorMapEncodeTiled failed");
     const int num_b = c.kW * c.kH * q.chunks;
-    const int smem2 = num_b * 64 * 128 + q.stages * kConvBM * 128 + 512 + 2 * 2 * 4 * c.kW * 3 * 32 * 4 + 2 * q.out_stage_stride + 1024 + 256;
+    const int smem2 = num_b * 64 * 128 + q.stages * kConvBM * 128 + 512 + conv_edge_bytes(c) + 2 * q.out_stage_stride + 1024 + 256;
     const int tiles_per_n2 = q.tiles_m * q.n_img;
     int per_n2 = sm_count() / q.tiles_n;
     if (per_n2 > tiles_per_n2) per_n2 = tiles_per_n2;
