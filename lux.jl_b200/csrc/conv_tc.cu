@@ -489,8 +489,9 @@ conv_tc_wgrad2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
       bool ok = true;
       for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
         const int grp = item % groups, z = item / groups;
+        const int kb_lo = z * p.kb_per_split, kb_hi = min(p.kb_total, kb_lo + p.kb_per_split);
         const int ct = grp % p.co_tiles, chunk = (grp / p.co_tiles) % p.chunks, th = grp / (p.co_tiles * p.chunks);
-        for (int kb = z; kb < p.kb_total; kb += p.splits) {   // interleaved: concurrent CTAs read neighbouring blocks
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, p.status, 0x20000u)) { ok = false; break; }
           const int img = kb / p.s_blocks, s0 = (kb % p.s_blocks) * 64;
           const uint32_t sA = smem_base + stage * STAGE_BYTES, sB = sA + A_BYTES;
@@ -512,10 +513,11 @@ conv_tc_wgrad2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
       bool ok = true;
       for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
         const int z = item / groups;
+        const int kb_lo = z * p.kb_per_split, kb_hi = min(p.kb_total, kb_lo + p.kb_per_split);
         if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1u, p.status, 0x40000u)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = z; kb < p.kb_total; kb += p.splits) {   // interleaved: concurrent CTAs read neighbouring blocks
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {
           if (!mbar_wait(&full[stage], phase, p.status, 0x80000u)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sA = smem_base + stage * STAGE_BYTES, sB = sA + A_BYTES;
@@ -525,7 +527,7 @@ conv_tc_wgrad2_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
           for (int ks = 0; ks < 4; ++ks) {
             const uint64_t ad = ((uint64_t)p.desc_hi << 32) | (uint64_t)(a_lo32 + ks * p.k_advance);
             const uint64_t bd = ((uint64_t)p.desc_hi << 32) | (uint64_t)(b_lo32 + ks * p.k_advance);
-            umma<false>(d_tmem, ad, bd, p.idesc, (kb != z || ks != 0) ? 1u : 0u);
+            umma<false>(d_tmem, ad, bd, p.idesc, (kb > kb_lo || ks != 0) ? 1u : 0u);
           }
           umma_commit(&empty[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -612,11 +614,11 @@ __global__ void __launch_bounds__(256) conv_wgrad2_reduce_kernel(T* __restrict__
 // multiple of 8 and blocks start on a multiple of 64, so a row end can only fall on a chunk boundary), stored at the
 // chunk's swizzled place in the tap's tile. Operand traffic per block: (kH + 1) * 8 KB + 2 KB.
 //
-// A work item is (64-channel chunk, K split z); split z takes the position blocks z, z + splits, ... so that the CTAs
-// running at the same time read neighbouring blocks of the same channel rows (whole DRAM pages get used while they are
-// open; with one contiguous range per CTA every 128-byte row piece came from a page of its own).
-// partial[z][chunk][pair][(th & 1)*64 + co][tw*64 + ci] in fp32, reduced in a fixed order afterwards. For an odd kH the upper half of the last pair multiplies whatever follows the dy tiles in
-// the stage (the first x tile); those accumulator rows are never read.
+// A work item is (64-channel chunk, K split z) with one contiguous range of position blocks per split (measured faster
+// than interleaved blocks: consecutive blocks of a CTA share the shifted dy rows and 256-byte L2 sectors).
+// partial[z][chunk][pair][(th & 1)*64 + co][tw*64 + ci] in fp32, reduced in a fixed order afterwards. For an odd kH the
+// upper half of the last pair multiplies whatever follows the dy tiles in the stage (the first x tile); those accumulator
+// rows are never read.
 struct ConvWg3Params {
   int32_t n_img;
   int32_t W;
@@ -699,7 +701,8 @@ conv_tc_wgrad_rows_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
       bool ok = true;
       for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
         const int chunk = item % p.chunks, z = item / p.chunks;
-        for (int kb = z; kb < p.kb_total; kb += p.splits) {
+        const int kb_lo = z * p.kb_per_split, kb_hi = min(p.kb_total, kb_lo + p.kb_per_split);
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, p.status, 0x20000u)) { ok = false; break; }
           const int img = kb / p.s_blocks, s0 = (kb % p.s_blocks) * 64;
           const uint32_t sA = smem_base + stage * stage_bytes, sB = sA + a_bytes, sH = sB + KW * TILE;
@@ -718,9 +721,10 @@ conv_tc_wgrad_rows_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
       bool ok = true;
       for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
         const int z = item / p.chunks;
+        const int kb_lo = z * p.kb_per_split, kb_hi = min(p.kb_total, kb_lo + p.kb_per_split);
         if (!mbar_wait(acc_empty, acc_phase ^ 1u, p.status, 0x40000u)) { ok = false; break; }
         tc_fence_after();
-        for (int kb = z; kb < p.kb_total; kb += p.splits) {
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {
           if (!mbar_wait(&raw_full[stage], phase, p.status, 0x80000u) || !mbar_wait(&full[stage], phase, p.status, 0x80000u)) {
             ok = false;
             break;
@@ -734,7 +738,7 @@ conv_tc_wgrad_rows_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
             for (int ks = 0; ks < 4; ++ks) {
               const uint64_t ad = ((uint64_t)p.desc_hi << 32) | (uint64_t)(a_lo32 + ks * p.k_advance);
               const uint64_t bd = ((uint64_t)p.desc_hi << 32) | (uint64_t)(b_lo32 + ks * p.k_advance);
-              umma<false>(tmem_base + pi * BN, ad, bd, p.idesc, (kb != z || ks != 0) ? 1u : 0u);
+              umma<false>(tmem_base + pi * BN, ad, bd, p.idesc, (kb > kb_lo || ks != 0) ? 1u : 0u);
             }
           }
           umma_commit(&empty[stage]);
@@ -752,8 +756,9 @@ conv_tc_wgrad_rows_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
     bool ok = true;
     for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
       const int z = item / p.chunks;
+      const int kb_lo = z * p.kb_per_split, kb_hi = min(p.kb_total, kb_lo + p.kb_per_split);
       // main loop: the tap tiles of every stage
-      for (int kb = z; kb < p.kb_total; kb += p.splits) {
+      for (int kb = kb_lo; kb < kb_hi; ++kb) {
         if (!mbar_wait_warp(&raw_full[stage], phase, p.status, 0x200000u)) { ok = false; break; }
         if (KW > 1) {
           uint8_t* sB = smem_gen + stage * stage_bytes + a_bytes;
