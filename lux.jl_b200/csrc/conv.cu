@@ -201,15 +201,18 @@ int32_t lb2_conv_bwd(void* dw, void* dx, void* db, const void* dy, const void* o
   float* red = reinterpret_cast<float*>(ws + lay.g_bytes);
   const int64_t S = y_spatial(g);
   const void* gptr = dy;
+  const int route = (flags & LB2_FLAG_FORCE_SIMT) ? 0 : (lay.tc_bytes > 0 ? conv_route(g, dtype) : 0);
+  // identity activation on the bf16 fast case: the filter-gradient kernel adds up dy on the side, no pass of its own
+  const bool db_by_wgrad = act == LB2_ACT_IDENTITY && db && dw && route == 1 && dtype == LB2_BF16 && aligned_to(dy, 16) &&
+                           aligned_to(x, 16) && aligned_to(dx, 16) && conv_tc_wgrad_makes_db(g, dtype);
   if (act != LB2_ACT_IDENTITY) {
     rc = launch_act_bwd(ws, db, dy, out, preact, S, g.cout, g.batch, g.cout, g.cout, g.cout, dtype, act, 0, red, st);
     if (rc != LB2_OK) return rc;
     gptr = ws;
-  } else if (db) {
+  } else if (db && !db_by_wgrad) {
     rc = launch_act_bwd(nullptr, db, dy, nullptr, nullptr, S, g.cout, g.batch, g.cout, g.cout, g.cout, dtype, act, 0, red, st);
     if (rc != LB2_OK) return rc;
   }
-  const int route = (flags & LB2_FLAG_FORCE_SIMT) ? 0 : (lay.tc_bytes > 0 ? conv_route(g, dtype) : 0);
   const bool x_is_copy = (flags & LB2_FLAG_X_COPY_GIVEN) != 0;
   LB2_REQUIRE(!x_is_copy || (route == 2 && aligned_to(x, 256)), LB2_BAD_ARG,
               "LB2_FLAG_X_COPY_GIVEN: this geometry does not run on the path that leaves a copy of x (or the pointer is not a workspace start)");
@@ -221,7 +224,7 @@ int32_t lb2_conv_bwd(void* dw, void* dx, void* db, const void* dy, const void* o
     return conv_tc_f32_bwd(dw, (dx && nx > 0) ? dx : nullptr, x, gptr, w, g, tc_ws, st);
   }
   if (dw) {
-    rc = tc ? conv_tc_wgrad(dw, x, gptr, g, dtype, tc_ws, st) : conv_wgrad_direct(dw, x, gptr, g, dtype, st);
+    rc = tc ? conv_tc_wgrad(dw, x, gptr, g, dtype, tc_ws, st, db_by_wgrad ? db : nullptr) : conv_wgrad_direct(dw, x, gptr, g, dtype, st);
     if (rc != LB2_OK) return rc;
   }
   if (dx && nx > 0) {

@@ -24,7 +24,10 @@ size_t conv_tc_bwd_workspace_bytes(const ConvGeom& g, int32_t dtype);
 int32_t conv_tc_fwd(void* y, void* preact, const void* x, const void* w, const void* bias, const ConvGeom& g,
                     int32_t dtype, int32_t act, void* ws, cudaStream_t st);
 int32_t conv_tc_dgrad(void* dx, const void* gy, const void* w, const ConvGeom& g, int32_t dtype, void* ws, cudaStream_t st);
-int32_t conv_tc_wgrad(void* dw, const void* x, const void* gy, const ConvGeom& g, int32_t dtype, void* ws, cudaStream_t st);
+// `db` (optional): also the bias gradient sum_{positions, images} gy, where conv_tc_wgrad_makes_db says the kernel can
+int32_t conv_tc_wgrad(void* dw, const void* x, const void* gy, const ConvGeom& g, int32_t dtype, void* ws, cudaStream_t st,
+                      void* db = nullptr);
+bool conv_tc_wgrad_makes_db(const ConvGeom& g, int32_t dtype);
 
 // General bf16 tensor-core path on channel-innermost copies (conv_cw.cu): any 2-D stride / padding / dilation /
 // kernel size / channel counts with groups == 1.

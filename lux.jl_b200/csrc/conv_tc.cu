@@ -618,7 +618,8 @@ __global__ void __launch_bounds__(256) conv_wgrad2_reduce_kernel(T* __restrict__
 // than interleaved blocks: consecutive blocks of a CTA share the shifted dy rows and 256-byte L2 sectors).
 // partial[z][chunk][pair][(th & 1)*64 + co][tw*64 + ci] in fp32, reduced in a fixed order afterwards. For an odd kH the
 // upper half of the last pair multiplies whatever follows the dy tiles in the stage (the first x tile); those accumulator
-// rows are never read.
+// rows are never read. With a bias gradient requested the same warps also add up the unshifted dy tile of every stage
+// (db = sum of dy over positions and images; partial sums per split, reduced with the filter gradient).
 struct ConvWg3Params {
   int32_t n_img;
   int32_t W;
@@ -628,6 +629,8 @@ struct ConvWg3Params {
   uint32_t idesc;
   uint32_t desc_hi, desc_lbo, k_advance;   // both operands K-major SW128
   float* partial;
+  float* db_partial;                // [split][64] sums of dy over the split's positions, or null
+  int32_t db_th;                    // the kernel row whose dy tile is unshifted (th = pad_h)
   unsigned int* status;
   int16_t row_shift[16];            // per kernel row th: (th - pad_h) * W
 };
@@ -757,9 +760,26 @@ conv_tc_wgrad_rows_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
     for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
       const int z = item / p.chunks;
       const int kb_lo = z * p.kb_per_split, kb_hi = min(p.kb_total, kb_lo + p.kb_per_split);
+      // bias gradient on the side: the unshifted dy tile of every stage is the split's share of dy, each element once
+      const bool with_db = p.db_partial != nullptr && item % p.chunks == 0;
+      float db_acc[2] = {0.f, 0.f};
       // main loop: the tap tiles of every stage
       for (int kb = kb_lo; kb < kb_hi; ++kb) {
         if (!mbar_wait_warp(&raw_full[stage], phase, p.status, 0x200000u)) { ok = false; break; }
+        if (with_db) {
+          const uint8_t* gt = smem_gen + stage * stage_bytes + p.db_th * TILE;
+#pragma unroll
+          for (int i = 0; i < 2; ++i) {
+            const int task = tid + i * 256;
+            const int r = task >> 3, c = task & 7;
+            const uint4 v = *reinterpret_cast<const uint4*>(gt + (r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4));
+            const uint32_t wds[4] = {v.x, v.y, v.z, v.w};
+            float sum = 0.f;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) sum += __uint_as_float(wds[k] << 16) + __uint_as_float(wds[k] & 0xFFFF0000u);
+            db_acc[i] += sum;
+          }
+        }
         if (KW > 1) {
           uint8_t* sB = smem_gen + stage * stage_bytes + a_bytes;
           const uint8_t* centre = sB + PAD * TILE;
@@ -803,6 +823,16 @@ conv_tc_wgrad_rows_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
         if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
       }
       if (!ok) break;
+      if (with_db) {   // the eight lanes of a row (chunks 0-7) are neighbours in the warp
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          float v = db_acc[i];
+          v += __shfl_xor_sync(0xffffffffu, v, 1);
+          v += __shfl_xor_sync(0xffffffffu, v, 2);
+          v += __shfl_xor_sync(0xffffffffu, v, 4);
+          if ((tid & 7) == 0) p.db_partial[z * 64 + (tid >> 3) + 32 * i] = v;
+        }
+      }
       // epilogue: the accumulators of this item
       if (!mbar_wait_warp(acc_full, acc_phase, p.status, 0x100000u)) { ok = false; break; }
       tc_fence_after();
@@ -843,8 +873,14 @@ conv_tc_wgrad_rows_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
 template <typename T>
 __global__ void __launch_bounds__(256) conv_wgrad_rows_reduce_kernel(T* __restrict__ dw, const float* __restrict__ partial,
                                                                      int kW, int kH, int cin, int cout, int flip, int chunks,
-                                                                     int pairs, int splits) {
+                                                                     int pairs, int splits, T* __restrict__ db,
+                                                                     const float* __restrict__ db_partial) {
   __shared__ float part[4][64];
+  if (db != nullptr && blockIdx.x == 0 && threadIdx.x < 64 && (int)threadIdx.x < cout) {   // db[co] = sum over splits, ascending
+    float s = 0.f;
+    for (int z = 0; z < splits; ++z) s += db_partial[z * 64 + threadIdx.x];
+    db[threadIdx.x] = from_f32<T>(s);
+  }
   const int bn = kW * 64;
   const int64_t per_split = (int64_t)chunks * pairs * 128 * bn;
   const int col = threadIdx.x & 63, zs = threadIdx.x >> 6;
@@ -1114,9 +1150,15 @@ static Wg3Plan wg3_plan(const ConvGeom& g) {
 static size_t wg3_partial_bytes(const ConvGeom& g, const Wg3Plan& w) {
   return align_up((size_t)w.splits * w.chunks * w.pairs * 128 * (g.k[0] * 64) * sizeof(float), 1024);
 }
+static size_t wg3_db_partial_bytes(const Wg3Plan& w) { return align_up((size_t)w.splits * 64 * sizeof(float), 1024); }
 static size_t wg_any_partial_bytes(const ConvGeom& g) {
   const Wg3Plan w3 = wg3_plan(g);
-  return w3.ok ? wg3_partial_bytes(g, w3) : wg2_partial_bytes(g, wg2_plan(g));
+  return w3.ok ? wg3_partial_bytes(g, w3) + wg3_db_partial_bytes(w3) : wg2_partial_bytes(g, wg2_plan(g));
+}
+
+bool conv_tc_wgrad_makes_db(const ConvGeom& g, int32_t dtype) {
+  // the unshifted dy tile must exist (0 <= pad_h < kH) and the input position blocks must cover every output position
+  return dtype == LB2_BF16 && wg3_plan(g).ok && g.pad_lo[1] >= 0 && g.pad_lo[1] < g.k[1] && g.out[1] <= g.in[1];
 }
 
 size_t conv_tc_bwd_workspace_bytes(const ConvGeom& g, int32_t dtype) {
@@ -1133,7 +1175,7 @@ int32_t conv_tc_dgrad(void* dx, const void* gy, const void* w, const ConvGeom& g
   return run_conv_gemm(dx, nullptr, nullptr, LB2_ACT_IDENTITY, gy, w, c, pack_geom(g, c, 1), static_cast<uint8_t*>(ws), st);
 }
 
-int32_t conv_tc_wgrad(void* dw, const void* x, const void* gy, const ConvGeom& g, int32_t dtype, void* ws_, cudaStream_t st) {
+int32_t conv_tc_wgrad(void* dw, const void* x, const void* gy, const ConvGeom& g, int32_t dtype, void* ws_, cudaStream_t st, void* db) {
   if (dtype == LB2_F32) return fail(LB2_BAD_ARG, "Float32 gradients are computed by conv_tc_f32_bwd");
   using T = __nv_bfloat16;
   uint8_t* ws = static_cast<uint8_t*>(ws_);
@@ -1152,6 +1194,10 @@ int32_t conv_tc_wgrad(void* dw, const void* x, const void* gy, const ConvGeom& g
     q.desc_lbo = 1u << 16;
     q.k_advance = 32u >> 4;
     q.partial = partial;
+    float* db_partial = reinterpret_cast<float*>(ws + copies_bytes(f) + wg3_partial_bytes(g, w3));
+    const bool with_db = db != nullptr && conv_tc_wgrad_makes_db(g, dtype);
+    q.db_partial = with_db ? db_partial : nullptr;
+    q.db_th = f.pad_h;
     q.status = device_status_word();
     LB2_REQUIRE(q.status != nullptr, LB2_LAUNCH_FAIL, "conv_tc: device status word unavailable");
     for (int th = 0; th < f.kH; ++th) q.row_shift[th] = (int16_t)((th - f.pad_h) * f.W);
@@ -1186,7 +1232,7 @@ int32_t conv_tc_wgrad(void* dw, const void* x, const void* gy, const ConvGeom& g
     if (rc3 != LB2_OK) return rc3;
     const int64_t per_split3 = (int64_t)w3.chunks * w3.pairs * 128 * (f.kW * 64);
     conv_wgrad_rows_reduce_kernel<T><<<(unsigned)(per_split3 / 64), 256, 0, st>>>((T*)dw, partial, g.k[0], g.k[1], g.cin, g.cout, g.flip,
-                                                                               w3.chunks, w3.pairs, w3.splits);
+                                                                               w3.chunks, w3.pairs, w3.splits, with_db ? (T*)db : nullptr, db_partial);
     LB2_CHECK_LAUNCH("conv_wgrad_rows_reduce");
     return LB2_OK;
   }

@@ -362,6 +362,9 @@ TC_CONV_CASES = [
     ((16, 6), (4, 2), 16, 16, (3, 0, 1, 0), True),
     ((16, 9), (1, 3), 128, 64, (0, 0, 1, 1), False),
     ((8, 3), (3, 3), 8, 8, 1, False),
+    # output shorter / taller than the input: the bias gradient rides on the filter-gradient kernel only in the first
+    ((16, 8), (3, 3), 16, 32, (1, 1, 0, 0), False),
+    ((16, 4), (3, 3), 16, 32, (1, 1, 2, 2), False),
 ]
 
 
