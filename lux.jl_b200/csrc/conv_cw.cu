@@ -658,6 +658,38 @@ __global__ void __launch_bounds__(64 * kCwReduceSlices) conv_cw_wgrad_reduce_ker
   dw[kw + (int64_t)g.kW * (kh + (int64_t)g.kH * (ci + (int64_t)g.cin * co))] = from_f32<T>(s);
 }
 
+// The same sum for unfolded filters (every layer but a small-channel stem), one block per (output channel, 64-channel
+// chunk of the input): the four y slices take taps y, y + 4, ..., each thread adds the splits of its (tap, input channel)
+// in ascending order from consecutive floats of the partial rows, the block collects the kW*kH x 64 values in shared
+// memory in dw's own order and writes them as ONE contiguous run of dw (the per-slot kernel above writes 2-byte elements
+// kW*kH apart and needs a block per 64 outputs: 36864 blocks of one load each for a 3x3 512->512 filter).
+template <typename T>
+__global__ void __launch_bounds__(256) conv_cw_wgrad_reduce_rows_kernel(T* __restrict__ dw, const float* __restrict__ partial,
+                                                                        const CwReduce g) {
+  extern __shared__ float cw_reduce_tile[];   // [64 input channels][taps], dw's order
+  const int taps = g.kW * g.kH;
+  const int chunk = blockIdx.x % g.chunks, co = blockIdx.x / g.chunks;
+  const int ct = co / 128, row = co % 128;
+  const int bn = g.pairs_per_group * 64;
+  const int64_t split_stride = (int64_t)g.co_tiles * g.groups * 128 * bn;
+  const int col = threadIdx.x & 63, y = threadIdx.x >> 6;
+  for (int tap = y; tap < taps; tap += 4) {
+    const int pair = tap * g.chunks + chunk;
+    const int grp = pair / g.pairs_per_group, slot = pair % g.pairs_per_group;
+    const float* src = partial + (((int64_t)(grp * g.co_tiles + ct)) * 128 + row) * bn + slot * 64 + col;
+    float s = 0.f;
+#pragma unroll 4
+    for (int z = 0; z < g.splits; ++z) s += __ldcs(src + z * split_stride);
+    const int th = tap / g.kW, tw = tap % g.kW;
+    const int kw = g.flip ? tw : g.kW - 1 - tw, kh = g.flip ? th : g.kH - 1 - th;
+    cw_reduce_tile[col * taps + kw + g.kW * kh] = s;
+  }
+  __syncthreads();
+  const int n_ci = min(64, g.cin - chunk * 64);
+  T* dst = dw + ((int64_t)co * g.cin + chunk * 64) * taps;
+  for (int e = threadIdx.x; e < n_ci * taps; e += 256) dst[e] = from_f32<T>(cw_reduce_tile[e]);
+}
+
 // ----------------------------------------------------------------------------------------------
 // host side
 // ----------------------------------------------------------------------------------------------
@@ -794,18 +826,28 @@ int32_t cw_launch_fwd(const CUtensorMap& mX, const CUtensorMap& mW, const CwFwdP
 }
 
 // sums[ch][0..1] = sum over the CTAs of column tile ch / bn (ascending block index) of their partial rows
-__global__ void __launch_bounds__(128) cw_sums_finish_kernel(float* __restrict__ sums, const float* __restrict__ partial, int grid, int tiles_n,
+__global__ void __launch_bounds__(256) cw_sums_finish_kernel(float* __restrict__ sums, const float* __restrict__ partial, int grid, int tiles_n,
                                                              int bn, int cout) {
-  const int ch = blockIdx.x * blockDim.x + threadIdx.x;
+  // one warp per channel: lane l adds the CTA rows tn + (l, l + 32, ...) * tiles_n in ascending order, the lanes are
+  // combined by a butterfly (a fixed order)
+  const int ch = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (ch >= cout) return;
   const int tn = ch / bn, j = ch % bn;
   double a = 0.0, q = 0.0;
-  for (int k = tn; k < grid; k += tiles_n) {
-    a += (double)partial[((int64_t)k * bn + j) * 2];
-    q += (double)partial[((int64_t)k * bn + j) * 2 + 1];
+  for (int k = tn + lane * tiles_n; k < grid; k += 32 * tiles_n) {
+    const float2 v = *reinterpret_cast<const float2*>(partial + ((int64_t)k * bn + j) * 2);
+    a += (double)v.x;
+    q += (double)v.y;
   }
-  sums[ch * 2] = (float)a;
-  sums[ch * 2 + 1] = (float)q;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    a += __shfl_xor_sync(0xffffffffu, a, o);
+    q += __shfl_xor_sync(0xffffffffu, q, o);
+  }
+  if (lane == 0) {
+    sums[ch * 2] = (float)a;
+    sums[ch * 2 + 1] = (float)q;
+  }
 }
 
 // One implicit-GEMM launch: grid of OW x OH x NI positions, n_out channels, the given taps of the packed filter.
@@ -843,7 +885,7 @@ int32_t cw_run_gemm(void* out, void* preact, const void* bias, int32_t act, cons
   const int32_t rc = bn == 64 ? cw_launch_fwd<64>(mX, mW, p, act, st, &grid)
                    : bn == 128 ? cw_launch_fwd<128>(mX, mW, p, act, st, &grid) : cw_launch_fwd<256>(mX, mW, p, act, st, &grid);
   if (rc != LB2_OK || sums == nullptr) return rc;
-  cw_sums_finish_kernel<<<(unsigned)((n_out + 127) / 128), 128, 0, st>>>(sums, sums_partial, grid, p.tiles_n, bn, n_out);
+  cw_sums_finish_kernel<<<(unsigned)((n_out + 7) / 8), 256, 0, st>>>(sums, sums_partial, grid, p.tiles_n, bn, n_out);
   LB2_CHECK_LAUNCH("conv_cw channel sums");
   return LB2_OK;
 }
@@ -1013,8 +1055,12 @@ int32_t conv_cw_bwd(void* dw, void* dx, const void* x, const void* gy, const voi
        : pl.ppg == 3 ? launch(conv_cw_wgrad_kernel<3>, 3) : launch(conv_cw_wgrad_kernel<4>, 4);
     if (rc != LB2_OK) return rc;
     CwReduce rd{g.k[0], g.k[1], g.cin, g.cout, g.flip, fold, pl.chunks, pl.co_tiles, pl.groups, pl.ppg, pl.splits};
-    conv_cw_wgrad_reduce_kernel<__nv_bfloat16><<<(unsigned)((int64_t)pl.groups * pl.co_tiles * 128 * pl.ppg), dim3(64, kCwReduceSlices), 0, st>>>(
-        (__nv_bfloat16*)dw, q.partial, rd);
+    if (fold == 0 && g.k[0] * g.k[1] * 64 * sizeof(float) <= 48 * 1024)
+      conv_cw_wgrad_reduce_rows_kernel<__nv_bfloat16><<<(unsigned)((int64_t)g.cout * pl.chunks), 256, g.k[0] * g.k[1] * 64 * sizeof(float), st>>>(
+          (__nv_bfloat16*)dw, q.partial, rd);
+    else
+      conv_cw_wgrad_reduce_kernel<__nv_bfloat16><<<(unsigned)((int64_t)pl.groups * pl.co_tiles * 128 * pl.ppg), dim3(64, kCwReduceSlices), 0, st>>>(
+          (__nv_bfloat16*)dw, q.partial, rd);
     LB2_CHECK_LAUNCH("conv_cw_wgrad_reduce");
   }
 
