@@ -793,7 +793,9 @@ def build_resnet18(L, torch, device, rank, batch, dtype):
         statistics come from the convolution's epilogue where the general tensor-core path runs it. Pullback
         Δ -> (∂weight, ∂x, ∂scale, ∂bias)."""
         c = params[ib].shape[0]
-        rm, rv = rstats.setdefault(ib, (torch.zeros(c, device=device, dtype=dtype), torch.ones(c, device=device, dtype=dtype)))
+        if ib not in rstats:    # running mean / variance start at 0 / 1 (created once, not per step)
+            rstats[ib] = (torch.zeros(c, device=device, dtype=dtype), torch.ones(c, device=device, dtype=dtype))
+        rm, rv = rstats[ib]
         y, new, pb = L.rrule_conv_batchnorm(act, params[ic], h, cdims, params[ib], params[ib + 1], rm, rv, 0.1, 1e-5)
         rstats[ib] = new
         return y, pb

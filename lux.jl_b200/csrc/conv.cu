@@ -124,7 +124,7 @@ int32_t lb2_conv_fwd_sums_is_fused(const lb2_conv_desc* d, int32_t dtype) {
   ConvGeom g;
   if (!valid_dtype(dtype) || make_geom(d, &g) != LB2_OK || y_numel(g) == 0) return 0;
   if (conv_route(g, dtype) != 2) return 0;
-  return (int64_t)g.k[0] * g.k[1] * ((g.cin + 63) / 64) >= 16 ? 1 : 0;
+  return conv_cw_fwd_kblocks(g) >= 16 ? 1 : 0;   // counted as the kernel runs it: a folded 7x7 stem has 4, not 49
 }
 
 size_t lb2_conv_fwd_sums_workspace_bytes(const lb2_conv_desc* d, int32_t dtype) {

@@ -32,6 +32,7 @@ bool conv_tc_wgrad_makes_db(const ConvGeom& g, int32_t dtype);
 // General bf16 tensor-core path on channel-innermost copies (conv_cw.cu): any 2-D stride / padding / dilation /
 // kernel size / channel counts with groups == 1.
 bool conv_cw_supported(const ConvGeom& g, int32_t dtype);
+int conv_cw_fwd_kblocks(const ConvGeom& g);
 size_t conv_cw_fwd_workspace_bytes(const ConvGeom& g);
 size_t conv_cw_bwd_workspace_bytes(const ConvGeom& g);
 int32_t conv_cw_fwd(void* y, void* preact, const void* x, const void* w, const void* bias, const ConvGeom& g, int32_t act,

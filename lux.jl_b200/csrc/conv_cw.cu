@@ -893,6 +893,13 @@ int32_t cw_run_gemm(void* out, void* preact, const void* bias, int32_t act, cons
 }  // namespace
 
 // ---- public (library-internal) interface ------------------------------------------------------------
+// k-blocks (64-wide contraction steps) one output tile of the forward kernel takes: taps x channel chunks, or the
+// folded tap count of a small-channel stem
+int conv_cw_fwd_kblocks(const ConvGeom& g) {
+  const int fold = cw_fold(g);
+  return fold ? cw_fold_taps(g, fold) : g.k[0] * g.k[1] * ((g.cin + 63) / 64);
+}
+
 bool conv_cw_supported(const ConvGeom& g, int32_t dtype) {
   if (dtype != LB2_BF16 || g.ndim != 2 || g.groups != 1) return false;
   if (g.out[0] <= 0 || g.out[1] <= 0 || g.batch <= 0 || g.cin <= 0 || g.cout <= 0) return false;
