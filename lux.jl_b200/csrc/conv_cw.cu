@@ -180,6 +180,49 @@ __global__ void __launch_bounds__(256) cw_pack_filter_kernel(__nv_bfloat16* __re
   }
 }
 
+// The same packing for unfolded filters, one block per (packed row, 64-channel chunk): the block's kW*kH x 64 filter
+// elements are read in the filter's own order (one contiguous run for the forward packing, 64 runs of kW*kH elements for
+// the data-gradient packing), turned in shared memory and written as kW*kH runs of 128 bytes. The flat kernel above reads
+// 2-byte elements kW*kH (forward) or kW*kH*cin (data gradient) apart.
+__global__ void __launch_bounds__(256) cw_pack_filter_rows_kernel(__nv_bfloat16* __restrict__ wp, const __nv_bfloat16* __restrict__ w,
+                                                                  const CwPack g) {
+  extern __shared__ __nv_bfloat16 cw_pack_tile[];   // [64 contracted channels][taps], the filter's (kh, kw) order
+  const int taps = g.kW * g.kH;
+  const int kc = g.transpose ? g.cout : g.cin;
+  const int nc = g.transpose ? g.cin : g.cout;
+  const int chunk = blockIdx.x % g.chunks, row = blockIdx.x / g.chunks;
+  const int n_c = row < nc ? min(64, kc - chunk * 64) : 0;
+  for (int e = threadIdx.x; e < 64 * taps; e += 256) {
+    const int c = e / taps, t = e - c * taps;
+    __nv_bfloat16 v = __float2bfloat16_rn(0.f);
+    if (c < n_c) {
+      const int64_t src = g.transpose ? ((int64_t)(chunk * 64 + c) * g.cin + row) * taps + t
+                                      : ((int64_t)row * g.cin + chunk * 64) * taps + e;
+      v = w[src];
+    }
+    cw_pack_tile[e] = v;
+  }
+  __syncthreads();
+  __nv_bfloat16* dst = wp + (int64_t)row * g.k_total + chunk * 64;
+  for (int e = threadIdx.x; e < 64 * taps; e += 256) {
+    const int tap = e >> 6, j = e & 63;
+    const int tw = tap % g.kW, th = tap / g.kW;
+    const int kw = g.flip ? tw : g.kW - 1 - tw, kh = g.flip ? th : g.kH - 1 - th;
+    dst[(int64_t)tap * g.chunks * 64 + j] = cw_pack_tile[j * taps + kh * g.kW + kw];
+  }
+}
+
+unsigned flat_grid(int64_t total);
+
+// filter packing of either kind
+static void cw_pack_filter(__nv_bfloat16* wp, const __nv_bfloat16* w, const CwPack& pk, cudaStream_t st) {
+  const size_t tile = (size_t)pk.kW * pk.kH * 64 * sizeof(__nv_bfloat16);
+  if (pk.fold == 0 && tile <= 48 * 1024)
+    cw_pack_filter_rows_kernel<<<(unsigned)((int64_t)pk.n_rows * pk.chunks), 256, tile, st>>>(wp, w, pk);
+  else
+    cw_pack_filter_kernel<<<flat_grid((int64_t)pk.n_rows * pk.k_total), 256, 0, st>>>(wp, w, pk);
+}
+
 // ----------------------------------------------------------------------------------------------
 // forward / data-gradient kernel
 // ----------------------------------------------------------------------------------------------
@@ -940,7 +983,7 @@ int32_t conv_cw_fwd(void* y, void* preact, const void* x, const void* w, const v
   const int n_taps = fold ? cw_fold_taps(g, fold) : g.k[0] * g.k[1];
   pk.n_rows = round_up(g.cout, cw_bn(g.cout));
   pk.k_total = n_taps * pk.chunks * 64;
-  cw_pack_filter_kernel<<<flat_grid((int64_t)pk.n_rows * pk.k_total), 256, 0, st>>>(wp, (const __nv_bfloat16*)w, pk);
+  cw_pack_filter(wp, (const __nv_bfloat16*)w, pk, st);
   LB2_CHECK_LAUNCH("conv_cw filter packing");
   CwTap taps[kCwMaxKb];
   for (int t = 0; t < n_taps; ++t) {
@@ -1062,7 +1105,9 @@ int32_t conv_cw_bwd(void* dw, void* dx, const void* x, const void* gy, const voi
        : pl.ppg == 3 ? launch(conv_cw_wgrad_kernel<3>, 3) : launch(conv_cw_wgrad_kernel<4>, 4);
     if (rc != LB2_OK) return rc;
     CwReduce rd{g.k[0], g.k[1], g.cin, g.cout, g.flip, fold, pl.chunks, pl.co_tiles, pl.groups, pl.ppg, pl.splits};
-    if (fold == 0 && g.k[0] * g.k[1] * 64 * sizeof(float) <= 48 * 1024)
+    // few splits = a large filter: per-(channel, chunk) blocks with contiguous writes; many splits = a small filter
+    // with little else to parallelise over: the per-slot kernel, whose y slices share the splits
+    if (fold == 0 && pl.splits <= 16 && g.k[0] * g.k[1] * 64 * sizeof(float) <= 48 * 1024)
       conv_cw_wgrad_reduce_rows_kernel<__nv_bfloat16><<<(unsigned)((int64_t)g.cout * pl.chunks), 256, g.k[0] * g.k[1] * 64 * sizeof(float), st>>>(
           (__nv_bfloat16*)dw, q.partial, rd);
     else
@@ -1080,7 +1125,7 @@ int32_t conv_cw_bwd(void* dw, void* dx, const void* x, const void* gy, const voi
     pk.chunks = (g.cout + 63) / 64;
     pk.n_rows = round_up(g.cin, cw_bn(g.cin));
     pk.k_total = g.k[0] * g.k[1] * pk.chunks * 64;
-    cw_pack_filter_kernel<<<flat_grid((int64_t)pk.n_rows * pk.k_total), 256, 0, st>>>(wp, (const __nv_bfloat16*)w, pk);
+    cw_pack_filter(wp, (const __nv_bfloat16*)w, pk, st);
     LB2_CHECK_LAUNCH("conv_cw filter packing (data gradient)");
     const int sw = g.stride[0], sh = g.stride[1];
     auto class_taps = [&](int pw, int ph, CwTap* taps) {
