@@ -16,7 +16,10 @@
 // The filter gradient (conv_tc_wgrad2_kernel) contracts over (s, image): M = 128 output channels (rows of dy),
 // N = kW*64 = the kW taps of a kernel row x 64 input channels, read from kW-1 W-shifted copies of x made by one
 // bandwidth pass (the unshifted tap comes from x itself); fp32 partials per K-split in the workspace and a
-// fixed-order reduction — deterministic.
+// fixed-order reduction — deterministic. With at most 64 output channels (conv_tc_wgrad_rows_kernel) the kernel-row shift
+// moves onto dy, two kernel rows share one 128-row MMA, and the tap tiles are cut out of the unshifted x tile in shared
+// memory, so no copies of x are made and x and dy are read once; the bias gradient of an identity-activation layer is
+// summed from the same dy tiles.
 //
 // Roofline: tensor pipe; algorithmic FLOPs = 2*Wo*Ho*N*Cout*Cin*kW*kH per pass.
 #include "conv.cuh"
