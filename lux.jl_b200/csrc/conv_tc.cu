@@ -617,8 +617,8 @@ __global__ void __launch_bounds__(256) conv_wgrad2_reduce_kernel(T* __restrict__
 // multiple of 8 and blocks start on a multiple of 64, so a row end can only fall on a chunk boundary), stored at the
 // chunk's swizzled place in the tap's tile. Operand traffic per block: (kH + 1) * 8 KB + 2 KB.
 //
-// A work item is (64-channel chunk, K split z) with one contiguous range of position blocks per split (measured faster
-// than interleaved blocks: consecutive blocks of a CTA share the shifted dy rows and 256-byte L2 sectors).
+// A work item is (64-channel chunk, K split z) with one contiguous range of position blocks per split (interleaved
+// blocks measured the same kernel time; consecutive blocks of a CTA share the shifted dy rows and 256-byte L2 sectors).
 // partial[z][chunk][pair][(th & 1)*64 + co][tw*64 + ci] in fp32, reduced in a fixed order afterwards. For an odd kH the
 // upper half of the last pair multiplies whatever follows the dy tiles in the stage (the first x tile); those accumulator
 // rows are never read. With a bias gradient requested the same warps also add up the unshifted dy tile of every stage
